@@ -1,0 +1,465 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM, operands staged in
+// shared memory by TMA, 128-byte swizzle), persistent over output tiles, warp-specialised:
+//   warp 0      : TMA producer (one elected lane)
+//   warp 1      : TMEM allocator + MMA issuer (one elected lane)
+//   warps 2..5  : epilogue (TMEM -> registers -> fused epilogue -> global)
+// TMEM holds two accumulator buffers, so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// D[M,N] = epilogue( A[M,K] * B[N,K]^T ).  Each operand is either "K-major" (the contraction
+// dimension is the contiguous one, i.e. A stored [M,K] / B stored [N,K]) or "MN-major" (stored
+// transposed, [K,M] / [K,N]).  The three combinations a linear layer needs are
+//   forward  y  = x W^T      : A K-major,  B K-major
+//   dgrad    dx = dy W       : A K-major,  B MN-major
+//   wgrad    dW = dy^T x     : A MN-major, B MN-major
+// so neither activations nor weights are ever transposed in memory.
+//
+// Replaces the reference's scalar 16x16 tiled matmul (crates/wgpu-backend/src/shaders.wgsl:571),
+// its CPU linear (crates/ndarray-backend/src/lib.rs:478) and the fused_linear_bias{,_relu,_gelu}
+// op sequences (crates/candle-backend/src/lib.rs:220-312).
+#include "gemm_tcgen05.h"
+
+#include "rb_common.cuh"
+
+namespace rb {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;   // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kNumThreads = 192;
+constexpr int kNumEpilogueWarps = 4;
+
+struct EpiParams {
+  void* d;
+  long long ldd;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  long long ldr;
+  const __nv_bfloat16* aux_in;
+  long long ld_aux_in;
+  __nv_bfloat16* aux_out;
+  long long ld_aux_out;
+  int act;
+  int out_f32;
+  int accumulate;
+  float alpha;
+};
+
+template <int BLOCK_N, int STAGES>
+struct SmemLayout {
+  static constexpr int kABytes = kBlockM * kBlockK * 2;
+  static constexpr int kBBytes = BLOCK_N * kBlockK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
+  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16;
+};
+
+// Processes 32 consecutive accumulator columns of one output row.
+__device__ __forceinline__ void epilogue_chunk(const EpiParams& ep, uint32_t (&r)[32], long long row, int col0, int N) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
+  const bool full = (col0 + 32 <= N);
+
+  if (ep.bias != nullptr) {
+    if (full) {
+      const uint4* bp = reinterpret_cast<const uint4*>(ep.bias + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 b = __ldg(bp + q);
+        float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+        v[q * 8 + 0] += f0.x; v[q * 8 + 1] += f0.y; v[q * 8 + 2] += f1.x; v[q * 8 + 3] += f1.y;
+        v[q * 8 + 4] += f2.x; v[q * 8 + 5] += f2.y; v[q * 8 + 6] += f3.x; v[q * 8 + 7] += f3.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < N) v[j] += __bfloat162float(ep.bias[col0 + j]);
+    }
+  }
+
+  if (ep.act == RB_ACT_GELU || ep.act == RB_ACT_RELU || ep.act == RB_ACT_SILU) {
+    if (ep.aux_out != nullptr) {   // keep the pre-activation for the backward pass
+      __nv_bfloat16* ap = ep.aux_out + row * ep.ld_aux_out + col0;
+      if (full) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 o;
+          o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]); o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+          o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]); o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+          reinterpret_cast<uint4*>(ap)[q] = o;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < N) ap[j] = __float2bfloat16(v[j]);
+      }
+      // the backward pass sees the bf16-rounded pre-activation; use the same value here
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __bfloat162float(__float2bfloat16(v[j]));
+    }
+    if (ep.act == RB_ACT_GELU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+    } else if (ep.act == RB_ACT_RELU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = silu(v[j]);
+    }
+  } else if (ep.act == RB_ACT_DGELU || ep.act == RB_ACT_DRELU || ep.act == RB_ACT_DSILU || ep.act == RB_ACT_MUL) {
+    // multiply by act'(aux_in) (or by aux_in itself for RB_ACT_MUL)
+    const __nv_bfloat16* ap = ep.aux_in + row * ep.ld_aux_in + col0;
+    float a[32];
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 b = __ldg(reinterpret_cast<const uint4*>(ap) + q);
+        float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+        a[q * 8 + 0] = f0.x; a[q * 8 + 1] = f0.y; a[q * 8 + 2] = f1.x; a[q * 8 + 3] = f1.y;
+        a[q * 8 + 4] = f2.x; a[q * 8 + 5] = f2.y; a[q * 8 + 6] = f3.x; a[q * 8 + 7] = f3.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) a[j] = (col0 + j < N) ? __bfloat162float(ap[j]) : 0.f;
+    }
+    if (ep.act == RB_ACT_DGELU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= gelu_tanh_grad(a[j]);
+    } else if (ep.act == RB_ACT_DRELU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = a[j] > 0.f ? v[j] : 0.f;
+    } else if (ep.act == RB_ACT_DSILU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= silu_grad(a[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= a[j];
+    }
+  }
+
+  if (ep.residual != nullptr) {
+    const __nv_bfloat16* rp = ep.residual + row * ep.ldr + col0;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 b = __ldg(reinterpret_cast<const uint4*>(rp) + q);
+        float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+        v[q * 8 + 0] += f0.x; v[q * 8 + 1] += f0.y; v[q * 8 + 2] += f1.x; v[q * 8 + 3] += f1.y;
+        v[q * 8 + 4] += f2.x; v[q * 8 + 5] += f2.y; v[q * 8 + 6] += f3.x; v[q * 8 + 7] += f3.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < N) v[j] += __bfloat162float(rp[j]);
+    }
+  }
+
+  if (ep.out_f32) {
+    float* dp = reinterpret_cast<float*>(ep.d) + row * ep.ldd + col0;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        float4 o = make_float4(v[q * 4 + 0], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+        if (ep.accumulate) {
+          float4 old = reinterpret_cast<float4*>(dp)[q];
+          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+        }
+        reinterpret_cast<float4*>(dp)[q] = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < N) dp[j] = ep.accumulate ? dp[j] + v[j] : v[j];
+    }
+  } else {
+    __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(ep.d) + row * ep.ldd + col0;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (ep.accumulate) {
+          uint4 b = reinterpret_cast<uint4*>(dp)[q];
+          float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+          v[q * 8 + 0] += f0.x; v[q * 8 + 1] += f0.y; v[q * 8 + 2] += f1.x; v[q * 8 + 3] += f1.y;
+          v[q * 8 + 4] += f2.x; v[q * 8 + 5] += f2.y; v[q * 8 + 6] += f3.x; v[q * 8 + 7] += f3.y;
+        }
+        uint4 o;
+        o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]); o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+        o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]); o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+        reinterpret_cast<uint4*>(dp)[q] = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < N) {
+          float o = v[j];
+          if (ep.accumulate) o += __bfloat162float(dp[j]);
+          dp[j] = __float2bfloat16(o);
+        }
+    }
+  }
+}
+
+template <int A_MN, int B_MN, int BLOCK_N, int STAGES>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
+                 int K, int group_m, EpiParams ep, unsigned int* status) {
+  using L = SmemLayout<BLOCK_N, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzle atoms need 1024-byte aligned tiles
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = smem_u32(bars + STAGES);
+  const uint32_t bar_tfull = smem_u32(bars + 2 * STAGES);
+  const uint32_t bar_tempty = smem_u32(bars + 2 * STAGES + 2);
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t kTmemCols = (2 * BLOCK_N < 32) ? 32 : 2 * BLOCK_N;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, kNumEpilogueWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int num_m = (M + kBlockM - 1) / kBlockM;
+  const int num_n = (N + BLOCK_N - 1) / BLOCK_N;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + kBlockK - 1) / kBlockK;
+  const int group_size = group_m * num_n;
+
+  auto decode_tile = [&](int tile, int& m_blk, int& n_blk) {
+    const int group = tile / group_size;
+    const int first_m = group * group_m;
+    const int gm = min(group_m, num_m - first_m);
+    const int in_group = tile - group * group_size;
+    m_blk = first_m + in_group % gm;
+    n_blk = in_group / gm;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int m_blk, n_blk;
+        decode_tile(tile, m_blk, n_blk);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, status, 1)) { ok = false; break; }
+          const uint32_t full = bar_full + 8 * s;
+          mbar_arrive_expect_tx(full, L::kStageBytes);
+          const uint32_t sa = smem_base + s * L::kStageBytes;
+          const uint32_t sb = sa + L::kABytes;
+          if (A_MN == 0) {
+            tma_load_2d(sa, &tmA, kb * kBlockK, m_blk * kBlockM, full);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBlockM / 64; ++j)
+              tma_load_2d(sa + j * (kBlockK * 128), &tmA, m_blk * kBlockM + j * 64, kb * kBlockK, full);
+          }
+          if (B_MN == 0) {
+            tma_load_2d(sb, &tmB, kb * kBlockK, n_blk * BLOCK_N, full);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_N / 64; ++j)
+              tma_load_2d(sb + j * (kBlockK * 128), &tmB, n_blk * BLOCK_N + j * 64, kb * kBlockK, full);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer
+      constexpr uint32_t idesc = umma_idesc_bf16(kBlockM, BLOCK_N, A_MN, B_MN);
+      uint32_t it = 0, t = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+        const uint32_t acc = t & 1, acc_ph = (t >> 1) & 1;
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, status, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, status, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * L::kStageBytes;
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            // K-major: 32 bytes per UMMA_K step inside the swizzle row; 8-row groups 1024 B apart.
+            // MN-major: 16 k-rows of 128 B per step; 64-wide MN atoms kBlockK*128 B apart.
+            const uint64_t da = A_MN ? umma_smem_desc_sw128(sa + k * (kUmmaK * 128), kBlockK * 128, 1024)
+                                     : umma_smem_desc_sw128(sa + k * (kUmmaK * 2), 16, 1024);
+            const uint64_t db = B_MN ? umma_smem_desc_sw128(sb + k * (kUmmaK * 128), kBlockK * 128, 1024)
+                                     : umma_smem_desc_sw128(sb + k * (kUmmaK * 2), 16, 1024);
+            umma_bf16_ss(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * s);   // frees the smem stage once these MMAs have read it
+        }
+        if (ok) umma_commit(bar_tfull + 8 * acc);   // accumulator complete
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- epilogue warps
+    const int q = warp & 3;   // TMEM lane quarter this warp may read
+    uint32_t t = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+      int m_blk, n_blk;
+      decode_tile(tile, m_blk, n_blk);
+      const uint32_t acc = t & 1, acc_ph = (t >> 1) & 1;
+      if (!mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, status, 4)) break;
+      tc_fence_after();
+      const long long row = static_cast<long long>(m_blk) * kBlockM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (c == BLOCK_N / 32 - 1) {
+          // all of this warp's accumulator reads are done: hand the buffer back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+        }
+        const int col0 = n_blk * BLOCK_N + c * 32;
+        if (row < M && col0 < N) epilogue_chunk(ep, r, row, col0, N);
+      }
+    }
+  }
+
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      // give copies and MMAs that are still in flight time to land before TMEM is released
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace rb
+
+// ---------------------------------------------------------------------------------------------
+// host launcher
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+template <int A_MN, int B_MN, int BLOCK_N, int STAGES>
+int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, int grid, cudaStream_t stream) {
+  using L = rb::SmemLayout<BLOCK_N, STAGES>;
+  auto kern = rb::gemm_bf16_kernel<A_MN, B_MN, BLOCK_N, STAGES>;
+  const int smem = L::kTotal + 1024;
+  static bool configured = false;   // per instantiation
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  rb::EpiParams ep;
+  ep.d = g.d; ep.ldd = g.ldd;
+  ep.bias = reinterpret_cast<const __nv_bfloat16*>(g.bias);
+  ep.residual = reinterpret_cast<const __nv_bfloat16*>(g.residual); ep.ldr = g.ldr;
+  ep.aux_in = reinterpret_cast<const __nv_bfloat16*>(g.aux_in); ep.ld_aux_in = g.ld_aux_in;
+  ep.aux_out = reinterpret_cast<__nv_bfloat16*>(g.aux_out); ep.ld_aux_out = g.ld_aux_out;
+  ep.act = g.act; ep.out_f32 = g.out_f32; ep.accumulate = g.accumulate; ep.alpha = g.alpha;
+  const int group_m = g.group_m > 0 ? g.group_m : 8;
+  kern<<<grid, rb::kNumThreads, smem, stream>>>(*ta, *tb, g.M, g.N, g.K, group_m, ep, rbhost::status_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int BLOCK_N, int STAGES>
+int dispatch_major(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, int grid, cudaStream_t s) {
+  if (!g.a_mn_major && !g.b_mn_major) return launch<0, 0, BLOCK_N, STAGES>(g, ta, tb, grid, s);
+  if (!g.a_mn_major && g.b_mn_major) return launch<0, 1, BLOCK_N, STAGES>(g, ta, tb, grid, s);
+  if (g.a_mn_major && g.b_mn_major) return launch<1, 1, BLOCK_N, STAGES>(g, ta, tb, grid, s);
+  return launch<1, 0, BLOCK_N, STAGES>(g, ta, tb, grid, s);
+}
+
+int pick_block_n(int M, int N, int sms) {
+  // cost model: waves x tile width; wider tiles are preferred on a tie (fewer operand re-reads)
+  const int cands[3] = {256, 128, 64};
+  long long best_cost = -1;
+  int best = 128;
+  const long long num_m = (M + 127) / 128;
+  for (int c = 0; c < 3; ++c) {
+    const int bn = cands[c];
+    if (bn > 64 && N <= bn / 2) continue;
+    const long long tiles = num_m * ((N + bn - 1) / bn);
+    const long long waves = (tiles + sms - 1) / sms;
+    // a 64-wide tile runs at roughly 0.6x, a 128-wide at 0.9x the MMA efficiency of a 256-wide one
+    const long long cost = waves * bn * (bn == 256 ? 100 : (bn == 128 ? 108 : 150));
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
+}  // namespace
+
+RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
+  const RbGemmArgs& g = *args;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return -1;
+  // TMA needs 16-byte aligned bases and pitches
+  if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15) || (g.lda & 7) ||
+      (g.ldb & 7))
+    return -2;
+  // vector epilogue accesses need 16-byte aligned rows
+  const int dalign = g.out_f32 ? 4 : 8;
+  if ((g.ldd % dalign) || (reinterpret_cast<uintptr_t>(g.d) & 15)) return -3;
+  if (g.residual && ((g.ldr & 7) || (reinterpret_cast<uintptr_t>(g.residual) & 15))) return -3;
+  if (g.aux_in && ((g.ld_aux_in & 7) || (reinterpret_cast<uintptr_t>(g.aux_in) & 15))) return -3;
+  if (g.aux_out && ((g.ld_aux_out & 7) || (reinterpret_cast<uintptr_t>(g.aux_out) & 15))) return -3;
+  if (g.bias && (reinterpret_cast<uintptr_t>(g.bias) & 15)) return -3;
+  if ((g.act >= RB_ACT_DGELU && g.act <= RB_ACT_MUL) && !g.aux_in) return -4;
+
+  const int sms = rbhost::device_sm_count();
+  int bn = g.block_n;
+  if (bn != 64 && bn != 128 && bn != 256) bn = pick_block_n(g.M, g.N, sms);
+
+  int err = 0;
+  const CUtensorMap* ta = g.a_mn_major
+                              ? rbhost::get_tmap_2d(g.a, 2, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, 64, 64, 1, &err)
+                              : rbhost::get_tmap_2d(g.a, 2, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, 64, 128, 1, &err);
+  if (!ta) return err ? err : -5;
+  const CUtensorMap* tb = g.b_mn_major
+                              ? rbhost::get_tmap_2d(g.b, 2, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, 64, 1, &err)
+                              : rbhost::get_tmap_2d(g.b, 2, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, 64, (uint32_t)bn, 1, &err);
+  if (!tb) return err ? err : -5;
+
+  const long long tiles = (long long)((g.M + 127) / 128) * ((g.N + bn - 1) / bn);
+  int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;
+  switch (bn) {
+    case 256: return dispatch_major<256, 4>(g, ta, tb, grid, stream);
+    case 128: return dispatch_major<128, 6>(g, ta, tb, grid, stream);
+    default: return dispatch_major<64, 8>(g, ta, tb, grid, stream);
+  }
+}

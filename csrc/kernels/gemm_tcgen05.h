@@ -1,0 +1,44 @@
+// C interface of the tcgen05 bf16 GEMM (see gemm_tcgen05.cu).  Plain C so that it can be bound
+// with ctypes; every pointer is a device pointer.
+#pragma once
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum RbAct {
+  RB_ACT_NONE = 0,
+  RB_ACT_GELU = 1,    // tanh-approximated GELU (the reference's definition, crates/ndarray-backend/src/lib.rs:565)
+  RB_ACT_RELU = 2,
+  RB_ACT_SILU = 3,
+  RB_ACT_DGELU = 4,   // multiply the result by gelu'(aux_in)
+  RB_ACT_DRELU = 5,   // zero the result where aux_in <= 0
+  RB_ACT_DSILU = 6,   // multiply the result by silu'(aux_in)
+  RB_ACT_MUL = 7      // multiply the result by aux_in
+};
+
+typedef struct RbGemmArgs {
+  const void* a;        // bf16; K-major: [M,K] pitch lda; MN-major: [K,M] pitch lda
+  const void* b;        // bf16; K-major: [N,K] pitch ldb; MN-major: [K,N] pitch ldb
+  void* d;              // [M,N] pitch ldd, bf16 or fp32
+  const void* bias;     // bf16 [N] or NULL, added before the activation
+  const void* residual; // bf16 [M,N] pitch ldr or NULL, added after the activation
+  const void* aux_in;   // bf16 [M,N] pitch ld_aux_in, operand of the RB_ACT_D* / RB_ACT_MUL epilogues
+  void* aux_out;        // bf16 [M,N] pitch ld_aux_out or NULL: receives the pre-activation
+  long long lda, ldb, ldd, ldr, ld_aux_in, ld_aux_out;
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  int act;              // RbAct
+  int out_f32;          // 1: d is fp32
+  int accumulate;       // 1: d += result
+  float alpha;          // scales the accumulator before everything else
+  int block_n;          // 0 = choose; else 64 / 128 / 256
+  int group_m;          // 0 = default (8): M-tiles per rasterisation group
+  int max_ctas;         // 0 = one per SM; else cap on the persistent grid
+} RbGemmArgs;
+
+// Returns 0 on success, a negative code for rejected arguments, a positive cudaError otherwise.
+int rb_gemm_bf16(const RbGemmArgs* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

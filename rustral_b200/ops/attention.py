@@ -1,0 +1,108 @@
+"""Flash attention (causal / full, MHA / GQA) with a differentiable wrapper and a plain reference."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import _native as N
+
+
+def attention_reference(q, k, v, causal: bool, scale: float | None = None):
+    """fp32 softmax(QK^T * scale + mask) V on [B, S, H, D] tensors (GQA: fewer K/V heads)."""
+    B, Sq, H, D = q.shape
+    Sk, Hk = k.shape[1], k.shape[2]
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(H // Hk, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(H // Hk, dim=1)
+    s = qf @ kf.transpose(-1, -2) * scale
+    if causal:
+        i = torch.arange(Sq, device=q.device)[:, None] + (Sk - Sq)
+        j = torch.arange(Sk, device=q.device)[None, :]
+        s = s.masked_fill(j > i, float("-inf"))
+    p = torch.softmax(s, -1)
+    return (p @ vf).permute(0, 2, 1, 3).to(q.dtype)
+
+
+def _strides3(t):
+    # [B, S, H, D] view -> element strides (batch, row, head)
+    return (t.stride(0), t.stride(1), t.stride(2))
+
+
+def _fill(args, q, k, v, o, causal, scale):
+    B, Sq, H, D = q.shape
+    args.q, args.k, args.v, args.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("o_strides", o)):
+        st = _strides3(t)
+        arr = getattr(args, name)
+        arr[0], arr[1], arr[2] = st
+    args.batch, args.heads, args.kv_heads = B, H, k.shape[2]
+    args.seq_q, args.seq_k, args.head_dim = Sq, k.shape[1], D
+    args.causal, args.scale = int(causal), scale
+
+
+def attention_forward(q, k, v, causal: bool, scale: float, out=None, want_lse: bool = True):
+    """q: [B, Sq, H, D]; k, v: [B, Sk, Hkv, D] (any strides with a contiguous D).  Returns (o, lse)."""
+    B, Sq, H, D = q.shape
+    for t in (q, k, v):
+        if t.dtype != torch.bfloat16 or t.stride(3) != 1:
+            raise TypeError("attention: bf16 tensors with a contiguous head dimension are required")
+    o = out if out is not None else torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device) if want_lse else None
+    a = N.RbAttnArgs()
+    _fill(a, q, k, v, o, causal, scale)
+    a.lse = N.ptr(lse)
+    N.check(N.kernels().rb_attention_fwd(a, N.stream_ptr()), "rb_attention_fwd")
+    return o, lse
+
+
+def attention_backward(do, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None):
+    B, Sq, H, D = q.shape
+    if do.stride(3) != 1 or _strides3(do) != _strides3(o):
+        do = _match(do, o)
+    dq = dq if dq is not None else torch.empty_like(q)
+    dk = dk if dk is not None else torch.empty_like(k)
+    dv = dv if dv is not None else torch.empty_like(v)
+    delta = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+    a = N.RbAttnArgs()
+    _fill(a, q, k, v, o, causal, scale)
+    a.d_o = do.data_ptr()
+    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    for name, t in (("dq_strides", dq), ("dk_strides", dk), ("dv_strides", dv)):
+        st = _strides3(t)
+        arr = getattr(a, name)
+        arr[0], arr[1], arr[2] = st
+    a.lse, a.delta = lse.data_ptr(), delta.data_ptr()
+    N.check(N.kernels().rb_attention_bwd(a, N.stream_ptr()), "rb_attention_bwd")
+    return dq, dk, dv
+
+
+def _match(do, o):
+    """A copy of `do` laid out with the strides of `o` (the kernel reads both with one stride set)."""
+    buf = torch.empty_strided(o.shape, o.stride(), dtype=do.dtype, device=do.device)
+    buf.copy_(do)
+    return buf
+
+
+class _FlashFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        o, lse = attention_forward(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = attention_backward(do, q, k, v, o, lse, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def flash_attention(q, k, v, causal: bool = True, scale: float | None = None):
+    """Differentiable attention on [B, S, H, D] tensors.  CUDA: tiled flash kernels; CPU: reference math."""
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if not q.is_cuda:
+        return attention_reference(q, k, v, causal, scale)
+    return _FlashFn.apply(q, k, v, causal, scale)

@@ -1,0 +1,172 @@
+"""bf16 GEMM with fused epilogues on the tcgen05 kernel; fp32 torch math for CPU tensors.
+
+``gemm(a, b)`` computes ``D[M,N] = epilogue(alpha * A[M,K] @ B[N,K]^T)``.  ``a_mn`` / ``b_mn`` say that
+the operand is handed over transposed (``[K,M]`` / ``[K,N]``), which is how the backward GEMMs of a
+linear layer read activations and weights without a transpose in memory.
+
+Epilogue order: ``+ bias`` -> activation (or multiply by ``act'(aux_in)``) -> ``+ residual`` ->
+``+ D`` when ``accumulate``.  ``aux_out`` receives the pre-activation for the backward pass.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import _native as N
+
+_ACT_FWD = {"gelu", "relu", "silu"}
+_ACT_BWD = {"dgelu", "drelu", "dsilu", "mul"}
+
+
+def _gelu_tanh(x):
+    return 0.5 * x * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * x ** 3)))
+
+
+def _gelu_tanh_grad(x):
+    k0, k1 = math.sqrt(2.0 / math.pi), 0.044715
+    u = k0 * (x + k1 * x ** 3)
+    t = torch.tanh(u)
+    return 0.5 * (1 + t) + 0.5 * x * (1 - t * t) * k0 * (1 + 3 * k1 * x * x)
+
+
+def act_reference(name: str, x: torch.Tensor) -> torch.Tensor:
+    if name == "gelu":
+        return _gelu_tanh(x)
+    if name == "relu":
+        return torch.relu(x)
+    if name == "silu":
+        return x * torch.sigmoid(x)
+    return x
+
+
+def act_grad_reference(name: str, x: torch.Tensor) -> torch.Tensor:
+    if name == "gelu":
+        return _gelu_tanh_grad(x)
+    if name == "relu":
+        return (x > 0).to(x.dtype)
+    if name == "silu":
+        s = torch.sigmoid(x)
+        return s * (1 + x * (1 - s))
+    return torch.ones_like(x)
+
+
+def _gemm_cpu(a, b, a_mn, b_mn, bias, act, residual, aux_in, aux_out, out, out_dtype, accumulate, alpha):
+    A = a.float().t() if a_mn else a.float()
+    B = b.float().t() if b_mn else b.float()
+    v = alpha * (A @ B.t())
+    if bias is not None:
+        v = v + bias.float()
+    if act in _ACT_FWD:
+        if aux_out is not None:
+            aux_out.copy_(v.to(aux_out.dtype))
+            v = aux_out.float()
+        v = act_reference(act, v)
+    elif act in _ACT_BWD:
+        ax = aux_in.float()
+        v = v * (ax if act == "mul" else act_grad_reference(act[1:], ax))
+    if residual is not None:
+        v = v + residual.float()
+    if out is None:
+        out = torch.empty(v.shape, dtype=out_dtype, device=a.device)
+        accumulate = False
+    if accumulate:
+        out.copy_((out.float() + v).to(out.dtype))
+    else:
+        out.copy_(v.to(out.dtype))
+    return out
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, act: str = "none",
+         residual=None, aux_in=None, aux_out=None, out=None, out_dtype=None, accumulate: bool = False,
+         alpha: float = 1.0, block_n: int = 0, group_m: int = 0, max_ctas: int = 0) -> torch.Tensor:
+    assert a.dim() == 2 and b.dim() == 2
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    Nn, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"gemm: contraction sizes differ ({K} vs {Kb})")
+    if out is not None:
+        out_dtype = out.dtype
+    elif out_dtype is None:
+        out_dtype = a.dtype if a.dtype in (torch.bfloat16, torch.float32) else torch.float32
+    if act not in N.ACT:
+        raise ValueError(f"gemm: unknown epilogue activation {act!r}")
+    if not a.is_cuda:
+        return _gemm_cpu(a, b, a_mn, b_mn, bias, act, residual, aux_in, aux_out, out, out_dtype, accumulate, alpha)
+
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm: CUDA operands must be bf16 (accumulation is fp32)")
+    if a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("gemm: operands must have a contiguous last dimension")
+    if out is None:
+        out = torch.empty((M, Nn), dtype=out_dtype, device=a.device)
+        accumulate = False
+    if out.stride(1) != 1 or out.shape != (M, Nn):
+        raise ValueError("gemm: bad output tensor")
+    for t, nm in ((bias, "bias"), (residual, "residual"), (aux_in, "aux_in"), (aux_out, "aux_out")):
+        if t is not None and t.dtype != torch.bfloat16:
+            raise TypeError(f"gemm: {nm} must be bf16")
+    g = N.RbGemmArgs()
+    g.a, g.b, g.d = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    g.bias = N.ptr(bias)
+    g.residual = N.ptr(residual)
+    g.aux_in = N.ptr(aux_in)
+    g.aux_out = N.ptr(aux_out)
+    g.lda, g.ldb, g.ldd = a.stride(0), b.stride(0), out.stride(0)
+    g.ldr = residual.stride(0) if residual is not None else 0
+    g.ld_aux_in = aux_in.stride(0) if aux_in is not None else 0
+    g.ld_aux_out = aux_out.stride(0) if aux_out is not None else 0
+    g.M, g.N, g.K = M, Nn, K
+    g.a_mn_major, g.b_mn_major = int(a_mn), int(b_mn)
+    g.act = N.ACT[act]
+    g.out_f32 = int(out.dtype == torch.float32)
+    g.accumulate = int(accumulate)
+    g.alpha = alpha
+    g.block_n, g.group_m, g.max_ctas = block_n, group_m, max_ctas
+    N.check(N.kernels().rb_gemm_bf16(g, N.stream_ptr()), "rb_gemm_bf16")
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = act(x W^T + b) (+ residual); W is [out, in] as in the reference's Linear (crates/nn/src/linear.rs:21)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, act, residual):
+        x2 = x.reshape(-1, x.shape[-1])
+        need_pre = act in _ACT_FWD and (x.requires_grad or w.requires_grad)
+        pre = torch.empty((x2.shape[0], w.shape[0]), dtype=x.dtype, device=x.device) if need_pre else None
+        res2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
+        y = gemm(x2, w, bias=bias, act=act, residual=res2, aux_out=pre, out_dtype=x.dtype)
+        ctx.save_for_backward(x2, w, pre)
+        ctx.act = act
+        ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
+        ctx.x_shape = x.shape
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, pre = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dres = dy if ctx.has_res else None
+        if ctx.act in _ACT_FWD:
+            from .elementwise import unary_bwd
+            dz = unary_bwd(ctx.act, pre, dy2)
+        else:
+            dz = dy2
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dz, w, b_mn=True, out_dtype=x2.dtype).reshape(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dz, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            from .elementwise import sum_dim0
+            db = sum_dim0(dz).to(w.dtype)
+        return dx, dw, db, None, dres
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias=None, act: str = "none", residual=None) -> torch.Tensor:
+    """Differentiable fused linear: ``act(x @ w.T + bias) + residual``."""
+    return _LinearFn.apply(x, w, bias, act, residual)

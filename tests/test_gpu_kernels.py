@@ -1,0 +1,203 @@
+"""Numerics of the non-GEMM sm_100a kernels against the fp32 reference path of the same ops (CPU tensors)."""
+import math
+
+import pytest
+import torch
+
+from rustral_b200 import ops
+from rustral_b200.ops import norm as norm_ops
+from rustral_b200.ops import attention as attn_ops
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16)
+
+
+def _close(out, ref, tol=2e-2, what=""):
+    out, ref = out.float().cpu(), ref.float().cpu()
+    err = (out - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err <= tol * scale, f"{what}: max abs err {err:.4g} vs scale {scale:.4g}"
+
+
+@pytest.mark.parametrize("rows,n", [(7, 64), (33, 768), (128, 1000), (5, 2048), (9, 4096), (3, 8192), (1024, 768)])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_fwd_bwd(rows, n, rms, cuda_status):
+    x, g, b, dy, dres = _bf((rows, n), 1), _bf((n,), 2) + 1, _bf((n,), 3), _bf((rows, n), 4), _bf((rows, n), 5)
+    beta = None if rms else b
+    yc, mc, rc = norm_ops.norm_forward(x, g, beta, 1e-5, rms)
+    yg, mg, rg = norm_ops.norm_forward(x.cuda(), g.cuda(), None if rms else b.cuda(), 1e-5, rms)
+    _close(yg, yc, what="y")
+    _close(rg, rc, tol=1e-3, what="rstd")
+    dxc, dgc, dbc = norm_ops.norm_backward(dy, x, g, mc, rc, rms, dres=dres)
+    dxg, dgg, dbg = norm_ops.norm_backward(dy.cuda(), x.cuda(), g.cuda(), mg, rg, rms, dres=dres.cuda())
+    _close(dxg, dxc, what="dx")
+    _close(dgg, dgc, tol=1e-2, what="dgamma")
+    if not rms:
+        _close(dbg, dbc, tol=1e-2, what="dbeta")
+    # run-twice determinism of the parameter gradients
+    _, dgg2, _ = norm_ops.norm_backward(dy.cuda(), x.cuda(), g.cuda(), mg, rg, rms, dres=dres.cuda())
+    assert torch.equal(dgg, dgg2)
+
+
+@pytest.mark.parametrize("rows,n_valid,n_pad", [(5, 10, 16), (64, 1000, 1000), (16, 50257, 50304), (3, 37, 37)])
+def test_cross_entropy(rows, n_valid, n_pad, cuda_status):
+    logits = _bf((rows, n_pad), 1, 2.0)
+    t = torch.randint(0, n_valid, (rows,), generator=torch.Generator().manual_seed(2))
+    t[0] = -100
+    lc, lsec, gc = ops.cross_entropy_fwd_bwd(logits, t, n_valid, 0.25)
+    lg, lseg, gg = ops.cross_entropy_fwd_bwd(logits.cuda(), t.cuda(), n_valid, 0.25)
+    _close(lg, lc, tol=1e-3, what="loss")
+    _close(lseg, lsec, tol=1e-3, what="lse")
+    _close(gg, gc, tol=2e-2, what="dlogits")
+    assert gg[:, n_valid:].abs().sum().item() == 0
+    # in-place variant
+    l2 = logits.cuda().clone()
+    ops.cross_entropy_fwd_bwd(l2, t.cuda(), n_valid, 0.25, dlogits=l2)
+    assert torch.equal(l2, gg)
+
+
+def test_softmax_rows(cuda_status):
+    x = torch.randn(17, 333)
+    for fn in (ops.softmax, ops.log_softmax):
+        xc = x.clone().requires_grad_()
+        xg = x.cuda().requires_grad_()
+        yc, yg = fn(xc), fn(xg)
+        _close(yg, yc, tol=1e-5, what=fn.__name__)
+        w = torch.randn(17, 333)
+        (yc * w).sum().backward()
+        (yg * w.cuda()).sum().backward()
+        _close(xg.grad, xc.grad, tol=1e-4, what=fn.__name__ + " grad")
+
+
+@pytest.mark.parametrize("B,S,H,Hk,D,causal", [(2, 128, 4, 4, 64, True), (1, 200, 3, 3, 64, True),
+                                               (2, 96, 4, 2, 64, False), (1, 256, 4, 1, 128, True),
+                                               (1, 77, 2, 2, 128, False), (2, 1024, 2, 2, 64, True)])
+def test_flash_attention_fwd_bwd(B, S, H, Hk, D, causal, cuda_status):
+    q, k, v = _bf((B, S, H, D), 1), _bf((B, S, Hk, D), 2), _bf((B, S, Hk, D), 3)
+    do = _bf((B, S, H, D), 4)
+    qc, kc, vc = (t.float().requires_grad_() for t in (q, k, v))
+    oc = attn_ops.attention_reference(qc, kc, vc, causal)
+    (oc * do.float()).sum().backward()
+    qg, kg, vg = (t.cuda().requires_grad_() for t in (q, k, v))
+    og = ops.flash_attention(qg, kg, vg, causal)
+    (og.float() * do.cuda().float()).sum().backward()
+    _close(og, oc, what="o")
+    _close(qg.grad, qc.grad, tol=3e-2, what="dq")
+    _close(kg.grad, kc.grad, tol=3e-2, what="dk")
+    _close(vg.grad, vc.grad, tol=3e-2, what="dv")
+
+
+def test_flash_attention_packed_qkv(cuda_status):
+    # q, k, v as strided views of one [B, S, 3*H*D] projection output, gradients written packed
+    B, S, H, D = 2, 192, 3, 64
+    qkv = _bf((B, S, 3 * H * D), 7).cuda()
+    q, k, v = (qkv[:, :, i * H * D:(i + 1) * H * D].view(B, S, H, D) for i in range(3))
+    o, lse = attn_ops.attention_forward(q, k, v, True, 1 / math.sqrt(D))
+    ref = attn_ops.attention_reference(q.cpu(), k.cpu(), v.cpu(), True)
+    _close(o, ref, what="o packed")
+    do = _bf((B, S, H, D), 8).cuda()
+    dqkv = torch.zeros_like(qkv)
+    dq, dk, dv = (dqkv[:, :, i * H * D:(i + 1) * H * D].view(B, S, H, D) for i in range(3))
+    attn_ops.attention_backward(do, q, k, v, o, lse, True, 1 / math.sqrt(D), dq=dq, dk=dk, dv=dv)
+    qc, kc, vc = (t.cpu().float().requires_grad_() for t in (q, k, v))
+    (attn_ops.attention_reference(qc, kc, vc, True) * do.cpu().float()).sum().backward()
+    _close(dq, qc.grad, tol=3e-2, what="dq packed")
+    _close(dk, kc.grad, tol=3e-2, what="dk packed")
+    _close(dv, vc.grad, tol=3e-2, what="dv packed")
+
+
+def test_embedding_fwd_bwd(cuda_status):
+    V, Dm, B, S = 1000, 64, 4, 32
+    wte, wpe = _bf((V, Dm), 1), _bf((S, Dm), 2)
+    ids = torch.randint(0, 50, (B * S,), generator=torch.Generator().manual_seed(3))   # many duplicates
+    yc = ops.embedding_forward(ids, wte, wpe, S)
+    yg = ops.embedding_forward(ids.cuda(), wte.cuda(), wpe.cuda(), S)
+    _close(yg, yc, tol=1e-2)
+    dy = _bf((B * S, Dm), 4)
+    dwc, dpc = torch.zeros(V, Dm), torch.zeros(S, Dm)
+    ops.embedding_backward(ids, dy, dwc, dpc, S)
+    dwg, dpg = torch.zeros(V, Dm, device="cuda"), torch.zeros(S, Dm, device="cuda")
+    ops.embedding_backward(ids.cuda(), dy.cuda(), dwg, dpg, S)
+    _close(dwg, dwc, tol=1e-4, what="dwte")
+    _close(dpg, dpc, tol=1e-4, what="dwpe")
+    dwg2 = torch.zeros(V, Dm, device="cuda")
+    ops.embedding_backward(ids.cuda(), dy.cuda(), dwg2, None, S)
+    assert torch.equal(dwg, dwg2)
+
+
+def test_adam_and_sgd(cuda_status):
+    n = 10007
+    torch.manual_seed(0)
+    p, g = torch.randn(n), torch.randn(n)
+    for decoupled in (True, False):
+        pc, mc, vc = p.clone(), torch.zeros(n), torch.zeros(n)
+        pg, mg, vg = p.cuda(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+        lowp = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        for step in (1, 2, 3):
+            kw = dict(lr=1e-2, weight_decay=0.1, step=step, decoupled=decoupled, grad_scale=0.5)
+            ops.adam_step(pc, mc, vc, g, **kw)
+            ops.adam_step(pg, mg, vg, g.cuda(), p_lowp=lowp, **kw)
+        _close(pg, pc, tol=1e-5, what="adam p")
+        _close(lowp, pc, tol=1e-2, what="adam bf16 copy")
+    # clipping and overflow skip decided on the device
+    pg = p.cuda()
+    gn = ops.optim.sqrt_scalar(ops.sumsq(g.cuda()))
+    _close(gn, g.norm(), tol=1e-5)
+    inf = torch.ones((), dtype=torch.int32, device="cuda")
+    before = pg.clone()
+    ops.adam_step(pg, torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda"), g.cuda(), lr=1e-2, step=1,
+                  found_inf=inf)
+    assert torch.equal(pg, before)
+    pc2, pg2 = p.clone(), p.cuda()
+    ops.sgd_step(pc2, g, lr=0.1, momentum=0.9, weight_decay=0.01, mom=torch.zeros(n))
+    ops.sgd_step(pg2, g.cuda(), lr=0.1, momentum=0.9, weight_decay=0.01, mom=torch.zeros(n, device="cuda"))
+    _close(pg2, pc2, tol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_elementwise_family(dtype, cuda_status):
+    torch.manual_seed(1)
+    a = (torch.rand(37, 53) + 0.5).to(dtype)
+    b = (torch.rand(37, 53) + 0.5).to(dtype)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    for op in ("add", "mul", "sub", "div", "maximum"):
+        _close(ops.binary(op, a.cuda(), b.cuda()), ops.binary(op, a, b), tol, op)
+    for op in ("relu", "sigmoid", "tanh", "exp", "log", "sqrt", "neg", "gelu", "silu"):
+        _close(ops.unary(op, (a - 1).cuda() if op in ("relu", "gelu", "silu", "tanh") else a.cuda()),
+               ops.unary(op, (a - 1) if op in ("relu", "gelu", "silu", "tanh") else a), tol, op)
+    for op in ("add_scalar", "mul_scalar", "gt_scalar", "fill"):
+        _close(ops.scalar_op(op, a.cuda(), 0.75), ops.scalar_op(op, a, 0.75), tol, op)
+    for op in ("relu", "gelu", "silu", "sigmoid", "tanh"):
+        _close(ops.unary_bwd(op, (a - 1).cuda(), b.cuda()), ops.unary_bwd(op, a - 1, b), tol, "d" + op)
+    _close(ops.add_row_vector(a.cuda(), b[0].cuda()), ops.add_row_vector(a, b[0]), tol)
+    _close(ops.sum_dim0(a.cuda()), ops.sum_dim0(a), 1e-4)
+    _close(ops.sum_all(a.cuda()), ops.sum_all(a), 1e-4)
+    _close(ops.transpose2d(a.cuda()), a.t(), 0)
+    idx = torch.tensor([3, 0, 36, 3])
+    _close(ops.gather_rows(a.cuda(), idx.cuda()), a[idx], 0)
+    out = torch.zeros(40, 53, dtype=dtype, device="cuda")
+    ops.scatter_rows(a[:3].cuda(), torch.tensor([5, 7, 9]).cuda(), out)
+    assert torch.equal(out[[5, 7, 9]].cpu(), a[:3])
+    _close(ops.broadcast_to(a[:1].cuda(), 6, 53), a[:1].expand(6, 53), 0)
+    _close(ops.apply_mask(a.cuda(), (b > 1).to(dtype).cuda(), -1e9), torch.where(b > 1, a, torch.full_like(a, -1e9)), 0)
+    assert torch.equal(ops.argmax_rows(a.cuda()).cpu(), a.float().argmax(-1))
+    big = torch.randn(3000, 40).to(dtype)
+    _close(ops.sum_dim0(big.cuda()), big.float().sum(0), 1e-3)
+
+
+def test_dropout(cuda_status):
+    x = torch.ones(100000)
+    y, mask = ops.dropout(x.cuda(), 0.3, True, seed=5, return_mask=True)
+    keep = mask.float().mean().item()
+    assert abs(keep - 0.7) < 0.01
+    assert torch.allclose(y[mask.bool()], torch.full_like(y[mask.bool()], 1 / 0.7))
+    y2 = ops.dropout(x.cuda(), 0.3, True, seed=5)
+    assert torch.equal(y, y2)
+    # PCG-hash generator: identical keep mask on host and device
+    yp, mp = ops.dropout(x.cuda(), 0.25, True, seed=123, rng="pcg", return_mask=True)
+    from rustral_b200.ops.elementwise import dropout_mask_reference
+    assert torch.equal(mp.bool().cpu(), dropout_mask_reference(100000, 0.25, 123))
