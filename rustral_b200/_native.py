@@ -198,7 +198,15 @@ def ptr(t) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+# Kernel launches issued per native entry point (entries not listed launch one kernel).
+_LAUNCHES = {"rb_norm_bwd": 2, "rb_sumsq": 2, "rb_sum_all": 2, "rb_sum_dim0_staged": 2, "rb_attention_bwd": 3,
+             "rb_embedding_bwd": 5, "rb_status_read": 0}
+launch_count = 0
+
+
 def check(code: int, what: str) -> None:
+    global launch_count
+    launch_count += _LAUNCHES.get(what, 1)
     if code != 0:
         if code > 0:
             raise NativeError(f"{what}: CUDA error {code}")

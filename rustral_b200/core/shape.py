@@ -1,0 +1,53 @@
+"""Validated shapes and the shape policy (crates/core/src/shape.rs:6-57, shape_policy.rs:8)."""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass
+
+from .errors import InvalidShape
+
+
+@dataclass(frozen=True)
+class Shape:
+    """A non-empty shape whose dimensions are all non-zero."""
+    dims: tuple
+
+    def __init__(self, dims):
+        dims = tuple(int(d) for d in dims)
+        if len(dims) == 0:
+            raise InvalidShape("shape must have at least one dimension")
+        if any(d <= 0 for d in dims):
+            raise InvalidShape(f"shape dimensions must be positive, got {dims}")
+        object.__setattr__(self, "dims", dims)
+
+    @property
+    def rank(self) -> int:
+        return len(self.dims)
+
+    def numel(self) -> int:
+        n = 1
+        for d in self.dims:
+            n *= d
+        return n
+
+    def __iter__(self):
+        return iter(self.dims)
+
+    def __len__(self):
+        return len(self.dims)
+
+    def __getitem__(self, i):
+        return self.dims[i]
+
+
+class ShapePolicy(enum.Enum):
+    """How much shapes may vary between steps; decides CUDA-graph capture and arena pooling."""
+    STATIC = "static"
+    DYNAMIC_BOUNDED = "dynamic_bounded"
+    DYNAMIC_UNBOUNDED = "dynamic_unbounded"
+
+    def supports_cuda_graph_capture(self) -> bool:
+        return self is ShapePolicy.STATIC
+
+    def prefers_arena_pool(self) -> bool:
+        return self in (ShapePolicy.STATIC, ShapePolicy.DYNAMIC_BOUNDED)

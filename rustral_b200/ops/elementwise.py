@@ -101,7 +101,7 @@ def scalar_op(op: str, a, s: float, out=None):
 def unary_bwd(op: str, x, dy, out=None):
     """dy * op'(x) for relu / sigmoid / tanh / gelu / silu."""
     if not x.is_cuda:
-        from .gemm import act_grad_reference
+        from .matmul import act_grad_reference
         xf = x.float()
         if op == "sigmoid":
             s = torch.sigmoid(xf)

@@ -1,0 +1,58 @@
+"""Gradient reduction + sharded optimizer step + parameter gather for data-parallel ranks (ZeRO).
+
+Two interchangeable implementations behind one interface:
+
+* ``NcclZeroComm``  -- library collectives (reduce-scatter, all-gather over NCCL, or gloo for CPU ranks).  This is
+  the measured baseline and the path CPU-rank tests use.
+* ``FusedZeroComm`` -- the peer-memory kernels of ``csrc/comm``: every rank reads its gradient shard from all
+  peers over NVLink, reduces in fp32, applies AdamW to its fp32 master shard and pushes the updated bf16
+  parameters into every peer's working copy, all in one kernel (see rustral_b200/parallel/symm.py).
+
+Shard geometry: the flat parameter index space is padded to a multiple of world * 128 and cut into equal
+contiguous ranges, rank r owning [r * n/W, (r+1) * n/W) (the reference shards by flat index as well,
+crates/distributed/src/fsdp.rs:199-210, handing the remainder to the first ranks instead of padding).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+
+
+class NcclZeroComm:
+    def __init__(self, trainer):
+        self.t = trainer
+        P = trainer.engine.params
+        self.grad_shard = torch.zeros(trainer.shard_len, dtype=torch.float32, device=trainer.device)
+        self.norm_sq = torch.zeros(1, dtype=torch.float32, device=trainer.device)
+        self.norm = torch.zeros((), dtype=torch.float32, device=trainer.device)
+
+    def reduce_and_step(self, loss: torch.Tensor, lr):
+        t = self.t
+        eng, P = t.engine, t.engine.params
+        pg = t.pg
+        # gradients: sum over ranks, each rank keeps its shard
+        dist.reduce_scatter_tensor(self.grad_shard, P.grad, op=dist.ReduceOp.SUM, group=pg)
+        P.grad[t.shard].copy_(self.grad_shard)
+        # global gradient norm from the shards
+        ops.sumsq(self.grad_shard, out=self.norm_sq.view(()))
+        dist.all_reduce(self.norm_sq, group=pg)
+        ops.optim.sqrt_scalar(self.norm_sq.view(()), out=self.norm)
+        eng.optimizer_step(lr, shard=t.shard, grad_norm=self.norm)
+        # parameters: every rank gathers the updated working copy
+        dist.all_gather_into_tensor(P.lowp, P.lowp[t.shard].clone(), group=pg)
+        lbuf = loss.reshape(1).clone()
+        dist.all_reduce(lbuf, group=pg)
+        return lbuf.view(())
+
+
+def make_zero_comm(trainer, kind: str = "auto"):
+    if kind in ("auto", "fused") and trainer.device.type == "cuda":
+        try:
+            from .fused_zero import FusedZeroComm
+            return FusedZeroComm(trainer)
+        except Exception:
+            if kind == "fused":
+                raise
+    return NcclZeroComm(trainer)
