@@ -1,0 +1,291 @@
+// Peer-memory communication kernels (NVLink P2P loads / stores from inside the kernels; no TMA multicast,
+// no multimem in this file).  See symm.h for the protocol.
+//
+// Replaces the reference's host-slice collectives and its one-blocking-all-reduce-per-parameter step
+// (crates/distributed/src/lib.rs:180-209,378-386), its ZeRO broadcast-per-parameter (crates/distributed/src/zero.rs:104-123)
+// and the placeholder FSDP reduce-scatter / gather (crates/distributed/src/fsdp.rs:252-338).
+#include "symm.h"
+
+#include <string.h>
+
+#include "rb_common.cuh"
+
+namespace rb {
+
+constexpr int kSignalSlots = 64;   // channels per pad = kSignalSlots / world is never needed: pad is [channel][world]
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Bounded wait on `world` flags of one channel of the local pad.  One thread polls; returns false on expiry.
+__device__ __forceinline__ bool wait_flags(const unsigned int* pad, int world, int channel, unsigned int value,
+                                           unsigned long long limit_ns, unsigned int* status, unsigned int where) {
+  const unsigned int* f = pad + channel * world;
+  const unsigned long long t0 = globaltimer_ns();
+  for (int r = 0; r < world; ++r) {
+    while (true) {
+      const unsigned int v = ld_acquire_sys(f + r);
+      if (static_cast<int>(v - value) >= 0) break;     // wrap-safe "v >= value"
+      if (globaltimer_ns() - t0 > limit_ns) {
+        status_set(status, kStatusFlagTimeout, where);
+        return false;
+      }
+      __nanosleep(200);
+    }
+  }
+  return true;
+}
+
+__global__ void signal_all_kernel(void* const* pad_ptrs, int world, int my_rank, int channel, unsigned int value) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    __threadfence_system();   // everything this stream wrote before is visible before the flag
+    st_release_sys(reinterpret_cast<unsigned int*>(pad_ptrs[r]) + channel * world + my_rank, value);
+  }
+}
+
+__global__ void wait_all_kernel(const unsigned int* pad, int world, int channel, unsigned int value,
+                                unsigned long long limit_ns, unsigned int* status) {
+  if (threadIdx.x == 0) wait_flags(pad, world, channel, value, limit_ns, status, 100 + channel);
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Phase 1: reduce this rank's shard over all peers, publish the partial norm.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int kZeroThreads = 256;
+constexpr int kMaxWorld = 16;
+
+struct ZeroDev {
+  const float* grads[kMaxWorld];
+  __nv_bfloat16* lowp[kMaxWorld];
+  unsigned int* pads[kMaxWorld];
+  float* norms[kMaxWorld];
+};
+
+__global__ void __launch_bounds__(kZeroThreads)
+zero_reduce_kernel(ZeroDev d, RbZeroArgs a, unsigned int* status, unsigned int* block_counter) {
+  __shared__ int ok_sh;
+  __shared__ float red[kZeroThreads / 32];
+  if (threadIdx.x == 0)
+    ok_sh = wait_flags(reinterpret_cast<const unsigned int*>(a.local_pad), a.world, 0, a.epoch,
+                       static_cast<unsigned long long>(a.limit_ms) * 1000000ull, status, 10) ? 1 : 0;
+  __syncthreads();
+  const bool ok = ok_sh != 0;
+  float sq = 0.f;
+  if (ok) {
+    const long long n4 = a.shard_len / 4;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+      for (int r = 0; r < a.world; ++r) {   // fixed order: the reduced value does not depend on timing
+        const float4 g = *(reinterpret_cast<const float4*>(d.grads[r] + a.shard_off) + i);   // peer load over NVLink
+        acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+      }
+      reinterpret_cast<float4*>(a.grad_shard)[i] = acc;
+      sq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    }
+  }
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < kZeroThreads / 32; ++w) t += red[w];
+    a.partials[blockIdx.x] = t;
+    __threadfence();
+    const unsigned int done = atomicAdd(block_counter, 1u);
+    if (done == gridDim.x - 1) {
+      // last CTA: fold the per-CTA partials in index order and publish to every rank
+      __threadfence();
+      float tot = 0.f;
+      for (unsigned int b = 0; b < gridDim.x; ++b) tot += reinterpret_cast<volatile float*>(a.partials)[b];
+      for (int r = 0; r < a.world; ++r) d.norms[r][a.rank] = tot;
+      __threadfence_system();
+      for (int r = 0; r < a.world; ++r) st_release_sys(d.pads[r] + 1 * a.world + a.rank, a.epoch);
+      *block_counter = 0;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Phase 2: AdamW on the shard, push bf16 parameters to every rank.
+// ------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kZeroThreads)
+zero_adam_push_kernel(ZeroDev d, RbZeroArgs a, unsigned int* status, unsigned int* block_counter) {
+  __shared__ int ok_sh;
+  __shared__ float coef_sh;
+  if (threadIdx.x == 0) {
+    const bool ok = wait_flags(reinterpret_cast<const unsigned int*>(a.local_pad), a.world, 1, a.epoch,
+                               static_cast<unsigned long long>(a.limit_ms) * 1000000ull, status, 11);
+    float coef = 1.f;
+    if (ok && a.max_grad_norm > 0.f) {
+      float tot = 0.f;
+      for (int r = 0; r < a.world; ++r) tot += reinterpret_cast<volatile float*>(a.norm_slots)[r];
+      const float c = a.max_grad_norm / (sqrtf(tot) + 1e-6f);
+      if (c < 1.f) coef = c;
+    }
+    ok_sh = ok ? 1 : 0;
+    coef_sh = coef;
+  }
+  __syncthreads();
+  if (ok_sh) {
+    const float coef = coef_sh;
+    const float inv_bc1 = 1.f / a.bc1, inv_bc2 = 1.f / a.bc2;
+    const long long n4 = a.shard_len / 4;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+      const float4 g4 = reinterpret_cast<const float4*>(a.grad_shard)[i];
+      float4 p4 = reinterpret_cast<float4*>(a.master)[i];
+      float4 m4 = reinterpret_cast<float4*>(a.m)[i];
+      float4 v4 = reinterpret_cast<float4*>(a.v)[i];
+      float g[4] = {g4.x, g4.y, g4.z, g4.w}, p[4] = {p4.x, p4.y, p4.z, p4.w};
+      float m[4] = {m4.x, m4.y, m4.z, m4.w}, v[4] = {v4.x, v4.y, v4.z, v4.w};
+      const float wd = (a.shard_off + i * 4 < a.decay_end) ? a.weight_decay : 0.f;   // groups are 128-aligned
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float gj = g[j] * coef;
+        m[j] = a.beta1 * m[j] + (1.f - a.beta1) * gj;
+        v[j] = a.beta2 * v[j] + (1.f - a.beta2) * gj * gj;
+        const float upd = (m[j] * inv_bc1) / (sqrtf(v[j] * inv_bc2) + a.eps) + wd * p[j];
+        p[j] -= a.lr * upd;
+      }
+      reinterpret_cast<float4*>(a.master)[i] = make_float4(p[0], p[1], p[2], p[3]);
+      reinterpret_cast<float4*>(a.m)[i] = make_float4(m[0], m[1], m[2], m[3]);
+      reinterpret_cast<float4*>(a.v)[i] = make_float4(v[0], v[1], v[2], v[3]);
+      uint2 o;
+      o.x = pack_bf16x2(p[0], p[1]);
+      o.y = pack_bf16x2(p[2], p[3]);
+#pragma unroll 1
+      for (int r = 0; r < a.world; ++r)   // the all-gather: a direct store into every rank's working copy
+        *reinterpret_cast<uint2*>(d.lowp[r] + a.shard_off + i * 4) = o;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int done = atomicAdd(block_counter, 1u);
+    if (done == gridDim.x - 1) {
+      __threadfence_system();
+      for (int r = 0; r < a.world; ++r) st_release_sys(d.pads[r] + 2 * a.world + a.rank, a.epoch);
+      *block_counter = 0;
+    }
+  }
+}
+
+}  // namespace rb
+
+namespace {
+unsigned int* block_counter() {
+  static unsigned int* ptrs[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (!ptrs[dev]) {
+    unsigned int* p = nullptr;
+    if (cudaMalloc(&p, 2 * sizeof(unsigned int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, 2 * sizeof(unsigned int));
+    ptrs[dev] = p;
+  }
+  return ptrs[dev];
+}
+
+// Copies the [world] pointer arrays (device memory) into the by-value kernel argument.
+int load_dev(const RbZeroArgs& a, rb::ZeroDev& d) {
+  if (a.world < 1 || a.world > rb::kMaxWorld) return -1;
+  void* tmp[4][rb::kMaxWorld];
+  const void* src[4] = {a.grad_ptrs_dev, a.lowp_ptrs_dev, a.pad_ptrs_dev, a.norm_ptrs_dev};
+  for (int k = 0; k < 4; ++k)
+    if (cudaMemcpy(tmp[k], src[k], sizeof(void*) * a.world, cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+  for (int r = 0; r < a.world; ++r) {
+    d.grads[r] = reinterpret_cast<const float*>(tmp[0][r]);
+    d.lowp[r] = reinterpret_cast<__nv_bfloat16*>(tmp[1][r]);
+    d.pads[r] = reinterpret_cast<unsigned int*>(tmp[2][r]);
+    d.norms[r] = reinterpret_cast<float*>(tmp[3][r]);
+  }
+  return 0;
+}
+}  // namespace
+
+RB_API void* rb_symm_alloc(long long bytes) {
+  void* p = nullptr;
+  if (bytes <= 0 || cudaMalloc(&p, static_cast<size_t>(bytes)) != cudaSuccess) return nullptr;
+  cudaMemset(p, 0, static_cast<size_t>(bytes));
+  cudaDeviceSynchronize();
+  return p;
+}
+RB_API int rb_symm_free(void* ptr) { return static_cast<int>(cudaFree(ptr)); }
+RB_API int rb_ipc_export(void* ptr, unsigned char* handle64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+RB_API void* rb_ipc_import(const unsigned char* handle64) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return p;
+}
+RB_API int rb_ipc_close(void* ptr) { return static_cast<int>(cudaIpcCloseMemHandle(ptr)); }
+
+RB_API int rb_signal_all(void* const* pad_ptrs_dev, int world, int my_rank, int channel, unsigned int value, void* stream_v) {
+  if (world < 1 || world > 32 || channel < 0 || (channel + 1) * world > rb::kSignalSlots * 4) return -1;
+  rb::signal_all_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(pad_ptrs_dev, world, my_rank, channel, value);
+  return static_cast<int>(cudaGetLastError());
+}
+RB_API int rb_wait_all(const void* local_pad, int world, int channel, unsigned int value, int limit_ms, void* stream_v) {
+  if (world < 1 || world > 32 || channel < 0) return -1;
+  rb::wait_all_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      reinterpret_cast<const unsigned int*>(local_pad), world, channel, value,
+      static_cast<unsigned long long>(limit_ms > 0 ? limit_ms : 2000) * 1000000ull, rbhost::status_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
+static rb::ZeroDev g_zero_dev;
+static const void* g_zero_dev_key = nullptr;
+
+static int zero_prepare(const RbZeroArgs* a) {
+  if (!a || a->shard_len <= 0 || (a->shard_len % 4) || (a->shard_off % 4)) return -1;
+  if (g_zero_dev_key != a->grad_ptrs_dev) {   // pointer tables are fixed for the life of a trainer: read them once
+    const int rc = load_dev(*a, g_zero_dev);
+    if (rc != 0) return rc;
+    g_zero_dev_key = a->grad_ptrs_dev;
+  }
+  return 0;
+}
+
+RB_API int rb_zero_reduce(const RbZeroArgs* a, void* stream_v) {
+  const int rc = zero_prepare(a);
+  if (rc != 0) return rc;
+  unsigned int* ctr = block_counter();
+  if (!ctr) return -3;
+  int grid = rbhost::device_sm_count() * 2;
+  if (grid > 1024) grid = 1024;
+  rb::zero_reduce_kernel<<<grid, rb::kZeroThreads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      g_zero_dev, *a, rbhost::status_ptr(), ctr);
+  return static_cast<int>(cudaGetLastError());
+}
+
+RB_API int rb_zero_adam_push(const RbZeroArgs* a, void* stream_v) {
+  const int rc = zero_prepare(a);
+  if (rc != 0) return rc;
+  unsigned int* ctr = block_counter();
+  if (!ctr) return -3;
+  const int grid = rbhost::device_sm_count() * 2;
+  rb::zero_adam_push_kernel<<<grid, rb::kZeroThreads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      g_zero_dev, *a, rbhost::status_ptr(), ctr + 1);
+  return static_cast<int>(cudaGetLastError());
+}

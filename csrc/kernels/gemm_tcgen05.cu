@@ -204,7 +204,8 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& ep, uint32_t (&r
 template <int A_MN, int B_MN, int BLOCK_N, int STAGES>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
-                 int K, int group_m, EpiParams ep, unsigned int* status) {
+                 int K, int group_m, int num_splits, int kb_per_split, long long d_split_stride, EpiParams ep,
+                 unsigned int* status) {
   using L = SmemLayout<BLOCK_N, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms need 1024-byte aligned tiles
@@ -220,7 +221,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  constexpr uint32_t kTmemCols = (2 * BLOCK_N < 32) ? 32 : 2 * BLOCK_N;
+  // TMEM allocations are powers of two >= 32 columns
+  constexpr uint32_t kTmemCols = (2 * BLOCK_N <= 32) ? 32 : (2 * BLOCK_N <= 64) ? 64 : (2 * BLOCK_N <= 128) ? 128
+                                 : (2 * BLOCK_N <= 256) ? 256 : 512;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -248,10 +251,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_m = (M + kBlockM - 1) / kBlockM;
   const int num_n = (N + BLOCK_N - 1) / BLOCK_N;
   const int num_tiles = num_m * num_n;
-  const int num_kb = (K + kBlockK - 1) / kBlockK;
+  const int num_kb_total = (K + kBlockK - 1) / kBlockK;
   const int group_size = group_m * num_n;
+  // Work units: (split, tile).  With split-K every unit reduces its own K range into its own fp32 slab
+  // d + split * d_split_stride; a second kernel folds the slabs in a fixed order.
+  const int num_units = num_tiles * num_splits;
 
-  auto decode_tile = [&](int tile, int& m_blk, int& n_blk) {
+  auto decode_tile = [&](int unit, int& m_blk, int& n_blk, int& kb0, int& kb1) {
+    const int split = unit / num_tiles;
+    const int tile = unit - split * num_tiles;
+    kb0 = split * kb_per_split;
+    kb1 = min(num_kb_total, kb0 + kb_per_split);
     const int group = tile / group_size;
     const int first_m = group * group_m;
     const int gm = min(group_m, num_m - first_m);
@@ -265,10 +275,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // ------------------------------------------------------------------ TMA producer
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int m_blk, n_blk;
-        decode_tile(tile, m_blk, n_blk);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      for (int tile = blockIdx.x; tile < num_units && ok; tile += gridDim.x) {
+        int m_blk, n_blk, kb0, kb1;
+        decode_tile(tile, m_blk, n_blk, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, status, 1)) { ok = false; break; }
           const uint32_t full = bar_full + 8 * s;
@@ -298,12 +308,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = umma_idesc_bf16(kBlockM, BLOCK_N, A_MN, B_MN);
       uint32_t it = 0, t = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+      for (int tile = blockIdx.x; tile < num_units && ok; tile += gridDim.x, ++t) {
+        int m_blk, n_blk, kb0, kb1;
+        decode_tile(tile, m_blk, n_blk, kb0, kb1);
         const uint32_t acc = t & 1, acc_ph = (t >> 1) & 1;
         if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, status, 2)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, status, 3)) { ok = false; break; }
           tc_fence_after();
@@ -317,7 +329,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                      : umma_smem_desc_sw128(sa + k * (kUmmaK * 2), 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc_sw128(sb + k * (kUmmaK * 128), kBlockK * 128, 1024)
                                      : umma_smem_desc_sw128(sb + k * (kUmmaK * 2), 16, 1024);
-            umma_bf16_ss(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16_ss(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(bar_empty + 8 * s);   // frees the smem stage once these MMAs have read it
         }
@@ -328,9 +340,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // -------------------------------------------------------------------- epilogue warps
     const int q = warp & 3;   // TMEM lane quarter this warp may read
     uint32_t t = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
-      int m_blk, n_blk;
-      decode_tile(tile, m_blk, n_blk);
+    for (int tile = blockIdx.x; tile < num_units; tile += gridDim.x, ++t) {
+      int m_blk, n_blk, kb0, kb1;
+      decode_tile(tile, m_blk, n_blk, kb0, kb1);
+      EpiParams epu = ep;
+      if (num_splits > 1)
+        epu.d = reinterpret_cast<float*>(ep.d) + static_cast<long long>(tile / num_tiles) * d_split_stride;
       const uint32_t acc = t & 1, acc_ph = (t >> 1) & 1;
       if (!mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, status, 4)) break;
       tc_fence_after();
@@ -348,7 +363,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
         }
         const int col0 = n_blk * BLOCK_N + c * 32;
-        if (row < M && col0 < N) epilogue_chunk(ep, r, row, col0, N);
+        if (row < M && col0 < N) epilogue_chunk(epu, r, row, col0, N);
       }
     }
   }
@@ -365,6 +380,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// d (+)= sum_s ws[s] (slabs of M*N fp32, dense), s ascending: the order is fixed, so the result is reproducible.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long slab, void* d, long long ldd, int M, int N,
+                     int out_f32, int accumulate) {
+  const long long n4 = static_cast<long long>(M) * N / 4;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    float4 acc = reinterpret_cast<const float4*>(ws)[i];
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = reinterpret_cast<const float4*>(ws + s * slab)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const long long e = i * 4;
+    const long long row = e / N;
+    const int col = static_cast<int>(e - row * N);
+    if (out_f32) {
+      float4* dp = reinterpret_cast<float4*>(reinterpret_cast<float*>(d) + row * ldd + col);
+      if (accumulate) { const float4 o = *dp; acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w; }
+      *dp = acc;
+    } else {
+      uint2* dp = reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(d) + row * ldd + col);
+      if (accumulate) {
+        const uint2 o = *dp;
+        const float2 a = unpack_bf16x2(o.x), b = unpack_bf16x2(o.y);
+        acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+      }
+      uint2 o;
+      o.x = pack_bf16x2(acc.x, acc.y);
+      o.y = pack_bf16x2(acc.z, acc.w);
+      *dp = o;
+    }
+  }
+}
+
 }  // namespace rb
 
 // ---------------------------------------------------------------------------------------------
@@ -373,7 +422,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 namespace {
 
 template <int A_MN, int B_MN, int BLOCK_N, int STAGES>
-int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, int grid, cudaStream_t stream) {
+int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, int grid, int splits, cudaStream_t stream) {
   using L = rb::SmemLayout<BLOCK_N, STAGES>;
   auto kern = rb::gemm_bf16_kernel<A_MN, B_MN, BLOCK_N, STAGES>;
   const int smem = L::kTotal + 1024;
@@ -391,34 +440,69 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
   ep.aux_out = reinterpret_cast<__nv_bfloat16*>(g.aux_out); ep.ld_aux_out = g.ld_aux_out;
   ep.act = g.act; ep.out_f32 = g.out_f32; ep.accumulate = g.accumulate; ep.alpha = g.alpha;
   const int group_m = g.group_m > 0 ? g.group_m : 8;
-  kern<<<grid, rb::kNumThreads, smem, stream>>>(*ta, *tb, g.M, g.N, g.K, group_m, ep, rbhost::status_ptr());
+  const int num_kb = (g.K + rb::kBlockK - 1) / rb::kBlockK;
+  int kb_per = num_kb;
+  long long slab = 0;
+  if (splits > 1) {
+    kb_per = (num_kb + splits - 1) / splits;
+    splits = (num_kb + kb_per - 1) / kb_per;   // no split may end up with an empty K range
+    slab = static_cast<long long>(g.M) * g.N;
+    ep.d = g.workspace; ep.ldd = g.N; ep.out_f32 = 1; ep.accumulate = 0;
+  }
+  kern<<<grid, rb::kNumThreads, smem, stream>>>(*ta, *tb, g.M, g.N, g.K, group_m, splits, kb_per, slab, ep,
+                                                rbhost::status_ptr());
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || splits <= 1) return static_cast<int>(e);
+  const long long n4 = slab / 4;
+  int rgrid = static_cast<int>((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
+  rb::splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(reinterpret_cast<const float*>(g.workspace), splits, slab, g.d,
+                                                      g.ldd, g.M, g.N, g.out_f32, g.accumulate);
   return static_cast<int>(cudaGetLastError());
 }
 
 template <int BLOCK_N, int STAGES>
-int dispatch_major(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, int grid, cudaStream_t s) {
-  if (!g.a_mn_major && !g.b_mn_major) return launch<0, 0, BLOCK_N, STAGES>(g, ta, tb, grid, s);
-  if (!g.a_mn_major && g.b_mn_major) return launch<0, 1, BLOCK_N, STAGES>(g, ta, tb, grid, s);
-  if (g.a_mn_major && g.b_mn_major) return launch<1, 1, BLOCK_N, STAGES>(g, ta, tb, grid, s);
-  return launch<1, 0, BLOCK_N, STAGES>(g, ta, tb, grid, s);
+int dispatch_major(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, int grid, int splits,
+                   cudaStream_t s) {
+  if (!g.a_mn_major && !g.b_mn_major) return launch<0, 0, BLOCK_N, STAGES>(g, ta, tb, grid, splits, s);
+  if (!g.a_mn_major && g.b_mn_major) return launch<0, 1, BLOCK_N, STAGES>(g, ta, tb, grid, splits, s);
+  if (g.a_mn_major && g.b_mn_major) return launch<1, 1, BLOCK_N, STAGES>(g, ta, tb, grid, splits, s);
+  return launch<1, 0, BLOCK_N, STAGES>(g, ta, tb, grid, splits, s);
 }
 
-int pick_block_n(int M, int N, int sms) {
-  // cost model: waves x tile width; wider tiles are preferred on a tie (fewer operand re-reads)
-  const int cands[3] = {256, 128, 64};
-  long long best_cost = -1;
-  int best = 128;
-  const long long num_m = (M + 127) / 128;
-  for (int c = 0; c < 3; ++c) {
+// Relative time of one tile column unit per tile width: narrow tiles re-read the A operand from shared
+// memory more often per MMA (measured on B200: 128-wide runs ~1.3x, 64-wide ~2.3x slower than 256-wide).
+int width_cost(int bn) { return bn == 256 ? 100 : bn == 192 ? 104 : bn == 128 ? 132 : 235; }
+
+long long plan_cost(int M, int N, int bn, int splits, int sms) {
+  const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + bn - 1) / bn) * splits;
+  const long long waves = (tiles + sms - 1) / sms;
+  // per-unit time ~ bn * K/splits (+ a fixed prologue/epilogue share that split-K multiplies)
+  return waves * bn * width_cost(bn) * (1000 / splits + 40);
+}
+
+void pick_plan(const RbGemmArgs& g, int sms, int& bn_out, int& splits_out) {
+  const int cands[4] = {256, 192, 128, 64};
+  const int split_cands[7] = {1, 2, 3, 4, 6, 8, 12};
+  const bool can_split = g.workspace != nullptr && g.act == RB_ACT_NONE && !g.bias && !g.residual && !g.aux_out &&
+                         (g.N % 4 == 0) && (static_cast<long long>(g.M) * g.N % 4 == 0);
+  long long best = -1;
+  bn_out = 128; splits_out = 1;
+  for (int c = 0; c < 4; ++c) {
     const int bn = cands[c];
-    if (bn > 64 && N <= bn / 2) continue;
-    const long long tiles = num_m * ((N + bn - 1) / bn);
-    const long long waves = (tiles + sms - 1) / sms;
-    // a 64-wide tile runs at roughly 0.6x, a 128-wide at 0.9x the MMA efficiency of a 256-wide one
-    const long long cost = waves * bn * (bn == 256 ? 100 : (bn == 128 ? 108 : 150));
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    if (g.block_n && g.block_n != bn) continue;
+    if (!g.block_n && bn > 64 && g.N <= bn / 2) continue;
+    for (int si = 0; si < 7; ++si) {
+      const int sp = split_cands[si];
+      if (g.splits > 0 && sp != g.splits) continue;
+      if (sp > 1) {
+        if (!can_split) continue;
+        if (g.splits <= 0 && g.K / sp < 1024) continue;
+        if (static_cast<long long>(sp) * g.M * g.N * 4 > g.workspace_bytes) continue;
+      }
+      const long long cost = plan_cost(g.M, g.N, bn, sp, sms);
+      if (best < 0 || cost < best) { best = cost; bn_out = bn; splits_out = sp; }
+    }
   }
-  return best;
 }
 
 }  // namespace
@@ -441,8 +525,10 @@ RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
   if ((g.act >= RB_ACT_DGELU && g.act <= RB_ACT_MUL) && !g.aux_in) return -4;
 
   const int sms = rbhost::device_sm_count();
-  int bn = g.block_n;
-  if (bn != 64 && bn != 128 && bn != 256) bn = pick_block_n(g.M, g.N, sms);
+  if (g.block_n != 0 && g.block_n != 64 && g.block_n != 128 && g.block_n != 192 && g.block_n != 256) return -6;
+  int bn = 128, splits = 1;
+  pick_plan(g, sms, bn, splits);
+  if (g.splits > 1 && splits != g.splits) return -7;   // a forced split count that cannot be honoured
 
   int err = 0;
   const CUtensorMap* ta = g.a_mn_major
@@ -454,12 +540,13 @@ RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
                               : rbhost::get_tmap_2d(g.b, 2, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, 64, (uint32_t)bn, 1, &err);
   if (!tb) return err ? err : -5;
 
-  const long long tiles = (long long)((g.M + 127) / 128) * ((g.N + bn - 1) / bn);
+  const long long tiles = (long long)((g.M + 127) / 128) * ((g.N + bn - 1) / bn) * splits;
   int grid = static_cast<int>(tiles < sms ? tiles : sms);
   if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;
   switch (bn) {
-    case 256: return dispatch_major<256, 4>(g, ta, tb, grid, stream);
-    case 128: return dispatch_major<128, 6>(g, ta, tb, grid, stream);
-    default: return dispatch_major<64, 8>(g, ta, tb, grid, stream);
+    case 256: return dispatch_major<256, 4>(g, ta, tb, grid, splits, stream);
+    case 192: return dispatch_major<192, 5>(g, ta, tb, grid, splits, stream);
+    case 128: return dispatch_major<128, 6>(g, ta, tb, grid, splits, stream);
+    default: return dispatch_major<64, 8>(g, ta, tb, grid, splits, stream);
   }
 }

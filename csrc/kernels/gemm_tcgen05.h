@@ -31,9 +31,12 @@ typedef struct RbGemmArgs {
   int out_f32;          // 1: d is fp32
   int accumulate;       // 1: d += result
   float alpha;          // scales the accumulator before everything else
-  int block_n;          // 0 = choose; else 64 / 128 / 256
+  int block_n;          // 0 = choose; else 64 / 128 / 192 / 256
   int group_m;          // 0 = default (8): M-tiles per rasterisation group
   int max_ctas;         // 0 = one per SM; else cap on the persistent grid
+  int splits;           // 0 = choose (split-K only when a workspace is given); 1 = never split; else forced count
+  void* workspace;      // fp32 scratch for split-K partial sums (splits * M * N floats), or NULL
+  long long workspace_bytes;
 } RbGemmArgs;
 
 // Returns 0 on success, a negative code for rejected arguments, a positive cudaError otherwise.

@@ -217,18 +217,31 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy, const __nv
   }
 }
 
-// out[col] (+)= sum_p partial[p][col], p in a fixed order.
-__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials, int n,
-                                       float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= n) return;
+// out[col] (+)= sum_p partial[p][col].  Eight row groups per CTA each sum every eighth partial, then the
+// groups are folded in index order: parallel enough to hide latency, and the order is fixed.
+__global__ void __launch_bounds__(256)
+norm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials, int n, float* __restrict__ dgamma,
+                       float* __restrict__ dbeta, int accumulate) {
+  __shared__ float sa[8][33], sb[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + tx;
   float a = 0.f, b = 0.f;
-  for (int p = 0; p < num_partials; ++p) {
-    a += partial[static_cast<long long>(p) * n + col];
-    if (dbeta) b += partial[static_cast<long long>(num_partials + p) * n + col];
+  if (col < n) {
+    for (int p = ty; p < num_partials; p += 8) {
+      a += partial[static_cast<long long>(p) * n + col];
+      if (dbeta) b += partial[static_cast<long long>(num_partials + p) * n + col];
+    }
   }
-  dgamma[col] = accumulate ? dgamma[col] + a : a;
-  if (dbeta) dbeta[col] = accumulate ? dbeta[col] + b : b;
+  sa[ty][tx] = a;
+  sb[ty][tx] = b;
+  __syncthreads();
+  if (ty == 0 && col < n) {
+    float ta = 0.f, tb = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) { ta += sa[g][tx]; tb += sb[g][tx]; }
+    dgamma[col] = accumulate ? dgamma[col] + ta : ta;
+    if (dbeta) dbeta[col] = accumulate ? dbeta[col] + tb : tb;
+  }
 }
 
 }  // namespace rb
@@ -325,7 +338,7 @@ RB_API int rb_norm_bwd(const void* dy, long long lddy, const void* x, long long 
 #undef RB_LAUNCH
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
-  rb::norm_bwd_reduce_kernel<<<(n + 127) / 128, 128, 0, stream>>>(partial, grid, n, dgamma, rms ? nullptr : dbeta,
+  rb::norm_bwd_reduce_kernel<<<(n + 31) / 32, 256, 0, stream>>>(partial, grid, n, dgamma, rms ? nullptr : dbeta,
                                                                  accumulate);
   return static_cast<int>(cudaGetLastError());
 }

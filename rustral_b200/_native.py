@@ -29,7 +29,8 @@ class RbGemmArgs(C.Structure):
         ("a_mn_major", c_int), ("b_mn_major", c_int),
         ("act", c_int), ("out_f32", c_int), ("accumulate", c_int),
         ("alpha", c_float),
-        ("block_n", c_int), ("group_m", c_int), ("max_ctas", c_int),
+        ("block_n", c_int), ("group_m", c_int), ("max_ctas", c_int), ("splits", c_int),
+        ("workspace", c_void_p), ("workspace_bytes", c_ll),
     ]
 
 

@@ -77,9 +77,23 @@ def _gemm_cpu(a, b, a_mn, b_mn, bias, act, residual, aux_in, aux_out, out, out_d
     return out
 
 
+_workspaces: dict = {}
+WORKSPACE_BYTES = 128 << 20
+
+
+def _workspace(device) -> torch.Tensor:
+    """Split-K scratch, one per device and stream, allocated on first use."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.empty(WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, act: str = "none",
          residual=None, aux_in=None, aux_out=None, out=None, out_dtype=None, accumulate: bool = False,
-         alpha: float = 1.0, block_n: int = 0, group_m: int = 0, max_ctas: int = 0) -> torch.Tensor:
+         alpha: float = 1.0, block_n: int = 0, group_m: int = 0, max_ctas: int = 0, splits: int = 0) -> torch.Tensor:
     assert a.dim() == 2 and b.dim() == 2
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
     Nn, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
@@ -122,7 +136,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     g.out_f32 = int(out.dtype == torch.float32)
     g.accumulate = int(accumulate)
     g.alpha = alpha
-    g.block_n, g.group_m, g.max_ctas = block_n, group_m, max_ctas
+    g.block_n, g.group_m, g.max_ctas, g.splits = block_n, group_m, max_ctas, splits
+    if splits != 1 and K >= 2048 and act == "none" and bias is None and residual is None:
+        ws = _workspace(a.device)
+        g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel()
     N.check(N.kernels().rb_gemm_bf16(g, N.stream_ptr()), "rb_gemm_bf16")
     return out
 

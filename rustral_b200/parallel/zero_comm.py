@@ -33,7 +33,11 @@ class NcclZeroComm:
         eng, P = t.engine, t.engine.params
         pg = t.pg
         # gradients: sum over ranks, each rank keeps its shard
-        dist.reduce_scatter_tensor(self.grad_shard, P.grad, op=dist.ReduceOp.SUM, group=pg)
+        if P.grad.is_cuda:
+            dist.reduce_scatter_tensor(self.grad_shard, P.grad, op=dist.ReduceOp.SUM, group=pg)
+        else:   # gloo has no reduce-scatter: all-reduce and keep the shard
+            dist.all_reduce(P.grad, group=pg)
+            self.grad_shard.copy_(P.grad[t.shard])
         P.grad[t.shard].copy_(self.grad_shard)
         # global gradient norm from the shards
         ops.sumsq(self.grad_shard, out=self.norm_sq.view(()))
@@ -41,10 +45,27 @@ class NcclZeroComm:
         ops.optim.sqrt_scalar(self.norm_sq.view(()), out=self.norm)
         eng.optimizer_step(lr, shard=t.shard, grad_norm=self.norm)
         # parameters: every rank gathers the updated working copy
-        dist.all_gather_into_tensor(P.lowp, P.lowp[t.shard].clone(), group=pg)
+        if P.lowp.is_cuda:
+            dist.all_gather_into_tensor(P.lowp, P.lowp[t.shard].clone(), group=pg)
+        else:
+            parts = [torch.empty(t.shard_len, dtype=P.lowp.dtype) for _ in range(t.world)]
+            dist.all_gather(parts, P.lowp[t.shard].clone(), group=pg)
+            P.lowp.copy_(torch.cat(parts))
         lbuf = loss.reshape(1).clone()
         dist.all_reduce(lbuf, group=pg)
         return lbuf.view(())
+
+
+    def gather_master(self) -> None:
+        """Every rank updated only its shard of the fp32 master copy: collect the shards (for checkpoints)."""
+        t = self.t
+        P = t.engine.params
+        parts = [torch.empty(t.shard_len, dtype=torch.float32, device=P.master.device) for _ in range(t.world)]
+        dist.all_gather(parts, P.master[t.shard].clone(), group=t.pg)
+        P.master.copy_(torch.cat(parts))
+
+    def close(self) -> None:
+        pass
 
 
 def make_zero_comm(trainer, kind: str = "auto"):

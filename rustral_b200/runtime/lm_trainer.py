@@ -42,6 +42,8 @@ class LMTrainer:
             device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))) if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
         if self.device.type == "cuda":
+            if self.device.index is None:
+                self.device = torch.device("cuda", torch.cuda.current_device())
             torch.cuda.set_device(self.device)
         self.pg = process_group
         self.world = 1
@@ -98,7 +100,15 @@ class LMTrainer:
 
     # -------------------------------------------------------------------------------------------------
     def state_dict(self) -> dict:
+        if self.comm is not None:
+            self.comm.gather_master()
         return self.engine.params.state_dict()
+
+    def close(self) -> None:
+        """Releases peer mappings (collective when world > 1)."""
+        if self.comm is not None:
+            self.comm.close()
+            self.comm = None
 
     def load_state_dict(self, state: dict) -> None:
         self.engine.params.load_state_dict(state)

@@ -44,7 +44,7 @@ def test_gemm_majors(M, N, K, a_mn, b_mn, cuda_status):
     _close(out, ref)
 
 
-@pytest.mark.parametrize("block_n", [64, 128, 256])
+@pytest.mark.parametrize("block_n", [64, 128, 192, 256])
 def test_gemm_block_n(block_n, cuda_status):
     M, N, K = 384, 512, 320
     a, b = _mk((M, K), 3), _mk((N, K), 4)
@@ -92,9 +92,24 @@ def test_linear_autograd_matches_cpu(cuda_status):
     b = (torch.randn(224) * 0.1).to(torch.bfloat16)
     outs = []
     for dev in ("cpu", "cuda"):
-        xd, wd, bd = (t.to(dev).requires_grad_() for t in (x, w, b))
+        xd, wd, bd = (t.detach().clone().to(dev).requires_grad_() for t in (x, w, b))
         y = ops.linear(xd, wd, bd, "gelu")
         y.float().sum().backward()
         outs.append((y.float().cpu(), xd.grad.float().cpu(), wd.grad.float().cpu(), bd.grad.float().cpu()))
     for c, g in zip(*outs):
         _close(g, c, tol=3e-2)
+
+
+@pytest.mark.parametrize("splits", [0, 2, 3, 8])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_split_k_wgrad_shape(splits, out_dtype, cuda_status):
+    # weight-gradient shape: small output, long contraction; split-K partial sums are folded in a fixed order
+    M, N, K = 768, 264, 8192
+    a, b = _mk((K, M), 11), _mk((K, N), 12)
+    ref = _ref(a, b, True, True)
+    out = torch.full((M, N), 2.0, dtype=out_dtype, device="cuda")
+    ops.gemm(a.cuda(), b.cuda(), a_mn=True, b_mn=True, out=out, accumulate=True, splits=splits)
+    _close(out, ref + 2.0, tol=1e-2 if out_dtype == torch.float32 else 2e-2)
+    out2 = torch.full((M, N), 2.0, dtype=out_dtype, device="cuda")
+    ops.gemm(a.cuda(), b.cuda(), a_mn=True, b_mn=True, out=out2, accumulate=True, splits=splits)
+    assert torch.equal(out, out2)
