@@ -8,5 +8,12 @@ from .module import (Module, NamedParameters, Trainable, StatefulModule, Saveabl
 from .backend import (Backend, CpuBackend, B200Backend, BackendCapabilities, OperationType, ConvLayout, TrainingDtype,
                       default_backend, set_default_backend)
 from .tensor_ops import TensorOps, TensorInPlaceOps, FusionOps, AttentionOps, QuantizationOps
+from .operation_profiler import (OperationProfiler, OperationStats, OperationGuard, ProfilerSnapshot, DeviceType,
+                                 shape_bucket, operation_profiler_from_env, finish_profile_from_env)
+from .memory_profiler import MemoryProfiler, AllocationTracker, OOMRisk, global_profiler, track_tensor
+from .tensor_pool import TensorPool, PoolStrategy, PooledTensor, pool_from_env
+from .numerics import (DType, Tolerance, NumericsConfig, NumericsValidator, OpFamily, ToleranceConfig, assert_close,
+                       assert_slices_close)
+from .fusion import FusionPattern, PatternMatcher, FusionOptimizer, FusionTestHarness, generate_random_data
 
 __all__ = [n for n in dir() if not n.startswith("_")]
