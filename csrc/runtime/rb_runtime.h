@@ -1,0 +1,52 @@
+// C interface of the host runtime library (librb200_runtime.so): paged-KV block allocator, request scheduler
+// core, tile-configuration search and a memory-mapped token loader.  No GPU code; bound with ctypes.
+#pragma once
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+// ---- paged KV block allocator --------------------------------------------------------------------------------
+typedef struct RbBlockAllocator RbBlockAllocator;
+RbBlockAllocator* rb_ba_create(int num_blocks, int block_size);
+void rb_ba_destroy(RbBlockAllocator* a);
+int rb_ba_num_free(const RbBlockAllocator* a);
+int rb_ba_num_blocks(const RbBlockAllocator* a);
+int rb_ba_block_size(const RbBlockAllocator* a);
+// Grows sequence `seq_id` so that it can hold `num_tokens` tokens in total (allocating ceil(n / block_size) blocks
+// minus what it already owns).  Returns the number of newly allocated blocks, or -1 when there are not enough free
+// blocks (nothing is allocated in that case).  A second call for the same sequence EXTENDS its table.
+int rb_ba_reserve(RbBlockAllocator* a, int64_t seq_id, int num_tokens);
+// Can `num_tokens` more tokens be held for this sequence (existing or new) without running out of blocks?
+int rb_ba_can_reserve(const RbBlockAllocator* a, int64_t seq_id, int num_tokens);
+int rb_ba_free(RbBlockAllocator* a, int64_t seq_id);           // returns the number of blocks released
+int rb_ba_table_len(const RbBlockAllocator* a, int64_t seq_id);
+int rb_ba_table(const RbBlockAllocator* a, int64_t seq_id, int32_t* out, int max_out);   // copies the table; returns its length
+int64_t rb_ba_slot(const RbBlockAllocator* a, int64_t seq_id, int token_index);          // block * block_size + offset, -1 if unmapped
+int rb_ba_num_sequences(const RbBlockAllocator* a);
+
+// ---- tile-configuration search (autotuner core) --------------------------------------------------------------
+// A search space is a list of dimensions, each with a list of integer choices.  Strategies: 0 grid, 1 random,
+// 2 evolutionary, 3 bayesian-style (explore / exploit around the incumbent).  The caller measures each proposed
+// configuration and reports the time; the searcher never runs kernels itself.
+typedef struct RbSearch RbSearch;
+RbSearch* rb_search_create(int strategy, int num_dims, const int* dim_sizes, const int* choices_flat, uint64_t seed,
+                           int max_evals);
+void rb_search_destroy(RbSearch* s);
+int rb_search_next(RbSearch* s, int* config_out);                 // 1 = config_out filled, 0 = search complete
+void rb_search_report(RbSearch* s, const int* config, double time_us);
+int rb_search_best(const RbSearch* s, int* config_out, double* time_us_out);   // 1 if any result was reported
+int rb_search_num_evals(const RbSearch* s);
+
+// ---- memory-mapped token dataset ----------------------------------------------------------------------------------
+typedef struct RbTokenFile RbTokenFile;
+RbTokenFile* rb_tokens_open(const char* path, int bytes_per_token);      // 2 (uint16) or 4 (int32)
+void rb_tokens_close(RbTokenFile* f);
+int64_t rb_tokens_len(const RbTokenFile* f);
+// Fills out[batch, seq_len + 1] (int64) with windows starting at the given offsets; returns 0 on success.
+int rb_tokens_gather(const RbTokenFile* f, const int64_t* offsets, int batch, int seq_len_plus1, int64_t* out);
+// Deterministic window offsets for (seed, step): uniform over valid starts.
+void rb_tokens_sample_offsets(const RbTokenFile* f, uint64_t seed, uint64_t step, int batch, int seq_len_plus1,
+                              int64_t* offsets_out);
+#ifdef __cplusplus
+}
+#endif

@@ -31,7 +31,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
 ]
-CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-march=x86-64-v2", "-fopenmp", "-Wall"]
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-march=x86-64-v2", "-Wall", "-pthread"]
 
 
 def _nvcc() -> str:
@@ -96,7 +96,7 @@ def _build_cxx(subdir: str, libname: str, force: bool, verbose: bool) -> Path:
     return _compile_group(
         srcs, hdrs, LIB_DIR / libname,
         lambda s, o: [cxx, *CXX_FLAGS, *inc, "-c", s, "-o", o],
-        lambda objs, out: [cxx, "-shared", "-fopenmp", *objs, "-o", out, "-lpthread"],
+        lambda objs, out: [cxx, "-shared", "-pthread", *objs, "-o", out],
         verbose, force)
 
 

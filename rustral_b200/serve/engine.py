@@ -1,0 +1,140 @@
+"""ServingEngine: continuous batching around a real model step, with latency accounting
+(crates/nn/src/continuous_batching.rs:496-546)."""
+from __future__ import annotations
+
+import statistics
+import time
+from dataclasses import dataclass
+
+import torch
+
+from .model_runner import ModelRunner
+from .sampler import Sampler
+from .scheduler import RequestPriority, RequestState, Scheduler, SchedulingPolicy
+
+
+@dataclass
+class ServingMetrics:
+    completed: int
+    output_tokens: int
+    wall_s: float
+    ttft_p50_ms: float
+    ttft_p99_ms: float
+    itl_p50_ms: float
+    itl_p99_ms: float
+    output_tokens_per_s: float
+
+    def to_dict(self) -> dict:
+        return dict(self.__dict__)
+
+
+def _pct(xs, q):
+    if not xs:
+        return 0.0
+    xs = sorted(xs)
+    return xs[min(len(xs) - 1, int(round(q * (len(xs) - 1))))]
+
+
+class ServingEngine:
+    def __init__(self, runner: ModelRunner, max_batch_size: int = 64, policy: SchedulingPolicy = SchedulingPolicy.FCFS,
+                 sampler: Sampler | None = None, eos_id: int | None = None):
+        self.runner = runner
+        self.scheduler = Scheduler(runner.cache, max_batch_size, policy)
+        self.sampler = sampler or Sampler.greedy()
+        self.eos_id = eos_id
+        self.callbacks: dict = {}
+        self.steps = 0
+
+    def submit(self, prompt, max_tokens: int, priority: RequestPriority = RequestPriority.NORMAL, callback=None,
+               arrival_time: float | None = None) -> int:
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        if len(prompt) + max_tokens > self.runner.cfg.seq_len:
+            raise ValueError(f"prompt + max_tokens exceeds the model's context of {self.runner.cfg.seq_len}")
+        rid = self.scheduler.add_request(prompt, max_tokens, priority, self.eos_id, arrival_time)
+        if callback is not None:
+            self.callbacks[rid] = callback
+        return rid
+
+    def step(self) -> dict:
+        """One iteration: schedule, run the model (prefills one by one, decodes as one batch), sample, update.
+        Returns request id -> new token."""
+        sch = self.scheduler
+        done_before = len(sch.completed)
+        batch = sch.schedule()
+        for r in sch.completed[done_before:]:
+            cb = self.callbacks.pop(r.id, None)
+            if cb is not None:
+                cb(r)
+        if len(batch) == 0:
+            return {}
+        outputs = {}
+        vocab = self.runner.cfg.vocab_size
+        dec_ids, dec_tok, dec_len = [], [], []
+        for rid, inp, n, pre in zip(batch.request_ids, batch.input_ids, batch.seq_lens, batch.is_prefill):
+            if pre:
+                logits = self.runner.prefill(rid, inp)
+                outputs[rid] = int(self.sampler.sample(logits[:vocab].unsqueeze(0))[0])
+            else:
+                dec_ids.append(rid)
+                dec_tok.append(inp[0])
+                dec_len.append(n)
+        if dec_ids:
+            logits = self.runner.decode(dec_ids, dec_tok, dec_len)
+            toks = self.sampler.sample(logits[:, :vocab]).tolist()
+            outputs.update(dict(zip(dec_ids, toks)))
+        if self.runner.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        sch.update(outputs, time.perf_counter())
+        self.steps += 1
+        return outputs
+
+    def run_to_completion(self, max_steps: int = 1 << 30) -> list:
+        n = 0
+        while self.scheduler.has_work() and n < max_steps:
+            self.step()
+            n += 1
+        self.scheduler._retire()
+        return self.scheduler.completed
+
+    def generate(self, prompt, max_tokens: int) -> list:
+        rid = self.submit(prompt, max_tokens)
+        self.run_to_completion()
+        return self.scheduler.get(rid).generated
+
+    def metrics(self, wall_s: float) -> ServingMetrics:
+        done = self.scheduler.completed
+        ttft = [(r.first_token_time - r.arrival_time) * 1e3 for r in done if r.first_token_time is not None]
+        itl = []
+        for r in done:
+            itl += [(b - a) * 1e3 for a, b in zip(r.token_times, r.token_times[1:])]
+        out_tokens = sum(len(r.generated) for r in done)
+        return ServingMetrics(len(done), out_tokens, wall_s, _pct(ttft, 0.5), _pct(ttft, 0.99), _pct(itl, 0.5), _pct(itl, 0.99),
+                              out_tokens / wall_s if wall_s > 0 else 0.0)
+
+
+def run_poisson_workload(engine: ServingEngine, num_requests: int, rate_per_s: float, prompt_range=(128, 2048),
+                         output_range=(128, 512), seed: int = 0, time_limit_s: float = 3600.0) -> ServingMetrics:
+    """Open-loop load test: requests arrive by a Poisson process at `rate_per_s`, prompt and output lengths uniform in
+    the given ranges, prompt tokens uniform random; the engine steps in real time and a request is submitted once
+    its arrival time has passed (its latency clock starts at the ARRIVAL time, so queueing counts)."""
+    g = torch.Generator().manual_seed(seed)
+    vocab = engine.runner.cfg.vocab_size
+    gaps = torch.empty(num_requests).exponential_(rate_per_s, generator=g)
+    arrivals = torch.cumsum(gaps, 0).tolist()
+    plen = torch.randint(prompt_range[0], prompt_range[1] + 1, (num_requests,), generator=g).tolist()
+    olen = torch.randint(output_range[0], output_range[1] + 1, (num_requests,), generator=g).tolist()
+    prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in plen]
+    t0 = time.perf_counter()
+    nxt = 0
+    while (nxt < num_requests or engine.scheduler.has_work()) and time.perf_counter() - t0 < time_limit_s:
+        now = time.perf_counter() - t0
+        while nxt < num_requests and arrivals[nxt] <= now:
+            engine.submit(prompts[nxt], olen[nxt], arrival_time=t0 + arrivals[nxt])
+            nxt += 1
+        if engine.scheduler.has_work():
+            engine.step()
+        elif nxt < num_requests:
+            time.sleep(min(0.001, max(0.0, arrivals[nxt] - now)))
+    engine.scheduler._retire()
+    return engine.metrics(time.perf_counter() - t0)

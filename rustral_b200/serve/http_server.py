@@ -1,0 +1,199 @@
+"""HTTP front end (crates/inference-server/src/main.rs:23-251): GET /health, /ready, /v1/metadata, /metrics and
+POST /v1/infer (one Linear artifact, {"input": [[f32]]} -> {"output": [[f32]]}) plus POST /v1/generate for the
+decoder engine ({"prompt": [ids], "max_tokens": n} -> {"tokens": [ids]}).  Standard-library server, one engine thread;
+request handlers hand work to it through a bounded InferencePool, so the model is never entered concurrently.
+
+    python -m rustral_b200.serve.http_server --artifact linear.safetensors --in-features 4 --out-features 3 --bias
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import signal
+import threading
+import time
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+import torch
+
+from ..runtime.inference import InferencePool
+
+
+class ServerState:
+    def __init__(self, infer_fn=None, generate_fn=None, metadata=None, workers: int = 1, queue_bound: int = 64):
+        self.metadata = metadata or {}
+        self.ready = True
+        self.requests_total = 0
+        self.errors_total = 0
+        self.latency_ns_sum = 0
+        self.lock = threading.Lock()
+        self.infer_pool = InferencePool(workers, queue_bound, infer_fn) if infer_fn else None
+        self.generate_pool = InferencePool(1, queue_bound, generate_fn) if generate_fn else None
+
+    def record(self, ns: int, ok: bool) -> None:
+        with self.lock:
+            self.requests_total += 1
+            self.latency_ns_sum += ns
+            if not ok:
+                self.errors_total += 1
+
+    def prometheus(self) -> str:
+        with self.lock:
+            return ("# TYPE rustral_infer_requests_total counter\n"
+                    f"rustral_infer_requests_total {self.requests_total}\n"
+                    "# TYPE rustral_infer_errors_total counter\n"
+                    f"rustral_infer_errors_total {self.errors_total}\n"
+                    "# TYPE rustral_infer_latency_ns_sum counter\n"
+                    f"rustral_infer_latency_ns_sum {self.latency_ns_sum}\n")
+
+    def shutdown(self):
+        for p in (self.infer_pool, self.generate_pool):
+            if p is not None:
+                p.shutdown()
+
+
+class BadRequest(Exception):
+    pass
+
+
+def make_handler(state: ServerState):
+    class Handler(BaseHTTPRequestHandler):
+        protocol_version = "HTTP/1.1"
+
+        def log_message(self, fmt, *args):   # quiet by default
+            pass
+
+        def _send(self, code: int, body, ctype="application/json"):
+            data = body if isinstance(body, bytes) else (body if isinstance(body, str) else json.dumps(body)).encode()
+            self.send_response(code)
+            self.send_header("Content-Type", ctype)
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
+
+        def do_GET(self):
+            if self.path == "/health":
+                self._send(200, {"status": "ok"})
+            elif self.path == "/ready":
+                self._send(200 if state.ready else 503, {"ready": state.ready})
+            elif self.path == "/v1/metadata":
+                self._send(200, state.metadata)
+            elif self.path == "/metrics":
+                self._send(200, state.prometheus(), "text/plain; version=0.0.4")
+            else:
+                self._send(404, {"error": "not found"})
+
+        def do_POST(self):
+            t0 = time.perf_counter_ns()
+            ok = False
+            try:
+                n = int(self.headers.get("Content-Length", "0"))
+                try:
+                    body = json.loads(self.rfile.read(n) or b"{}")
+                except json.JSONDecodeError as e:
+                    raise BadRequest(f"invalid JSON: {e}")
+                if self.path == "/v1/infer" and state.infer_pool is not None:
+                    out = state.infer_pool.infer(body)
+                elif self.path == "/v1/generate" and state.generate_pool is not None:
+                    out = state.generate_pool.infer(body)
+                else:
+                    self._send(404, {"error": "not found"})
+                    return
+                ok = True
+                self._send(200, out)
+            except BadRequest as e:
+                self._send(400, {"error": str(e)})
+            except Exception as e:   # noqa: BLE001 - a handler must always answer
+                self._send(500, {"error": f"{type(e).__name__}: {e}"})
+            finally:
+                state.record(time.perf_counter_ns() - t0, ok)
+
+    return Handler
+
+
+def linear_infer_fn(linear, in_features: int):
+    """Validation of the reference server: non-empty batch, every row of length in_features (main.rs:203-214)."""
+    from ..core import ForwardCtx
+
+    def fn(body):
+        rows = body.get("input")
+        if not isinstance(rows, list) or len(rows) == 0:
+            raise BadRequest("input must be a non-empty list of rows")
+        for r in rows:
+            if not isinstance(r, list) or len(r) != in_features:
+                raise BadRequest(f"every row must have {in_features} values")
+        dev = linear.weight.tensor.device
+        x = torch.tensor(rows, dtype=torch.float32).to(dev, linear.weight.tensor.dtype)
+        with torch.no_grad():
+            y = linear(x, ForwardCtx.inference())
+        return {"output": y.float().cpu().tolist()}
+
+    return fn
+
+
+def engine_generate_fn(engine):
+    def fn(body):
+        prompt = body.get("prompt")
+        if not isinstance(prompt, list) or not prompt or not all(isinstance(t, int) for t in prompt):
+            raise BadRequest("prompt must be a non-empty list of token ids")
+        vocab = engine.runner.cfg.vocab_size
+        if any(t < 0 or t >= vocab for t in prompt):
+            raise BadRequest("token id out of range")
+        max_tokens = int(body.get("max_tokens", 16))
+        try:
+            return {"tokens": engine.generate(prompt, max_tokens)}
+        except ValueError as e:
+            raise BadRequest(str(e))
+
+    return fn
+
+
+def serve(state: ServerState, host: str = "127.0.0.1", port: int = 8080, install_signal_handlers: bool = True):
+    """Blocks until SIGINT / SIGTERM (graceful: in-flight requests finish)."""
+    httpd = ThreadingHTTPServer((host, port), make_handler(state))
+    if install_signal_handlers:
+        def stop(*_):
+            state.ready = False
+            threading.Thread(target=httpd.shutdown, daemon=True).start()
+        signal.signal(signal.SIGINT, stop)
+        signal.signal(signal.SIGTERM, stop)
+    try:
+        httpd.serve_forever()
+    finally:
+        httpd.server_close()
+        state.shutdown()
+    return httpd
+
+
+def start_background(state: ServerState, host: str = "127.0.0.1", port: int = 0):
+    """Starts the server on a thread (tests, notebooks); returns (httpd, thread).  port 0 picks a free port."""
+    httpd = ThreadingHTTPServer((host, port), make_handler(state))
+    th = threading.Thread(target=httpd.serve_forever, daemon=True)
+    th.start()
+    return httpd, th
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description="rustral-b200 inference server")
+    ap.add_argument("--artifact", required=True, help="safetensors file of one Linear (keys weight, bias)")
+    ap.add_argument("--bind", default="127.0.0.1:8080")
+    ap.add_argument("--in-features", type=int, required=True)
+    ap.add_argument("--out-features", type=int, required=True)
+    ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--device", default="cpu")
+    a = ap.parse_args(argv)
+    from ..core import B200Backend, CpuBackend
+    from ..nn.linear import LinearBuilder
+    from ..runtime.model_io import load_model_from_path
+    backend = CpuBackend() if a.device == "cpu" else B200Backend()
+    lin = LinearBuilder(a.in_features, a.out_features).with_bias(a.bias).build(backend)
+    load_model_from_path(lin, a.artifact)          # strict: missing / extra keys and shape mismatches are errors
+    host, port = a.bind.rsplit(":", 1)
+    state = ServerState(linear_infer_fn(lin, a.in_features),
+                        metadata={"model": "linear", "in_features": a.in_features, "out_features": a.out_features,
+                                  "bias": a.bias, "backend": backend.name})
+    serve(state, host, int(port))
+
+
+if __name__ == "__main__":
+    main()

@@ -201,3 +201,56 @@ def test_dropout(cuda_status):
     yp, mp = ops.dropout(x.cuda(), 0.25, True, seed=123, rng="pcg", return_mask=True)
     from rustral_b200.ops.elementwise import dropout_mask_reference
     assert torch.equal(mp.bool().cpu(), dropout_mask_reference(100000, 0.25, 123))
+
+
+@pytest.mark.parametrize("H,Hk,D", [(4, 4, 64), (8, 2, 128), (32, 8, 128), (12, 1, 64)])
+def test_paged_attention_and_kv_append(H, Hk, D, cuda_status):
+    from rustral_b200.ops import paged
+    torch.manual_seed(0)
+    nb, bs, B = 64, 16, 5
+    ctx = torch.tensor([1, 16, 17, 100, 333], dtype=torch.int32)
+    kc = torch.zeros(nb, bs, Hk, D, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    perm = torch.randperm(nb)
+    max_blocks = 21
+    bt = torch.zeros(B, max_blocks, dtype=torch.int32)
+    used = 0
+    for b in range(B):
+        n = (int(ctx[b]) + bs - 1) // bs
+        bt[b, :n] = perm[used:used + n].to(torch.int32)
+        used += n
+    # fill the caches through kv_append (CPU reference and CUDA kernel) from random packed K/V rows
+    kcg, vcg = kc.cuda(), vc.cuda()
+    for b in range(B):
+        n = int(ctx[b])
+        kv = _bf((n, 2 * Hk * D), 10 + b)
+        toks = torch.arange(n)
+        slots = bt[b, toks // bs].long() * bs + toks % bs
+        paged.kv_append(kv[:, :Hk * D], kv[:, Hk * D:], kc, vc, slots)
+        kvg = kv.cuda()
+        paged.kv_append(kvg[:, :Hk * D], kvg[:, Hk * D:], kcg, vcg, slots.cuda())
+    assert torch.equal(kcg.cpu(), kc) and torch.equal(vcg.cpu(), vc)
+    q = _bf((B, H * D), 3)
+    ref = paged.paged_attention_decode(q, kc, vc, bt, ctx)
+    out = paged.paged_attention_decode(q.cuda(), kcg, vcg, bt.cuda(), ctx.cuda())
+    _close(out, ref, what="paged decode")
+
+
+def test_rope_and_swiglu(cuda_status):
+    from rustral_b200.ops import rotary
+    B, S, H, D = 2, 48, 6, 64
+    x = _bf((B * S, H * D + 32), 1)
+    for inverse in (False, True):
+        xc, xg = x.clone(), x.cuda().clone()
+        rotary.rope_(xc, H, D, S, theta=500000.0, inverse=inverse)
+        rotary.rope_(xg, H, D, S, theta=500000.0, inverse=inverse)
+        _close(xg, xc, what="rope")
+        assert torch.equal(xg[:, H * D:].cpu(), x[:, H * D:])        # columns past the heads are untouched
+    pos = torch.randint(0, 4000, (B * S,))
+    xc, xg = x.clone(), x.cuda().clone()
+    rotary.rope_(xc, H, D, positions=pos, theta=10000.0)
+    rotary.rope_(xg, H, D, positions=pos.cuda(), theta=10000.0)
+    _close(xg, xc, what="rope positions")
+    gu, dh = _bf((70, 256), 2), _bf((70, 128), 3)
+    _close(rotary.swiglu_forward(gu.cuda()), rotary.swiglu_forward(gu), what="swiglu")
+    _close(rotary.swiglu_backward(dh.cuda(), gu.cuda()), rotary.swiglu_backward(dh, gu), what="swiglu bwd")

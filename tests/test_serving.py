@@ -1,0 +1,126 @@
+"""Serving stack on the CPU reference path: caches, scheduler, engine (paged decode == full re-forward), HTTP."""
+import json
+import urllib.request
+
+import pytest
+import torch
+
+from rustral_b200.models.config import preset
+from rustral_b200.runtime.fused_gpt import FusedGPTEngine
+from rustral_b200.serve import (CacheConfig, KVCache, ModelRunner, PagedCache, RequestPriority, Sampler, Scheduler,
+                                SchedulingPolicy, ServingEngine, SlidingWindowCache, run_poisson_workload)
+
+
+def test_kv_cache_append_stores_values_and_rejects_overflow():
+    c = KVCache(CacheConfig(num_heads=4, head_dim=8, max_seq_len=6).with_gqa(2))
+    k, v = torch.randn(1, 2, 4, 8), torch.randn(1, 2, 4, 8)
+    c.append(k, v)
+    kk, vv = c.get()
+    assert kk.shape == (1, 2, 4, 8) and torch.allclose(kk.float(), k, atol=1e-2) and torch.allclose(vv.float(), v, atol=1e-2)
+    with pytest.raises(Exception):
+        c.append(torch.randn(1, 2, 3, 8), torch.randn(1, 2, 3, 8))
+    assert CacheConfig(32, 128, 4096, num_layers=32).with_gqa(8).memory_bytes() == 2 * 8 * 4096 * 128 * 32 * 2
+
+
+def test_sliding_window_keeps_last_entries_in_order():
+    c = SlidingWindowCache(CacheConfig(1, 2, 100), window=3)
+    for i in range(5):
+        c.append(torch.full((1, 1, 1, 2), float(i)), torch.full((1, 1, 1, 2), float(i)))
+    k, _ = c.get()
+    assert k[0, 0, :, 0].float().tolist() == [2.0, 3.0, 4.0]
+
+
+def test_paged_cache_second_allocate_extends_table():
+    pc = PagedCache(8, 16, allocate_storage=False)
+    assert pc.allocate(7, 20) and pc.block_table(7) == [0, 1]
+    assert pc.allocate(7, 40) and pc.block_table(7) == [0, 1, 2]       # extended, not overwritten
+    assert pc.slot(7, 33) == 2 * 16 + 1
+    assert not pc.allocate(9, 16 * 6) and pc.free_blocks == 5          # refused, nothing leaked
+    assert pc.free(7) == 3 and pc.free_blocks == 8 and pc.block_table(7) == []
+
+
+def test_scheduler_admission_policy_and_memory_pressure():
+    pc = PagedCache(4, 16, allocate_storage=False)
+    s = Scheduler(pc, max_batch_size=8, policy=SchedulingPolicy.PRIORITY)
+    a = s.add_request(list(range(20)), 4, RequestPriority.LOW)
+    b = s.add_request(list(range(20)), 4, RequestPriority.HIGH)
+    c = s.add_request(list(range(40)), 4, RequestPriority.LOW)        # does not fit while a and b run
+    batch = s.schedule()
+    assert batch.request_ids == [b, a] and all(batch.is_prefill)
+    s.update({a: 5, b: 6})
+    batch = s.schedule()
+    assert batch.input_ids == [[6], [5]] and not any(batch.is_prefill)
+    for _ in range(3):
+        s.update({a: 1, b: 1})
+        batch = s.schedule()
+    assert s.stats.completed == 2 and batch.request_ids == [c]
+    assert pc.free_blocks == 4 - 3
+
+
+def test_engine_paged_decode_matches_full_reforward():
+    for name in ("gpt2-test", "llama-test"):
+        cfg = preset(name, seq_len=64, d_model=64, ffn_dim=128)
+        runner = ModelRunner(cfg, device="cpu", num_blocks=32)
+        eng = ServingEngine(runner, max_batch_size=4)
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 17, 9)]
+        ids = [eng.submit(p, 5) for p in prompts]
+        eng.run_to_completion()
+        ref = FusedGPTEngine(cfg, "cpu")
+        ref.params = runner.params
+        for p, rid in zip(prompts, ids):
+            toks = list(p)
+            for _ in range(5):
+                pad = toks + [0] * (cfg.seq_len - len(toks))
+                toks.append(int(ref.logits(torch.tensor([pad]))[0, len(toks) - 1].argmax()))
+            assert eng.scheduler.get(rid).generated == toks[len(p):]
+        assert runner.cache.free_blocks == 32
+        m = eng.metrics(1.0)
+        assert m.completed == 3 and m.output_tokens == 15 and m.ttft_p50_ms >= 0
+
+
+def test_poisson_workload_and_sampler():
+    cfg = preset("gpt2-test", seq_len=64, d_model=64, ffn_dim=128)
+    eng = ServingEngine(ModelRunner(cfg, device="cpu", num_blocks=64), max_batch_size=8)
+    m = run_poisson_workload(eng, 6, rate_per_s=200.0, prompt_range=(4, 12), output_range=(2, 4), seed=1)
+    assert m.completed == 6 and m.output_tokens >= 12 and m.output_tokens_per_s > 0
+    s = Sampler(temperature=1.0, top_k=5, top_p=0.9, seed=3)
+    logits = torch.randn(4, 50)
+    t = s.sample(logits)
+    top5 = logits.topk(5, -1).indices
+    assert all(int(t[i]) in top5[i].tolist() for i in range(4))
+    assert Sampler.greedy().sample(logits).tolist() == logits.argmax(-1).tolist()
+
+
+def test_http_server_routes_and_validation(tmp_path):
+    from rustral_b200.core import CpuBackend
+    from rustral_b200.nn.linear import LinearBuilder
+    from rustral_b200.runtime.model_io import load_model_from_path, save_model_to_path
+    from rustral_b200.serve.http_server import ServerState, linear_infer_fn, start_background
+    b = CpuBackend()
+    lin = LinearBuilder(4, 3).with_bias().build(b)
+    path = str(tmp_path / "lin.safetensors")
+    save_model_to_path(lin, path)
+    lin2 = LinearBuilder(4, 3).with_bias().seed(9).build(b)
+    load_model_from_path(lin2, path)
+    state = ServerState(linear_infer_fn(lin2, 4), metadata={"model": "linear"})
+    httpd, _ = start_background(state)
+    base = f"http://127.0.0.1:{httpd.server_address[1]}"
+    try:
+        assert json.load(urllib.request.urlopen(base + "/health"))["status"] == "ok"
+        assert json.load(urllib.request.urlopen(base + "/v1/metadata"))["model"] == "linear"
+        req = urllib.request.Request(base + "/v1/infer", json.dumps({"input": [[1, 2, 3, 4]]}).encode(),
+                                     {"Content-Type": "application/json"})
+        out = json.load(urllib.request.urlopen(req))["output"]
+        want = lin(torch.tensor([[1., 2., 3., 4.]])).tolist()
+        assert torch.allclose(torch.tensor(out), torch.tensor(want), atol=1e-5)
+        for bad in ({"input": []}, {"input": [[1, 2]]}):
+            req = urllib.request.Request(base + "/v1/infer", json.dumps(bad).encode())
+            with pytest.raises(urllib.error.HTTPError) as e:
+                urllib.request.urlopen(req)
+            assert e.value.code == 400
+        text = urllib.request.urlopen(base + "/metrics").read().decode()
+        assert "rustral_infer_requests_total 3" in text and "rustral_infer_errors_total 2" in text
+    finally:
+        httpd.shutdown()
+        state.shutdown()
