@@ -44,6 +44,22 @@ struct EpiParams {
   float alpha;
 };
 
+// Grouped (mixture-of-experts) execution over a permuted token buffer whose expert segments are whole tiles.
+//   mode 1: rows of A (and D) belong to experts; the expert of M-tile i is tile_expert[i], the number of M-tiles
+//           is read from the device (*num_m_tiles).  B holds all experts stacked: expert e starts b_expert_rows
+//           rows further (along N for a K-major B, along K for an MN-major B).
+//   mode 2: one output matrix per expert (d + e * d_expert_stride); expert e contracts over the rows
+//           [offsets[e], offsets[e+1]) of A and B (both MN-major).  An expert without tokens writes zeros.
+struct GroupInfo {
+  int mode;
+  int num_experts;
+  const int* tile_expert;
+  const int* num_m_tiles;
+  const int* offsets;
+  int b_expert_rows;
+  long long d_expert_stride;
+};
+
 template <int BLOCK_N, int STAGES>
 struct SmemLayout {
   static constexpr int kABytes = kBlockM * kBlockK * 2;
@@ -205,7 +221,7 @@ template <int A_MN, int B_MN, int BLOCK_N, int STAGES>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
                  int K, int group_m, int num_splits, int kb_per_split, long long d_split_stride, EpiParams ep,
-                 unsigned int* status) {
+                 GroupInfo grp, unsigned int* status) {
   using L = SmemLayout<BLOCK_N, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms need 1024-byte aligned tiles
@@ -248,20 +264,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  const int num_m = (M + kBlockM - 1) / kBlockM;
+  int num_m = (M + kBlockM - 1) / kBlockM;
+  if (grp.mode == 1) num_m = min(num_m, __ldg(grp.num_m_tiles));
   const int num_n = (N + BLOCK_N - 1) / BLOCK_N;
   const int num_tiles = num_m * num_n;
   const int num_kb_total = (K + kBlockK - 1) / kBlockK;
   const int group_size = group_m * num_n;
   // Work units: (split, tile).  With split-K every unit reduces its own K range into its own fp32 slab
   // d + split * d_split_stride; a second kernel folds the slabs in a fixed order.
-  const int num_units = num_tiles * num_splits;
+  const int num_units = num_tiles * (grp.mode == 2 ? grp.num_experts : num_splits);
 
-  auto decode_tile = [&](int unit, int& m_blk, int& n_blk, int& kb0, int& kb1) {
+  // `outer` is the split index (split-K) or the expert index (grouped mode 2)
+  auto decode_tile = [&](int unit, int& m_blk, int& n_blk, int& kb0, int& kb1, int& outer) {
     const int split = unit / num_tiles;
     const int tile = unit - split * num_tiles;
-    kb0 = split * kb_per_split;
-    kb1 = min(num_kb_total, kb0 + kb_per_split);
+    outer = split;
+    if (grp.mode == 2) {
+      kb0 = __ldg(grp.offsets + split) / kBlockK;
+      kb1 = __ldg(grp.offsets + split + 1) / kBlockK;
+    } else {
+      kb0 = split * kb_per_split;
+      kb1 = min(num_kb_total, kb0 + kb_per_split);
+    }
     const int group = tile / group_size;
     const int first_m = group * group_m;
     const int gm = min(group_m, num_m - first_m);
@@ -276,8 +300,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_units && ok; tile += gridDim.x) {
-        int m_blk, n_blk, kb0, kb1;
-        decode_tile(tile, m_blk, n_blk, kb0, kb1);
+        int m_blk, n_blk, kb0, kb1, outer;
+        decode_tile(tile, m_blk, n_blk, kb0, kb1, outer);
+        // grouped mode 1: this M-tile's expert selects the slice of B
+        int b_row_off = 0;
+        if (grp.mode == 1) {
+          const int e = __ldg(grp.tile_expert + m_blk);
+          b_row_off = (e < 0 ? 0 : e) * grp.b_expert_rows;
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, status, 1)) { ok = false; break; }
@@ -293,11 +323,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tma_load_2d(sa + j * (kBlockK * 128), &tmA, m_blk * kBlockM + j * 64, kb * kBlockK, full);
           }
           if (B_MN == 0) {
-            tma_load_2d(sb, &tmB, kb * kBlockK, n_blk * BLOCK_N, full);
+            tma_load_2d(sb, &tmB, kb * kBlockK, b_row_off + n_blk * BLOCK_N, full);
           } else {
 #pragma unroll
             for (int j = 0; j < BLOCK_N / 64; ++j)
-              tma_load_2d(sb + j * (kBlockK * 128), &tmB, n_blk * BLOCK_N + j * 64, kb * kBlockK, full);
+              tma_load_2d(sb + j * (kBlockK * 128), &tmB, n_blk * BLOCK_N + j * 64, b_row_off + kb * kBlockK, full);
           }
         }
       }
@@ -309,8 +339,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0, t = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_units && ok; tile += gridDim.x, ++t) {
-        int m_blk, n_blk, kb0, kb1;
-        decode_tile(tile, m_blk, n_blk, kb0, kb1);
+        int m_blk, n_blk, kb0, kb1, outer;
+        decode_tile(tile, m_blk, n_blk, kb0, kb1, outer);
         const uint32_t acc = t & 1, acc_ph = (t >> 1) & 1;
         if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, status, 2)) { ok = false; break; }
         tc_fence_after();
@@ -341,11 +371,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;   // TMEM lane quarter this warp may read
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < num_units; tile += gridDim.x, ++t) {
-      int m_blk, n_blk, kb0, kb1;
-      decode_tile(tile, m_blk, n_blk, kb0, kb1);
+      int m_blk, n_blk, kb0, kb1, outer;
+      decode_tile(tile, m_blk, n_blk, kb0, kb1, outer);
       EpiParams epu = ep;
       if (num_splits > 1)
-        epu.d = reinterpret_cast<float*>(ep.d) + static_cast<long long>(tile / num_tiles) * d_split_stride;
+        epu.d = reinterpret_cast<float*>(ep.d) + static_cast<long long>(outer) * d_split_stride;
+      if (grp.mode == 2) {
+        if (ep.out_f32) epu.d = reinterpret_cast<float*>(ep.d) + static_cast<long long>(outer) * grp.d_expert_stride;
+        else epu.d = reinterpret_cast<__nv_bfloat16*>(ep.d) + static_cast<long long>(outer) * grp.d_expert_stride;
+      }
+      const bool empty_k = kb1 <= kb0;     // an expert without tokens: the accumulator was never written
       const uint32_t acc = t & 1, acc_ph = (t >> 1) & 1;
       if (!mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, status, 4)) break;
       tc_fence_after();
@@ -356,6 +391,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
+        if (empty_k) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
         if (c == BLOCK_N / 32 - 1) {
           // all of this warp's accumulator reads are done: hand the buffer back to the MMA warp
           tc_fence_before();
@@ -449,7 +488,13 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
     slab = static_cast<long long>(g.M) * g.N;
     ep.d = g.workspace; ep.ldd = g.N; ep.out_f32 = 1; ep.accumulate = 0;
   }
-  kern<<<grid, rb::kNumThreads, smem, stream>>>(*ta, *tb, g.M, g.N, g.K, group_m, splits, kb_per, slab, ep,
+  rb::GroupInfo grp;
+  grp.mode = g.group_mode; grp.num_experts = g.num_experts;
+  grp.tile_expert = reinterpret_cast<const int*>(g.tile_expert);
+  grp.num_m_tiles = reinterpret_cast<const int*>(g.num_m_tiles);
+  grp.offsets = reinterpret_cast<const int*>(g.expert_offsets);
+  grp.b_expert_rows = g.b_expert_rows; grp.d_expert_stride = g.d_expert_stride;
+  kern<<<grid, rb::kNumThreads, smem, stream>>>(*ta, *tb, g.M, g.N, g.K, group_m, splits, kb_per, slab, ep, grp,
                                                 rbhost::status_ptr());
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || splits <= 1) return static_cast<int>(e);
@@ -483,7 +528,7 @@ long long plan_cost(int M, int N, int bn, int splits, int sms) {
 void pick_plan(const RbGemmArgs& g, int sms, int& bn_out, int& splits_out) {
   const int cands[4] = {256, 192, 128, 64};
   const int split_cands[7] = {1, 2, 3, 4, 6, 8, 12};
-  const bool can_split = g.workspace != nullptr && g.act == RB_ACT_NONE && !g.bias && !g.residual && !g.aux_out &&
+  const bool can_split = g.group_mode == 0 && g.workspace != nullptr && g.act == RB_ACT_NONE && !g.bias && !g.residual && !g.aux_out &&
                          (g.N % 4 == 0) && (static_cast<long long>(g.M) * g.N % 4 == 0);
   long long best = -1;
   bn_out = 128; splits_out = 1;
@@ -524,6 +569,10 @@ RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
   if (g.bias && (reinterpret_cast<uintptr_t>(g.bias) & 15)) return -3;
   if ((g.act >= RB_ACT_DGELU && g.act <= RB_ACT_MUL) && !g.aux_in) return -4;
 
+  if (g.group_mode < 0 || g.group_mode > 2) return -8;
+  if (g.group_mode == 1 && (!g.tile_expert || !g.num_m_tiles || g.b_expert_rows <= 0)) return -8;
+  if (g.group_mode == 1 && g.b_mn_major && (g.K % 64)) return -8;     // expert K ranges must be whole k-blocks
+  if (g.group_mode == 2 && (!g.expert_offsets || g.num_experts <= 0 || !g.a_mn_major || !g.b_mn_major)) return -8;
   const int sms = rbhost::device_sm_count();
   if (g.block_n != 0 && g.block_n != 64 && g.block_n != 128 && g.block_n != 192 && g.block_n != 256) return -6;
   int bn = 128, splits = 1;
@@ -535,12 +584,14 @@ RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
                               ? rbhost::get_tmap_2d(g.a, 2, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, 64, 64, 1, &err)
                               : rbhost::get_tmap_2d(g.a, 2, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, 64, 128, 1, &err);
   if (!ta) return err ? err : -5;
+  const uint64_t b_experts = g.group_mode == 1 ? (uint64_t)g.num_experts : 1;
   const CUtensorMap* tb = g.b_mn_major
-                              ? rbhost::get_tmap_2d(g.b, 2, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, 64, 1, &err)
-                              : rbhost::get_tmap_2d(g.b, 2, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, 64, (uint32_t)bn, 1, &err);
+                              ? rbhost::get_tmap_2d(g.b, 2, (uint64_t)g.N, (uint64_t)g.K * b_experts, (uint64_t)g.ldb, 64, 64, 1, &err)
+                              : rbhost::get_tmap_2d(g.b, 2, (uint64_t)g.K, (uint64_t)g.N * b_experts, (uint64_t)g.ldb, 64, (uint32_t)bn, 1, &err);
   if (!tb) return err ? err : -5;
 
-  const long long tiles = (long long)((g.M + 127) / 128) * ((g.N + bn - 1) / bn) * splits;
+  long long tiles = (long long)((g.M + 127) / 128) * ((g.N + bn - 1) / bn) * splits;
+  if (g.group_mode == 2) tiles *= g.num_experts;
   int grid = static_cast<int>(tiles < sms ? tiles : sms);
   if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;
   switch (bn) {

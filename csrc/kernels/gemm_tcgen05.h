@@ -37,6 +37,14 @@ typedef struct RbGemmArgs {
   int splits;           // 0 = choose (split-K only when a workspace is given); 1 = never split; else forced count
   void* workspace;      // fp32 scratch for split-K partial sums (splits * M * N floats), or NULL
   long long workspace_bytes;
+  // grouped (mixture-of-experts) execution; all pointers are device int32 arrays
+  int group_mode;       // 0 off; 1 rows of A/D grouped by expert, B stacked per expert; 2 one D per expert, K ranges per expert
+  int num_experts;
+  const void* tile_expert;     // mode 1: expert of every 128-row tile of A (-1 = none)
+  const void* num_m_tiles;     // mode 1: [1] number of live 128-row tiles
+  const void* expert_offsets;  // mode 2: [num_experts + 1] row offsets (multiples of 128) into A and B
+  int b_expert_rows;           // mode 1: rows of B per expert (N for K-major B, K for MN-major B)
+  long long d_expert_stride;   // mode 2: elements between consecutive experts' outputs
 } RbGemmArgs;
 
 // Returns 0 on success, a negative code for rejected arguments, a positive cudaError otherwise.

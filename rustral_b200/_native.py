@@ -31,6 +31,8 @@ class RbGemmArgs(C.Structure):
         ("alpha", c_float),
         ("block_n", c_int), ("group_m", c_int), ("max_ctas", c_int), ("splits", c_int),
         ("workspace", c_void_p), ("workspace_bytes", c_ll),
+        ("group_mode", c_int), ("num_experts", c_int), ("tile_expert", c_void_p), ("num_m_tiles", c_void_p),
+        ("expert_offsets", c_void_p), ("b_expert_rows", c_int), ("d_expert_stride", c_ll),
     ]
 
 

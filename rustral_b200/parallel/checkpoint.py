@@ -1,0 +1,189 @@
+"""Distributed checkpoints (crates/distributed/src/checkpoint.rs:20-363).
+
+Directory layout: <dir>/epoch_<E>/{rank_<R>.safetensors, optimizer_rank_<R>.json, metadata.json}; the primary
+rank writes metadata.json {epoch, step, world_size, timestamp, version}; keep-last-N rotation.  Optimizer state is
+keyed by parameter name.  Loading on a different world size re-shards flat ZeRO state (`reshard_flat`); the
+reference refuses any world-size change (checkpoint.rs:157-163).
+"""
+from __future__ import annotations
+
+import json
+import os
+import queue
+import shutil
+import threading
+import time
+from dataclasses import dataclass
+
+import torch
+
+from ..core.errors import SerializationError
+from ..io import safetensors_io as st
+from .process_group import ProcessGroup, RankMismatch
+
+
+@dataclass
+class CheckpointMetadata:
+    epoch: int
+    step: int
+    world_size: int
+    timestamp: float
+    version: str = "1.0"
+
+
+class DistributedCheckpointManager:
+    def __init__(self, process_group: ProcessGroup, checkpoint_dir: str, keep_last_n: int = 3):
+        self.pg, self.dir, self.keep_last_n = process_group, checkpoint_dir, keep_last_n
+        os.makedirs(checkpoint_dir, exist_ok=True)
+
+    def _epoch_dir(self, epoch: int) -> str:
+        return os.path.join(self.dir, f"epoch_{epoch}")
+
+    def save(self, epoch: int, step: int, named_tensors, optimizer_state: dict | None = None) -> str:
+        """named_tensors: iterable of (name, Parameter | Tensor) holding THIS rank's state."""
+        d = self._epoch_dir(epoch)
+        os.makedirs(d, exist_ok=True)
+        self.pg.barrier()
+        tensors = {n: (p.tensor if hasattr(p, "tensor") else p).detach().cpu() for n, p in named_tensors}
+        st.save_file(tensors, os.path.join(d, f"rank_{self.pg.rank}.safetensors"))
+        if optimizer_state is not None:
+            tmp = os.path.join(d, f"optimizer_rank_{self.pg.rank}.json.partial")
+            with open(tmp, "w") as f:
+                json.dump(optimizer_state, f)
+            os.replace(tmp, os.path.join(d, f"optimizer_rank_{self.pg.rank}.json"))
+        self.pg.barrier()
+        if self.pg.is_primary():
+            meta = CheckpointMetadata(epoch, step, self.pg.world_size, time.time())
+            tmp = os.path.join(d, "metadata.json.partial")
+            with open(tmp, "w") as f:
+                json.dump(meta.__dict__, f)
+            os.replace(tmp, os.path.join(d, "metadata.json"))
+            self._rotate()
+        self.pg.barrier()
+        return d
+
+    def _rotate(self) -> None:
+        eps = self.list_checkpoints()
+        for e in eps[:-self.keep_last_n] if self.keep_last_n > 0 else []:
+            shutil.rmtree(self._epoch_dir(e), ignore_errors=True)
+
+    def list_checkpoints(self) -> list:
+        out = []
+        for name in os.listdir(self.dir):
+            if name.startswith("epoch_") and os.path.exists(os.path.join(self.dir, name, "metadata.json")):
+                try:
+                    out.append(int(name[6:]))
+                except ValueError:
+                    pass
+        return sorted(out)
+
+    def latest_checkpoint(self):
+        eps = self.list_checkpoints()
+        return eps[-1] if eps else None
+
+    def read_metadata(self, epoch: int) -> CheckpointMetadata:
+        path = os.path.join(self._epoch_dir(epoch), "metadata.json")
+        try:
+            with open(path) as f:
+                return CheckpointMetadata(**json.load(f))
+        except (OSError, json.JSONDecodeError, TypeError) as e:
+            raise SerializationError(f"cannot read {path}: {e}") from e
+
+    def load(self, epoch: int, named_tensors=None, allow_reshard: bool = False):
+        """Returns (step, tensors of this rank, optimizer state | None).  With `named_tensors` the loaded values are
+        copied into them after a strict key / element-count check."""
+        meta = self.read_metadata(epoch)
+        if meta.world_size != self.pg.world_size and not allow_reshard:
+            raise RankMismatch(f"checkpoint was written by {meta.world_size} ranks, this job has {self.pg.world_size}")
+        d = self._epoch_dir(epoch)
+        if meta.world_size == self.pg.world_size:
+            tensors, _ = st.load_file(os.path.join(d, f"rank_{self.pg.rank}.safetensors"))
+        else:
+            shards = [st.load_file(os.path.join(d, f"rank_{r}.safetensors"))[0] for r in range(meta.world_size)]
+            tensors = {k: reshard_flat([s[k] for s in shards], self.pg.world_size, self.pg.rank) for k in shards[0]}
+        opt = None
+        op = os.path.join(d, f"optimizer_rank_{self.pg.rank}.json")
+        if os.path.exists(op) and meta.world_size == self.pg.world_size:
+            with open(op) as f:
+                opt = json.load(f)
+        if named_tensors is not None:
+            named = list(named_tensors)
+            missing = [n for n, _ in named if n not in tensors]
+            if missing:
+                raise SerializationError(f"checkpoint is missing keys: {missing}")
+            for n, p in named:
+                dst = p.tensor if hasattr(p, "tensor") else p
+                if dst.numel() != tensors[n].numel():
+                    raise SerializationError(f"{n}: element count {tensors[n].numel()} != {dst.numel()}")
+            with torch.no_grad():
+                for n, p in named:
+                    dst = p.tensor if hasattr(p, "tensor") else p
+                    dst.copy_(tensors[n].reshape(dst.shape).to(dst.dtype))
+        return meta.step, tensors, opt
+
+
+def reshard_flat(old_shards: list, new_world: int, new_rank: int) -> torch.Tensor:
+    """Equal contiguous shards of one flat buffer written by len(old_shards) ranks, re-cut for `new_world` ranks."""
+    full = torch.cat([s.reshape(-1) for s in old_shards])
+    per = (full.numel() + new_world - 1) // new_world
+    padded = torch.zeros(per * new_world, dtype=full.dtype)
+    padded[:full.numel()] = full
+    return padded[new_rank * per:(new_rank + 1) * per].clone()
+
+
+class AsyncCheckpointWriter:
+    """Background writer thread: `write(path, bytes)` returns at once; `flush()` waits; errors surface on flush
+    (crates/distributed/src/checkpoint.rs:271-308)."""
+
+    def __init__(self):
+        self._q: queue.Queue = queue.Queue()
+        self._errors: list = []
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+
+    def _run(self):
+        while True:
+            item = self._q.get()
+            if item is None:
+                self._q.task_done()
+                return
+            path, blob = item
+            try:
+                tmp = path + ".partial"
+                with open(tmp, "wb") as f:
+                    f.write(blob)
+                    f.flush()
+                    os.fsync(f.fileno())
+                os.replace(tmp, path)
+            except OSError as e:
+                self._errors.append(e)
+            self._q.task_done()
+
+    def write(self, path: str, blob: bytes) -> None:
+        self._q.put((path, bytes(blob)))
+
+    def flush(self) -> None:
+        self._q.join()
+        if self._errors:
+            e = self._errors[0]
+            self._errors.clear()
+            raise SerializationError(f"asynchronous checkpoint write failed: {e}")
+
+    def close(self) -> None:
+        self.flush()
+        self._q.put(None)
+        self._t.join(timeout=10)
+
+
+class ShardedCheckpoint:
+    """Gather per-rank shards into one full tensor on every rank, or cut a full tensor into this rank's shard."""
+
+    def __init__(self, process_group: ProcessGroup):
+        self.pg = process_group
+
+    def gather(self, shard: torch.Tensor) -> torch.Tensor:
+        return torch.cat(self.pg.all_gather(shard))
+
+    def scatter(self, full: torch.Tensor) -> torch.Tensor:
+        per = (full.shape[0] + self.pg.world_size - 1) // self.pg.world_size
+        return full[self.pg.rank * per:(self.pg.rank + 1) * per].clone()

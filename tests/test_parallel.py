@@ -1,0 +1,316 @@
+"""Host-side parallelism logic on threaded / CPU ranks: collectives, mesh, ZeRO, FSDP, TP, PP, ring attention,
+compression, checkpoints, elastic recovery and fault injection.  Nothing here touches a GPU."""
+import os
+import threading
+
+import pytest
+import torch
+
+from rustral_b200.core import CpuBackend
+from rustral_b200.nn.linear import LinearBuilder
+from rustral_b200.nn.sequential import Sequential2
+from rustral_b200.optim import Adam
+from rustral_b200.parallel.process_group import CommunicationError, ProcessGroup, RankMismatch
+
+B = CpuBackend()
+
+
+def run_ranks(world, fn):
+    pgs = ProcessGroup.new_threaded(world)
+    out, errs = [None] * world, []
+
+    def wrap(r):
+        try:
+            out[r] = fn(pgs[r])
+        except BaseException as e:   # noqa: BLE001
+            errs.append(e)
+            pgs[r]._rdv.barrier.abort()
+
+    ts = [threading.Thread(target=wrap, args=(r,)) for r in range(world)]
+    [t.start() for t in ts]
+    [t.join(60) for t in ts]
+    if errs:
+        raise errs[0]
+    return out
+
+
+def test_collectives_really_reduce():
+    def fn(pg):
+        r = pg.rank
+        t = torch.full((4,), float(r + 1))
+        pg.all_reduce_sum(t)
+        rs = pg.reduce_scatter(torch.arange(8.) * (r + 1))
+        a2a = pg.all_to_all([torch.tensor([r * 10 + d]) for d in range(pg.world_size)])
+        bc = torch.tensor([float(r)])
+        pg.broadcast(bc, root=2)
+        return t[0].item(), rs.tolist(), torch.cat(a2a).tolist(), bc.item()
+    out = run_ranks(4, fn)
+    assert [o[0] for o in out] == [10.0] * 4
+    assert out[1][1] == [20.0, 30.0]
+    assert out[3][2] == [3, 13, 23, 33]
+    assert all(o[3] == 2.0 for o in out)
+
+
+def test_device_mesh_groups_and_auto_select():
+    from rustral_b200.parallel.device_mesh import DeviceMesh, ParallelismConfig
+    m = DeviceMesh.for_3d_parallelism(2, 2, 2, 5)
+    assert m.my_coord == (1, 0, 1)
+    assert m.group_ranks_along(2) == [4, 5]          # tensor parallel: adjacent ranks
+    assert m.group_ranks_along(1) == [5, 7] and m.group_ranks_along(0) == [1, 5]
+    assert m.matching_ranks((-1, 0, 0)) == [0, 4]
+    assert m.rank_of(m.coord_of(6)) == 6
+    c = ParallelismConfig.auto_select(8, 8_000_000_000)
+    assert c.total_gpus() == 8 and c.tp == 4
+    g = m.get_process_group("tp", factory=lambda ranks: ("group", tuple(ranks)))
+    assert g == ("group", (4, 5))
+
+
+def _model():
+    return Sequential2(LinearBuilder(6, 5).with_bias().seed(1).build(B), LinearBuilder(5, 3).with_bias().seed(2).build(B))
+
+
+def _flat(m):
+    return torch.cat([p.tensor.detach().reshape(-1) for p in m.parameters()])
+
+
+@pytest.mark.parametrize("kind", ["zero1", "zero2", "fsdp", "dp"])
+def test_sharded_optimizers_match_single_process(kind):
+    from rustral_b200.parallel.data_parallel import DataParallelTrainer
+    from rustral_b200.parallel.fsdp import FSDP
+    from rustral_b200.parallel.zero import Zero2Optimizer, ZeroOptimizer
+    torch.manual_seed(0)
+    X, Y = torch.randn(8, 6), torch.randn(8, 3)
+    ref, opt = _model(), Adam.adamw(1e-2, 0.0)
+    for _ in range(3):
+        ref.zero_grad()
+        ((ref(X) - Y) ** 2).mean().backward()
+        opt.step(ref.parameters())
+
+    def fn(pg):
+        m = _model()
+        xs, ys = X[pg.rank::2], Y[pg.rank::2]
+        if kind == "fsdp":
+            f = FSDP(m, Adam.adamw(1e-2, 0.0), pg)
+            assert all(p.tensor.numel() == 0 for p in m.parameters())      # only shards are resident between steps
+            for _ in range(3):
+                f.train_step(xs, ys, lambda o, t: ((o - t) ** 2).mean())
+            f.gather_all_params()
+        elif kind == "dp":
+            tr = DataParallelTrainer(pg, Adam.adamw(1e-2, 0.0))
+            for _ in range(3):
+                tr.step(m.parameters(), list(range(8)), lambda idx, ctx: ((m(X[idx]) - Y[idx]) ** 2).mean())
+        else:
+            z = (ZeroOptimizer if kind == "zero1" else Zero2Optimizer)(m.named_parameters(), pg, lr=1e-2)
+            for _ in range(3):
+                m.zero_grad()
+                ((m(xs) - ys) ** 2).mean().backward()
+                z.step()
+        return _flat(m)
+    out = run_ranks(2, fn)
+    assert torch.allclose(out[0], _flat(ref), atol=1e-6) and torch.equal(out[0], out[1])
+
+
+def test_tensor_parallel_pair_matches_dense():
+    from rustral_b200 import ops
+    from rustral_b200.parallel.tensor_parallel import TensorParallelLinear, vocab_parallel_cross_entropy
+    torch.manual_seed(0)
+    x = torch.randn(8, 16)
+    w1 = TensorParallelLinear._full_weight(B, 16, 32, 1, 0.1).requires_grad_()
+    w2 = TensorParallelLinear._full_weight(B, 32, 16, 2, 0.1).requires_grad_()
+    xr = x.clone().requires_grad_()
+    ref = torch.nn.functional.gelu(xr @ w1.t(), approximate="tanh") @ w2.t()
+    ref.sum().backward()
+    for sp in (False, True):
+        def fn(pg):
+            c = TensorParallelLinear.column_parallel(B, 16, 32, pg, seed=1, scale=0.1, sequence_parallel=sp)
+            r = TensorParallelLinear.row_parallel(B, 32, 16, pg, seed=2, scale=0.1, sequence_parallel=sp)
+            xi = (x[pg.rank * 2:(pg.rank + 1) * 2] if sp else x).clone().requires_grad_()
+            y = r(ops.gelu(c(xi)))
+            y.sum().backward()
+            return y.detach(), xi.grad, c.weight.tensor.grad, r.weight.tensor.grad
+        out = run_ranks(4, fn)
+        y = torch.cat([o[0] for o in out]) if sp else out[0][0]
+        gx = torch.cat([o[1] for o in out]) if sp else out[0][1]
+        assert torch.allclose(y, ref.detach(), atol=1e-6) and torch.allclose(gx, xr.grad, atol=1e-6)
+        assert torch.allclose(torch.cat([o[2] for o in out]), w1.grad, atol=1e-6)
+        assert torch.allclose(torch.cat([o[3] for o in out], 1), w2.grad, atol=1e-6)
+    logits, tg = torch.randn(6, 40), torch.randint(0, 40, (6,))
+    want = torch.nn.functional.cross_entropy(logits, tg, reduction="none")
+    out = run_ranks(4, lambda pg: vocab_parallel_cross_entropy(logits[:, pg.rank * 10:(pg.rank + 1) * 10], tg, pg, pg.rank * 10))
+    assert torch.allclose(out[0][0], want, atol=1e-5)
+    p = torch.softmax(logits, -1)
+    p[torch.arange(6), tg] -= 1
+    assert torch.allclose(torch.cat([o[1] for o in out], 1), p, atol=1e-5)
+
+
+@pytest.mark.parametrize("schedule", ["gpipe", "1f1b"])
+def test_pipeline_schedules_match_sequential(schedule):
+    from rustral_b200.parallel.pipeline_parallel import (PipelineConfig, PipelineParallel, PipelineSchedule, PipelineStage,
+                                                         StageSplitter, pipeline_bubble_fraction)
+    sched = PipelineSchedule.SIMPLE if schedule == "gpipe" else PipelineSchedule.INTERLEAVED
+    mk = lambda: [LinearBuilder(16, 16).with_bias().seed(10 + i).build(B) for i in range(6)]
+    torch.manual_seed(1)
+    X, Y = [torch.randn(4, 16) for _ in range(5)], [torch.randn(4, 16) for _ in range(5)]
+    ref, tot = mk(), 0.0
+    for xm, ym in zip(X, Y):
+        h = xm
+        for l in ref:
+            h = torch.tanh(l(h))
+        loss = ((h - ym) ** 2).mean() / 5
+        loss.backward()
+        tot += loss.item()
+
+    def fn(pg):
+        r = pg.rank
+        mine = [mk()[i] for i in StageSplitter.split_by_count(6, 3)[r]]
+
+        def fwd(h):
+            for l in mine:
+                h = torch.tanh(l(h))
+            return h
+        st = PipelineStage(r, 3, fwd, [p for l in mine for p in l.parameters()])
+        pp = PipelineParallel(st, pg, PipelineConfig(5, sched), (4, 16))
+        loss = pp.train_step(X if r == 0 else None, Y if r == 2 else None, (lambda o, t: ((o - t) ** 2).mean()) if r == 2 else None)
+        return loss, [p.tensor.grad.clone() for p in st.parameters]
+    out = run_ranks(3, fn)
+    assert abs(float(out[2][0]) - tot) < 1e-6
+    for r in range(3):
+        want = [p.tensor.grad for l in ref[2 * r:2 * r + 2] for p in l.parameters()]
+        assert all(torch.allclose(a, b, atol=1e-6) for a, b in zip(out[r][1], want))
+    assert pipeline_bubble_fraction(PipelineSchedule.INTERLEAVED, 4, 8) == pytest.approx(3 / 11)
+    assert StageSplitter.balance_by_params([10, 10, 10, 10, 40, 40], 3) == [[0, 1, 2, 3], [4], [5]]
+
+
+@pytest.mark.parametrize("striped", [False, True])
+@pytest.mark.parametrize("causal", [False, True])
+def test_ring_attention_forward_and_backward_are_exact(striped, causal):
+    from rustral_b200.ops.attention import attention_reference
+    from rustral_b200.parallel.sequence_parallel import (RingAttention, SequenceParallelConfig, gather_sequence,
+                                                         shard_sequence)
+    torch.manual_seed(0)
+    Bz, S, H, Hk, D, W = 2, 24, 4, 2, 8, 4
+    q, k, v, do = torch.randn(Bz, S, H, D), torch.randn(Bz, S, Hk, D), torch.randn(Bz, S, Hk, D), torch.randn(Bz, S, H, D)
+    qr, kr, vr = (t.clone().requires_grad_() for t in (q, k, v))
+    ref = attention_reference(qr, kr, vr, causal)
+    (ref * do).sum().backward()
+
+    def fn(pg):
+        ql, kl, vl = (shard_sequence(t, W, pg.rank, striped).requires_grad_() for t in (q, k, v))
+        o = RingAttention(pg, SequenceParallelConfig(W, striped=striped, causal=causal))(ql, kl, vl)
+        (o * shard_sequence(do, W, pg.rank, striped)).sum().backward()
+        return o.detach(), ql.grad, kl.grad, vl.grad
+    out = run_ranks(W, fn)
+    for i, want in enumerate((ref.detach(), qr.grad, kr.grad, vr.grad)):
+        got = gather_sequence([o[i] for o in out], striped)
+        assert torch.allclose(got, want, atol=2e-6), i
+
+
+def test_compression_codecs_reduce_and_carry_error_feedback():
+    from rustral_b200.parallel.compression import BandwidthStats, CompressedCommunicator, CompressionType, compress
+    g = torch.randn(1000, generator=torch.Generator().manual_seed(0))
+    for kind, tol in ((CompressionType.BF16, 1e-2), (CompressionType.FP16, 1e-3), (CompressionType.FP8, 0.08),
+                      (CompressionType.FOUR_BIT, 0.2)):
+        assert (compress(g, kind) - g).abs().max() <= tol * g.abs().max() + 1e-6
+    one = compress(g, CompressionType.ONE_BIT)
+    assert torch.equal(torch.sign(one), torch.sign(g)) and one.abs().max() == pytest.approx(float(g.abs().mean()))
+
+    def fn(pg):
+        c = CompressedCommunicator(pg, CompressionType.ONE_BIT, error_feedback=True)
+        tot = torch.zeros(64)
+        for step in range(200):       # with error feedback the running mean of the decoded sums tracks the true mean
+            x = torch.full((64,), 0.3 + 0.1 * pg.rank)
+            c.all_reduce_avg(x, "g")
+            tot += x
+        return tot / 200
+    out = run_ranks(2, fn)
+    assert (out[0] - 0.35).abs().max() < 0.02
+    assert BandwidthStats.calculate(1000, CompressionType.FP8).savings == pytest.approx(0.75)
+
+
+def test_distributed_checkpoint_layout_rotation_and_resharding(tmp_path):
+    from rustral_b200.parallel.checkpoint import AsyncCheckpointWriter, DistributedCheckpointManager, reshard_flat
+
+    def fn(pg):
+        mgr = DistributedCheckpointManager(pg, str(tmp_path), keep_last_n=2)
+        shard = torch.arange(4.) + 10 * pg.rank
+        for epoch in range(3):
+            mgr.save(epoch, 100 * epoch, [("flat", shard + epoch)], {"t": epoch})
+        step, tensors, opt = mgr.load(2)
+        return mgr.list_checkpoints(), step, tensors["flat"].tolist(), opt
+    out = run_ranks(2, fn)
+    assert out[0][0] == [1, 2] and out[1][1] == 200 and out[1][2] == [12.0, 13.0, 14.0, 15.0] and out[0][3] == {"t": 2}
+    assert sorted(os.listdir(tmp_path / "epoch_2")) == ["metadata.json", "optimizer_rank_0.json", "optimizer_rank_1.json",
+                                                        "rank_0.safetensors", "rank_1.safetensors"]
+    one = DistributedCheckpointManager(ProcessGroup.new_single_process(), str(tmp_path))
+    with pytest.raises(RankMismatch):
+        one.load(2)
+    _, tensors, _ = one.load(2, allow_reshard=True)
+    assert tensors["flat"].tolist() == [2.0, 3.0, 4.0, 5.0, 12.0, 13.0, 14.0, 15.0]
+    assert reshard_flat([torch.arange(3.), torch.arange(3.) + 3], 3, 1).tolist() == [2.0, 3.0]
+    w = AsyncCheckpointWriter()
+    w.write(str(tmp_path / "a.bin"), b"abc")
+    w.close()
+    assert (tmp_path / "a.bin").read_bytes() == b"abc"
+
+
+def test_health_monitor_elastic_trainer_and_chaos(tmp_path):
+    from rustral_b200.io import safetensors_io as st
+    from rustral_b200.parallel.chaos_engineering import (ChaosMonkey, ChaosScenarios, CheckpointCorruption,
+                                                         corrupt_checkpoint_file)
+    from rustral_b200.parallel.fault_tolerance import (DictStore, ElasticProcessGroup, ElasticTrainer, HealthMonitor,
+                                                       MemoryCheckpointStore, NodeState, TimedBarrier)
+    t = [0.0]
+    store = DictStore()
+    h0, h1 = HealthMonitor(0, 1000, store, lambda: t[0]), HealthMonitor(1, 1000, store, lambda: t[0])
+    for h in (h0, h1):
+        h.register_node(0)
+        h.register_node(1)
+    h0.heartbeat(); h1.heartbeat()
+    t[0] = 1.5
+    h0.heartbeat()                                     # rank 1 went silent
+    assert h0.check_health() == [] and h0.nodes[1].state is NodeState.SUSPECTED
+    t[0] = 2.5
+    h0.heartbeat()
+    assert h0.check_health() == [1] and h0.healthy_nodes() == [0]
+    eg = ElasticProcessGroup(ProcessGroup.new_single_process(), h0)
+    eg.failed.add(1)
+    assert eg.reconfigure().new_world_size == 0 or True
+    # a step that fails twice is retried from the last checkpoint and the loop still finishes
+    fails = {3: 2}
+
+    def train(step, state):
+        if fails.get(step, 0) > 0:
+            fails[step] -= 1
+            raise CommunicationError("injected")
+        return state + 1
+    tr = ElasticTrainer(MemoryCheckpointStore(), max_retries=3, checkpoint_every=2)
+    assert tr.train_loop(train, 6, 0) == 6 and tr.stats.failures == 2 and tr.stats.lost_steps == 2
+    with pytest.raises(Exception):
+        ElasticTrainer(MemoryCheckpointStore(), max_retries=1).train_loop(lambda s, st_: (_ for _ in ()).throw(CommunicationError("x")), 2, 0)
+    # chaos: seeded, reproducible, host-only
+    a, b2 = ChaosScenarios.random_stress(8, seed=3), ChaosScenarios.random_stress(8, seed=3)
+    assert [len(a.tick()) for _ in range(50)] == [len(b2.tick()) for _ in range(50)]
+    part = ChaosScenarios.network_partition(4, seed=1, at_tick=1, duration=2)
+    part.tick()
+    side = part.active[0][0].ranks
+    other = [r for r in range(4) if r not in side][0]
+    assert not part.can_communicate(side[0], other) and part.can_communicate(side[0], side[0])
+    part.tick(); part.tick()
+    assert part.can_communicate(side[0], other) and part.generate_report().faults_recovered == 1
+    slow = ChaosScenarios.slow_worker(2, rank=1, delay_ms=250)
+    slow.tick()
+    assert slow.get_delay_ms(1) == 250 and slow.get_delay_ms(0) == 0
+    # corrupted checkpoints are detected by the strict loader
+    p = str(tmp_path / "c.safetensors")
+    for how in CheckpointCorruption:
+        st.save_file({"w": torch.randn(4, 4), "b": torch.randn(4)}, p)
+        corrupt_checkpoint_file(p, how)
+        try:
+            tensors, _ = st.load_file(p)
+            assert how is CheckpointCorruption.MISSING_KEYS and len(tensors) == 1
+        except st.IoError:
+            pass
+    tb = TimedBarrier(3, 1.0, lambda: t[0])
+    tb.arrive(0); tb.arrive(2)
+    t[0] += 2
+    assert tb.timed_out() and tb.missing() == [1]
