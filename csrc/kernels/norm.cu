@@ -342,3 +342,37 @@ RB_API int rb_norm_bwd(const void* dy, long long lddy, const void* x, long long 
                                                                  accumulate);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// rb_norm_bwd_noalloc: the backward pass with its partial-sum scratch in a library-owned device array.
+// ---------------------------------------------------------------------------------------------------------------
+// Capacity of the built-in scratch: 2 x 296 partial rows of up to 4096 columns (9.25 MiB of fp32).  The array is
+// part of the library image, so every GPU that loads this library holds it until the process exits.
+constexpr long long kNoAllocScratchFloats = 2LL * 296 * 4096;
+static __device__ __align__(256) float g_norm_bwd_scratch[kNoAllocScratchFloats];
+
+RB_API long long rb_norm_bwd_noalloc_capacity_floats(void) { return kNoAllocScratchFloats; }
+
+RB_API int rb_norm_bwd_noalloc(const void* dy, long long lddy, const void* x, long long ldx, const void* gamma,
+                               const float* mean, const float* rstd, const void* dres, long long lddres, void* dx,
+                               long long lddx, float* dgamma, float* dbeta, int rows, int n, int rms, int accumulate,
+                               void* stream_v) {
+  // In host code the array's name is only a stand-in for the device symbol; the address a kernel can use has to be
+  // asked for, once per device and with that device current.
+  static float* scratch_by_device[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -20;
+  if (scratch_by_device[dev] == nullptr) {
+    float* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_norm_bwd_scratch);
+    if (e != cudaSuccess || p == nullptr) return e != cudaSuccess ? static_cast<int>(e) : -21;
+    scratch_by_device[dev] = p;
+  }
+  const int parts = rb_norm_bwd_num_partials(rows, n);
+  if (parts <= 0) return -1;                                                       // unsupported row length
+  if (2LL * parts * n > kNoAllocScratchFloats) return -22;                         // beyond the built-in scratch
+  // The partial rows are fully overwritten by the first kernel before the second one reads them, so nothing
+  // of an earlier call's contents needs clearing.
+  return rb_norm_bwd(dy, lddy, x, ldx, gamma, mean, rstd, dres, lddres, dx, lddx, dgamma, dbeta, scratch_by_device[dev],
+                     rows, n, rms, accumulate, stream_v);
+}
