@@ -1,0 +1,139 @@
+"""Recurrent cells (crates/nn/src/lstm.rs:10-470): LSTM (gate order i, f, o, g), GRU (standard equations: the reset gate
+is used, which the reference computes and ignores, lstm.rs:203-300), stacked and bidirectional wrappers."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from ..core import ForwardCtx, Module, Parameter, Saveable, StatefulModule, Trainable
+
+
+@dataclass
+class LstmConfig:
+    input_size: int
+    hidden_size: int
+
+
+class RnnCell(Module, Trainable, Saveable, StatefulModule):
+    hidden_size: int
+
+    def step(self, x, state, ctx):
+        raise NotImplementedError
+
+    def hidden_of(self, state):
+        return state
+
+    def forward_sequence(self, xs, ctx: ForwardCtx, state=None):
+        """xs: [T, B, I].  Returns (outputs [T, B, H], final state)."""
+        if state is None:
+            state = self.initial_state(xs.shape[1], ctx, xs)
+        outs = []
+        for t in range(xs.shape[0]):
+            state = self.step(xs[t], state, ctx)
+            outs.append(self.hidden_of(state))
+        return torch.stack(outs), state
+
+
+class LstmCell(RnnCell):
+    """Parameters wx [4H, I], wh [4H, H], b [4H]; the two gate matmuls are one fused GEMM each."""
+
+    def __init__(self, config: LstmConfig, wx: Parameter, wh: Parameter, b: Parameter):
+        self.config, self.wx, self.wh, self.b = config, wx, wh, b
+        self.hidden_size = config.hidden_size
+
+    @classmethod
+    def new(cls, backend, input_size: int, hidden_size: int, seed: int = 42):
+        s = hidden_size ** -0.5
+        return cls(LstmConfig(input_size, hidden_size), backend.uniform_parameter("wx", (4 * hidden_size, input_size), seed, s),
+                   backend.uniform_parameter("wh", (4 * hidden_size, hidden_size), seed + 1, s),
+                   backend.constant_parameter("b", (4 * hidden_size,), 0.0))
+
+    def initial_state(self, batch: int, ctx=None, like=None):
+        dev = self.wx.tensor.device
+        z = torch.zeros(batch, self.hidden_size, dtype=self.wx.tensor.dtype, device=dev)
+        return z, z.clone()
+
+    def hidden_of(self, state):
+        return state[0]
+
+    def step(self, x, state, ctx=None):
+        h, c = state
+        H = self.hidden_size
+        gates = ops.linear(x, self.wx.tensor, self.b.tensor) + ops.linear(h, self.wh.tensor)
+        gf = gates.float()
+        i, f, o, g = torch.sigmoid(gf[:, :H]), torch.sigmoid(gf[:, H:2 * H]), torch.sigmoid(gf[:, 2 * H:3 * H]), torch.tanh(gf[:, 3 * H:])
+        c2 = f * c.float() + i * g
+        h2 = o * torch.tanh(c2)
+        return h2.to(x.dtype), c2.to(x.dtype)
+
+    def forward(self, x_state, ctx=None):
+        x, state = x_state
+        return self.step(x, state, ctx)
+
+
+class GruCell(RnnCell):
+    def __init__(self, config: LstmConfig, wx: Parameter, wh: Parameter, b: Parameter):
+        self.config, self.wx, self.wh, self.b = config, wx, wh, b
+        self.hidden_size = config.hidden_size
+
+    @classmethod
+    def new(cls, backend, input_size: int, hidden_size: int, seed: int = 42):
+        s = hidden_size ** -0.5
+        return cls(LstmConfig(input_size, hidden_size), backend.uniform_parameter("wx", (3 * hidden_size, input_size), seed, s),
+                   backend.uniform_parameter("wh", (3 * hidden_size, hidden_size), seed + 1, s),
+                   backend.constant_parameter("b", (3 * hidden_size,), 0.0))
+
+    def initial_state(self, batch: int, ctx=None, like=None):
+        return torch.zeros(batch, self.hidden_size, dtype=self.wx.tensor.dtype, device=self.wx.tensor.device)
+
+    def step(self, x, h, ctx=None):
+        H = self.hidden_size
+        gx = ops.linear(x, self.wx.tensor, self.b.tensor).float()
+        gh = ops.linear(h, self.wh.tensor).float()
+        r = torch.sigmoid(gx[:, :H] + gh[:, :H])
+        z = torch.sigmoid(gx[:, H:2 * H] + gh[:, H:2 * H])
+        n = torch.tanh(gx[:, 2 * H:] + r * gh[:, 2 * H:])
+        return ((1 - z) * n + z * h.float()).to(x.dtype)
+
+    def forward(self, x_state, ctx=None):
+        x, h = x_state
+        return self.step(x, h, ctx)
+
+
+class StackedLstm(Module, Trainable, Saveable):
+    def __init__(self, cells: list):
+        self.layers = cells
+
+    @classmethod
+    def new(cls, backend, input_size: int, hidden_size: int, num_layers: int, seed: int = 42):
+        return cls([LstmCell.new(backend, input_size if i == 0 else hidden_size, hidden_size, seed + 10 * i)
+                    for i in range(num_layers)])
+
+    def forward_sequence(self, xs, ctx: ForwardCtx, states=None):
+        finals = []
+        for i, cell in enumerate(self.layers):
+            xs, st = cell.forward_sequence(xs, ctx, None if states is None else states[i])
+            finals.append(st)
+        return xs, finals
+
+    forward = forward_sequence
+
+
+class BidirectionalRnn(Module, Trainable, Saveable):
+    """Forward and backward passes over the sequence; outputs concatenated along the feature dimension."""
+
+    def __init__(self, fwd: RnnCell, bwd: RnnCell):
+        self.fwd, self.bwd = fwd, bwd
+
+    def forward_sequence(self, xs, ctx: ForwardCtx):
+        of, sf = self.fwd.forward_sequence(xs, ctx)
+        ob, sb = self.bwd.forward_sequence(torch.flip(xs, (0,)), ctx)
+        return torch.cat([of, torch.flip(ob, (0,))], -1), (sf, sb)
+
+    forward = forward_sequence
+
+    def final_hidden(self, xs, ctx: ForwardCtx):
+        _, (sf, sb) = self.forward_sequence(xs, ctx)
+        return torch.cat([self.fwd.hidden_of(sf), self.bwd.hidden_of(sb)], -1)

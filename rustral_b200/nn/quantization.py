@@ -1,0 +1,167 @@
+"""Weight quantization: INT8 (per-tensor / per-channel / asymmetric), INT4 group-wise, FP8 formats, fake-quant for QAT
+(crates/nn/src/quantization.rs:27-560).  Weights are stored quantized; the forward pass dequantizes into the compute
+dtype and runs the tensor-core GEMM (the reference dequantizes to f32 and calls a plain matmul)."""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from ..core import ForwardCtx, Module, InvalidArgument
+
+
+class QuantizationScheme(enum.Enum):
+    INT8 = "int8"
+    INT8_ASYMMETRIC = "int8_asymmetric"
+    INT8_PER_CHANNEL = "int8_per_channel"
+    INT4 = "int4"
+    FP8_E4M3 = "fp8_e4m3"
+    FP8_E5M2 = "fp8_e5m2"
+
+    @property
+    def bits(self) -> int:
+        return 4 if self is QuantizationScheme.INT4 else 8
+
+    @property
+    def compression_ratio(self) -> float:
+        return 32.0 / self.bits
+
+
+@dataclass
+class QuantConfig:
+    scheme: QuantizationScheme = QuantizationScheme.INT8
+    group_size: int = 128
+    symmetric: bool = True
+    per_channel: bool = False
+    outlier_threshold: float = 0.0
+
+
+@dataclass
+class QuantParams:
+    scale: torch.Tensor
+    zero_point: torch.Tensor
+
+    @classmethod
+    def from_tensor(cls, t: torch.Tensor, symmetric: bool = True, dim: int | None = None) -> "QuantParams":
+        f = t.detach().float()
+        if symmetric:
+            amax = f.abs().amax() if dim is None else f.abs().amax(dim, keepdim=True)
+            scale = (amax / 127.0).clamp_min(1e-12)
+            return cls(scale, torch.zeros_like(scale))
+        lo = f.amin() if dim is None else f.amin(dim, keepdim=True)
+        hi = f.amax() if dim is None else f.amax(dim, keepdim=True)
+        scale = ((hi - lo) / 255.0).clamp_min(1e-12)
+        zp = torch.round(-lo / scale) - 128
+        return cls(scale, zp)
+
+    def quantize(self, t: torch.Tensor) -> torch.Tensor:
+        q = torch.round(t.float() / self.scale) + self.zero_point
+        return q.clamp(-128, 127).to(torch.int8)
+
+    def dequantize(self, q: torch.Tensor, dtype=torch.float32) -> torch.Tensor:
+        return ((q.float() - self.zero_point) * self.scale).to(dtype)
+
+
+class QuantizedLinear(Module):
+    """int8 weights [out, in] with per-tensor or per-output-channel scales."""
+
+    def __init__(self, qweight, params: QuantParams, bias=None, compute_dtype=torch.float32):
+        self.qweight, self.params, self.bias, self.compute_dtype = qweight, params, bias, compute_dtype
+
+    @classmethod
+    def from_linear(cls, linear, scheme: QuantizationScheme = QuantizationScheme.INT8):
+        w = linear.weight.tensor.detach()
+        per_ch = scheme is QuantizationScheme.INT8_PER_CHANNEL
+        p = QuantParams.from_tensor(w, symmetric=scheme is not QuantizationScheme.INT8_ASYMMETRIC, dim=1 if per_ch else None)
+        return cls(p.quantize(w), p, None if linear.bias is None else linear.bias.tensor.detach(), w.dtype)
+
+    def dequantized_weight(self):
+        return self.params.dequantize(self.qweight, self.compute_dtype)
+
+    def forward(self, x, ctx: ForwardCtx | None = None):
+        return ops.linear(x, self.dequantized_weight().contiguous(), self.bias)
+
+    def memory_bytes(self) -> int:
+        return self.qweight.numel() + self.params.scale.numel() * 4
+
+
+class GPTQLinear(Module):
+    """int4 group-wise quantization: scale = absmax / 7 per group of `group_size` input features, zero point 8, two
+    nibbles per byte.  (Round-to-nearest; no Hessian-based error compensation, as in the reference.)"""
+
+    def __init__(self, packed, scales, shape, group_size: int, bias=None, compute_dtype=torch.float32):
+        self.packed, self.scales, self.shape, self.group_size = packed, scales, tuple(shape), group_size
+        self.bias, self.compute_dtype = bias, compute_dtype
+
+    @classmethod
+    def from_linear(cls, linear, group_size: int = 128):
+        w = linear.weight.tensor.detach().float()
+        out, inn = w.shape
+        if inn % group_size or inn % 2:
+            raise InvalidArgument("in_features must be a multiple of the group size and even")
+        g = w.view(out, inn // group_size, group_size)
+        scales = (g.abs().amax(-1, keepdim=True) / 7.0).clamp_min(1e-12)
+        q = (torch.round(g / scales) + 8).clamp(0, 15).to(torch.uint8).view(out, inn)
+        packed = (q[:, 0::2] | (q[:, 1::2] << 4)).contiguous()
+        return cls(packed, scales.squeeze(-1), (out, inn), group_size,
+                   None if linear.bias is None else linear.bias.tensor.detach(), linear.weight.tensor.dtype)
+
+    def dequantized_weight(self):
+        out, inn = self.shape
+        q = torch.empty((out, inn), dtype=torch.uint8, device=self.packed.device)
+        q[:, 0::2] = self.packed & 0xF
+        q[:, 1::2] = self.packed >> 4
+        g = (q.float() - 8.0).view(out, inn // self.group_size, self.group_size) * self.scales.unsqueeze(-1)
+        return g.view(out, inn).to(self.compute_dtype)
+
+    def forward(self, x, ctx: ForwardCtx | None = None):
+        return ops.linear(x, self.dequantized_weight().contiguous(), self.bias)
+
+    def memory_bytes(self) -> int:
+        return self.packed.numel() + self.scales.numel() * 4
+
+
+class DynamicQuantizer:
+    """Quantizes activations on the fly (per tensor, symmetric) and reports the error."""
+
+    def quantize(self, t: torch.Tensor):
+        p = QuantParams.from_tensor(t)
+        return p.quantize(t), p
+
+    def roundtrip_error(self, t: torch.Tensor) -> float:
+        q, p = self.quantize(t)
+        return float((p.dequantize(q) - t.float()).abs().max())
+
+
+class QATTrainer:
+    """Fake quantization with a straight-through estimator for quantization-aware training."""
+
+    @staticmethod
+    def fake_quantize(t: torch.Tensor, num_bits: int = 8) -> torch.Tensor:
+        qmax = 2 ** (num_bits - 1) - 1
+        scale = (t.detach().abs().amax() / qmax).clamp_min(1e-12)
+        q = torch.clamp(torch.round(t / scale), -qmax - 1, qmax) * scale
+        return t + (q - t).detach()
+
+
+def quantize_model(model, scheme: QuantizationScheme = QuantizationScheme.INT8, group_size: int = 128):
+    """Replaces every Linear attribute (recursively, lists included) by its quantized counterpart; returns the count."""
+    from .linear import Linear
+    n = 0
+    for k, v in list(vars(model).items()):
+        if isinstance(v, Linear):
+            setattr(model, k, GPTQLinear.from_linear(v, group_size) if scheme is QuantizationScheme.INT4
+                    else QuantizedLinear.from_linear(v, scheme))
+            n += 1
+        elif isinstance(v, list):
+            for i, e in enumerate(v):
+                if isinstance(e, Linear):
+                    v[i] = GPTQLinear.from_linear(e, group_size) if scheme is QuantizationScheme.INT4 else QuantizedLinear.from_linear(e, scheme)
+                    n += 1
+                elif hasattr(e, "__dict__"):
+                    n += quantize_model(e, scheme, group_size)
+        elif hasattr(v, "__dict__") and not isinstance(v, (torch.Tensor, type)) and hasattr(v, "named_parameters"):
+            n += quantize_model(v, scheme, group_size)
+    return n

@@ -1,0 +1,374 @@
+"""Autotuner: search over kernel tile configurations with CUDA-event timing and a persistent cache
+(crates/autotuner/src/{lib,kernel_config,search,tuner,cache}.rs).
+
+The search strategies (grid, random, evolutionary, explore/exploit) live in C++ (csrc/runtime/search.cpp); this
+package defines the tunable kernels, times candidates on the device and stores winners in a JSON cache keyed by
+(kernel id, device, dtype, shape bucket).  Unlike the reference's tuner, it is wired to real kernels: `tune_gemm`
+picks tile width, split-K factor and rasterisation group for the tcgen05 GEMM, and `GemmTuningTable.apply` feeds
+the cached choice back into `ops.gemm`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+import json
+import os
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import _native as N
+
+
+class Strategy(enum.IntEnum):
+    GRID = 0
+    RANDOM = 1
+    EVOLUTIONARY = 2
+    BAYESIAN = 3
+
+
+def dim_bucket(n: int) -> str:
+    """Tiny < 256, Small <= 512, Medium < 2048, Large < 8192, XLarge (crates/autotuner/src/kernel_config.rs)."""
+    return "tiny" if n < 256 else "small" if n <= 512 else "medium" if n < 2048 else "large" if n < 8192 else "xlarge"
+
+
+@dataclass(frozen=True)
+class MatmulShapeBucket:
+    m: str
+    n: str
+    k: str
+
+    @classmethod
+    def of(cls, M: int, N_: int, K: int):
+        return cls(dim_bucket(M), dim_bucket(N_), dim_bucket(K))
+
+    def cache_key(self) -> str:
+        return f"matmul_{self.m}_{self.n}_{self.k}"
+
+
+@dataclass
+class ConfigSpace:
+    dims: dict          # name -> list of int choices
+
+    def size(self) -> int:
+        n = 1
+        for v in self.dims.values():
+            n *= len(v)
+        return n
+
+    @classmethod
+    def matmul_full(cls):
+        return cls({"block_n": [64, 128, 192, 256], "splits": [1, 2, 3, 4, 6, 8], "group_m": [4, 8, 16]})
+
+    @classmethod
+    def matmul_reduced(cls):
+        return cls({"block_n": [128, 192, 256], "splits": [1, 2, 4], "group_m": [8]})
+
+
+@dataclass
+class PerfMetrics:
+    time_us: float
+    tflops: float = 0.0
+    gbytes_per_s: float = 0.0
+
+    @classmethod
+    def from_duration(cls, time_us: float, flops: float = 0.0, bytes_: float = 0.0):
+        s = time_us * 1e-6
+        return cls(time_us, flops / s / 1e12 if s > 0 else 0.0, bytes_ / s / 1e9 if s > 0 else 0.0)
+
+
+class SearchHandle:
+    """Thin wrapper over the C++ searcher."""
+
+    def __init__(self, space: ConfigSpace, strategy: Strategy, seed: int = 0, max_evals: int = 0):
+        self.names = list(space.dims)
+        sizes = [len(space.dims[n]) for n in self.names]
+        flat = [c for n in self.names for c in space.dims[n]]
+        self._lib = N.runtime()
+        self._sizes = (C.c_int * len(sizes))(*sizes)
+        self._flat = (C.c_int * len(flat))(*flat)
+        self._h = self._lib.rb_search_create(int(strategy), len(sizes), self._sizes, self._flat, seed, max_evals)
+        if not self._h:
+            raise ValueError("invalid search space")
+        self._buf = (C.c_int * len(sizes))()
+
+    def next_config(self):
+        if not self._lib.rb_search_next(self._h, self._buf):
+            return None
+        return dict(zip(self.names, list(self._buf)))
+
+    def report(self, config: dict, time_us: float) -> None:
+        arr = (C.c_int * len(self.names))(*[config[n] for n in self.names])
+        self._lib.rb_search_report(self._h, arr, float(time_us))
+
+    def best(self):
+        t = C.c_double()
+        if not self._lib.rb_search_best(self._h, self._buf, C.byref(t)):
+            return None, float("inf")
+        return dict(zip(self.names, list(self._buf))), t.value
+
+    def num_evals(self) -> int:
+        return self._lib.rb_search_num_evals(self._h)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.rb_search_destroy(h)
+
+
+@dataclass
+class TunerConfig:
+    strategy: Strategy = Strategy.BAYESIAN
+    warmup: int = 3
+    timing: int = 10
+    max_tuning_time_s: float = 60.0
+    max_evals: int = 48
+    use_cache: bool = True
+    cache_results: bool = True
+    min_improvement_pct: float = 1.0
+    verbose: bool = False
+    ci_mode: bool = False
+    enabled: bool = True
+    device_id: str = ""
+    dtype: str = "bf16"
+    seed: int = 0
+
+    @classmethod
+    def fast(cls):
+        return cls(Strategy.RANDOM, warmup=2, timing=5, max_tuning_time_s=10.0, max_evals=12)
+
+    @classmethod
+    def ci_safe(cls):
+        return cls(Strategy.RANDOM, warmup=1, timing=2, max_tuning_time_s=5.0, max_evals=5, ci_mode=True)
+
+    @classmethod
+    def disabled(cls):
+        return cls(enabled=False)
+
+
+@dataclass
+class CacheEntry:
+    config: dict
+    time_us: float
+    device_id: str
+    dtype: str
+    shape_bucket: str
+    timestamp: float
+    version: str = "1"
+    num_samples: int = 0
+
+
+class ConfigCache:
+    """JSON at <cache>/rustral/autotuner/kernel_configs.json; entries older than 30 days or from another device are
+    ignored on load."""
+
+    MAX_AGE_S = 30 * 24 * 3600
+
+    def __init__(self, path: str | None = None, device_id: str = ""):
+        base = os.environ.get("RUSTRAL_CACHE_DIR") or os.path.join(os.path.expanduser("~"), ".cache", "rustral")
+        self.path = path or os.path.join(base, "autotuner", "kernel_configs.json")
+        self.device_id = device_id
+        self.entries: dict = {}
+        self.hits = self.misses = 0
+        self.load()
+
+    @staticmethod
+    def key(kernel_id: str, device_id: str, dtype: str, bucket: str) -> str:
+        return f"{kernel_id}|{device_id}|{dtype}|{bucket}"
+
+    def load(self) -> None:
+        try:
+            with open(self.path) as f:
+                raw = json.load(f)
+        except (OSError, json.JSONDecodeError):
+            return
+        now = time.time()
+        for k, e in raw.items():
+            try:
+                ce = CacheEntry(**e)
+            except TypeError:
+                continue
+            if now - ce.timestamp <= self.MAX_AGE_S and (not self.device_id or ce.device_id == self.device_id):
+                self.entries[k] = ce
+
+    def save(self) -> None:
+        os.makedirs(os.path.dirname(self.path), exist_ok=True)
+        tmp = self.path + ".partial"
+        with open(tmp, "w") as f:
+            json.dump({k: e.__dict__ for k, e in self.entries.items()}, f, indent=1)
+        os.replace(tmp, self.path)
+
+    def get_config(self, kernel_id, device_id, dtype, bucket):
+        e = self.entries.get(self.key(kernel_id, device_id, dtype, bucket))
+        if e is None:
+            self.misses += 1
+        else:
+            self.hits += 1
+        return e
+
+    def store_config(self, kernel_id, device_id, dtype, bucket, config: dict, time_us: float, num_samples: int) -> None:
+        self.entries[self.key(kernel_id, device_id, dtype, bucket)] = CacheEntry(dict(config), time_us, device_id, dtype, bucket,
+                                                                                 time.time(), "1", num_samples)
+
+    def hit_rate(self) -> float:
+        tot = self.hits + self.misses
+        return self.hits / tot if tot else 0.0
+
+
+TuningCache = ConfigCache
+
+
+class TunableKernel:
+    """kernel_id / config_space / with_config(config) -> callable / input_signature (shape bucket string)."""
+
+    kernel_id = "kernel"
+
+    def config_space(self) -> ConfigSpace:
+        raise NotImplementedError
+
+    def with_config(self, config: dict):
+        raise NotImplementedError
+
+    def default_config(self) -> dict:
+        return {k: v[0] for k, v in self.config_space().dims.items()}
+
+    def input_signature(self) -> str:
+        return "-"
+
+    def flops(self) -> float:
+        return 0.0
+
+
+def benchmark_kernel(fn, warmup: int, iters: int) -> float:
+    """Median microseconds per call: CUDA events on the current stream when a GPU is present, host clock otherwise."""
+    for _ in range(warmup):
+        fn()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+    else:
+        ts = []
+        for _ in range(iters):
+            t0 = time.perf_counter()
+            fn()
+            ts.append((time.perf_counter() - t0) * 1e6)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+@dataclass
+class TuningResult:
+    config: dict
+    time_us: float
+    default_time_us: float
+    evaluated: int
+    from_cache: bool = False
+
+    @property
+    def improvement_pct(self) -> float:
+        return 100.0 * (self.default_time_us - self.time_us) / self.default_time_us if self.default_time_us > 0 else 0.0
+
+
+class AutoTuner:
+    def __init__(self, config: TunerConfig | None = None, cache: ConfigCache | None = None):
+        self.config = config or TunerConfig()
+        if not self.config.device_id:
+            self.config.device_id = torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu"
+        self.cache = cache or ConfigCache(device_id=self.config.device_id)
+        self.stats = {"tuned": 0, "cache_hits": 0}
+
+    def tune(self, kernel: TunableKernel) -> TuningResult:
+        cfg = self.config
+        default = kernel.default_config()
+        if not cfg.enabled:
+            return TuningResult(default, 0.0, 0.0, 0)
+        bucket = kernel.input_signature()
+        if cfg.use_cache:
+            e = self.cache.get_config(kernel.kernel_id, cfg.device_id, cfg.dtype, bucket)
+            if e is not None:
+                self.stats["cache_hits"] += 1
+                t = benchmark_kernel(kernel.with_config(e.config), cfg.warmup, cfg.timing)
+                return TuningResult(dict(e.config), t, t, 0, True)
+        t_default = benchmark_kernel(kernel.with_config(default), cfg.warmup, cfg.timing)
+        search = SearchHandle(kernel.config_space(), cfg.strategy, cfg.seed, min(cfg.max_evals, 5) if cfg.ci_mode else cfg.max_evals)
+        search.report(default, t_default)
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < cfg.max_tuning_time_s:
+            c = search.next_config()
+            if c is None:
+                break
+            try:
+                t = benchmark_kernel(kernel.with_config(c), cfg.warmup, cfg.timing)
+            except Exception:   # noqa: BLE001 - a configuration the kernel rejects is simply not a candidate
+                t = float("inf")
+            if t != float("inf"):
+                search.report(c, t)
+            if cfg.verbose:
+                print(f"[tune] {kernel.kernel_id} {c} -> {t:.1f} us")
+        best, t_best = search.best()
+        if best is None or (t_default - t_best) / t_default * 100.0 < cfg.min_improvement_pct:
+            best, t_best = default, t_default
+        if cfg.cache_results:
+            self.cache.store_config(kernel.kernel_id, cfg.device_id, cfg.dtype, bucket, best, t_best, search.num_evals())
+            self.cache.save()
+        self.stats["tuned"] += 1
+        return TuningResult(best, t_best, t_default, search.num_evals())
+
+
+class GemmKernel(TunableKernel):
+    """The tcgen05 GEMM at one problem shape: tile width, split-K factor, rasterisation group."""
+
+    kernel_id = "gemm_bf16_tcgen05"
+
+    def __init__(self, M: int, N_: int, K: int, a_mn: bool = False, b_mn: bool = False, out_f32: bool = False, reduced: bool = True):
+        self.M, self.N, self.K, self.a_mn, self.b_mn, self.out_f32, self.reduced = M, N_, K, a_mn, b_mn, out_f32, reduced
+        dev = "cuda"
+        g = torch.Generator().manual_seed(0)
+        mk = lambda *s: (torch.randn(*s, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+        self.a = mk(K, M) if a_mn else mk(M, K)
+        self.b = mk(K, N_) if b_mn else mk(N_, K)
+        self.out = torch.empty((M, N_), dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
+
+    def config_space(self):
+        return ConfigSpace.matmul_reduced() if self.reduced else ConfigSpace.matmul_full()
+
+    def default_config(self):
+        return {"block_n": 0, "splits": 0, "group_m": 0}        # the kernel's own cost model
+
+    def input_signature(self):
+        return MatmulShapeBucket.of(self.M, self.N, self.K).cache_key() + f"_{int(self.a_mn)}{int(self.b_mn)}{int(self.out_f32)}"
+
+    def flops(self):
+        return 2.0 * self.M * self.N * self.K
+
+    def with_config(self, config: dict):
+        from ..ops import gemm
+        return lambda: gemm(self.a, self.b, a_mn=self.a_mn, b_mn=self.b_mn, out=self.out, block_n=config["block_n"],
+                            splits=config["splits"], group_m=config["group_m"])
+
+
+def tune_gemm(M: int, N_: int, K: int, tuner: AutoTuner | None = None, **kw) -> TuningResult:
+    return (tuner or AutoTuner(TunerConfig.fast())).tune(GemmKernel(M, N_, K, **kw))
+
+
+class PreTuner:
+    """Tunes the GEMM shapes of a model configuration ahead of time (crates/autotuner/src/lib.rs PreTuner)."""
+
+    def __init__(self, tuner: AutoTuner | None = None):
+        self.tuner = tuner or AutoTuner(TunerConfig.fast())
+
+    def shapes_for(self, cfg, tokens: int) -> list:
+        d, f = cfg.d_model, cfg.ffn_dim
+        fwd = [(tokens, cfg.qkv_dim, d), (tokens, d, d), (tokens, f if cfg.arch == "gpt2" else 2 * f, d), (tokens, d, f)]
+        return fwd + [(tokens, cfg.vocab_padded, d)]
+
+    def pretune(self, cfg, tokens: int) -> dict:
+        return {s: self.tuner.tune(GemmKernel(*s)) for s in self.shapes_for(cfg, tokens)}

@@ -1,0 +1,293 @@
+"""Core contracts and nn modules on the CPU reference backend: naming stability, strict I/O, gradient checks, goldens."""
+import json
+import math
+import os
+
+import pytest
+import torch
+
+from rustral_b200.core import (CpuBackend, ForwardCtx, Mode, Shape, ShapePolicy, InvalidShape, SerializationError, ShapeMismatch,
+                               OperationProfiler, MemoryProfiler, TensorPool, PoolStrategy, NumericsValidator, DType, OpFamily,
+                               ToleranceConfig, FusionOptimizer, FusionPattern, PatternMatcher, FusionTestHarness, assert_close)
+from rustral_b200.nn import *
+from rustral_b200.optim import Adam, AdamW, Sgd, WarmupCosine, OneCycleLR, PlateauLR, StepDecay, LossScaleScheduler, MixedPrecisionOptimizer
+from rustral_b200.runtime.model_io import load_model, save_model
+
+B = CpuBackend()
+
+
+def test_shape_ctx_and_capabilities():
+    with pytest.raises(InvalidShape):
+        Shape([])
+    with pytest.raises(InvalidShape):
+        Shape([3, 0])
+    assert Shape([2, 3]).numel() == 6
+    a, b = ForwardCtx.train(B), ForwardCtx.inference(B)
+    assert a.is_training() and not b.is_training() and a.run_id != b.run_id and a.mode is Mode.TRAIN
+    assert ShapePolicy.STATIC.supports_cuda_graph_capture() and not ShapePolicy.DYNAMIC_UNBOUNDED.supports_cuda_graph_capture()
+    caps = B.capabilities()
+    assert caps.clamp_batch_size(10_000) == caps.max_batch_size and not caps.recommends_mixed_precision()
+
+
+def test_named_parameters_are_stable_and_match_the_reference_names():
+    blk = TapeTransformerEncoderLayer.new(B, TapeTransformerEncoderConfig(32, 4, 64))
+    names = [n for n, _ in blk.named_parameters()]
+    assert names == ["ln1.weight", "ln1.bias", "attn.wq.weight", "attn.wq.bias", "attn.wk.weight", "attn.wk.bias",
+                     "attn.wv.weight", "attn.wv.bias", "attn.wo.weight", "attn.wo.bias", "ln2.weight", "ln2.bias",
+                     "ffn.fc1.weight", "ffn.fc1.bias", "ffn.fc2.weight", "ffn.fc2.bias"]
+    enc = TransformerEncoder.new(B, TransformerEncoderConfig(32, 4, 2, 64, 0.0, 16), 50)
+    n2 = [n for n, _ in enc.named_parameters()]
+    assert n2[0] == "token_embedding.embed" and "layers.1.self_attn.out_proj.weight" in n2 and n2[-1] == "final_norm.bias"
+    seq = chain(LinearBuilder(4, 4).build(B), LinearBuilder(4, 2).with_bias().build(B))
+    assert [n for n, _ in seq.named_parameters()] == ["first.weight", "second.weight", "second.bias"]
+    assert [n for n, _ in MultiHeadAttention.new(B, 32, 4).named_parameters()][0] == "attention.q_proj.weight"
+    assert [n for n, _ in Embedding.new(B, 10, 4).named_parameters()] == ["embed"]
+
+
+def test_every_parameter_of_a_block_gets_a_nonzero_gradient():
+    ctx = ForwardCtx.train(B)
+    blk = TapeTransformerEncoderLayer.new(B, TapeTransformerEncoderConfig(32, 4, 64, causal=True))
+    x = torch.randn(2, 10, 32)
+    blk(x, ctx).square().sum().backward()
+    for n, p in blk.named_parameters():
+        assert p.grad is not None and float(p.grad.abs().sum()) > 0, n
+
+
+def test_linear_builder_defaults_and_fused_activations():
+    a, b = LinearBuilder(6, 4).with_bias().build(B), LinearBuilder(6, 4).with_bias().build(B)
+    assert torch.equal(a.weight.tensor, b.weight.tensor)                     # seed 42 by default
+    assert not torch.equal(a.weight.tensor, LinearBuilder(6, 4).seed(7).build(B).weight.tensor)
+    x = torch.randn(3, 6)
+    g = LinearBuilder(6, 4).with_bias().activation("gelu").build(B)
+    want = torch.nn.functional.gelu(x @ g.weight.tensor.t() + g.bias.tensor, approximate="tanh")
+    assert torch.allclose(g(x), want, atol=1e-6)
+    with pytest.raises(Exception):
+        LinearBuilder(6, 4).activation("relu").build(B)                        # fused activations need a bias
+    with pytest.raises(ShapeMismatch):
+        a(torch.randn(3, 5))
+
+
+@pytest.mark.parametrize("what", ["linear", "layer_norm", "embedding", "cross_entropy", "gelu", "rms_norm"])
+def test_finite_difference_gradients(what):
+    """Central differences, eps 1e-3, tolerance 1e-2 (crates/autodiff/tests/finite_difference.rs)."""
+    from rustral_b200 import ops
+    torch.manual_seed(0)
+    if what == "linear":
+        leaves = [torch.randn(3, 5), torch.randn(4, 5), torch.randn(4)]
+        f = lambda x, w, b: ops.linear(x, w, b).square().sum()
+    elif what == "layer_norm":
+        leaves = [torch.randn(3, 8), torch.rand(8) + 0.5, torch.randn(8)]
+        f = lambda x, g, b: (ops.layer_norm(x, g, b) * torch.arange(8.)).sum()
+    elif what == "rms_norm":
+        leaves = [torch.randn(3, 8), torch.rand(8) + 0.5]
+        f = lambda x, g: (ops.rms_norm(x, g) * torch.arange(8.)).sum()
+    elif what == "embedding":
+        ids = torch.tensor([1, 3, 1])
+        leaves = [torch.randn(5, 4)]
+        f = lambda t: (ops.embedding(ids, t) * torch.arange(12.).view(3, 4)).sum()
+    elif what == "cross_entropy":
+        tg = torch.tensor([0, 2, 1])
+        leaves = [torch.randn(3, 4)]
+        f = lambda l: ops.cross_entropy(l, tg)
+    else:
+        leaves = [torch.randn(7)]
+        f = lambda x: ops.gelu(x).sum()
+    req = [l.clone().requires_grad_() for l in leaves]
+    f(*req).backward()
+    for li, leaf in enumerate(leaves):
+        flat = leaf.reshape(-1)
+        for i in range(0, flat.numel(), max(1, flat.numel() // 6)):
+            def at(delta):
+                mod = [l.clone() for l in leaves]
+                mod[li].reshape(-1)[i] += delta
+                return float(f(*mod))
+            fd = (at(1e-3) - at(-1e-3)) / 2e-3
+            an = float(req[li].grad.reshape(-1)[i])
+            assert abs(fd - an) <= 1e-2 * max(1.0, abs(fd)), (what, li, i, fd, an)
+
+
+def test_golden_softmax_against_f64():
+    from rustral_b200 import ops
+    x = torch.tensor([[1.0, 2.0, 3.0, 4.0], [-1000.0, 0.0, 1000.0, 999.0]])
+    want = torch.softmax(x.double(), -1)
+    assert_close(ops.softmax(x), want, ToleranceConfig.for_family(OpFamily.SOFTMAX))
+    assert_close(torch.exp(ops.log_softmax(x)), want, ToleranceConfig.for_family(OpFamily.SOFTMAX))
+
+
+def test_model_io_roundtrip_and_strict_negatives():
+    m1 = TapeTransformerEncoderLayer.new(B, TapeTransformerEncoderConfig(16, 2, 32), seed=1)
+    m2 = TapeTransformerEncoderLayer.new(B, TapeTransformerEncoderConfig(16, 2, 32), seed=2)
+    blob = save_model(m1)
+    load_model(m2, blob)
+    x = torch.randn(1, 5, 16)
+    assert torch.equal(m1(x), m2(x))
+    from rustral_b200.io import deserialize, serialize
+    tensors, meta = deserialize(blob)
+    assert "rustral.parameter_ids" in meta and set(json.loads(meta["rustral.parameter_ids"])) == set(tensors)
+    for mutate in ("missing", "extra", "shape", "dtype"):
+        t = dict(tensors)
+        if mutate == "missing":
+            t.pop("ln1.weight")
+        elif mutate == "extra":
+            t["bogus"] = torch.zeros(1)
+        elif mutate == "shape":
+            t["ln1.weight"] = torch.zeros(17)
+        else:
+            t["ln1.weight"] = t["ln1.weight"].to(torch.bfloat16)
+        before = m2.ln1.weight.tensor.clone()
+        with pytest.raises((SerializationError, ShapeMismatch)):
+            load_model(m2, serialize(t))
+        assert torch.equal(m2.ln1.weight.tensor, before)             # nothing was written
+
+
+def test_three_runs_are_bitwise_identical():
+    def run():
+        torch.manual_seed(0)
+        ctx = ForwardCtx.train(B)
+        m = TapeTransformerEncoderLayer.new(B, TapeTransformerEncoderConfig(16, 2, 32))
+        opt = Adam(1e-2)
+        x = torch.randn(2, 6, 16, generator=torch.Generator().manual_seed(1))
+        for _ in range(5):
+            m.zero_grad()
+            m(x, ctx).square().mean().backward()
+            opt.step(m.parameters())
+        return torch.cat([p.tensor.reshape(-1) for p in m.parameters()])
+    a, b, c = run(), run(), run()
+    assert torch.equal(a, b) and torch.equal(b, c)
+
+
+def test_optimizers_schedulers_and_loss_scaling():
+    p0 = torch.randn(50)
+    g = torch.randn(50)
+    from rustral_b200.core import Parameter
+    for decoupled in (False, True):
+        p = Parameter("p", p0.clone())
+        ref = torch.nn.Parameter(p0.clone())
+        ropt = (torch.optim.AdamW if decoupled else torch.optim.Adam)([ref], lr=1e-2, weight_decay=0.1, eps=1e-8)
+        opt = Adam(1e-2, weight_decay=0.1, decoupled=decoupled)
+        for _ in range(4):
+            ref.grad = g.clone()
+            ropt.step()
+            opt.step([p], {p.id: g})
+        assert torch.allclose(p.tensor, ref.detach(), atol=1e-6)
+    p = Parameter("p", p0.clone())
+    ref = torch.nn.Parameter(p0.clone())
+    ropt, opt = torch.optim.SGD([ref], lr=0.1, momentum=0.9), Sgd(0.1, momentum=0.9)
+    for _ in range(3):
+        ref.grad = g.clone()
+        ropt.step()
+        opt.step([p], {p.id: g})
+    assert torch.allclose(p.tensor, ref.detach(), atol=1e-6)                 # momentum is really used
+    s = WarmupCosine(1e-3, 1e-5, 10, 100)
+    assert s.get_lr(0) == 0 and s.get_lr(10) == pytest.approx(1e-3) and s.get_lr(100) == pytest.approx(1e-5)
+    assert OneCycleLR(1.0, 100).get_lr(50) == pytest.approx(1.0) and StepDecay(1.0, 0.5, 10).get_lr(25) == 0.25
+    pl = PlateauLR(1.0, 0.1, 0.5, patience=1)
+    for l in (1.0, 1.0, 1.0, 1.0):
+        pl.report_loss(l)
+    assert pl.current_lr() == 0.5
+    ls = LossScaleScheduler(1024, growth_interval=2)
+    assert ls.step(True) and ls.scale == 512 and not ls.step(False) and not ls.step(False) and ls.scale == 1024
+    p = Parameter("p", p0.clone())
+    mp = MixedPrecisionOptimizer(Adam(1e-2), loss_scale=LossScaleScheduler(8.0))
+    assert mp.step([p], {p.id: g * 8.0}) and not mp.step([p], {p.id: torch.full((50,), float("inf"))})
+    q = Parameter("q", p0.clone())
+    Adam(1e-2).step([q], {q.id: g})
+    assert torch.allclose(p.tensor, q.tensor, atol=1e-6)                     # gradients were UNscaled before the step
+
+
+def test_profilers_pool_numerics_and_fusion():
+    prof = OperationProfiler(use_cuda_events=False)
+    ctx = ForwardCtx.train(B, profiler=prof)
+    LinearBuilder(8, 8).with_bias().build(B)(torch.randn(4, 8), ctx)
+    with prof.guard("custom", (4, 8)):
+        pass
+    assert prof.stats["linear"].count == 1 and "4x8" in prof.stats["custom"].shape_buckets
+    base = {"linear": prof.stats["linear"].mean_ms / 10}
+    assert prof.check_regression(base, 0.2)[0][0] == "linear" and json.loads(prof.export_json())["linear"]["count"] == 1
+    mem = MemoryProfiler(capacity_bytes=1000)
+    h = mem.alloc("acts", 600)
+    assert mem.predict_oom_risk(300) == "critical" and mem.find_leaks()[0][1] == "acts"
+    mem.free(h)
+    assert mem.current == 0 and mem.peak == 600 and len(json.loads(mem.export_timeline())) == 2
+    pool = TensorPool(PoolStrategy.TRAINING_ARENA)
+    t = pool.acquire((16, 16))
+    pool.begin_step()
+    assert pool.acquire((16, 16)) is t and pool.stats()["hits"] == 1
+    v = NumericsValidator()
+    assert v.validate_arrays([1.0, 2.0], [1.0, 2.0 + 1e-7]).ok and not v.validate_arrays([1.0, float("nan")], [1.0, 2.0]).ok
+    assert PatternMatcher().find(["matmul", "add_row_vector", "gelu", "relu"])[0][2] is FusionPattern.MATMUL_BIAS_GELU
+    x, w, b = torch.randn(5, 7), torch.randn(3, 7), torch.randn(3)
+    r = FusionTestHarness(repeats=2).run_test(lambda: torch.relu(x @ w.t() + b), lambda: FusionOptimizer(B).apply_matmul_bias_relu(x, w, b))
+    assert r.passed and r.max_abs_err < 1e-5
+
+
+def test_moe_quantization_conv_lstm_readouts():
+    ctx = ForwardCtx.train(B)
+    layer = ExpertLayer.new(B, MoEConfig(32, 4, 64, 2))
+    x = torch.randn(3, 10, 32, requires_grad=True)
+    out = layer(x, ctx)
+    (out.output.sum() + out.aux_loss).backward()
+    assert all(p.grad is not None for p in layer.parameters()) and 0 < float(out.aux_loss) < 0.1
+    assert ExpertParallel(8, 4, 1).local_experts() == [1, 5]
+    lin = LinearBuilder(128, 16).with_bias().build(B)
+    xi = torch.randn(4, 128)
+    assert (QuantizedLinear.from_linear(lin)(xi) - lin(xi)).abs().max() < 0.1
+    assert GPTQLinear.from_linear(lin, 64).memory_bytes() < lin.weight.tensor.numel() * 4 / 6
+    fq = QATTrainer.fake_quantize(xi.clone().requires_grad_(), 8)
+    fq.sum().backward()
+    conv = Conv2d.new(B, Conv2dConfig(5, 3, 3, in_channels=2))
+    img = torch.randn(2, 2, 8, 8)
+    assert torch.allclose(conv(img), torch.nn.functional.conv2d(img, conv.weight.tensor, conv.bias.tensor, padding=1), atol=1e-5)
+    from rustral_b200.symbolic import Vocabulary
+    labels = Vocabulary.with_specials("<unk>", ["pos", "neg"])
+    ro = Readout.new(B, labels, 8)
+    pred = ro.predict(torch.randn(3, 8), ctx)
+    assert len(pred) == 3 and pred[0].label in labels.tokens() and 0 <= pred[0].score <= 1
+    assert len(MultiReadout.new(B, ["a", "b", "c"], 8).top_k(torch.randn(2, 8), ctx, 2)[0]) == 2
+
+
+def test_onnx_export_structure_and_dashboard():
+    from rustral_b200.utils import onnx_export, tui
+    w, b = torch.randn(3, 4), torch.randn(3)
+    blob = onnx_export.export_linear_f32(4, 3, w, b)
+
+    def fields(buf):
+        i, out = 0, []
+        while i < len(buf):
+            key = 0; shift = 0
+            while True:
+                c = buf[i]; i += 1
+                key |= (c & 0x7F) << shift; shift += 7
+                if not c & 0x80:
+                    break
+            num, wire = key >> 3, key & 7
+            if wire == 0:
+                v = 0; shift = 0
+                while True:
+                    c = buf[i]; i += 1
+                    v |= (c & 0x7F) << shift; shift += 7
+                    if not c & 0x80:
+                        break
+                out.append((num, v))
+            else:
+                ln = 0; shift = 0
+                while True:
+                    c = buf[i]; i += 1
+                    ln |= (c & 0x7F) << shift; shift += 7
+                    if not c & 0x80:
+                        break
+                out.append((num, buf[i:i + ln])); i += ln
+        return out
+    model = dict((n, v) for n, v in fields(blob) if n in (1, 7, 8))
+    assert model[1] == 9 and dict(fields(model[8]))[2] == 17
+    graph = fields(model[7])
+    ops_ = [dict(fields(v))[4].decode() for n, v in graph if n == 1]
+    assert ops_ == ["MatMul", "Add"]
+    init = [dict(fields(v)) for n, v in graph if n == 5]
+    wt = torch.frombuffer(bytearray(init[0][9]), dtype=torch.float32).view(4, 3)
+    assert torch.equal(wt, w.t().contiguous())
+    d = tui.TrainingDashboard()
+    for i in range(5):
+        tui.EpochSnapshot(i, 1.0 / (i + 1), 0.5).push_to_dashboard(d)
+    import io
+    assert "loss 0.2000" in tui.DashboardRenderer(d, io.StringIO(), False).render_text()
