@@ -179,6 +179,33 @@ zero_adam_push_kernel(ZeroDev d, RbZeroArgs a, unsigned int* status, unsigned in
   }
 }
 
+// out[r, :] = sum_s slots[s][r, :] (+ residual[r, :]), s ascending: the tail of the fused GEMM -> reduce-scatter.
+__global__ void __launch_bounds__(256)
+tp_reduce_slots_kernel(const __nv_bfloat16* __restrict__ slots, int world, long long slot_elems,
+                       const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out) {
+  const long long n8 = slot_elems / 8;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (residual) {
+      const uint4 u = reinterpret_cast<const uint4*>(residual)[i];
+      const uint32_t* pu = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(pu[j]); acc[2 * j] = f.x; acc[2 * j + 1] = f.y; }
+    }
+    for (int s = 0; s < world; ++s) {
+      const uint4 u = reinterpret_cast<const uint4*>(slots + s * slot_elems)[i];
+      const uint32_t* pu = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(pu[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
 }  // namespace rb
 
 namespace {
@@ -287,5 +314,16 @@ RB_API int rb_zero_adam_push(const RbZeroArgs* a, void* stream_v) {
   const int grid = rbhost::device_sm_count() * 2;
   rb::zero_adam_push_kernel<<<grid, rb::kZeroThreads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
       g_zero_dev, *a, rbhost::status_ptr(), ctr + 1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+RB_API int rb_tp_reduce_slots(const void* slots, int world, long long slot_elems, const void* residual, void* out,
+                              void* stream_v) {
+  if (world < 1 || slot_elems <= 0 || (slot_elems % 8)) return -1;
+  long long blocks = (slot_elems / 8 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  rb::tp_reduce_slots_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(slots), world, slot_elems, reinterpret_cast<const __nv_bfloat16*>(residual),
+      reinterpret_cast<__nv_bfloat16*>(out));
   return static_cast<int>(cudaGetLastError());
 }

@@ -48,6 +48,9 @@ typedef struct RbZeroArgs {
 // every rank's working copy, then raise the "parameters pushed" flag on every peer.
 int rb_zero_reduce(const RbZeroArgs* args, void* stream);
 int rb_zero_adam_push(const RbZeroArgs* args, void* stream);
+// out[rows, n] = sum over `world` receive slots (dense, slot_elems bf16 each, rank order) (+ residual): the owner-side
+// tail of the fused GEMM -> reduce-scatter (peer_mode 2 of rb_gemm_bf16).
+int rb_tp_reduce_slots(const void* slots, int world, long long slot_elems, const void* residual, void* out, void* stream);
 #ifdef __cplusplus
 }
 #endif

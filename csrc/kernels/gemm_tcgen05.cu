@@ -18,6 +18,9 @@
 // op sequences (crates/candle-backend/src/lib.rs:220-312).
 #include "gemm_tcgen05.h"
 
+#include <stdlib.h>
+#include <string.h>
+
 #include "rb_common.cuh"
 
 namespace rb {
@@ -25,8 +28,9 @@ namespace rb {
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;   // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kNumThreads = 192;
-constexpr int kNumEpilogueWarps = 4;
+constexpr int kNumEpilogueWarps = 8;   // two groups of four: each group covers all 128 TMEM lanes and half of the columns
+constexpr int kNumEpiThreads = kNumEpilogueWarps * 32;
+constexpr int kNumThreads = 64 + kNumEpiThreads;
 
 struct EpiParams {
   void* d;
@@ -42,6 +46,7 @@ struct EpiParams {
   int out_f32;
   int accumulate;
   float alpha;
+  int staged;   // bf16 output goes through a per-warp shared-memory tile and leaves as whole 128/256-byte row segments
 };
 
 // Grouped (mixture-of-experts) execution over a permuted token buffer whose expert segments are whole tiles.
@@ -60,6 +65,40 @@ struct GroupInfo {
   long long d_expert_stride;
 };
 
+// Fusion with tensor-parallel collectives over peer memory (NVLink loads / stores issued by this kernel).
+//   mode 1 (all-gather -> GEMM): the A operand [M, K] is sharded by rows over `world` ranks.  This rank's rows are
+//           already in a_full; the other ranks' 128-row tiles are copied from their (peer-mapped) shards into a_full by
+//           the epilogue warps of all CTAs at kernel start, 16 rows at a time, each piece adding one to the tile's
+//           counter; the TMA producer waits (bounded) until a remote tile's counter reaches epoch * 8 before loading
+//           it.  Local tiles are scheduled first, so the transfer overlaps their math.
+//   mode 2 (GEMM -> reduce-scatter): the output rows are owned by ranks (rows_per_rank each).  The epilogue stores
+//           every tile straight into the OWNER's receive slot for this rank (d_peer[owner] + rank slot), as whole
+//           row segments through the staged store; tiles of the next rank come first and this rank's own last, so
+//           at any time the ranks send to different peers.  A small kernel on the owner then folds the slots in
+//           rank order.
+struct PeerInfo {
+  int mode, world, rank, rows_per_rank;
+  const __nv_bfloat16* a_peer[8];
+  __nv_bfloat16* a_full;
+  unsigned int* ready;
+  unsigned int epoch;
+  __nv_bfloat16* d_peer[8];
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_gpu_add(unsigned int* p, unsigned int v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+constexpr int kCopyParts = 8;     // a remote 128-row tile is pulled as 8 pieces of 16 rows, by up to 8 different CTAs
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 template <int BLOCK_N, int STAGES>
 struct SmemLayout {
   static constexpr int kABytes = kBlockM * kBlockK * 2;
@@ -68,11 +107,19 @@ struct SmemLayout {
   static constexpr int kBarOffset = STAGES * kStageBytes;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
   static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16;
+  // optional output staging (EpiParams::staged): per epilogue warp 32 rows x kStageCols bf16
+  static constexpr int kStageCols = (BLOCK_N % 128 == 0) ? 64 : 32;
+  static constexpr int kStagingOffset = (kTotal + 15) & ~15;
+  static constexpr int kStagingBytesPerWarp = 32 * kStageCols * 2;
+  static constexpr int kTotalStaged = kStagingOffset + kNumEpilogueWarps * kStagingBytesPerWarp;
 };
 
-// Processes 32 consecutive accumulator columns of one output row.
-__device__ __forceinline__ void epilogue_chunk(const EpiParams& ep, uint32_t (&r)[32], long long row, int col0, int N) {
-  float v[32];
+// Epilogue arithmetic on 32 consecutive accumulator columns of one output row (everything but the final store).
+// STORE_AUX: write the pre-activation to aux_out from here (one 64-byte piece per thread).  PRE_ONLY: stop after
+// the bias, leaving the pre-activation in v (the staged path writes it out itself, coalesced).
+template <bool STORE_AUX = true, bool PRE_ONLY = false>
+__device__ __forceinline__ void epilogue_math(const EpiParams& ep, uint32_t (&r)[32], long long row, int col0, int N,
+                                              float (&v)[32]) {
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
   const bool full = (col0 + 32 <= N);
@@ -94,10 +141,13 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& ep, uint32_t (&r
     }
   }
 
+  if (PRE_ONLY) return;
+
   if (ep.act == RB_ACT_GELU || ep.act == RB_ACT_RELU || ep.act == RB_ACT_SILU) {
     if (ep.aux_out != nullptr) {   // keep the pre-activation for the backward pass
       __nv_bfloat16* ap = ep.aux_out + row * ep.ld_aux_out + col0;
-      if (full) {
+      if (!STORE_AUX) {
+      } else if (full) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint4 o;
@@ -116,7 +166,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& ep, uint32_t (&r
     }
     if (ep.act == RB_ACT_GELU) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+      for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_fast(v[j]);
     } else if (ep.act == RB_ACT_RELU) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
@@ -142,7 +192,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& ep, uint32_t (&r
     }
     if (ep.act == RB_ACT_DGELU) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] *= gelu_tanh_grad(a[j]);
+      for (int j = 0; j < 32; ++j) v[j] *= gelu_tanh_grad_fast(a[j]);
     } else if (ep.act == RB_ACT_DRELU) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = a[j] > 0.f ? v[j] : 0.f;
@@ -172,6 +222,11 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& ep, uint32_t (&r
     }
   }
 
+}
+
+// Stores 32 consecutive columns of one output row from registers.
+__device__ __forceinline__ void epilogue_store(const EpiParams& ep, float (&v)[32], long long row, int col0, int N) {
+  const bool full = (col0 + 32 <= N);
   if (ep.out_f32) {
     float* dp = reinterpret_cast<float*>(ep.d) + row * ep.ldd + col0;
     if (full) {
@@ -217,11 +272,17 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& ep, uint32_t (&r
   }
 }
 
+__device__ __forceinline__ void epilogue_chunk(const EpiParams& ep, uint32_t (&r)[32], long long row, int col0, int N) {
+  float v[32];
+  epilogue_math(ep, r, row, col0, N, v);
+  epilogue_store(ep, v, row, col0, N);
+}
+
 template <int A_MN, int B_MN, int BLOCK_N, int STAGES>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
                  int K, int group_m, int num_splits, int kb_per_split, long long d_split_stride, EpiParams ep,
-                 GroupInfo grp, unsigned int* status) {
+                 GroupInfo grp, PeerInfo peer, unsigned int* status) {
   using L = SmemLayout<BLOCK_N, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms need 1024-byte aligned tiles
@@ -292,6 +353,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int in_group = tile - group * group_size;
     m_blk = first_m + in_group % gm;
     n_blk = in_group / gm;
+    if (peer.mode == 1) {          // consumption order starts at this rank's own rows
+      m_blk += peer.rank * (peer.rows_per_rank / kBlockM);
+      if (m_blk >= num_m) m_blk -= num_m;
+    } else if (peer.mode == 2) {   // rows of the next rank first, this rank's own rows last
+      m_blk += ((peer.rank + 1) % peer.world) * (peer.rows_per_rank / kBlockM);
+      if (m_blk >= num_m) m_blk -= num_m;
+    }
   };
 
   if (warp == 0) {
@@ -307,6 +375,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (grp.mode == 1) {
           const int e = __ldg(grp.tile_expert + m_blk);
           b_row_off = (e < 0 ? 0 : e) * grp.b_expert_rows;
+        }
+        if (peer.mode == 1 && (m_blk * kBlockM) / peer.rows_per_rank != peer.rank) {
+          // a remote tile: wait until the copy warps of whichever CTA owns it have landed it in a_full
+          const unsigned long long t0 = globaltimer_ns();
+          const unsigned int target = peer.epoch * kCopyParts;
+          while (static_cast<int>(ld_acquire_gpu(peer.ready + m_blk) - target) < 0) {
+            if (*abort_flag || globaltimer_ns() - t0 > kFlagWaitLimitNs) {
+              *abort_flag = 1;
+              status_set(status, kStatusFlagTimeout, 5);
+              ok = false;
+              break;
+            }
+            __nanosleep(100);
+          }
+          if (!ok) break;
+          fence_proxy_async_all();     // the tile was written with ordinary stores; TMA reads it through the async proxy
         }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
@@ -369,6 +453,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // -------------------------------------------------------------------- epilogue warps
     const int q = warp & 3;   // TMEM lane quarter this warp may read
+    const int ew = warp - 2;  // 0..7
+    const int cgrp = ew >> 2; // which half of the tile's columns this warp handles
+    if (peer.mode == 1) {
+      // ---- all-gather duty: land the remote rows of A in a_full, 16 rows at a time, in the order the tiles are consumed
+      const int tpr = peer.rows_per_rank / kBlockM;
+      const int remote_items = (num_m - tpr) * kCopyParts;
+      const int et = threadIdx.x - 64;                    // index among the epilogue threads
+      const int total = (kBlockM / kCopyParts) * (K / 8); // 16-byte chunks per piece
+      for (int item = blockIdx.x; item < remote_items; item += gridDim.x) {
+        const int c = item / kCopyParts, part = item - c * kCopyParts;
+        int mt = c + tpr + peer.rank * tpr;               // consumption order -> global tile index
+        while (mt >= num_m) mt -= num_m;
+        const int owner = (mt * kBlockM) / peer.rows_per_rank;
+        const long long row0 = static_cast<long long>(mt) * kBlockM + part * (kBlockM / kCopyParts);
+        const uint4* src = reinterpret_cast<const uint4*>(peer.a_peer[owner] +
+                                                          (row0 - static_cast<long long>(owner) * peer.rows_per_rank) * K);
+        uint4* dst = reinterpret_cast<uint4*>(peer.a_full + row0 * K);
+        int i = et;
+        for (; i + 7 * kNumEpiThreads < total; i += 8 * kNumEpiThreads) {       // eight peer loads in flight per thread
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = src[i + u * kNumEpiThreads];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) dst[i + u * kNumEpiThreads] = v[u];
+        }
+        for (; i < total; i += kNumEpiThreads) dst[i] = src[i];
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kNumEpiThreads) : "memory");
+        if (et == 0) {
+          fence_proxy_async_all();
+          red_release_gpu_add(peer.ready + mt, 1u);
+        }
+      }
+    }
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < num_units; tile += gridDim.x, ++t) {
       int m_blk, n_blk, kb0, kb1, outer;
@@ -380,14 +498,87 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (ep.out_f32) epu.d = reinterpret_cast<float*>(ep.d) + static_cast<long long>(outer) * grp.d_expert_stride;
         else epu.d = reinterpret_cast<__nv_bfloat16*>(ep.d) + static_cast<long long>(outer) * grp.d_expert_stride;
       }
+      if (peer.mode == 2) {
+        // this tile's rows belong to `owner`; write into the owner's receive slot for this rank
+        const int owner = (m_blk * kBlockM) / peer.rows_per_rank;
+        epu.d = peer.d_peer[owner] + (static_cast<long long>(peer.rank) - owner) * peer.rows_per_rank * ep.ldd;
+      }
       const bool empty_k = kb1 <= kb0;     // an expert without tokens: the accumulator was never written
       const uint32_t acc = t & 1, acc_ph = (t >> 1) & 1;
       if (!mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, status, 4)) break;
       tc_fence_after();
       const long long row = static_cast<long long>(m_blk) * kBlockM + q * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
+      if (epu.staged) {
+        // registers -> swizzled per-warp tile in shared memory -> whole row segments to global / peer memory
+        constexpr int SC = L::kStageCols, CPR = SC / 8;           // staged columns, 16-byte chunks per row
+        const uint32_t stg = smem_base + L::kStagingOffset + ew * L::kStagingBytesPerWarp;
+        constexpr int NB = (BLOCK_N / 2) / SC;                    // column blocks per warp group
+        const bool two_pass = epu.aux_out != nullptr &&
+                              (epu.act == RB_ACT_GELU || epu.act == RB_ACT_RELU || epu.act == RB_ACT_SILU);
+        const int num_pass = two_pass ? 2 : 1;
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        for (int hp = 0; hp < NB * num_pass; ++hp) {
+          // with a saved pre-activation every column block is read from TMEM twice: first the pre-activation
+          // goes out to aux_out, then the activated value to d
+          const int h = hp / num_pass;
+          const bool pre_pass = two_pass && (hp - h * num_pass) == 0;
+          const bool last_pass = hp == NB * num_pass - 1;
+          __nv_bfloat16* dbase = pre_pass ? epu.aux_out : reinterpret_cast<__nv_bfloat16*>(epu.d);
+          const long long dld = pre_pass ? epu.ld_aux_out : epu.ldd;
+#pragma unroll 1
+          for (int cc = 0; cc < SC / 32; ++cc) {
+            const int c = cgrp * (BLOCK_N / 64) + h * (SC / 32) + cc;
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c * 32, r);
+            tmem_ld_wait();
+            if (last_pass && cc == SC / 32 - 1) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+            }
+            const int col0 = n_blk * BLOCK_N + c * 32;
+            float v[32];
+            if (empty_k) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
+            if (row < M && col0 < N) {
+              if (pre_pass) epilogue_math<false, true>(epu, r, row, col0, N, v);
+              else epilogue_math<false, false>(epu, r, row, col0, N, v);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            }
+#pragma unroll
+            for (int qq = 0; qq < 4; ++qq) {
+              const int chunk = cc * 4 + qq;
+              const uint32_t addr = stg + lane * (SC * 2) + ((chunk ^ (lane & (CPR - 1))) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                           "r"(pack_bf16x2(v[qq * 8 + 0], v[qq * 8 + 1])), "r"(pack_bf16x2(v[qq * 8 + 2], v[qq * 8 + 3])),
+                           "r"(pack_bf16x2(v[qq * 8 + 4], v[qq * 8 + 5])), "r"(pack_bf16x2(v[qq * 8 + 6], v[qq * 8 + 7]))
+                           : "memory");
+            }
+          }
+          __syncwarp();
+          constexpr int RPI = 32 / CPR;                            // rows written per warp instruction
+          const int ch = lane % CPR, rsub = lane / CPR;
+          const int colg = n_blk * BLOCK_N + cgrp * (BLOCK_N / 2) + h * SC + ch * 8;
+#pragma unroll 4
+          for (int r0 = 0; r0 < 32; r0 += RPI) {
+            const int rl = r0 + rsub;
+            const long long rg = static_cast<long long>(m_blk) * kBlockM + q * 32 + rl;
+            uint4 val;
+            const uint32_t addr = stg + rl * (SC * 2) + ((ch ^ (rl & (CPR - 1))) << 4);
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr));
+            if (rg < M && colg < N) *reinterpret_cast<uint4*>(dbase + rg * dld + colg) = val;
+          }
+          __syncwarp();
+        }
+        continue;
+      }
+#pragma unroll 1
+      for (int c = cgrp * (BLOCK_N / 64); c < (cgrp + 1) * (BLOCK_N / 64); ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
@@ -395,7 +586,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (c == BLOCK_N / 32 - 1) {
+        if (c == (cgrp + 1) * (BLOCK_N / 64) - 1) {
           // all of this warp's accumulator reads are done: hand the buffer back to the MMA warp
           tc_fence_before();
           __syncwarp();
@@ -460,16 +651,31 @@ splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long slab, v
 // ---------------------------------------------------------------------------------------------
 namespace {
 
+// RUSTRAL_GEMM_STAGED=0/1 turns the shared-memory staged output path off / on for ordinary (non-peer) GEMMs.
+bool staged_store_default() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("RUSTRAL_GEMM_STAGED");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 template <int A_MN, int B_MN, int BLOCK_N, int STAGES>
 int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, int grid, int splits, cudaStream_t stream) {
   using L = rb::SmemLayout<BLOCK_N, STAGES>;
   auto kern = rb::gemm_bf16_kernel<A_MN, B_MN, BLOCK_N, STAGES>;
-  const int smem = L::kTotal + 1024;
-  static bool configured = false;   // per instantiation
-  if (!configured) {
+  // Staged (coalesced) stores: plain bf16 outputs whose rows are whole 16-byte chunks.  Always on for peer stores.
+  const bool can_stage = !g.out_f32 && !g.accumulate && splits <= 1 && (g.N % 8 == 0) && g.group_mode != 2 &&
+                         L::kTotalStaged + 1024 <= 232448;
+  const bool staged = can_stage && (g.peer_mode == 2 || staged_store_default());
+  if (g.peer_mode == 2 && !staged) return -11;
+  const int smem = (staged ? L::kTotalStaged : L::kTotal) + 1024;
+  static int configured = 0;   // per instantiation: largest size set so far
+  if (configured < smem) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured = smem;
   }
   rb::EpiParams ep;
   ep.d = g.d; ep.ldd = g.ldd;
@@ -478,6 +684,7 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
   ep.aux_in = reinterpret_cast<const __nv_bfloat16*>(g.aux_in); ep.ld_aux_in = g.ld_aux_in;
   ep.aux_out = reinterpret_cast<__nv_bfloat16*>(g.aux_out); ep.ld_aux_out = g.ld_aux_out;
   ep.act = g.act; ep.out_f32 = g.out_f32; ep.accumulate = g.accumulate; ep.alpha = g.alpha;
+  ep.staged = staged ? 1 : 0;
   const int group_m = g.group_m > 0 ? g.group_m : 8;
   const int num_kb = (g.K + rb::kBlockK - 1) / rb::kBlockK;
   int kb_per = num_kb;
@@ -494,7 +701,17 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
   grp.num_m_tiles = reinterpret_cast<const int*>(g.num_m_tiles);
   grp.offsets = reinterpret_cast<const int*>(g.expert_offsets);
   grp.b_expert_rows = g.b_expert_rows; grp.d_expert_stride = g.d_expert_stride;
-  kern<<<grid, rb::kNumThreads, smem, stream>>>(*ta, *tb, g.M, g.N, g.K, group_m, splits, kb_per, slab, ep, grp,
+  rb::PeerInfo peer;
+  memset(&peer, 0, sizeof(peer));
+  peer.mode = g.peer_mode; peer.world = g.peer_world; peer.rank = g.peer_rank; peer.rows_per_rank = g.rows_per_rank;
+  peer.a_full = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(g.a));
+  peer.ready = reinterpret_cast<unsigned int*>(g.ready_flags);
+  peer.epoch = g.peer_epoch;
+  for (int r = 0; r < 8; ++r) {
+    peer.a_peer[r] = reinterpret_cast<const __nv_bfloat16*>(g.peer_ptrs[r]);
+    peer.d_peer[r] = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(g.peer_ptrs[r]));
+  }
+  kern<<<grid, rb::kNumThreads, smem, stream>>>(*ta, *tb, g.M, g.N, g.K, group_m, splits, kb_per, slab, ep, grp, peer,
                                                 rbhost::status_ptr());
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || splits <= 1) return static_cast<int>(e);
@@ -528,7 +745,7 @@ long long plan_cost(int M, int N, int bn, int splits, int sms) {
 void pick_plan(const RbGemmArgs& g, int sms, int& bn_out, int& splits_out) {
   const int cands[4] = {256, 192, 128, 64};
   const int split_cands[7] = {1, 2, 3, 4, 6, 8, 12};
-  const bool can_split = g.group_mode == 0 && g.workspace != nullptr && g.act == RB_ACT_NONE && !g.bias && !g.residual && !g.aux_out &&
+  const bool can_split = g.group_mode == 0 && g.peer_mode == 0 && g.workspace != nullptr && g.act == RB_ACT_NONE && !g.bias && !g.residual && !g.aux_out &&
                          (g.N % 4 == 0) && (static_cast<long long>(g.M) * g.N % 4 == 0);
   long long best = -1;
   bn_out = 128; splits_out = 1;
@@ -573,6 +790,15 @@ RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
   if (g.group_mode == 1 && (!g.tile_expert || !g.num_m_tiles || g.b_expert_rows <= 0)) return -8;
   if (g.group_mode == 1 && g.b_mn_major && (g.K % 64)) return -8;     // expert K ranges must be whole k-blocks
   if (g.group_mode == 2 && (!g.expert_offsets || g.num_experts <= 0 || !g.a_mn_major || !g.b_mn_major)) return -8;
+  if (g.peer_mode < 0 || g.peer_mode > 2) return -11;
+  if (g.peer_mode != 0) {
+    if (g.peer_world < 2 || g.peer_world > 8 || g.peer_rank < 0 || g.peer_rank >= g.peer_world) return -11;
+    if (g.rows_per_rank <= 0 || (g.rows_per_rank % 128) || g.rows_per_rank * g.peer_world != g.M) return -11;
+    if (g.a_mn_major || g.group_mode != 0 || g.out_f32) return -11;
+    for (int r = 0; r < g.peer_world; ++r)
+      if (!g.peer_ptrs[r] || (reinterpret_cast<uintptr_t>(g.peer_ptrs[r]) & 15)) return -11;
+    if (g.peer_mode == 1 && (!g.ready_flags || g.lda != g.K)) return -11;       // a_full is dense [M, K]
+  }
   const int sms = rbhost::device_sm_count();
   if (g.block_n != 0 && g.block_n != 64 && g.block_n != 128 && g.block_n != 192 && g.block_n != 256) return -6;
   int bn = 128, splits = 1;

@@ -133,6 +133,13 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap* tmap, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_src), "r"(x), "r"(y)
@@ -271,6 +278,27 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
   float du = k0 * (1.f + 3.f * k1 * x2);
   return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
 }
+// tanh.approx.f32 (one MUFU instruction, max relative error about 2^-11): for GEMM epilogues, whose results are
+// rounded to bf16 (2^-9) anyway and whose four warps have to keep up with the tensor cores.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float u = k0 * fmaf(k1 * x * x, x, x);
+  const float hx = 0.5f * x;
+  return fmaf(hx, tanh_fast(u), hx);
+}
+__device__ __forceinline__ float gelu_tanh_grad_fast(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float x2 = x * x;
+  const float u = k0 * fmaf(k1 * x2, x, x);
+  const float t = tanh_fast(u);
+  const float du = k0 * fmaf(3.f * k1, x2, 1.f);
+  return fmaf(0.5f * x * (1.f - t * t), du, fmaf(0.5f, t, 0.5f));
+}
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float silu_grad(float x) {
   float s = 1.f / (1.f + __expf(-x));
@@ -310,6 +338,9 @@ namespace rbhost {
 // Returns nullptr (and sets *err) on failure.
 const CUtensorMap* get_tmap_2d(const void* base, int elem_bytes, uint64_t inner, uint64_t outer, uint64_t ld,
                                uint32_t box_inner, uint32_t box_outer, int swizzle128, int* err);
+
+const CUtensorMap* get_tmap_4d(const void* base, int elem_bytes, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                               const uint32_t box[4], int swizzle128, int* err);
 
 int device_sm_count();
 

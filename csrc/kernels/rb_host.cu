@@ -84,6 +84,45 @@ const CUtensorMap* get_tmap_2d(const void* base, int elem_bytes, uint64_t inner,
   return m;
 }
 
+// 4-D variant for [batch, seq, head, dim] views: dims / strides are given innermost first, strides in BYTES for
+// dimensions 1..3 (dimension 0 is contiguous).
+const CUtensorMap* get_tmap_4d(const void* base, int elem_bytes, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                               const uint32_t box[4], int swizzle128, int* err) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  Key k;
+  k.v[0] = reinterpret_cast<uint64_t>(base);
+  k.v[1] = dims[0] | (dims[1] << 20) | (dims[2] << 40);
+  k.v[2] = dims[3] | (static_cast<uint64_t>(box[0]) << 32) | (static_cast<uint64_t>(box[2]) << 44);
+  k.v[3] = strides_bytes[0];
+  k.v[4] = strides_bytes[1];
+  k.v[5] = strides_bytes[2];
+  k.v[6] = static_cast<uint64_t>(elem_bytes) | (static_cast<uint64_t>(swizzle128) << 8) | (4ull << 16) |
+           (static_cast<uint64_t>(box[1]) << 24) | (static_cast<uint64_t>(box[3]) << 40);
+  k.v[7] = static_cast<uint64_t>(dev);
+  std::lock_guard<std::mutex> lock(g_mu);
+  auto it = g_cache.find(k);
+  if (it != g_cache.end()) return it->second;
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { if (err) *err = -10; return nullptr; }
+  CUtensorMap* m = new CUtensorMap;
+  cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t gstride[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t bx[4] = {box[0], box[1], box[2], box[3]};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(m, dt, 4, const_cast<void*>(base), gdim, gstride, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    delete m;
+    if (err) *err = -100 - static_cast<int>(r);
+    return nullptr;
+  }
+  g_cache.emplace(k, m);
+  return m;
+}
+
 int device_sm_count() {
   static int cached[64] = {0};
   int dev = 0;

@@ -33,6 +33,8 @@ class RbGemmArgs(C.Structure):
         ("workspace", c_void_p), ("workspace_bytes", c_ll),
         ("group_mode", c_int), ("num_experts", c_int), ("tile_expert", c_void_p), ("num_m_tiles", c_void_p),
         ("expert_offsets", c_void_p), ("b_expert_rows", c_int), ("d_expert_stride", c_ll),
+        ("peer_mode", c_int), ("peer_world", c_int), ("peer_rank", c_int), ("rows_per_rank", c_int),
+        ("peer_epoch", C.c_uint), ("ready_flags", c_void_p), ("peer_ptrs", c_void_p * 8),
     ]
 
 

@@ -1,0 +1,153 @@
+"""Micro-benchmarks of single kernels with roofline fractions.
+
+    python -m rustral_b200.bench.kernels gemm --m 32768 --n 2304 --k 768 [--act gelu] [--iters 10]
+    python -m rustral_b200.bench.kernels attention --batch 32 --seq 1024 --heads 12 --head-dim 64 [--impl tc|mma] [--backward]
+    python -m rustral_b200.bench.kernels norm --rows 32768 --n 768
+    python -m rustral_b200.bench.kernels adam --numel 124000000
+
+Timing: CUDA events around each call on the current stream, `--warmup` untimed calls first, a 256 MiB buffer is
+overwritten between timed calls so every call starts with a cold L2; the median is reported.  Fractions are
+against the copy bandwidth and cuBLAS bf16 throughput measured on the same GPU type (`MEASURED_PEAKS.json` at the
+repository root when present, else 6650 GB/s and 1590 TFLOP/s).  One JSON line per run.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+
+def peaks() -> dict:
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def timed(fn, warmup: int, iters: int) -> float:
+    """Median milliseconds per call, cold L2."""
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def report(name: str, ms: float, flops: float, nbytes: float, extra: dict) -> dict:
+    pk = peaks()
+    out = {"kernel": name, "us": round(ms * 1e3, 2), **extra}
+    if flops:
+        out["tflops"] = round(flops / ms / 1e9, 1)
+        out["frac_of_bf16_peak"] = round(out["tflops"] / pk["bf16_tflops"], 3)
+    if nbytes:
+        out["gbs"] = round(nbytes / ms / 1e6, 1)
+        out["frac_of_hbm_peak"] = round(out["gbs"] / pk["hbm_gbs"], 3)
+    out["peaks"] = pk["source"]
+    print(json.dumps(out))
+    return out
+
+
+def bench_gemm(a):
+    from ..ops.matmul import gemm
+    dev = "cuda"
+    x = torch.randn(a.m, a.k, device=dev).bfloat16()
+    w = (torch.randn(a.n, a.k, device=dev) * 0.02).bfloat16()
+    out = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=dev)
+    pre = torch.empty_like(out) if a.act != "none" else None
+    bias = torch.zeros(a.n, dtype=torch.bfloat16, device=dev) if a.bias or a.act != "none" else None
+    fn = lambda: gemm(x, w, out=out, act=a.act, aux_out=pre, bias=bias, block_n=a.block_n)
+    ms = timed(fn, a.warmup, a.iters)
+    nbytes = 2.0 * (a.m * a.k + a.n * a.k + a.m * a.n * (2 if pre is not None else 1))
+    return report("gemm_bf16_tcgen05", ms, 2.0 * a.m * a.n * a.k, nbytes,
+                  {"m": a.m, "n": a.n, "k": a.k, "act": a.act})
+
+
+def bench_attention(a):
+    from ..ops import attention as A
+    B, S, H, D = a.batch, a.seq, a.heads, a.head_dim
+    hk = a.kv_heads or H
+    mk = lambda *s: torch.randn(*s, device="cuda").bfloat16()
+    q, k, v = mk(B, S, H, D), mk(B, S, hk, D), mk(B, S, hk, D)
+    o = torch.empty_like(q)
+    sc = 1.0 / math.sqrt(D)
+    flops_fwd = 4.0 * B * H * S * S * D * (0.5 if a.causal else 1.0)
+    if not a.backward:
+        ms = timed(lambda: A.attention_forward(q, k, v, a.causal, sc, out=o, impl=a.impl), a.warmup, a.iters)
+        return report(f"attention_fwd_{a.impl}", ms, flops_fwd, 0, {"batch": B, "seq": S, "heads": H, "head_dim": D})
+    o, lse = A.attention_forward(q, k, v, a.causal, sc, impl=a.impl)
+    do = torch.randn_like(o)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ms = timed(lambda: A.attention_backward(do, q, k, v, o, lse, a.causal, sc, dq, dk, dv), a.warmup, a.iters)
+    return report("attention_bwd", ms, 2.5 * flops_fwd, 0, {"batch": B, "seq": S, "heads": H, "head_dim": D})
+
+
+def bench_norm(a):
+    from ..ops import norm as Nn
+    x = torch.randn(a.rows, a.n, device="cuda").bfloat16()
+    g = torch.ones(a.n, device="cuda").bfloat16()
+    b = torch.zeros(a.n, device="cuda").bfloat16()
+    fn = lambda: Nn.layer_norm(x, g, b, 1e-5)
+    ms = timed(fn, a.warmup, a.iters)
+    return report("layer_norm_fwd", ms, 0, 4.0 * a.rows * a.n, {"rows": a.rows, "n": a.n})
+
+
+def bench_adam(a):
+    from ..ops import optim as O
+    n = a.numel
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda") * 1e-3
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    lowp = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    fn = lambda: O.adam_step(p, m, v, g, lr=1e-3, step=1, p_lowp=lowp)
+    ms = timed(fn, a.warmup, a.iters)
+    return report("adam_step", ms, 0, n * (4 * 4 + 3 * 4 + 2.0), {"numel": n})
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="rustral_b200.bench.kernels")
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=10)
+    sub = ap.add_subparsers(dest="op", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=8192)
+    g.add_argument("--n", type=int, default=8192)
+    g.add_argument("--k", type=int, default=8192)
+    g.add_argument("--act", default="none")
+    g.add_argument("--bias", action="store_true")
+    g.add_argument("--block-n", type=int, default=0)
+    t = sub.add_parser("attention")
+    t.add_argument("--batch", type=int, default=32)
+    t.add_argument("--seq", type=int, default=1024)
+    t.add_argument("--heads", type=int, default=12)
+    t.add_argument("--kv-heads", type=int, default=0)
+    t.add_argument("--head-dim", type=int, default=64)
+    t.add_argument("--impl", default="tc", choices=["tc", "mma"])
+    t.add_argument("--no-causal", dest="causal", action="store_false")
+    t.add_argument("--backward", action="store_true")
+    n = sub.add_parser("norm")
+    n.add_argument("--rows", type=int, default=32768)
+    n.add_argument("--n", type=int, default=768)
+    d = sub.add_parser("adam")
+    d.add_argument("--numel", type=int, default=124_000_000)
+    a = ap.parse_args(argv)
+    return {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam}[a.op](a)
+
+
+if __name__ == "__main__":
+    main()

@@ -42,7 +42,13 @@ def _fill(args, q, k, v, o, causal, scale):
     args.causal, args.scale = int(causal), scale
 
 
-def attention_forward(q, k, v, causal: bool, scale: float, out=None, want_lse: bool = True):
+N.optional_sig("rb_attention_fwd_tc", [N.C.POINTER(N.RbAttnArgs), N.c_void_p])
+
+# "tc": tcgen05 / TMEM kernel (falls back to "mma" for shapes it does not take); "mma": the mma.sync kernel.
+FORWARD_IMPL = __import__("os").environ.get("RUSTRAL_ATTN_IMPL", "tc")
+
+
+def attention_forward(q, k, v, causal: bool, scale: float, out=None, want_lse: bool = True, impl: str | None = None):
     """q: [B, Sq, H, D]; k, v: [B, Sk, Hkv, D] (any strides with a contiguous D).  Returns (o, lse)."""
     B, Sq, H, D = q.shape
     for t in (q, k, v):
@@ -53,7 +59,13 @@ def attention_forward(q, k, v, causal: bool, scale: float, out=None, want_lse: b
     a = N.RbAttnArgs()
     _fill(a, q, k, v, o, causal, scale)
     a.lse = N.ptr(lse)
-    N.check(N.kernels().rb_attention_fwd(a, N.stream_ptr()), "rb_attention_fwd")
+    lib = N.kernels()
+    if (impl or FORWARD_IMPL) == "tc" and hasattr(lib, "rb_attention_fwd_tc"):
+        rc = lib.rb_attention_fwd_tc(a, N.stream_ptr())
+        if rc != -9:
+            N.check(rc, "rb_attention_fwd_tc")
+            return o, lse
+    N.check(lib.rb_attention_fwd(a, N.stream_ptr()), "rb_attention_fwd")
     return o, lse
 
 
@@ -105,4 +117,19 @@ def flash_attention(q, k, v, causal: bool = True, scale: float | None = None):
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
     if not q.is_cuda:
         return attention_reference(q, k, v, causal, scale)
-    return _FlashFn.apply(q, k, v, causal, scale)
+    D = q.shape[-1]
+    in_dtype = q.dtype
+    if in_dtype != torch.bfloat16:
+        q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    if D not in (64, 128):
+        # The kernels take head dimensions 64 and 128.  Zero columns change neither QK^T nor the kept
+        # columns of PV, so other sizes run padded (the scale stays that of the true head dimension).
+        if D > 128:
+            raise ValueError(f"flash_attention: head dimension {D} > 128 is not supported")
+        Dp = 64 if D < 64 else 128
+        pad = lambda t: torch.nn.functional.pad(t, (0, Dp - D))
+        o = _FlashFn.apply(pad(q), pad(k), pad(v), causal, scale)[..., :D]
+    else:
+        q, k, v = (t if t.stride(3) == 1 else t.contiguous() for t in (q, k, v))
+        o = _FlashFn.apply(q, k, v, causal, scale)
+    return o if in_dtype == torch.bfloat16 else o.to(in_dtype)

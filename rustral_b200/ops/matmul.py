@@ -93,7 +93,12 @@ def _workspace(device) -> torch.Tensor:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, act: str = "none",
          residual=None, aux_in=None, aux_out=None, out=None, out_dtype=None, accumulate: bool = False,
-         alpha: float = 1.0, block_n: int = 0, group_m: int = 0, max_ctas: int = 0, splits: int = 0) -> torch.Tensor:
+         alpha: float = 1.0, block_n: int = 0, group_m: int = 0, max_ctas: int = 0, splits: int = 0,
+         peer: dict | None = None) -> torch.Tensor:
+    """`peer` selects the tensor-parallel modes of the kernel (see parallel/fused_tp.py): a dict with `mode`
+    (1: remote row blocks of A are pulled from the peers' shards inside the kernel; 2: output row blocks are
+    stored into their owner's receive slot), `world`, `rank`, `rows_per_rank`, `epoch`, `ready_flags` (pointer,
+    mode 1) and `peer_ptrs` (one device address per rank)."""
     assert a.dim() == 2 and b.dim() == 2
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
     Nn, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
@@ -137,7 +142,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     g.accumulate = int(accumulate)
     g.alpha = alpha
     g.block_n, g.group_m, g.max_ctas, g.splits = block_n, group_m, max_ctas, splits
-    if splits != 1 and K >= 2048 and act == "none" and bias is None and residual is None:
+    if peer is not None:
+        g.peer_mode, g.peer_world, g.peer_rank = peer["mode"], peer["world"], peer["rank"]
+        g.rows_per_rank, g.peer_epoch = peer["rows_per_rank"], peer["epoch"] & 0xFFFFFFFF
+        g.ready_flags = peer.get("ready_flags")
+        for r, pp in enumerate(peer["peer_ptrs"]):
+            g.peer_ptrs[r] = pp
+        g.splits = 1
+    elif splits != 1 and K >= 2048 and act == "none" and bias is None and residual is None:
         ws = _workspace(a.device)
         g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel()
     N.check(N.kernels().rb_gemm_bf16(g, N.stream_ptr()), "rb_gemm_bf16")

@@ -102,6 +102,7 @@ class TensorParallelLinear(Module, Trainable, Saveable):
     def __init__(self, style: ParallelStyle, weight: Parameter, bias, process_group: ProcessGroup, in_dim: int, out_dim: int,
                  gather_output: bool = False, input_is_parallel: bool = True, sequence_parallel: bool = False,
                  activation: str = "none"):
+        self.fused_tp = None     # a parallel.fused_tp.FusedTP: sequence-parallel layers then run the fused kernels
         self.style, self.weight, self.bias, self._pg = style, weight, bias, process_group
         self.in_dim, self.out_dim = in_dim, out_dim
         self.gather_output, self.input_is_parallel, self.sequence_parallel = gather_output, input_is_parallel, sequence_parallel
@@ -136,8 +137,43 @@ class TensorParallelLinear(Module, Trainable, Saveable):
         bp = backend.constant_parameter("bias", (out_dim,), 0.0) if bias else None
         return cls(ParallelStyle.ROW, wp, bp, pg, in_dim, out_dim, False, input_is_parallel, sequence_parallel)
 
+    def use_fused(self, fused_tp) -> "TensorParallelLinear":
+        """Route the sequence-parallel forward and backward through the fused all-gather->GEMM / GEMM->reduce-scatter
+        kernels of `fused_tp` (CUDA, rows per rank a multiple of 128; other inputs keep the collective path)."""
+        self.fused_tp = fused_tp
+        return self
+
+    def _fused_forward(self, x, residual):
+        from .fused_tp import ColumnSeqParallelFn, RowSeqParallelFn
+        tp = self.fused_tp
+        b = None if self.bias is None else self.bias.tensor
+        x2 = x.reshape(-1, x.shape[-1])
+        if self.style is ParallelStyle.COLUMN:
+            y = ColumnSeqParallelFn.apply(x2, self.weight.tensor, b, self.activation, tp)
+            return y.reshape(x.shape[0] * tp.world, *x.shape[1:-1], y.shape[-1])
+        res2 = None
+        if residual is not None and b is None:
+            res2 = residual.reshape(-1, residual.shape[-1])
+        y = RowSeqParallelFn.apply(x2, self.weight.tensor, res2, tp)
+        y = y.reshape(x.shape[0] // tp.world, *x.shape[1:-1], y.shape[-1])
+        if b is not None:
+            y = y + b
+            if residual is not None:
+                y = y + residual
+        return y
+
+    def _can_fuse(self, x) -> bool:
+        if self.fused_tp is None or not self.sequence_parallel or not x.is_cuda or x.dtype != torch.bfloat16:
+            return False
+        rows = x.numel() // x.shape[-1]
+        if self.style is ParallelStyle.COLUMN:
+            return self.fused_tp.supports(rows)
+        return self.input_is_parallel and rows % self.fused_tp.world == 0 and self.fused_tp.supports(rows // self.fused_tp.world)
+
     def forward(self, x, ctx: ForwardCtx | None = None, residual=None):
         pg = self._pg
+        if self._can_fuse(x):
+            return self._fused_forward(x, residual)
         b = None if self.bias is None else self.bias.tensor
         if self.style is ParallelStyle.COLUMN:
             x = _GatherSeq.apply(x, pg) if self.sequence_parallel else _CopyToTP.apply(x, pg)

@@ -283,3 +283,23 @@ def test_moe_plan_is_deterministic_and_padded(cuda_status):
     for a in ("counts", "offsets", "slot_pos", "row_slot", "tile_expert", "num_tiles"):
         assert torch.equal(getattr(pg, a).cpu(), getattr(pc, a)), a
     assert all(int(o) % 128 == 0 for o in pc.offsets)
+
+
+@pytest.mark.parametrize("B,Sq,Sk,H,Hk,D,causal", [(2, 128, 128, 4, 4, 64, True), (1, 200, 200, 3, 3, 64, True),
+                                                  (2, 96, 96, 4, 2, 64, False), (1, 256, 256, 4, 1, 128, True),
+                                                  (1, 77, 77, 2, 2, 128, False), (2, 1024, 1024, 2, 2, 64, True),
+                                                  (1, 64, 320, 2, 2, 64, True), (1, 384, 384, 2, 2, 128, True)])
+def test_flash_attention_forward_tcgen05(B, Sq, Sk, H, Hk, D, causal, cuda_status):
+    q, k, v = _bf((B, Sq, H, D), 1), _bf((B, Sk, Hk, D), 2), _bf((B, Sk, Hk, D), 3)
+    ref = attn_ops.attention_reference(q, k, v, causal)
+    scale = 1 / math.sqrt(D)
+    o_tc, lse_tc = attn_ops.attention_forward(q.cuda(), k.cuda(), v.cuda(), causal, scale, impl="tc")
+    o_mma, lse_mma = attn_ops.attention_forward(q.cuda(), k.cuda(), v.cuda(), causal, scale, impl="mma")
+    _close(o_tc, ref, what="tc o")
+    _close(lse_tc, lse_mma, tol=1e-3, what="tc lse")
+    # packed QKV views (strided heads) go through the 4-D tensor maps unchanged
+    if Sq == Sk and H == Hk:
+        qkv = torch.cat([q.reshape(B, Sq, -1), k.reshape(B, Sq, -1), v.reshape(B, Sq, -1)], -1).cuda()
+        qs, ks, vs = (qkv[:, :, i * H * D:(i + 1) * H * D].view(B, Sq, H, D) for i in range(3))
+        o2, _ = attn_ops.attention_forward(qs, ks, vs, causal, scale, impl="tc")
+        assert torch.equal(o2, o_tc)
