@@ -1,0 +1,479 @@
+// Flash attention backward on the 5th-generation tensor cores: two kernels from one template, no atomics.
+//
+//   MODE_DKV  one CTA owns 128 keys of one (batch, kv head) and walks over the query tiles that see them
+//             (all query heads of the group):  dV += P^T dO,  dK += dS^T Q   (accumulators stay in TMEM for the whole walk)
+//   MODE_DQ   one CTA owns 128 queries of one (batch, head) and walks over the key tiles they see:  dQ += dS K
+//
+// Per (query tile, key tile) pair, in both modes:
+//   S  = Q K^T, dP = dO V^T        tcgen05.mma (SS) into two 128-column TMEM accumulators
+//   P  = exp2(S * scale * log2e - lse * log2e), dS = P * (dP - delta)
+//                                   eight warps; a thread owns one query row (its TMEM lane) and 64 of the 128 keys;
+//                                   P and dS go to shared memory as bf16 in the 128-byte-swizzled layout
+//   dV / dK / dQ                    tcgen05.mma (SS) reading P and dS either K-major (dQ) or transposed through an
+//                                   MN-major descriptor (dV, dK), and dO / Q / K MN-major straight from their row layout
+// The tiles of the walk arrive by TMA (4-D maps over the strided [batch, seq, head, dim] views), double buffered when
+// shared memory allows.  The S / dP products of step t+1 are issued before the dV / dK / dQ products of step t, so the
+// tensor cores work on them while the warps are still in step t's exponentials.
+//
+// Roles: warps 0-7 softmax / dS / epilogue, warp 8 TMA producer, warp 9 MMA issuer.  Every wait is bounded.
+// Same semantics as the mma.sync backward in attention.cu (causal alignment to the end of the keys, GQA).
+#include "attention.h"
+
+#include "rb_common.cuh"
+
+namespace rb {
+
+constexpr int kBtThreads = 320;
+constexpr int kBtTile = 128;
+constexpr float kBtLog2e = 1.4426950408889634f;
+constexpr int MODE_DKV = 0;
+constexpr int MODE_DQ = 1;
+
+struct BtParams {
+  const float* lse;
+  const float* delta;
+  __nv_bfloat16* out0;      // MODE_DKV: dK;  MODE_DQ: dQ
+  __nv_bfloat16* out1;      // MODE_DKV: dV
+  long long o0_bs, o0_rs, o0_hs, o1_bs, o1_rs, o1_hs;
+  int seq_q, seq_k, heads, kv_heads, causal;
+  float scale;
+};
+
+__device__ __forceinline__ float bt_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int D, int MODE>
+struct BtSmem {
+  static constexpr int kHalf = kBtTile * 128;                  // 128 rows x 128 B: one 64-column swizzle atom column
+  static constexpr int kTileBytes = (D / 64) * kHalf;          // one [128, D] operand tile
+  // streamed pair double buffered when it fits: always for head dim 64, for head dim 128 only in MODE_DQ (no P buffer)
+  static constexpr int kStages = (D == 64 || MODE == MODE_DQ) ? 2 : 1;
+  static constexpr int kRes0 = 0;                              // resident pair: (K, V) in MODE_DKV, (Q, dO) in MODE_DQ
+  static constexpr int kRes1 = kRes0 + kTileBytes;
+  static constexpr int kStream = kRes1 + kTileBytes;           // per stage: two tiles
+  static constexpr int kDs = kStream + kStages * 2 * kTileBytes;
+  static constexpr int kP = kDs + 2 * kHalf;
+  static constexpr int kBar = kP + (MODE == MODE_DKV ? 2 * kHalf : 0);
+  static constexpr int kNumBars = 12;
+  static constexpr int kTotal = kBar + kNumBars * 8 + 16;
+};
+
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_delta_tc_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                     long long bs, long long rs, long long hs, int heads, int seq_q) {
+  // one warp per (head, row): delta = sum_d dO * O
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long idx = static_cast<long long>(blockIdx.x) * 4 + warp;
+  const int b = blockIdx.y;
+  if (idx >= static_cast<long long>(heads) * seq_q) return;
+  const int h = static_cast<int>(idx / seq_q), r = static_cast<int>(idx % seq_q);
+  const long long off = b * bs + h * hs + static_cast<long long>(r) * rs;
+  float acc = 0.f;
+  for (int c = lane * 2; c < D; c += 64) {
+    const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(o + off + c));
+    const float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(d_o + off + c));
+    acc += a.x * g.x + a.y * g.y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) delta[(static_cast<long long>(b) * heads + h) * seq_q + r] = acc;
+}
+
+template <int D, int MODE>
+__global__ void __launch_bounds__(kBtThreads, 1)
+attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BtParams p,
+                   unsigned int* status) {
+  using L = BtSmem<D, MODE>;
+  constexpr int STAGES = L::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
+  const uint32_t b0 = smem_u32(bars);
+  const uint32_t bar_res = b0, bar_tfull = b0 + 8, bar_tempty = b0 + 24, bar_sdp_full = b0 + 40, bar_sdp_empty = b0 + 48,
+                 bar_p_full = b0 + 56, bar_p_empty = b0 + 64, bar_acc_full = b0 + 72;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int blk = gridDim.x - 1 - blockIdx.x;
+  const int b = blockIdx.z;
+  const int group = p.heads / p.kv_heads;
+  const int shift = p.seq_k - p.seq_q;
+  const int n_q_tiles = (p.seq_q + kBtTile - 1) / kBtTile;
+  const int n_k_tiles = (p.seq_k + kBtTile - 1) / kBtTile;
+
+  // The walk: MODE_DKV over (head of the group, query tile >= first), MODE_DQ over key tiles <= last.
+  int own0, walk_first, walk_count, n_it, head_q0, head_k;
+  if (MODE == MODE_DKV) {
+    own0 = blk * kBtTile;                       // first key of the owned tile
+    head_k = blockIdx.y;
+    head_q0 = head_k * group;
+    walk_first = 0;
+    if (p.causal && own0 - shift > 0) walk_first = (own0 - shift) / kBtTile;
+    walk_count = n_q_tiles - walk_first;
+    if (walk_count < 0) walk_count = 0;
+    n_it = walk_count * group;
+  } else {
+    own0 = blk * kBtTile;                       // first query of the owned tile
+    head_q0 = blockIdx.y;
+    head_k = head_q0 / group;
+    walk_first = 0;
+    walk_count = n_k_tiles;
+    if (p.causal) {
+      const int lim = (own0 + kBtTile - 1 + shift) / kBtTile + 1;
+      if (lim < walk_count) walk_count = lim;
+    }
+    n_it = walk_count;
+  }
+  auto walk_decode = [&](int it, int& hq, int& q0, int& k0) {
+    if (MODE == MODE_DKV) {
+      const int g = it / walk_count;
+      hq = head_q0 + g;
+      q0 = (walk_first + it - g * walk_count) * kBtTile;
+      k0 = own0;
+    } else {
+      hq = head_q0;
+      q0 = own0;
+      k0 = it * kBtTile;
+    }
+  };
+
+  constexpr uint32_t kTmemCols = 512;           // S [0,128)  dP [128,256)  accumulators from 256
+  if (threadIdx.x == 0) {
+    mbar_init(bar_res, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_tfull + 8 * s, 1);
+      mbar_init(bar_tempty + 8 * s, 1);
+    }
+    mbar_init(bar_sdp_full, 1);
+    mbar_init(bar_sdp_empty, 8);
+    mbar_init(bar_p_full, 8);
+    mbar_init(bar_p_empty, 1);
+    mbar_init(bar_acc_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmdO);
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 128, tmem_acc0 = tmem_base + 256, tmem_acc1 = tmem_base + 256 + D;
+
+  const uint32_t sRes0 = sbase + L::kRes0, sRes1 = sbase + L::kRes1, sStream = sbase + L::kStream;
+  const uint32_t sDs = sbase + L::kDs, sP = sbase + L::kP;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
+      mbar_arrive_expect_tx(bar_res, 2 * L::kTileBytes);
+#pragma unroll
+      for (int hf = 0; hf < D / 64; ++hf) {
+        if (MODE == MODE_DKV) {
+          tma_load_4d(sRes0 + hf * L::kHalf, &tmK, hf * 64, head_k, own0, b, bar_res);
+          tma_load_4d(sRes1 + hf * L::kHalf, &tmV, hf * 64, head_k, own0, b, bar_res);
+        } else {
+          tma_load_4d(sRes0 + hf * L::kHalf, &tmQ, hf * 64, head_q0, own0, b, bar_res);
+          tma_load_4d(sRes1 + hf * L::kHalf, &tmdO, hf * 64, head_q0, own0, b, bar_res);
+        }
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(bar_tempty + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, status, 41)) break;
+        int hq, q0, k0;
+        walk_decode(it, hq, q0, k0);
+        mbar_arrive_expect_tx(bar_tfull + 8 * s, 2 * L::kTileBytes);
+        const uint32_t d0 = sStream + s * 2 * L::kTileBytes, d1 = d0 + L::kTileBytes;
+#pragma unroll
+        for (int hf = 0; hf < D / 64; ++hf) {
+          if (MODE == MODE_DKV) {
+            tma_load_4d(d0 + hf * L::kHalf, &tmQ, hf * 64, hq, q0, b, bar_tfull + 8 * s);
+            tma_load_4d(d1 + hf * L::kHalf, &tmdO, hf * 64, hq, q0, b, bar_tfull + 8 * s);
+          } else {
+            tma_load_4d(d0 + hf * L::kHalf, &tmK, hf * 64, head_k, k0, b, bar_tfull + 8 * s);
+            tma_load_4d(d1 + hf * L::kHalf, &tmV, hf * 64, head_k, k0, b, bar_tfull + 8 * s);
+          }
+        }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_t = umma_idesc_bf16(128, D, 1, 1);      // dV, dK: A (P / dS) and B (dO / Q) both MN-major
+      constexpr uint32_t idesc_q = umma_idesc_bf16(128, D, 0, 1);      // dQ: A = dS K-major, B = K MN-major
+      auto issue_sdp = [&](int it) -> bool {
+        const int s = it % STAGES;
+        if (!mbar_wait(bar_tfull + 8 * s, (it / STAGES) & 1, abort_flag, status, 42)) return false;
+        if (!mbar_wait(bar_sdp_empty, (it & 1) ^ 1, abort_flag, status, 43)) return false;
+        tc_fence_after();
+        const uint32_t t0 = sStream + s * 2 * L::kTileBytes, t1 = t0 + L::kTileBytes;
+        const uint32_t aQ = MODE == MODE_DKV ? t0 : sRes0, adO = MODE == MODE_DKV ? t1 : sRes1;
+        const uint32_t bK = MODE == MODE_DKV ? sRes0 : t0, bV = MODE == MODE_DKV ? sRes1 : t1;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * L::kHalf + (ks & 3) * 32;
+          umma_bf16_ss(tmem_s, umma_smem_desc_sw128(aQ + off, 16, 1024), umma_smem_desc_sw128(bK + off, 16, 1024), idesc_s,
+                       ks != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * L::kHalf + (ks & 3) * 32;
+          umma_bf16_ss(tmem_dp, umma_smem_desc_sw128(adO + off, 16, 1024), umma_smem_desc_sw128(bV + off, 16, 1024), idesc_s,
+                       ks != 0 ? 1u : 0u);
+        }
+        umma_commit(bar_sdp_full);
+        return true;
+      };
+      bool ok = mbar_wait(bar_res, 0, abort_flag, status, 44);
+      if (ok && n_it > 0) ok = issue_sdp(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it % STAGES;
+        // With two stages the next S / dP pair goes to the tensor cores ahead of this step's accumulations; with one
+        // stage its operands can only be loaded after those accumulations have released the buffer.
+        if (STAGES == 2 && it + 1 < n_it) {
+          ok = issue_sdp(it + 1);
+          if (!ok) break;
+        }
+        if (!mbar_wait(bar_p_full, it & 1, abort_flag, status, 45)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t t0 = sStream + s * 2 * L::kTileBytes, t1 = t0 + L::kTileBytes;
+        if (MODE == MODE_DKV) {
+#pragma unroll
+          for (int ks = 0; ks < kBtTile / 16; ++ks) {      // dK += dS^T Q   (k = query rows)
+            umma_bf16_ss(tmem_acc0, umma_smem_desc_sw128(sDs + ks * 2048, L::kHalf, 1024),
+                         umma_smem_desc_sw128(t0 + ks * 2048, L::kHalf, 1024), idesc_t, (it != 0 || ks != 0) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int ks = 0; ks < kBtTile / 16; ++ks) {      // dV += P^T dO
+            umma_bf16_ss(tmem_acc1, umma_smem_desc_sw128(sP + ks * 2048, L::kHalf, 1024),
+                         umma_smem_desc_sw128(t1 + ks * 2048, L::kHalf, 1024), idesc_t, (it != 0 || ks != 0) ? 1u : 0u);
+          }
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < kBtTile / 16; ++ks) {      // dQ += dS K     (k = keys)
+            umma_bf16_ss(tmem_acc0, umma_smem_desc_sw128(sDs + (ks >> 2) * L::kHalf + (ks & 3) * 32, 16, 1024),
+                         umma_smem_desc_sw128(t0 + ks * 2048, L::kHalf, 1024), idesc_q, (it != 0 || ks != 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(bar_p_empty);
+        umma_commit(bar_tempty + 8 * s);
+        if (STAGES == 1 && it + 1 < n_it) ok = issue_sdp(it + 1);
+      }
+      if (ok && n_it > 0) umma_commit(bar_acc_full);
+    }
+  } else {
+    // ------------------------------------------------------------------ P / dS and the final read-out
+    const int qtr = warp & 3, cg = warp >> 2;              // TMEM lane quarter, column half
+    const int row = qtr * 32 + lane;                       // query row inside the tile == TMEM lane
+    const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
+    const float sl2 = p.scale * kBtLog2e;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      int hq, q0, k0;
+      walk_decode(it, hq, q0, k0);
+      const int q_idx = q0 + row;
+      const bool q_ok = q_idx < p.seq_q;
+      const long long stat = (static_cast<long long>(b) * p.heads + hq) * p.seq_q + q_idx;
+      const float lse2 = q_ok ? __ldg(p.lse + stat) * kBtLog2e : 0.f;
+      const float dlt = q_ok ? __ldg(p.delta + stat) : 0.f;
+      const int key_lim = q_ok ? (p.causal ? min(p.seq_k - 1, q_idx + shift) : p.seq_k - 1) : -1;   // last visible key
+      const int kbase = k0 + cg * 64;
+      const bool need_mask = (kbase + 63 > key_lim);
+      if (!mbar_wait(bar_sdp_full, it & 1, abort_flag, status, 46)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t pp[32], ds[32];                             // 64 columns each, packed bf16 pairs
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32(tmem_s + lane_off + cg * 64 + c * 32, rs);
+        tmem_ld_32x32(tmem_dp + lane_off + cg * 64 + c * 32, rd);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = bt_ex2(fmaf(__uint_as_float(rs[2 * i]), sl2, -lse2));
+          float p1 = bt_ex2(fmaf(__uint_as_float(rs[2 * i + 1]), sl2, -lse2));
+          if (need_mask) {
+            const int key = kbase + c * 32 + 2 * i;
+            if (key > key_lim) p0 = 0.f;
+            if (key + 1 > key_lim) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(rd[2 * i]) - dlt);
+          const float d1 = p1 * (__uint_as_float(rd[2 * i + 1]) - dlt);
+          pp[c * 16 + i] = pack_bf16x2(p0, p1);
+          ds[c * 16 + i] = pack_bf16x2(d0, d1);
+        }
+      }
+      // S and dP are in registers: the next pair of products may overwrite them
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sdp_empty);
+      // the previous step's dV / dK / dQ products have finished reading P and dS
+      if (!mbar_wait(bar_p_empty, (it & 1) ^ 1, abort_flag, status, 47)) { ok = false; break; }
+      // this warp group's 64 keys are one 128-byte-swizzled atom: row `row`, eight 16-byte chunks
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const uint32_t off = cg * L::kHalf + row * 128 + ((ch ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sDs + off), "r"(ds[4 * ch]), "r"(ds[4 * ch + 1]),
+                     "r"(ds[4 * ch + 2]), "r"(ds[4 * ch + 3])
+                     : "memory");
+        if (MODE == MODE_DKV) {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + off), "r"(pp[4 * ch]), "r"(pp[4 * ch + 1]),
+                       "r"(pp[4 * ch + 2]), "r"(pp[4 * ch + 3])
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p_full);
+    }
+
+    // ---- read-out: TMEM lane = key (MODE_DKV) or query (MODE_DQ) row of the owned tile; this warp group's half of D
+    if (ok) {
+      bool have = n_it > 0;
+      if (have && !mbar_wait(bar_acc_full, 0, abort_flag, status, 48)) have = false, ok = false;
+      if (ok) {
+        tc_fence_after();
+        const int r_idx = own0 + row;
+        const int limit = MODE == MODE_DKV ? p.seq_k : p.seq_q;
+        const int head_out = MODE == MODE_DKV ? head_k : head_q0;
+        constexpr int CW = D / 2;                            // columns per warp group
+#pragma unroll
+        for (int which = 0; which < (MODE == MODE_DKV ? 2 : 1); ++which) {
+          const uint32_t tacc = which == 0 ? tmem_acc0 : tmem_acc1;
+          const float mul = which == 0 ? p.scale : 1.f;      // dK and dQ carry the softmax scale, dV does not
+          __nv_bfloat16* base = which == 0 ? p.out0 : p.out1;
+          const long long bs = which == 0 ? p.o0_bs : p.o1_bs, rs_ = which == 0 ? p.o0_rs : p.o1_rs,
+                          hs = which == 0 ? p.o0_hs : p.o1_hs;
+#pragma unroll
+          for (int c = 0; c < CW / 32; ++c) {
+            uint32_t r[32];
+            if (have) {
+              tmem_ld_32x32(tacc + lane_off + cg * CW + c * 32, r);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = 0u;
+            }
+            if (r_idx < limit) {
+              __nv_bfloat16* op = base + b * bs + head_out * hs + static_cast<long long>(r_idx) * rs_ + cg * CW + c * 32;
+#pragma unroll
+              for (int v4 = 0; v4 < 4; ++v4) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r[v4 * 8 + 0]) * mul, __uint_as_float(r[v4 * 8 + 1]) * mul);
+                o.y = pack_bf16x2(__uint_as_float(r[v4 * 8 + 2]) * mul, __uint_as_float(r[v4 * 8 + 3]) * mul);
+                o.z = pack_bf16x2(__uint_as_float(r[v4 * 8 + 4]) * mul, __uint_as_float(r[v4 * 8 + 5]) * mul);
+                o.w = pack_bf16x2(__uint_as_float(r[v4 * 8 + 6]) * mul, __uint_as_float(r[v4 * 8 + 7]) * mul);
+                reinterpret_cast<uint4*>(op)[v4] = o;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    if (*abort_flag) {
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace rb
+
+namespace {
+const CUtensorMap* bt_map(const void* base, const long long* strides, int seq, int heads, int batch, int D, int* err) {
+  long long s[3] = {strides[0] > 0 ? strides[0] : 8, strides[1] > 0 ? strides[1] : D, strides[2] > 0 ? strides[2] : D};
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)heads, (uint64_t)seq, (uint64_t)batch};
+  const uint64_t str[3] = {(uint64_t)s[2] * 2, (uint64_t)s[1] * 2, (uint64_t)s[0] * 2};
+  const uint32_t box[4] = {64, 1, (uint32_t)rb::kBtTile, 1};
+  return rbhost::get_tmap_4d(base, 2, dims, str, box, 1, err);
+}
+
+template <int D, int MODE>
+int bt_launch(const CUtensorMap* tq, const CUtensorMap* tk, const CUtensorMap* tv, const CUtensorMap* tdo,
+              const rb::BtParams& p, dim3 grid, cudaStream_t stream) {
+  auto kern = rb::attn_bwd_tc_kernel<D, MODE>;
+  const int smem = rb::BtSmem<D, MODE>::kTotal + 1024;
+  static bool cfg = false;
+  if (!cfg) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cfg = true;
+  }
+  kern<<<grid, rb::kBtThreads, smem, stream>>>(*tq, *tk, *tv, *tdo, p, rbhost::status_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+}  // namespace
+
+// Backward pass on the tcgen05 path (three launches: delta, dK/dV, dQ).  Returns -9 when the problem is outside what
+// these kernels take (the caller then uses rb_attention_bwd).
+RB_API int rb_attention_bwd_tc(const RbAttnArgs* a, void* stream_v) {
+  if (a->batch <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->heads % a->kv_heads) return -1;
+  if (a->head_dim != 64 && a->head_dim != 128) return -9;
+  if (a->seq_q <= 0 || a->seq_k <= 0 || (a->causal && a->seq_q > a->seq_k)) return -1;
+  if (!a->lse || !a->delta) return -2;
+  const void* ptrs[8] = {a->q, a->k, a->v, a->o, a->d_o, a->dq, a->dk, a->dv};
+  for (int i = 0; i < 8; ++i)
+    if (!ptrs[i] || (reinterpret_cast<uintptr_t>(ptrs[i]) & 15)) return -9;
+  const long long* strs[7] = {a->q_strides, a->k_strides, a->v_strides, a->o_strides, a->dq_strides, a->dk_strides, a->dv_strides};
+  for (int i = 0; i < 7; ++i)
+    for (int j = 0; j < 3; ++j)
+      if (strs[i][j] % 8) return -9;
+  const int D = a->head_dim;
+  int err = 0;
+  const CUtensorMap* tq = bt_map(a->q, a->q_strides, a->seq_q, a->heads, a->batch, D, &err);
+  const CUtensorMap* tk = bt_map(a->k, a->k_strides, a->seq_k, a->kv_heads, a->batch, D, &err);
+  const CUtensorMap* tv = bt_map(a->v, a->v_strides, a->seq_k, a->kv_heads, a->batch, D, &err);
+  const CUtensorMap* tdo = bt_map(a->d_o, a->o_strides, a->seq_q, a->heads, a->batch, D, &err);
+  if (!tq || !tk || !tv || !tdo) return err ? err : -5;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+
+  const long long rows = static_cast<long long>(a->heads) * a->seq_q;
+  dim3 dgrid(static_cast<unsigned>((rows + 3) / 4), a->batch);
+  const __nv_bfloat16* o = reinterpret_cast<const __nv_bfloat16*>(a->o);
+  const __nv_bfloat16* d_o = reinterpret_cast<const __nv_bfloat16*>(a->d_o);
+  if (D == 64)
+    rb::attn_delta_tc_kernel<64><<<dgrid, 128, 0, stream>>>(o, d_o, a->delta, a->o_strides[0], a->o_strides[1],
+                                                             a->o_strides[2], a->heads, a->seq_q);
+  else
+    rb::attn_delta_tc_kernel<128><<<dgrid, 128, 0, stream>>>(o, d_o, a->delta, a->o_strides[0], a->o_strides[1],
+                                                              a->o_strides[2], a->heads, a->seq_q);
+
+  rb::BtParams p;
+  p.lse = a->lse; p.delta = a->delta;
+  p.seq_q = a->seq_q; p.seq_k = a->seq_k; p.heads = a->heads; p.kv_heads = a->kv_heads; p.causal = a->causal;
+  p.scale = a->scale;
+  // dK / dV
+  p.out0 = reinterpret_cast<__nv_bfloat16*>(a->dk); p.out1 = reinterpret_cast<__nv_bfloat16*>(a->dv);
+  p.o0_bs = a->dk_strides[0]; p.o0_rs = a->dk_strides[1]; p.o0_hs = a->dk_strides[2];
+  p.o1_bs = a->dv_strides[0]; p.o1_rs = a->dv_strides[1]; p.o1_hs = a->dv_strides[2];
+  dim3 kvgrid((a->seq_k + rb::kBtTile - 1) / rb::kBtTile, a->kv_heads, a->batch);
+  int rc = D == 64 ? bt_launch<64, rb::MODE_DKV>(tq, tk, tv, tdo, p, kvgrid, stream)
+                   : bt_launch<128, rb::MODE_DKV>(tq, tk, tv, tdo, p, kvgrid, stream);
+  if (rc != 0) return rc;
+  // dQ
+  p.out0 = reinterpret_cast<__nv_bfloat16*>(a->dq); p.out1 = nullptr;
+  p.o0_bs = a->dq_strides[0]; p.o0_rs = a->dq_strides[1]; p.o0_hs = a->dq_strides[2];
+  dim3 qgrid((a->seq_q + rb::kBtTile - 1) / rb::kBtTile, a->heads, a->batch);
+  return D == 64 ? bt_launch<64, rb::MODE_DQ>(tq, tk, tv, tdo, p, qgrid, stream)
+                 : bt_launch<128, rb::MODE_DQ>(tq, tk, tv, tdo, p, qgrid, stream);
+}

@@ -43,9 +43,12 @@ def _fill(args, q, k, v, o, causal, scale):
 
 
 N.optional_sig("rb_attention_fwd_tc", [N.C.POINTER(N.RbAttnArgs), N.c_void_p])
+N.optional_sig("rb_attention_bwd_tc", [N.C.POINTER(N.RbAttnArgs), N.c_void_p])
+N._LAUNCHES["rb_attention_bwd_tc"] = 3
 
 # "tc": tcgen05 / TMEM kernel (falls back to "mma" for shapes it does not take); "mma": the mma.sync kernel.
 FORWARD_IMPL = __import__("os").environ.get("RUSTRAL_ATTN_IMPL", "tc")
+BACKWARD_IMPL = __import__("os").environ.get("RUSTRAL_ATTN_BWD_IMPL", FORWARD_IMPL)
 
 
 def attention_forward(q, k, v, causal: bool, scale: float, out=None, want_lse: bool = True, impl: str | None = None):
@@ -69,7 +72,7 @@ def attention_forward(q, k, v, causal: bool, scale: float, out=None, want_lse: b
     return o, lse
 
 
-def attention_backward(do, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None):
+def attention_backward(do, q, k, v, o, lse, causal: bool, scale: float, dq=None, dk=None, dv=None, impl: str | None = None):
     B, Sq, H, D = q.shape
     if do.stride(3) != 1 or _strides3(do) != _strides3(o):
         do = _match(do, o)
@@ -86,7 +89,13 @@ def attention_backward(do, q, k, v, o, lse, causal: bool, scale: float, dq=None,
         arr = getattr(a, name)
         arr[0], arr[1], arr[2] = st
     a.lse, a.delta = lse.data_ptr(), delta.data_ptr()
-    N.check(N.kernels().rb_attention_bwd(a, N.stream_ptr()), "rb_attention_bwd")
+    lib = N.kernels()
+    if (impl or BACKWARD_IMPL) == "tc" and hasattr(lib, "rb_attention_bwd_tc"):
+        rc = lib.rb_attention_bwd_tc(a, N.stream_ptr())
+        if rc != -9:
+            N.check(rc, "rb_attention_bwd_tc")
+            return dq, dk, dv
+    N.check(lib.rb_attention_bwd(a, N.stream_ptr()), "rb_attention_bwd")
     return dq, dk, dv
 
 

@@ -303,3 +303,29 @@ def test_flash_attention_forward_tcgen05(B, Sq, Sk, H, Hk, D, causal, cuda_statu
         qs, ks, vs = (qkv[:, :, i * H * D:(i + 1) * H * D].view(B, Sq, H, D) for i in range(3))
         o2, _ = attn_ops.attention_forward(qs, ks, vs, causal, scale, impl="tc")
         assert torch.equal(o2, o_tc)
+
+
+@pytest.mark.parametrize("B,Sq,Sk,H,Hk,D,causal", [
+    (2, 256, 256, 4, 4, 64, True), (1, 384, 384, 2, 2, 128, True), (2, 200, 200, 4, 2, 64, True),
+    (1, 128, 320, 4, 1, 64, True), (2, 160, 288, 2, 2, 128, False), (1, 512, 512, 3, 3, 64, False),
+])
+def test_flash_attention_backward_tcgen05(B, Sq, Sk, H, Hk, D, causal, cuda_status):
+    q, k, v = _bf((B, Sq, H, D), 1), _bf((B, Sk, Hk, D), 2), _bf((B, Sk, Hk, D), 3)
+    do = _bf((B, Sq, H, D), 4)
+    qc, kc, vc = (t.float().requires_grad_() for t in (q, k, v))
+    (attn_ops.attention_reference(qc, kc, vc, causal) * do.float()).sum().backward()
+    scale = 1 / math.sqrt(D)
+    qg, kg, vg, dog = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    o, lse = attn_ops.attention_forward(qg, kg, vg, causal, scale, impl="tc")
+    dq, dk, dv = attn_ops.attention_backward(dog, qg, kg, vg, o, lse, causal, scale, impl="tc")
+    _close(dq, qc.grad, tol=3e-2, what="tc dq")
+    _close(dk, kc.grad, tol=3e-2, what="tc dk")
+    _close(dv, vc.grad, tol=3e-2, what="tc dv")
+    # bit-reproducible: no atomics anywhere in the backward pass
+    dq2, dk2, dv2 = attn_ops.attention_backward(dog, qg, kg, vg, o, lse, causal, scale, impl="tc")
+    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    # the mma.sync path gives the same gradients within rounding
+    dq3, dk3, dv3 = attn_ops.attention_backward(dog, qg, kg, vg, o, lse, causal, scale, impl="mma")
+    _close(dq, dq3, tol=3e-2, what="tc vs mma dq")
+    _close(dk, dk3, tol=3e-2, what="tc vs mma dk")
+    _close(dv, dv3, tol=3e-2, what="tc vs mma dv")
