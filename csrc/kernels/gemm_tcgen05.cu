@@ -71,6 +71,9 @@ struct GroupInfo {
 //           the epilogue warps of all CTAs at kernel start, 16 rows at a time, each piece adding one to the tile's
 //           counter; the TMA producer waits (bounded) until a remote tile's counter reaches epoch * 8 before loading
 //           it.  Local tiles are scheduled first, so the transfer overlaps their math.
+//   mode 3 (weight all-gather -> GEMM, the FSDP / ZeRO-3 case): the B operand [N, K] is sharded by rows over the
+//           ranks; same pull-and-flag mechanism as mode 1 on 128-row blocks of B, with the tiles visited N-major
+//           starting at this rank's own block of output columns.
 //   mode 2 (GEMM -> reduce-scatter): the output rows are owned by ranks (rows_per_rank each).  The epilogue stores
 //           every tile straight into the OWNER's receive slot for this rank (d_peer[owner] + rank slot), as whole
 //           row segments through the staged store; tiles of the next rank come first and this rank's own last, so
@@ -356,6 +359,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (peer.mode == 1) {          // consumption order starts at this rank's own rows
       m_blk += peer.rank * (peer.rows_per_rank / kBlockM);
       if (m_blk >= num_m) m_blk -= num_m;
+    } else if (peer.mode == 3) {   // N-major walk starting at this rank's own columns
+      const int n_i = tile / num_m;
+      m_blk = tile - n_i * num_m;
+      n_blk = n_i + peer.rank * (peer.rows_per_rank / BLOCK_N);
+      if (n_blk >= num_n) n_blk -= num_n;
     } else if (peer.mode == 2) {   // rows of the next rank first, this rank's own rows last
       m_blk += ((peer.rank + 1) % peer.world) * (peer.rows_per_rank / kBlockM);
       if (m_blk >= num_m) m_blk -= num_m;
@@ -376,21 +384,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int e = __ldg(grp.tile_expert + m_blk);
           b_row_off = (e < 0 ? 0 : e) * grp.b_expert_rows;
         }
-        if (peer.mode == 1 && (m_blk * kBlockM) / peer.rows_per_rank != peer.rank) {
-          // a remote tile: wait until the copy warps of whichever CTA owns it have landed it in a_full
-          const unsigned long long t0 = globaltimer_ns();
+        if (peer.mode == 1 || peer.mode == 3) {
+          // remote 128-row blocks this tile reads: wait until the copy warps have landed all their pieces
+          const int blk0 = peer.mode == 1 ? m_blk : n_blk * (BLOCK_N / 128);
+          const int nblk = peer.mode == 1 ? 1 : BLOCK_N / 128;
           const unsigned int target = peer.epoch * kCopyParts;
-          while (static_cast<int>(ld_acquire_gpu(peer.ready + m_blk) - target) < 0) {
-            if (*abort_flag || globaltimer_ns() - t0 > kFlagWaitLimitNs) {
-              *abort_flag = 1;
-              status_set(status, kStatusFlagTimeout, 5);
-              ok = false;
-              break;
+          for (int bi = blk0; bi < blk0 + nblk && ok; ++bi) {
+            if ((bi * 128) / peer.rows_per_rank == peer.rank) continue;
+            const unsigned long long t0 = globaltimer_ns();
+            while (static_cast<int>(ld_acquire_gpu(peer.ready + bi) - target) < 0) {
+              if (*abort_flag || globaltimer_ns() - t0 > kFlagWaitLimitNs) {
+                *abort_flag = 1;
+                status_set(status, kStatusFlagTimeout, 5);
+                ok = false;
+                break;
+              }
+              __nanosleep(100);
             }
-            __nanosleep(100);
           }
           if (!ok) break;
-          fence_proxy_async_all();     // the tile was written with ordinary stores; TMA reads it through the async proxy
+          fence_proxy_async_all();     // the rows were written with ordinary stores; TMA reads them through the async proxy
         }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
@@ -455,16 +468,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;   // TMEM lane quarter this warp may read
     const int ew = warp - 2;  // 0..7
     const int cgrp = ew >> 2; // which half of the tile's columns this warp handles
-    if (peer.mode == 1) {
+    if (peer.mode == 1 || peer.mode == 3) {
       // ---- all-gather duty: land the remote rows of A in a_full, 16 rows at a time, in the order the tiles are consumed
       const int tpr = peer.rows_per_rank / kBlockM;
-      const int remote_items = (num_m - tpr) * kCopyParts;
+      const int num_blk = peer.mode == 1 ? num_m : N / kBlockM;      // 128-row blocks of the gathered operand
+      const int remote_items = (num_blk - tpr) * kCopyParts;
       const int et = threadIdx.x - 64;                    // index among the epilogue threads
       const int total = (kBlockM / kCopyParts) * (K / 8); // 16-byte chunks per piece
       for (int item = blockIdx.x; item < remote_items; item += gridDim.x) {
         const int c = item / kCopyParts, part = item - c * kCopyParts;
         int mt = c + tpr + peer.rank * tpr;               // consumption order -> global tile index
-        while (mt >= num_m) mt -= num_m;
+        while (mt >= num_blk) mt -= num_blk;
         const int owner = (mt * kBlockM) / peer.rows_per_rank;
         const long long row0 = static_cast<long long>(mt) * kBlockM + part * (kBlockM / kCopyParts);
         const uint4* src = reinterpret_cast<const uint4*>(peer.a_peer[owner] +
@@ -704,7 +718,7 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
   rb::PeerInfo peer;
   memset(&peer, 0, sizeof(peer));
   peer.mode = g.peer_mode; peer.world = g.peer_world; peer.rank = g.peer_rank; peer.rows_per_rank = g.rows_per_rank;
-  peer.a_full = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(g.a));
+  peer.a_full = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(g.peer_mode == 3 ? g.b : g.a));
   peer.ready = reinterpret_cast<unsigned int*>(g.ready_flags);
   peer.epoch = g.peer_epoch;
   for (int r = 0; r < 8; ++r) {
@@ -790,11 +804,26 @@ RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
   if (g.group_mode == 1 && (!g.tile_expert || !g.num_m_tiles || g.b_expert_rows <= 0)) return -8;
   if (g.group_mode == 1 && g.b_mn_major && (g.K % 64)) return -8;     // expert K ranges must be whole k-blocks
   if (g.group_mode == 2 && (!g.expert_offsets || g.num_experts <= 0 || !g.a_mn_major || !g.b_mn_major)) return -8;
-  if (g.peer_mode < 0 || g.peer_mode > 2) return -11;
+  if (g.peer_mode < 0 || g.peer_mode > 3) return -11;
+  RbGemmArgs forced;
+  if (g.peer_mode == 3) {
+    // tiles must not straddle two ranks' blocks of B: the tile width divides the rows per rank
+    if (g.rows_per_rank <= 0 || (g.rows_per_rank % 128)) return -11;
+    const int want = (g.rows_per_rank % 256 == 0) ? 256 : 128;
+    if (g.block_n != 0 && g.block_n != 128 && g.block_n != want) return -11;
+    if (g.block_n == 0) {
+      forced = g;
+      forced.block_n = want;
+      return rb_gemm_bf16(&forced, stream_v);
+    }
+  }
   if (g.peer_mode != 0) {
     if (g.peer_world < 2 || g.peer_world > 8 || g.peer_rank < 0 || g.peer_rank >= g.peer_world) return -11;
-    if (g.rows_per_rank <= 0 || (g.rows_per_rank % 128) || g.rows_per_rank * g.peer_world != g.M) return -11;
-    if (g.a_mn_major || g.group_mode != 0 || g.out_f32) return -11;
+    if (g.rows_per_rank <= 0 || (g.rows_per_rank % 128) ||
+        g.rows_per_rank * g.peer_world != (g.peer_mode == 3 ? g.N : g.M))
+      return -11;
+    if (g.peer_mode == 3 && (g.b_mn_major || !g.ready_flags || g.ldb != g.K)) return -11;   // b_full is dense [N, K]
+    if ((g.peer_mode == 1 && g.a_mn_major) || g.group_mode != 0 || g.out_f32) return -11;
     for (int r = 0; r < g.peer_world; ++r)
       if (!g.peer_ptrs[r] || (reinterpret_cast<uintptr_t>(g.peer_ptrs[r]) & 15)) return -11;
     if (g.peer_mode == 1 && (!g.ready_flags || g.lda != g.K)) return -11;       // a_full is dense [M, K]

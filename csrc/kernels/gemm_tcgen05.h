@@ -46,12 +46,13 @@ typedef struct RbGemmArgs {
   int b_expert_rows;           // mode 1: rows of B per expert (N for K-major B, K for MN-major B)
   long long d_expert_stride;   // mode 2: elements between consecutive experts' outputs
   // fusion with tensor-parallel collectives over peer memory (NVLink); see PeerInfo in gemm_tcgen05.cu
-  int peer_mode;               // 0 off; 1 all-gather(A) -> GEMM; 2 GEMM -> reduce-scatter (stores into the owners' slots)
+  int peer_mode;               // 0 off; 1 all-gather(A rows) -> GEMM; 2 GEMM -> reduce-scatter (stores into the owners'
+                               // slots); 3 all-gather(B rows, a row-sharded weight) -> GEMM
   int peer_world, peer_rank;
-  int rows_per_rank;           // M / peer_world, a multiple of 128
-  unsigned int peer_epoch;     // mode 1: value the ready flags take for this call (strictly increasing)
-  void* ready_flags;           // mode 1: local u32 [M / 128]
-  const void* peer_ptrs[8];    // mode 1: every rank's A shard [rows_per_rank, K]; mode 2: every rank's receive buffer
+  int rows_per_rank;           // M / peer_world (mode 3: N / peer_world), a multiple of 128
+  unsigned int peer_epoch;     // mode 1 / 3: call counter of this workspace (the block counters reach 8 * epoch)
+  void* ready_flags;           // mode 1 / 3: local u32 counters, one per 128-row block of the gathered operand
+  const void* peer_ptrs[8];    // mode 1 / 3: every rank's shard [rows_per_rank, K] of A / B; mode 2: every rank's receive buffer
                                //         [peer_world][rows_per_rank, ldd] (this rank writes slot peer_rank)
 } RbGemmArgs;
 

@@ -52,6 +52,20 @@ class _RsWorkspace:
         self.channel = channel
 
 
+class WeightShard:
+    """A row shard [N / W, K] of a weight that lives in symmetric memory (so peers can pull it from inside a GEMM),
+    with this rank's landing buffer for the gathered [N, K] weight and its per-block counters."""
+
+    def __init__(self, ctx: "FusedTP", rows: int, k: int, channel: int):
+        self.rows, self.k = rows, k
+        self.buf = SymmetricBuffer(rows * k * 2, ctx.group, ctx.device)
+        self.tensor = self.buf.view(torch.bfloat16, rows * k).view(rows, k)
+        self.full = torch.empty((rows * ctx.world, k), dtype=torch.bfloat16, device=ctx.device)
+        self.flags = torch.zeros(rows * ctx.world // ROW_BLOCK, dtype=torch.int32, device=ctx.device)
+        self.epoch = 0
+        self.channel = channel
+
+
 class FusedTP:
     """Workspaces and flags of the fused tensor-parallel GEMMs for one tensor-parallel group.
 
@@ -104,9 +118,10 @@ class FusedTP:
         return y, ws.a_full
 
     # ------------------------------------------------------------------------------------------ GEMM -> reduce-scatter
-    def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, residual=None, out=None):
-        """Y_local[M / W, N] = sum over ranks of (X_r @ W_r^T)[own rows] (+ residual).  `x` is [M, K_local]."""
-        m = x.shape[0]
+    def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, residual=None, out=None):
+        """Y_local[M / W, N] = sum over ranks of (X_r @ W_r^T)[own rows] (+ residual).  `x` is [M, K_local]
+        (or [K_local, M] with `a_mn`)."""
+        m = x.shape[1] if a_mn else x.shape[0]
         n = w.shape[1] if b_mn else w.shape[0]
         if m % self.world or not self.supports(m // self.world):
             raise ValueError(f"gemm_rs: M / world ({m} / {self.world}) must be a multiple of {ROW_BLOCK}")
@@ -116,7 +131,7 @@ class FusedTP:
         par = ws.epoch & 1
         slots = ws.slots[par]
         local_view = slots.view(torch.bfloat16, m * n).view(m, n)
-        gemm(x, w, b_mn=b_mn, out=local_view,
+        gemm(x, w, a_mn=a_mn, b_mn=b_mn, out=local_view,
              peer={"mode": 2, "world": self.world, "rank": self.rank, "rows_per_rank": rows, "epoch": ws.epoch,
                    "ready_flags": None, "peer_ptrs": slots.peer_ptrs})
         # every rank's partial rows have landed in this rank's slots
@@ -128,8 +143,39 @@ class FusedTP:
                                                N.stream_ptr()), "rb_tp_reduce_slots")
         return out
 
+    # ------------------------------------------------------------------------------------------ weight all-gather -> GEMM
+    def shard_weight(self, w_shard: torch.Tensor) -> WeightShard:
+        """Moves this rank's row shard of a weight into symmetric memory (collective; same order on every rank)."""
+        rows, k = w_shard.shape
+        if not self.supports(rows):
+            raise ValueError(f"shard_weight: rows per rank ({rows}) must be a multiple of {ROW_BLOCK}")
+        key = ("w", len(self._ws))
+        channel = len(self._ws)
+        if (channel + 1) * self.world * 4 > self.pad.nbytes:
+            raise N.NativeError("FusedTP: out of signal channels")
+        ws = WeightShard(self, rows, k, channel)
+        ws.tensor.copy_(w_shard)
+        self._ws[key] = ws
+        return ws
+
+    def fsdp_gemm(self, x: torch.Tensor, ws: WeightShard, *, bias=None, act: str = "none", aux_out=None, out=None):
+        """Y[M, N] = act(X @ allgather_rows(W_shard)^T + b): the ZeRO-3 / FSDP parameter all-gather fused into the GEMM
+        that consumes it.  Returns (Y, W_full); W_full stays valid until the next call with the same shard."""
+        ws.epoch += 1
+        ws.full[self.rank * ws.rows:(self.rank + 1) * ws.rows].copy_(ws.tensor)
+        # every rank has finished writing its shard (optimizer step) before any rank pulls it
+        self.pad.signal_all(ws.channel, ws.epoch)
+        self.pad.wait_all(ws.channel, ws.epoch, self.limit_ms)
+        y = gemm(x, ws.full, bias=bias, act=act, aux_out=aux_out, out=out, out_dtype=torch.bfloat16,
+                 peer={"mode": 3, "world": self.world, "rank": self.rank, "rows_per_rank": ws.rows, "epoch": ws.epoch,
+                       "ready_flags": ws.flags.data_ptr(), "peer_ptrs": ws.buf.peer_ptrs})
+        return y, ws.full
+
     def close(self) -> None:
         for ws in self._ws.values():
+            if isinstance(ws, WeightShard):
+                ws.buf.close()
+                continue
             for buf in (ws.shard if isinstance(ws, _AgWorkspace) else ws.slots):
                 buf.close()
         self._ws = {}
@@ -176,3 +222,32 @@ class RowSeqParallelFn(torch.autograd.Function):
         dx, dy_full = ctx.tp.ag_gemm(dy_local, w, b_mn=True)                       # [M, k_local] = allgather(dy) @ W
         dw = gemm(dy_full, x, a_mn=True, b_mn=True, out_dtype=torch.bfloat16)      # [N, k_local] = dy^T x
         return dx, dw, (dy_local if ctx.has_res else None), None
+
+
+class FSDPLinearFn(torch.autograd.Function):
+    """y = act(x W^T + b) with W row-sharded over the data-parallel ranks (FSDP / ZeRO-3).
+
+    Forward: the parameter all-gather runs inside the GEMM (peer mode 3).  Backward: dx uses the gathered weight the
+    forward left in this rank's landing buffer; the weight gradient dW = dy^T x is reduce-scattered from inside its
+    GEMM (peer mode 2), so each rank ends with the summed gradient of its own shard.  Returns dW for `w_shard_param`
+    (a tensor of the shard's shape that only carries the gradient)."""
+
+    @staticmethod
+    def forward(ctx, x, w_shard_param, bias, act, tp: FusedTP, ws: WeightShard):
+        x2 = x.reshape(-1, x.shape[-1])
+        need_pre = act != "none"
+        pre = torch.empty((x2.shape[0], ws.rows * tp.world), dtype=torch.bfloat16, device=x.device) if need_pre else None
+        y, w_full = tp.fsdp_gemm(x2, ws, bias=bias, act=act, aux_out=pre)
+        ctx.save_for_backward(x2, pre)
+        ctx.w_full, ctx.act, ctx.tp, ctx.has_bias, ctx.x_shape = w_full, act, tp, bias is not None, x.shape
+        return y.reshape(*x.shape[:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, pre = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dz = unary_bwd(ctx.act, pre, dy2) if pre is not None else dy2
+        dx = gemm(dz, ctx.w_full, b_mn=True, out_dtype=torch.bfloat16)                # [M, K] = dz @ W
+        dw_shard = ctx.tp.gemm_rs(dz, x2, a_mn=True, b_mn=True)                       # rows of dz^T x, summed over ranks
+        db = dz.float().sum(0).to(dz.dtype) if ctx.has_bias else None
+        return dx.reshape(ctx.x_shape), dw_shard, db, None, None, None

@@ -59,6 +59,36 @@ def check(tp, rank, world, dev):
     out["gemm_rs_err"] = max(errs)
     out["gemm_rs_repeatable"] = same
 
+    # FSDP / ZeRO-3: row-sharded weight gathered inside the consuming GEMM, gradient reduce-scattered inside the wgrad GEMM
+    from rustral_b200.parallel.fused_tp import FSDPLinearFn
+    n_r, Kf, Mf = 256, 192, 384
+    w_full = torch.randn(n_r * world, Kf, generator=torch.Generator().manual_seed(9)).mul(0.05).bfloat16().to(dev)
+    wsh = tp.shard_weight(w_full[rank * n_r:(rank + 1) * n_r])
+    errs, same = [], True
+    for it in range(2):
+        xf = torch.randn(Mf, Kf, generator=g).bfloat16().to(dev)
+        y, wf = tp.fsdp_gemm(xf, wsh)
+        assert torch.equal(wf, w_full), "gathered weight differs"
+        errs.append(rel_err(y, xf.float() @ w_full.float().t()))
+        y2, _ = tp.fsdp_gemm(xf, wsh)
+        same = same and torch.equal(y, y2)
+    out["fsdp_gemm_err"] = max(errs)
+    out["fsdp_gemm_repeatable"] = same
+    xf = torch.randn(Mf, Kf, generator=g).bfloat16().to(dev).requires_grad_()
+    wparam = wsh.tensor.detach().clone().requires_grad_()
+    bias = torch.zeros(n_r * world, dtype=torch.bfloat16, device=dev, requires_grad=True)
+    yf = FSDPLinearFn.apply(xf, wparam, bias, "gelu", tp, wsh)
+    gyf = torch.randn(Mf, n_r * world, generator=g).bfloat16().to(dev)
+    yf.backward(gyf)
+    xr = xf.detach().float().requires_grad_()
+    wr = w_full.float().requires_grad_()
+    yr = torch.nn.functional.gelu(xr @ wr.t(), approximate="tanh")
+    yr.backward(gyf.float())
+    dw_sum = wr.grad.clone()
+    dist.all_reduce(dw_sum)
+    out["fsdp_layer_err"] = {"y": rel_err(yf, yr), "dx": rel_err(xf.grad, xr.grad),
+                             "dw_shard": rel_err(wparam.grad, dw_sum[rank * n_r:(rank + 1) * n_r])}
+
     # sequence-parallel MLP: column (gelu) -> row, fused vs collectives
     from rustral_b200.core import B200Backend
     from rustral_b200.parallel.process_group import ProcessGroup
@@ -120,8 +150,24 @@ def bench(tp, rank, world, dev, iters):
         def gemm_only2():
             gemm(x2, w2, out=part)
 
+        # FSDP: weight [Nn * world, K] row-sharded, tokens local
+        wsh = tp.shard_weight(w)
+        w_gathered = torch.empty(Nn * world, K, dtype=torch.bfloat16, device=dev)
+        xt = torch.randn(M, K, device=dev).bfloat16()
+
+        def fused_fsdp():
+            tp.fsdp_gemm(xt, wsh)
+
+        def nccl_fsdp():
+            dist.all_gather_into_tensor(w_gathered, w)
+            gemm(xt, w_gathered)
+
+        def gemm_only3():
+            gemm(xt, w_gathered)
+
         row = {"rows_per_rank": rows, "K": K, "N": Nn}
-        for name, fn in (("fused_ag_gemm", fused_ag), ("nccl_ag_then_gemm", nccl_ag), ("gemm_alone", gemm_only),
+        for name, fn in (("fused_fsdp_gemm", fused_fsdp), ("nccl_allgather_w_then_gemm", nccl_fsdp), ("gemm_alone_fsdp_shape", gemm_only3),
+                         ("fused_ag_gemm", fused_ag), ("nccl_ag_then_gemm", nccl_ag), ("gemm_alone", gemm_only),
                          ("fused_gemm_rs", fused_rs), ("gemm_then_nccl_rs", nccl_rs), ("gemm_alone_rs_shape", gemm_only2)):
             for _ in range(3):
                 fn()

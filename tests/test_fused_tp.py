@@ -30,6 +30,9 @@ def test_fused_tp_two_gpus():
     assert out["gemm_rs_err"] < 1e-2 and out["gemm_rs_repeatable"]
     for name, err in out["layer_err"].items():
         assert err < 3e-2, (name, out["layer_err"])
+    assert out["fsdp_gemm_err"] < 1e-2 and out["fsdp_gemm_repeatable"]
+    for name, err in out["fsdp_layer_err"].items():
+        assert err < 3e-2, (name, out["fsdp_layer_err"])
 
 
 def test_fused_tp_rejects_bad_shapes_on_cpu():
