@@ -68,8 +68,8 @@ struct GroupInfo {
 // Fusion with tensor-parallel collectives over peer memory (NVLink loads / stores issued by this kernel).
 //   mode 1 (all-gather -> GEMM): the A operand [M, K] is sharded by rows over `world` ranks.  This rank's rows are
 //           already in a_full; the other ranks' 128-row tiles are copied from their (peer-mapped) shards into a_full by
-//           the epilogue warps of all CTAs at kernel start, 16 rows at a time, each piece adding one to the tile's
-//           counter; the TMA producer waits (bounded) until a remote tile's counter reaches epoch * 8 before loading
+//           the epilogue warps of all CTAs whenever they have no accumulator to drain, 4 rows at a time, each piece adding one to the tile's
+//           counter; the TMA producer waits (bounded) until a remote tile's counter reaches epoch * 32 before loading
 //           it.  Local tiles are scheduled first, so the transfer overlaps their math.
 //   mode 3 (weight all-gather -> GEMM, the FSDP / ZeRO-3 case): the B operand [N, K] is sharded by rows over the
 //           ranks; same pull-and-flag mechanism as mode 1 on 128-row blocks of B, with the tiles visited N-major
@@ -99,7 +99,7 @@ __device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) 
 __device__ __forceinline__ void red_release_gpu_add(unsigned int* p, unsigned int v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-constexpr int kCopyParts = 8;     // a remote 128-row tile is pulled as 8 pieces of 16 rows, by up to 8 different CTAs
+constexpr int kCopyParts = 32;    // a remote 128-row block is pulled as 32 pieces of 4 rows, by different warps of different CTAs
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 template <int BLOCK_N, int STAGES>
@@ -468,39 +468,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;   // TMEM lane quarter this warp may read
     const int ew = warp - 2;  // 0..7
     const int cgrp = ew >> 2; // which half of the tile's columns this warp handles
-    if (peer.mode == 1 || peer.mode == 3) {
-      // ---- all-gather duty: land the remote rows of A in a_full, 16 rows at a time, in the order the tiles are consumed
-      const int tpr = peer.rows_per_rank / kBlockM;
-      const int num_blk = peer.mode == 1 ? num_m : N / kBlockM;      // 128-row blocks of the gathered operand
-      const int remote_items = (num_blk - tpr) * kCopyParts;
-      const int et = threadIdx.x - 64;                    // index among the epilogue threads
-      const int total = (kBlockM / kCopyParts) * (K / 8); // 16-byte chunks per piece
-      for (int item = blockIdx.x; item < remote_items; item += gridDim.x) {
-        const int c = item / kCopyParts, part = item - c * kCopyParts;
-        int mt = c + tpr + peer.rank * tpr;               // consumption order -> global tile index
-        while (mt >= num_blk) mt -= num_blk;
-        const int owner = (mt * kBlockM) / peer.rows_per_rank;
-        const long long row0 = static_cast<long long>(mt) * kBlockM + part * (kBlockM / kCopyParts);
-        const uint4* src = reinterpret_cast<const uint4*>(peer.a_peer[owner] +
-                                                          (row0 - static_cast<long long>(owner) * peer.rows_per_rank) * K);
-        uint4* dst = reinterpret_cast<uint4*>(peer.a_full + row0 * K);
-        int i = et;
-        for (; i + 7 * kNumEpiThreads < total; i += 8 * kNumEpiThreads) {       // eight peer loads in flight per thread
-          uint4 v[8];
+    // ---- all-gather duty (peer modes 1 and 3): every epilogue warp of every CTA owns a strided share of the 16-row
+    // pieces of the remote rows, in the order the tiles consume them.  A warp pulls pieces whenever its next
+    // accumulator is not ready yet, and finishes its share after its last tile; nothing a piece needs ever waits.
+    const bool gathers = peer.mode == 1 || peer.mode == 3;
+    const int tpr = gathers ? peer.rows_per_rank / kBlockM : 0;
+    const int num_blk = peer.mode == 1 ? num_m : N / kBlockM;          // 128-row blocks of the gathered operand
+    const int remote_items = gathers ? (num_blk - tpr) * kCopyParts : 0;
+    const int item_stride = gridDim.x * kNumEpilogueWarps;
+    int next_item = blockIdx.x * kNumEpilogueWarps + ew;
+    auto copy_one = [&]() {
+      const int c = next_item / kCopyParts, part = next_item - c * kCopyParts;
+      next_item += item_stride;
+      int mt = c + tpr + peer.rank * tpr;                 // consumption order -> global block index
+      while (mt >= num_blk) mt -= num_blk;
+      const int owner = (mt * kBlockM) / peer.rows_per_rank;
+      const long long row0 = static_cast<long long>(mt) * kBlockM + part * (kBlockM / kCopyParts);
+      const uint4* src = reinterpret_cast<const uint4*>(peer.a_peer[owner] +
+                                                        (row0 - static_cast<long long>(owner) * peer.rows_per_rank) * K);
+      uint4* dst = reinterpret_cast<uint4*>(peer.a_full + row0 * K);
+      const int total = (kBlockM / kCopyParts) * (K / 8);   // 16-byte chunks per piece
+      int i = lane;
+      for (; i + 7 * 32 < total; i += 8 * 32) {             // eight peer loads in flight per thread
+        uint4 v[8];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) v[u] = src[i + u * kNumEpiThreads];
+        for (int u = 0; u < 8; ++u) v[u] = src[i + u * 32];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) dst[i + u * kNumEpiThreads] = v[u];
-        }
-        for (; i < total; i += kNumEpiThreads) dst[i] = src[i];
-        __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(kNumEpiThreads) : "memory");
-        if (et == 0) {
-          fence_proxy_async_all();
-          red_release_gpu_add(peer.ready + mt, 1u);
-        }
+        for (int u = 0; u < 8; ++u) dst[i + u * 32] = v[u];
       }
-    }
+      for (; i < total; i += 32) dst[i] = src[i];
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) {
+        fence_proxy_async_all();
+        red_release_gpu_add(peer.ready + mt, 1u);
+      }
+      __syncwarp();
+    };
     uint32_t t = 0;
     for (int tile = blockIdx.x; tile < num_units; tile += gridDim.x, ++t) {
       int m_blk, n_blk, kb0, kb1, outer;
@@ -519,6 +523,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       const bool empty_k = kb1 <= kb0;     // an expert without tokens: the accumulator was never written
       const uint32_t acc = t & 1, acc_ph = (t >> 1) & 1;
+      while (next_item < remote_items && !mbar_test(bar_tfull + 8 * acc, acc_ph)) copy_one();
       if (!mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, status, 4)) break;
       tc_fence_after();
       const long long row = static_cast<long long>(m_blk) * kBlockM + q * 32 + lane;
@@ -610,6 +615,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (row < M && col0 < N) epilogue_chunk(epu, r, row, col0, N);
       }
     }
+    while (next_item < remote_items && !*abort_flag) copy_one();
   }
 
   __syncthreads();

@@ -50,7 +50,7 @@ typedef struct RbGemmArgs {
                                // slots); 3 all-gather(B rows, a row-sharded weight) -> GEMM
   int peer_world, peer_rank;
   int rows_per_rank;           // M / peer_world (mode 3: N / peer_world), a multiple of 128
-  unsigned int peer_epoch;     // mode 1 / 3: call counter of this workspace (the block counters reach 8 * epoch)
+  unsigned int peer_epoch;     // mode 1 / 3: call counter of this workspace (the block counters reach 32 * epoch)
   void* ready_flags;           // mode 1 / 3: local u32 counters, one per 128-row block of the gathered operand
   const void* peer_ptrs[8];    // mode 1 / 3: every rank's shard [rows_per_rank, K] of A / B; mode 2: every rank's receive buffer
                                //         [peer_world][rows_per_rank, ldd] (this rank writes slot peer_rank)

@@ -163,7 +163,7 @@ def _segments(pl: MoEPlan):
 
 
 def grouped_gemm(xp: torch.Tensor, W: torch.Tensor, pl: MoEPlan, *, b_mn: bool = False, act: str = "none", aux_out=None,
-                 aux_in=None) -> torch.Tensor:
+                 aux_in=None, out: torch.Tensor | None = None) -> torch.Tensor:
     """Per-expert matmul over the permuted buffer.  b_mn False: W [E, N, K], y = xp @ W[e]^T.  b_mn True: W [E, K, N]
     (the dgrad form: y = xp @ W[e])."""
     E = pl.num_experts
@@ -179,7 +179,7 @@ def grouped_gemm(xp: torch.Tensor, W: torch.Tensor, pl: MoEPlan, *, b_mn: bool =
                        aux_out=None if aux_out is None else aux_out[o:o + c])
             y[o:o + c] = seg
         return y
-    y = torch.empty((rows, Nn), dtype=xp.dtype, device=xp.device)
+    y = out if out is not None else torch.empty((rows, Nn), dtype=xp.dtype, device=xp.device)
     W2 = W.reshape(-1, W.shape[2])
     g = N.RbGemmArgs()
     g.a, g.b, g.d = xp.data_ptr(), W2.data_ptr(), y.data_ptr()

@@ -1,0 +1,27 @@
+"""Expert-parallel MoE layer (dispatch / combine over peer memory) on two GPUs against the single-device layer."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+WORKER = os.path.join(ROOT, "tests", "mp_ep_worker.py")
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_ep_two_gpus():
+    env = dict(os.environ)
+    env["NCCL_NVLS_ENABLE"] = "0"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29661", WORKER, "--mode", "check"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["status_max"] == 0
+    for kind, errs in out["err"].items():
+        for name, err in errs.items():
+            assert err < 4e-2, (kind, name, out["err"])
