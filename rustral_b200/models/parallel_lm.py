@@ -1,0 +1,309 @@
+"""Llama-style decoder language model for tensor-, pipeline- and expert-parallel training.
+
+One class covers the dense model (RMSNorm, rotary GQA attention, SwiGLU MLP) and the mixture-of-experts variant
+(top-k SwiGLU experts in place of the MLP).  It is written against the differentiable ops of `rustral_b200.ops`, so
+torch.autograd drives the backward pass while every matmul, attention, norm, rotary, SwiGLU, routing and loss kernel
+is one of the framework's own.
+
+Parallel layouts:
+
+* tensor parallel with sequence parallelism: between blocks a rank holds a contiguous block of the (batch * seq)
+  rows; QKV and gate/up are column-parallel (all-gather of the rows fused into the GEMM), the output and down
+  projections are row-parallel (reduce-scatter fused into the GEMM epilogue), see parallel/fused_tp.py.  The LM head
+  is column-parallel over the vocabulary with a vocabulary-parallel cross-entropy.  Without a `fused_tp` context the
+  same maths runs over ProcessGroup collectives (the baseline the fused kernels are measured against).
+* pipeline parallel: a stage owns a contiguous range of blocks (`first_layer`, `last_layer`), optionally the
+  embedding and the head; `embed` / `blocks` / `loss` are the pieces parallel/pipeline_parallel.py schedules.
+* expert parallel: the experts of every MoE block are spread over the ranks of `ep` (parallel/expert_parallel.py);
+  attention and the dense parameters are replicated and their gradients averaged over the group.
+
+The reference has no such model: its tensor-parallel layers are forward-only over host slices
+(crates/distributed/src/tensor_parallel.rs:119-173), its MoE routes with host loops (crates/nn/src/moe.rs:277-370).
+"""
+from __future__ import annotations
+
+import math
+import zlib
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import moe as moe_ops
+from ..ops import rotary
+
+
+@dataclass
+class ParallelLMConfig:
+    vocab_size: int = 32000
+    d_model: int = 512
+    n_layer: int = 4
+    n_head: int = 8
+    n_kv_head: int = 8
+    ffn_hidden: int = 1536
+    seq_len: int = 512
+    rope_theta: float = 500000.0
+    eps: float = 1e-5
+    num_experts: int = 0          # > 0: every block's MLP is a top-k mixture of SwiGLU experts
+    top_k: int = 2
+    aux_coef: float = 0.01
+    init_std: float = 0.02
+
+    @property
+    def head_dim(self) -> int:
+        return self.d_model // self.n_head
+
+    def params_per_layer(self) -> int:
+        d, hd = self.d_model, self.head_dim
+        attn = d * (self.n_head + 2 * self.n_kv_head) * hd + self.n_head * hd * d
+        mlp = 3 * d * self.ffn_hidden * max(1, self.num_experts) + (self.num_experts * d if self.num_experts else 0)
+        return attn + mlp + 2 * d
+
+    def num_params(self) -> int:
+        return self.n_layer * self.params_per_layer() + 2 * self.vocab_size * self.d_model + self.d_model
+
+    def flops_per_token(self) -> float:
+        """Training FLOPs per token (forward + backward = 3 x forward), active parameters only, causal attention."""
+        d, hd = self.d_model, self.head_dim
+        attn_proj = d * (self.n_head + 2 * self.n_kv_head) * hd + self.n_head * hd * d
+        mlp = 3 * d * self.ffn_hidden * (self.top_k if self.num_experts else 1)
+        dense = self.n_layer * (attn_proj + mlp) + self.vocab_size * d
+        attn = self.n_layer * 2 * self.seq_len * d * 0.5 * 2          # QK^T and PV, causal half
+        return 6.0 * dense + 3.0 * attn
+
+
+def llama_8b(**kw) -> ParallelLMConfig:
+    base = dict(vocab_size=128256, d_model=4096, n_layer=32, n_head=32, n_kv_head=8, ffn_hidden=14336, seq_len=4096,
+                rope_theta=500000.0)
+    base.update(kw)
+    return ParallelLMConfig(**base)
+
+
+def moe_24l(**kw) -> ParallelLMConfig:
+    base = dict(vocab_size=32000, d_model=2048, n_layer=24, n_head=16, n_kv_head=16, ffn_hidden=8192, seq_len=2048,
+                num_experts=8, top_k=2, aux_coef=0.01)
+    base.update(kw)
+    return ParallelLMConfig(**base)
+
+
+class _VocabParallelCE(torch.autograd.Function):
+    """Mean cross-entropy over rows with the vocabulary split over the tensor-parallel group."""
+
+    @staticmethod
+    def forward(ctx, local_logits, targets, pg, vocab_start):
+        from ..parallel.tensor_parallel import vocab_parallel_cross_entropy
+        loss, grad = vocab_parallel_cross_entropy(local_logits, targets, pg, vocab_start)
+        ctx.save_for_backward((grad / loss.numel()).to(local_logits.dtype))
+        return loss.mean()
+
+    @staticmethod
+    def backward(ctx, g):
+        (grad,) = ctx.saved_tensors
+        return grad * g.to(grad.dtype), None, None, None
+
+
+class ParallelDecoderLM:
+    """Parameters live in `self.params` (bf16 leaves); `self.replicated` names those every tensor-parallel rank holds
+    in full and sees different rows of (their gradients are summed over the group by `sync_grads`)."""
+
+    def __init__(self, cfg: ParallelLMConfig, device, *, tp_pg=None, fused_tp=None, ep=None, dp_group=None,
+                 first_layer: int = 0, last_layer: int | None = None, has_embed: bool = True, has_head: bool = True,
+                 seed: int = 0):
+        self.cfg, self.device = cfg, torch.device(device)
+        self.tp_pg, self.fused_tp, self.ep, self.dp_group = tp_pg, fused_tp, ep, dp_group
+        self.tp = tp_pg.world_size if tp_pg is not None else 1
+        self.tp_rank = tp_pg.rank if tp_pg is not None else 0
+        self.first_layer = first_layer
+        self.last_layer = cfg.n_layer if last_layer is None else last_layer
+        self.has_embed, self.has_head = has_embed, has_head
+        if cfg.n_head % self.tp or cfg.n_kv_head % self.tp or cfg.ffn_hidden % self.tp or cfg.vocab_size % self.tp:
+            raise ValueError("heads, KV heads, FFN width and vocabulary must be divisible by the tensor-parallel size")
+        self.params: dict = {}
+        self.replicated: set = set()
+        self.expert_names: set = set()
+        self._init(seed)
+
+    # ------------------------------------------------------------------------------------------------ parameters
+    def _rand(self, shape, seed, std=None):
+        g = torch.Generator(device=self.device).manual_seed(seed)
+        std = self.cfg.init_std if std is None else std
+        t = torch.empty(shape, dtype=torch.float32, device=self.device).normal_(0.0, std, generator=g)
+        return t.to(torch.bfloat16).requires_grad_()
+
+    def _init(self, seed: int) -> None:
+        c, tp, r = self.cfg, self.tp, self.tp_rank
+        d, hd = c.d_model, c.head_dim
+        hq, hk, f = c.n_head // tp, c.n_kv_head // tp, c.ffn_hidden // tp
+        P = self.params
+        # a shard's seed depends on (parameter, shard) only, so a gathered checkpoint is the same for every layout
+        sd = lambda name, shard=0: (zlib.crc32(f"{seed}/{name}".encode()) & 0x7FFFFFFF) * 64 + shard
+        if self.has_embed:
+            P["wte"] = self._rand((c.vocab_size, d), sd("wte"))
+            self.replicated.add("wte")
+        for l in range(self.first_layer, self.last_layer):
+            p = f"l{l}."
+            P[p + "attn_norm"] = torch.ones(d, dtype=torch.bfloat16, device=self.device, requires_grad=True)
+            P[p + "wqkv"] = self._rand(((hq + 2 * hk) * hd, d), sd(p + "wqkv", r))
+            P[p + "wo"] = self._rand((d, hq * hd), sd(p + "wo", r), c.init_std / math.sqrt(2 * c.n_layer))
+            P[p + "mlp_norm"] = torch.ones(d, dtype=torch.bfloat16, device=self.device, requires_grad=True)
+            self.replicated.update({p + "attn_norm", p + "mlp_norm"})
+            if c.num_experts:
+                el = c.num_experts // (self.ep.world if self.ep is not None else 1)
+                er = self.ep.rank if self.ep is not None else 0
+                P[p + "router"] = self._rand((c.num_experts, d), sd(p + "router"))
+                P[p + "w1"] = self._rand((el, 2 * c.ffn_hidden, d), sd(p + "w1", er))
+                P[p + "w2"] = self._rand((el, d, c.ffn_hidden), sd(p + "w2", er), c.init_std / math.sqrt(2 * c.n_layer))
+                self.replicated.add(p + "router")
+                self.expert_names.update({p + "w1", p + "w2"})
+            else:
+                P[p + "wgu"] = self._rand((2 * f, d), sd(p + "wgu", r))
+                P[p + "wdown"] = self._rand((d, f), sd(p + "wdown", r), c.init_std / math.sqrt(2 * c.n_layer))
+        if self.has_head:
+            P["final_norm"] = torch.ones(d, dtype=torch.bfloat16, device=self.device, requires_grad=True)
+            P["head"] = self._rand((c.vocab_size // tp, d), sd("head", r))
+            self.replicated.add("final_norm")
+
+    def parameters(self):
+        return list(self.params.values())
+
+    def local_param_count(self) -> int:
+        return sum(p.numel() for p in self.params.values())
+
+    # ------------------------------------------------------------------------------------------------ layers
+    def _col(self, x, w):
+        """Column-parallel projection of sequence-sharded rows: [R / tp, d] -> [R, n / tp]."""
+        if self.tp == 1:
+            return ops.linear(x, w)
+        if self.fused_tp is not None and self.fused_tp.supports(x.shape[0]):
+            from ..parallel.fused_tp import ColumnSeqParallelFn
+            return ColumnSeqParallelFn.apply(x, w, None, "none", self.fused_tp)
+        from ..parallel.tensor_parallel import _GatherSeq
+        return ops.linear(_GatherSeq.apply(x, self.tp_pg), w)
+
+    def _row(self, x, w, residual):
+        """Row-parallel projection back to sequence-sharded rows: [R, k / tp] -> [R / tp, d] (+ residual)."""
+        if self.tp == 1:
+            return ops.linear(x, w, None, "none", residual)
+        if self.fused_tp is not None and x.shape[0] % self.tp == 0 and self.fused_tp.supports(x.shape[0] // self.tp):
+            from ..parallel.fused_tp import RowSeqParallelFn
+            return RowSeqParallelFn.apply(x, w, residual, self.fused_tp)
+        from ..parallel.tensor_parallel import _ReduceScatterSeq
+        return _ReduceScatterSeq.apply(ops.linear(x, w), self.tp_pg) + residual
+
+    def _block(self, l: int, x, batch: int, seq: int):
+        c, P, p = self.cfg, self.params, f"l{l}."
+        hd = c.head_dim
+        hq, hk = c.n_head // self.tp, c.n_kv_head // self.tp
+        h = ops.rms_norm(x, P[p + "attn_norm"], c.eps)
+        qkv = self._col(h, P[p + "wqkv"])                                   # [B*S, (hq + 2 hk) * hd]
+        q = rotary.rope(qkv[:, :hq * hd].reshape(batch, seq, hq, hd), seq, theta=c.rope_theta)
+        k = rotary.rope(qkv[:, hq * hd:(hq + hk) * hd].reshape(batch, seq, hk, hd), seq, theta=c.rope_theta)
+        v = qkv[:, (hq + hk) * hd:].reshape(batch, seq, hk, hd)
+        o = ops.flash_attention(q, k, v, True)
+        x = self._row(o.reshape(batch * seq, hq * hd), P[p + "wo"], x)
+        h = ops.rms_norm(x, P[p + "mlp_norm"], c.eps)
+        aux = None
+        if c.num_experts:
+            if self.ep is not None:
+                from ..parallel.expert_parallel import ep_moe_mlp
+                y, aux = ep_moe_mlp(h, P[p + "router"], P[p + "w1"], P[p + "w2"], self.ep, c.top_k, "swiglu")
+            else:
+                y, aux = moe_ops.moe_mlp(h, P[p + "router"], P[p + "w1"], P[p + "w2"], c.top_k, "swiglu")
+            x = x + y
+        else:
+            gu = self._col(h, P[p + "wgu"])
+            x = self._row(rotary.swiglu(gu), P[p + "wdown"], x)
+        return x, aux
+
+    # ------------------------------------------------------------------------------------------------ forward
+    def local_rows(self, batch: int, seq: int) -> slice:
+        rows = batch * seq
+        if rows % self.tp:
+            raise ValueError("batch * seq must be divisible by the tensor-parallel size")
+        n = rows // self.tp
+        return slice(self.tp_rank * n, (self.tp_rank + 1) * n)
+
+    def embed(self, ids: torch.Tensor) -> torch.Tensor:
+        """ids [B, S] (the same on every tensor-parallel rank) -> this rank's rows [B*S / tp, d]."""
+        B, S = ids.shape
+        flat = ids.reshape(-1)[self.local_rows(B, S)].contiguous()
+        return ops.embedding(flat, self.params["wte"])
+
+    def blocks(self, x, batch: int, seq: int):
+        aux_total = None
+        for l in range(self.first_layer, self.last_layer):
+            x, aux = self._block(l, x, batch, seq)
+            if aux is not None:
+                aux_total = aux if aux_total is None else aux_total + aux
+        return x, aux_total
+
+    def loss(self, x, targets: torch.Tensor) -> torch.Tensor:
+        """x: this rank's rows after the last block; targets [B, S] (all rows)."""
+        c = self.cfg
+        h = ops.rms_norm(x, self.params["final_norm"], c.eps)
+        logits = self._col(h, self.params["head"])                          # [B*S, V / tp]
+        t = targets.reshape(-1)
+        if self.tp == 1:
+            return ops.cross_entropy(logits, t)
+        return _VocabParallelCE.apply(logits, t, self.tp_pg, self.tp_rank * (c.vocab_size // self.tp))
+
+    def forward_loss(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens [B, S + 1] -> scalar training loss (next-token cross-entropy + aux_coef * load-balancing loss)."""
+        ids, targets = tokens[:, :-1], tokens[:, 1:]
+        B, S = ids.shape
+        x, aux = self.blocks(self.embed(ids), B, S)
+        loss = self.loss(x, targets)
+        if aux is not None:
+            loss = loss + self.cfg.aux_coef * aux / (self.last_layer - self.first_layer)
+        return loss
+
+    # ------------------------------------------------------------------------------------------------ gradients
+    def sync_grads(self, main_grads: dict) -> None:
+        """Sum the gradients of replicated parameters over the tensor-parallel group; average dense gradients over
+        the data / expert-parallel group and rescale the expert gradients (which already hold every rank's tokens)."""
+        if self.tp > 1:
+            for name in sorted(self.replicated):
+                if name in main_grads:
+                    dist.all_reduce(main_grads[name], group=self.tp_pg.group)
+        if self.dp_group is not None or self.ep is not None:
+            group = self.dp_group if self.dp_group is not None else self.ep.group
+            world = dist.get_world_size(group)
+            for name in sorted(main_grads):
+                g = main_grads[name]
+                if name in self.expert_names and self.ep is not None:
+                    g.mul_(1.0 / world)
+                else:
+                    dist.all_reduce(g, group=group)
+                    g.mul_(1.0 / world)
+
+
+class MixedPrecisionAdamW:
+    """AdamW on fp32 master weights with bf16 working copies (one fused kernel per tensor), gradients accumulated
+    in fp32 across micro-batches."""
+
+    def __init__(self, model: ParallelDecoderLM, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
+                 weight_decay: float = 0.1):
+        self.model, self.lr, self.betas, self.eps, self.wd = model, lr, betas, eps, weight_decay
+        self.master = {n: p.detach().float() for n, p in model.params.items()}
+        self.m = {n: torch.zeros_like(v) for n, v in self.master.items()}
+        self.v = {n: torch.zeros_like(v) for n, v in self.master.items()}
+        self.main_grads = {n: torch.zeros_like(v) for n, v in self.master.items()}
+        self.step_count = 0
+
+    def accumulate(self) -> None:
+        """Fold the bf16 `.grad` of the micro-batch just finished into the fp32 accumulators."""
+        for n, p in self.model.params.items():
+            if p.grad is not None:
+                self.main_grads[n].add_(p.grad)
+                p.grad = None
+
+    def step(self, grad_scale: float = 1.0) -> None:
+        self.step_count += 1
+        self.model.sync_grads(self.main_grads)
+        for n, p in self.model.params.items():
+            decay = self.wd if p.dim() >= 2 else 0.0
+            ops.adam_step(self.master[n].view(-1), self.m[n].view(-1), self.v[n].view(-1), self.main_grads[n].view(-1),
+                                lr=self.lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps, weight_decay=decay,
+                                step=self.step_count, grad_scale=grad_scale, p_lowp=p.data.view(-1))
+            self.main_grads[n].zero_()

@@ -98,6 +98,7 @@ class PipelineParallel:
         self.stage, self.pg, self.cfg = stage, process_group, config
         self.act_shape, self.act_dtype, self.device = tuple(act_shape), act_dtype, torch.device(device)
         self._comm_stream = torch.cuda.Stream(self.device) if (self.device.type == "cuda" and config.async_comm) else None
+        self.after_backward = None      # optional callable run after every micro-batch backward (e.g. fp32 accumulation)
 
     # ---- p2p ------------------------------------------------------------------------------------------------------------
     def _recv(self, src: int, tag: int) -> torch.Tensor:
@@ -145,6 +146,8 @@ class PipelineParallel:
             out.backward(g)
         if not st.is_first:
             self._send(x.grad, st.stage_id - 1, 2 * i + 1)
+        if self.after_backward is not None:
+            self.after_backward()
 
     def train_step(self, inputs=None, targets=None, loss_fn=None) -> torch.Tensor | None:
         """Gradients accumulate in the stage's parameters (zero them beforehand).  Returns the mean loss on the last
