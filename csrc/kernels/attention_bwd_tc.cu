@@ -62,24 +62,37 @@ struct BtSmem {
 };
 
 template <int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 attn_delta_tc_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
                      long long bs, long long rs, long long hs, int heads, int seq_q) {
-  // one warp per (head, row): delta = sum_d dO * O
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long idx = static_cast<long long>(blockIdx.x) * 4 + warp;
+  // delta[b, h, r] = sum_d dO * O.  D / 8 adjacent lanes share a row (one 16-byte load of each tensor per lane).
+  constexpr int TPR = D / 8;                       // threads per row: 8 or 16
+  constexpr int RPB = 256 / TPR;                   // rows per block
   const int b = blockIdx.y;
-  if (idx >= static_cast<long long>(heads) * seq_q) return;
-  const int h = static_cast<int>(idx / seq_q), r = static_cast<int>(idx % seq_q);
-  const long long off = b * bs + h * hs + static_cast<long long>(r) * rs;
+  const long long idx = static_cast<long long>(blockIdx.x) * RPB + threadIdx.x / TPR;
+  const int part = threadIdx.x % TPR;
   float acc = 0.f;
-  for (int c = lane * 2; c < D; c += 64) {
-    const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(o + off + c));
-    const float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(d_o + off + c));
-    acc += a.x * g.x + a.y * g.y;
+  const bool live = idx < static_cast<long long>(heads) * seq_q;
+  int h = 0, r = 0;
+  if (live) {
+    // rows are walked (row, head)-major so that neighbouring threads read neighbouring memory in a [B, S, H, D] tensor
+    r = static_cast<int>(idx / heads);
+    h = static_cast<int>(idx % heads);
+    const long long off = b * bs + h * hs + static_cast<long long>(r) * rs + part * 8;
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + off));
+    const uint4 g = __ldg(reinterpret_cast<const uint4*>(d_o + off));
+    const uint32_t* ua = reinterpret_cast<const uint32_t*>(&a);
+    const uint32_t* ug = reinterpret_cast<const uint32_t*>(&g);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = unpack_bf16x2(ua[j]), y = unpack_bf16x2(ug[j]);
+      acc = fmaf(x.x, y.x, acc);
+      acc = fmaf(x.y, y.y, acc);
+    }
   }
-  acc = warp_sum(acc);
-  if (lane == 0) delta[(static_cast<long long>(b) * heads + h) * seq_q + r] = acc;
+#pragma unroll
+  for (int m = TPR / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+  if (live && part == 0) delta[(static_cast<long long>(b) * heads + h) * seq_q + r] = acc;
 }
 
 template <int D, int MODE>
@@ -448,14 +461,15 @@ RB_API int rb_attention_bwd_tc(const RbAttnArgs* a, void* stream_v) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
 
   const long long rows = static_cast<long long>(a->heads) * a->seq_q;
-  dim3 dgrid(static_cast<unsigned>((rows + 3) / 4), a->batch);
+  const int rows_per_block = 256 / (D / 8);
+  dim3 dgrid(static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block), a->batch);
   const __nv_bfloat16* o = reinterpret_cast<const __nv_bfloat16*>(a->o);
   const __nv_bfloat16* d_o = reinterpret_cast<const __nv_bfloat16*>(a->d_o);
   if (D == 64)
-    rb::attn_delta_tc_kernel<64><<<dgrid, 128, 0, stream>>>(o, d_o, a->delta, a->o_strides[0], a->o_strides[1],
+    rb::attn_delta_tc_kernel<64><<<dgrid, 256, 0, stream>>>(o, d_o, a->delta, a->o_strides[0], a->o_strides[1],
                                                              a->o_strides[2], a->heads, a->seq_q);
   else
-    rb::attn_delta_tc_kernel<128><<<dgrid, 128, 0, stream>>>(o, d_o, a->delta, a->o_strides[0], a->o_strides[1],
+    rb::attn_delta_tc_kernel<128><<<dgrid, 256, 0, stream>>>(o, d_o, a->delta, a->o_strides[0], a->o_strides[1],
                                                               a->o_strides[2], a->heads, a->seq_q);
 
   rb::BtParams p;

@@ -146,11 +146,13 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy, const __nv
   const float inv_n = 1.f / static_cast<float>(n);
   float* sg = sm + (slot * 2 + 0) * n_pad;
   float* sb = sm + (slot * 2 + 1) * n_pad;
+  // A thread sees the same columns in every row it processes, so the dgamma / dbeta sums stay in registers
+  // until the end of the walk.
+  float ag[CHUNKS][8], ab[CHUNKS][8];
 #pragma unroll
   for (int c = 0; c < CHUNKS; ++c) {
-    const int col = col_of<CHUNKS, WPR>(wr, c, lane);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { sg[col + j] = 0.f; sb[col + j] = 0.f; }
+    for (int j = 0; j < 8; ++j) { ag[c][j] = 0.f; ab[c][j] = 0.f; }
   }
 
   for (long long base = static_cast<long long>(blockIdx.x) * RPB; base < rows;
@@ -173,8 +175,8 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy, const __nv
         for (int j = 0; j < 8; ++j) {
           const float xhat = (xv[c][j] - mean) * rstd;
           const float d = gy[c][j];
-          sg[col + j] += d * xhat;
-          sb[col + j] += d;
+          ag[c][j] = fmaf(d, xhat, ag[c][j]);
+          ab[c][j] += d;
           const float gd = d * g[j];
           xv[c][j] = xhat;
           gy[c][j] = gd;
@@ -204,6 +206,12 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy, const __nv
     }
   }
 
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = col_of<CHUNKS, WPR>(wr, c, lane);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { sg[col + j] = ag[c][j]; sb[col + j] = ab[c][j]; }
+  }
   __syncthreads();
   for (int col = threadIdx.x; col < n; col += blockDim.x) {
     float a = 0.f, b = 0.f;

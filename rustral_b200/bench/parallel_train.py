@@ -57,6 +57,7 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--capacity-factor", type=float, default=1.5, help="expert-parallel receive capacity (x balanced share)")
     ap.add_argument("--unfused", action="store_true")
     ap.add_argument("--same-batch", action="store_true", help="train on one fixed batch (tests: the loss must fall)")
     a = ap.parse_args(argv)
@@ -95,7 +96,8 @@ def main(argv=None):
                 pp_pg = g
     if a.ep > 1:
         from ..parallel.expert_parallel import FusedEP
-        ep_ctx = FusedEP(None, dev, cfg.num_experts, cfg.d_model, max_tokens=a.micro_batch * S, k=cfg.top_k)
+        ep_ctx = FusedEP(None, dev, cfg.num_experts, cfg.d_model, max_tokens=a.micro_batch * S, k=cfg.top_k,
+                         capacity_factor=a.capacity_factor if a.capacity_factor > 0 else None)
 
     per_stage = cfg.n_layer // a.pp
     model = ParallelDecoderLM(cfg, dev, tp_pg=tp_pg, fused_tp=fused_tp, ep=ep_ctx,

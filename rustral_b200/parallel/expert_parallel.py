@@ -46,13 +46,17 @@ class EPPlan:
     recv: M.MoEPlan               # grouped-GEMM plan of this rank's receive buffer (local experts)
     tokens: int
     k: int
+    dropped: torch.Tensor | None = None   # number of this rank's (token, choice) pairs beyond the capacity (device scalar)
 
 
 class FusedEP:
-    """Buffers and flags of one expert-parallel group.  `max_tokens` is the largest number of local tokens of a call;
-    the receive buffers are sized for the worst case (every pair of every rank routed here)."""
+    """Buffers and flags of one expert-parallel group.  `max_tokens` is the largest number of local tokens of a call.
+    Without a `capacity_factor` the receive buffers hold the worst case (every pair of every rank routed here) and no
+    token is ever dropped; with one they hold `capacity_factor * max_tokens * k` rows (the balanced share times the
+    factor) and pairs that would land beyond that are dropped, on every rank alike (`EPPlan.dropped` counts them)."""
 
-    def __init__(self, group, device, num_experts: int, d_model: int, max_tokens: int, k: int, limit_ms: int = 5000):
+    def __init__(self, group, device, num_experts: int, d_model: int, max_tokens: int, k: int, limit_ms: int = 5000,
+                 capacity_factor: float | None = None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -61,7 +65,8 @@ class FusedEP:
         self.device = torch.device(device)
         self.E, self.El, self.d, self.k = num_experts, num_experts // self.world, d_model, k
         self.limit_ms = limit_ms
-        cap = self.world * max_tokens * k + self.El * M.ROW_ALIGN
+        rows = self.world * max_tokens * k if capacity_factor is None else int(capacity_factor * max_tokens * k)
+        cap = min(rows, self.world * max_tokens * k) + self.El * M.ROW_ALIGN
         self.cap = (cap + 127) // 128 * 128
         nbytes = self.cap * d_model * 2
         self.pad = SignalPad(group, self.device)
@@ -93,18 +98,22 @@ class FusedEP:
         base = off + table[:self.rank].sum(0)                          # this rank's rows start after lower ranks' rows
         e = idx.reshape(-1).long()
         pos = local.slot_pos.long() - local.offsets.long()[e]          # position inside this rank's group for expert e
-        dest_row = (base[e] + pos).to(torch.int32)
+        row = base[e] + pos
+        fits = row < self.cap                                         # the same verdict on every rank
+        dest_row = torch.where(fits, row, torch.full_like(row, -1)).to(torch.int32)
         dest_rank = (e // El).to(torch.int32)
-        # receive side
-        my_counts = seg.view(W, El)[self.rank].to(torch.int32)
+        dropped = (~fits).sum()
+        # receive side (segments cut at the capacity)
         recv_off = torch.zeros(El + 1, dtype=torch.int64, device=idx.device)
         recv_off[1:] = torch.cumsum(pr[self.rank], 0)
+        recv_off = recv_off.clamp(max=self.cap)
+        my_counts = torch.minimum(seg.view(W, El)[self.rank], self.cap - recv_off[:-1]).clamp(min=0).to(torch.int32)
         tiles = torch.arange(self.cap // 128, device=idx.device) * 128
         te = torch.bucketize(tiles, recv_off[1:], right=True)
         tile_expert = torch.where(tiles < recv_off[-1], te, torch.full_like(te, -1)).to(torch.int32)
         num_tiles = (recv_off[-1:] // 128).to(torch.int32)
         recv = M.MoEPlan(my_counts, recv_off.to(torch.int32), None, None, tile_expert, num_tiles, self.cap, El, k)
-        return EPPlan(dest_rank, dest_row, seg.to(torch.int32), recv, T, k)
+        return EPPlan(dest_rank, dest_row, seg.to(torch.int32), recv, T, k, dropped)
 
     # ---------------------------------------------------------------------------------------------- transport
     def push(self, src: torch.Tensor, pl: EPPlan, to: str, scale=None) -> torch.Tensor:
