@@ -206,6 +206,57 @@ tp_reduce_slots_kernel(const __nv_bfloat16* __restrict__ slots, int world, long 
   }
 }
 
+// One-shot all-reduce / all-gather over symmetric staging buffers (see symm.h).  Every CTA waits for the flags
+// itself, so no grid-wide barrier is needed; CTA 0 raises this rank's flags before waiting.
+__global__ void __launch_bounds__(256)
+tp_allreduce_kernel(void* const* __restrict__ stage_ptrs, void* const* __restrict__ pad_ptrs,
+                    const unsigned int* __restrict__ local_pad, int world, int rank, int channel, unsigned int epoch,
+                    const unsigned int* __restrict__ epoch_dev, unsigned long long limit_ns,
+                    const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out, int rows, int cols,
+                    int gather, unsigned int* status) {
+  __shared__ int ok_s;
+  // A call captured in a CUDA graph cannot carry its epoch as a launch argument: it reads the counter that an
+  // earlier kernel of the same stream has advanced.
+  if (epoch_dev != nullptr) epoch = *epoch_dev;
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<unsigned int*>(pad_ptrs[threadIdx.x]) + channel * world + rank, epoch);
+  }
+  if (threadIdx.x == 0) ok_s = wait_flags(local_pad, world, channel, epoch, limit_ns, status, 120 + channel) ? 1 : 0;
+  __syncthreads();
+  if (!ok_s) return;
+  const int c8 = cols / 8;
+  const long long n8 = static_cast<long long>(rows) * c8;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    if (gather) {
+      const long long r = i / c8, c = i - r * c8;
+      for (int s = 0; s < world; ++s) {
+        const uint4 v = reinterpret_cast<const uint4*>(stage_ptrs[s])[i];
+        reinterpret_cast<uint4*>(out + (r * world + s) * static_cast<long long>(cols))[c] = v;
+      }
+      continue;
+    }
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (residual) {
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(residual) + i);
+      const uint32_t* pu = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(pu[j]); acc[2 * j] = f.x; acc[2 * j + 1] = f.y; }
+    }
+    for (int s = 0; s < world; ++s) {
+      const uint4 u = reinterpret_cast<const uint4*>(stage_ptrs[s])[i];
+      const uint32_t* pu = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(pu[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
 }  // namespace rb
 
 namespace {
@@ -325,5 +376,20 @@ RB_API int rb_tp_reduce_slots(const void* slots, int world, long long slot_elems
   rb::tp_reduce_slots_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
       reinterpret_cast<const __nv_bfloat16*>(slots), world, slot_elems, reinterpret_cast<const __nv_bfloat16*>(residual),
       reinterpret_cast<__nv_bfloat16*>(out));
+  return static_cast<int>(cudaGetLastError());
+}
+
+RB_API int rb_tp_allreduce(void* const* stage_ptrs_dev, void* const* pad_ptrs_dev, const void* local_pad, int world,
+                           int rank, int channel, unsigned int epoch, const unsigned int* epoch_dev, int limit_ms,
+                           const void* residual, void* out, int rows, int cols, int gather, void* stream_v) {
+  if (!stage_ptrs_dev || !pad_ptrs_dev || !local_pad || !out || world < 1 || world > 8 || rank < 0 || rank >= world) return -1;
+  if (rows <= 0 || cols <= 0 || (cols % 8) || channel < 0 || limit_ms <= 0) return -1;
+  const long long n8 = static_cast<long long>(rows) * (cols / 8);
+  long long blocks = (n8 + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  rb::tp_allreduce_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      stage_ptrs_dev, pad_ptrs_dev, reinterpret_cast<const unsigned int*>(local_pad), world, rank, channel, epoch, epoch_dev,
+      static_cast<unsigned long long>(limit_ms) * 1000000ull, reinterpret_cast<const __nv_bfloat16*>(residual),
+      reinterpret_cast<__nv_bfloat16*>(out), rows, cols, gather, rbhost::status_ptr());
   return static_cast<int>(cudaGetLastError());
 }

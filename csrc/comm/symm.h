@@ -51,6 +51,19 @@ int rb_zero_adam_push(const RbZeroArgs* args, void* stream);
 // out[rows, n] = sum over `world` receive slots (dense, slot_elems bf16 each, rank order) (+ residual): the owner-side
 // tail of the fused GEMM -> reduce-scatter (peer_mode 2 of rb_gemm_bf16).
 int rb_tp_reduce_slots(const void* slots, int world, long long slot_elems, const void* residual, void* out, void* stream);
+// One-shot all-reduce / all-gather for small tensor-parallel activations (decode steps, short prefills).
+// Every rank has written its [rows, cols] bf16 contribution into its own symmetric staging buffer (stage_ptrs_dev[r]
+// is rank r's, peer-mapped).  The kernel raises this rank's flag on every peer, waits (bounded, limit_ms) for all
+// flags of (channel, epoch), then
+//   gather == 0: out[rows, cols]           = sum over ranks (rank order, fp32) (+ residual[rows, cols])
+//   gather == 1: out[rows, world * cols]   = the contributions side by side, rank r in columns [r*cols, (r+1)*cols)
+// Callers alternate between two staging buffers from call to call; a flag for call n+1 is only raised after the
+// rank has finished reading call n, so a buffer is never overwritten while a peer still reads it.
+// `epoch_dev` (optional): device word holding the epoch, advanced by the caller with a kernel earlier in the stream;
+// it replaces the `epoch` argument, so that a call captured in a CUDA graph sees a new epoch at every replay.
+int rb_tp_allreduce(void* const* stage_ptrs_dev, void* const* pad_ptrs_dev, const void* local_pad, int world, int rank,
+                    int channel, unsigned int epoch, const unsigned int* epoch_dev, int limit_ms, const void* residual,
+                    void* out, int rows, int cols, int gather, void* stream);
 #ifdef __cplusplus
 }
 #endif

@@ -630,10 +630,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
-// d (+)= sum_s ws[s] (slabs of M*N fp32, dense), s ascending: the order is fixed, so the result is reproducible.
+// d (+)= sum_s ws[s] (+ bias) (+ residual)  (slabs of M*N fp32, dense), s ascending: the order is fixed, so the
+// result is reproducible.
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long slab, void* d, long long ldd, int M, int N,
-                     int out_f32, int accumulate) {
+                     int out_f32, int accumulate, const __nv_bfloat16* __restrict__ bias,
+                     const __nv_bfloat16* __restrict__ residual, long long ldr) {
   const long long n4 = static_cast<long long>(M) * N / 4;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
@@ -645,6 +647,16 @@ splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long slab, v
     const long long e = i * 4;
     const long long row = e / N;
     const int col = static_cast<int>(e - row * N);
+    if (bias != nullptr) {
+      const uint2 b = __ldg(reinterpret_cast<const uint2*>(bias + col));
+      const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y);
+      acc.x += b0.x; acc.y += b0.y; acc.z += b1.x; acc.w += b1.y;
+    }
+    if (residual != nullptr) {
+      const uint2 r = __ldg(reinterpret_cast<const uint2*>(residual + row * ldr + col));
+      const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y);
+      acc.x += r0.x; acc.y += r0.y; acc.z += r1.x; acc.w += r1.y;
+    }
     if (out_f32) {
       float4* dp = reinterpret_cast<float4*>(reinterpret_cast<float*>(d) + row * ldd + col);
       if (accumulate) { const float4 o = *dp; acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w; }
@@ -714,6 +726,7 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
     splits = (num_kb + kb_per - 1) / kb_per;   // no split may end up with an empty K range
     slab = static_cast<long long>(g.M) * g.N;
     ep.d = g.workspace; ep.ldd = g.N; ep.out_f32 = 1; ep.accumulate = 0;
+    ep.bias = nullptr; ep.residual = nullptr;          // applied once, by the kernel that folds the slabs
   }
   rb::GroupInfo grp;
   grp.mode = g.group_mode; grp.num_experts = g.num_experts;
@@ -738,7 +751,9 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
   const long long n4 = slab / 4;
   int rgrid = static_cast<int>((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
   rb::splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(reinterpret_cast<const float*>(g.workspace), splits, slab, g.d,
-                                                      g.ldd, g.M, g.N, g.out_f32, g.accumulate);
+                                                      g.ldd, g.M, g.N, g.out_f32, g.accumulate,
+                                                      reinterpret_cast<const __nv_bfloat16*>(g.bias),
+                                                      reinterpret_cast<const __nv_bfloat16*>(g.residual), g.ldr);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -765,8 +780,8 @@ long long plan_cost(int M, int N, int bn, int splits, int sms) {
 void pick_plan(const RbGemmArgs& g, int sms, int& bn_out, int& splits_out) {
   const int cands[4] = {256, 192, 128, 64};
   const int split_cands[7] = {1, 2, 3, 4, 6, 8, 12};
-  const bool can_split = g.group_mode == 0 && g.peer_mode == 0 && g.workspace != nullptr && g.act == RB_ACT_NONE && !g.bias && !g.residual && !g.aux_out &&
-                         (g.N % 4 == 0) && (static_cast<long long>(g.M) * g.N % 4 == 0);
+  const bool can_split = g.group_mode == 0 && g.peer_mode == 0 && g.workspace != nullptr && g.act == RB_ACT_NONE && !g.aux_out &&
+                         (g.N % 4 == 0) && (static_cast<long long>(g.M) * g.N % 4 == 0) && (!g.residual || (g.ldr % 4 == 0));
   long long best = -1;
   bn_out = 128; splits_out = 1;
   for (int c = 0; c < 4; ++c) {

@@ -60,8 +60,12 @@ const CUtensorMap* get_tmap_2d(const void* base, int elem_bytes, uint64_t inner,
   auto it = g_cache.find(k);
   if (it != g_cache.end()) return it->second;
   // The encode is a driver call and needs this thread to have the device's primary context bound; a thread that has
-  // made no runtime call yet (an autograd worker) has none until a runtime call binds it.
-  cudaFree(nullptr);
+  // made no runtime call yet (an autograd worker) has none.  cudaSetDevice binds it and, unlike cudaFree(0), is legal
+  // while a stream is being captured into a graph.
+  {
+    int cur = 0;
+    if (cudaGetDevice(&cur) == cudaSuccess) cudaSetDevice(cur);
+  }
   EncodeTiledFn fn = encode_fn();
   if (!fn) { if (err) *err = -10; return nullptr; }
   if (g_cache.size() > 65536) {   // bound the cache; maps are cheap to rebuild
@@ -107,8 +111,12 @@ const CUtensorMap* get_tmap_4d(const void* base, int elem_bytes, const uint64_t 
   auto it = g_cache.find(k);
   if (it != g_cache.end()) return it->second;
   // The encode is a driver call and needs this thread to have the device's primary context bound; a thread that has
-  // made no runtime call yet (an autograd worker) has none until a runtime call binds it.
-  cudaFree(nullptr);
+  // made no runtime call yet (an autograd worker) has none.  cudaSetDevice binds it and, unlike cudaFree(0), is legal
+  // while a stream is being captured into a graph.
+  {
+    int cur = 0;
+    if (cudaGetDevice(&cur) == cudaSuccess) cudaSetDevice(cur);
+  }
   EncodeTiledFn fn = encode_fn();
   if (!fn) { if (err) *err = -10; return nullptr; }
   CUtensorMap* m = new CUtensorMap;

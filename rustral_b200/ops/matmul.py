@@ -149,7 +149,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         for r, pp in enumerate(peer["peer_ptrs"]):
             g.peer_ptrs[r] = pp
         g.splits = 1
-    elif splits != 1 and K >= 2048 and act == "none" and bias is None and residual is None:
+    elif splits != 1 and K >= 2048 and act == "none":
         ws = _workspace(a.device)
         g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel()
     N.check(N.kernels().rb_gemm_bf16(g, N.stream_ptr()), "rb_gemm_bf16")

@@ -11,7 +11,9 @@ N.optional_sig("rb_kv_append", [N.c_void_p, N.c_ll, N.c_void_p, N.c_ll, N.c_void
                                 N.c_int, N.c_ll, N.c_void_p])
 N.optional_sig("rb_paged_attention_decode", [N.c_void_p, N.c_ll, N.c_void_p, N.c_ll, N.c_void_p, N.c_void_p, N.c_void_p,
                                              N.c_int, N.c_void_p, N.c_int, N.c_int, N.c_int, N.c_int, N.c_int, N.c_ll,
-                                             N.c_float, N.c_void_p])
+                                             N.c_float, N.c_void_p, N.c_void_p])
+N.optional_sig("rb_paged_attention_scratch_floats", [N.c_int, N.c_int, N.c_int, N.c_int, N.c_int], N.c_ll)
+N._LAUNCHES["rb_paged_attention_decode"] = 2
 
 
 def kv_append(k_new, v_new, k_cache, v_cache, slot_mapping):
@@ -55,8 +57,11 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, context_lens, scal
             return out
         return r
     out = out if out is not None else torch.empty((B, heads * d), dtype=q.dtype, device=q.device)
-    N.check(N.kernels().rb_paged_attention_decode(q2.data_ptr(), q2.stride(0), out.data_ptr(), out.stride(0),
-                                                  k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
-                                                  block_tables.shape[1], context_lens.data_ptr(), B, heads, hk, d, bs, nb,
-                                                  scale, N.stream_ptr()), "rb_paged_attention_decode")
+    lib = N.kernels()
+    scratch = torch.empty(lib.rb_paged_attention_scratch_floats(B, heads, d, block_tables.shape[1], bs), dtype=torch.float32,
+                          device=q.device)
+    N.check(lib.rb_paged_attention_decode(q2.data_ptr(), q2.stride(0), out.data_ptr(), out.stride(0),
+                                          k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+                                          block_tables.shape[1], context_lens.data_ptr(), B, heads, hk, d, bs, nb,
+                                          scale, scratch.data_ptr(), N.stream_ptr()), "rb_paged_attention_decode")
     return out

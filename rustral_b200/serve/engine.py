@@ -114,10 +114,12 @@ class ServingEngine:
 
 
 def run_poisson_workload(engine: ServingEngine, num_requests: int, rate_per_s: float, prompt_range=(128, 2048),
-                         output_range=(128, 512), seed: int = 0, time_limit_s: float = 3600.0) -> ServingMetrics:
+                         output_range=(128, 512), seed: int = 0, time_limit_s: float = 3600.0, clock=None) -> ServingMetrics:
     """Open-loop load test: requests arrive by a Poisson process at `rate_per_s`, prompt and output lengths uniform in
     the given ranges, prompt tokens uniform random; the engine steps in real time and a request is submitted once
-    its arrival time has passed (its latency clock starts at the ARRIVAL time, so queueing counts)."""
+    its arrival time has passed (its latency clock starts at the ARRIVAL time, so queueing counts).  `clock(now)`
+    may replace each loop iteration's time by an agreed one (tensor-parallel ranks: rank 0's), so that all ranks
+    admit the same requests in the same iteration."""
     g = torch.Generator().manual_seed(seed)
     vocab = engine.runner.cfg.vocab_size
     gaps = torch.empty(num_requests).exponential_(rate_per_s, generator=g)
@@ -127,8 +129,12 @@ def run_poisson_workload(engine: ServingEngine, num_requests: int, rate_per_s: f
     prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in plen]
     t0 = time.perf_counter()
     nxt = 0
-    while (nxt < num_requests or engine.scheduler.has_work()) and time.perf_counter() - t0 < time_limit_s:
+    while nxt < num_requests or engine.scheduler.has_work():
         now = time.perf_counter() - t0
+        if clock is not None:
+            now = clock(now)
+        if now >= time_limit_s:
+            break
         while nxt < num_requests and arrivals[nxt] <= now:
             engine.submit(prompts[nxt], olen[nxt], arrival_time=t0 + arrivals[nxt])
             nxt += 1

@@ -23,16 +23,41 @@ from .kv_cache import PagedCache
 
 
 class ModelRunner:
-    def __init__(self, cfg: GPTConfig, params: FlatParams | None = None, device=None, num_blocks: int = 1024,
-                 block_size: int = 16, seed: int = 0):
+    """`tp` (a parallel.tp_inference.TPInferenceComm) makes this rank one shard of a tensor-parallel model: `params`
+    then holds this rank's shard (serve.weights.InferenceWeights), the cache holds this rank's KV heads, and the
+    attention-output, down-projection and LM-head results are exchanged with one-shot peer-memory collectives.  All
+    ranks run the same calls in the same order and obtain bit-identical logits."""
+
+    def __init__(self, cfg: GPTConfig, params=None, device=None, num_blocks: int = 1024,
+                 block_size: int = 16, seed: int = 0, tp=None):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.cfg = cfg
         self.device = torch.device(device)
+        self.tp = tp
+        self.tp_world = tp.world if tp is not None else 1
+        if tp is not None:
+            if cfg.arch != "llama" or cfg.n_head % tp.world or cfg.n_kv_head % tp.world or cfg.ffn_dim % tp.world or \
+                    cfg.vocab_padded % (8 * tp.world):
+                raise ValueError("tensor-parallel serving: llama-style model whose heads, FFN and vocabulary divide evenly")
+            if params is None:
+                from .weights import InferenceWeights
+                params = InferenceWeights.random_llama(cfg, self.device, tp.rank, tp.world, seed)
         self.params = params if params is not None else FlatParams(cfg, self.device, seed)
         self.dtype = self.params.lowp.dtype
-        self.cache = PagedCache(num_blocks, block_size, cfg.n_layer, cfg.n_kv_head, cfg.head_dim, self.dtype, self.device)
+        self.n_head, self.n_kv_head = cfg.n_head // self.tp_world, cfg.n_kv_head // self.tp_world
+        self.cache = PagedCache(num_blocks, block_size, cfg.n_layer, self.n_kv_head, cfg.head_dim, self.dtype, self.device)
         self.block_size = block_size
+        self.use_graphs = True          # CUDA-graph replay of decode steps
+        self._graphs: dict = {}
+
+    def _row_parallel(self, a, w, bias, residual):
+        """a @ w^T (+ bias) + residual; with tensor parallelism the partial products are summed over the ranks."""
+        if self.tp is None:
+            return gemm(a, w, bias=bias, residual=residual)
+        rows = a.shape[0]
+        gemm(a, w, out=self.tp.staging(rows, w.shape[0]))
+        return self.tp.all_reduce(rows, w.shape[0], residual=residual)
 
     # ---- shared layer body ------------------------------------------------------------------------------------
     def _norm(self, x, name):
@@ -45,13 +70,17 @@ class ModelRunner:
         h = self._norm(x1, p + "ln2")
         if cfg.arch == "llama":
             gu = gemm(h, P.w(p + "ffn.gate_up.weight"))
-            return gemm(rope_ops.swiglu_forward(gu), P.w(p + "ffn.down.weight"), residual=x1)
+            return self._row_parallel(rope_ops.swiglu_forward(gu), P.w(p + "ffn.down.weight"), None, x1)
         h = gemm(h, P.w(p + "ffn.fc1.weight"), bias=P.w(p + "ffn.fc1.bias"), act="gelu")
         return gemm(h, P.w(p + "ffn.fc2.weight"), bias=P.w(p + "ffn.fc2.bias"), residual=x1)
 
     def _head(self, x):
         P, cfg = self.params, self.cfg
         xf = self._norm(x, "final_norm")
+        if self.tp is not None:
+            w = P.w("head.weight")
+            gemm(xf, w, out=self.tp.staging(xf.shape[0], w.shape[0]))
+            return self.tp.all_gather_cols(xf.shape[0], w.shape[0])
         return gemm(xf, P.w("tok_embed.embed" if cfg.tie_embeddings else "head.weight"))
 
     def _embed(self, ids, positions):
@@ -68,7 +97,7 @@ class ModelRunner:
         logits of the last position, [vocab_padded]."""
         cfg, P = self.cfg, self.params
         L = len(tokens)
-        H, Hk, D = cfg.n_head, cfg.n_kv_head, cfg.head_dim
+        H, Hk, D = self.n_head, self.n_kv_head, cfg.head_dim
         rms = cfg.arch == "llama"
         ids = torch.tensor(tokens, dtype=torch.int64, device=self.device)
         pos = torch.arange(L, dtype=torch.int64, device=self.device)
@@ -90,29 +119,21 @@ class ModelRunner:
                 a, _ = attn_ops.attention_forward(q, k2.view(1, L, Hk, D), v2.view(1, L, Hk, D), True, scale, want_lse=False)
             else:
                 a = attn_ops.attention_reference(q, k2.view(1, L, Hk, D), v2.view(1, L, Hk, D), True, scale)
-            x = gemm(a.reshape(L, H * D), P.w(p + "attn.wo.weight"), bias=None if rms else P.w(p + "attn.wo.bias"), residual=x)
+            x = self._row_parallel(a.reshape(L, H * D), P.w(p + "attn.wo.weight"), None if rms else P.w(p + "attn.wo.bias"), x)
             x = self._mlp(x, p)
-        return self._head(x[L - 1:L].contiguous())[0]
+        logits = self._head(x[L - 1:L].contiguous())[0]
+        if self.tp is not None:
+            self.tp.end_step()
+        return logits
 
     # ---- decode ------------------------------------------------------------------------------------------------------
-    @torch.no_grad()
-    def decode(self, seq_ids: list, last_tokens: list, context_lens: list) -> torch.Tensor:
-        """One new token per sequence.  context_lens[i] counts the tokens in the cache AFTER this token is appended.
-        Returns logits [batch, vocab_padded]."""
+    def _decode_body(self, ids, ctx, bt):
+        """The device-side part of a decode step on static tensors (captured into a CUDA graph per batch size)."""
         cfg, P = self.cfg, self.params
-        B = len(seq_ids)
-        H, Hk, D = cfg.n_head, cfg.n_kv_head, cfg.head_dim
+        B = ids.shape[0]
+        H, Hk, D = self.n_head, self.n_kv_head, cfg.head_dim
         rms = cfg.arch == "llama"
-        dev = self.device
-        ids = torch.tensor(last_tokens, dtype=torch.int64, device=dev)
-        ctx = torch.tensor(context_lens, dtype=torch.int32, device=dev)
         pos = (ctx - 1).to(torch.int64)
-        tables = [self.cache.block_table(s) for s in seq_ids]
-        max_blocks = max(len(t) for t in tables)
-        bt_host = torch.zeros((B, max_blocks), dtype=torch.int32)
-        for i, t in enumerate(tables):
-            bt_host[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
-        bt = bt_host.to(dev)
         slots = bt.gather(1, (pos // self.block_size).view(B, 1)).view(B).to(torch.int64) * self.block_size + pos % self.block_size
         x = self._embed(ids, pos)
         scale = 1.0 / math.sqrt(D)
@@ -124,6 +145,59 @@ class ModelRunner:
                 rope_ops.rope_(qkv, H + Hk, D, positions=pos, theta=cfg.rope_theta)
             paged_ops.kv_append(qkv[:, H * D:(H + Hk) * D], qkv[:, (H + Hk) * D:], self.cache.k[l], self.cache.v[l], slots)
             a = paged_ops.paged_attention_decode(qkv[:, :H * D], self.cache.k[l], self.cache.v[l], bt, ctx, scale)
-            x = gemm(a, P.w(p + "attn.wo.weight"), bias=None if rms else P.w(p + "attn.wo.bias"), residual=x)
+            x = self._row_parallel(a, P.w(p + "attn.wo.weight"), None if rms else P.w(p + "attn.wo.bias"), x)
             x = self._mlp(x, p)
-        return self._head(x)
+        logits = self._head(x)
+        if self.tp is not None:
+            self.tp.end_step()
+        return logits
+
+    def _fill_tables(self, seq_ids, width: int) -> torch.Tensor:
+        tables = [self.cache.block_table(s) for s in seq_ids]
+        bt_host = torch.zeros((len(seq_ids), width), dtype=torch.int32)
+        for i, t in enumerate(tables):
+            bt_host[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+        return bt_host
+
+    @torch.no_grad()
+    def decode(self, seq_ids: list, last_tokens: list, context_lens: list) -> torch.Tensor:
+        """One new token per sequence.  context_lens[i] counts the tokens in the cache AFTER this token is appended.
+        Returns logits [batch, vocab_padded] (with CUDA graphs: valid until the next decode call)."""
+        B = len(seq_ids)
+        dev = self.device
+        if self.use_graphs and dev.type == "cuda":
+            return self._decode_graphed(seq_ids, last_tokens, context_lens)
+        ids = torch.tensor(last_tokens, dtype=torch.int64, device=dev)
+        ctx = torch.tensor(context_lens, dtype=torch.int32, device=dev)
+        max_blocks = max(len(self.cache.block_table(s)) for s in seq_ids)
+        bt = self._fill_tables(seq_ids, max_blocks).to(dev)
+        return self._decode_body(ids, ctx, bt)
+
+    def _decode_graphed(self, seq_ids, last_tokens, context_lens) -> torch.Tensor:
+        """Replays one captured CUDA graph per batch size: the ~10 launches per layer of a decode step are
+        launch-bound from Python, the graph submits them in one call.  Inputs live in static device tensors that
+        are refreshed (three small copies) before each replay."""
+        B = len(seq_ids)
+        dev = self.device
+        width = (self.cfg.seq_len + self.block_size - 1) // self.block_size
+        g = self._graphs.get(B)
+        if g is None:
+            ids = torch.zeros(B, dtype=torch.int64, device=dev)
+            ctx = torch.ones(B, dtype=torch.int32, device=dev)
+            bt = torch.zeros((B, width), dtype=torch.int32, device=dev)
+            g = {"ids": ids, "ctx": ctx, "bt": bt, "graph": None, "out": None}
+            self._graphs[B] = g
+        g["ids"].copy_(torch.tensor(last_tokens, dtype=torch.int64), non_blocking=True)
+        g["ctx"].copy_(torch.tensor(context_lens, dtype=torch.int32), non_blocking=True)
+        g["bt"].copy_(self._fill_tables(seq_ids, width), non_blocking=True)
+        if g["graph"] is None:
+            # first use of this batch size: one eager run (lazy kernel configuration, tensor-map cache), then capture
+            out = self._decode_body(g["ids"], g["ctx"], g["bt"])
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                g["out"] = self._decode_body(g["ids"], g["ctx"], g["bt"])
+            g["graph"] = graph
+            return out
+        g["graph"].replay()
+        return g["out"]
