@@ -630,6 +630,273 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Two-CTA variant (cta_group::2): the two CTAs of a cluster share one 256 x BLOCK_N output tile.  Each CTA loads the
+// 128 rows of A it owns and HALF of the B tile (BLOCK_N / 2 rows) into its own shared memory; the even CTA issues
+// tcgen05.mma.cta_group::2, which reads both halves of B and writes each CTA's 128 accumulator rows into that CTA's
+// TMEM.  Per k-block a CTA moves 16 KB + 16 KB instead of 16 KB + 32 KB through the L2 -> SM fabric, which is what
+// bounds the one-CTA kernel on short-K problems.  No TMA multicast: every load targets the loading CTA's own memory
+// and reports its bytes to the leader's barrier; tcgen05.commit signals both CTAs' barriers.
+// Plain (non-grouped, non-peer) problems only; the epilogue is the staged / direct epilogue of the one-CTA kernel.
+// ------------------------------------------------------------------------------------------------------------------
+template <int BLOCK_N, int STAGES>
+struct SmemLayoutPair {
+  static constexpr int kABytes = kBlockM * kBlockK * 2;
+  static constexpr int kBBytes = (BLOCK_N / 2) * kBlockK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16;
+  static constexpr int kStageCols = (BLOCK_N % 128 == 0) ? 64 : 32;
+  static constexpr int kStagingOffset = (kTotal + 15) & ~15;
+  static constexpr int kStagingBytesPerWarp = 32 * kStageCols * 2;
+  static constexpr int kTotalStaged = kStagingOffset + kNumEpilogueWarps * kStagingBytesPerWarp;
+};
+
+template <int A_MN, int B_MN, int BLOCK_N, int STAGES>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
+                      int K, int group_m, int num_splits, int kb_per_split, long long d_split_stride, EpiParams ep,
+                      unsigned int* status) {
+  using L = SmemLayoutPair<BLOCK_N, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = smem_u32(bars + STAGES);
+  const uint32_t bar_tfull = smem_u32(bars + 2 * STAGES);
+  const uint32_t bar_tempty = smem_u32(bars + 2 * STAGES + 2);
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();       // 0: leader (issues the MMAs), 1: peer
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+  constexpr uint32_t kTmemCols = (2 * BLOCK_N <= 64) ? 64 : (2 * BLOCK_N <= 128) ? 128 : (2 * BLOCK_N <= 256) ? 256 : 512;
+  constexpr int kPairM = 2 * kBlockM;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);                // leader: its own expect_tx arrival (+ both CTAs' bytes)
+      mbar_init(bar_empty + 8 * s, 1);               // one multicast commit per use
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 2 * kNumEpilogueWarps);   // leader: the epilogue warps of both CTAs
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_ptr_smem), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                 // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int num_m = (M + kPairM - 1) / kPairM;
+  const int num_n = (N + BLOCK_N - 1) / BLOCK_N;
+  const int num_tiles = num_m * num_n;
+  const int num_kb_total = (K + kBlockK - 1) / kBlockK;
+  const int group_size = group_m * num_n;
+  const int num_units = num_tiles * num_splits;
+
+  auto decode_tile = [&](int unit, int& m_blk, int& n_blk, int& kb0, int& kb1, int& split) {
+    split = unit / num_tiles;
+    const int tile = unit - split * num_tiles;
+    kb0 = split * kb_per_split;
+    kb1 = min(num_kb_total, kb0 + kb_per_split);
+    const int group = tile / group_size;
+    const int first_m = group * group_m;
+    const int gm = min(group_m, num_m - first_m);
+    const int in_group = tile - group * group_size;
+    m_blk = first_m + in_group % gm;
+    n_blk = in_group / gm;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ TMA producer (both CTAs)
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_units && ok; tile += num_clusters) {
+        int m_blk, n_blk, kb0, kb1, split;
+        decode_tile(tile, m_blk, n_blk, kb0, kb1, split);
+        const int a_row = m_blk * kPairM + static_cast<int>(cta_rank) * kBlockM;
+        const int b_row = n_blk * BLOCK_N + static_cast<int>(cta_rank) * (BLOCK_N / 2);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, status, 11)) { ok = false; break; }
+          const uint32_t full_local = bar_full + 8 * s;
+          if (cta_rank == 0) mbar_arrive_expect_tx(full_local, 2 * L::kStageBytes);
+          const uint32_t full = mapa_shared(full_local, 0);
+          const uint32_t sa = smem_base + s * L::kStageBytes;
+          const uint32_t sb = sa + L::kABytes;
+          if (A_MN == 0) {
+            tma_load_2d_pair(sa, &tmA, kb * kBlockK, a_row, full);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBlockM / 64; ++j)
+              tma_load_2d_pair(sa + j * (kBlockK * 128), &tmA, a_row + j * 64, kb * kBlockK, full);
+          }
+          if (B_MN == 0) {
+            tma_load_2d_pair(sb, &tmB, kb * kBlockK, b_row, full);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_N / 2 / 64; ++j)
+              tma_load_2d_pair(sb + j * (kBlockK * 128), &tmB, b_row + j * 64, kb * kBlockK, full);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && cta_rank == 0) {
+      // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+      constexpr uint32_t idesc = umma_idesc_bf16(kPairM, BLOCK_N, A_MN, B_MN);
+      uint32_t it = 0, t = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_units && ok; tile += num_clusters, ++t) {
+        int m_blk, n_blk, kb0, kb1, split;
+        decode_tile(tile, m_blk, n_blk, kb0, kb1, split);
+        const uint32_t acc = t & 1, acc_ph = (t >> 1) & 1;
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, status, 12)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, status, 13)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * L::kStageBytes;
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint64_t da = A_MN ? umma_smem_desc_sw128(sa + k * (kUmmaK * 128), kBlockK * 128, 1024)
+                                     : umma_smem_desc_sw128(sa + k * (kUmmaK * 2), 16, 1024);
+            const uint64_t db = B_MN ? umma_smem_desc_sw128(sb + k * (kUmmaK * 128), kBlockK * 128, 1024)
+                                     : umma_smem_desc_sw128(sb + k * (kUmmaK * 2), 16, 1024);
+            umma_bf16_ss_pair(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+          }
+          umma_commit_pair(bar_empty + 8 * s, 3);     // both CTAs may refill this stage
+        }
+        if (ok) umma_commit_pair(bar_tfull + 8 * acc, 3);   // both CTAs' accumulator halves are complete
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- epilogue warps (both CTAs)
+    const int q = warp & 3;
+    const int ew = warp - 2;
+    const int cgrp = ew >> 2;
+    uint32_t t = 0;
+    for (int tile = cluster_id; tile < num_units; tile += num_clusters, ++t) {
+      int m_blk, n_blk, kb0, kb1, split;
+      decode_tile(tile, m_blk, n_blk, kb0, kb1, split);
+      EpiParams epu = ep;
+      if (num_splits > 1)
+        epu.d = reinterpret_cast<float*>(ep.d) + static_cast<long long>(split) * d_split_stride;
+      const uint32_t acc = t & 1, acc_ph = (t >> 1) & 1;
+      if (!mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, status, 14)) break;
+      tc_fence_after();
+      const long long row0 = static_cast<long long>(m_blk) * kPairM + static_cast<long long>(cta_rank) * kBlockM + q * 32;
+      const long long row = row0 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
+      const uint32_t tempty_leader = mapa_shared(bar_tempty + 8 * acc, 0);
+      if (epu.staged) {
+        constexpr int SC = L::kStageCols, CPR = SC / 8;
+        const uint32_t stg = smem_base + L::kStagingOffset + ew * L::kStagingBytesPerWarp;
+        constexpr int NB = (BLOCK_N / 2) / SC;
+        const bool two_pass = epu.aux_out != nullptr &&
+                              (epu.act == RB_ACT_GELU || epu.act == RB_ACT_RELU || epu.act == RB_ACT_SILU);
+        const int num_pass = two_pass ? 2 : 1;
+#pragma unroll 1
+        for (int hp = 0; hp < NB * num_pass; ++hp) {
+          const int h = hp / num_pass;
+          const bool pre_pass = two_pass && (hp - h * num_pass) == 0;
+          const bool last_pass = hp == NB * num_pass - 1;
+          __nv_bfloat16* dbase = pre_pass ? epu.aux_out : reinterpret_cast<__nv_bfloat16*>(epu.d);
+          const long long dld = pre_pass ? epu.ld_aux_out : epu.ldd;
+#pragma unroll 1
+          for (int cc = 0; cc < SC / 32; ++cc) {
+            const int c = cgrp * (BLOCK_N / 64) + h * (SC / 32) + cc;
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c * 32, r);
+            tmem_ld_wait();
+            if (last_pass && cc == SC / 32 - 1) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive_cluster(tempty_leader);
+            }
+            const int col0 = n_blk * BLOCK_N + c * 32;
+            float v[32];
+            if (row < M && col0 < N) {
+              if (pre_pass) epilogue_math<false, true>(epu, r, row, col0, N, v);
+              else epilogue_math<false, false>(epu, r, row, col0, N, v);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            }
+#pragma unroll
+            for (int qq = 0; qq < 4; ++qq) {
+              const int chunk = cc * 4 + qq;
+              const uint32_t addr = stg + lane * (SC * 2) + ((chunk ^ (lane & (CPR - 1))) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                           "r"(pack_bf16x2(v[qq * 8 + 0], v[qq * 8 + 1])), "r"(pack_bf16x2(v[qq * 8 + 2], v[qq * 8 + 3])),
+                           "r"(pack_bf16x2(v[qq * 8 + 4], v[qq * 8 + 5])), "r"(pack_bf16x2(v[qq * 8 + 6], v[qq * 8 + 7]))
+                           : "memory");
+            }
+          }
+          __syncwarp();
+          constexpr int RPI = 32 / CPR;
+          const int ch = lane % CPR, rsub = lane / CPR;
+          const int colg = n_blk * BLOCK_N + cgrp * (BLOCK_N / 2) + h * SC + ch * 8;
+#pragma unroll 4
+          for (int r0 = 0; r0 < 32; r0 += RPI) {
+            const int rl = r0 + rsub;
+            const long long rg = row0 + rl;
+            uint4 val;
+            const uint32_t addr = stg + rl * (SC * 2) + ((ch ^ (rl & (CPR - 1))) << 4);
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w) : "r"(addr));
+            if (rg < M && colg < N) *reinterpret_cast<uint4*>(dbase + rg * dld + colg) = val;
+          }
+          __syncwarp();
+        }
+        continue;
+      }
+#pragma unroll 1
+      for (int c = cgrp * (BLOCK_N / 64); c < (cgrp + 1) * (BLOCK_N / 64); ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (c == (cgrp + 1) * (BLOCK_N / 64) - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty_leader);
+        }
+        const int col0 = n_blk * BLOCK_N + c * 32;
+        if (row < M && col0 < N) epilogue_chunk(epu, r, row, col0, N);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                 // the leader's MMAs read this CTA's shared memory until here
+  if (warp == 1) {
+    if (*abort_flag) {
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
 // d (+)= sum_s ws[s] (+ bias) (+ residual)  (slabs of M*N fp32, dense), s ascending: the order is fixed, so the
 // result is reproducible.
 __global__ void __launch_bounds__(256)
@@ -766,6 +1033,73 @@ int dispatch_major(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap
   return launch<1, 0, BLOCK_N, STAGES>(g, ta, tb, grid, splits, s);
 }
 
+// RUSTRAL_GEMM_2CTA=0 keeps every problem on the one-CTA kernel.
+bool pair_kernel_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("RUSTRAL_GEMM_2CTA");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+template <int A_MN, int B_MN>
+int launch_pair(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb_half, int clusters, int splits,
+                cudaStream_t stream) {
+  constexpr int BLOCK_N = 256, STAGES = 6;
+  using L = rb::SmemLayoutPair<BLOCK_N, STAGES>;
+  auto kern = rb::gemm_bf16_pair_kernel<A_MN, B_MN, BLOCK_N, STAGES>;
+  const bool staged = !g.out_f32 && !g.accumulate && splits <= 1 && (g.N % 8 == 0) && staged_store_default() &&
+                      L::kTotalStaged + 1024 <= 232448;
+  const int smem = (staged ? L::kTotalStaged : L::kTotal) + 1024;
+  static int configured = 0;
+  if (configured < smem) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = smem;
+  }
+  rb::EpiParams ep;
+  ep.d = g.d; ep.ldd = g.ldd;
+  ep.bias = reinterpret_cast<const __nv_bfloat16*>(g.bias);
+  ep.residual = reinterpret_cast<const __nv_bfloat16*>(g.residual); ep.ldr = g.ldr;
+  ep.aux_in = reinterpret_cast<const __nv_bfloat16*>(g.aux_in); ep.ld_aux_in = g.ld_aux_in;
+  ep.aux_out = reinterpret_cast<__nv_bfloat16*>(g.aux_out); ep.ld_aux_out = g.ld_aux_out;
+  ep.act = g.act; ep.out_f32 = g.out_f32; ep.accumulate = g.accumulate; ep.alpha = g.alpha;
+  ep.staged = staged ? 1 : 0;
+  const int group_m = g.group_m > 0 ? g.group_m : 4;      // in 256-row units
+  const int num_kb = (g.K + rb::kBlockK - 1) / rb::kBlockK;
+  int kb_per = num_kb;
+  long long slab = 0;
+  if (splits > 1) {
+    kb_per = (num_kb + splits - 1) / splits;
+    splits = (num_kb + kb_per - 1) / kb_per;
+    slab = static_cast<long long>(g.M) * g.N;
+    ep.d = g.workspace; ep.ldd = g.N; ep.out_f32 = 1; ep.accumulate = 0;
+    ep.bias = nullptr; ep.residual = nullptr;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.blockDim = dim3(rb::kNumThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *ta, *tb_half, g.M, g.N, g.K, group_m, splits, kb_per, slab, ep,
+                                     rbhost::status_ptr());
+  if (e != cudaSuccess || splits <= 1) return static_cast<int>(e);
+  const long long n4 = slab / 4;
+  int rgrid = static_cast<int>((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
+  rb::splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(reinterpret_cast<const float*>(g.workspace), splits, slab, g.d,
+                                                      g.ldd, g.M, g.N, g.out_f32, g.accumulate,
+                                                      reinterpret_cast<const __nv_bfloat16*>(g.bias),
+                                                      reinterpret_cast<const __nv_bfloat16*>(g.residual), g.ldr);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // Relative time of one tile column unit per tile width: narrow tiles re-read the A operand from shared
 // memory more often per MMA (measured on B200: 128-wide runs ~1.3x, 64-wide ~2.3x slower than 256-wide).
 int width_cost(int bn) { return bn == 256 ? 100 : bn == 192 ? 104 : bn == 128 ? 132 : 235; }
@@ -866,6 +1200,19 @@ RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
                               : rbhost::get_tmap_2d(g.b, 2, (uint64_t)g.K, (uint64_t)g.N * b_experts, (uint64_t)g.ldb, 64, (uint32_t)bn, 1, &err);
   if (!tb) return err ? err : -5;
 
+  if (bn == 256 && g.peer_mode == 0 && g.group_mode == 0 && g.M > 128 && g.max_ctas == 0 && pair_kernel_enabled()) {
+    // two-CTA kernel: 256 x 256 tiles per CTA pair, each CTA loads half of the B tile
+    const CUtensorMap* tb_half =
+        g.b_mn_major ? tb : rbhost::get_tmap_2d(g.b, 2, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, 64, 128, 1, &err);
+    if (!tb_half) return err ? err : -5;
+    const long long tiles2 = (long long)((g.M + 255) / 256) * ((g.N + 255) / 256) * splits;
+    const int max_clusters = sms / 2;
+    const int clusters = static_cast<int>(tiles2 < max_clusters ? tiles2 : max_clusters);
+    if (!g.a_mn_major && !g.b_mn_major) return launch_pair<0, 0>(g, ta, tb_half, clusters, splits, stream);
+    if (!g.a_mn_major && g.b_mn_major) return launch_pair<0, 1>(g, ta, tb_half, clusters, splits, stream);
+    if (g.a_mn_major && g.b_mn_major) return launch_pair<1, 1>(g, ta, tb_half, clusters, splits, stream);
+    return launch_pair<1, 0>(g, ta, tb_half, clusters, splits, stream);
+  }
   long long tiles = (long long)((g.M + 127) / 128) * ((g.N + bn - 1) / bn) * splits;
   if (g.group_mode == 2) tiles *= g.num_experts;
   int grid = static_cast<int>(tiles < sms ? tiles : sms);
