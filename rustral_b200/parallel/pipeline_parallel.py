@@ -182,6 +182,34 @@ class PipelineParallel:
                 "num_stages": self.stage.num_stages, "num_micro_batches": self.cfg.num_micro_batches}
 
 
+class PipelineComm:
+    """Point-to-point channel between adjacent stages (crates/distributed/src/pipeline_parallel.rs:377-413, where the
+    queues are in-process `Mutex<Vec>`s).  Tags keep activations (even) and gradients (odd) of a micro-batch apart."""
+
+    def __init__(self, process_group: ProcessGroup, stage_id: int, num_stages: int):
+        self.pg, self.stage_id, self.num_stages = process_group, stage_id, num_stages
+
+    def send_activation(self, t: torch.Tensor, micro_batch: int) -> None:
+        if self.stage_id + 1 >= self.num_stages:
+            raise DistributedError("the last stage has no successor")
+        self.pg.send(t, self.stage_id + 1, 2 * micro_batch)
+
+    def recv_activation(self, buf: torch.Tensor, micro_batch: int) -> torch.Tensor:
+        if self.stage_id == 0:
+            raise DistributedError("the first stage has no predecessor")
+        return self.pg.recv(buf, self.stage_id - 1, 2 * micro_batch)
+
+    def send_gradient(self, t: torch.Tensor, micro_batch: int) -> None:
+        if self.stage_id == 0:
+            raise DistributedError("the first stage has no predecessor")
+        self.pg.send(t, self.stage_id - 1, 2 * micro_batch + 1)
+
+    def recv_gradient(self, buf: torch.Tensor, micro_batch: int) -> torch.Tensor:
+        if self.stage_id + 1 >= self.num_stages:
+            raise DistributedError("the last stage has no successor")
+        return self.pg.recv(buf, self.stage_id + 1, 2 * micro_batch + 1)
+
+
 def create_pipeline(layers: list, process_group: ProcessGroup, config: PipelineConfig, act_shape, act_dtype=torch.float32,
                     device="cpu", ctx=None) -> PipelineParallel:
     """Splits `layers` (modules with forward(x, ctx)) evenly over the ranks of `process_group`."""

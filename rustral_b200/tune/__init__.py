@@ -372,3 +372,64 @@ class PreTuner:
 
     def pretune(self, cfg, tokens: int) -> dict:
         return {s: self.tuner.tune(GemmKernel(*s)) for s in self.shapes_for(cfg, tokens)}
+
+
+class _StrategySearch:
+    """Named front ends of the C++ searcher, one per strategy of the reference (crates/autotuner/src/search.rs:
+    GridSearch, RandomSearch, EvolutionarySearch, BayesianSearch)."""
+    strategy = Strategy.GRID
+
+    def __init__(self, space: ConfigSpace, seed: int = 0, max_evals: int = 0):
+        self.handle = SearchHandle(space, self.strategy, seed, max_evals)
+
+    def next_config(self):
+        return self.handle.next_config()
+
+    def report(self, config: dict, time_us: float) -> None:
+        self.handle.report(config, time_us)
+
+    def best(self):
+        return self.handle.best()
+
+
+class GridSearch(_StrategySearch):
+    strategy = Strategy.GRID
+
+
+class RandomSearch(_StrategySearch):
+    strategy = Strategy.RANDOM
+
+
+class EvolutionarySearch(_StrategySearch):
+    strategy = Strategy.EVOLUTIONARY
+
+
+class BayesianSearch(_StrategySearch):
+    """Explore / exploit search over the discrete space (the native searcher keeps per-choice statistics and samples
+    configurations in proportion to their expected improvement)."""
+    strategy = Strategy.BAYESIAN
+
+
+@dataclass
+class TuningSession:
+    """Record of one tuning run (crates/autotuner/src/tuner.rs: TuningSession): what was tried, in order, and the best."""
+    kernel: str
+    shape_key: str
+    trials: list = field(default_factory=list)        # (config dict, time in us)
+    started_at: float = field(default_factory=time.time)
+    finished_at: float | None = None
+
+    def record(self, config: dict, time_us: float) -> None:
+        self.trials.append((dict(config), float(time_us)))
+
+    def finish(self) -> None:
+        self.finished_at = time.time()
+
+    @property
+    def best(self):
+        return min(self.trials, key=lambda t: t[1]) if self.trials else (None, float("inf"))
+
+    def to_dict(self) -> dict:
+        cfg, t = self.best
+        return {"kernel": self.kernel, "shape_key": self.shape_key, "num_trials": len(self.trials), "best_config": cfg,
+                "best_time_us": t, "elapsed_s": (self.finished_at or time.time()) - self.started_at}

@@ -291,3 +291,46 @@ def test_onnx_export_structure_and_dashboard():
         tui.EpochSnapshot(i, 1.0 / (i + 1), 0.5).push_to_dashboard(d)
     import io
     assert "loss 0.2000" in tui.DashboardRenderer(d, io.StringIO(), False).render_text()
+
+
+def test_gpu_profiler_chrome_trace_and_bandwidth(tmp_path):
+    import json
+    from rustral_b200.core.gpu_profiler import BandwidthCalculator, GpuProfiler, export_chrome_trace
+    prof = GpuProfiler("cpu")
+    with prof.scope("matmul", m=8):
+        torch.randn(64, 64) @ torch.randn(64, 64)
+    with prof.scope("copy", category="transfer"):
+        torch.randn(1024).clone()
+    prof.record_memory()
+    trace = json.loads(export_chrome_trace(prof, str(tmp_path / "t.json")))
+    names = [e["name"] for e in trace["traceEvents"]]
+    assert names == ["matmul", "copy", "memory"] and trace["traceEvents"][0]["ph"] == "X"
+    assert prof.summary()["matmul"]["count"] == 1
+    bw = BandwidthCalculator(peak_gbs=1000.0)
+    assert abs(bw.gbs(1e9, 1e6) - 1.0) < 1e-9 and abs(bw.utilization(1e9, 1e3) - 1.0) < 1e-9
+
+
+def test_search_strategies_tuning_session_and_tui_hook():
+    import io
+    from types import SimpleNamespace
+    from rustral_b200.runtime.tui_hook import TuiHook
+    from rustral_b200.tune import BayesianSearch, ConfigSpace, GridSearch, TuningSession
+    space = ConfigSpace({"block_n": [64, 128, 256], "group_m": [4, 8]})
+    cost = lambda c: abs(c["block_n"] - 128) + c["group_m"]
+    for cls in (GridSearch, BayesianSearch):
+        s = cls(space, seed=1, max_evals=12)
+        sess = TuningSession("gemm", "m128_n128_k128")
+        while True:
+            c = s.next_config()
+            if c is None:
+                break
+            s.report(c, cost(c))
+            sess.record(c, cost(c))
+        sess.finish()
+        best, t = s.best()
+        assert best == {"block_n": 128, "group_m": 4} and t == 4
+        assert sess.to_dict()["best_config"] == best
+    hook = TuiHook(start_thread=False)
+    hook.on_epoch(SimpleNamespace(epoch=3, train_loss=1.25))
+    assert hook.dashboard.epoch == 3 and hook.dashboard.losses[-1] == 1.25
+    hook.close()

@@ -314,3 +314,43 @@ def test_health_monitor_elastic_trainer_and_chaos(tmp_path):
     tb.arrive(0); tb.arrive(2)
     t[0] += 2
     assert tb.timed_out() and tb.missing() == [1]
+
+
+def test_pipeline_comm_and_nccl_facade_on_cpu():
+    import threading
+    import torch.distributed as dist
+    from rustral_b200.parallel.pipeline_parallel import PipelineComm
+    from rustral_b200.parallel.process_group import ProcessGroup
+    groups = ProcessGroup.new_threaded(2)
+    got = {}
+
+    def stage(r):
+        comm = PipelineComm(groups[r], r, 2)
+        if r == 0:
+            comm.send_activation(torch.arange(4.0), 3)
+            got["grad"] = comm.recv_gradient(torch.empty(4), 3)
+        else:
+            x = comm.recv_activation(torch.empty(4), 3)
+            comm.send_gradient(x * 2, 3)
+
+    ts = [threading.Thread(target=stage, args=(r,)) for r in range(2)]
+    [t.start() for t in ts]
+    [t.join(10) for t in ts]
+    assert torch.equal(got["grad"], torch.arange(4.0) * 2)
+
+    # the NCCL facade runs over gloo on CPU tensors (a world of one is enough for the call surface)
+    from rustral_b200.parallel.compression import CompressionType
+    from rustral_b200.parallel.nccl import NcclCommunicator, NcclCompressedCommunicator, NcclProcessGroup
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:29933", rank=0, world_size=1)
+    try:
+        comm = NcclCommunicator()
+        t = torch.ones(8)
+        assert torch.equal(comm.all_reduce(t.clone(), "avg"), t)
+        assert comm.all_gather(torch.ones(2, 3)).shape == (2, 3)
+        assert comm.reduce_scatter(torch.ones(4, 2)).shape == (4, 2)
+        assert torch.equal(comm.broadcast(t.clone()), t)
+        cc = NcclCompressedCommunicator(comm, CompressionType.BF16)
+        assert torch.allclose(cc.all_reduce_mean(torch.full((4,), 0.5)), torch.full((4,), 0.5))
+        assert NcclProcessGroup().world_size == 1
+    finally:
+        dist.destroy_process_group()
