@@ -294,39 +294,60 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
     const float sl2 = p.scale * kBtLog2e;
     bool ok = true;
+    // log-sum-exp and delta of this thread's row are fetched one step ahead: the load latency hides behind a whole step
+    auto load_stats = [&](int it, float& lse2, float& dlt) {
+      int hq, q0, k0;
+      walk_decode(it, hq, q0, k0);
+      const int q_idx = q0 + row;
+      if (q_idx < p.seq_q) {
+        const long long stat = (static_cast<long long>(b) * p.heads + hq) * p.seq_q + q_idx;
+        lse2 = __ldg(p.lse + stat) * kBtLog2e;
+        dlt = __ldg(p.delta + stat);
+      } else {
+        lse2 = 0.f;
+        dlt = 0.f;
+      }
+    };
+    float lse2_next = 0.f, dlt_next = 0.f;
+    if (n_it > 0) load_stats(0, lse2_next, dlt_next);
     for (int it = 0; it < n_it && ok; ++it) {
       int hq, q0, k0;
       walk_decode(it, hq, q0, k0);
       const int q_idx = q0 + row;
       const bool q_ok = q_idx < p.seq_q;
-      const long long stat = (static_cast<long long>(b) * p.heads + hq) * p.seq_q + q_idx;
-      const float lse2 = q_ok ? __ldg(p.lse + stat) * kBtLog2e : 0.f;
-      const float dlt = q_ok ? __ldg(p.delta + stat) : 0.f;
+      const float lse2 = lse2_next, dlt = dlt_next;
+      if (it + 1 < n_it) load_stats(it + 1, lse2_next, dlt_next);
       const int key_lim = q_ok ? (p.causal ? min(p.seq_k - 1, q_idx + shift) : p.seq_k - 1) : -1;   // last visible key
       const int kbase = k0 + cg * 64;
       const bool need_mask = (kbase + 63 > key_lim);
       if (!mbar_wait(bar_sdp_full, it & 1, abort_flag, status, 46)) { ok = false; break; }
       tc_fence_after();
       uint32_t pp[32], ds[32];                             // 64 columns each, packed bf16 pairs
+      // 16 columns of S and of dP per step; the loads of step c + 1 are in flight while step c is computed
+      const uint32_t ts = tmem_s + lane_off + cg * 64, td = tmem_dp + lane_off + cg * 64;
+      uint32_t rs[2][16], rd[2][16];
+      tmem_ld_32x16(ts, rs[0]);
+      tmem_ld_32x16(td, rd[0]);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rd[32];
-        tmem_ld_32x32(tmem_s + lane_off + cg * 64 + c * 32, rs);
-        tmem_ld_32x32(tmem_dp + lane_off + cg * 64 + c * 32, rd);
+      for (int c = 0; c < 4; ++c) {
         tmem_ld_wait();
+        if (c + 1 < 4) {
+          tmem_ld_32x16(ts + (c + 1) * 16, rs[(c + 1) & 1]);
+          tmem_ld_32x16(td + (c + 1) * 16, rd[(c + 1) & 1]);
+        }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p0 = bt_ex2(fmaf(__uint_as_float(rs[2 * i]), sl2, -lse2));
-          float p1 = bt_ex2(fmaf(__uint_as_float(rs[2 * i + 1]), sl2, -lse2));
+        for (int i = 0; i < 8; ++i) {
+          float p0 = bt_ex2(fmaf(__uint_as_float(rs[c & 1][2 * i]), sl2, -lse2));
+          float p1 = bt_ex2(fmaf(__uint_as_float(rs[c & 1][2 * i + 1]), sl2, -lse2));
           if (need_mask) {
-            const int key = kbase + c * 32 + 2 * i;
+            const int key = kbase + c * 16 + 2 * i;
             if (key > key_lim) p0 = 0.f;
             if (key + 1 > key_lim) p1 = 0.f;
           }
-          const float d0 = p0 * (__uint_as_float(rd[2 * i]) - dlt);
-          const float d1 = p1 * (__uint_as_float(rd[2 * i + 1]) - dlt);
-          pp[c * 16 + i] = pack_bf16x2(p0, p1);
-          ds[c * 16 + i] = pack_bf16x2(d0, d1);
+          const float d0 = p0 * (__uint_as_float(rd[c & 1][2 * i]) - dlt);
+          const float d1 = p1 * (__uint_as_float(rd[c & 1][2 * i + 1]) - dlt);
+          pp[c * 8 + i] = pack_bf16x2(p0, p1);
+          ds[c * 8 + i] = pack_bf16x2(d0, d1);
         }
       }
       // S and dP are in registers: the next pair of products may overwrite them

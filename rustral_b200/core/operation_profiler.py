@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import enum
 import json
+import os
 import time
 from dataclasses import dataclass, field
 
@@ -93,6 +94,8 @@ class OperationGuard:
             dev = DeviceType.CUDA if (self.p.use_cuda_events and torch.cuda.is_available()) else DeviceType.CPU
         self.device = dev
         if dev is DeviceType.CUDA:
+            if self.p.nvtx:
+                torch.cuda.nvtx.range_push(self.name)      # shows up as a named range in Nsight timelines
             self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             self._ev[0].record()
         else:
@@ -102,6 +105,8 @@ class OperationGuard:
     def __exit__(self, *exc):
         if self.device is DeviceType.CUDA:
             self._ev[1].record()
+            if self.p.nvtx:
+                torch.cuda.nvtx.range_pop()
             self.p._pending.append((self.name, self.bucket, self._ev))
             if len(self.p._pending) >= self.p.max_pending:
                 self.p.resolve()
@@ -111,9 +116,12 @@ class OperationGuard:
 
 
 class OperationProfiler:
-    def __init__(self, enabled: bool = True, use_cuda_events: bool = True, max_pending: int = 4096):
+    def __init__(self, enabled: bool = True, use_cuda_events: bool = True, max_pending: int = 4096,
+                 nvtx: bool | None = None):
         self.enabled = enabled
         self.use_cuda_events = use_cuda_events
+        # NVTX ranges around CUDA-timed operations (RUSTRAL_PROFILE_NVTX=1 turns them on by default)
+        self.nvtx = (os.environ.get("RUSTRAL_PROFILE_NVTX", "0") == "1") if nvtx is None else nvtx
         self.max_pending = max_pending
         self.stats: dict = {}
         self._pending: list = []

@@ -292,3 +292,42 @@ class StateSync:
 
     def is_complete(self) -> bool:
         return len(self.synced) >= self.target_world_size and self.can_proceed()
+
+
+class StepWatchdog:
+    """Host-side wall-clock limit per training step.
+
+    `with watchdog.step():` arms a timer; if the block has not finished after `limit_s` the watchdog records the
+    overrun and calls `on_timeout` from its own thread (e.g. to mark the rank as suspected in the health monitor or to
+    abort the process group).  Leaving the block after an overrun raises `CommunicationError`, which is what
+    `ElasticTrainer` treats as recoverable.  Device-side waits are bounded on their own and report through the
+    status word; this is the host's counterpart for a step that stalls anywhere else (a collective, a data loader)."""
+
+    def __init__(self, limit_s: float, on_timeout=None):
+        self.limit_s, self.on_timeout = limit_s, on_timeout
+        self.overruns = 0
+        self._timer = None
+        self._fired = False
+
+    def _fire(self):
+        self._fired = True
+        self.overruns += 1
+        if self.on_timeout is not None:
+            self.on_timeout()
+
+    def step(self):
+        return self
+
+    def __enter__(self):
+        import threading
+        self._fired = False
+        self._timer = threading.Timer(self.limit_s, self._fire)
+        self._timer.daemon = True
+        self._timer.start()
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        self._timer.cancel()
+        if self._fired and exc_type is None:
+            raise CommunicationError(f"step exceeded its wall-clock limit of {self.limit_s} s")
+        return False

@@ -27,6 +27,8 @@ N.optional_sig("rb_signal_all", [N.c_void_p, N.c_int, N.c_int, N.c_int, C.c_uint
 N.optional_sig("rb_wait_all", [N.c_void_p, N.c_int, N.c_int, C.c_uint, N.c_int, N.c_void_p])
 
 SIGNAL_PAD_BYTES = 4096
+GUARD_BYTES = 256                      # canary region before and after every symmetric buffer
+_CANARY = 0x5AA5C33C
 
 
 class _RawCudaBuffer:
@@ -52,12 +54,21 @@ class SymmetricBuffer:
         self.rank = dist.get_rank(group)
         self.nbytes = nbytes
         self.device = torch.device(device)
-        ptr = lib.rb_symm_alloc(nbytes)
-        if not ptr:
+        # the usable range sits between two guard regions filled with a canary pattern: a kernel of any rank that
+        # writes past either end of a buffer is caught by `check_canaries()` on the host instead of silently
+        # corrupting a neighbouring allocation
+        padded = (nbytes + 15) // 16 * 16
+        base = lib.rb_symm_alloc(padded + 2 * GUARD_BYTES)
+        if not base:
             raise N.NativeError(f"symmetric allocation of {nbytes} bytes failed")
-        self.local_ptr = int(ptr)
+        self._base_ptr = int(base)
+        self.local_ptr = self._base_ptr + GUARD_BYTES
+        whole = tensor_from_ptr(self._base_ptr, padded + 2 * GUARD_BYTES, self.device)
+        self._guards = (whole[:GUARD_BYTES].view(torch.int32), whole[GUARD_BYTES + padded:].view(torch.int32))
+        for g in self._guards:
+            g.fill_(_CANARY)
         handle = C.create_string_buffer(64)
-        N.check(lib.rb_ipc_export(self.local_ptr, handle), "rb_ipc_export")
+        N.check(lib.rb_ipc_export(self._base_ptr, handle), "rb_ipc_export")
         handles = [None] * self.world
         dist.all_gather_object(handles, bytes(handle.raw), group=group)
         self.peer_ptrs = []
@@ -69,7 +80,7 @@ class SymmetricBuffer:
             p = lib.rb_ipc_import(C.create_string_buffer(h, 64))
             if not p:
                 raise N.NativeError(f"rank {self.rank}: cannot map the symmetric buffer of rank {r} (no peer access?)")
-            self.peer_ptrs.append(int(p))
+            self.peer_ptrs.append(int(p) + GUARD_BYTES)
             self._imported.append(int(p))
         self.local = tensor_from_ptr(self.local_ptr, nbytes, self.device)
         self.ptrs_dev = torch.tensor(self.peer_ptrs, dtype=torch.int64, device=self.device)
@@ -79,6 +90,10 @@ class SymmetricBuffer:
         t = self.local[byte_offset:]
         t = t.view(dtype)
         return t if numel is None else t[:numel]
+
+    def check_canaries(self) -> bool:
+        """True when the guard words before and after this rank's buffer are intact (synchronises the device)."""
+        return all(bool((g == _CANARY).all()) for g in self._guards)
 
     def close(self) -> None:
         """Unmaps the peers and frees the local allocation.  Collective: call on every rank, with no kernel in flight."""
@@ -91,8 +106,9 @@ class SymmetricBuffer:
         dist.barrier(group=self.group)
         if self.local_ptr:
             self.local = None
-            lib.rb_symm_free(self.local_ptr)
-            self.local_ptr = 0
+            self._guards = ()
+            lib.rb_symm_free(self._base_ptr)
+            self.local_ptr = self._base_ptr = 0
 
 
 class SignalPad(SymmetricBuffer):

@@ -210,6 +210,8 @@ def main():
     else:
         out["bench"] = bench(tp, rank, world, dev, a.iters)
     torch.cuda.synchronize()
+    bufs = [tp.pad] + [b for ws in tp._ws.values() for b in (getattr(ws, "shard", None) or getattr(ws, "slots", None) or [ws.buf])]
+    out["canaries_ok"] = all(b.check_canaries() for b in bufs)
     out["status"] = _native.read_status()[0]
     st = torch.tensor([out["status"]], device=dev)
     dist.all_reduce(st, op=dist.ReduceOp.MAX)

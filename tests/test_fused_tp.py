@@ -25,7 +25,7 @@ def _run(nproc, mode, port):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_fused_tp_two_gpus():
     out = _run(2, "check", 29641)
-    assert out["status_max"] == 0
+    assert out["status_max"] == 0 and out["canaries_ok"]
     assert out["ag_gemm_err"] < 1e-2 and out["ag_gemm_repeatable"]
     assert out["gemm_rs_err"] < 1e-2 and out["gemm_rs_repeatable"]
     for name, err in out["layer_err"].items():

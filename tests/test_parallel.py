@@ -354,3 +354,23 @@ def test_pipeline_comm_and_nccl_facade_on_cpu():
         assert NcclProcessGroup().world_size == 1
     finally:
         dist.destroy_process_group()
+
+
+def test_step_watchdog_and_profiler_nvtx_flag():
+    import time
+    from rustral_b200.core.operation_profiler import OperationProfiler
+    from rustral_b200.parallel.fault_tolerance import StepWatchdog
+    from rustral_b200.parallel.process_group import CommunicationError
+    fired = []
+    wd = StepWatchdog(0.05, on_timeout=lambda: fired.append(1))
+    with wd.step():
+        pass                                  # fast step: nothing happens
+    assert wd.overruns == 0
+    with pytest.raises(CommunicationError):
+        with wd.step():
+            time.sleep(0.2)
+    assert wd.overruns == 1 and fired == [1]
+    prof = OperationProfiler(enabled=True, use_cuda_events=False, nvtx=True)
+    with prof.guard("op"):
+        pass
+    assert prof.stats["op"].count == 1 and prof.nvtx
