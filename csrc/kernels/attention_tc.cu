@@ -197,33 +197,30 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int key_lim = p.causal ? min(p.seq_k - 1, q_idx + shift) : p.seq_k - 1;     // last visible key
       // Only tiles that cross the causal diagonal or the end of the keys need per-element masking.
       const bool need_mask = (k0 + kTcTile - 1 > key_lim);
-      // pass 1: row maximum.  16 columns per step; the load of step c + 1 is in flight while step c is reduced.
+      // pass 1: row maximum
       float mx = m_run;
-      {
-        uint32_t r[2][16];
-        tmem_ld_32x16(tmem_s + lane_off, r[0]);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_off + c * 32, r);
+        tmem_ld_wait();
         float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          tmem_ld_wait();
-          if (c + 1 < 8) tmem_ld_32x16(tmem_s + lane_off + (c + 1) * 16, r[(c + 1) & 1]);
-          if (need_mask) {
+          for (int i = 0; i < 32; i += 4) {
+            const int kb = k0 + c * 32 + i;
+            m0 = fmaxf(m0, kb <= key_lim ? __uint_as_float(r[i]) : -INFINITY);
+            m1 = fmaxf(m1, kb + 1 <= key_lim ? __uint_as_float(r[i + 1]) : -INFINITY);
+            m2 = fmaxf(m2, kb + 2 <= key_lim ? __uint_as_float(r[i + 2]) : -INFINITY);
+            m3 = fmaxf(m3, kb + 3 <= key_lim ? __uint_as_float(r[i + 3]) : -INFINITY);
+          }
+        } else {
 #pragma unroll
-            for (int i = 0; i < 16; i += 4) {
-              const int kb = k0 + c * 16 + i;
-              m0 = fmaxf(m0, kb <= key_lim ? __uint_as_float(r[c & 1][i]) : -INFINITY);
-              m1 = fmaxf(m1, kb + 1 <= key_lim ? __uint_as_float(r[c & 1][i + 1]) : -INFINITY);
-              m2 = fmaxf(m2, kb + 2 <= key_lim ? __uint_as_float(r[c & 1][i + 2]) : -INFINITY);
-              m3 = fmaxf(m3, kb + 3 <= key_lim ? __uint_as_float(r[c & 1][i + 3]) : -INFINITY);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; i += 4) {
-              m0 = fmaxf(m0, __uint_as_float(r[c & 1][i]));
-              m1 = fmaxf(m1, __uint_as_float(r[c & 1][i + 1]));
-              m2 = fmaxf(m2, __uint_as_float(r[c & 1][i + 2]));
-              m3 = fmaxf(m3, __uint_as_float(r[c & 1][i + 3]));
-            }
+          for (int i = 0; i < 32; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(r[i]));
+            m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(r[i + 2]));
+            m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
           }
         }
         mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
@@ -232,40 +229,44 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const float alpha = ex2_approx((m_run - m_safe) * sl2);
       const float msc = m_safe * sl2;
       m_run = mx;
+      // P may be overwritten once the previous PV has read it
+      if (!mbar_wait(bar_pempty, (j & 1) ^ 1, abort_flag, status, 29)) { ok = false; break; }
       // pass 2: probabilities -> shared memory (swizzled, K-major A operand of the PV product)
       float rs0 = 0.f, rs1 = 0.f;
-      {
-        uint32_t r[2][16];
-        tmem_ld_32x16(tmem_s + lane_off, r[0]);
-        // P may be overwritten once the previous PV has read it
-        if (!mbar_wait(bar_pempty, (j & 1) ^ 1, abort_flag, status, 29)) { ok = false; break; }
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_off + c * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          tmem_ld_wait();
-          if (c + 1 < 8) tmem_ld_32x16(tmem_s + lane_off + (c + 1) * 16, r[(c + 1) & 1]);
-          uint32_t packed[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float p0 = ex2_approx(fmaf(__uint_as_float(r[c & 1][2 * i]), sl2, -msc));
-            float p1 = ex2_approx(fmaf(__uint_as_float(r[c & 1][2 * i + 1]), sl2, -msc));
-            if (need_mask) {
-              const int key = k0 + c * 16 + 2 * i;
-              if (key > key_lim) p0 = 0.f;
-              if (key + 1 > key_lim) p1 = 0.f;
-            }
+          for (int i = 0; i < 16; ++i) {
+            const int key = k0 + c * 32 + 2 * i;
+            const float p0 = (key <= key_lim) ? ex2_approx(fmaf(__uint_as_float(r[2 * i]), sl2, -msc)) : 0.f;
+            const float p1 = (key + 1 <= key_lim) ? ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), sl2, -msc)) : 0.f;
             rs0 += p0;
             rs1 += p1;
             packed[i] = pack_bf16x2(p0, p1);
           }
-          // 16 keys = 2 chunks of 16 bytes; key half (c >> 2), chunk index inside the 128-byte row ((c & 3) * 2 + q)
+        } else {
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const int chunk = (c & 3) * 2 + q;
-            const uint32_t addr = sP + (c >> 2) * L::kHalf + row * 128 + ((chunk ^ (row & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * q]), "r"(packed[4 * q + 1]),
-                         "r"(packed[4 * q + 2]), "r"(packed[4 * q + 3])
-                         : "memory");
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), sl2, -msc));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), sl2, -msc));
+            rs0 += p0;
+            rs1 += p1;
+            packed[i] = pack_bf16x2(p0, p1);
           }
+        }
+        // 32 keys = 4 chunks of 16 bytes; key half (c >> 1), chunk index inside the 128-byte row ((c & 1) * 4 + q)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = (c & 1) * 4 + q;
+          const uint32_t addr = sP + (c >> 1) * L::kHalf + row * 128 + ((chunk ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * q]), "r"(packed[4 * q + 1]),
+                       "r"(packed[4 * q + 2]), "r"(packed[4 * q + 3])
+                       : "memory");
         }
       }
       const float rs = rs0 + rs1;
@@ -281,16 +282,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // fold this tile's PV into the running output
       if (!mbar_wait(bar_pvfull, j & 1, abort_flag, status, 30)) { ok = false; break; }
       tc_fence_after();
-      {
-        uint32_t r[2][16];
-        tmem_ld_32x16(tmem_pv + lane_off, r[0]);
 #pragma unroll
-        for (int c = 0; c < D / 16; ++c) {
-          tmem_ld_wait();
-          if (c + 1 < D / 16) tmem_ld_32x16(tmem_pv + lane_off + (c + 1) * 16, r[(c + 1) & 1]);
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_pv + lane_off + c * 32, r);
+        tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) o_acc[c * 16 + i] = fmaf(o_acc[c * 16 + i], alpha, __uint_as_float(r[c & 1][i]));
-        }
+        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
       }
       tc_fence_before();
       __syncwarp();
