@@ -103,7 +103,8 @@ def main(argv=None):
     model = ParallelDecoderLM(cfg, dev, tp_pg=tp_pg, fused_tp=fused_tp, ep=ep_ctx,
                               first_layer=pp_idx * per_stage, last_layer=(pp_idx + 1) * per_stage if pp_idx < a.pp - 1 else cfg.n_layer,
                               has_embed=pp_idx == 0, has_head=pp_idx == a.pp - 1, seed=1)
-    opt = MixedPrecisionAdamW(model, lr=a.lr)
+    # expert parallel: ZeRO-1 over the data-parallel ranks for the dense (replicated) parameters
+    opt = MixedPrecisionAdamW(model, lr=a.lr, use_zero1=a.ep > 1)
     dp = a.ep                                                  # data-parallel replicas (expert-parallel ranks see different data)
     local_batch = a.global_batch // dp
     if local_batch % a.micro_batch:
@@ -181,7 +182,8 @@ def main(argv=None):
             "config": {"model": a.config, "layers": cfg.n_layer, "d_model": cfg.d_model, "seq_len": S,
                        "global_batch": a.global_batch, "micro_batch": a.micro_batch,
                        "parallelism": f"tp{a.tp}-pp{a.pp}-ep{a.ep}", "fused": not a.unfused,
-                       "params_total": cfg.num_params(), "params_local": model.local_param_count()},
+                       "params_total": cfg.num_params(), "params_local": model.local_param_count(),
+                       "zero1_dense": a.ep > 1, "optimizer_state_bytes_local": opt.state_bytes()},
             "model_tflops_per_s_per_gpu": round(cfg.flops_per_token() * tokens / (ms_step / 1e3) / 1e12 / world, 1),
             "losses": [round(v, 4) for v in lt.tolist()], "device_status": int(status),
             "data": "synthetic (uniform random token ids), random-init weights"}))

@@ -280,16 +280,34 @@ class ParallelDecoderLM:
 
 class MixedPrecisionAdamW:
     """AdamW on fp32 master weights with bf16 working copies (one fused kernel per tensor), gradients accumulated
-    in fp32 across micro-batches."""
+    in fp32 across micro-batches.
+
+    `zero1_group`: ZeRO-1 over that data-parallel group for the replicated (non-expert) parameters, in the reference's
+    form (crates/distributed/src/zero.rs:72-123): every such parameter has one owner rank (round-robin in name
+    order); only the owner keeps its fp32 master copy and Adam moments and runs the update, then broadcasts the new
+    bf16 values.  Expert parameters are already unique to their rank and are always updated locally."""
 
     def __init__(self, model: ParallelDecoderLM, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
-                 weight_decay: float = 0.1):
+                 weight_decay: float = 0.1, zero1_group=None, use_zero1: bool = False):
         self.model, self.lr, self.betas, self.eps, self.wd = model, lr, betas, eps, weight_decay
-        self.master = {n: p.detach().float() for n, p in model.params.items()}
+        self.zero1 = use_zero1
+        self.zero1_group = zero1_group
+        self.owner: dict = {}
+        if use_zero1:
+            world, rank = dist.get_world_size(zero1_group), dist.get_rank(zero1_group)
+            dense = [n for n in sorted(model.params) if n not in model.expert_names]
+            self.owner = {n: i % world for i, n in enumerate(dense)}
+            self._rank = rank
+        owned = lambda n: (not use_zero1) or n in model.expert_names or self.owner[n] == self._rank
+        self.master = {n: p.detach().float() for n, p in model.params.items() if owned(n)}
         self.m = {n: torch.zeros_like(v) for n, v in self.master.items()}
         self.v = {n: torch.zeros_like(v) for n, v in self.master.items()}
-        self.main_grads = {n: torch.zeros_like(v) for n, v in self.master.items()}
+        self.main_grads = {n: torch.zeros(p.shape, dtype=torch.float32, device=p.device) for n, p in model.params.items()}
         self.step_count = 0
+
+    def state_bytes(self) -> int:
+        """Bytes of optimizer state held by this rank (master weights + both moments)."""
+        return sum(3 * v.numel() * 4 for v in self.master.values())
 
     def accumulate(self) -> None:
         """Fold the bf16 `.grad` of the micro-batch just finished into the fp32 accumulators."""
@@ -302,8 +320,15 @@ class MixedPrecisionAdamW:
         self.step_count += 1
         self.model.sync_grads(self.main_grads)
         for n, p in self.model.params.items():
-            decay = self.wd if p.dim() >= 2 else 0.0
-            ops.adam_step(self.master[n].view(-1), self.m[n].view(-1), self.v[n].view(-1), self.main_grads[n].view(-1),
-                                lr=self.lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps, weight_decay=decay,
-                                step=self.step_count, grad_scale=grad_scale, p_lowp=p.data.view(-1))
+            if n in self.master:
+                decay = self.wd if p.dim() >= 2 else 0.0
+                ops.adam_step(self.master[n].view(-1), self.m[n].view(-1), self.v[n].view(-1), self.main_grads[n].view(-1),
+                              lr=self.lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps, weight_decay=decay,
+                              step=self.step_count, grad_scale=grad_scale, p_lowp=p.data.view(-1))
             self.main_grads[n].zero_()
+        if self.zero1:
+            for n in sorted(self.owner):                      # the owner publishes the updated working copy
+                src = self.owner[n]
+                if self.zero1_group is not None:
+                    src = dist.get_global_rank(self.zero1_group, src)
+                dist.broadcast(self.model.params[n].data, src=src, group=self.zero1_group)
