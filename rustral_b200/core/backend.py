@@ -1,7 +1,7 @@
 """Backends: the CPU reference backend and the B200 backend (crates/core/src/backend.rs:5-205).
 
 A backend is a device plus a default dtype, a capability record and the op tables.  There are exactly two:
-``CpuBackend`` (fp32, the numerical oracle, BASELINE config 1) and ``B200Backend`` (bf16 parameters and
+``CpuBackend`` (fp32, the numerical oracle) and ``B200Backend`` (bf16 parameters and
 activations with fp32 accumulation, served only by the sm_100a kernels).
 """
 from __future__ import annotations

@@ -71,12 +71,12 @@ class GPTConfig:
 
 
 PRESETS = {
-    # BASELINE config 1: tiny LM for the CPU reference backend
+    # tiny LM for the CPU reference backend
     "tiny-lm": dict(vocab_size=1024, seq_len=64, n_layer=2, n_head=4, d_model=128, ffn_dim=512, arch="gpt2",
                     tie_embeddings=False, vocab_multiple=1),
-    # BASELINE config 2
+    # GPT-2 small: the headline training benchmark
     "gpt2-small": dict(vocab_size=50257, seq_len=1024, n_layer=12, n_head=12, d_model=768, ffn_dim=3072, arch="gpt2"),
-    # BASELINE config 3 / 5
+    # Llama-style 8B: tensor / pipeline parallel training and serving
     "llama-8b": dict(vocab_size=128256, seq_len=4096, n_layer=32, n_head=32, n_kv_head=8, d_model=4096, ffn_dim=14336,
                      arch="llama", rope_theta=500000.0),
     # small shapes for tests

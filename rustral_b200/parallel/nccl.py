@@ -3,7 +3,7 @@ NcclCompressedCommunicator).
 
 The reference declares the NCCL C API itself and hands it host pointers on a null stream (nccl.rs:240-249), which a
 real NCCL rejects.  Here the communicator is torch.distributed's NCCL backend (device tensors, the current stream),
-and it is the BASELINE transport: the fused peer-memory kernels of this package are measured against it.  On CPU
+and it is the baseline transport: the fused peer-memory kernels of this package are measured against it.  On CPU
 tensors (gloo) the same calls work, which is how the host-side logic is tested.
 """
 from __future__ import annotations
