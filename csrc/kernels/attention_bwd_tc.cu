@@ -7,7 +7,7 @@
 // Per (query tile, key tile) pair, in both modes:
 //   S  = Q K^T, dP = dO V^T        tcgen05.mma (SS) into two 128-column TMEM accumulators
 //   P  = exp2(S * scale * log2e - lse * log2e), dS = P * (dP - delta)
-//                                   eight warps; a thread owns one query row (its TMEM lane) and 64 of the 128 keys;
+//                                   sixteen warps; a thread owns one query row (its TMEM lane) and 32 of the 128 keys;
 //                                   P and dS go to shared memory as bf16 in the 128-byte-swizzled layout
 //   dV / dK / dQ                    tcgen05.mma (SS) reading P and dS either K-major (dQ) or transposed through an
 //                                   MN-major descriptor (dV, dK), and dO / Q / K MN-major straight from their row layout
@@ -15,7 +15,8 @@
 // shared memory allows.  The S / dP products of step t+1 are issued before the dV / dK / dQ products of step t, so the
 // tensor cores work on them while the warps are still in step t's exponentials.
 //
-// Roles: warps 0-7 softmax / dS / epilogue, warp 8 TMA producer, warp 9 MMA issuer.  Every wait is bounded.
+// Roles: warps 0-15 softmax / dS / epilogue (four lane quarters x four 32-key column groups), warp 16 TMA producer,
+// warp 17 MMA issuer.  Every wait is bounded.
 // Same semantics as the mma.sync backward in attention.cu (causal alignment to the end of the keys, GQA).
 #include "attention.h"
 
@@ -23,8 +24,11 @@
 
 namespace rb {
 
-constexpr int kBtThreads = 320;
 constexpr int kBtTile = 128;
+constexpr int kBtColGroups = 2;                    // compute warps = 4 lane quarters x this many column groups
+constexpr int kBtComputeWarps = 4 * kBtColGroups;
+constexpr int kBtThreads = 32 * (kBtComputeWarps + 2);
+constexpr int kBtColsPerGroup = kBtTile / kBtColGroups;   // keys per compute thread and step
 constexpr float kBtLog2e = 1.4426950408889634f;
 constexpr int MODE_DKV = 0;
 constexpr int MODE_DQ = 1;
@@ -35,7 +39,7 @@ struct BtParams {
   __nv_bfloat16* out0;      // MODE_DKV: dK;  MODE_DQ: dQ
   __nv_bfloat16* out1;      // MODE_DKV: dV
   long long o0_bs, o0_rs, o0_hs, o1_bs, o1_rs, o1_hs;
-  int seq_q, seq_k, heads, kv_heads, causal;
+  int seq_q, seq_k, heads, kv_heads, causal, batch;
   float scale;
 };
 
@@ -51,13 +55,15 @@ struct BtSmem {
   static constexpr int kTileBytes = (D / 64) * kHalf;          // one [128, D] operand tile
   // streamed pair double buffered when it fits: always for head dim 64, for head dim 128 only in MODE_DQ (no P buffer)
   static constexpr int kStages = (D == 64 || MODE == MODE_DQ) ? 2 : 1;
+  // the owned ("resident") pair of the NEXT work item is prefetched while the current one is processed when it fits
+  static constexpr int kResStages = (D == 64) ? 2 : 1;
   static constexpr int kRes0 = 0;                              // resident pair: (K, V) in MODE_DKV, (Q, dO) in MODE_DQ
-  static constexpr int kRes1 = kRes0 + kTileBytes;
-  static constexpr int kStream = kRes1 + kTileBytes;           // per stage: two tiles
+  static constexpr int kRes1 = kRes0 + kTileBytes;             // (per resident stage: two tiles)
+  static constexpr int kStream = kResStages * 2 * kTileBytes;  // per stage: two tiles
   static constexpr int kDs = kStream + kStages * 2 * kTileBytes;
   static constexpr int kP = kDs + 2 * kHalf;
   static constexpr int kBar = kP + (MODE == MODE_DKV ? 2 * kHalf : 0);
-  static constexpr int kNumBars = 12;
+  static constexpr int kNumBars = 16;
   static constexpr int kTotal = kBar + kNumBars * 8 + 16;
 };
 
@@ -107,67 +113,81 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t sbase = smem_u32(smem);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
   const uint32_t b0 = smem_u32(bars);
-  const uint32_t bar_res = b0, bar_tfull = b0 + 8, bar_tempty = b0 + 24, bar_sdp_full = b0 + 40, bar_sdp_empty = b0 + 48,
-                 bar_p_full = b0 + 56, bar_p_empty = b0 + 64, bar_acc_full = b0 + 72;
+  const uint32_t bar_tfull = b0 + 8, bar_tempty = b0 + 24, bar_sdp_full = b0 + 40, bar_sdp_empty = b0 + 48,
+                 bar_p_full = b0 + 56, bar_p_empty = b0 + 64, bar_acc_full = b0 + 72, bar_res = b0 + 104;
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
+  const uint32_t bar_res_empty = b0 + 80, bar_acc_empty = b0 + 96;      // bar_res / bar_res_empty: two slots each
+  constexpr int RS = L::kResStages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int blk = gridDim.x - 1 - blockIdx.x;
-  const int b = blockIdx.z;
   const int group = p.heads / p.kv_heads;
   const int shift = p.seq_k - p.seq_q;
   const int n_q_tiles = (p.seq_q + kBtTile - 1) / kBtTile;
   const int n_k_tiles = (p.seq_k + kBtTile - 1) / kBtTile;
 
-  // The walk: MODE_DKV over (head of the group, query tile >= first), MODE_DQ over key tiles <= last.
-  int own0, walk_first, walk_count, n_it, head_q0, head_k;
-  if (MODE == MODE_DKV) {
-    own0 = blk * kBtTile;                       // first key of the owned tile
-    head_k = blockIdx.y;
-    head_q0 = head_k * group;
-    walk_first = 0;
-    if (p.causal && own0 - shift > 0) walk_first = (own0 - shift) / kBtTile;
-    walk_count = n_q_tiles - walk_first;
-    if (walk_count < 0) walk_count = 0;
-    n_it = walk_count * group;
-  } else {
-    own0 = blk * kBtTile;                       // first query of the owned tile
-    head_q0 = blockIdx.y;
-    head_k = head_q0 / group;
-    walk_first = 0;
-    walk_count = n_k_tiles;
-    if (p.causal) {
-      const int lim = (own0 + kBtTile - 1 + shift) / kBtTile + 1;
-      if (lim < walk_count) walk_count = lim;
-    }
-    n_it = walk_count;
-  }
-  auto walk_decode = [&](int it, int& hq, int& q0, int& k0) {
+  // Work items: one owned tile of one (head, batch).  A CTA is persistent and takes items blockIdx.x, + gridDim.x, ...;
+  // items are numbered so that the long walks come first (MODE_DKV: early key tiles, MODE_DQ: late query tiles).
+  struct Work { int own0, walk_first, walk_count, n_it, head_q0, head_k, b; };
+  const int n_own = MODE == MODE_DKV ? n_k_tiles : n_q_tiles;
+  const int ny = MODE == MODE_DKV ? p.kv_heads : p.heads;
+  const int total_items = n_own * ny * p.batch;
+  auto get_work = [&](int item, Work& w) {
+    const int per_tile = ny * p.batch;
+    const int tw = item / per_tile;
+    const int yz = item - tw * per_tile;
+    const int y = yz % ny;
+    w.b = yz / ny;
+    const int blk = (MODE == MODE_DKV || !p.causal) ? tw : n_own - 1 - tw;
+    w.own0 = blk * kBtTile;
+    w.walk_first = 0;
     if (MODE == MODE_DKV) {
-      const int g = it / walk_count;
-      hq = head_q0 + g;
-      q0 = (walk_first + it - g * walk_count) * kBtTile;
-      k0 = own0;
+      w.head_k = y;
+      w.head_q0 = y * group;
+      if (p.causal && w.own0 - shift > 0) w.walk_first = (w.own0 - shift) / kBtTile;
+      w.walk_count = n_q_tiles - w.walk_first;
+      if (w.walk_count < 0) w.walk_count = 0;
+      w.n_it = w.walk_count * group;
     } else {
-      hq = head_q0;
-      q0 = own0;
+      w.head_q0 = y;
+      w.head_k = y / group;
+      w.walk_count = n_k_tiles;
+      if (p.causal) {
+        const int lim = (w.own0 + kBtTile - 1 + shift) / kBtTile + 1;
+        if (lim < w.walk_count) w.walk_count = lim;
+      }
+      w.n_it = w.walk_count;
+    }
+  };
+  auto walk_decode = [&](const Work& w, int it, int& hq, int& q0, int& k0) {
+    if (MODE == MODE_DKV) {
+      const int g = it / w.walk_count;
+      hq = w.head_q0 + g;
+      q0 = (w.walk_first + it - g * w.walk_count) * kBtTile;
+      k0 = w.own0;
+    } else {
+      hq = w.head_q0;
+      q0 = w.own0;
       k0 = it * kBtTile;
     }
   };
 
   constexpr uint32_t kTmemCols = 512;           // S [0,128)  dP [128,256)  accumulators from 256
   if (threadIdx.x == 0) {
-    mbar_init(bar_res, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_res + 8 * s, 1);
+      mbar_init(bar_res_empty + 8 * s, 1);
+    }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull + 8 * s, 1);
       mbar_init(bar_tempty + 8 * s, 1);
     }
     mbar_init(bar_sdp_full, 1);
-    mbar_init(bar_sdp_empty, 8);
-    mbar_init(bar_p_full, 8);
+    mbar_init(bar_sdp_empty, kBtComputeWarps);
+    mbar_init(bar_p_full, kBtComputeWarps);
     mbar_init(bar_p_empty, 1);
     mbar_init(bar_acc_full, 1);
+    mbar_init(bar_acc_empty, kBtComputeWarps);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmQ);
@@ -175,7 +195,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmdO);
   }
-  if (warp == 9) {
+  if (warp == kBtComputeWarps + 1) {
     tmem_alloc(smem_u32(tmem_ptr_smem), kTmemCols);
     tmem_relinquish();
   }
@@ -188,53 +208,67 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t sRes0 = sbase + L::kRes0, sRes1 = sbase + L::kRes1, sStream = sbase + L::kStream;
   const uint32_t sDs = sbase + L::kDs, sP = sbase + L::kP;
 
-  if (warp == 8) {
+  // Running counters: `wi` counts this CTA's work items, `git` its steps over all items, `ai` its items that have at
+  // least one step; the barrier phases follow them, so every role derives the same parities independently.
+  if (warp == kBtComputeWarps) {
     if (lane == 0) {
       // ---------------------------------------------------------------- TMA producer
-      mbar_arrive_expect_tx(bar_res, 2 * L::kTileBytes);
-#pragma unroll
-      for (int hf = 0; hf < D / 64; ++hf) {
-        if (MODE == MODE_DKV) {
-          tma_load_4d(sRes0 + hf * L::kHalf, &tmK, hf * 64, head_k, own0, b, bar_res);
-          tma_load_4d(sRes1 + hf * L::kHalf, &tmV, hf * 64, head_k, own0, b, bar_res);
-        } else {
-          tma_load_4d(sRes0 + hf * L::kHalf, &tmQ, hf * 64, head_q0, own0, b, bar_res);
-          tma_load_4d(sRes1 + hf * L::kHalf, &tmdO, hf * 64, head_q0, own0, b, bar_res);
-        }
-      }
-      for (int it = 0; it < n_it; ++it) {
-        const int s = it % STAGES;
-        if (!mbar_wait(bar_tempty + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, status, 41)) break;
-        int hq, q0, k0;
-        walk_decode(it, hq, q0, k0);
-        mbar_arrive_expect_tx(bar_tfull + 8 * s, 2 * L::kTileBytes);
-        const uint32_t d0 = sStream + s * 2 * L::kTileBytes, d1 = d0 + L::kTileBytes;
+      uint32_t git = 0, wi = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++wi) {
+        Work w;
+        get_work(item, w);
+        // the resident pair is free once the previous item's products have all been issued and completed
+        const uint32_t rsl = wi % RS;
+        if (!mbar_wait(bar_res_empty + 8 * rsl, ((wi / RS) & 1) ^ 1, abort_flag, status, 40)) break;
+        const uint32_t rfull = bar_res + 8 * rsl;
+        const uint32_t r0 = sRes0 + rsl * 2 * L::kTileBytes, r1 = sRes1 + rsl * 2 * L::kTileBytes;
+        mbar_arrive_expect_tx(rfull, 2 * L::kTileBytes);
 #pragma unroll
         for (int hf = 0; hf < D / 64; ++hf) {
           if (MODE == MODE_DKV) {
-            tma_load_4d(d0 + hf * L::kHalf, &tmQ, hf * 64, hq, q0, b, bar_tfull + 8 * s);
-            tma_load_4d(d1 + hf * L::kHalf, &tmdO, hf * 64, hq, q0, b, bar_tfull + 8 * s);
+            tma_load_4d(r0 + hf * L::kHalf, &tmK, hf * 64, w.head_k, w.own0, w.b, rfull);
+            tma_load_4d(r1 + hf * L::kHalf, &tmV, hf * 64, w.head_k, w.own0, w.b, rfull);
           } else {
-            tma_load_4d(d0 + hf * L::kHalf, &tmK, hf * 64, head_k, k0, b, bar_tfull + 8 * s);
-            tma_load_4d(d1 + hf * L::kHalf, &tmV, hf * 64, head_k, k0, b, bar_tfull + 8 * s);
+            tma_load_4d(r0 + hf * L::kHalf, &tmQ, hf * 64, w.head_q0, w.own0, w.b, rfull);
+            tma_load_4d(r1 + hf * L::kHalf, &tmdO, hf * 64, w.head_q0, w.own0, w.b, rfull);
+          }
+        }
+        for (int it = 0; it < w.n_it; ++it, ++git) {
+          const uint32_t s = git % STAGES;
+          if (!mbar_wait(bar_tempty + 8 * s, ((git / STAGES) & 1) ^ 1, abort_flag, status, 41)) { ok = false; break; }
+          int hq, q0, k0;
+          walk_decode(w, it, hq, q0, k0);
+          mbar_arrive_expect_tx(bar_tfull + 8 * s, 2 * L::kTileBytes);
+          const uint32_t d0 = sStream + s * 2 * L::kTileBytes, d1 = d0 + L::kTileBytes;
+#pragma unroll
+          for (int hf = 0; hf < D / 64; ++hf) {
+            if (MODE == MODE_DKV) {
+              tma_load_4d(d0 + hf * L::kHalf, &tmQ, hf * 64, hq, q0, w.b, bar_tfull + 8 * s);
+              tma_load_4d(d1 + hf * L::kHalf, &tmdO, hf * 64, hq, q0, w.b, bar_tfull + 8 * s);
+            } else {
+              tma_load_4d(d0 + hf * L::kHalf, &tmK, hf * 64, w.head_k, k0, w.b, bar_tfull + 8 * s);
+              tma_load_4d(d1 + hf * L::kHalf, &tmV, hf * 64, w.head_k, k0, w.b, bar_tfull + 8 * s);
+            }
           }
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kBtComputeWarps + 1) {
     if (lane == 0) {
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_t = umma_idesc_bf16(128, D, 1, 1);      // dV, dK: A (P / dS) and B (dO / Q) both MN-major
       constexpr uint32_t idesc_q = umma_idesc_bf16(128, D, 0, 1);      // dQ: A = dS K-major, B = K MN-major
-      auto issue_sdp = [&](int it) -> bool {
-        const int s = it % STAGES;
-        if (!mbar_wait(bar_tfull + 8 * s, (it / STAGES) & 1, abort_flag, status, 42)) return false;
-        if (!mbar_wait(bar_sdp_empty, (it & 1) ^ 1, abort_flag, status, 43)) return false;
+      uint32_t res_off = 0;                            // byte offset of the current item's resident pair
+      auto issue_sdp = [&](uint32_t g) -> bool {      // g: running step index
+        const uint32_t s = g % STAGES;
+        if (!mbar_wait(bar_tfull + 8 * s, (g / STAGES) & 1, abort_flag, status, 42)) return false;
+        if (!mbar_wait(bar_sdp_empty, (g & 1) ^ 1, abort_flag, status, 43)) return false;
         tc_fence_after();
         const uint32_t t0 = sStream + s * 2 * L::kTileBytes, t1 = t0 + L::kTileBytes;
-        const uint32_t aQ = MODE == MODE_DKV ? t0 : sRes0, adO = MODE == MODE_DKV ? t1 : sRes1;
-        const uint32_t bK = MODE == MODE_DKV ? sRes0 : t0, bV = MODE == MODE_DKV ? sRes1 : t1;
+        const uint32_t aQ = MODE == MODE_DKV ? t0 : sRes0 + res_off, adO = MODE == MODE_DKV ? t1 : sRes1 + res_off;
+        const uint32_t bK = MODE == MODE_DKV ? sRes0 + res_off : t0, bV = MODE == MODE_DKV ? sRes1 + res_off : t1;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (ks >> 2) * L::kHalf + (ks & 3) * 32;
@@ -250,178 +284,208 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         umma_commit(bar_sdp_full);
         return true;
       };
-      bool ok = mbar_wait(bar_res, 0, abort_flag, status, 44);
-      if (ok && n_it > 0) ok = issue_sdp(0);
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int s = it % STAGES;
-        // With two stages the next S / dP pair goes to the tensor cores ahead of this step's accumulations; with one
-        // stage its operands can only be loaded after those accumulations have released the buffer.
-        if (STAGES == 2 && it + 1 < n_it) {
-          ok = issue_sdp(it + 1);
-          if (!ok) break;
+      uint32_t git = 0, wi = 0, ai = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++wi) {
+        Work w;
+        get_work(item, w);
+        const uint32_t rsl = wi % RS;
+        res_off = rsl * 2 * L::kTileBytes;
+        if (!mbar_wait(bar_res + 8 * rsl, (wi / RS) & 1, abort_flag, status, 44)) break;
+        if (w.n_it > 0) {
+          // the warps have read out the previous item's accumulators
+          if (!mbar_wait(bar_acc_empty, (ai & 1) ^ 1, abort_flag, status, 49)) break;
+          ok = issue_sdp(git);
         }
-        if (!mbar_wait(bar_p_full, it & 1, abort_flag, status, 45)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t t0 = sStream + s * 2 * L::kTileBytes, t1 = t0 + L::kTileBytes;
-        if (MODE == MODE_DKV) {
-#pragma unroll
-          for (int ks = 0; ks < kBtTile / 16; ++ks) {      // dK += dS^T Q   (k = query rows)
-            umma_bf16_ss(tmem_acc0, umma_smem_desc_sw128(sDs + ks * 2048, L::kHalf, 1024),
-                         umma_smem_desc_sw128(t0 + ks * 2048, L::kHalf, 1024), idesc_t, (it != 0 || ks != 0) ? 1u : 0u);
+        for (int it = 0; it < w.n_it && ok; ++it, ++git) {
+          const uint32_t s = git % STAGES;
+          // With two stages the next S / dP pair goes to the tensor cores ahead of this step's accumulations; with one
+          // stage its operands can only be loaded after those accumulations have released the buffer.
+          if (STAGES == 2 && it + 1 < w.n_it) {
+            ok = issue_sdp(git + 1);
+            if (!ok) break;
           }
+          if (!mbar_wait(bar_p_full, git & 1, abort_flag, status, 45)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t t0 = sStream + s * 2 * L::kTileBytes, t1 = t0 + L::kTileBytes;
+          if (MODE == MODE_DKV) {
 #pragma unroll
-          for (int ks = 0; ks < kBtTile / 16; ++ks) {      // dV += P^T dO
-            umma_bf16_ss(tmem_acc1, umma_smem_desc_sw128(sP + ks * 2048, L::kHalf, 1024),
-                         umma_smem_desc_sw128(t1 + ks * 2048, L::kHalf, 1024), idesc_t, (it != 0 || ks != 0) ? 1u : 0u);
-          }
-        } else {
+            for (int ks = 0; ks < kBtTile / 16; ++ks) {      // dK += dS^T Q   (k = query rows)
+              umma_bf16_ss(tmem_acc0, umma_smem_desc_sw128(sDs + ks * 2048, L::kHalf, 1024),
+                           umma_smem_desc_sw128(t0 + ks * 2048, L::kHalf, 1024), idesc_t, (it != 0 || ks != 0) ? 1u : 0u);
+            }
 #pragma unroll
-          for (int ks = 0; ks < kBtTile / 16; ++ks) {      // dQ += dS K     (k = keys)
-            umma_bf16_ss(tmem_acc0, umma_smem_desc_sw128(sDs + (ks >> 2) * L::kHalf + (ks & 3) * 32, 16, 1024),
-                         umma_smem_desc_sw128(t0 + ks * 2048, L::kHalf, 1024), idesc_q, (it != 0 || ks != 0) ? 1u : 0u);
+            for (int ks = 0; ks < kBtTile / 16; ++ks) {      // dV += P^T dO
+              umma_bf16_ss(tmem_acc1, umma_smem_desc_sw128(sP + ks * 2048, L::kHalf, 1024),
+                           umma_smem_desc_sw128(t1 + ks * 2048, L::kHalf, 1024), idesc_t, (it != 0 || ks != 0) ? 1u : 0u);
+            }
+          } else {
+#pragma unroll
+            for (int ks = 0; ks < kBtTile / 16; ++ks) {      // dQ += dS K     (k = keys)
+              umma_bf16_ss(tmem_acc0, umma_smem_desc_sw128(sDs + (ks >> 2) * L::kHalf + (ks & 3) * 32, 16, 1024),
+                           umma_smem_desc_sw128(t0 + ks * 2048, L::kHalf, 1024), idesc_q, (it != 0 || ks != 0) ? 1u : 0u);
+            }
           }
+          umma_commit(bar_p_empty);
+          umma_commit(bar_tempty + 8 * s);
+          if (STAGES == 1 && it + 1 < w.n_it) ok = issue_sdp(git + 1);
         }
-        umma_commit(bar_p_empty);
-        umma_commit(bar_tempty + 8 * s);
-        if (STAGES == 1 && it + 1 < n_it) ok = issue_sdp(it + 1);
+        if (!ok) break;
+        if (w.n_it > 0) {
+          umma_commit(bar_acc_full);
+          ++ai;
+        }
+        umma_commit(bar_res_empty + 8 * rsl);     // every product that reads this resident pair has completed by then
       }
-      if (ok && n_it > 0) umma_commit(bar_acc_full);
     }
   } else {
-    // ------------------------------------------------------------------ P / dS and the final read-out
-    const int qtr = warp & 3, cg = warp >> 2;              // TMEM lane quarter, column half
+    // ------------------------------------------------------------------ P / dS and the read-out of every item
+    const int qtr = warp & 3, cg = warp >> 2;              // TMEM lane quarter, column group
+    constexpr int GC = kBtColsPerGroup;                    // columns (keys) per thread and step: 64 or 32
     const int row = qtr * 32 + lane;                       // query row inside the tile == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
     const float sl2 = p.scale * kBtLog2e;
     bool ok = true;
-    // log-sum-exp and delta of this thread's row are fetched one step ahead: the load latency hides behind a whole step
-    auto load_stats = [&](int it, float& lse2, float& dlt) {
-      int hq, q0, k0;
-      walk_decode(it, hq, q0, k0);
-      const int q_idx = q0 + row;
-      if (q_idx < p.seq_q) {
-        const long long stat = (static_cast<long long>(b) * p.heads + hq) * p.seq_q + q_idx;
-        lse2 = __ldg(p.lse + stat) * kBtLog2e;
-        dlt = __ldg(p.delta + stat);
-      } else {
-        lse2 = 0.f;
-        dlt = 0.f;
-      }
-    };
-    float lse2_next = 0.f, dlt_next = 0.f;
-    if (n_it > 0) load_stats(0, lse2_next, dlt_next);
-    for (int it = 0; it < n_it && ok; ++it) {
-      int hq, q0, k0;
-      walk_decode(it, hq, q0, k0);
-      const int q_idx = q0 + row;
-      const bool q_ok = q_idx < p.seq_q;
-      const float lse2 = lse2_next, dlt = dlt_next;
-      if (it + 1 < n_it) load_stats(it + 1, lse2_next, dlt_next);
-      const int key_lim = q_ok ? (p.causal ? min(p.seq_k - 1, q_idx + shift) : p.seq_k - 1) : -1;   // last visible key
-      const int kbase = k0 + cg * 64;
-      const bool need_mask = (kbase + 63 > key_lim);
-      if (!mbar_wait(bar_sdp_full, it & 1, abort_flag, status, 46)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t pp[32], ds[32];                             // 64 columns each, packed bf16 pairs
-      // 16 columns of S and of dP per step; the loads of step c + 1 are in flight while step c is computed
-      const uint32_t ts = tmem_s + lane_off + cg * 64, td = tmem_dp + lane_off + cg * 64;
-      uint32_t rs[2][16], rd[2][16];
-      tmem_ld_32x16(ts, rs[0]);
-      tmem_ld_32x16(td, rd[0]);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_wait();
-        if (c + 1 < 4) {
-          tmem_ld_32x16(ts + (c + 1) * 16, rs[(c + 1) & 1]);
-          tmem_ld_32x16(td + (c + 1) * 16, rd[(c + 1) & 1]);
+    uint32_t git = 0, ai = 0;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      Work w;
+      get_work(item, w);
+      const int b = w.b;
+      // log-sum-exp and delta of this thread's row are fetched one step ahead: the load latency hides behind a step
+      auto load_stats = [&](int it, float& lse2, float& dlt) {
+        int hq, q0, k0;
+        walk_decode(w, it, hq, q0, k0);
+        const int q_idx = q0 + row;
+        if (q_idx < p.seq_q) {
+          const long long stat = (static_cast<long long>(b) * p.heads + hq) * p.seq_q + q_idx;
+          lse2 = __ldg(p.lse + stat) * kBtLog2e;
+          dlt = __ldg(p.delta + stat);
+        } else {
+          lse2 = 0.f;
+          dlt = 0.f;
         }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float p0 = bt_ex2(fmaf(__uint_as_float(rs[c & 1][2 * i]), sl2, -lse2));
-          float p1 = bt_ex2(fmaf(__uint_as_float(rs[c & 1][2 * i + 1]), sl2, -lse2));
-          if (need_mask) {
-            const int key = kbase + c * 16 + 2 * i;
-            if (key > key_lim) p0 = 0.f;
-            if (key + 1 > key_lim) p1 = 0.f;
-          }
-          const float d0 = p0 * (__uint_as_float(rd[c & 1][2 * i]) - dlt);
-          const float d1 = p1 * (__uint_as_float(rd[c & 1][2 * i + 1]) - dlt);
-          pp[c * 8 + i] = pack_bf16x2(p0, p1);
-          ds[c * 8 + i] = pack_bf16x2(d0, d1);
-        }
-      }
-      // S and dP are in registers: the next pair of products may overwrite them
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_sdp_empty);
-      // the previous step's dV / dK / dQ products have finished reading P and dS
-      if (!mbar_wait(bar_p_empty, (it & 1) ^ 1, abort_flag, status, 47)) { ok = false; break; }
-      // this warp group's 64 keys are one 128-byte-swizzled atom: row `row`, eight 16-byte chunks
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        const uint32_t off = cg * L::kHalf + row * 128 + ((ch ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sDs + off), "r"(ds[4 * ch]), "r"(ds[4 * ch + 1]),
-                     "r"(ds[4 * ch + 2]), "r"(ds[4 * ch + 3])
-                     : "memory");
-        if (MODE == MODE_DKV) {
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + off), "r"(pp[4 * ch]), "r"(pp[4 * ch + 1]),
-                       "r"(pp[4 * ch + 2]), "r"(pp[4 * ch + 3])
-                       : "memory");
-        }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p_full);
-    }
-
-    // ---- read-out: TMEM lane = key (MODE_DKV) or query (MODE_DQ) row of the owned tile; this warp group's half of D
-    if (ok) {
-      bool have = n_it > 0;
-      if (have && !mbar_wait(bar_acc_full, 0, abort_flag, status, 48)) have = false, ok = false;
-      if (ok) {
+      };
+      float lse2_next = 0.f, dlt_next = 0.f;
+      if (w.n_it > 0) load_stats(0, lse2_next, dlt_next);
+      for (int it = 0; it < w.n_it && ok; ++it, ++git) {
+        int hq, q0, k0;
+        walk_decode(w, it, hq, q0, k0);
+        const int q_idx = q0 + row;
+        const bool q_ok = q_idx < p.seq_q;
+        const float lse2 = lse2_next, dlt = dlt_next;
+        if (it + 1 < w.n_it) load_stats(it + 1, lse2_next, dlt_next);
+        const int key_lim = q_ok ? (p.causal ? min(p.seq_k - 1, q_idx + shift) : p.seq_k - 1) : -1;   // last visible key
+        const int kbase = k0 + cg * GC;
+        const bool need_mask = (kbase + GC - 1 > key_lim);
+        if (!mbar_wait(bar_sdp_full, git & 1, abort_flag, status, 46)) { ok = false; break; }
         tc_fence_after();
-        const int r_idx = own0 + row;
-        const int limit = MODE == MODE_DKV ? p.seq_k : p.seq_q;
-        const int head_out = MODE == MODE_DKV ? head_k : head_q0;
-        constexpr int CW = D / 2;                            // columns per warp group
+        uint32_t pp[GC / 2], ds[GC / 2];                     // GC columns each, packed bf16 pairs
+        // 16 columns of S and of dP per step; the loads of step c + 1 are in flight while step c is computed
+        const uint32_t ts = tmem_s + lane_off + cg * GC, td = tmem_dp + lane_off + cg * GC;
+        uint32_t rs[2][16], rd[2][16];
+        tmem_ld_32x16(ts, rs[0]);
+        tmem_ld_32x16(td, rd[0]);
 #pragma unroll
-        for (int which = 0; which < (MODE == MODE_DKV ? 2 : 1); ++which) {
-          const uint32_t tacc = which == 0 ? tmem_acc0 : tmem_acc1;
-          const float mul = which == 0 ? p.scale : 1.f;      // dK and dQ carry the softmax scale, dV does not
-          __nv_bfloat16* base = which == 0 ? p.out0 : p.out1;
-          const long long bs = which == 0 ? p.o0_bs : p.o1_bs, rs_ = which == 0 ? p.o0_rs : p.o1_rs,
-                          hs = which == 0 ? p.o0_hs : p.o1_hs;
+        for (int c = 0; c < GC / 16; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < GC / 16) {
+            tmem_ld_32x16(ts + (c + 1) * 16, rs[(c + 1) & 1]);
+            tmem_ld_32x16(td + (c + 1) * 16, rd[(c + 1) & 1]);
+          }
 #pragma unroll
-          for (int c = 0; c < CW / 32; ++c) {
-            uint32_t r[32];
-            if (have) {
-              tmem_ld_32x32(tacc + lane_off + cg * CW + c * 32, r);
-              tmem_ld_wait();
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) r[i] = 0u;
+          for (int i = 0; i < 8; ++i) {
+            float p0 = bt_ex2(fmaf(__uint_as_float(rs[c & 1][2 * i]), sl2, -lse2));
+            float p1 = bt_ex2(fmaf(__uint_as_float(rs[c & 1][2 * i + 1]), sl2, -lse2));
+            if (need_mask) {
+              const int key = kbase + c * 16 + 2 * i;
+              if (key > key_lim) p0 = 0.f;
+              if (key + 1 > key_lim) p1 = 0.f;
             }
-            if (r_idx < limit) {
-              __nv_bfloat16* op = base + b * bs + head_out * hs + static_cast<long long>(r_idx) * rs_ + cg * CW + c * 32;
+            const float d0 = p0 * (__uint_as_float(rd[c & 1][2 * i]) - dlt);
+            const float d1 = p1 * (__uint_as_float(rd[c & 1][2 * i + 1]) - dlt);
+            pp[c * 8 + i] = pack_bf16x2(p0, p1);
+            ds[c * 8 + i] = pack_bf16x2(d0, d1);
+          }
+        }
+        // S and dP are in registers: the next pair of products may overwrite them
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sdp_empty);
+        // the previous step's dV / dK / dQ products have finished reading P and dS
+        if (!mbar_wait(bar_p_empty, (git & 1) ^ 1, abort_flag, status, 47)) { ok = false; break; }
+        // 64 keys are one 128-byte-swizzled atom (row `row`, eight 16-byte chunks); this thread owns GC / 8 of the chunks
+        constexpr int CH = GC / 8;
+        const int atom = (cg * GC) / 64, ch0 = ((cg * GC) % 64) / 8;
 #pragma unroll
-              for (int v4 = 0; v4 < 4; ++v4) {
-                uint4 o;
-                o.x = pack_bf16x2(__uint_as_float(r[v4 * 8 + 0]) * mul, __uint_as_float(r[v4 * 8 + 1]) * mul);
-                o.y = pack_bf16x2(__uint_as_float(r[v4 * 8 + 2]) * mul, __uint_as_float(r[v4 * 8 + 3]) * mul);
-                o.z = pack_bf16x2(__uint_as_float(r[v4 * 8 + 4]) * mul, __uint_as_float(r[v4 * 8 + 5]) * mul);
-                o.w = pack_bf16x2(__uint_as_float(r[v4 * 8 + 6]) * mul, __uint_as_float(r[v4 * 8 + 7]) * mul);
-                reinterpret_cast<uint4*>(op)[v4] = o;
-              }
+        for (int ch = 0; ch < CH; ++ch) {
+          const uint32_t off = atom * L::kHalf + row * 128 + (((ch0 + ch) ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sDs + off), "r"(ds[4 * ch]), "r"(ds[4 * ch + 1]),
+                       "r"(ds[4 * ch + 2]), "r"(ds[4 * ch + 3])
+                       : "memory");
+          if (MODE == MODE_DKV) {
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + off), "r"(pp[4 * ch]), "r"(pp[4 * ch + 1]),
+                         "r"(pp[4 * ch + 2]), "r"(pp[4 * ch + 3])
+                         : "memory");
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_p_full);
+      }
+      if (!ok) break;
+
+      // ---- read-out: TMEM lane = key (MODE_DKV) or query (MODE_DQ) row of the owned tile; this group's share of D
+      const bool have = w.n_it > 0;
+      if (have && !mbar_wait(bar_acc_full, ai & 1, abort_flag, status, 48)) { ok = false; break; }
+      tc_fence_after();
+      const int r_idx = w.own0 + row;
+      const int limit = MODE == MODE_DKV ? p.seq_k : p.seq_q;
+      const int head_out = MODE == MODE_DKV ? w.head_k : w.head_q0;
+      constexpr int CW = D / kBtColGroups;                 // output columns per column group (16, 32 or 64)
+#pragma unroll
+      for (int which = 0; which < (MODE == MODE_DKV ? 2 : 1); ++which) {
+        const uint32_t tacc = which == 0 ? tmem_acc0 : tmem_acc1;
+        const float mul = which == 0 ? p.scale : 1.f;      // dK and dQ carry the softmax scale, dV does not
+        __nv_bfloat16* base = which == 0 ? p.out0 : p.out1;
+        const long long bs = which == 0 ? p.o0_bs : p.o1_bs, rs_ = which == 0 ? p.o0_rs : p.o1_rs,
+                        hs = which == 0 ? p.o0_hs : p.o1_hs;
+#pragma unroll
+        for (int c = 0; c < CW / 16; ++c) {
+          uint32_t r[16];
+          if (have) {
+            tmem_ld_32x16(tacc + lane_off + cg * CW + c * 16, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = 0u;
+          }
+          if (r_idx < limit) {
+            __nv_bfloat16* op = base + b * bs + head_out * hs + static_cast<long long>(r_idx) * rs_ + cg * CW + c * 16;
+#pragma unroll
+            for (int v4 = 0; v4 < 2; ++v4) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[v4 * 8 + 0]) * mul, __uint_as_float(r[v4 * 8 + 1]) * mul);
+              o.y = pack_bf16x2(__uint_as_float(r[v4 * 8 + 2]) * mul, __uint_as_float(r[v4 * 8 + 3]) * mul);
+              o.z = pack_bf16x2(__uint_as_float(r[v4 * 8 + 4]) * mul, __uint_as_float(r[v4 * 8 + 5]) * mul);
+              o.w = pack_bf16x2(__uint_as_float(r[v4 * 8 + 6]) * mul, __uint_as_float(r[v4 * 8 + 7]) * mul);
+              reinterpret_cast<uint4*>(op)[v4] = o;
             }
           }
         }
+      }
+      if (have) {
+        // the accumulators are in registers / memory: the next item's products may overwrite them
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_empty);
+        ++ai;
       }
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kBtComputeWarps + 1) {
     if (*abort_flag) {
       const unsigned long long t0 = globaltimer_ns();
       while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -496,19 +560,24 @@ RB_API int rb_attention_bwd_tc(const RbAttnArgs* a, void* stream_v) {
   rb::BtParams p;
   p.lse = a->lse; p.delta = a->delta;
   p.seq_q = a->seq_q; p.seq_k = a->seq_k; p.heads = a->heads; p.kv_heads = a->kv_heads; p.causal = a->causal;
+  p.batch = a->batch;
   p.scale = a->scale;
   // dK / dV
   p.out0 = reinterpret_cast<__nv_bfloat16*>(a->dk); p.out1 = reinterpret_cast<__nv_bfloat16*>(a->dv);
   p.o0_bs = a->dk_strides[0]; p.o0_rs = a->dk_strides[1]; p.o0_hs = a->dk_strides[2];
   p.o1_bs = a->dv_strides[0]; p.o1_rs = a->dv_strides[1]; p.o1_hs = a->dv_strides[2];
-  dim3 kvgrid((a->seq_k + rb::kBtTile - 1) / rb::kBtTile, a->kv_heads, a->batch);
+  // persistent CTAs: one per SM, each walks over work items (owned tile, head, batch)
+  const int sms = rbhost::device_sm_count();
+  const long long kv_items = static_cast<long long>((a->seq_k + rb::kBtTile - 1) / rb::kBtTile) * a->kv_heads * a->batch;
+  dim3 kvgrid(static_cast<unsigned>(kv_items < sms ? kv_items : sms));
   int rc = D == 64 ? bt_launch<64, rb::MODE_DKV>(tq, tk, tv, tdo, p, kvgrid, stream)
                    : bt_launch<128, rb::MODE_DKV>(tq, tk, tv, tdo, p, kvgrid, stream);
   if (rc != 0) return rc;
   // dQ
   p.out0 = reinterpret_cast<__nv_bfloat16*>(a->dq); p.out1 = nullptr;
   p.o0_bs = a->dq_strides[0]; p.o0_rs = a->dq_strides[1]; p.o0_hs = a->dq_strides[2];
-  dim3 qgrid((a->seq_q + rb::kBtTile - 1) / rb::kBtTile, a->heads, a->batch);
+  const long long q_items = static_cast<long long>((a->seq_q + rb::kBtTile - 1) / rb::kBtTile) * a->heads * a->batch;
+  dim3 qgrid(static_cast<unsigned>(q_items < sms ? q_items : sms));
   return D == 64 ? bt_launch<64, rb::MODE_DQ>(tq, tk, tv, tdo, p, qgrid, stream)
                  : bt_launch<128, rb::MODE_DQ>(tq, tk, tv, tdo, p, qgrid, stream);
 }
