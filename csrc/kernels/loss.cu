@@ -180,6 +180,47 @@ softmax_rows_bwd_kernel(const float* __restrict__ out, const float* __restrict__
 
 }  // namespace rb
 
+namespace rb {
+__global__ void __launch_bounds__(256)
+ce_grad_lse_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
+                   const float* __restrict__ lse, __nv_bfloat16* __restrict__ dlogits, long long ldd, int rows, int n,
+                   float grad_scale) {
+  const int c8 = n / 8;
+  const long long total = static_cast<long long>(rows) * c8;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long r = i / c8;
+    const int c = static_cast<int>(i - r * c8) * 8;
+    const float l = __ldg(lse + r);
+    const long long t = __ldg(targets + r);
+    const uint4 u = *reinterpret_cast<const uint4*>(logits + r * ld + c);
+    const uint32_t* pu = reinterpret_cast<const uint32_t*>(&u);
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(pu[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = (__expf(v[j] - l) - ((c + j) == t ? 1.f : 0.f)) * grad_scale;
+    uint4 o;
+    o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]); o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(dlogits + r * ldd + c) = o;
+  }
+}
+}  // namespace rb
+
+RB_API int rb_cross_entropy_grad_lse(const void* logits, long long ld, const long long* targets, const float* lse,
+                                     void* dlogits, long long ldd, int rows, int n, float grad_scale, void* stream_v) {
+  if (rows <= 0 || n <= 0) return 0;
+  if (!logits || !targets || !lse || !dlogits || (n % 8) || (ld % 8) || (ldd % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(dlogits)) & 15) return -2;
+  const long long total = static_cast<long long>(rows) * (n / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  rb::ce_grad_lse_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(logits), ld, targets, lse, reinterpret_cast<__nv_bfloat16*>(dlogits), ldd,
+      rows, n, grad_scale);
+  return static_cast<int>(cudaGetLastError());
+}
+
 RB_API int rb_cross_entropy(const void* logits, long long ld, const long long* targets, float* loss, float* lse,
                             void* dlogits, long long ldd, int rows, int n_valid, int n_pad, float grad_scale,
                             long long ignore_index, void* stream_v) {

@@ -219,9 +219,35 @@ class AllReduceOp:
         return y / self.pg.world_size if self.op == "mean" else y
 
 
+def _vocab_parallel_cross_entropy_cuda(local_logits, targets, pg: ProcessGroup, vocab_start: int):
+    """CUDA path: the fused loss kernel yields this shard's log-sum-exp and target logit per row, two small
+    collectives combine them over the ranks, a second kernel writes (softmax - onehot) for this shard."""
+    from .. import _native as N
+    from ..ops.loss import cross_entropy_fwd_bwd
+    rows, n = local_logits.shape
+    local_t = targets.to(torch.int64) - vocab_start
+    mine = (local_t >= 0) & (local_t < n)
+    t_masked = torch.where(mine, local_t, torch.full_like(local_t, -100))
+    loss_l, lse_l, _ = cross_entropy_fwd_bwd(local_logits, t_masked, want_grad=False)      # loss = lse - z_target (owned rows)
+    target_logit = torch.where(mine, lse_l - loss_l, torch.zeros_like(lse_l))
+    lse = torch.logsumexp(torch.stack(pg.all_gather(lse_l)), 0)
+    pg.all_reduce_sum(target_logit, "vp_target")
+    grad = torch.empty_like(local_logits)
+    N.optional_sig("rb_cross_entropy_grad_lse", [N.c_void_p, N.c_ll, N.c_void_p, N.c_void_p, N.c_void_p, N.c_ll, N.c_int,
+                                                 N.c_int, N.c_float, N.c_void_p])
+    N.check(N.kernels().rb_cross_entropy_grad_lse(local_logits.data_ptr(), local_logits.stride(0), t_masked.data_ptr(),
+                                                  lse.data_ptr(), grad.data_ptr(), grad.stride(0), rows, n, 1.0,
+                                                  N.stream_ptr()), "rb_cross_entropy_grad_lse")
+    return lse - target_logit, grad
+
+
 def vocab_parallel_cross_entropy(local_logits: torch.Tensor, targets: torch.Tensor, pg: ProcessGroup, vocab_start: int):
     """Cross-entropy over a vocabulary sharded across the TP group: local_logits [rows, V/W].  Returns (loss [rows],
-    dlogits_local [rows, V/W]) with two small collectives (max and sum-exp) plus one for the target logit."""
+    dlogits_local [rows, V/W]).  CUDA bf16 shards whose width is a multiple of 8 take the native kernels; everything
+    else the tensor-op form below (two small collectives for max and sum-exp plus one for the target logit)."""
+    if local_logits.is_cuda and local_logits.dtype == torch.bfloat16 and local_logits.shape[1] % 8 == 0 and \
+            local_logits.stride(1) == 1 and local_logits.stride(0) % 8 == 0:
+        return _vocab_parallel_cross_entropy_cuda(local_logits, targets, pg, vocab_start)
     lf = local_logits.float()
     rows, n = lf.shape
     gmax = lf.amax(-1)
