@@ -19,6 +19,7 @@ crates/runtime/examples/wikitext2_lm.rs:120-137.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -209,6 +210,9 @@ class FusedGPTEngine:
         self._acts = None
         self._acts_tokens = 0
         self.loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
+        # CUDA-graph replay of the micro-batch forward + backward (about 380 launches): RUSTRAL_TRAIN_GRAPHS=0 disables it
+        self.use_graphs = self.device.type == "cuda" and os.environ.get("RUSTRAL_TRAIN_GRAPHS", "1") != "0"
+        self._fb_graphs: dict = {}
         self.grad_norm_sq = torch.zeros((), dtype=torch.float32, device=self.device)
         self.grad_norm = torch.zeros((), dtype=torch.float32, device=self.device)
         self.kernel_launches = 0
@@ -370,6 +374,35 @@ class FusedGPTEngine:
         ops.embedding_backward(ids.reshape(-1), dx, P.g("tok_embed.embed"),
                                P.g("pos_embed.embed") if cfg.arch == "gpt2" else None, S)
 
+    def _forward_backward_graphed(self, ids, targets, grad_scale: float, first_micro: bool) -> None:
+        """`forward_backward` replayed from a CUDA graph.  One graph per (shape, first_micro, grad_scale); the first
+        two calls of a key run eagerly (lazy kernel configuration, scratch allocation, tensor-map cache), the third
+        is captured and every later one is a copy of the token ids into static buffers plus one graph launch."""
+        key = (tuple(ids.shape), bool(first_micro), float(grad_scale))
+        g = self._fb_graphs.get(key)
+        if g is None:
+            g = {"calls": 0, "graph": None, "ids": torch.empty_like(ids, memory_format=torch.contiguous_format),
+                 "tgt": torch.empty_like(targets, memory_format=torch.contiguous_format)}
+            self._fb_graphs[key] = g
+        if g["graph"] is None and g["calls"] < 2:
+            g["calls"] += 1
+            self.forward_backward(ids, targets, grad_scale, first_micro)
+            return
+        g["ids"].copy_(ids)
+        g["tgt"].copy_(targets)
+        from .. import _native
+        if g["graph"] is None:
+            torch.cuda.current_stream(self.device).synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = _native.launch_count
+            with torch.cuda.graph(graph):
+                self.forward_backward(g["ids"], g["tgt"], grad_scale, first_micro)
+            g["launches"] = _native.launch_count - before      # kernels recorded in the graph
+            _native.launch_count = before                      # nothing ran during capture
+            g["graph"] = graph
+        g["graph"].replay()
+        _native.launch_count += g["launches"]                  # a replay launches every recorded kernel
+
     @staticmethod
     def _attention_backward_cpu(do, q, k, v, scale, dq, dk, dv):
         qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
@@ -415,7 +448,10 @@ class FusedGPTEngine:
         total_tokens = total_tokens or ids.numel()
         self.loss_acc.zero_()
         for i in range(0, N, mb):
-            self.forward_backward(ids[i:i + mb], targets[i:i + mb], 1.0 / total_tokens, first_micro=(i == 0))
+            if self.use_graphs:
+                self._forward_backward_graphed(ids[i:i + mb], targets[i:i + mb], 1.0 / total_tokens, i == 0)
+            else:
+                self.forward_backward(ids[i:i + mb], targets[i:i + mb], 1.0 / total_tokens, first_micro=(i == 0))
         if do_step:
             self.optimizer_step(lr)
         return ops.scalar_op("mul_scalar", self.loss_acc.view(1), 1.0 / total_tokens).view(())
