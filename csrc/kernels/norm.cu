@@ -257,6 +257,7 @@ norm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials, int 
 namespace {
 struct NormCfg { int chunks, wpr; };
 inline NormCfg cfg_for(int n) {
+  if (n <= 768) return {3, 1};        // 768-wide rows (d_model of the headline model): no idle lanes, fewer registers
   if (n <= 1024) return {4, 1};
   if (n <= 2048) return {4, 2};
   if (n <= 4096) return {4, 4};
@@ -279,7 +280,8 @@ RB_API int rb_norm_bwd_num_partials(int rows, int n) {
 
 #define RB_NORM_DISPATCH(N_, MACRO)                   \
   {                                                   \
-    if ((N_) <= 1024) { MACRO(4, 1) }                 \
+    if ((N_) <= 768) { MACRO(3, 1) }                  \
+    else if ((N_) <= 1024) { MACRO(4, 1) }            \
     else if ((N_) <= 2048) { MACRO(4, 2) }            \
     else if ((N_) <= 4096) { MACRO(4, 4) }            \
     else { MACRO(8, 4) }                              \
