@@ -329,3 +329,35 @@ def test_flash_attention_backward_tcgen05(B, Sq, Sk, H, Hk, D, causal, cuda_stat
     _close(dq, dq3, tol=3e-2, what="tc vs mma dq")
     _close(dk, dk3, tol=3e-2, what="tc vs mma dk")
     _close(dv, dv3, tol=3e-2, what="tc vs mma dv")
+
+
+def test_bounded_wait_expires_and_reports_without_losing_the_context():
+    """A flag that nothing ever sets: the wait kernel gives up after its limit, records the timeout in the device
+    status word, and the context keeps working (this is what a rank sees when a peer never signals)."""
+    import time
+    from rustral_b200 import _native as N
+    from rustral_b200.parallel import symm  # noqa: F401  (declares rb_wait_all)
+    lib = N.kernels()
+    lib.rb_init()
+    N.read_status(clear=True)
+    pad = torch.zeros(1024, dtype=torch.int32, device="cuda")          # a private "signal pad": nobody writes to it
+    t0 = time.perf_counter()
+    N.check(lib.rb_wait_all(pad.data_ptr(), 2, 0, 1, 50, N.stream_ptr()), "rb_wait_all")     # 50 ms limit
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    bits, where = N.read_status(clear=True)
+    assert bits != 0 and where == 100, (bits, where)                 # timeout bit set, raised by the channel-0 wait
+    assert 0.03 < waited < 2.0, waited
+    with pytest.raises(N.NativeError):
+        N.check(lib.rb_wait_all(pad.data_ptr(), 2, 0, 1, 20, N.stream_ptr()), "rb_wait_all")
+        N.raise_on_status()
+    # the context is intact: a GEMM runs and is correct, and the status word is clean again
+    a, b = _bf((128, 64), 1).cuda(), _bf((64, 64), 2).cuda()
+    out = ops.gemm(a, b)
+    _close(out, a.float().cpu() @ b.float().cpu().t(), tol=2e-2, what="gemm after timeout")
+    assert N.read_status(clear=True)[0] == 0
+    # a flag that IS set lets the wait through at once
+    pad[:2] = 1
+    N.check(lib.rb_wait_all(pad.data_ptr(), 2, 0, 1, 50, N.stream_ptr()), "rb_wait_all")
+    torch.cuda.synchronize()
+    assert N.read_status(clear=True)[0] == 0
