@@ -50,6 +50,7 @@ def main(argv=None):
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--ep", type=int, default=1)
+    ap.add_argument("--fsdp", type=int, default=1, help="data-parallel ranks with ZeRO-3 sharded block weights (fused all-gather)")
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--global-batch", type=int, default=8)
@@ -69,8 +70,10 @@ def main(argv=None):
         dist.init_process_group("nccl", device_id=dev)
     if a.ep > 1 and (a.tp > 1 or a.pp > 1):
         raise SystemExit("expert parallelism is combined with data parallelism only")
-    if a.tp * a.pp * a.ep != world:
-        raise SystemExit(f"tp*pp*ep = {a.tp * a.pp * a.ep} but WORLD_SIZE = {world}")
+    if a.fsdp > 1 and (a.tp > 1 or a.pp > 1 or a.ep > 1):
+        raise SystemExit("--fsdp is combined with plain data parallelism only")
+    if a.tp * a.pp * a.ep * a.fsdp != world:
+        raise SystemExit(f"tp*pp*ep*fsdp = {a.tp * a.pp * a.ep * a.fsdp} but WORLD_SIZE = {world}")
 
     from .. import _native
     from ..models.parallel_lm import MixedPrecisionAdamW, ParallelDecoderLM
@@ -80,7 +83,11 @@ def main(argv=None):
 
     tp_pg = pp_pg = None
     fused_tp = ep_ctx = None
-    tp_idx, pp_idx = (rank % a.tp, rank // a.tp) if a.ep == 1 else (0, 0)
+    tp_idx, pp_idx = (rank % a.tp, rank // a.tp) if (a.ep == 1 and a.fsdp == 1) else (0, 0)
+    fsdp_ctx = None
+    if a.fsdp > 1:
+        from ..parallel.fused_tp import FusedTP
+        fsdp_ctx = FusedTP(None, dev)
     if a.tp > 1:
         for p in range(a.pp):                                  # every rank takes part in creating every group
             g = ProcessGroup.new_torch_subgroup(range(p * a.tp, (p + 1) * a.tp))
@@ -102,10 +109,10 @@ def main(argv=None):
     per_stage = cfg.n_layer // a.pp
     model = ParallelDecoderLM(cfg, dev, tp_pg=tp_pg, fused_tp=fused_tp, ep=ep_ctx,
                               first_layer=pp_idx * per_stage, last_layer=(pp_idx + 1) * per_stage if pp_idx < a.pp - 1 else cfg.n_layer,
-                              has_embed=pp_idx == 0, has_head=pp_idx == a.pp - 1, seed=1)
+                              has_embed=pp_idx == 0, has_head=pp_idx == a.pp - 1, seed=1, fsdp=fsdp_ctx)
     # expert parallel: ZeRO-1 over the data-parallel ranks for the dense (replicated) parameters
     opt = MixedPrecisionAdamW(model, lr=a.lr, use_zero1=a.ep > 1)
-    dp = a.ep                                                  # data-parallel replicas (expert-parallel ranks see different data)
+    dp = a.ep * a.fsdp                                         # data-parallel replicas (these ranks see different data)
     local_batch = a.global_batch // dp
     if local_batch % a.micro_batch:
         raise SystemExit("the per-replica batch must be a multiple of the micro-batch")
@@ -126,7 +133,7 @@ def main(argv=None):
                                 act_shape=(a.micro_batch * S // a.tp, cfg.d_model), act_dtype=torch.bfloat16, device=dev)
         pipe.after_backward = opt.accumulate
 
-    gen = torch.Generator().manual_seed(1234 + (rank if a.ep > 1 else 0))   # TP / PP ranks of a replica see the same batch
+    gen = torch.Generator().manual_seed(1234 + (rank if dp > 1 else 0))     # TP / PP ranks of a replica see the same batch
 
     def make_batch():
         return torch.randint(0, cfg.vocab_size, (local_batch, S + 1), generator=gen, dtype=torch.int64).to(dev)
@@ -181,7 +188,8 @@ def main(argv=None):
             "n_gpus": world, "ms_per_step": round(ms_step, 2), "steps": a.steps, "warmup": a.warmup, "dtype": "bf16",
             "config": {"model": a.config, "layers": cfg.n_layer, "d_model": cfg.d_model, "seq_len": S,
                        "global_batch": a.global_batch, "micro_batch": a.micro_batch,
-                       "parallelism": f"tp{a.tp}-pp{a.pp}-ep{a.ep}", "fused": not a.unfused,
+                       "parallelism": f"tp{a.tp}-pp{a.pp}-ep{a.ep}" + (f"-fsdp{a.fsdp}" if a.fsdp > 1 else ""),
+                       "fused": not a.unfused,
                        "params_total": cfg.num_params(), "params_local": model.local_param_count(),
                        "zero1_dense": a.ep > 1, "optimizer_state_bytes_local": opt.state_bytes()},
             "model_tflops_per_s_per_gpu": round(cfg.flops_per_token() * tokens / (ms_step / 1e3) / 1e12 / world, 1),
@@ -193,6 +201,8 @@ def main(argv=None):
         fused_tp.close()
     if ep_ctx is not None:
         ep_ctx.close()
+    if fsdp_ctx is not None:
+        fsdp_ctx.close()
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -109,9 +109,16 @@ class ParallelDecoderLM:
 
     def __init__(self, cfg: ParallelLMConfig, device, *, tp_pg=None, fused_tp=None, ep=None, dp_group=None,
                  first_layer: int = 0, last_layer: int | None = None, has_embed: bool = True, has_head: bool = True,
-                 seed: int = 0):
+                 seed: int = 0, fsdp=None):
+        """`fsdp` (a parallel.fused_tp.FusedTP over the data-parallel group): ZeRO-3 for the block weights.  Each rank
+        keeps 1/W of the rows of every projection in symmetric memory; the forward all-gathers them inside the
+        consuming GEMM and the weight gradient is reduce-scattered inside its GEMM (FSDPLinearFn)."""
         self.cfg, self.device = cfg, torch.device(device)
         self.tp_pg, self.fused_tp, self.ep, self.dp_group = tp_pg, fused_tp, ep, dp_group
+        self.fsdp = fsdp
+        self.fsdp_shards: dict = {}
+        if fsdp is not None and (tp_pg is not None or ep is not None):
+            raise ValueError("fsdp is combined with plain data parallelism only")
         self.tp = tp_pg.world_size if tp_pg is not None else 1
         self.tp_rank = tp_pg.rank if tp_pg is not None else 0
         self.first_layer = first_layer
@@ -131,6 +138,20 @@ class ParallelDecoderLM:
         t = torch.empty(shape, dtype=torch.float32, device=self.device).normal_(0.0, std, generator=g)
         return t.to(torch.bfloat16).requires_grad_()
 
+    def _weight(self, name: str, shape, sd, tp_rank: int, std):
+        """A block projection: the tensor-parallel shard, or with `fsdp` this data-parallel rank's row shard of it,
+        stored in symmetric memory (the parameter IS the symmetric buffer, so optimizer updates are visible to peers)."""
+        if self.fsdp is None:
+            return self._rand(shape, sd(name, tp_rank), std)
+        W, r = self.fsdp.world, self.fsdp.rank
+        rows = shape[0] // W
+        if shape[0] % W or not self.fsdp.supports(rows):
+            raise ValueError(f"fsdp: {name} has {shape[0]} rows, not a multiple of 128 x {W}")
+        shard = self._rand((rows, shape[1]), sd(name, r), std).detach()
+        ws = self.fsdp.shard_weight(shard, pooled=True)
+        self.fsdp_shards[name] = ws
+        return ws.tensor.requires_grad_()
+
     def _init(self, seed: int) -> None:
         c, tp, r = self.cfg, self.tp, self.tp_rank
         d, hd = c.d_model, c.head_dim
@@ -144,8 +165,8 @@ class ParallelDecoderLM:
         for l in range(self.first_layer, self.last_layer):
             p = f"l{l}."
             P[p + "attn_norm"] = torch.ones(d, dtype=torch.bfloat16, device=self.device, requires_grad=True)
-            P[p + "wqkv"] = self._rand(((hq + 2 * hk) * hd, d), sd(p + "wqkv", r))
-            P[p + "wo"] = self._rand((d, hq * hd), sd(p + "wo", r), c.init_std / math.sqrt(2 * c.n_layer))
+            P[p + "wqkv"] = self._weight(p + "wqkv", ((hq + 2 * hk) * hd, d), sd, r, None)
+            P[p + "wo"] = self._weight(p + "wo", (d, hq * hd), sd, r, c.init_std / math.sqrt(2 * c.n_layer))
             P[p + "mlp_norm"] = torch.ones(d, dtype=torch.bfloat16, device=self.device, requires_grad=True)
             self.replicated.update({p + "attn_norm", p + "mlp_norm"})
             if c.num_experts:
@@ -157,8 +178,8 @@ class ParallelDecoderLM:
                 self.replicated.add(p + "router")
                 self.expert_names.update({p + "w1", p + "w2"})
             else:
-                P[p + "wgu"] = self._rand((2 * f, d), sd(p + "wgu", r))
-                P[p + "wdown"] = self._rand((d, f), sd(p + "wdown", r), c.init_std / math.sqrt(2 * c.n_layer))
+                P[p + "wgu"] = self._weight(p + "wgu", (2 * f, d), sd, r, None)
+                P[p + "wdown"] = self._weight(p + "wdown", (d, f), sd, r, c.init_std / math.sqrt(2 * c.n_layer))
         if self.has_head:
             P["final_norm"] = torch.ones(d, dtype=torch.bfloat16, device=self.device, requires_grad=True)
             P["head"] = self._rand((c.vocab_size // tp, d), sd("head", r))
@@ -171,8 +192,15 @@ class ParallelDecoderLM:
         return sum(p.numel() for p in self.params.values())
 
     # ------------------------------------------------------------------------------------------------ layers
-    def _col(self, x, w):
+    def _fsdp_linear(self, x, name: str):
+        from ..parallel.fused_tp import FSDPLinearFn
+        return FSDPLinearFn.apply(x, self.params[name], None, "none", self.fsdp, self.fsdp_shards[name])
+
+    def _col(self, x, name: str):
         """Column-parallel projection of sequence-sharded rows: [R / tp, d] -> [R, n / tp]."""
+        if name in self.fsdp_shards:
+            return self._fsdp_linear(x, name)
+        w = self.params[name]
         if self.tp == 1:
             return ops.linear(x, w)
         if self.fused_tp is not None and self.fused_tp.supports(x.shape[0]):
@@ -181,8 +209,11 @@ class ParallelDecoderLM:
         from ..parallel.tensor_parallel import _GatherSeq
         return ops.linear(_GatherSeq.apply(x, self.tp_pg), w)
 
-    def _row(self, x, w, residual):
+    def _row(self, x, name: str, residual):
         """Row-parallel projection back to sequence-sharded rows: [R, k / tp] -> [R / tp, d] (+ residual)."""
+        if name in self.fsdp_shards:
+            return self._fsdp_linear(x, name) + residual
+        w = self.params[name]
         if self.tp == 1:
             return ops.linear(x, w, None, "none", residual)
         if self.fused_tp is not None and x.shape[0] % self.tp == 0 and self.fused_tp.supports(x.shape[0] // self.tp):
@@ -196,12 +227,12 @@ class ParallelDecoderLM:
         hd = c.head_dim
         hq, hk = c.n_head // self.tp, c.n_kv_head // self.tp
         h = ops.rms_norm(x, P[p + "attn_norm"], c.eps)
-        qkv = self._col(h, P[p + "wqkv"])                                   # [B*S, (hq + 2 hk) * hd]
+        qkv = self._col(h, p + "wqkv")                                   # [B*S, (hq + 2 hk) * hd]
         q = rotary.rope(qkv[:, :hq * hd].reshape(batch, seq, hq, hd), seq, theta=c.rope_theta)
         k = rotary.rope(qkv[:, hq * hd:(hq + hk) * hd].reshape(batch, seq, hk, hd), seq, theta=c.rope_theta)
         v = qkv[:, (hq + hk) * hd:].reshape(batch, seq, hk, hd)
         o = ops.flash_attention(q, k, v, True)
-        x = self._row(o.reshape(batch * seq, hq * hd), P[p + "wo"], x)
+        x = self._row(o.reshape(batch * seq, hq * hd), p + "wo", x)
         h = ops.rms_norm(x, P[p + "mlp_norm"], c.eps)
         aux = None
         if c.num_experts:
@@ -212,8 +243,8 @@ class ParallelDecoderLM:
                 y, aux = moe_ops.moe_mlp(h, P[p + "router"], P[p + "w1"], P[p + "w2"], c.top_k, "swiglu")
             x = x + y
         else:
-            gu = self._col(h, P[p + "wgu"])
-            x = self._row(rotary.swiglu(gu), P[p + "wdown"], x)
+            gu = self._col(h, p + "wgu")
+            x = self._row(rotary.swiglu(gu), p + "wdown", x)
         return x, aux
 
     # ------------------------------------------------------------------------------------------------ forward
@@ -242,7 +273,7 @@ class ParallelDecoderLM:
         """x: this rank's rows after the last block; targets [B, S] (all rows)."""
         c = self.cfg
         h = ops.rms_norm(x, self.params["final_norm"], c.eps)
-        logits = self._col(h, self.params["head"])                          # [B*S, V / tp]
+        logits = self._col(h, "head")                          # [B*S, V / tp]
         t = targets.reshape(-1)
         if self.tp == 1:
             return ops.cross_entropy(logits, t)
@@ -266,6 +297,14 @@ class ParallelDecoderLM:
             for name in sorted(self.replicated):
                 if name in main_grads:
                     dist.all_reduce(main_grads[name], group=self.tp_pg.group)
+        if self.fsdp is not None:
+            world = self.fsdp.world
+            for name in sorted(main_grads):
+                g = main_grads[name]
+                if name not in self.fsdp_shards:                 # replicated: average over the data-parallel ranks
+                    dist.all_reduce(g, group=self.fsdp.group)
+                g.mul_(1.0 / world)                              # sharded: already summed inside the wgrad GEMM
+            return
         if self.dp_group is not None or self.ep is not None:
             group = self.dp_group if self.dp_group is not None else self.ep.group
             world = dist.get_world_size(group)

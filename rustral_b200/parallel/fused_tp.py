@@ -56,11 +56,14 @@ class WeightShard:
     """A row shard [N / W, K] of a weight that lives in symmetric memory (so peers can pull it from inside a GEMM),
     with this rank's landing buffer for the gathered [N, K] weight and its per-block counters."""
 
-    def __init__(self, ctx: "FusedTP", rows: int, k: int, channel: int):
+    def __init__(self, ctx: "FusedTP", rows: int, k: int, channel: int, full: torch.Tensor | None = None):
         self.rows, self.k = rows, k
         self.buf = SymmetricBuffer(rows * k * 2, ctx.group, ctx.device)
         self.tensor = self.buf.view(torch.bfloat16, rows * k).view(rows, k)
-        self.full = torch.empty((rows * ctx.world, k), dtype=torch.bfloat16, device=ctx.device)
+        # landing buffer of the gathered weight: private, or one shared by every shard of this shape (`pooled`), in
+        # which case it only holds this weight until the next gather of that shape
+        self.pooled = full is not None
+        self.full = full if full is not None else torch.empty((rows * ctx.world, k), dtype=torch.bfloat16, device=ctx.device)
         self.flags = torch.zeros(rows * ctx.world // ROW_BLOCK, dtype=torch.int32, device=ctx.device)
         self.epoch = 0
         self.channel = channel
@@ -80,6 +83,7 @@ class FusedTP:
         self.limit_ms = limit_ms
         self.pad = SignalPad(group, self.device)
         self._ws: dict = {}
+        self._full_pool: dict = {}
 
     def _workspace(self, kind: str, rows: int, width: int):
         key = (kind, rows, width)
@@ -144,8 +148,10 @@ class FusedTP:
         return out
 
     # ------------------------------------------------------------------------------------------ weight all-gather -> GEMM
-    def shard_weight(self, w_shard: torch.Tensor) -> WeightShard:
-        """Moves this rank's row shard of a weight into symmetric memory (collective; same order on every rank)."""
+    def shard_weight(self, w_shard: torch.Tensor, pooled: bool = False) -> WeightShard:
+        """Moves this rank's row shard of a weight into symmetric memory (collective; same order on every rank).
+        `pooled`: all shards of one shape share a single landing buffer for the gathered weight, so a rank holds one
+        gathered weight per shape instead of one per layer (the backward pass gathers again)."""
         rows, k = w_shard.shape
         if not self.supports(rows):
             raise ValueError(f"shard_weight: rows per rank ({rows}) must be a multiple of {ROW_BLOCK}")
@@ -153,7 +159,13 @@ class FusedTP:
         channel = len(self._ws)
         if (channel + 1) * self.world * 4 > self.pad.nbytes:
             raise N.NativeError("FusedTP: out of signal channels")
-        ws = WeightShard(self, rows, k, channel)
+        full = None
+        if pooled:
+            full = self._full_pool.get((rows, k))
+            if full is None:
+                full = torch.empty((rows * self.world, k), dtype=torch.bfloat16, device=self.device)
+                self._full_pool[(rows, k)] = full
+        ws = WeightShard(self, rows, k, channel, full)
         ws.tensor.copy_(w_shard)
         self._ws[key] = ws
         return ws
@@ -239,7 +251,7 @@ class FSDPLinearFn(torch.autograd.Function):
         pre = torch.empty((x2.shape[0], ws.rows * tp.world), dtype=torch.bfloat16, device=x.device) if need_pre else None
         y, w_full = tp.fsdp_gemm(x2, ws, bias=bias, act=act, aux_out=pre)
         ctx.save_for_backward(x2, pre)
-        ctx.w_full, ctx.act, ctx.tp, ctx.has_bias, ctx.x_shape = w_full, act, tp, bias is not None, x.shape
+        ctx.w_full, ctx.act, ctx.tp, ctx.has_bias, ctx.x_shape, ctx.ws = w_full, act, tp, bias is not None, x.shape, ws
         return y.reshape(*x.shape[:-1], y.shape[-1])
 
     @staticmethod
@@ -247,6 +259,9 @@ class FSDPLinearFn(torch.autograd.Function):
         x2, pre = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
         dz = unary_bwd(ctx.act, pre, dy2) if pre is not None else dy2
+        if ctx.ws.pooled:
+            # the shared landing buffer has been reused since the forward pass: gather this weight again
+            dist.all_gather_into_tensor(ctx.w_full, ctx.ws.tensor.detach(), group=ctx.tp.group)
         dx = gemm(dz, ctx.w_full, b_mn=True, out_dtype=torch.bfloat16)                # [M, K] = dz @ W
         dw_shard = ctx.tp.gemm_rs(dz, x2, a_mn=True, b_mn=True)                       # rows of dz^T x, summed over ranks
         db = dz.float().sum(0).to(dz.dtype) if ctx.has_bias else None

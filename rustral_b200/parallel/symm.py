@@ -26,7 +26,7 @@ N.optional_sig("rb_ipc_close", [N.c_void_p])
 N.optional_sig("rb_signal_all", [N.c_void_p, N.c_int, N.c_int, N.c_int, C.c_uint, N.c_void_p])
 N.optional_sig("rb_wait_all", [N.c_void_p, N.c_int, N.c_int, C.c_uint, N.c_int, N.c_void_p])
 
-SIGNAL_PAD_BYTES = 4096
+SIGNAL_PAD_BYTES = 65536               # 16384 flag words: 2048 channels at 8 ranks
 GUARD_BYTES = 256                      # canary region before and after every symmetric buffer
 _CANARY = 0x5AA5C33C
 

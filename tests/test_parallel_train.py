@@ -43,3 +43,9 @@ def test_pipeline_parallel_1f1b_trains():
 def test_expert_parallel_trains():
     out = _run(29674, "--config", "tiny-moe", "--ep", "2", "--global-batch", "8", "--micro-batch", "2")
     assert out["losses"][-1] < out["losses"][0] - 0.05, out["losses"]
+
+
+def test_fsdp_fused_weight_gather_trains():
+    out = _run(29675, "--config", "tiny", "--fsdp", "2", "--global-batch", "8", "--micro-batch", "2")
+    assert out["config"]["parallelism"].endswith("fsdp2")
+    assert out["losses"][-1] < out["losses"][0] - 0.05, out["losses"]
