@@ -97,6 +97,12 @@ class Tape:
         t0 = time.perf_counter()
         return self._record(name, fn(*[self.values[t] for t in tids]), t0)
 
+    def apply(self, name: str, fn) -> TensorId:
+        """Records the result of `fn()` (a differentiable computation over parameters and earlier tape values, e.g. a
+        whole module forward) as one tape op."""
+        t0 = time.perf_counter()
+        return self._record(name, fn(), t0)
+
     # ---- recorded ops -----------------------------------------------------------------------------------------------
     def add(self, a, b): return self._op("add", lambda x, y: x + y, a, b)
     def sub(self, a, b): return self._op("sub", lambda x, y: x - y, a, b)

@@ -23,9 +23,26 @@ class Sst2Example:
     label: int
 
 
+def _parse_sst2_tsv(path: str) -> list:
+    """`sentence<TAB>label` lines under a header row (the legacy GLUE layout, sst2.rs:93)."""
+    out = []
+    with open(path, encoding="utf-8") as f:
+        for i, line in enumerate(f):
+            line = line.rstrip("\n")
+            if not line or (i == 0 and line.lower().startswith("sentence")):
+                continue
+            text, _, label = line.rpartition("\t")
+            if text and label.strip() in ("0", "1"):
+                out.append(Sst2Example(text, int(label)))
+    return out
+
+
 def load_sst2(split: str = "train") -> list:
     name = {"train": "train.jsonl", "dev": "dev.jsonl", "validation": "dev.jsonl"}[split]
     path = os.path.join(cache_root(), "datasets", "sst2", name)
+    legacy = path[:-len(".jsonl")] + ".tsv"
+    if not os.path.exists(path) and os.path.exists(legacy):
+        return _parse_sst2_tsv(legacy)
     if not os.path.exists(path):
         path = fetch_url(SST2_URLS["train" if split == "train" else "dev"], None, os.path.join("datasets", "sst2"), name)
     out = []
@@ -41,6 +58,9 @@ def load_sst2(split: str = "train") -> list:
 def load_wikitext2(split: str = "train") -> str:
     name = f"wiki.{split}.tokens"
     path = os.path.join(cache_root(), "datasets", "wikitext-2", name)
+    legacy = os.path.join(cache_root(), "datasets", "wikitext-2", f"{split}.txt")     # pre-staged plain-text layout
+    if not os.path.exists(path) and os.path.exists(legacy):
+        path = legacy
     if not os.path.exists(path):
         path = fetch_url(WIKITEXT2_URLS[split], None, os.path.join("datasets", "wikitext-2"), name)
     with open(path, encoding="utf-8") as f:

@@ -14,3 +14,102 @@ def test_tiny_lm_cpu_trains_and_roundtrips(tmp_path):
     assert abs(m["loss_start"] - 6.93) < 0.2                      # ln(1024) at initialisation
     assert json.load(open(tmp_path / "manifest.json"))["steps"] == 12
     assert (tmp_path / "model.safetensors").exists() and (tmp_path / "tiny_lm.jsonl").exists()
+
+
+def _load_example(name):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location(name, os.path.join(root, "examples", name + ".py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+_SST2_TSV = ("sentence\tlabel\nthis movie was great\t1\nawful boring waste of time\t0\n"
+             "the acting was wonderful and inspired\t1\ncompletely terrible\t0\nfun and exciting and amazing\t1\n"
+             "bad bad bad really bad\t0\nlovely and heartwarming\t1\nawful again ugh\t0\n"
+             "brilliant performance throughout\t1\ndisappointing ending\t0\n")
+
+
+def _stage_sst2(tmp_path, monkeypatch, reps=1):
+    d = tmp_path / "cache" / "datasets" / "sst2"
+    d.mkdir(parents=True)
+    body = _SST2_TSV + "".join(_SST2_TSV.split("\n", 1)[1] for _ in range(reps - 1))
+    (d / "train.tsv").write_text(body)
+    (d / "dev.tsv").write_text(_SST2_TSV)
+    monkeypatch.setenv("RUSTRAL_CACHE_DIR", str(tmp_path / "cache"))
+    monkeypatch.setenv("RUSTRAL_DATASET_OFFLINE", "1")
+    monkeypatch.setenv("RUSTRAL_DATASET_SKIP_CHECKSUM", "1")
+
+
+def test_sst2_classifier_runs_offline_quick(tmp_path, monkeypatch):
+    """The pre-staged tiny corpus, `--quick`, and a well-formed manifest (crates/runtime/tests/sst2_smoke.rs)."""
+    from rustral_b200.bench.manifest import validate_manifest
+    _stage_sst2(tmp_path, monkeypatch)
+    out = tmp_path / "out"
+    _load_example("sst2_classifier").main(["--quick", "--out-dir", str(out)])
+    m = json.load(open(out / "manifest.json"))
+    assert m["task"] == "sst2_classifier" and m["quick_mode"] and "dev_accuracy" in m and "git_sha" in m
+    assert m["vocab_size"] > 4 and m["train_examples"] == 10 and len(m["dataset_hash_fnv1a"]) == 16
+    assert m["diagnostics"]["dev_label_counts"] == [5, 5] and sum(m["diagnostics"]["dev_positive_prob_hist"]) == 10
+    assert validate_manifest(m) == [] and (out / "vocab.txt").read_text().startswith("<pad>\n<unk>\n<bos>\n<eos>\n")
+
+
+def test_sst2_classifier_overfits_small_set(tmp_path, monkeypatch):
+    """Training works end to end: the first 32 examples are memorised (crates/runtime/tests/sst2_overfit.rs)."""
+    _stage_sst2(tmp_path, monkeypatch, reps=4)
+    m = _load_example("sst2_classifier").main(["--overfit-32", "--epochs", "30", "--batch", "8", "--out-dir", str(tmp_path / "o")])
+    assert m["overfit_32"] and m["dev_accuracy"] >= 0.95, m["dev_accuracy"]
+    assert m["diagnostics"]["epoch_losses"][-1] < 0.5 * m["diagnostics"]["epoch_losses"][0]
+
+
+def _stage_wikitext(tmp_path, monkeypatch):
+    d = tmp_path / "cache" / "datasets" / "wikitext-2"
+    d.mkdir(parents=True)
+    words = "the of and in to a was is for as on with by that it from at his an were are which this be".split()
+    text = "\n".join(" ".join(words[(i * 7 + j * (3 + i % 5)) % len(words)] for j in range(12)) + " ." for i in range(120))
+    for s in ("train", "valid", "test"):
+        (d / f"{s}.txt").write_text(text)
+    monkeypatch.setenv("RUSTRAL_CACHE_DIR", str(tmp_path / "cache"))
+    monkeypatch.setenv("RUSTRAL_DATASET_OFFLINE", "1")
+
+
+def test_wikitext2_lm_runs_offline_quick(tmp_path, monkeypatch):
+    """crates/runtime/tests/wikitext2_lm_smoke.rs: offline `--quick` run, manifest fields, vocabulary file."""
+    from rustral_b200.bench.manifest import validate_manifest
+    _stage_wikitext(tmp_path, monkeypatch)
+    out = tmp_path / "out"
+    m = _load_example("wikitext2_lm").main(["--quick", "--block-size", "16", "--d-model", "32", "--num-heads", "2",
+                                            "--ffn-dim", "64", "--num-layers", "1", "--out-dir", str(out)])
+    assert m["task"] == "wikitext2_word_lm" and m["dev_perplexity"] > 1.0 and m["vocab_size"] > 4
+    assert m["dev_perplexity"] <= 1.2 * m["vocab_size"]            # no worse than uniform after one epoch
+    assert validate_manifest(json.load(open(out / "manifest.json"))) == [] and (out / "vocab.txt").exists()
+
+
+def test_wikitext2_lm_overfits_tiny(tmp_path, monkeypatch):
+    """crates/runtime/tests/wikitext2_overfit.rs: eight windows are memorised."""
+    _stage_wikitext(tmp_path, monkeypatch)
+    m = _load_example("wikitext2_lm").main(["--overfit-tiny", "--block-size", "16", "--epochs", "60", "--batch", "8",
+                                            "--out-dir", str(tmp_path / "o")])
+    assert m["dev_perplexity"] < 2.0, m["dev_perplexity"]
+
+
+def test_manifest_validation_and_curation(tmp_path):
+    """scripts/bench/test_validate_manifest.py: missing keys and missing SST-2 diagnostics are reported."""
+    from rustral_b200.bench import manifest as M
+    good = M.write_manifest(str(tmp_path / "m.json"), "sst2_classifier", {
+        "model_type": "transformer_encoder", "seed": 1, "total_params": 10, "vocab_size": 8, "epochs": 1, "batch_size": 2,
+        "learning_rate": 1e-3, "dataset_hash_fnv1a": "0" * 16, "train_elapsed_sec": 0.1, "dataset": "d", "tokenizer": "t",
+        "quick_mode": True, "dev_accuracy": 0.5, "dev_loss": float("nan")},
+        {k: [] for k in M.SST2_DIAGNOSTICS})
+    assert M.validate_manifest(good) == [] and good["dev_loss"] is None and "git_sha" in good
+    bad = dict(good)
+    del bad["seed"], bad["dev_accuracy"]
+    bad["diagnostics"] = {}
+    errs = M.validate_manifest(bad)
+    assert len(errs) == 3 and any("seed" in e for e in errs) and any("diagnostics missing" in e for e in errs)
+    cur = M.curate("sst2_classifier", "dev_accuracy", "v0", [dict(good, seed=s, dev_accuracy=a) for s, a in ((1, 0.5), (2, 0.7))])
+    assert M.validate_curated(cur) == [] and abs(cur["aggregate"]["mean"] - 0.6) < 1e-9 and cur["aggregate"]["n"] == 2
+    assert M.validate_curated({"runs": []})[-1].endswith("non-empty array")
+    p = tmp_path / "c.json"
+    p.write_text(json.dumps(cur))
+    assert M.main([str(p), str(tmp_path / "m.json")]) == 0
