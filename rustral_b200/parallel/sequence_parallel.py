@@ -229,9 +229,21 @@ class RingAttention:
     def __init__(self, process_group: ProcessGroup, config: SequenceParallelConfig | None = None):
         self.pg = process_group
         self.config = config or SequenceParallelConfig(process_group.world_size)
+        self._peer = None
+
+    def use_peer_memory(self, ring) -> "RingAttention":
+        """Routes CUDA bf16 calls through `ring` (a `peer_ring.PeerRing` over the same ranks): K / V blocks are pulled
+        from the owners' symmetric buffers over NVLink under the attention of the previous block instead of being
+        relayed by send / recv.  Pass None to go back to the relayed path."""
+        if ring is not None and ring.world != self.pg.world_size:
+            raise DistributedError("the peer ring spans a different number of ranks")
+        self._peer = ring
+        return self
 
     def compute(self, q, k, v, scale: float | None = None):
         scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+        if self._peer is not None and q.is_cuda and q.dtype == torch.bfloat16:
+            return self._peer.attention(q, k, v, self.config.causal, self.config.striped, scale)
         return _RingAttentionFn.apply(q, k, v, self.pg, self.config.causal, self.config.striped, scale)
 
     __call__ = compute
