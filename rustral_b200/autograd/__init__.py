@@ -1,5 +1,5 @@
 """Reverse-mode differentiation facade (Tape) and activation checkpointing."""
-from .tape import Tape, TensorId, GradientStore, TapeModule
+from .tape import Tape, TensorId, GradientStore, TapeModule, GradExt
 from .checkpoint import (CheckpointConfig, checkpoint_segment, CheckpointedTransformerLayer, CheckpointManager, MemoryStats,
                          checkpoint_model)
 

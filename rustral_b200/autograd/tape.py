@@ -54,6 +54,7 @@ class Tape:
         self.param_map: dict = {}
         self._leaves: list = []
         self.num_ops = 0
+        self.last_gradients = None       # GradientStore of the most recent backward()
 
     # ---- leaves ----------------------------------------------------------------------------------------------------
     def watch(self, t: torch.Tensor) -> TensorId:
@@ -179,7 +180,25 @@ class Tape:
         leaves = [t for t in self._leaves if self.values[t].requires_grad]
         grads = torch.autograd.grad(out, [self.values[t] for t in leaves], grad_outputs=seed, allow_unused=True)
         store = {t: g for t, g in zip(leaves, grads) if g is not None}
-        return GradientStore(store, dict(self.param_map))
+        self.last_gradients = GradientStore(store, dict(self.param_map))
+        return self.last_gradients
+
+
+class GradExt:
+    """Gradient lookup for a `Parameter` (crates/autodiff/src/lib.rs:1280-1310): from a tape whose backward has run
+    (`gradient`), or from a `GradientStore` plus the tape's parameter map (`gradient_from_store`)."""
+
+    @staticmethod
+    def gradient(param: Parameter, tape: "Tape"):
+        store = getattr(tape, "last_gradients", None)
+        return None if store is None else store.param_gradient(param)
+
+    @staticmethod
+    def gradient_from_store(param: Parameter, grads: GradientStore, param_map: dict | None = None):
+        if param_map is None:
+            return grads.param_gradient(param)
+        tid = param_map.get(param.id)
+        return None if tid is None else grads.get(tid)
 
 
 class TapeModule:

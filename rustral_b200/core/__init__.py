@@ -7,7 +7,7 @@ from .module import (Module, NamedParameters, Trainable, StatefulModule, Saveabl
                      collect_named_parameter_ids)
 from .backend import (Backend, CpuBackend, B200Backend, BackendCapabilities, OperationType, ConvLayout, TrainingDtype,
                       default_backend, set_default_backend)
-from .tensor_ops import TensorOps, TensorInPlaceOps, FusionOps, AttentionOps, QuantizationOps
+from .tensor_ops import TensorOps, TensorInPlaceOps, TensorView, FusionOps, AttentionOps, QuantizationOps
 from .operation_profiler import (OperationProfiler, OperationStats, OperationGuard, ProfilerSnapshot, DeviceType,
                                  shape_bucket, operation_profiler_from_env, finish_profile_from_env)
 from .memory_profiler import MemoryProfiler, AllocationTracker, OOMRisk, global_profiler, track_tensor

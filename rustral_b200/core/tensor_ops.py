@@ -251,6 +251,21 @@ class TensorInPlaceOps:
         return ops.binary("add", y, ops.scalar_op("mul_scalar", x, alpha), out=y)
 
 
+class TensorView:
+    """Zero-copy fp32 view of host tensors (crates/core/src/backend.rs:414-422).  Only tensors that live in host memory
+    as contiguous fp32 can be viewed; device tensors are refused, as the reference's GPU backends refuse them: the
+    caller makes the transfer explicit (`tensor.cpu()`) instead of paying for a hidden one."""
+
+    @staticmethod
+    def as_slice_f32(t):
+        """A flat numpy float32 array sharing the tensor's memory (row-major)."""
+        if t.is_cuda:
+            raise InvalidArgument("as_slice_f32: the tensor lives on the GPU; copy it to the host explicitly")
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise InvalidArgument("as_slice_f32 needs a contiguous float32 tensor")
+        return t.detach().reshape(-1).numpy()
+
+
 class FusionOps:
     """Single-kernel linear + bias (+ activation): the GEMM epilogue does the rest (crates/core/src/backend.rs:475)."""
 

@@ -59,6 +59,30 @@ class Parallel3DTrainer:
         return None
 
 
+class Parallel3DLayer:
+    """One tensor-parallel linear layer inside a 3-D parallel model: column-parallel over the mesh's tensor group
+    (crates/distributed/src/parallelism_3d.rs:216-243).  `gather_output=False` keeps the output sharded for a
+    following row-parallel layer."""
+
+    def __init__(self, in_features: int, out_features: int, tp_group: ProcessGroup, backend, gather_output: bool = True,
+                 bias: bool = False, seed: int = 42):
+        from .tensor_parallel import TensorParallelLinear
+        self.tp_group = tp_group
+        self.linear = TensorParallelLinear.column_parallel(backend, in_features, out_features, tp_group, bias=bias, seed=seed,
+                                                           gather_output=gather_output)
+
+    def forward(self, x, ctx=None):
+        return self.linear(x, ctx)
+
+    __call__ = forward
+
+    def parameters(self) -> list:
+        return self.linear.parameters()
+
+    def named_parameters(self) -> list:
+        return [("linear." + n, p) for n, p in self.linear.named_parameters()]
+
+
 def create_3d_parallel_model(build_layer, num_layers: int, mesh: DeviceMesh) -> list:
     """This rank's layers: the contiguous slice of `num_layers` owned by its pipeline coordinate; `build_layer(i)`
     constructs layer i (tensor-parallel inside, if it wants, from the mesh's tp group)."""

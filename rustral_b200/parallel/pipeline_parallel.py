@@ -223,3 +223,65 @@ def create_pipeline(layers: list, process_group: ProcessGroup, config: PipelineC
 
     params = [p for l in mine for p in (l.parameters() if hasattr(l, "parameters") else [])]
     return PipelineParallel(PipelineStage(r, S, fwd, params), process_group, config, act_shape, act_dtype, device)
+
+
+class SequentialStage:
+    """A list of layers run in order: the stage type of the in-process `PipelineParallelTrainer`
+    (crates/distributed/src/tensor_parallel.rs:192-236)."""
+
+    def __init__(self, stage_id: int, num_stages: int, micro_batch_size: int):
+        self.stage_id, self.num_stages, self.micro_batch_size = stage_id, num_stages, micro_batch_size
+        self.layers: list = []
+
+    def add_layer(self, layer) -> None:
+        self.layers.append(layer)
+
+    def forward(self, x, ctx=None):
+        for layer in self.layers:
+            x = layer(x, ctx)
+        return x
+
+    def parameters(self) -> list:
+        return [p for l in self.layers if hasattr(l, "parameters") for p in l.parameters()]
+
+
+class PipelineParallelTrainer:
+    """All stages in ONE process, micro-batched (crates/distributed/src/tensor_parallel.rs:242-308): the batch is cut
+    into micro-batches of the first stage's size, every micro-batch runs through all stages, the losses are averaged
+    and (unlike the reference, whose backward returns its argument) gradients flow through torch.autograd and are
+    accumulated over the micro-batches, so one optimizer step follows the call.  The multi-rank pipeline is
+    `PipelineParallel`."""
+
+    def __init__(self, num_stages: int):
+        self.num_stages = num_stages
+        self.stages: list = []
+
+    def add_stage(self, stage: SequentialStage) -> None:
+        if len(self.stages) >= self.num_stages:
+            raise DistributedError("more stages than num_stages")
+        self.stages.append(stage)
+
+    def forward(self, x, ctx=None):
+        for st in self.stages:
+            x = st.forward(x, ctx)
+        return x
+
+    def parameters(self) -> list:
+        return [p for st in self.stages for p in st.parameters()]
+
+    def split_into_micro_batches(self, batch) -> list:
+        mb = self.stages[0].micro_batch_size if self.stages else 1
+        return [batch[i:i + mb] for i in range(0, len(batch), mb)]
+
+    def train_step(self, batch, loss_fn, ctx=None) -> float:
+        """`loss_fn(micro_batch, forward, ctx) -> scalar loss tensor`, where `forward` is this trainer's forward.
+        Returns the mean micro-batch loss; parameter `.grad`s hold the gradient of that mean."""
+        micro = self.split_into_micro_batches(batch)
+        if not micro:
+            return 0.0
+        total = 0.0
+        for mb in micro:
+            loss = loss_fn(mb, self.forward, ctx)
+            (loss / len(micro)).backward()
+            total += float(loss.detach())
+        return total / len(micro)

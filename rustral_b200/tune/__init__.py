@@ -433,3 +433,145 @@ class TuningSession:
         cfg, t = self.best
         return {"kernel": self.kernel, "shape_key": self.shape_key, "num_trials": len(self.trials), "best_config": cfg,
                 "best_time_us": t, "elapsed_s": (self.finished_at or time.time()) - self.started_at}
+
+
+# ---------------------------------------------------------------------------------------------- typed op configurations
+class MatmulAlgorithm(enum.Enum):
+    """Matmul implementation families (crates/autotuner/src/kernel_config.rs:266-300).  The first seven are the
+    reference's names; the last three are what the sm_100a GEMM actually offers."""
+    NAIVE = "naive"
+    TILED = "tiled"
+    TILED_VECTORIZED = "tiled_vectorized"
+    STRASSEN = "strassen"
+    WARP_SPECIALIZED = "warp_specialized"
+    TENSOR_CORE_WMMA = "tensor_core_wmma"
+    TENSOR_CORE_MMA = "tensor_core_mma"
+    TCGEN05_ONE_CTA = "tcgen05_one_cta"          # 128 x {64,128,192,256} tiles, one CTA per tile
+    TCGEN05_TWO_CTA = "tcgen05_two_cta"          # 256 x 256 tiles on a CTA pair (cta_group::2)
+    TCGEN05_SPLIT_K = "tcgen05_split_k"          # one-CTA tiles with a deterministic split-K fold
+
+    def uses_tensor_cores(self) -> bool:
+        return self in (MatmulAlgorithm.TENSOR_CORE_WMMA, MatmulAlgorithm.TENSOR_CORE_MMA, MatmulAlgorithm.TCGEN05_ONE_CTA,
+                        MatmulAlgorithm.TCGEN05_TWO_CTA, MatmulAlgorithm.TCGEN05_SPLIT_K)
+
+    def recommended_tile(self) -> tuple:
+        """(m, n, k) of one tile."""
+        return {MatmulAlgorithm.NAIVE: (32, 32, 1), MatmulAlgorithm.TILED: (128, 128, 8),
+                MatmulAlgorithm.TILED_VECTORIZED: (128, 128, 16), MatmulAlgorithm.STRASSEN: (256, 256, 64),
+                MatmulAlgorithm.WARP_SPECIALIZED: (256, 128, 64), MatmulAlgorithm.TENSOR_CORE_WMMA: (128, 256, 32),
+                MatmulAlgorithm.TENSOR_CORE_MMA: (256, 256, 64), MatmulAlgorithm.TCGEN05_ONE_CTA: (128, 256, 64),
+                MatmulAlgorithm.TCGEN05_TWO_CTA: (256, 256, 64), MatmulAlgorithm.TCGEN05_SPLIT_K: (128, 128, 64)}[self]
+
+
+class ConvAlgorithm(enum.Enum):
+    DIRECT = "direct"
+    WINOGRAD = "winograd"
+    FFT = "fft"
+    IM2COL = "im2col"
+    IMPLICIT_GEMM = "implicit_gemm"
+
+
+class ReduceAlgorithm(enum.Enum):
+    TREE = "tree"
+    WARP_SHUFFLE = "warp_shuffle"
+    ATOMIC = "atomic"
+    TWO_PASS = "two_pass"
+
+
+@dataclass(frozen=True)
+class OpConfig:
+    """A typed kernel configuration (crates/autotuner/src/lib.rs:79-87): `kind` is one of matmul / conv2d / reduce /
+    elementwise / attention and `fields` holds that variant's members.  `to_kernel_config()` gives the dict the
+    tunable kernels of this package take."""
+    kind: str
+    fields: tuple                                  # sorted (name, value) pairs: hashable and comparable
+
+    @classmethod
+    def _make(cls, kind, **kw):
+        return cls(kind, tuple(sorted(kw.items())))
+
+    @classmethod
+    def matmul(cls, algorithm: MatmulAlgorithm, block_m: int, block_n: int, block_k: int, num_stages: int, splits: int = 1,
+               group_m: int = 8):
+        return cls._make("matmul", algorithm=algorithm, block_m=block_m, block_n=block_n, block_k=block_k,
+                         num_stages=num_stages, splits=splits, group_m=group_m)
+
+    @classmethod
+    def conv2d(cls, algorithm: ConvAlgorithm, tile_size: int, num_filters: int):
+        return cls._make("conv2d", algorithm=algorithm, tile_size=tile_size, num_filters=num_filters)
+
+    @classmethod
+    def reduce(cls, block_size: int, items_per_thread: int, algorithm: ReduceAlgorithm):
+        return cls._make("reduce", block_size=block_size, items_per_thread=items_per_thread, algorithm=algorithm)
+
+    @classmethod
+    def elementwise(cls, block_size: int, items_per_thread: int, vector_width: int):
+        return cls._make("elementwise", block_size=block_size, items_per_thread=items_per_thread, vector_width=vector_width)
+
+    @classmethod
+    def attention(cls, block_size_m: int, block_size_n: int, use_flash: bool):
+        return cls._make("attention", block_size_m=block_size_m, block_size_n=block_size_n, use_flash=use_flash)
+
+    def __getitem__(self, name):
+        return dict(self.fields)[name]
+
+    def to_kernel_config(self) -> dict:
+        d = dict(self.fields)
+        if self.kind == "matmul":
+            return {"block_n": d["block_n"], "splits": d["splits"], "group_m": d["group_m"]}
+        return {k: (v.value if isinstance(v, enum.Enum) else v) for k, v in d.items()}
+
+    @classmethod
+    def from_gemm_config(cls, config: dict, M: int = 0) -> "OpConfig":
+        """Typed view of a `GemmKernel` configuration dict (0 = the kernel's own cost model picks)."""
+        bn, sp = int(config.get("block_n", 0)), int(config.get("splits", 0))
+        if sp > 1:
+            alg = MatmulAlgorithm.TCGEN05_SPLIT_K
+        elif bn == 256 and M > 128:
+            alg = MatmulAlgorithm.TCGEN05_TWO_CTA
+        else:
+            alg = MatmulAlgorithm.TCGEN05_ONE_CTA
+        return cls.matmul(alg, 256 if alg is MatmulAlgorithm.TCGEN05_TWO_CTA else 128, bn, 64,
+                          6 if alg is MatmulAlgorithm.TCGEN05_TWO_CTA else 4, max(sp, 1) if sp else 0, int(config.get("group_m", 0)))
+
+
+class ConfigurableKernel:
+    """A kernel object that carries its current typed configuration (crates/autotuner/src/lib.rs:107-113)."""
+
+    _op_config: OpConfig | None = None
+
+    def apply_config(self, config: OpConfig) -> None:
+        self._op_config = config
+
+    def current_config(self) -> OpConfig | None:
+        return self._op_config
+
+
+class KernelFactory:
+    """Hands out (kernel, configuration) pairs: the cached winner when the tuner's cache has one for the kernel's
+    shape bucket, otherwise the result of a tuning run (crates/autotuner/src/lib.rs:186-232).  `default_configs`
+    are the configurations used when tuning is disabled."""
+
+    def __init__(self, tuner: AutoTuner | None = None):
+        self.tuner = tuner or AutoTuner(TunerConfig.fast())
+        self.default_configs = {
+            "matmul_default": OpConfig.matmul(MatmulAlgorithm.TCGEN05_ONE_CTA, 128, 256, 64, 4, 0, 0),
+            "conv2d_default": OpConfig.conv2d(ConvAlgorithm.IMPLICIT_GEMM, 16, 64),
+            "attention_default": OpConfig.attention(128, 128, True),
+            "reduce_default": OpConfig.reduce(256, 8, ReduceAlgorithm.TWO_PASS),
+            "elementwise_default": OpConfig.elementwise(256, 8, 8)}
+
+    def get_kernel(self, kernel: TunableKernel):
+        """Returns (kernel, config dict).  A `ConfigurableKernel` also gets the typed configuration applied."""
+        cfg = self.tuner.config
+        config = None
+        if cfg.enabled and cfg.use_cache:
+            e = self.tuner.cache.get_config(kernel.kernel_id, cfg.device_id, cfg.dtype, kernel.input_signature())
+            if e is not None:
+                self.tuner.stats["cache_hits"] += 1
+                config = dict(e.config)
+        if config is None:
+            config = self.tuner.tune(kernel).config
+        if isinstance(kernel, ConfigurableKernel) and {"block_n", "splits"} <= set(config):
+            kernel.apply_config(OpConfig.from_gemm_config(config, getattr(kernel, "M", 0)))
+        return kernel, config

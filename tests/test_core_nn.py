@@ -334,3 +334,95 @@ def test_search_strategies_tuning_session_and_tui_hook():
     hook.on_epoch(SimpleNamespace(epoch=3, train_loss=1.25))
     assert hook.dashboard.epoch == 3 and hook.dashboard.losses[-1] == 1.25
     hook.close()
+
+
+def test_grad_ext_tensor_view_and_tape_trainer():
+    """Gradient lookup by parameter, the zero-copy host view, and TapeTrainer end to end on a separable toy problem."""
+    import numpy as np
+    from rustral_b200.autograd import GradExt, Tape
+    from rustral_b200.core import CpuBackend, ForwardCtx, TensorView
+    from rustral_b200.core.errors import InvalidArgument
+    from rustral_b200.core.module import Module, Trainable
+    from rustral_b200.nn.linear import LinearBuilder
+    from rustral_b200.optim import Adam
+    from rustral_b200.runtime.tape_trainer import SupervisedTapeModel, Trainer
+    be = CpuBackend()
+    lin = LinearBuilder(3, 2).with_bias().seed(1).build(be)
+    tape = Tape(ForwardCtx.train(be))
+    x = tape.constant(torch.tensor([[1.0, 2.0, 3.0]]))
+    w, b = tape.watch_parameter(lin.weight), tape.watch_parameter(lin.bias)
+    loss = tape.sum_all_tape(tape.linear_tape(x, w, b))
+    assert GradExt.gradient(lin.weight, tape) is None                       # no backward yet
+    store = tape.backward(loss)
+    g = GradExt.gradient(lin.weight, tape)
+    assert torch.equal(g, torch.tensor([[1.0, 2.0, 3.0], [1.0, 2.0, 3.0]]))
+    assert torch.equal(GradExt.gradient_from_store(lin.bias, store, tape.param_map), torch.ones(2))
+    assert GradExt.gradient_from_store(lin.bias, store) is store.param_gradient(lin.bias)
+    t = torch.arange(6, dtype=torch.float32).reshape(2, 3)
+    v = TensorView.as_slice_f32(t)
+    v[0] = 9.0
+    assert isinstance(v, np.ndarray) and v.shape == (6,) and float(t[0, 0]) == 9.0      # shares memory
+    with pytest.raises(InvalidArgument):
+        TensorView.as_slice_f32(t.t())
+
+    class Toy(Module, Trainable, SupervisedTapeModel):
+        def __init__(self):
+            self.fc = LinearBuilder(2, 2).with_bias().seed(3).build(be)
+
+        def forward(self, x, ctx):
+            return self.fc(x, ctx)
+
+        def forward_tape(self, x, tape, ctx):
+            return tape.apply("toy", lambda: self.forward(x, ctx))
+
+    g = torch.Generator().manual_seed(0)
+    xs = torch.randn(64, 2, generator=g)
+    data = [(xs[i], int(xs[i, 0] > xs[i, 1])) for i in range(64)]
+    rep = Trainer.classification(Adam(lr=0.1)).epochs(15).batch_size(16).seed(0).fit(be, Toy(), data)
+    assert len(rep.epochs) == 15 and rep.accuracy > 0.9 and rep.epochs[-1].mean_loss < 0.5 * rep.epochs[0].mean_loss
+    assert rep.throughput.examples_per_sec > 0
+
+
+def test_kernel_factory_and_op_config():
+    from rustral_b200.tune import (AutoTuner, ConfigCache, ConfigSpace, ConfigurableKernel, ConvAlgorithm, KernelFactory,
+                                   MatmulAlgorithm, OpConfig, TunableKernel, TunerConfig)
+    assert MatmulAlgorithm.TCGEN05_TWO_CTA.uses_tensor_cores() and not MatmulAlgorithm.TILED.uses_tensor_cores()
+    assert MatmulAlgorithm.TENSOR_CORE_MMA.recommended_tile() == (256, 256, 64)
+    a = OpConfig.matmul(MatmulAlgorithm.TILED, 128, 128, 32, 2)
+    assert a == OpConfig.matmul(MatmulAlgorithm.TILED, 128, 128, 32, 2) and a != OpConfig.conv2d(ConvAlgorithm.DIRECT, 16, 64)
+    assert a["block_k"] == 32 and a.to_kernel_config() == {"block_n": 128, "splits": 1, "group_m": 8}
+    assert OpConfig.from_gemm_config({"block_n": 256, "splits": 1, "group_m": 8}, M=4096)["algorithm"] is MatmulAlgorithm.TCGEN05_TWO_CTA
+    assert OpConfig.from_gemm_config({"block_n": 128, "splits": 4, "group_m": 8})["algorithm"] is MatmulAlgorithm.TCGEN05_SPLIT_K
+
+    class Fake(TunableKernel, ConfigurableKernel):
+        kernel_id = "fake_gemm"
+        M = 4096
+        calls = []
+
+        def config_space(self):
+            return ConfigSpace({"block_n": [128, 256], "splits": [1, 2], "group_m": [8]})
+
+        def default_config(self):
+            return {"block_n": 128, "splits": 2, "group_m": 8}
+
+        def input_signature(self):
+            return "m4k_n4k_k4k"
+
+        def with_config(self, config):
+            import time as _t
+            cost = 0.002 if (config["block_n"], config["splits"]) == (256, 1) else 0.004
+            return lambda: (Fake.calls.append(dict(config)), _t.sleep(cost))
+
+    import tempfile
+    with tempfile.TemporaryDirectory() as d:
+        cfg = TunerConfig.fast()
+        cfg.device_id, cfg.min_improvement_pct, cfg.warmup, cfg.timing = "test", 5.0, 1, 3
+        tuner = AutoTuner(cfg, ConfigCache(os.path.join(d, "cache.json"), "test"))
+        fac = KernelFactory(tuner)
+        k, conf = fac.get_kernel(Fake())
+        assert (conf["block_n"], conf["splits"]) == (256, 1) and tuner.stats["tuned"] == 1
+        assert k.current_config()["algorithm"] is MatmulAlgorithm.TCGEN05_TWO_CTA
+        n = len(Fake.calls)
+        _, conf2 = fac.get_kernel(Fake())                      # second request: served from the cache, nothing timed
+        assert conf2 == conf and len(Fake.calls) == n and tuner.stats["cache_hits"] == 1
+        assert "matmul_default" in fac.default_configs and fac.default_configs["conv2d_default"].kind == "conv2d"

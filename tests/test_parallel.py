@@ -374,3 +374,41 @@ def test_step_watchdog_and_profiler_nvtx_flag():
     with prof.guard("op"):
         pass
     assert prof.stats["op"].count == 1 and prof.nvtx
+
+
+def test_in_process_pipeline_trainer_and_3d_layer():
+    """The single-process micro-batched pipeline trainer accumulates the gradient of the mean loss; Parallel3DLayer
+    is a column-parallel linear over the tensor group."""
+    from rustral_b200.core import CpuBackend, ForwardCtx
+    from rustral_b200.nn.linear import LinearBuilder
+    from rustral_b200.parallel.parallelism_3d import Parallel3DLayer
+    from rustral_b200.parallel.pipeline_parallel import PipelineParallelTrainer, SequentialStage
+    from rustral_b200.parallel.process_group import DistributedError, ProcessGroup
+    be = CpuBackend()
+    tr = PipelineParallelTrainer(2)
+    l1, l2 = LinearBuilder(4, 8).with_bias().seed(1).build(be), LinearBuilder(8, 2).with_bias().seed(2).build(be)
+    s0, s1 = SequentialStage(0, 2, 4), SequentialStage(1, 2, 4)
+    s0.add_layer(l1)
+    s1.add_layer(l2)
+    tr.add_stage(s0)
+    tr.add_stage(s1)
+    with pytest.raises(DistributedError):
+        tr.add_stage(SequentialStage(2, 2, 4))
+    x = torch.randn(10, 4, generator=torch.Generator().manual_seed(0))
+    ctx = ForwardCtx.train(be)
+    loss_fn = lambda mb, fwd, c: fwd(mb, c).pow(2).mean()
+    assert [len(m) for m in tr.split_into_micro_batches(x)] == [4, 4, 2]
+    loss = tr.train_step(x, loss_fn, ctx)
+    ref = sum(l2(l1(m, ctx), ctx).pow(2).mean() for m in (x[:4], x[4:8], x[8:])) / 3
+    assert abs(loss - float(ref)) < 1e-6 and len(tr.parameters()) == 4
+    g_ref = torch.autograd.grad(ref, l1.weight.tensor)[0]
+    assert torch.allclose(l1.weight.tensor.grad, g_ref, atol=1e-6)
+
+    def worker(pg):
+        layer = Parallel3DLayer(6, 8, pg, be, gather_output=True, seed=5)
+        y = layer(torch.ones(3, 6))
+        return y, [n for n, _ in layer.named_parameters()]
+    outs = run_ranks(2, worker)
+    full = Parallel3DLayer(6, 8, ProcessGroup.new_single_process(), be, seed=5)(torch.ones(3, 6))
+    for y, names in outs:
+        assert y.shape == (3, 8) and torch.allclose(y, full, atol=1e-6) and names == ["linear.weight"]
