@@ -5,6 +5,7 @@ pipeline parallel (1F1B) and expert parallel, one rank per GPU under torch.distr
         -m rustral_b200.bench.parallel_train --config llama-8b --tp 8 --global-batch 64 --micro-batch 1
     ... --config llama-8b --tp 4 --pp 2 --global-batch 64 --micro-batch 8          (8 micro-batches, 1F1B)
     ... --config moe-24l --ep 8 --global-batch 128 --micro-batch 4
+    ... --config llama-8b --cp 8 --seq 65536 --global-batch 1 --micro-batch 1      (context parallel, 8192 tokens per GPU)
     add --unfused for the same run over NCCL collectives (tensor parallel) as the comparison arm
 
 Synthetic data (uniform random token ids from a seed), random-init weights, AdamW with fp32 master weights.
@@ -51,6 +52,9 @@ def main(argv=None):
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--ep", type=int, default=1)
     ap.add_argument("--fsdp", type=int, default=1, help="data-parallel ranks with ZeRO-3 sharded block weights (fused all-gather)")
+    ap.add_argument("--cp", type=int, default=1, help="context-parallel ranks: every sequence is split over them (ring attention "
+                    "over NVLink peer memory)")
+    ap.add_argument("--cp-contiguous", action="store_true", help="contiguous instead of striped token assignment")
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--global-batch", type=int, default=8)
@@ -72,8 +76,10 @@ def main(argv=None):
         raise SystemExit("expert parallelism is combined with data parallelism only")
     if a.fsdp > 1 and (a.tp > 1 or a.pp > 1 or a.ep > 1):
         raise SystemExit("--fsdp is combined with plain data parallelism only")
-    if a.tp * a.pp * a.ep * a.fsdp != world:
-        raise SystemExit(f"tp*pp*ep*fsdp = {a.tp * a.pp * a.ep * a.fsdp} but WORLD_SIZE = {world}")
+    if a.cp > 1 and (a.tp > 1 or a.pp > 1 or a.ep > 1 or a.fsdp > 1):
+        raise SystemExit("--cp is combined with plain data parallelism only")
+    if a.tp * a.pp * a.ep * a.fsdp * a.cp != world:
+        raise SystemExit(f"tp*pp*ep*fsdp*cp = {a.tp * a.pp * a.ep * a.fsdp * a.cp} but WORLD_SIZE = {world}")
 
     from .. import _native
     from ..models.parallel_lm import MixedPrecisionAdamW, ParallelDecoderLM
@@ -83,7 +89,11 @@ def main(argv=None):
 
     tp_pg = pp_pg = None
     fused_tp = ep_ctx = None
-    tp_idx, pp_idx = (rank % a.tp, rank // a.tp) if (a.ep == 1 and a.fsdp == 1) else (0, 0)
+    tp_idx, pp_idx = (rank % a.tp, rank // a.tp) if (a.ep == 1 and a.fsdp == 1 and a.cp == 1) else (0, 0)
+    cp_ctx = None
+    if a.cp > 1:
+        from ..parallel.peer_ring import PeerRing
+        cp_ctx = PeerRing(dist.group.WORLD, dev, a.micro_batch * (S // a.cp) * cfg.n_kv_head * cfg.head_dim)
     fsdp_ctx = None
     if a.fsdp > 1:
         from ..parallel.fused_tp import FusedTP
@@ -109,7 +119,8 @@ def main(argv=None):
     per_stage = cfg.n_layer // a.pp
     model = ParallelDecoderLM(cfg, dev, tp_pg=tp_pg, fused_tp=fused_tp, ep=ep_ctx,
                               first_layer=pp_idx * per_stage, last_layer=(pp_idx + 1) * per_stage if pp_idx < a.pp - 1 else cfg.n_layer,
-                              has_embed=pp_idx == 0, has_head=pp_idx == a.pp - 1, seed=1, fsdp=fsdp_ctx)
+                              has_embed=pp_idx == 0, has_head=pp_idx == a.pp - 1, seed=1, fsdp=fsdp_ctx,
+                              cp=cp_ctx, cp_striped=not a.cp_contiguous, dp_group=dist.group.WORLD if cp_ctx is not None else None)
     # expert parallel: ZeRO-1 over the data-parallel ranks for the dense (replicated) parameters
     opt = MixedPrecisionAdamW(model, lr=a.lr, use_zero1=a.ep > 1)
     dp = a.ep * a.fsdp                                         # data-parallel replicas (these ranks see different data)
@@ -180,6 +191,9 @@ def main(argv=None):
     if world > 1 and a.pp > 1:
         lt = torch.nan_to_num(lt, nan=0.0)
         dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+    if a.cp > 1:                                               # every rank holds the mean over ITS tokens
+        dist.all_reduce(lt)
+        lt /= world
     tokens = a.global_batch * S
     if rank == 0:
         ms_step = float(ms)
@@ -188,7 +202,8 @@ def main(argv=None):
             "n_gpus": world, "ms_per_step": round(ms_step, 2), "steps": a.steps, "warmup": a.warmup, "dtype": "bf16",
             "config": {"model": a.config, "layers": cfg.n_layer, "d_model": cfg.d_model, "seq_len": S,
                        "global_batch": a.global_batch, "micro_batch": a.micro_batch,
-                       "parallelism": f"tp{a.tp}-pp{a.pp}-ep{a.ep}" + (f"-fsdp{a.fsdp}" if a.fsdp > 1 else ""),
+                       "parallelism": f"tp{a.tp}-pp{a.pp}-ep{a.ep}" + (f"-fsdp{a.fsdp}" if a.fsdp > 1 else "") +
+                                      (f"-cp{a.cp}{'c' if a.cp_contiguous else 's'}" if a.cp > 1 else ""),
                        "fused": not a.unfused,
                        "params_total": cfg.num_params(), "params_local": model.local_param_count(),
                        "zero1_dense": a.ep > 1, "optimizer_state_bytes_local": opt.state_bytes()},
@@ -203,6 +218,8 @@ def main(argv=None):
         ep_ctx.close()
     if fsdp_ctx is not None:
         fsdp_ctx.close()
+    if cp_ctx is not None:
+        cp_ctx.close()
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -109,13 +109,23 @@ class ParallelDecoderLM:
 
     def __init__(self, cfg: ParallelLMConfig, device, *, tp_pg=None, fused_tp=None, ep=None, dp_group=None,
                  first_layer: int = 0, last_layer: int | None = None, has_embed: bool = True, has_head: bool = True,
-                 seed: int = 0, fsdp=None):
+                 seed: int = 0, fsdp=None, cp=None, cp_striped: bool = True):
         """`fsdp` (a parallel.fused_tp.FusedTP over the data-parallel group): ZeRO-3 for the block weights.  Each rank
         keeps 1/W of the rows of every projection in symmetric memory; the forward all-gathers them inside the
-        consuming GEMM and the weight gradient is reduce-scattered inside its GEMM (FSDPLinearFn)."""
+        consuming GEMM and the weight gradient is reduce-scattered inside its GEMM (FSDPLinearFn).
+
+        `cp` (a parallel.peer_ring.PeerRing): context parallelism.  Every rank of the ring holds 1/W of the tokens of
+        each sequence (striped: token t on rank t mod W, which balances causal attention; or contiguous), runs all
+        layers on them, and attention pulls the other ranks' K / V over NVLink.  Parameters are replicated over the
+        ring, so `dp_group` must span it: their gradients are averaged like data-parallel gradients."""
         self.cfg, self.device = cfg, torch.device(device)
         self.tp_pg, self.fused_tp, self.ep, self.dp_group = tp_pg, fused_tp, ep, dp_group
         self.fsdp = fsdp
+        self.cp, self.cp_striped = cp, cp_striped
+        if cp is not None and (tp_pg is not None or ep is not None or fsdp is not None):
+            raise ValueError("context parallelism is combined with plain data parallelism only")
+        if cp is not None and dp_group is None:
+            raise ValueError("context parallelism needs dp_group (a group spanning the ring) for the gradient average")
         self.fsdp_shards: dict = {}
         if fsdp is not None and (tp_pg is not None or ep is not None):
             raise ValueError("fsdp is combined with plain data parallelism only")
@@ -222,16 +232,20 @@ class ParallelDecoderLM:
         from ..parallel.tensor_parallel import _ReduceScatterSeq
         return _ReduceScatterSeq.apply(ops.linear(x, w), self.tp_pg) + residual
 
-    def _block(self, l: int, x, batch: int, seq: int):
+    def _block(self, l: int, x, batch: int, seq: int, positions=None):
         c, P, p = self.cfg, self.params, f"l{l}."
         hd = c.head_dim
         hq, hk = c.n_head // self.tp, c.n_kv_head // self.tp
         h = ops.rms_norm(x, P[p + "attn_norm"], c.eps)
         qkv = self._col(h, p + "wqkv")                                   # [B*S, (hq + 2 hk) * hd]
-        q = rotary.rope(qkv[:, :hq * hd].reshape(batch, seq, hq, hd), seq, theta=c.rope_theta)
-        k = rotary.rope(qkv[:, hq * hd:(hq + hk) * hd].reshape(batch, seq, hk, hd), seq, theta=c.rope_theta)
+        q = rotary.rope(qkv[:, :hq * hd].reshape(batch, seq, hq, hd), seq, positions=positions, theta=c.rope_theta)
+        k = rotary.rope(qkv[:, hq * hd:(hq + hk) * hd].reshape(batch, seq, hk, hd), seq, positions=positions,
+                        theta=c.rope_theta)
         v = qkv[:, (hq + hk) * hd:].reshape(batch, seq, hk, hd)
-        o = ops.flash_attention(q, k, v, True)
+        if self.cp is not None:
+            o = self.cp.attention(q, k, v.contiguous(), causal=True, striped=self.cp_striped)
+        else:
+            o = ops.flash_attention(q, k, v, True)
         x = self._row(o.reshape(batch * seq, hq * hd), p + "wo", x)
         h = ops.rms_norm(x, P[p + "mlp_norm"], c.eps)
         aux = None
@@ -261,10 +275,20 @@ class ParallelDecoderLM:
         flat = ids.reshape(-1)[self.local_rows(B, S)].contiguous()
         return ops.embedding(flat, self.params["wte"])
 
-    def blocks(self, x, batch: int, seq: int):
+    def cp_positions(self, seq: int) -> torch.Tensor:
+        """Positions (int64, ascending) of the tokens this context-parallel rank holds of a `seq`-token sequence."""
+        W, r = self.cp.world, self.cp.rank
+        if seq % W:
+            raise ValueError("the sequence length must be divisible by the context-parallel size")
+        if self.cp_striped:
+            return torch.arange(r, seq, W, device=self.device)
+        return torch.arange(r * (seq // W), (r + 1) * (seq // W), device=self.device)
+
+    def blocks(self, x, batch: int, seq: int, positions=None):
+        """`positions` (int64 [batch * seq], context parallelism): the position of every local token in its sequence."""
         aux_total = None
         for l in range(self.first_layer, self.last_layer):
-            x, aux = self._block(l, x, batch, seq)
+            x, aux = self._block(l, x, batch, seq, positions)
             if aux is not None:
                 aux_total = aux if aux_total is None else aux_total + aux
         return x, aux_total
@@ -283,7 +307,13 @@ class ParallelDecoderLM:
         """tokens [B, S + 1] -> scalar training loss (next-token cross-entropy + aux_coef * load-balancing loss)."""
         ids, targets = tokens[:, :-1], tokens[:, 1:]
         B, S = ids.shape
-        x, aux = self.blocks(self.embed(ids), B, S)
+        positions = None
+        if self.cp is not None:                      # this rank's tokens of every sequence; the loss is their mean
+            pos = self.cp_positions(S)
+            ids, targets = ids[:, pos].contiguous(), targets[:, pos].contiguous()
+            S = pos.numel()
+            positions = pos.repeat(B)
+        x, aux = self.blocks(self.embed(ids), B, S, positions)
         loss = self.loss(x, targets)
         if aux is not None:
             loss = loss + self.cfg.aux_coef * aux / (self.last_layer - self.first_layer)
