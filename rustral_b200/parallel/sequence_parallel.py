@@ -249,6 +249,77 @@ class RingAttention:
     __call__ = compute
 
 
+class _SeqToHeads(torch.autograd.Function):
+    """[B, S/W, H, D] sharded by sequence -> [B, S, H/W, D] sharded by heads (one all-to-all); the backward pass is the
+    inverse exchange."""
+
+    @staticmethod
+    def forward(ctx, x, pg):
+        ctx.pg = pg
+        return _seq_to_heads(x, pg)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _heads_to_seq(g.contiguous(), ctx.pg), None
+
+
+class _HeadsToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, pg):
+        ctx.pg = pg
+        return _heads_to_seq(x, pg)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _seq_to_heads(g.contiguous(), ctx.pg), None
+
+
+def _seq_to_heads(x, pg: ProcessGroup):
+    W = pg.world_size
+    B, Sl, H, D = x.shape
+    if H % W:
+        raise DistributedError("the number of heads must be divisible by the sequence-parallel size")
+    # chunk r: this rank's tokens of head group r, leading dimension = local sequence for the exchange
+    chunks = [x[:, :, r * (H // W):(r + 1) * (H // W)].permute(1, 0, 2, 3).contiguous() for r in range(W)]
+    got = pg.all_to_all(chunks)                               # got[src]: [Sl, B, H/W, D], rank src's tokens
+    return torch.cat(got, 0).permute(1, 0, 2, 3).contiguous()
+
+
+def _heads_to_seq(x, pg: ProcessGroup):
+    W = pg.world_size
+    B, S, Hl, D = x.shape
+    if S % W:
+        raise DistributedError("the sequence length must be divisible by the sequence-parallel size")
+    Sl = S // W
+    chunks = [x[:, r * Sl:(r + 1) * Sl].permute(2, 0, 1, 3).contiguous() for r in range(W)]     # [Hl, B, Sl, D]
+    got = pg.all_to_all(chunks)                               # got[src]: head group src of this rank's tokens
+    return torch.cat(got, 0).permute(1, 2, 0, 3).contiguous()
+
+
+class UlyssesAttention:
+    """Sequence parallelism by head exchange: the sequence-sharded q / k / v ([B, S/W, H, D], contiguous shards) are
+    all-to-all'ed into head shards over the FULL sequence ([B, S, H/W, D]), attention runs locally with the ordinary
+    flash kernel (causal masks need no special handling), and one more all-to-all returns the output to sequence
+    shards.  Four all-to-alls per layer move 4/W of the activations each; against ring attention this trades the
+    W - 1 K/V block pulls for a bound of W <= number of KV heads.  The reference has no such path (its only
+    all-to-all mention is a configuration flag, crates/nn/src/expert_choice.rs:49)."""
+
+    def __init__(self, process_group: ProcessGroup, causal: bool = True):
+        self.pg, self.causal = process_group, causal
+
+    def compute(self, q, k, v, scale: float | None = None):
+        W = self.pg.world_size
+        if k.shape[2] % W or q.shape[2] % W:
+            raise DistributedError("query and KV head counts must be divisible by the sequence-parallel size")
+        if W == 1:
+            return attn_ops.flash_attention(q, k, v, self.causal, scale)
+        qh, kh, vh = (_SeqToHeads.apply(t, self.pg) for t in (q, k, v))
+        o = attn_ops.flash_attention(qh, kh, vh, self.causal, scale)
+        return _HeadsToSeq.apply(o, self.pg)
+
+    __call__ = compute
+
+
 @dataclass
 class ContextParallelConfig:
     num_devices: int

@@ -412,3 +412,32 @@ def test_in_process_pipeline_trainer_and_3d_layer():
     full = Parallel3DLayer(6, 8, ProcessGroup.new_single_process(), be, seed=5)(torch.ones(3, 6))
     for y, names in outs:
         assert y.shape == (3, 8) and torch.allclose(y, full, atol=1e-6) and names == ["linear.weight"]
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_ulysses_attention_matches_full_attention(causal):
+    """Head-exchange sequence parallelism: forward and all three gradients equal single-device attention (GQA)."""
+    from rustral_b200.ops.attention import attention_reference
+    from rustral_b200.parallel.process_group import DistributedError
+    from rustral_b200.parallel.sequence_parallel import UlyssesAttention, gather_sequence, shard_sequence
+    torch.manual_seed(1)
+    Bz, S, H, Hk, D, W = 2, 12, 8, 4, 8, 4
+    q, k, v, do = torch.randn(Bz, S, H, D), torch.randn(Bz, S, Hk, D), torch.randn(Bz, S, Hk, D), torch.randn(Bz, S, H, D)
+    qr, kr, vr = (t.clone().requires_grad_() for t in (q, k, v))
+    ref = attention_reference(qr, kr, vr, causal)
+    (ref * do).sum().backward()
+
+    def fn(pg):
+        ql, kl, vl = (shard_sequence(t, W, pg.rank).requires_grad_() for t in (q, k, v))
+        o = UlyssesAttention(pg, causal)(ql, kl, vl)
+        (o * shard_sequence(do, W, pg.rank)).sum().backward()
+        return o.detach(), ql.grad, kl.grad, vl.grad
+    out = run_ranks(W, fn)
+    for i, want in enumerate((ref.detach(), qr.grad, kr.grad, vr.grad)):
+        assert torch.allclose(gather_sequence([o[i] for o in out]), want, atol=2e-6), i
+
+    def bad(pg):
+        with pytest.raises(DistributedError):
+            UlyssesAttention(pg)(torch.randn(1, 4, 3, 8), torch.randn(1, 4, 3, 8), torch.randn(1, 4, 3, 8))
+        return True
+    assert all(run_ranks(2, bad))
