@@ -2,10 +2,9 @@
 //
 // Decode attention is bandwidth-bound (every cached key and value is read once per step), so the kernel is built
 // around memory access and parallelism: one CTA per (sequence, KV head, 256-token slice of the context) serves all
-// query heads of that group (split-KV, so a batch of 32 sequences still fills 148 SMs); K rows are fetched
-// coalesced into a padded shared tile and scored with one lane per cached token, the weighted sum of values runs
-// with one lane per slice of the head dimension (coalesced), and a second kernel merges the slices'
-// (max, sum, output) triples.
+// query heads of that group (split-KV, so a batch of 32 sequences still fills 148 SMs); K and V rows are fetched
+// coalesced into a padded shared tile, the group's heads are the rows of mma.sync tensor-core tiles for both
+// Q K^T and P V, and a second kernel merges the slices' (max, sum, output) triples.
 //
 // The reference's PagedCache is block-table bookkeeping without tensor storage and its KVCache::append drops
 // the new entries (crates/nn/src/kv_cache.rs:172-216,382-432); this is the storage and the kernel they lack.
@@ -34,156 +33,209 @@ kv_append_kernel(const __nv_bfloat16* __restrict__ k_new, long long ld_k, const 
   }
 }
 
-constexpr int kMaxGroup = 8;     // query heads per KV head served by one CTA pass
+constexpr int kMaxGroup = 16;    // query heads per KV head served by one CTA pass (the M of the mma tile)
 constexpr int kPaWarps = 4;
 constexpr int kSplitTokens = 256;          // cached tokens per CTA (split-KV): 2 passes of 32 tokens per warp
 
+__device__ __forceinline__ void pa_ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void pa_ldsm_x4_t(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void pa_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pa_pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 // Split-KV decode attention.  One CTA = (sequence, KV head, 256-token slice of the context); the slices of a sequence
 // run on different SMs and a second kernel merges their (max, sum, accumulator) triples.  Inside a CTA a warp takes
-// 32 tokens at a time: the K rows are fetched with fully coalesced 16-byte loads (16 lanes per 256-byte row) into a
-// padded shared tile, then every lane scores ITS token against the group's query heads from shared memory; the value
-// pass walks the tokens with all lanes on one coalesced V row.
+// 32 tokens at a time.  Their K rows and then their V rows are fetched with fully coalesced 16-byte loads (16 lanes
+// per 256-byte row), all loads of a tile in flight at once, into a padded shared tile.  The query heads of the group
+// form the 16 rows of an m16n8k16 tensor-core tile (rows beyond the group are zero): S = Q K^T is 4 n-tiles x D/16
+// k-steps of mma.sync, the softmax runs on the accumulator fragments, and O += P V reuses those fragments as the A
+// operand against ldmatrix.trans-fed V.  One query token per sequence gives M <= 16, far below the 64-row minimum
+// of a tcgen05 tile, which is why this kernel is on the warp-level tensor path; it is bound by the K / V reads.
 template <int D>
-__global__ void __launch_bounds__(kPaWarps * 32)
+__global__ void __launch_bounds__(kPaWarps * 32, 3)
 paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, const __nv_bfloat16* __restrict__ k_cache,
                           const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables, int max_blocks,
                           const int* __restrict__ context_lens, int heads, int kv_heads, int block_size,
                           long long num_blocks, float scale, int g0, int gcount, float* __restrict__ partial, int nsplit) {
-  constexpr int DL = D / 32;                 // head-dim elements per lane in the value pass
-  constexpr int LPR = D / 8;                 // lanes per K row (16-byte pieces)
-  constexpr int RPI = 32 / LPR;              // K rows fetched per warp instruction
-  constexpr int KROW = D + 8;                // padded row (elements): 16-byte reads of 32 different rows hit 32 banks groups
+  constexpr int LPR = D / 8;                 // lanes per K / V row (16-byte pieces)
+  constexpr int RPI = 32 / LPR;              // rows fetched per warp instruction
+  constexpr int NLD = 32 / RPI;              // load instructions per 32-row tile
+  constexpr int KROW = D + 8;                // padded row (elements): ldmatrix rows 272 (144) bytes apart hit distinct banks
+  constexpr int NT = D / 8;                  // n-tiles of the output accumulator
   constexpr int kTileBytes = kPaWarps * 32 * KROW * 2;
   constexpr int kAccBytes = kPaWarps * kMaxGroup * D * 4;
-  __shared__ __align__(16) uint8_t big[kTileBytes > kAccBytes ? kTileBytes : kAccBytes];   // K tiles, later the warp merge
-  __shared__ float q_sh[kMaxGroup][D];
+  __shared__ __align__(16) uint8_t big[kTileBytes > kAccBytes ? kTileBytes : kAccBytes];   // K/V tiles, later the warp merge
+  __shared__ __align__(16) __nv_bfloat16 q_sh[kMaxGroup * KROW];
   __shared__ float m_sh[kPaWarps][kMaxGroup], l_sh[kPaWarps][kMaxGroup];
   const int b = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, tq = lane & 3;   // fragment coordinates: row (and row + 8), column pair
   const int group = heads / kv_heads;
   const int ctx = context_lens[b];
   const int t_begin = sp * kSplitTokens;
   if (t_begin >= ctx) return;
   const int t_end = min(ctx, t_begin + kSplitTokens);
   const int h_base = hk * group + g0;        // first query head of this pass
-  __nv_bfloat16* k_tile = reinterpret_cast<__nv_bfloat16*>(big) + warp * 32 * KROW;
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(big) + warp * 32 * KROW;
+  const uint32_t tile_u32 = smem_u32(tile);
+  const uint32_t q_u32 = smem_u32(q_sh);
 
-  for (int i = threadIdx.x; i < gcount * D; i += blockDim.x) {
-    const int g = i / D, d = i - g * D;
-    q_sh[g][d] = __bfloat162float(q[static_cast<long long>(b) * ld_q + static_cast<long long>(h_base + g) * D + d]) * scale;
+  // the group's query rows as bf16 [16][D] (rows >= gcount are zero)
+  for (int i = threadIdx.x; i < kMaxGroup * LPR; i += blockDim.x) {
+    const int g = i / LPR, c = (i - g * LPR) * 8;
+    uint4 u = make_uint4(0u, 0u, 0u, 0u);
+    if (g < gcount) {
+      const __nv_bfloat16* src = q + static_cast<long long>(b) * ld_q + static_cast<long long>(h_base + g) * D + c;
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = *reinterpret_cast<const uint32_t*>(src + 2 * j);   // rows are 4-byte aligned at least
+      u = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    *reinterpret_cast<uint4*>(q_sh + g * KROW + c) = u;
   }
   __syncthreads();
 
-  float m[kMaxGroup], l[kMaxGroup], acc[kMaxGroup][DL];
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows gq and gq + 8
+  float acc[NT][4];
 #pragma unroll
-  for (int g = 0; g < kMaxGroup; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-#pragma unroll
-    for (int j = 0; j < DL; ++j) acc[g][j] = 0.f;
-  }
+  for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
 
   const long long row = static_cast<long long>(kv_heads) * D;          // elements per cached token
+  const int piece = (lane % LPR) * 8;
   for (int base = t_begin + warp * 32; base < t_end; base += kPaWarps * 32) {
     const int tok = base + lane;
-    const bool valid = tok < t_end;
     long long slot = 0;
-    if (valid) {
+    if (tok < t_end) {
       const int blk_idx = tok / block_size;
       int blk = blk_idx < max_blocks ? block_tables[static_cast<long long>(b) * max_blocks + blk_idx] : -1;
       if (blk < 0 || blk >= num_blocks) blk = 0;                     // corrupt tables read block 0 instead of faulting
       slot = static_cast<long long>(blk) * block_size + (tok - blk_idx * block_size);
     }
     const int n_tok = min(32, t_end - base);
-    // ---- K rows of the 32 tokens -> shared tile (coalesced: LPR lanes per row)
-    __syncwarp();
+    long long off[NLD];                                              // element offset of this lane's piece, per load
 #pragma unroll
-    for (int r0 = 0; r0 < 32; r0 += RPI) {
-      const int r = r0 + lane / LPR;
+    for (int i = 0; i < NLD; ++i) {
+      const int r = i * RPI + lane / LPR;
       const long long slot_r = __shfl_sync(0xffffffffu, slot, r);
-      if (r < n_tok) {
-        const uint4 u = __ldg(reinterpret_cast<const uint4*>(k_cache + slot_r * row + static_cast<long long>(hk) * D) + (lane % LPR));
-        *reinterpret_cast<uint4*>(k_tile + r * KROW + (lane % LPR) * 8) = u;
-      }
+      off[i] = r < n_tok ? slot_r * row + static_cast<long long>(hk) * D + piece : -1;
     }
+    // ---- K rows -> registers (every load of the tile in flight) -> shared tile; rows past the context are zero
+    uint4 stage[NLD];
+#pragma unroll
+    for (int i = 0; i < NLD; ++i)
+      stage[i] = off[i] >= 0 ? __ldg(reinterpret_cast<const uint4*>(k_cache + off[i])) : make_uint4(0u, 0u, 0u, 0u);
+    __syncwarp();                                                    // the previous pass has finished with the tile
+#pragma unroll
+    for (int i = 0; i < NLD; ++i)
+      *reinterpret_cast<uint4*>(tile + (i * RPI + lane / LPR) * KROW + piece) = stage[i];
     __syncwarp();
-    // ---- scores: this lane's token against every query head of the group
-    float s[kMaxGroup];
+    // ---- V rows -> registers: in flight while the scores and the softmax are computed
 #pragma unroll
-    for (int g = 0; g < kMaxGroup; ++g) s[g] = 0.f;
-    if (valid) {
-      const __nv_bfloat16* kp = k_tile + lane * KROW;
-#pragma unroll 4
-      for (int c = 0; c < D; c += 8) {
-        const uint4 u = *reinterpret_cast<const uint4*>(kp + c);
-        const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+    for (int i = 0; i < NLD; ++i)
+      stage[i] = off[i] >= 0 ? __ldg(reinterpret_cast<const uint4*>(v_cache + off[i])) : make_uint4(0u, 0u, 0u, 0u);
+    // ---- S[16 heads, 32 tokens] = Q K^T
+    float s[4][4];
 #pragma unroll
-        for (int g = 0; g < kMaxGroup; ++g) {
-          if (g < gcount) {
-            const float* qq = &q_sh[g][c];
-            s[g] += qq[0] * f0.x + qq[1] * f0.y + qq[2] * f1.x + qq[3] * f1.y + qq[4] * f2.x + qq[5] * f2.y +
-                    qq[6] * f3.x + qq[7] * f3.y;
-          }
-        }
+    for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+    for (int k0 = 0; k0 < D; k0 += 16) {
+      uint32_t a[4];
+      // A fragment: matrices (rows 0-7, k0), (rows 8-15, k0), (rows 0-7, k0 + 8), (rows 8-15, k0 + 8)
+      pa_ldsm_x4(q_u32 + ((lane & 15) * KROW + k0 + (lane >> 4) * 8) * 2, a);
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        uint32_t bfr[4];
+        // B fragments of two n-tiles: (tokens 16np..+7, k0), (same tokens, k0 + 8), (tokens 16np + 8.., k0), (.., k0 + 8)
+        pa_ldsm_x4(tile_u32 + ((np * 16 + (lane & 7) + ((lane >> 4) << 3)) * KROW + k0 + ((lane >> 3) & 1) * 8) * 2, bfr);
+        pa_mma(s[2 * np], a, bfr[0], bfr[1]);
+        pa_mma(s[2 * np + 1], a, bfr[2], bfr[3]);
       }
     }
-    // ---- online softmax over the 32 tokens of this pass
-    float p[kMaxGroup];
+    // ---- online softmax over the 32 tokens; this thread holds 8 of them for rows gq and gq + 8
+    float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int g = 0; g < kMaxGroup; ++g) {
-      if (g < gcount) {
-        const float sv = valid ? s[g] : -INFINITY;
-        const float mx = fmaxf(m[g], warp_max(sv));
-        const float alpha = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - mx);
-        p[g] = valid ? __expf(sv - mx) : 0.f;
-        l[g] = l[g] * alpha + warp_sum(p[g]);
-        m[g] = mx;
+    for (int n = 0; n < 4; ++n) {
 #pragma unroll
-        for (int j = 0; j < DL; ++j) acc[g][j] *= alpha;
+      for (int j = 0; j < 2; ++j) {
+        const bool ok = n * 8 + 2 * tq + j < n_tok;
+        s[n][j] = ok ? s[n][j] * scale : -INFINITY;
+        s[n][2 + j] = ok ? s[n][2 + j] * scale : -INFINITY;
+        mx0 = fmaxf(mx0, s[n][j]);
+        mx1 = fmaxf(mx1, s[n][2 + j]);
       }
     }
-    // ---- values: lanes own slices of the head dimension; two tokens' rows are in flight at a time
-    for (int t = 0; t < n_tok; t += 2) {
-      const bool two = t + 1 < n_tok;
-      const long long slot_a = __shfl_sync(0xffffffffu, slot, t);
-      const long long slot_b = __shfl_sync(0xffffffffu, slot, two ? t + 1 : t);
-      const __nv_bfloat16* va = v_cache + slot_a * row + static_cast<long long>(hk) * D + lane * DL;
-      const __nv_bfloat16* vb = v_cache + slot_b * row + static_cast<long long>(hk) * D + lane * DL;
-      float v0[DL], v1[DL];
-      if (DL == 4) {
-        const uint2 ua = __ldg(reinterpret_cast<const uint2*>(va));
-        const uint2 ub = __ldg(reinterpret_cast<const uint2*>(vb));
-        const float2 a0 = unpack_bf16x2(ua.x), a1 = unpack_bf16x2(ua.y), b0 = unpack_bf16x2(ub.x), b1 = unpack_bf16x2(ub.y);
-        v0[0] = a0.x; v0[1] = a0.y; v0[2] = a1.x; v0[3] = a1.y;
-        v1[0] = b0.x; v1[1] = b0.y; v1[2] = b1.x; v1[3] = b1.y;
-      } else {
-        const float2 a0 = unpack_bf16x2(__ldg(reinterpret_cast<const uint32_t*>(va)));
-        const float2 b0 = unpack_bf16x2(__ldg(reinterpret_cast<const uint32_t*>(vb)));
-        v0[0] = a0.x; v0[1] = a0.y;
-        v1[0] = b0.x; v1[1] = b0.y;
-      }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);          // finite: token 0 of the pass is always valid
+    const float al0 = (m0 == -INFINITY) ? 0.f : __expf(m0 - mn0);
+    const float al1 = (m1 == -INFINITY) ? 0.f : __expf(m1 - mn1);
+    float sum0 = 0.f, sum1 = 0.f;
+    uint32_t pfr[2][4];                                              // P as the A operand of the two 16-token k-steps
 #pragma unroll
-      for (int g = 0; g < kMaxGroup; ++g) {
-        if (g < gcount) {
-          const float pa = __shfl_sync(0xffffffffu, p[g], t);
-          const float pb = two ? __shfl_sync(0xffffffffu, p[g], t + 1) : 0.f;
+    for (int n = 0; n < 4; ++n) {
+      const float p0 = __expf(s[n][0] - mn0), p1 = __expf(s[n][1] - mn0);
+      const float p2 = __expf(s[n][2] - mn1), p3 = __expf(s[n][3] - mn1);
+      sum0 += p0 + p1;
+      sum1 += p2 + p3;
+      pfr[n >> 1][(n & 1) * 2 + 0] = pa_pack_bf16(p0, p1);          // rows gq
+      pfr[n >> 1][(n & 1) * 2 + 1] = pa_pack_bf16(p2, p3);          // rows gq + 8
+    }
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+    l0 = l0 * al0 + sum0;
+    l1 = l1 * al1 + sum1;
+    m0 = mn0;
+    m1 = mn1;
 #pragma unroll
-          for (int j = 0; j < DL; ++j) acc[g][j] += pa * v0[j] + pb * v1[j];
-        }
+    for (int n = 0; n < NT; ++n) {
+      acc[n][0] *= al0; acc[n][1] *= al0; acc[n][2] *= al1; acc[n][3] *= al1;
+    }
+    // ---- V rows replace the K tile; O[16, D] += P[16, 32] V[32, D]
+    __syncwarp();                                                    // every lane has read its K fragments
+#pragma unroll
+    for (int i = 0; i < NLD; ++i)
+      *reinterpret_cast<uint4*>(tile + (i * RPI + lane / LPR) * KROW + piece) = stage[i];
+    __syncwarp();
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+      for (int n2 = 0; n2 < NT / 2; ++n2) {
+        uint32_t bfr[4];
+        // transposed 8x8 blocks: (tokens 16ks..+7, dims 16n2), (tokens +8, same dims), (tokens.., dims + 8), (+8, + 8)
+        pa_ldsm_x4_t(tile_u32 + ((ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KROW + n2 * 16 + (lane >> 4) * 8) * 2, bfr);
+        pa_mma(acc[2 * n2], pfr[ks], bfr[0], bfr[1]);
+        pa_mma(acc[2 * n2 + 1], pfr[ks], bfr[2], bfr[3]);
       }
     }
   }
 
   // ---- merge the warps, write this slice's (max, sum, accumulator) per head
-  __syncthreads();                            // every warp is done with its K tile: the buffer becomes the merge area
+  __syncthreads();                            // every warp is done with its tile: the buffer becomes the merge area
   float (*acc_sh)[kMaxGroup][D] = reinterpret_cast<float (*)[kMaxGroup][D]>(big);
+  if (tq == 0) {
+    m_sh[warp][gq] = m0; l_sh[warp][gq] = l0;
+    m_sh[warp][gq + 8] = m1; l_sh[warp][gq + 8] = l1;
+  }
 #pragma unroll
-  for (int g = 0; g < kMaxGroup; ++g) {
-    if (g < gcount) {
-      if (lane == 0) { m_sh[warp][g] = m[g]; l_sh[warp][g] = l[g]; }
-#pragma unroll
-      for (int j = 0; j < DL; ++j) acc_sh[warp][g][lane * DL + j] = acc[g][j];
-    }
+  for (int n = 0; n < NT; ++n) {
+    *reinterpret_cast<float2*>(&acc_sh[warp][gq][n * 8 + 2 * tq]) = make_float2(acc[n][0], acc[n][1]);
+    *reinterpret_cast<float2*>(&acc_sh[warp][gq + 8][n * 8 + 2 * tq]) = make_float2(acc[n][2], acc[n][3]);
   }
   __syncthreads();
   for (int i = threadIdx.x; i < gcount * D; i += blockDim.x) {

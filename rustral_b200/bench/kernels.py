@@ -119,6 +119,29 @@ def bench_adam(a):
     return report("adam_step", ms, 0, n * (4 * 4 + 3 * 4 + 2.0), {"numel": n})
 
 
+def bench_paged(a):
+    """Decode attention over a paged KV cache: `batch` sequences of `context` cached tokens, pages handed out in a
+    shuffled order so that consecutive pages of a sequence are not adjacent in memory."""
+    import math
+    from ..ops import paged
+    B, H, Hk, D, bs = a.batch, a.heads, a.kv_heads, a.head_dim, a.block_size
+    per = (a.context + bs - 1) // bs
+    nb = B * per + 1
+    g = torch.Generator().manual_seed(0)
+    kc = torch.randn(nb, bs, Hk, D, generator=g).bfloat16().cuda()
+    vc = torch.randn(nb, bs, Hk, D, generator=g).bfloat16().cuda()
+    bt = (torch.randperm(nb - 1, generator=g)[:B * per] + 1).to(torch.int32).view(B, per).cuda()
+    ctx = torch.full((B,), a.context, dtype=torch.int32, device="cuda")
+    q = torch.randn(B, H * D, generator=g).bfloat16().cuda()
+    out = torch.empty_like(q)
+    fn = lambda: paged.paged_attention_decode(q, kc, vc, bt, ctx, 1.0 / math.sqrt(D), out=out)
+    ms = timed(fn, a.warmup, a.iters)
+    kv_bytes = 2.0 * B * a.context * Hk * D * 2
+    return report("paged_decode_attention", ms, 0, kv_bytes,
+                  {"batch": B, "context": a.context, "heads": H, "kv_heads": Hk, "head_dim": D, "block_size": bs,
+                   "kv_cache_bytes": int(kv_bytes)})
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="rustral_b200.bench.kernels")
     ap.add_argument("--warmup", type=int, default=3)
@@ -145,8 +168,15 @@ def main(argv=None):
     n.add_argument("--n", type=int, default=768)
     d = sub.add_parser("adam")
     d.add_argument("--numel", type=int, default=124_000_000)
+    pg = sub.add_parser("paged")
+    pg.add_argument("--batch", type=int, default=64)
+    pg.add_argument("--context", type=int, default=4096)
+    pg.add_argument("--heads", type=int, default=32)
+    pg.add_argument("--kv-heads", type=int, default=8)
+    pg.add_argument("--head-dim", type=int, default=128)
+    pg.add_argument("--block-size", type=int, default=16)
     a = ap.parse_args(argv)
-    return {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam}[a.op](a)
+    return {"paged": bench_paged, "gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam}[a.op](a)
 
 
 if __name__ == "__main__":

@@ -203,7 +203,7 @@ def test_dropout(cuda_status):
     assert torch.equal(mp.bool().cpu(), dropout_mask_reference(100000, 0.25, 123))
 
 
-@pytest.mark.parametrize("H,Hk,D", [(4, 4, 64), (8, 2, 128), (32, 8, 128), (12, 1, 64)])
+@pytest.mark.parametrize("H,Hk,D", [(4, 4, 64), (8, 2, 128), (32, 8, 128), (12, 1, 64), (40, 2, 64)])
 def test_paged_attention_and_kv_append(H, Hk, D, cuda_status):
     from rustral_b200.ops import paged
     torch.manual_seed(0)
