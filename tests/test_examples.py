@@ -113,3 +113,35 @@ def test_manifest_validation_and_curation(tmp_path):
     p = tmp_path / "c.json"
     p.write_text(json.dumps(cur))
     assert M.main([str(p), str(tmp_path / "m.json")]) == 0
+
+
+def test_char_lm_trains_roundtrips_and_is_deterministic(tmp_path):
+    """crates/runtime/examples/emnlp_char_lm.rs: loss falls, save / load keeps the logits, three runs agree."""
+    mod = _load_example("emnlp_char_lm")
+    r = mod.train_once(42, False)
+    assert r["roundtrip_ok"] and r["epoch_losses"][-1] < 0.5 * r["epoch_losses"][0] and r["train_accuracy"] > 0.6
+    assert r["generated"].startswith(mod.PROMPT) and len(r["generated"]) == len(mod.PROMPT) + mod.GENERATE_LEN
+    rep = mod.main(["--determinism-check", "--out-dir", str(tmp_path)])
+    assert rep["all_equal"] and json.load(open(tmp_path / "emnlp_determinism_report.json"))["all_equal"]
+
+
+def test_nlp_eval_curates_multi_seed_runs(tmp_path, monkeypatch):
+    """scripts/eval/run_nlp_real.py: per-seed manifests of both tasks under one curated file each."""
+    from rustral_b200.bench import nlp_eval
+    from rustral_b200.bench.manifest import validate_curated
+    _stage_sst2(tmp_path, monkeypatch, reps=3)
+    d = tmp_path / "cache" / "datasets" / "wikitext-2"
+    d.mkdir(parents=True)
+    words = "the of and in to a was is for as on with by that it from at his an were are which this be".split()
+    text = "\n".join(" ".join(words[(i * 7 + j * (3 + i % 5)) % len(words)] for j in range(12)) + " ." for i in range(60))
+    for s in ("train", "valid", "test"):
+        (d / f"{s}.txt").write_text(text)
+    out = tmp_path / "nlp"
+    assert nlp_eval.main(["--benchmark", "--seeds", "0,1", "--out", str(out)]) == 0
+    for task, metric in (("sst2", "dev_accuracy"), ("wikitext2", "dev_perplexity")):
+        doc = json.load(open(out / f"{task}.json"))
+        assert validate_curated(doc) == [] and doc["metric"] == metric and doc["aggregate"]["n"] == 2
+        assert [r["seed"] for r in doc["runs"]] == [0, 1]
+        assert (out / "raw" / task / "seed1" / "manifest.json").exists()
+    seeds = json.load(open(out / "sst2.json"))["runs"]
+    assert seeds[0]["manifest"]["vocab_size"] == seeds[1]["manifest"]["vocab_size"]
