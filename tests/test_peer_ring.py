@@ -72,3 +72,36 @@ def test_peer_ring_attention_two_gpus():
         assert err < 2e-2, (name, out["errs"])
     for name, err in out["relay_match"].items():
         assert err < 1e-2, (name, out["relay_match"])
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("causal,striped", [(True, False), (True, True), (False, False)])
+def test_pull_and_deposit_schedules_agree(world, causal, striped):
+    """Host-side schedule of the ring at larger world sizes: a rank deposits a key / value gradient with an owner
+    exactly when the owner's fold mask expects it, every needed block is pulled once, nearest owner first, and
+    causally invisible blocks are neither pulled nor expected."""
+    from rustral_b200.parallel import sequence_parallel as sp
+    from rustral_b200.parallel.peer_ring import PeerRing
+    rings = []
+    for r in range(world):
+        ring = PeerRing.__new__(PeerRing)
+        ring.world, ring.rank = world, r
+        rings.append(ring)
+    for r, ring in enumerate(rings):
+        srcs = ring._sources(causal, striped)
+        assert len({s for s, _ in srcs}) == len(srcs) and all(s != r for s, _ in srcs)
+        dist_ = [(r - s) % world for s, _ in srcs]
+        assert dist_ == sorted(dist_)                                  # nearest first
+        for s, mode in srcs:
+            assert mode == sp._block_mode(r, s, causal, striped) != "skip"
+        visible = {s for s in range(world) if s != r and sp._block_mode(r, s, causal, striped) != "skip"}
+        assert {s for s, _ in srcs} == visible
+        if causal and not striped:
+            assert visible == set(range(r))                            # only earlier shards
+    for owner, ring in enumerate(rings):
+        mask = ring._contributors(causal, striped)
+        assert (mask >> owner) & 1                                     # the owner's own block
+        for q in range(world):
+            if q != owner:
+                deposits = any(s == owner for s, _ in rings[q]._sources(causal, striped))
+                assert deposits == bool((mask >> q) & 1), (owner, q)
