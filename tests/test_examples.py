@@ -145,3 +145,30 @@ def test_nlp_eval_curates_multi_seed_runs(tmp_path, monkeypatch):
         assert (out / "raw" / task / "seed1" / "manifest.json").exists()
     seeds = json.load(open(out / "sst2.json"))["runs"]
     assert seeds[0]["manifest"]["vocab_size"] == seeds[1]["manifest"]["vocab_size"]
+
+
+def test_pytorch_baselines_write_curated_manifests(tmp_path, monkeypatch):
+    """benchmarks/pytorch/*_baseline.py: plain-PyTorch runs of both tasks end in `<task>_pytorch.json`."""
+    from rustral_b200.bench import torch_baselines
+    from rustral_b200.bench.manifest import validate_curated
+    _stage_sst2(tmp_path, monkeypatch, reps=3)
+    _stage_wikitext_into(tmp_path / "cache")
+    out = tmp_path / "nlp"
+    small = ["--seq-len", "16", "--d-model", "32", "--num-heads", "2", "--ffn-dim", "64", "--num-layers", "1", "--quick",
+             "--seeds", "0,1", "--out", str(out)]
+    assert torch_baselines.main(["--task", "sst2", *small]) == 0
+    assert torch_baselines.main(["--task", "wikitext2", *small]) == 0
+    for task, metric in (("sst2", "dev_accuracy"), ("wikitext2", "dev_perplexity")):
+        doc = json.load(open(out / f"{task}_pytorch.json"))
+        assert validate_curated(doc) == [] and doc["metric"] == metric and doc["aggregate"]["n"] == 2
+        assert all(r["manifest"]["framework"] == "pytorch" for r in doc["runs"])
+    assert json.load(open(out / "wikitext2_pytorch.json"))["runs"][0]["manifest"]["dev_perplexity"] > 1.0
+
+
+def _stage_wikitext_into(cache):
+    d = cache / "datasets" / "wikitext-2"
+    d.mkdir(parents=True, exist_ok=True)
+    words = "the of and in to a was is for as on with by that it from at his an were are which this be".split()
+    text = "\n".join(" ".join(words[(i * 7 + j * (3 + i % 5)) % len(words)] for j in range(12)) + " ." for i in range(60))
+    for s in ("train", "valid", "test"):
+        (d / f"{s}.txt").write_text(text)
