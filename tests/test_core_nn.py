@@ -426,3 +426,18 @@ def test_kernel_factory_and_op_config():
         _, conf2 = fac.get_kernel(Fake())                      # second request: served from the cache, nothing timed
         assert conf2 == conf and len(Fake.calls) == n and tuner.stats["cache_hits"] == 1
         assert "matmul_default" in fac.default_configs and fac.default_configs["conv2d_default"].kind == "conv2d"
+
+
+def test_check_env_reports_toolkit_libraries_and_gpus():
+    from rustral_b200.utils import check_env
+    assert check_env.parse_nvcc_version("Cuda compilation tools, release 12.9, V12.9.86") == (12, 9)
+    assert check_env.parse_nvcc_version("garbage") is None
+    info = check_env.collect()
+    assert set(info["libraries"]) == {"librb200_kernels.so", "librb200_cpu.so", "librb200_runtime.so"}
+    assert info["ok"] == (not info["problems"]) and isinstance(info["gpus"], list)
+
+    class _Old:
+        stdout = "release 11.8, V11.8.89"
+    old = check_env.collect(run=lambda *a, **k: _Old())
+    if old["nvcc"]:
+        assert any("too old" in p for p in old["problems"]) and not old["ok"]
