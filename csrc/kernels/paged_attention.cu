@@ -50,6 +50,13 @@ __device__ __forceinline__ void pa_mma(float (&c)[4], const uint32_t (&a)[4], ui
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 16-byte asynchronous global -> shared copy; bytes == 0 writes zeros and reads nothing
+__device__ __forceinline__ void pa_cp_async16(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void pa_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void pa_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ uint32_t pa_pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -57,8 +64,10 @@ __device__ __forceinline__ uint32_t pa_pack_bf16(float lo, float hi) {
 
 // Split-KV decode attention.  One CTA = (sequence, KV head, 256-token slice of the context); the slices of a sequence
 // run on different SMs and a second kernel merges their (max, sum, accumulator) triples.  Inside a CTA a warp takes
-// 32 tokens at a time.  Their K rows and then their V rows are fetched with fully coalesced 16-byte loads (16 lanes
-// per 256-byte row), all loads of a tile in flight at once, into a padded shared tile.  The query heads of the group
+// 32 tokens at a time.  Their K rows and V rows are fetched with fully coalesced 16-byte asynchronous copies (cp.async,
+// 16 lanes per 256-byte row) into two padded shared tiles per warp; the K tile of the next pass is requested as soon
+// as the scores of this pass are computed and the V tile as soon as P V is done, so every warp always has a tile in
+// flight while it computes.  The query heads of the group
 // form the 16 rows of an m16n8k16 tensor-core tile (rows beyond the group are zero): S = Q K^T is 4 n-tiles x D/16
 // k-steps of mma.sync, the softmax runs on the accumulator fragments, and O += P V reuses those fragments as the A
 // operand against ldmatrix.trans-fed V.  One query token per sequence gives M <= 16, far below the 64-row minimum
@@ -74,10 +83,9 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, c
   constexpr int NLD = 32 / RPI;              // load instructions per 32-row tile
   constexpr int KROW = D + 8;                // padded row (elements): ldmatrix rows 272 (144) bytes apart hit distinct banks
   constexpr int NT = D / 8;                  // n-tiles of the output accumulator
-  constexpr int kTileBytes = kPaWarps * 32 * KROW * 2;
-  constexpr int kAccBytes = kPaWarps * kMaxGroup * D * 4;
-  __shared__ __align__(16) uint8_t big[kTileBytes > kAccBytes ? kTileBytes : kAccBytes];   // K/V tiles, later the warp merge
-  __shared__ __align__(16) __nv_bfloat16 q_sh[kMaxGroup * KROW];
+  constexpr int kTileElems = 32 * KROW;      // one K or V tile of one warp
+  extern __shared__ __align__(16) uint8_t big[];   // [warp][K tile, V tile] bf16, then q_sh; later the warp merge area
+  __nv_bfloat16* q_sh = reinterpret_cast<__nv_bfloat16*>(big) + kPaWarps * 2 * kTileElems;
   __shared__ float m_sh[kPaWarps][kMaxGroup], l_sh[kPaWarps][kMaxGroup];
   const int b = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,8 +96,8 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, c
   if (t_begin >= ctx) return;
   const int t_end = min(ctx, t_begin + kSplitTokens);
   const int h_base = hk * group + g0;        // first query head of this pass
-  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(big) + warp * 32 * KROW;
-  const uint32_t tile_u32 = smem_u32(tile);
+  const uint32_t kt_u32 = smem_u32(reinterpret_cast<__nv_bfloat16*>(big) + warp * 2 * kTileElems);
+  const uint32_t vt_u32 = kt_u32 + kTileElems * 2;
   const uint32_t q_u32 = smem_u32(q_sh);
 
   // the group's query rows as bf16 [16][D] (rows >= gcount are zero)
@@ -114,37 +122,48 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, c
 
   const long long row = static_cast<long long>(kv_heads) * D;          // elements per cached token
   const int piece = (lane % LPR) * 8;
-  for (int base = t_begin + warp * 32; base < t_end; base += kPaWarps * 32) {
-    const int tok = base + lane;
-    long long slot = 0;
+  const long long col = static_cast<long long>(hk) * D + piece;
+  const uint32_t dst_off = ((lane / LPR) * KROW + piece) * 2;          // byte offset of this lane's piece in a tile
+  int srow[NLD];                                                       // cache slot of the row behind each copy (-1: none)
+  int n_next = 0;
+  // cache slots of the 32 tokens that start at `first` (the host bounds num_blocks * block_size below 2^31)
+  auto locate = [&](int first) {
+    const int tok = first + lane;
+    int slot = 0;
     if (tok < t_end) {
       const int blk_idx = tok / block_size;
       int blk = blk_idx < max_blocks ? block_tables[static_cast<long long>(b) * max_blocks + blk_idx] : -1;
       if (blk < 0 || blk >= num_blocks) blk = 0;                     // corrupt tables read block 0 instead of faulting
-      slot = static_cast<long long>(blk) * block_size + (tok - blk_idx * block_size);
+      slot = blk * block_size + (tok - blk_idx * block_size);
     }
-    const int n_tok = min(32, t_end - base);
-    long long off[NLD];                                              // element offset of this lane's piece, per load
+    n_next = min(32, t_end - first);
 #pragma unroll
     for (int i = 0; i < NLD; ++i) {
       const int r = i * RPI + lane / LPR;
-      const long long slot_r = __shfl_sync(0xffffffffu, slot, r);
-      off[i] = r < n_tok ? slot_r * row + static_cast<long long>(hk) * D + piece : -1;
+      const int slot_r = __shfl_sync(0xffffffffu, slot, r);
+      srow[i] = r < n_next ? slot_r : -1;
     }
-    // ---- K rows -> registers (every load of the tile in flight) -> shared tile; rows past the context are zero
-    uint4 stage[NLD];
+  };
+  // one tile = NLD asynchronous 16-byte copies per lane, one commit group; rows past the context are zero-filled
+  auto request = [&](const __nv_bfloat16* cache, uint32_t tile_u32) {
 #pragma unroll
-    for (int i = 0; i < NLD; ++i)
-      stage[i] = off[i] >= 0 ? __ldg(reinterpret_cast<const uint4*>(k_cache + off[i])) : make_uint4(0u, 0u, 0u, 0u);
-    __syncwarp();                                                    // the previous pass has finished with the tile
-#pragma unroll
-    for (int i = 0; i < NLD; ++i)
-      *reinterpret_cast<uint4*>(tile + (i * RPI + lane / LPR) * KROW + piece) = stage[i];
+    for (int i = 0; i < NLD; ++i) {
+      const bool ok = srow[i] >= 0;
+      pa_cp_async16(tile_u32 + dst_off + i * RPI * KROW * 2, ok ? cache + srow[i] * row + col : cache, ok ? 16 : 0);
+    }
+    pa_cp_commit();
+  };
+  int base = t_begin + warp * 32;
+  if (base < t_end) {
+    locate(base);
+    request(k_cache, kt_u32);
+    request(v_cache, vt_u32);
+  }
+  for (; base < t_end; base += kPaWarps * 32) {
+    const int n_tok = n_next;
+    const bool more = base + kPaWarps * 32 < t_end;
+    pa_cp_wait<1>();                                                 // this pass's K tile has landed (V may be in flight)
     __syncwarp();
-    // ---- V rows -> registers: in flight while the scores and the softmax are computed
-#pragma unroll
-    for (int i = 0; i < NLD; ++i)
-      stage[i] = off[i] >= 0 ? __ldg(reinterpret_cast<const uint4*>(v_cache + off[i])) : make_uint4(0u, 0u, 0u, 0u);
     // ---- S[16 heads, 32 tokens] = Q K^T
     float s[4][4];
 #pragma unroll
@@ -158,10 +177,15 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, c
       for (int np = 0; np < 2; ++np) {
         uint32_t bfr[4];
         // B fragments of two n-tiles: (tokens 16np..+7, k0), (same tokens, k0 + 8), (tokens 16np + 8.., k0), (.., k0 + 8)
-        pa_ldsm_x4(tile_u32 + ((np * 16 + (lane & 7) + ((lane >> 4) << 3)) * KROW + k0 + ((lane >> 3) & 1) * 8) * 2, bfr);
+        pa_ldsm_x4(kt_u32 + ((np * 16 + (lane & 7) + ((lane >> 4) << 3)) * KROW + k0 + ((lane >> 3) & 1) * 8) * 2, bfr);
         pa_mma(s[2 * np], a, bfr[0], bfr[1]);
         pa_mma(s[2 * np + 1], a, bfr[2], bfr[3]);
       }
+    }
+    __syncwarp();                                                    // every lane has read its K fragments
+    if (more) {                                                      // the next pass's K tile flies under softmax and P V
+      locate(base + kPaWarps * 32);
+      request(k_cache, kt_u32);
     }
     // ---- online softmax over the 32 tokens; this thread holds 8 of them for rows gq and gq + 8
     float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -206,11 +230,8 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, c
     for (int n = 0; n < NT; ++n) {
       acc[n][0] *= al0; acc[n][1] *= al0; acc[n][2] *= al1; acc[n][3] *= al1;
     }
-    // ---- V rows replace the K tile; O[16, D] += P[16, 32] V[32, D]
-    __syncwarp();                                                    // every lane has read its K fragments
-#pragma unroll
-    for (int i = 0; i < NLD; ++i)
-      *reinterpret_cast<uint4*>(tile + (i * RPI + lane / LPR) * KROW + piece) = stage[i];
+    // ---- O[16, D] += P[16, 32] V[32, D]
+    if (more) pa_cp_wait<1>(); else pa_cp_wait<0>();                 // this pass's V tile has landed
     __syncwarp();
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
@@ -218,11 +239,13 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, c
       for (int n2 = 0; n2 < NT / 2; ++n2) {
         uint32_t bfr[4];
         // transposed 8x8 blocks: (tokens 16ks..+7, dims 16n2), (tokens +8, same dims), (tokens.., dims + 8), (+8, + 8)
-        pa_ldsm_x4_t(tile_u32 + ((ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KROW + n2 * 16 + (lane >> 4) * 8) * 2, bfr);
+        pa_ldsm_x4_t(vt_u32 + ((ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KROW + n2 * 16 + (lane >> 4) * 8) * 2, bfr);
         pa_mma(acc[2 * n2], pfr[ks], bfr[0], bfr[1]);
         pa_mma(acc[2 * n2 + 1], pfr[ks], bfr[2], bfr[3]);
       }
     }
+    __syncwarp();                                                    // every lane has read its V fragments
+    if (more) request(v_cache, vt_u32);
   }
 
   // ---- merge the warps, write this slice's (max, sum, accumulator) per head
@@ -309,7 +332,7 @@ RB_API int rb_paged_attention_decode(const void* q, long long ld_q, void* out, l
                                      float scale, float* scratch, void* stream_v) {
   if (batch <= 0) return 0;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || (head_dim != 64 && head_dim != 128) || block_size <= 0 ||
-      max_blocks <= 0 || !scratch)
+      max_blocks <= 0 || !scratch || num_blocks * block_size >= (1ll << 31))
     return -1;
   if ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) return -2;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
@@ -320,14 +343,27 @@ RB_API int rb_paged_attention_decode(const void* q, long long ld_q, void* out, l
   auto O = reinterpret_cast<__nv_bfloat16*>(out);
   auto K = reinterpret_cast<const __nv_bfloat16*>(k_cache);
   auto V = reinterpret_cast<const __nv_bfloat16*>(v_cache);
-  for (int g0 = 0; g0 < group; g0 += rb::kMaxGroup) {     // groups wider than 8 heads take several passes
+  // dynamic shared memory: per warp a K and a V tile of 32 padded rows, plus the 16 padded query rows
+  const int krow = head_dim + 8;
+  const int smem = (rb::kPaWarps * 2 * 32 + rb::kMaxGroup) * krow * 2;
+  static bool attr_set[64][2] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;
+  if (!attr_set[dev][head_dim == 128]) {
+    const cudaError_t e = head_dim == 128
+        ? cudaFuncSetAttribute(rb::paged_decode_split_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+        : cudaFuncSetAttribute(rb::paged_decode_split_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev][head_dim == 128] = true;
+  }
+  for (int g0 = 0; g0 < group; g0 += rb::kMaxGroup) {     // groups wider than 16 heads take several passes
     const int gc = group - g0 < rb::kMaxGroup ? group - g0 : rb::kMaxGroup;
     if (head_dim == 128)
-      rb::paged_decode_split_kernel<128><<<grid, rb::kPaWarps * 32, 0, stream>>>(Q, ld_q, K, V, block_tables, max_blocks,
+      rb::paged_decode_split_kernel<128><<<grid, rb::kPaWarps * 32, smem, stream>>>(Q, ld_q, K, V, block_tables, max_blocks,
                                                                                 context_lens, heads, kv_heads, block_size,
                                                                                 num_blocks, scale, g0, gc, scratch, nsplit);
     else
-      rb::paged_decode_split_kernel<64><<<grid, rb::kPaWarps * 32, 0, stream>>>(Q, ld_q, K, V, block_tables, max_blocks,
+      rb::paged_decode_split_kernel<64><<<grid, rb::kPaWarps * 32, smem, stream>>>(Q, ld_q, K, V, block_tables, max_blocks,
                                                                                context_lens, heads, kv_heads, block_size,
                                                                                num_blocks, scale, g0, gc, scratch, nsplit);
   }
