@@ -47,6 +47,22 @@ int rb_tokens_gather(const RbTokenFile* f, const int64_t* offsets, int batch, in
 // Deterministic window offsets for (seed, step): uniform over valid starts.
 void rb_tokens_sample_offsets(const RbTokenFile* f, uint64_t seed, uint64_t step, int batch, int seq_len_plus1,
                               int64_t* offsets_out);
+
+// ---- asynchronous checkpoint file writer ----------------------------------------------------------------------------
+// Worker threads write each job to "<path>.partial", fsync and rename it into place.  submit_* return a ticket (> 0)
+// or -1.  `copy` jobs duplicate the bytes at submission; `borrowed` jobs read the caller's buffer until the ticket
+// has been waited on.  wait: 0 done, 1 timed out (timeout_ms < 0 waits for ever).  flush: number of failed jobs since
+// the last take_error, -2 when still busy after timeout_ms.  take_error copies the latest message and clears the count.
+typedef struct RbAsyncWriter RbAsyncWriter;
+RbAsyncWriter* rb_aw_create(int num_threads);
+void rb_aw_destroy(RbAsyncWriter* w);                           // drains the queue first
+int64_t rb_aw_submit_copy(RbAsyncWriter* w, const char* path, const void* data, long long bytes);
+int64_t rb_aw_submit_borrowed(RbAsyncWriter* w, const char* path, const void* data, long long bytes);
+int rb_aw_wait(RbAsyncWriter* w, int64_t ticket, int timeout_ms);
+int rb_aw_flush(RbAsyncWriter* w, int timeout_ms);
+int rb_aw_pending(RbAsyncWriter* w);
+long long rb_aw_bytes_written(RbAsyncWriter* w);
+int rb_aw_take_error(RbAsyncWriter* w, char* buf, int buf_len);
 #ifdef __cplusplus
 }
 #endif

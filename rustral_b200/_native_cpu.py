@@ -50,3 +50,12 @@ def declare_runtime(lib) -> None:
     _sig(lib, "rb_tokens_len", [P], LL)
     _sig(lib, "rb_tokens_gather", [P, P, I, I, P], I)
     _sig(lib, "rb_tokens_sample_offsets", [P, C.c_uint64, C.c_uint64, I, I, P])
+    _sig(lib, "rb_aw_create", [I], P)
+    _sig(lib, "rb_aw_destroy", [P])
+    _sig(lib, "rb_aw_submit_copy", [P, C.c_char_p, P, LL], LL)
+    _sig(lib, "rb_aw_submit_borrowed", [P, C.c_char_p, P, LL], LL)
+    _sig(lib, "rb_aw_wait", [P, LL, I], I)
+    _sig(lib, "rb_aw_flush", [P, I], I)
+    _sig(lib, "rb_aw_pending", [P], I)
+    _sig(lib, "rb_aw_bytes_written", [P], LL)
+    _sig(lib, "rb_aw_take_error", [P, C.c_char_p, I], I)

@@ -9,9 +9,7 @@ from __future__ import annotations
 
 import json
 import os
-import queue
 import shutil
-import threading
 import time
 from dataclasses import dataclass
 
@@ -132,47 +130,76 @@ def reshard_flat(old_shards: list, new_world: int, new_rank: int) -> torch.Tenso
 
 
 class AsyncCheckpointWriter:
-    """Background writer thread: `write(path, bytes)` returns at once; `flush()` waits; errors surface on flush
-    (crates/distributed/src/checkpoint.rs:271-308)."""
+    """Background checkpoint writer: `write(path, bytes)` returns at once; `flush()` waits; errors surface on flush
+    (crates/distributed/src/checkpoint.rs:271-308).  The work is done by the C++ writer pool of the runtime library
+    (csrc/runtime/async_writer.cpp): worker threads write "<path>.partial", fsync and rename, outside the
+    interpreter lock.  `write_tensor` hands over a host tensor without copying it (pinned memory that a device-to-host
+    copy has filled, for instance) and returns a ticket; the tensor is kept alive until the ticket has been waited on."""
 
-    def __init__(self):
-        self._q: queue.Queue = queue.Queue()
-        self._errors: list = []
-        self._t = threading.Thread(target=self._run, daemon=True)
-        self._t.start()
+    def __init__(self, num_threads: int = 2):
+        from .. import _native as N
+        self._lib = N.runtime()
+        self._h = self._lib.rb_aw_create(int(num_threads))
+        if not self._h:
+            raise SerializationError("cannot start the asynchronous checkpoint writer")
+        self._borrowed: dict = {}
 
-    def _run(self):
-        while True:
-            item = self._q.get()
-            if item is None:
-                self._q.task_done()
-                return
-            path, blob = item
-            try:
-                tmp = path + ".partial"
-                with open(tmp, "wb") as f:
-                    f.write(blob)
-                    f.flush()
-                    os.fsync(f.fileno())
-                os.replace(tmp, path)
-            except OSError as e:
-                self._errors.append(e)
-            self._q.task_done()
+    def write(self, path: str, blob) -> int:
+        blob = bytes(blob)
+        t = self._lib.rb_aw_submit_copy(self._h, os.fsencode(path), blob, len(blob))
+        if t <= 0:
+            raise SerializationError(f"asynchronous checkpoint writer refused {path}")
+        return int(t)
 
-    def write(self, path: str, blob: bytes) -> None:
-        self._q.put((path, bytes(blob)))
+    def write_tensor(self, path: str, tensor) -> int:
+        """Queues the raw bytes of a contiguous host tensor; nothing is copied.  Do not modify the tensor until
+        `wait(ticket)` or `flush()` has returned."""
+        if tensor.is_cuda or not tensor.is_contiguous():
+            raise SerializationError("write_tensor takes a contiguous host tensor")
+        n = tensor.numel() * tensor.element_size()
+        t = self._lib.rb_aw_submit_borrowed(self._h, os.fsencode(path), tensor.data_ptr(), n)
+        if t <= 0:
+            raise SerializationError(f"asynchronous checkpoint writer refused {path}")
+        self._borrowed[int(t)] = tensor
+        return int(t)
+
+    def wait(self, ticket: int, timeout_s: float | None = None) -> bool:
+        """True when the job has finished (successfully or not; `flush` reports failures)."""
+        rc = self._lib.rb_aw_wait(self._h, int(ticket), -1 if timeout_s is None else int(timeout_s * 1000))
+        if rc == 0:
+            self._borrowed.pop(int(ticket), None)
+        return rc == 0
+
+    def pending(self) -> int:
+        return int(self._lib.rb_aw_pending(self._h))
+
+    def bytes_written(self) -> int:
+        return int(self._lib.rb_aw_bytes_written(self._h))
 
     def flush(self) -> None:
-        self._q.join()
-        if self._errors:
-            e = self._errors[0]
-            self._errors.clear()
-            raise SerializationError(f"asynchronous checkpoint write failed: {e}")
+        failed = self._lib.rb_aw_flush(self._h, -1)
+        self._borrowed.clear()
+        if failed > 0:
+            import ctypes
+            buf = ctypes.create_string_buffer(512)
+            self._lib.rb_aw_take_error(self._h, buf, 512)
+            raise SerializationError(f"asynchronous checkpoint write failed ({failed} job(s)): {buf.value.decode(errors='replace')}")
 
     def close(self) -> None:
-        self.flush()
-        self._q.put(None)
-        self._t.join(timeout=10)
+        if self._h:
+            try:
+                self.flush()
+            finally:
+                self._lib.rb_aw_destroy(self._h)
+                self._h = None
+
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                self._lib.rb_aw_destroy(self._h)
+                self._h = None
+        except Exception:       # noqa: BLE001 - interpreter shutdown
+            pass
 
 
 class ShardedCheckpoint:

@@ -441,3 +441,35 @@ def test_ulysses_attention_matches_full_attention(causal):
             UlyssesAttention(pg)(torch.randn(1, 4, 3, 8), torch.randn(1, 4, 3, 8), torch.randn(1, 4, 3, 8))
         return True
     assert all(run_ranks(2, bad))
+
+
+def test_native_async_writer_tickets_borrowed_buffers_and_errors(tmp_path):
+    """The C++ writer pool: many files, atomic rename, zero-copy tensor jobs with tickets, failures reported on flush
+    while later jobs still succeed."""
+    from rustral_b200.core.errors import SerializationError
+    from rustral_b200.parallel.checkpoint import AsyncCheckpointWriter
+    w = AsyncCheckpointWriter(num_threads=3)
+    blobs = {f"f{i}.bin": bytes([i]) * (1000 + 37 * i) for i in range(24)}
+    tickets = [w.write(str(tmp_path / n), b) for n, b in blobs.items()]
+    assert tickets == sorted(tickets) and len(set(tickets)) == 24
+    big = torch.arange(1 << 18, dtype=torch.float32)
+    t = w.write_tensor(str(tmp_path / "big.raw"), big)
+    assert w.wait(t, timeout_s=30)
+    assert torch.equal(torch.frombuffer(bytearray((tmp_path / "big.raw").read_bytes()), dtype=torch.float32), big)
+    w.write(str(tmp_path / "empty.bin"), b"")
+    w.flush()
+    assert w.pending() == 0 and w.bytes_written() == sum(map(len, blobs.values())) + big.numel() * 4
+    for n, b in blobs.items():
+        assert (tmp_path / n).read_bytes() == b
+    assert (tmp_path / "empty.bin").read_bytes() == b"" and not list(tmp_path.glob("*.partial"))
+    with pytest.raises(SerializationError):
+        w.write_tensor(str(tmp_path / "x"), torch.arange(10.).view(2, 5).t())     # not contiguous
+    w.write(str(tmp_path / "no_such_dir" / "x.bin"), b"zz")
+    w.write(str(tmp_path / "after.bin"), b"ok")
+    with pytest.raises(SerializationError, match="no_such_dir"):
+        w.flush()
+    assert (tmp_path / "after.bin").read_bytes() == b"ok"
+    w.flush()                                                                      # the error was consumed
+    assert not w.wait(10 ** 6, timeout_s=0.01)                                      # unknown ticket
+    w.close()
+    w.close()
