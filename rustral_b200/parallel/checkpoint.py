@@ -60,6 +60,35 @@ class DistributedCheckpointManager:
         self.pg.barrier()
         return d
 
+    def save_async(self, epoch: int, step: int, named_tensors, writer: "AsyncCheckpointWriter",
+                   optimizer_state: dict | None = None) -> str:
+        """Snapshots THIS rank's state into host memory and queues its files on `writer`; returns without waiting for
+        the disk, so training continues while the files are written.  The checkpoint only counts once
+        `finish_async(epoch, step, writer)` has run: it flushes the writer, and after a barrier the primary rank writes
+        metadata.json, the file whose presence marks an epoch directory as complete."""
+        d = self._epoch_dir(epoch)
+        os.makedirs(d, exist_ok=True)
+        tensors = {n: (p.tensor if hasattr(p, "tensor") else p).detach().to("cpu", copy=True) for n, p in named_tensors}
+        writer.write(os.path.join(d, f"rank_{self.pg.rank}.safetensors"), st.save_state_dict_typed(tensors, {}))
+        if optimizer_state is not None:
+            writer.write(os.path.join(d, f"optimizer_rank_{self.pg.rank}.json"), json.dumps(optimizer_state).encode())
+        return d
+
+    def finish_async(self, epoch: int, step: int, writer: "AsyncCheckpointWriter") -> str:
+        """Collective: waits for this rank's queued files, then publishes the checkpoint (metadata + rotation)."""
+        d = self._epoch_dir(epoch)
+        writer.flush()
+        self.pg.barrier()
+        if self.pg.is_primary():
+            meta = CheckpointMetadata(epoch, step, self.pg.world_size, time.time())
+            tmp = os.path.join(d, "metadata.json.partial")
+            with open(tmp, "w") as f:
+                json.dump(meta.__dict__, f)
+            os.replace(tmp, os.path.join(d, "metadata.json"))
+            self._rotate()
+        self.pg.barrier()
+        return d
+
     def _rotate(self) -> None:
         eps = self.list_checkpoints()
         for e in eps[:-self.keep_last_n] if self.keep_last_n > 0 else []:

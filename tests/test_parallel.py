@@ -473,3 +473,24 @@ def test_native_async_writer_tickets_borrowed_buffers_and_errors(tmp_path):
     assert not w.wait(10 ** 6, timeout_s=0.01)                                      # unknown ticket
     w.close()
     w.close()
+
+
+def test_asynchronous_distributed_checkpoint_is_published_only_when_finished(tmp_path):
+    from rustral_b200.parallel.checkpoint import AsyncCheckpointWriter, DistributedCheckpointManager
+
+    def fn(pg):
+        mgr = DistributedCheckpointManager(pg, str(tmp_path), keep_last_n=2)
+        w = AsyncCheckpointWriter()
+        shard = torch.arange(6.) + 100 * pg.rank
+        mgr.save_async(5, 500, [("flat", shard)], w, {"t": 5})
+        shard += 1000.0                                  # training goes on: the snapshot must not see this
+        pg.barrier()
+        visible_before = mgr.list_checkpoints()          # no metadata.json yet: not a checkpoint
+        mgr.finish_async(5, 500, w)
+        step, tensors, opt = mgr.load(5)
+        w.close()
+        return visible_before, mgr.list_checkpoints(), step, tensors["flat"].tolist(), opt
+    out = run_ranks(2, fn)
+    for r, (before, after, step, flat, opt) in enumerate(out):
+        assert before == [] and after == [5] and step == 500 and opt == {"t": 5}
+        assert flat == [100.0 * r + i for i in range(6)]
