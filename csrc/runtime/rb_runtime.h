@@ -1,5 +1,5 @@
-// C interface of the host runtime library (librb200_runtime.so): paged-KV block allocator, request scheduler
-// core, tile-configuration search and a memory-mapped token loader.  No GPU code; bound with ctypes.
+// C interface of the host runtime library (librb200_runtime.so): paged-KV block allocator, tile-configuration
+// search, a memory-mapped token loader and an asynchronous checkpoint file writer.  No GPU code; bound with ctypes.
 #pragma once
 #include <stdint.h>
 #ifdef __cplusplus
