@@ -1,5 +1,5 @@
-// C interface of the host runtime library (librb200_runtime.so): paged-KV block allocator, tile-configuration
-// search, a memory-mapped token loader and an asynchronous checkpoint file writer.  No GPU code; bound with ctypes.
+// C interface of the host runtime library (librb200_runtime.so): paged-KV block allocator, continuous-batching
+// scheduler core, tile-configuration search, a memory-mapped token loader and an asynchronous checkpoint file writer.  No GPU code; bound with ctypes.
 #pragma once
 #include <stdint.h>
 #ifdef __cplusplus
@@ -47,6 +47,30 @@ int rb_tokens_gather(const RbTokenFile* f, const int64_t* offsets, int batch, in
 // Deterministic window offsets for (seed, step): uniform over valid starts.
 void rb_tokens_sample_offsets(const RbTokenFile* f, uint64_t seed, uint64_t step, int batch, int seq_len_plus1,
                               int64_t* offsets_out);
+
+// ---- continuous-batching scheduler core -----------------------------------------------------------------------------
+// Decisions of one serving iteration over the block allocator `alloc` (not owned): retire finished requests, resume
+// paused ones, admit waiting ones while blocks and the prefill budget last, preempt a LOW-priority request when memory
+// has run out and something more urgent waits.  policy: 0 first come first served, 1 shortest remaining first,
+// 2 priority.  Request states: 0 waiting, 1 prefill, 2 generating, 3 paused, 4 completed.
+typedef struct RbScheduler RbScheduler;
+RbScheduler* rb_sched_create(RbBlockAllocator* alloc, int max_batch, int policy, double preemption_threshold,
+                             int max_prefill_tokens);
+void rb_sched_destroy(RbScheduler* s);
+int64_t rb_sched_add(RbScheduler* s, int prompt_len, int max_tokens, int priority, int has_eos, int64_t eos_id);  // id
+int rb_sched_has_work(const RbScheduler* s);
+void rb_sched_retire(RbScheduler* s);
+// Runs one iteration and fills the batch (policy order): ids, 1 where the whole prefix must be (re)computed, tokens in
+// the cache after the step.  Returns the batch size, -2 when cap is too small.
+int rb_sched_schedule(RbScheduler* s, int64_t* ids, int32_t* is_prefill, int32_t* seq_lens, int cap);
+int rb_sched_take_retired(RbScheduler* s, int64_t* ids, int cap);           // ids retired since the last call
+// Records one sampled token per request and grows its block table.  result[i]: 0 ignored (not running), 1 recorded,
+// 2 recorded and paused for lack of blocks.  Returns the number paused.
+int rb_sched_update(RbScheduler* s, const int64_t* ids, const int64_t* tokens, int n, int32_t* result);
+int rb_sched_state(const RbScheduler* s, int64_t id);                       // -1 unknown
+void rb_sched_stats(const RbScheduler* s, int64_t* out4);                   // completed, preempted, admitted, generated tokens
+int rb_sched_list(const RbScheduler* s, int which, int64_t* ids, int cap);  // which: 0 pending, 1 running, 2 paused; returns count
+void rb_sched_forget(RbScheduler* s, int64_t id);                           // drops the record of a completed request
 
 // ---- asynchronous checkpoint file writer ----------------------------------------------------------------------------
 // Worker threads write each job to "<path>.partial", fsync and rename it into place.  submit_* return a ticket (> 0)

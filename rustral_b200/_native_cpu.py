@@ -50,6 +50,18 @@ def declare_runtime(lib) -> None:
     _sig(lib, "rb_tokens_len", [P], LL)
     _sig(lib, "rb_tokens_gather", [P, P, I, I, P], I)
     _sig(lib, "rb_tokens_sample_offsets", [P, C.c_uint64, C.c_uint64, I, I, P])
+    _sig(lib, "rb_sched_create", [P, I, I, D, I], P)
+    _sig(lib, "rb_sched_destroy", [P])
+    _sig(lib, "rb_sched_add", [P, I, I, I, I, LL], LL)
+    _sig(lib, "rb_sched_has_work", [P], I)
+    _sig(lib, "rb_sched_retire", [P])
+    _sig(lib, "rb_sched_schedule", [P, P, P, P, I], I)
+    _sig(lib, "rb_sched_take_retired", [P, P, I], I)
+    _sig(lib, "rb_sched_update", [P, P, P, I, P], I)
+    _sig(lib, "rb_sched_state", [P, LL], I)
+    _sig(lib, "rb_sched_stats", [P, P])
+    _sig(lib, "rb_sched_list", [P, I, P, I], I)
+    _sig(lib, "rb_sched_forget", [P, LL])
     _sig(lib, "rb_aw_create", [I], P)
     _sig(lib, "rb_aw_destroy", [P])
     _sig(lib, "rb_aw_submit_copy", [P, C.c_char_p, P, LL], LL)

@@ -4,9 +4,14 @@ Each call to `schedule()` retires finished requests, resumes paused ones, admits
 last, preempts low-priority work under memory pressure and returns the batch for the next model step: full
 prompts for requests in prefill, the last token for requests in decode.  The scheduling policy is honoured
 (the reference stores it and never reads it), and the end-of-sequence id is configurable (the reference hard-codes 2).
+
+`Scheduler` keeps the decisions (queues, ordering, admission against the block allocator, preemption, retirement) in
+the C++ core of the runtime library (csrc/runtime/scheduler.cpp); this module keeps the tokens and the timing of each
+request.  `PyScheduler` is the same logic in Python, kept as the specification the core is tested against.
 """
 from __future__ import annotations
 
+import ctypes as C
 import enum
 import time
 from collections import deque
@@ -97,7 +102,9 @@ class SchedulerStats:
         return self.total_latency / self.completed if self.completed else 0.0
 
 
-class Scheduler:
+class PyScheduler:
+    """The scheduler in plain Python: the executable specification the native core (`Scheduler`) is tested against."""
+
     def __init__(self, cache: PagedCache, max_batch_size: int = 64, policy: SchedulingPolicy = SchedulingPolicy.FCFS,
                  preemption_threshold: float = 0.5, max_prefill_tokens: int = 8192):
         self.cache = cache
@@ -232,3 +239,139 @@ class Scheduler:
                 if r.id == rid:
                     return r
         return None
+
+
+_STATE_OF = {0: RequestState.WAITING, 1: RequestState.PREFILL, 2: RequestState.GENERATING, 3: RequestState.PAUSED,
+             4: RequestState.COMPLETED}
+_POLICY_CODE = {SchedulingPolicy.FCFS: 0, SchedulingPolicy.SRTF: 1, SchedulingPolicy.PRIORITY: 2}
+
+
+class Scheduler:
+    """Continuous-batching scheduler on the native core.  Same interface and decisions as `PyScheduler`."""
+
+    def __init__(self, cache: PagedCache, max_batch_size: int = 64, policy: SchedulingPolicy = SchedulingPolicy.FCFS,
+                 preemption_threshold: float = 0.5, max_prefill_tokens: int = 8192):
+        from .. import _native as N
+        self.cache = cache
+        self.max_batch_size, self.policy = max_batch_size, policy
+        self.preemption_threshold, self.max_prefill_tokens = preemption_threshold, max_prefill_tokens
+        self._lib = N.runtime()
+        self._h = self._lib.rb_sched_create(cache._h, max_batch_size, _POLICY_CODE[policy], float(preemption_threshold),
+                                            max_prefill_tokens)
+        if not self._h:
+            raise ValueError("Scheduler: max_batch_size and max_prefill_tokens must be positive")
+        self.requests: dict = {}
+        self.completed: list = []
+        self._latency = 0.0
+        cap = max_batch_size
+        self._ids, self._pre, self._lens = (C.c_int64 * cap)(), (C.c_int32 * cap)(), (C.c_int32 * cap)()
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.rb_sched_destroy(h)
+
+    # ---- submission -----------------------------------------------------------------------------------------
+    def add_request(self, prompt, max_tokens: int, priority: RequestPriority = RequestPriority.NORMAL, eos_id=None,
+                    arrival_time: float | None = None) -> int:
+        prompt = list(prompt)
+        rid = int(self._lib.rb_sched_add(self._h, len(prompt), int(max_tokens), int(priority), 0 if eos_id is None else 1,
+                                         0 if eos_id is None else int(eos_id)))
+        if rid < 0:
+            raise ValueError("Scheduler.add_request: invalid request")
+        req = Request(rid, prompt, max_tokens, priority, eos_id)
+        if arrival_time is not None:
+            req.arrival_time = arrival_time
+        self.requests[rid] = req
+        return rid
+
+    def has_work(self) -> bool:
+        return bool(self._lib.rb_sched_has_work(self._h))
+
+    # ---- one iteration ------------------------------------------------------------------------------------------
+    def _collect_retired(self) -> None:
+        buf = (C.c_int64 * 64)()
+        while True:
+            n = self._lib.rb_sched_take_retired(self._h, buf, 64)
+            for i in range(n):
+                r = self.requests[int(buf[i])]
+                r.state = RequestState.COMPLETED
+                r.finish_time = time.perf_counter()
+                self._latency += r.finish_time - r.arrival_time
+                self.completed.append(r)
+            if n < 64:
+                return
+
+    def _retire(self) -> None:
+        self._lib.rb_sched_retire(self._h)
+        self._collect_retired()
+
+    def schedule(self) -> Batch:
+        n = self._lib.rb_sched_schedule(self._h, self._ids, self._pre, self._lens, len(self._ids))
+        if n < 0:
+            raise RuntimeError(f"scheduler core failed ({n})")
+        self._collect_retired()
+        ids, inputs, lens, tables, pre = [], [], [], [], []
+        for i in range(n):
+            r = self.requests[int(self._ids[i])]
+            if self._pre[i]:
+                r.state = RequestState.PREFILL
+                inputs.append(r.prompt + r.generated)          # a resumed request re-runs its whole prefix
+            else:
+                inputs.append([r.last_token()])
+            pre.append(bool(self._pre[i]))
+            ids.append(r.id)
+            lens.append(int(self._lens[i]))
+            tables.append(self.cache.block_table(r.id))
+        return Batch(ids, inputs, lens, tables, pre)
+
+    def update(self, outputs: dict, now: float | None = None) -> None:
+        """outputs: request id -> sampled token.  Grows block tables; a request that finds no free block is paused."""
+        n = len(outputs)
+        if not n:
+            return
+        ids = (C.c_int64 * n)(*[int(k) for k in outputs])
+        toks = (C.c_int64 * n)(*[int(v) for v in outputs.values()])
+        res = (C.c_int32 * n)()
+        self._lib.rb_sched_update(self._h, ids, toks, n, res)
+        for i, (rid, tok) in enumerate(outputs.items()):
+            if res[i] == 0:
+                continue
+            r = self.requests[rid]
+            r.add_token(tok, now)
+            r.state = RequestState.PAUSED if res[i] == 2 else RequestState.GENERATING
+
+    # ---- inspection ---------------------------------------------------------------------------------------------
+    def get(self, rid: int):
+        return self.requests.get(rid)
+
+    def forget(self, rid: int) -> None:
+        """Drops a completed request's record (long-running servers call this after delivering the result)."""
+        r = self.requests.get(rid)
+        if r is not None and r.state is RequestState.COMPLETED:
+            self._lib.rb_sched_forget(self._h, rid)
+            del self.requests[rid]
+
+    def _listed(self, which: int) -> list:
+        n = self._lib.rb_sched_list(self._h, which, None, 0)
+        buf = (C.c_int64 * max(n, 1))()
+        self._lib.rb_sched_list(self._h, which, buf, n)
+        return [self.requests[int(buf[i])] for i in range(n)]
+
+    @property
+    def pending(self) -> list:
+        return self._listed(0)
+
+    @property
+    def running(self) -> dict:
+        return {r.id: r for r in self._listed(1)}
+
+    @property
+    def paused(self) -> list:
+        return self._listed(2)
+
+    @property
+    def stats(self) -> SchedulerStats:
+        out = (C.c_int64 * 4)()
+        self._lib.rb_sched_stats(self._h, out)
+        return SchedulerStats(int(out[0]), int(out[1]), int(out[2]), int(out[3]), self._latency)

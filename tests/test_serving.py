@@ -124,3 +124,43 @@ def test_http_server_routes_and_validation(tmp_path):
     finally:
         httpd.shutdown()
         state.shutdown()
+
+
+@pytest.mark.parametrize("policy", ["FCFS", "SRTF", "PRIORITY"])
+def test_native_scheduler_core_makes_the_same_decisions_as_the_python_specification(policy):
+    """Random arrivals, priorities, lengths and end-of-sequence hits on a cache small enough to force head-of-line
+    blocking, preemption and pause-on-update: batch for batch the C++ core and the Python scheduler agree."""
+    import random
+    from rustral_b200.serve.kv_cache import PagedCache
+    from rustral_b200.serve.scheduler import PyScheduler, RequestPriority, Scheduler, SchedulingPolicy
+    for seed in range(6):
+        rng = random.Random(seed)
+        caches = [PagedCache(num_blocks=24, block_size=4, allocate_storage=False) for _ in range(2)]
+        kw = dict(max_batch_size=5, policy=SchedulingPolicy[policy], preemption_threshold=0.5, max_prefill_tokens=40)
+        a, b = PyScheduler(caches[0], **kw), Scheduler(caches[1], **kw)
+        step, submitted = 0, 0
+        while step < 400 and (submitted < 40 or a.has_work()):
+            if submitted < 40 and rng.random() < 0.5:
+                prompt = [rng.randrange(3, 50) for _ in range(rng.randrange(1, 30))]
+                args = (prompt, rng.randrange(1, 12), RequestPriority(rng.randrange(0, 4)), 7 if rng.random() < 0.5 else None)
+                assert a.add_request(*args) == b.add_request(*args)
+                submitted += 1
+            ba, bb = a.schedule(), b.schedule()
+            assert (ba.request_ids, ba.input_ids, ba.seq_lens, ba.is_prefill) == (bb.request_ids, bb.input_ids, bb.seq_lens, bb.is_prefill)
+            assert ba.block_tables == bb.block_tables
+            assert a.has_work() == b.has_work() and caches[0].free_blocks == caches[1].free_blocks
+            outs = {rid: (7 if rng.random() < 0.1 else rng.randrange(8, 50)) for rid in ba.request_ids}
+            a.update(outs, now=float(step))
+            b.update(outs, now=float(step))
+            assert [r.id for r in a.paused] == [r.id for r in b.paused] and list(a.running) == list(b.running)
+            assert [r.id for r in a.pending] == [r.id for r in b.pending]
+            step += 1
+        a._retire()
+        b._retire()
+        sa, sb = a.stats, b.stats
+        assert (sa.completed, sa.preempted, sa.admitted, sa.total_generated) == (sb.completed, sb.preempted, sb.admitted, sb.total_generated)
+        assert [(r.id, r.generated) for r in a.completed] == [(r.id, r.generated) for r in b.completed]
+        assert sa.completed == 40 and not a.has_work() and caches[1].free_blocks == 24
+        assert all(b.get(r.id).state.value == "completed" for r in b.completed)
+        b.forget(b.completed[0].id)
+        assert b.get(b.completed[0].id) is None
