@@ -91,6 +91,16 @@ def _workspace(device) -> torch.Tensor:
     return ws
 
 
+# Optional tile-plan table: fn(M, N, K, a_mn, b_mn, out_is_f32) -> {"block_n", "splits", "group_m"} or None.  Installed by
+# tune.GemmTuningTable.apply(); consulted only for plain calls that leave the plan to the kernel's own cost model.
+_PLAN_HOOK = None
+
+
+def set_plan_hook(fn) -> None:
+    global _PLAN_HOOK
+    _PLAN_HOOK = fn
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, act: str = "none",
          residual=None, aux_in=None, aux_out=None, out=None, out_dtype=None, accumulate: bool = False,
          alpha: float = 1.0, block_n: int = 0, group_m: int = 0, max_ctas: int = 0, splits: int = 0,
@@ -122,6 +132,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         accumulate = False
     if out.stride(1) != 1 or out.shape != (M, Nn):
         raise ValueError("gemm: bad output tensor")
+    if _PLAN_HOOK is not None and block_n == 0 and splits == 0 and group_m == 0 and peer is None and max_ctas == 0:
+        plan = _PLAN_HOOK(M, Nn, K, a_mn, b_mn, out.dtype == torch.float32)
+        if plan:
+            block_n, splits, group_m = int(plan.get("block_n", 0)), int(plan.get("splits", 0)), int(plan.get("group_m", 0))
     for t, nm in ((bias, "bias"), (residual, "residual"), (aux_in, "aux_in"), (aux_out, "aux_out")):
         if t is not None and t.dtype != torch.bfloat16:
             raise TypeError(f"gemm: {nm} must be bf16")

@@ -359,6 +359,98 @@ def tune_gemm(M: int, N_: int, K: int, tuner: AutoTuner | None = None, **kw) -> 
     return (tuner or AutoTuner(TunerConfig.fast())).tune(GemmKernel(M, N_, K, **kw))
 
 
+class GemmTuningTable:
+    """The tuned GEMM plans of a cache, served back to `ops.gemm`.  `apply()` installs the table: from then on a plain
+    `gemm` call (no explicit tile plan, no peer mode) whose shape bucket has a cached winner runs with that winner
+    instead of the kernel's built-in cost model; `remove()` uninstalls it."""
+
+    def __init__(self, cache: ConfigCache | None = None, device_id: str | None = None, dtype: str = "bf16"):
+        if device_id is None:
+            device_id = torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu"
+        self.cache = cache or ConfigCache(device_id=device_id)
+        self.device_id, self.dtype = device_id, dtype
+        self.hits = self.misses = 0
+        self._memo: dict = {}
+
+    def lookup(self, M: int, N_: int, K: int, a_mn: bool = False, b_mn: bool = False, out_f32: bool = False):
+        key = MatmulShapeBucket.of(M, N_, K).cache_key() + f"_{int(a_mn)}{int(b_mn)}{int(out_f32)}"
+        if key not in self._memo:
+            e = self.cache.get_config(GemmKernel.kernel_id, self.device_id, self.dtype, key)
+            cfg = dict(e.config) if e is not None else None
+            if cfg is not None and not any(cfg.get(k, 0) for k in ("block_n", "splits", "group_m")):
+                cfg = None                       # the cached winner IS the built-in plan
+            self._memo[key] = cfg
+        cfg = self._memo[key]
+        if cfg is None:
+            self.misses += 1
+        else:
+            self.hits += 1
+        return cfg
+
+    def apply(self) -> "GemmTuningTable":
+        from ..ops import matmul
+        matmul.set_plan_hook(self.lookup)
+        return self
+
+    @staticmethod
+    def remove() -> None:
+        from ..ops import matmul
+        matmul.set_plan_hook(None)
+
+
+class AttentionKernel(TunableKernel):
+    """Flash attention forward (+ backward) at one shape: which implementation serves it, the tcgen05 kernels or the
+    mma.sync kernels (`impl` 0 / 1).  The result feeds `ops.attention.FORWARD_IMPL` / `BACKWARD_IMPL`."""
+
+    kernel_id = "flash_attention"
+    IMPLS = ("tc", "mma")
+
+    def __init__(self, batch: int, seq: int, heads: int, kv_heads: int, head_dim: int, causal: bool = True, backward: bool = True):
+        self.shape = (batch, seq, heads, kv_heads, head_dim)
+        self.causal, self.backward = causal, backward
+        self._t = None
+
+    def _tensors(self):
+        if self._t is None:
+            B, S, H, Hk, D = self.shape
+            g = torch.Generator().manual_seed(0)
+            mk = lambda h: torch.randn(B, S, h, D, generator=g).to(torch.bfloat16).cuda()
+            self._t = (mk(H), mk(Hk), mk(Hk), mk(H))
+        return self._t
+
+    def config_space(self):
+        return ConfigSpace({"impl": [0, 1]})
+
+    def default_config(self):
+        return {"impl": 0}
+
+    def input_signature(self):
+        B, S, H, Hk, D = self.shape
+        return f"b{dim_bucket(B)}_s{dim_bucket(S)}_h{H}_kv{Hk}_d{D}_{int(self.causal)}{int(self.backward)}"
+
+    def flops(self):
+        B, S, H, _, D = self.shape
+        return 4.0 * B * S * S * H * D * (3.5 if self.backward else 1.0) * (0.5 if self.causal else 1.0)
+
+    def with_config(self, config: dict):
+        import math
+        from ..ops import attention as A
+        impl = self.IMPLS[int(config["impl"])]
+        q, k, v, do = self._tensors()
+        scale = 1.0 / math.sqrt(q.shape[-1])
+
+        def run():
+            o, lse = A.attention_forward(q, k, v, self.causal, scale, impl=impl)
+            if self.backward:
+                A.attention_backward(do, q, k, v, o, lse, self.causal, scale, impl=impl)
+        return run
+
+
+def tune_attention(batch: int, seq: int, heads: int, kv_heads: int, head_dim: int, tuner: AutoTuner | None = None, **kw):
+    """Times both attention implementations at the shape and returns the TuningResult (config["impl"]: 0 tcgen05, 1 mma)."""
+    return (tuner or AutoTuner(TunerConfig.fast())).tune(AttentionKernel(batch, seq, heads, kv_heads, head_dim, **kw))
+
+
 class PreTuner:
     """Tunes the GEMM shapes of a model configuration ahead of time (crates/autotuner/src/lib.rs PreTuner)."""
 

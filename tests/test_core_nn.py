@@ -441,3 +441,35 @@ def test_check_env_reports_toolkit_libraries_and_gpus():
     old = check_env.collect(run=lambda *a, **k: _Old())
     if old["nvcc"]:
         assert any("too old" in p for p in old["problems"]) and not old["ok"]
+
+
+def test_gemm_tuning_table_feeds_cached_plans_back_into_gemm(tmp_path):
+    """A cached winner for a shape bucket is what `ops.gemm` is asked to run with once the table is applied; explicit
+    plans and uncached shapes are left alone."""
+    from rustral_b200.ops import matmul
+    from rustral_b200.tune import AttentionKernel, ConfigCache, GemmKernel, GemmTuningTable, MatmulShapeBucket
+    cache = ConfigCache(str(tmp_path / "cache.json"), "dev0")
+    key = MatmulShapeBucket.of(4096, 4096, 1024).cache_key() + "_000"
+    cache.store_config(GemmKernel.kernel_id, "dev0", "bf16", key, {"block_n": 192, "splits": 2, "group_m": 8}, 10.0, 5)
+    key2 = MatmulShapeBucket.of(300, 300, 300).cache_key() + "_000"
+    cache.store_config(GemmKernel.kernel_id, "dev0", "bf16", key2, {"block_n": 0, "splits": 0, "group_m": 0}, 10.0, 5)
+    cache.save()
+    table = GemmTuningTable(ConfigCache(str(tmp_path / "cache.json"), "dev0"), device_id="dev0")
+    table.cache.load()
+    assert table.lookup(4096, 4096, 1024) == {"block_n": 192, "splits": 2, "group_m": 8}
+    assert table.lookup(300, 300, 300) is None                 # the winner was the built-in plan
+    assert table.lookup(4096, 4096, 1024, b_mn=True) is None   # another operand layout: not tuned
+    assert (table.hits, table.misses) == (1, 2)
+    try:
+        table.apply()
+        assert matmul._PLAN_HOOK == table.lookup
+        x = torch.randn(8, 16)
+        w = torch.randn(4, 16)
+        assert torch.allclose(matmul.gemm(x, w), x @ w.t(), atol=1e-5)          # CPU tensors never consult the table
+    finally:
+        GemmTuningTable.remove()
+    assert matmul._PLAN_HOOK is None
+    k = AttentionKernel(4, 1024, 12, 12, 64)
+    assert k.config_space().size() == 2 and k.default_config() == {"impl": 0}
+    assert k.input_signature() == "bmedium_smedium_h12_kv12_d64_11".replace("bmedium", "btiny")
+    assert k.flops() == 4.0 * 4 * 1024 * 1024 * 12 * 64 * 3.5 * 0.5

@@ -361,3 +361,30 @@ def test_bounded_wait_expires_and_reports_without_losing_the_context():
     N.check(lib.rb_wait_all(pad.data_ptr(), 2, 0, 1, 50, N.stream_ptr()), "rb_wait_all")
     torch.cuda.synchronize()
     assert N.read_status(clear=True)[0] == 0
+
+
+def test_autotuner_tunes_real_kernels_and_feeds_gemm(tmp_path, cuda_status):
+    """The tuner times the tcgen05 GEMM's tile plans and both attention implementations with CUDA events, caches the
+    winners, and the applied table changes nothing about the result of a GEMM it serves."""
+    from rustral_b200.ops import matmul
+    from rustral_b200.tune import (AutoTuner, ConfigCache, GemmKernel, GemmTuningTable, TunerConfig, tune_attention, tune_gemm)
+    cfg = TunerConfig.fast()
+    cfg.max_evals, cfg.max_tuning_time_s, cfg.min_improvement_pct = 6, 20.0, 0.0
+    tuner = AutoTuner(cfg, ConfigCache(str(tmp_path / "tune.json"), cfg.device_id or torch.cuda.get_device_name(0)))
+    r = tune_gemm(2048, 1536, 512, tuner)
+    assert r.time_us > 0 and r.evaluated >= 1 and set(r.config) == {"block_n", "splits", "group_m"}
+    again = tune_gemm(2048, 1536, 512, tuner)
+    assert again.from_cache and again.config == r.config
+    ra = tune_attention(2, 512, 4, 2, 64, tuner)
+    assert ra.config["impl"] in (0, 1) and ra.time_us > 0
+    a = _bf((2048, 512), 1).cuda()
+    b = _bf((1536, 512), 2).cuda()
+    ref = matmul.gemm(a, b)
+    table = GemmTuningTable(tuner.cache, device_id=tuner.config.device_id)
+    try:
+        table.apply()
+        out = matmul.gemm(a, b)
+    finally:
+        GemmTuningTable.remove()
+    _close(out, ref, what="gemm under a tuned plan")
+    assert table.hits + table.misses == 1
