@@ -388,3 +388,25 @@ def test_autotuner_tunes_real_kernels_and_feeds_gemm(tmp_path, cuda_status):
         GemmTuningTable.remove()
     _close(out, ref, what="gemm under a tuned plan")
     assert table.hits + table.misses == 1
+
+
+@pytest.mark.parametrize("N,C,H,W,O,k,stride,nopad", [(4, 1, 28, 28, 8, 3, 1, False), (2, 3, 33, 47, 13, 3, 2, False),
+                                                       (1, 3, 64, 64, 16, 5, 1, True), (3, 2, 9, 7, 5, 1, 1, False)])
+def test_direct_conv2d_matches_fp32_convolution(N, C, H, W, O, k, stride, nopad, cuda_status):
+    """The direct kernel (inference path of Conv2d) against an fp32 PyTorch convolution, and against the im2col +
+    GEMM path that the same layer takes when gradients are needed."""
+    import torch.nn.functional as F
+    from rustral_b200.core import B200Backend, ForwardCtx
+    from rustral_b200.nn import Conv2d, Conv2dConfig
+    be = B200Backend()
+    conv = Conv2d.new(be, Conv2dConfig(O, k, k, stride=stride, no_padding=nopad, in_channels=C), seed=3)
+    conv.bias.tensor.data.copy_(_bf((O,), 9).cuda())
+    x = _bf((N, C, H, W), 4).cuda()
+    y = conv(x, ForwardCtx.inference(be))
+    pad = 0 if nopad else k // 2
+    ref = F.conv2d(x.float(), conv.weight.tensor.float(), conv.bias.tensor.float(), stride=stride, padding=pad)
+    assert y.shape == ref.shape and y.dtype == torch.bfloat16 and not y.requires_grad
+    _close(y, ref, what="direct conv2d")
+    y_train = conv(x, ForwardCtx.train(be))
+    assert y_train.requires_grad
+    _close(y_train, ref, what="im2col conv2d")
