@@ -6,8 +6,12 @@ from dataclasses import dataclass
 
 import torch
 
+from .. import _native as N_
 from .. import ops
 from ..core import ForwardCtx, Module, Parameter, Saveable, StatefulModule, Trainable
+
+
+N_.optional_sig("rb_lstm_gates_fwd", [N_.c_void_p, N_.c_ll, N_.c_void_p, N_.c_void_p, N_.c_void_p, N_.c_int, N_.c_int, N_.c_void_p])
 
 
 @dataclass
@@ -71,6 +75,28 @@ class LstmCell(RnnCell):
     def forward(self, x_state, ctx=None):
         x, state = x_state
         return self.step(x, state, ctx)
+
+    def forward_sequence(self, xs, ctx: ForwardCtx, state=None):
+        """Inference on the GPU: the input projections of ALL steps are one GEMM, and a step is one GEMM (h W_h^T with
+        that projection as its residual) plus the fused gate kernel.  With gradients, or on the CPU: the generic loop."""
+        needs_grad = torch.is_grad_enabled() and (xs.requires_grad or (ctx is not None and ctx.is_training()))
+        H = self.hidden_size
+        if not xs.is_cuda or xs.dtype != torch.bfloat16 or needs_grad or H % 8:
+            return super().forward_sequence(xs, ctx, state)
+        T, B, I = xs.shape
+        lib = N_.kernels()
+        with torch.no_grad():
+            h, c = state if state is not None else self.initial_state(B, ctx, xs)
+            h, c = h.contiguous(), c.contiguous().clone()
+            wx, wh, bias = self.wx.tensor.detach(), self.wh.tensor.detach(), self.b.tensor.detach()
+            xproj = ops.linear(xs.reshape(T * B, I).contiguous(), wx, bias).view(T, B, 4 * H)
+            outs = torch.empty((T, B, H), dtype=xs.dtype, device=xs.device)
+            for t in range(T):
+                gates = ops.linear(h, wh, None, "none", xproj[t])
+                N_.check(lib.rb_lstm_gates_fwd(gates.data_ptr(), gates.stride(0), c.data_ptr(), outs[t].data_ptr(), c.data_ptr(),
+                                               B, H, N_.stream_ptr()), "rb_lstm_gates_fwd")
+                h = outs[t]
+        return outs, (h, c)
 
 
 class GruCell(RnnCell):

@@ -410,3 +410,31 @@ def test_direct_conv2d_matches_fp32_convolution(N, C, H, W, O, k, stride, nopad,
     y_train = conv(x, ForwardCtx.train(be))
     assert y_train.requires_grad
     _close(y_train, ref, what="im2col conv2d")
+
+
+@pytest.mark.parametrize("T,B,I,H", [(12, 1, 128, 128), (7, 5, 40, 64)])
+def test_lstm_inference_sequence_matches_fp32_recurrence(T, B, I, H, cuda_status):
+    """The GPU inference path of LstmCell (one input-projection GEMM, then per step one GEMM + the fused gate kernel)
+    against the recurrence evaluated in fp32 PyTorch, and against the generic per-step path."""
+    from rustral_b200.core import B200Backend, ForwardCtx
+    from rustral_b200.nn import LstmCell
+    be = B200Backend()
+    cell = LstmCell.new(be, I, H, seed=5)
+    cell.b.tensor.data.copy_(_bf((4 * H,), 8, 0.1).cuda())
+    xs = _bf((T, B, I), 6).cuda()
+    outs, (h, c) = cell.forward_sequence(xs, ForwardCtx.inference(be))
+    wx, wh, b = cell.wx.tensor.float().cpu(), cell.wh.tensor.float().cpu(), cell.b.tensor.float().cpu()
+    hr, cr, ref = torch.zeros(B, H), torch.zeros(B, H), []
+    for t in range(T):
+        g = xs[t].float().cpu() @ wx.t() + hr @ wh.t() + b
+        i, f, o, gg = torch.sigmoid(g[:, :H]), torch.sigmoid(g[:, H:2 * H]), torch.sigmoid(g[:, 2 * H:3 * H]), torch.tanh(g[:, 3 * H:])
+        cr = f * cr + i * gg
+        hr = o * torch.tanh(cr)
+        ref.append(hr)
+    ref = torch.stack(ref)
+    assert outs.shape == (T, B, H) and not outs.requires_grad
+    _close(outs, ref, tol=3e-2, what="lstm outputs")
+    _close(c, cr, tol=3e-2, what="lstm cell state")
+    assert torch.equal(h, outs[-1])
+    slow, _ = super(LstmCell, cell).forward_sequence(xs, ForwardCtx.inference(be))
+    _close(outs, slow, tol=3e-2, what="fast vs generic lstm path")
