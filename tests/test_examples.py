@@ -172,3 +172,18 @@ def _stage_wikitext_into(cache):
     text = "\n".join(" ".join(words[(i * 7 + j * (3 + i % 5)) % len(words)] for j in range(12)) + " ." for i in range(60))
     for s in ("train", "valid", "test"):
         (d / f"{s}.txt").write_text(text)
+
+
+def test_bench_reference_arm_prints_one_json_line():
+    """`bench.py --impl reference` answers with a single JSON line and exit code 0 even where the reference cannot run."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2",
+                          "--warmup", "3"], capture_output=True, text=True, timeout=120, cwd=root)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [l for l in res.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1
+    doc = json.loads(lines[0])
+    assert doc["impl"] == "reference" and (("unavailable" in doc and isinstance(doc["unavailable"], str) and "\n" not in doc["unavailable"])
+                                           or "value" in doc)
