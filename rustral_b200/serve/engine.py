@@ -97,10 +97,25 @@ class ServingEngine:
         self.scheduler._retire()
         return self.scheduler.completed
 
-    def generate(self, prompt, max_tokens: int) -> list:
+    def generate(self, prompt, max_tokens: int, keep_record: bool = False) -> list:
+        """Runs one request to completion and returns its tokens.  The request's record is dropped afterwards (a
+        long-running server would otherwise accumulate every request it ever served) unless `keep_record`."""
         rid = self.submit(prompt, max_tokens)
         self.run_to_completion()
-        return self.scheduler.get(rid).generated
+        tokens = list(self.scheduler.get(rid).generated)
+        if not keep_record:
+            self.release(rid)
+        return tokens
+
+    def release(self, rid: int) -> None:
+        """Forgets a COMPLETED request: its entry in the scheduler (and the native core) and in `scheduler.completed`."""
+        sch = self.scheduler
+        r = sch.get(rid)
+        if r is None or r.state is not RequestState.COMPLETED:
+            return
+        sch.completed[:] = [c for c in sch.completed if c.id != rid]
+        if hasattr(sch, "forget"):
+            sch.forget(rid)
 
     def metrics(self, wall_s: float) -> ServingMetrics:
         done = self.scheduler.completed

@@ -164,3 +164,23 @@ def test_native_scheduler_core_makes_the_same_decisions_as_the_python_specificat
         assert all(b.get(r.id).state.value == "completed" for r in b.completed)
         b.forget(b.completed[0].id)
         assert b.get(b.completed[0].id) is None
+
+
+def test_generate_releases_the_request_record():
+    """A server that answers through `generate` does not accumulate finished requests, in Python or in the native core."""
+    cfg = preset("gpt2-test", seq_len=64, d_model=64, ffn_dim=128)
+    eng = ServingEngine(ModelRunner(cfg, device="cpu", num_blocks=32), max_batch_size=4)
+    for i in range(5):
+        toks = eng.generate([3, 4, 5 + i], 3)
+        assert len(toks) == 3
+    sch = eng.scheduler
+    assert sch.completed == [] and sch.requests == {} and not sch.has_work() and sch.stats.completed == 5
+    kept = eng.generate([7, 8], 2, keep_record=True)
+    assert len(sch.completed) == 1 and sch.completed[0].generated == kept
+    rid = sch.completed[0].id
+    eng.release(rid)
+    eng.release(rid)                                  # idempotent
+    assert sch.completed == [] and sch.get(rid) is None
+    pending = eng.submit([1, 2, 3], 2)
+    eng.release(pending)                              # not completed: left alone
+    assert sch.get(pending) is not None
