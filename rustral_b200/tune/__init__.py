@@ -240,11 +240,12 @@ class TunableKernel:
         return 0.0
 
 
-def benchmark_kernel(fn, warmup: int, iters: int) -> float:
-    """Median microseconds per call: CUDA events on the current stream when a GPU is present, host clock otherwise."""
+def benchmark_kernel(fn, warmup: int, iters: int, host_timed: bool = False) -> float:
+    """Median microseconds per call: CUDA events on the current stream when a GPU is present, host clock otherwise
+    (or when `host_timed`: a kernel object that does its work on the CPU sets `host_timed = True`)."""
     for _ in range(warmup):
         fn()
-    if torch.cuda.is_available():
+    if torch.cuda.is_available() and not host_timed:
         torch.cuda.synchronize()
         ts = []
         for _ in range(iters):
@@ -295,9 +296,9 @@ class AutoTuner:
             e = self.cache.get_config(kernel.kernel_id, cfg.device_id, cfg.dtype, bucket)
             if e is not None:
                 self.stats["cache_hits"] += 1
-                t = benchmark_kernel(kernel.with_config(e.config), cfg.warmup, cfg.timing)
+                t = benchmark_kernel(kernel.with_config(e.config), cfg.warmup, cfg.timing, getattr(kernel, "host_timed", False))
                 return TuningResult(dict(e.config), t, t, 0, True)
-        t_default = benchmark_kernel(kernel.with_config(default), cfg.warmup, cfg.timing)
+        t_default = benchmark_kernel(kernel.with_config(default), cfg.warmup, cfg.timing, getattr(kernel, "host_timed", False))
         search = SearchHandle(kernel.config_space(), cfg.strategy, cfg.seed, min(cfg.max_evals, 5) if cfg.ci_mode else cfg.max_evals)
         search.report(default, t_default)
         t0 = time.perf_counter()
@@ -306,7 +307,7 @@ class AutoTuner:
             if c is None:
                 break
             try:
-                t = benchmark_kernel(kernel.with_config(c), cfg.warmup, cfg.timing)
+                t = benchmark_kernel(kernel.with_config(c), cfg.warmup, cfg.timing, getattr(kernel, "host_timed", False))
             except Exception:   # noqa: BLE001 - a configuration the kernel rejects is simply not a candidate
                 t = float("inf")
             if t != float("inf"):

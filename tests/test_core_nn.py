@@ -396,6 +396,7 @@ def test_kernel_factory_and_op_config():
 
     class Fake(TunableKernel, ConfigurableKernel):
         kernel_id = "fake_gemm"
+        host_timed = True
         M = 4096
         calls = []
 
@@ -410,7 +411,7 @@ def test_kernel_factory_and_op_config():
 
         def with_config(self, config):
             import time as _t
-            cost = 0.002 if (config["block_n"], config["splits"]) == (256, 1) else 0.004
+            cost = 0.001 if (config["block_n"], config["splits"]) == (256, 1) else 0.008
             return lambda: (Fake.calls.append(dict(config)), _t.sleep(cost))
 
     import tempfile
