@@ -277,7 +277,9 @@ def dropout_mask_reference(n: int, p: float, seed: int):
 
 def dropout(a, p: float, training: bool = True, seed: int = 0, offset: int = 0, rng: str = "philox",
             return_mask: bool = False):
-    """Inverted dropout; identity when not training or p == 0."""
+    """Inverted dropout; identity when not training or p == 0.  p must lie in [0, 1)."""
+    if not (0.0 <= p < 1.0):
+        raise ValueError(f"dropout probability must be in [0, 1), got {p}")
     if not training or p <= 0.0:
         return (a, None) if return_mask else a
     if not a.is_cuda:
