@@ -4,6 +4,7 @@ decoder engine ({"prompt": [ids], "max_tokens": n} -> {"tokens": [ids]}).  Stand
 request handlers hand work to it through a bounded InferencePool, so the model is never entered concurrently.
 
     python -m rustral_b200.serve.http_server --artifact linear.safetensors --in-features 4 --out-features 3 --bias
+    python -m rustral_b200.serve.http_server --model llama-8b --device cuda:0 --weights llama.safetensors --bind 0.0.0.0:8080
 """
 from __future__ import annotations
 
@@ -173,25 +174,70 @@ def start_background(state: ServerState, host: str = "127.0.0.1", port: int = 0)
     return httpd, th
 
 
-def main(argv=None):
-    ap = argparse.ArgumentParser(description="rustral-b200 inference server")
-    ap.add_argument("--artifact", required=True, help="safetensors file of one Linear (keys weight, bias)")
-    ap.add_argument("--bind", default="127.0.0.1:8080")
-    ap.add_argument("--in-features", type=int, required=True)
-    ap.add_argument("--out-features", type=int, required=True)
-    ap.add_argument("--bias", action="store_true")
-    ap.add_argument("--device", default="cpu")
-    a = ap.parse_args(argv)
+def build_state(a) -> ServerState:
+    """The server state for parsed command-line arguments: a Linear artifact behind /v1/infer, or a decoder engine
+    (continuous batching over the paged KV cache) behind /v1/generate."""
     from ..core import B200Backend, CpuBackend
+    if a.model:
+        from ..models.config import preset
+        from .engine import ServingEngine
+        from .model_runner import ModelRunner
+        cfg = preset(a.model, **({"n_layer": a.layers} if a.layers else {}))
+        params = None
+        if a.device != "cpu" and cfg.arch == "llama":
+            from .weights import InferenceWeights           # bf16 inference weights (no optimizer buffers)
+            params = InferenceWeights.random_llama(cfg, a.device, 0, 1, a.seed)
+        runner = ModelRunner(cfg, params=params, device=a.device, num_blocks=a.blocks, block_size=a.page, seed=a.seed)
+        if a.weights:
+            from ..io import safetensors_io as st
+            tensors, _ = st.load_file(a.weights)            # strict: names and shapes must match the preset
+            if hasattr(runner.params, "tensors"):
+                runner.params.load_state_dict(tensors, cfg)
+            else:
+                runner.params.load_state_dict(tensors)
+        engine = ServingEngine(runner, max_batch_size=a.max_batch, eos_id=a.eos_id)
+        engine.generate([1, 2, 3], 2)                       # warm-up: compiles nothing, but touches every kernel once
+        meta = {"model": a.model, "layers": cfg.n_layer, "d_model": cfg.d_model, "vocab_size": cfg.vocab_size,
+                "context": cfg.seq_len, "page_size": a.page, "kv_blocks": a.blocks, "device": a.device,
+                "weights": a.weights or "random-init"}
+        return ServerState(generate_fn=engine_generate_fn(engine), metadata=meta)
+    if not a.artifact or not a.in_features or not a.out_features:
+        raise SystemExit("give --model NAME (decoder engine) or --artifact FILE --in-features N --out-features M (Linear)")
     from ..nn.linear import LinearBuilder
     from ..runtime.model_io import load_model_from_path
     backend = CpuBackend() if a.device == "cpu" else B200Backend()
     lin = LinearBuilder(a.in_features, a.out_features).with_bias(a.bias).build(backend)
     load_model_from_path(lin, a.artifact)          # strict: missing / extra keys and shape mismatches are errors
+    return ServerState(linear_infer_fn(lin, a.in_features),
+                       metadata={"model": "linear", "in_features": a.in_features, "out_features": a.out_features,
+                                 "bias": a.bias, "backend": backend.name})
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(description="rustral-b200 inference server")
+    ap.add_argument("--bind", default="127.0.0.1:8080")
+    ap.add_argument("--device", default="cpu")
+    g = ap.add_argument_group("Linear artifact (/v1/infer)")
+    g.add_argument("--artifact", help="safetensors file of one Linear (keys weight, bias)")
+    g.add_argument("--in-features", type=int, default=0)
+    g.add_argument("--out-features", type=int, default=0)
+    g.add_argument("--bias", action="store_true")
+    e = ap.add_argument_group("decoder engine (/v1/generate)")
+    e.add_argument("--model", help="model preset, e.g. llama-8b, gpt2-small")
+    e.add_argument("--layers", type=int, default=0, help="override the preset's depth")
+    e.add_argument("--weights", help="safetensors state dict of the model; random-init when absent")
+    e.add_argument("--blocks", type=int, default=4096, help="KV-cache pages")
+    e.add_argument("--page", type=int, default=16, help="tokens per KV-cache page")
+    e.add_argument("--max-batch", type=int, default=64)
+    e.add_argument("--eos-id", type=int, default=None)
+    e.add_argument("--seed", type=int, default=0)
+    return ap.parse_args(argv)
+
+
+def main(argv=None):
+    a = parse_args(argv)
+    state = build_state(a)
     host, port = a.bind.rsplit(":", 1)
-    state = ServerState(linear_infer_fn(lin, a.in_features),
-                        metadata={"model": "linear", "in_features": a.in_features, "out_features": a.out_features,
-                                  "bias": a.bias, "backend": backend.name})
     serve(state, host, int(port))
 
 

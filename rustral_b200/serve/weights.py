@@ -22,6 +22,37 @@ class InferenceWeights:
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.tensors.values())
 
+    def load_state_dict(self, state: dict, cfg: GPTConfig) -> None:
+        """Strict load of an UNSHARDED Llama-style checkpoint in the trainer's format (`FlatParams.state_dict`: fp32,
+        vocabulary unpadded, attention projections under attn.wq / wk / wv): every expected key present, no extra
+        key, shapes equal; nothing is written before all checks pass.  Tensor-parallel ranks load the full set and
+        cut their shard with `shard_of`."""
+        from ..core.errors import SerializationError, ShapeMismatch
+        plan = {}                                         # checkpoint key -> (destination tensor, row slice)
+        hd = cfg.head_dim
+        q_end, k_end = cfg.n_head * hd, (cfg.n_head + cfg.n_kv_head) * hd
+        for name, t in self.tensors.items():
+            if ".attn.wqkv." in name:
+                for nm, sl in (("wq", slice(0, q_end)), ("wk", slice(q_end, k_end)), ("wv", slice(k_end, t.shape[0]))):
+                    plan[name.replace("wqkv", nm)] = (t, sl)
+            elif name in ("tok_embed.embed", "head.weight"):
+                plan[name] = (t, slice(0, cfg.vocab_size))
+            else:
+                plan[name] = (t, slice(0, t.shape[0]))
+        missing = [k for k in plan if k not in state]
+        extra = [k for k in state if k not in plan]
+        if missing:
+            raise SerializationError(f"missing keys: {missing}")
+        if extra:
+            raise SerializationError(f"unexpected keys: {extra}")
+        for k, (t, sl) in plan.items():
+            want = (sl.stop - sl.start, *t.shape[1:])
+            if tuple(state[k].shape) != want:
+                raise ShapeMismatch(want, state[k].shape, k)
+        with torch.no_grad():
+            for k, (t, sl) in plan.items():
+                t[sl].copy_(state[k].to(t.device, t.dtype))
+
     # ------------------------------------------------------------------------------------------------ constructors
     @classmethod
     def random_llama(cls, cfg: GPTConfig, device, rank: int = 0, world: int = 1, seed: int = 0) -> "InferenceWeights":

@@ -184,3 +184,54 @@ def test_generate_releases_the_request_record():
     pending = eng.submit([1, 2, 3], 2)
     eng.release(pending)                              # not completed: left alone
     assert sch.get(pending) is not None
+
+
+def test_http_server_decoder_engine_mode_and_inference_weight_loading(tmp_path):
+    """`--model` builds the continuous-batching engine behind /v1/generate, with weights loaded strictly from a
+    checkpoint in the trainer's format; the served tokens are the engine's own greedy tokens."""
+    from rustral_b200.core.errors import SerializationError
+    from rustral_b200.io import safetensors_io as st
+    from rustral_b200.serve.http_server import build_state, parse_args, start_background
+    from rustral_b200.serve.weights import InferenceWeights
+    cfg = preset("llama-test", seq_len=64, d_model=64, ffn_dim=128)
+    donor = ModelRunner(cfg, device="cpu", num_blocks=16, seed=5)
+    path = str(tmp_path / "m.safetensors")
+    st.save_file(donor.params.state_dict(), path)
+    args = ["--model", "llama-test", "--weights", path, "--blocks", "32", "--max-batch", "4", "--seed", "1"]
+    import rustral_b200.models.config as C
+    saved = dict(C.PRESETS["llama-test"])
+    C.PRESETS["llama-test"].update(seq_len=64, d_model=64, ffn_dim=128)
+    try:
+        state = build_state(parse_args(args))
+    finally:
+        C.PRESETS["llama-test"].clear()
+        C.PRESETS["llama-test"].update(saved)
+    httpd, _ = start_background(state)
+    base = f"http://127.0.0.1:{httpd.server_address[1]}"
+    try:
+        meta = json.load(urllib.request.urlopen(base + "/v1/metadata"))
+        assert meta["model"] == "llama-test" and meta["weights"] == path and meta["kv_blocks"] == 32
+        req = urllib.request.Request(base + "/v1/generate", json.dumps({"prompt": [5, 6, 7, 8], "max_tokens": 6}).encode())
+        served = json.load(urllib.request.urlopen(req))["tokens"]
+        want = ServingEngine(donor, max_batch_size=2).generate([5, 6, 7, 8], 6)
+        assert served == want and len(served) == 6
+        bad = urllib.request.Request(base + "/v1/generate", json.dumps({"prompt": [10 ** 9]}).encode())
+        with pytest.raises(urllib.error.HTTPError) as e:
+            urllib.request.urlopen(bad)
+        assert e.value.code == 400
+    finally:
+        httpd.shutdown()
+        state.shutdown()
+    # the bf16 inference weight set loads the same checkpoint strictly
+    iw = InferenceWeights.random_llama(cfg, "cpu", seed=9)
+    sd = donor.params.state_dict()
+    iw.load_state_dict(sd, cfg)
+    hd = cfg.head_dim
+    assert torch.equal(iw.w("layers.0.attn.wqkv.weight")[:cfg.n_head * hd], sd["layers.0.attn.wq.weight"])
+    assert torch.equal(iw.w("tok_embed.embed")[:cfg.vocab_size], sd["tok_embed.embed"])
+    with pytest.raises(SerializationError):
+        iw.load_state_dict({k: v for k, v in sd.items() if k != "final_norm.weight"}, cfg)
+    with pytest.raises(SerializationError):
+        iw.load_state_dict(dict(sd, bogus=torch.zeros(1)), cfg)
+    with pytest.raises(SystemExit):
+        build_state(parse_args([]))
