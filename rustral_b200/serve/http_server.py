@@ -1,7 +1,8 @@
 """HTTP front end (crates/inference-server/src/main.rs:23-251): GET /health, /ready, /v1/metadata, /metrics and
 POST /v1/infer (one Linear artifact, {"input": [[f32]]} -> {"output": [[f32]]}) plus POST /v1/generate for the
-decoder engine ({"prompt": [ids], "max_tokens": n} -> {"tokens": [ids]}).  Standard-library server, one engine thread;
-request handlers hand work to it through a bounded InferencePool, so the model is never entered concurrently.
+decoder engine ({"prompt": [ids], "max_tokens": n} -> {"tokens": [ids]}).  Standard-library server; the model is never
+entered concurrently: /v1/infer goes through a bounded InferencePool, /v1/generate through one EngineLoop thread that
+batches the requests of all handlers continuously.
 
     python -m rustral_b200.serve.http_server --artifact linear.safetensors --in-features 4 --out-features 3 --bias
     python -m rustral_b200.serve.http_server --model llama-8b --device cuda:0 --weights llama.safetensors --bind 0.0.0.0:8080
@@ -21,7 +22,8 @@ from ..runtime.inference import InferencePool
 
 
 class ServerState:
-    def __init__(self, infer_fn=None, generate_fn=None, metadata=None, workers: int = 1, queue_bound: int = 64):
+    def __init__(self, infer_fn=None, generate_fn=None, metadata=None, workers: int = 1, queue_bound: int = 64,
+                 generate_workers: int = 1, engine_loop=None):
         self.metadata = metadata or {}
         self.ready = True
         self.requests_total = 0
@@ -29,7 +31,9 @@ class ServerState:
         self.latency_ns_sum = 0
         self.lock = threading.Lock()
         self.infer_pool = InferencePool(workers, queue_bound, infer_fn) if infer_fn else None
-        self.generate_pool = InferencePool(1, queue_bound, generate_fn) if generate_fn else None
+        # with an engine loop the handlers only wait on their own request, so many may be in flight at once
+        self.generate_pool = InferencePool(generate_workers, queue_bound, generate_fn) if generate_fn else None
+        self.engine_loop = engine_loop
 
     def record(self, ns: int, ok: bool) -> None:
         with self.lock:
@@ -51,6 +55,8 @@ class ServerState:
         for p in (self.infer_pool, self.generate_pool):
             if p is not None:
                 p.shutdown()
+        if self.engine_loop is not None:
+            self.engine_loop.shutdown()
 
 
 class BadRequest(Exception):
@@ -132,7 +138,81 @@ def linear_infer_fn(linear, in_features: int):
     return fn
 
 
-def engine_generate_fn(engine):
+class EngineLoop:
+    """One thread owns the engine: it takes submissions from the request handlers, steps the engine while there is
+    work, and wakes each handler when its request completes.  Requests that arrive while others are generating join
+    the running batch at the next iteration (continuous batching across HTTP requests), instead of queueing behind a
+    whole generation."""
+
+    def __init__(self, engine, max_pending: int = 256):
+        import queue
+        self.engine = engine
+        self._inbox: "queue.Queue" = queue.Queue(maxsize=max_pending)
+        self._waiting: dict = {}                     # request id -> (result box, event) of the handler waiting for it
+        self.steps = 0
+        self._stop = False
+        self._thread = threading.Thread(target=self._run, daemon=True, name="rustral-engine-loop")
+        self._thread.start()
+
+    def _admit(self, item) -> None:
+        prompt, max_tokens, box, ev = item
+        try:
+            self._waiting[self.engine.submit(prompt, max_tokens)] = (box, ev)
+        except Exception as e:   # noqa: BLE001 - delivered to the waiting handler
+            box.append((False, e))
+            ev.set()
+
+    def _deliver(self) -> None:
+        """Hands finished requests to their handlers and drops their records."""
+        eng = self.engine
+        eng.scheduler._retire()
+        for r in list(eng.scheduler.completed):
+            w = self._waiting.pop(r.id, None)
+            if w is not None:
+                w[0].append((True, list(r.generated)))
+                w[1].set()
+            eng.release(r.id)
+
+    def _run(self) -> None:
+        import queue
+        eng = self.engine
+        while not self._stop:
+            try:                                     # block only when the engine is idle
+                item = self._inbox.get(timeout=0.05) if not eng.scheduler.has_work() else self._inbox.get_nowait()
+                self._admit(item)
+                continue                             # take everything that is waiting before the next step
+            except queue.Empty:
+                pass
+            if eng.scheduler.has_work():
+                try:
+                    eng.step()
+                    self.steps += 1
+                except Exception as e:   # noqa: BLE001 - a failed step must not strand the waiting handlers
+                    for box, ev in self._waiting.values():
+                        box.append((False, e))
+                        ev.set()
+                    self._waiting.clear()
+                    continue
+                self._deliver()
+
+    def generate(self, prompt, max_tokens: int, timeout: float | None = 600.0) -> list:
+        box, ev = [], threading.Event()
+        self._inbox.put((list(prompt), int(max_tokens), box, ev), timeout=timeout)
+        if not ev.wait(timeout):
+            raise TimeoutError("generation timed out")
+        ok, val = box[0]
+        if not ok:
+            raise val
+        return val
+
+    def shutdown(self) -> None:
+        self._stop = True
+        self._thread.join(timeout=10)
+
+
+def engine_generate_fn(engine, loop: "EngineLoop | None" = None):
+    """Handler body of /v1/generate.  With `loop` the request joins the shared engine loop; without it the calling
+    thread runs the engine to completion (single-request use)."""
     def fn(body):
         prompt = body.get("prompt")
         if not isinstance(prompt, list) or not prompt or not all(isinstance(t, int) for t in prompt):
@@ -142,6 +222,8 @@ def engine_generate_fn(engine):
             raise BadRequest("token id out of range")
         max_tokens = int(body.get("max_tokens", 16))
         try:
+            if loop is not None:
+                return {"tokens": loop.generate(prompt, max_tokens)}
             return {"tokens": engine.generate(prompt, max_tokens)}
         except ValueError as e:
             raise BadRequest(str(e))
@@ -200,7 +282,9 @@ def build_state(a) -> ServerState:
         meta = {"model": a.model, "layers": cfg.n_layer, "d_model": cfg.d_model, "vocab_size": cfg.vocab_size,
                 "context": cfg.seq_len, "page_size": a.page, "kv_blocks": a.blocks, "device": a.device,
                 "weights": a.weights or "random-init"}
-        return ServerState(generate_fn=engine_generate_fn(engine), metadata=meta)
+        loop = EngineLoop(engine)
+        return ServerState(generate_fn=engine_generate_fn(engine, loop), metadata=meta, generate_workers=a.max_batch,
+                           engine_loop=loop)
     if not a.artifact or not a.in_features or not a.out_features:
         raise SystemExit("give --model NAME (decoder engine) or --artifact FILE --in-features N --out-features M (Linear)")
     from ..nn.linear import LinearBuilder

@@ -235,3 +235,39 @@ def test_http_server_decoder_engine_mode_and_inference_weight_loading(tmp_path):
         iw.load_state_dict(dict(sd, bogus=torch.zeros(1)), cfg)
     with pytest.raises(SystemExit):
         build_state(parse_args([]))
+
+
+def test_engine_loop_batches_concurrent_http_style_requests():
+    """Requests from several handler threads join one running batch: same tokens as one-at-a-time generation, far
+    fewer engine steps than the sum of the individual generations, records released afterwards."""
+    import threading
+    from rustral_b200.serve.http_server import EngineLoop
+    cfg = preset("gpt2-test", seq_len=64, d_model=64, ffn_dim=128)
+    runner = ModelRunner(cfg, device="cpu", num_blocks=64, seed=2)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 9, 3, 12, 7, 4)]
+    solo = ServingEngine(ModelRunner(cfg, device="cpu", num_blocks=64, seed=2), max_batch_size=8)
+    want = [solo.generate(p, 10) for p in prompts]
+    eng = ServingEngine(runner, max_batch_size=8)
+    loop = EngineLoop(eng)
+    got, errs = [None] * len(prompts), []
+
+    def worker(i):
+        try:
+            got[i] = loop.generate(prompts[i], 10, timeout=120)
+        except Exception as e:      # noqa: BLE001
+            errs.append(e)
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(len(prompts))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=180)
+    try:
+        assert not errs and got == want
+        assert loop.steps < 6 * 10                      # 60 steps one after another; batched: little more than 10
+        assert eng.scheduler.requests == {} and eng.scheduler.completed == [] and runner.cache.free_blocks == 64
+        with pytest.raises(ValueError):
+            loop.generate([], 3, timeout=10)            # the engine's own validation reaches the caller
+        assert loop.generate(prompts[0], 10, timeout=60) == want[0]     # and the loop is still alive
+    finally:
+        loop.shutdown()
