@@ -176,6 +176,8 @@ class EngineLoop:
     def _run(self) -> None:
         import queue
         eng = self.engine
+        if eng.runner.device.type == "cuda":         # the current device is per thread
+            torch.cuda.set_device(eng.runner.device)
         while not self._stop:
             try:                                     # block only when the engine is idle
                 item = self._inbox.get(timeout=0.05) if not eng.scheduler.has_work() else self._inbox.get_nowait()
