@@ -36,3 +36,74 @@ def load_from_hub(module, model_id: str, revision: str = "main", key_map=None, s
 
 
 __all__ = ["hub_url", "download_state_dict", "save_state_dict_to_file", "load_from_hub", "FetchError"]
+
+
+# ---- checkpoint name conversion ---------------------------------------------------------------------------------
+def _strip(state: dict, prefix: str) -> dict:
+    return {(k[len(prefix):] if k.startswith(prefix) else k): v for k, v in state.items()}
+
+
+def convert_hf_gpt2(state: dict, n_layer: int | None = None) -> dict:
+    """Hugging Face GPT-2 names and layouts -> this framework's (`FlatParams.load_state_dict`).  GPT-2 stores its
+    projections as Conv1D weights [in, out]; they are transposed to [out, in], and the fused c_attn is cut into
+    wq / wk / wv.  The tied `lm_head.weight` and the causal-mask buffers (`attn.bias`, `attn.masked_bias`) are dropped."""
+    s = _strip(state, "transformer.")
+    out = {"tok_embed.embed": s["wte.weight"].float(), "pos_embed.embed": s["wpe.weight"].float(),
+           "final_norm.weight": s["ln_f.weight"].float(), "final_norm.bias": s["ln_f.bias"].float()}
+    layers = n_layer if n_layer is not None else 1 + max(int(k.split(".")[1]) for k in s if k.startswith("h."))
+    for l in range(layers):
+        h, p = f"h.{l}.", f"layers.{l}."
+        d = s[h + "ln_1.weight"].shape[0]
+        w, b = s[h + "attn.c_attn.weight"].float(), s[h + "attn.c_attn.bias"].float()
+        for i, nm in enumerate(("wq", "wk", "wv")):
+            out[p + f"attn.{nm}.weight"] = w[:, i * d:(i + 1) * d].t().contiguous()
+            out[p + f"attn.{nm}.bias"] = b[i * d:(i + 1) * d].clone()
+        out[p + "attn.wo.weight"] = s[h + "attn.c_proj.weight"].float().t().contiguous()
+        out[p + "attn.wo.bias"] = s[h + "attn.c_proj.bias"].float()
+        out[p + "ffn.fc1.weight"] = s[h + "mlp.c_fc.weight"].float().t().contiguous()
+        out[p + "ffn.fc1.bias"] = s[h + "mlp.c_fc.bias"].float()
+        out[p + "ffn.fc2.weight"] = s[h + "mlp.c_proj.weight"].float().t().contiguous()
+        out[p + "ffn.fc2.bias"] = s[h + "mlp.c_proj.bias"].float()
+        for src, dst in (("ln_1", "ln1"), ("ln_2", "ln2")):
+            out[p + dst + ".weight"] = s[h + src + ".weight"].float()
+            out[p + dst + ".bias"] = s[h + src + ".bias"].float()
+    return out
+
+
+def convert_hf_llama(state: dict, n_layer: int | None = None, tie_embeddings: bool = False) -> dict:
+    """Hugging Face Llama names -> this framework's.  Layouts already agree ([out, in] matrices, rotate-half rotary
+    pairs); gate_proj and up_proj are stacked into ffn.gate_up (gate rows first)."""
+    s = _strip(state, "model.")
+    out = {"tok_embed.embed": s["embed_tokens.weight"].float(), "final_norm.weight": s["norm.weight"].float()}
+    if not tie_embeddings:
+        out["head.weight"] = (s["lm_head.weight"] if "lm_head.weight" in s else s["embed_tokens.weight"]).float()
+    layers = n_layer if n_layer is not None else 1 + max(int(k.split(".")[1]) for k in s if k.startswith("layers."))
+    for l in range(layers):
+        h, p = f"layers.{l}.", f"layers.{l}."
+        for src, dst in (("q_proj", "wq"), ("k_proj", "wk"), ("v_proj", "wv"), ("o_proj", "wo")):
+            out[p + f"attn.{dst}.weight"] = s[h + f"self_attn.{src}.weight"].float()
+        out[p + "ffn.gate_up.weight"] = torch.cat([s[h + "mlp.gate_proj.weight"].float(), s[h + "mlp.up_proj.weight"].float()], 0)
+        out[p + "ffn.down.weight"] = s[h + "mlp.down_proj.weight"].float()
+        out[p + "ln1.weight"] = s[h + "input_layernorm.weight"].float()
+        out[p + "ln2.weight"] = s[h + "post_attention_layernorm.weight"].float()
+    return out
+
+
+def config_from_hf(hf_config) -> "GPTConfig":
+    """GPTConfig for a Hugging Face GPT-2 or Llama configuration object (or dict)."""
+    from ..models.config import GPTConfig
+    c = hf_config if isinstance(hf_config, dict) else hf_config.to_dict()
+    if c.get("model_type") == "gpt2":
+        return GPTConfig(vocab_size=c["vocab_size"], seq_len=c["n_positions"], n_layer=c["n_layer"], n_head=c["n_head"],
+                         d_model=c["n_embd"], ffn_dim=c.get("n_inner") or 4 * c["n_embd"], arch="gpt2", n_kv_head=c["n_head"],
+                         norm_eps=c.get("layer_norm_epsilon", 1e-5), tie_embeddings=True)
+    if c.get("model_type") == "llama":
+        rope = c.get("rope_theta") or (c.get("rope_parameters") or {}).get("rope_theta", 10000.0)
+        return GPTConfig(vocab_size=c["vocab_size"], seq_len=c["max_position_embeddings"], n_layer=c["num_hidden_layers"],
+                         n_head=c["num_attention_heads"], d_model=c["hidden_size"], ffn_dim=c["intermediate_size"], arch="llama",
+                         n_kv_head=c.get("num_key_value_heads") or c["num_attention_heads"], rope_theta=float(rope),
+                         norm_eps=c.get("rms_norm_eps", 1e-5), tie_embeddings=bool(c.get("tie_word_embeddings", False)))
+    raise ValueError(f"unsupported Hugging Face model type {c.get('model_type')!r}")
+
+
+__all__ += ["convert_hf_gpt2", "convert_hf_llama", "config_from_hf"]

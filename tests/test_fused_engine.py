@@ -113,3 +113,30 @@ def test_engine_state_dict_roundtrip_is_strict():
     bad["final_norm.weight"] = torch.zeros(3)
     with pytest.raises(ShapeMismatch):
         b.params.load_state_dict(bad)
+
+
+def test_hugging_face_checkpoints_convert_and_reproduce_hf_logits():
+    """Independent oracle: random GPT-2 and Llama (GQA, rotary) models built by the `transformers` library, converted
+    with utils.hf, give the same logits through this framework's engine (CPU, fp32) to round-off."""
+    transformers = pytest.importorskip("transformers")
+    from rustral_b200.runtime.fused_gpt import FusedGPTEngine
+    from rustral_b200.utils.hf import config_from_hf, convert_hf_gpt2, convert_hf_llama
+    torch.manual_seed(0)
+    ids = torch.randint(0, 300, (2, 32))
+    hc = transformers.GPT2Config(vocab_size=300, n_positions=32, n_embd=64, n_layer=2, n_head=4, resid_pdrop=0.0,
+                                 embd_pdrop=0.0, attn_pdrop=0.0)
+    lc = transformers.LlamaConfig(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                  num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=32, rope_theta=10000.0,
+                                  rms_norm_eps=1e-5, tie_word_embeddings=False, attention_dropout=0.0)
+    for hf_cfg, cls, conv in ((hc, transformers.GPT2LMHeadModel, convert_hf_gpt2), (lc, transformers.LlamaForCausalLM, convert_hf_llama)):
+        model = cls(hf_cfg).eval()
+        cfg = config_from_hf(hf_cfg)
+        eng = FusedGPTEngine(cfg, "cpu")
+        eng.params.load_state_dict(conv(model.state_dict()))            # strict: every name and shape must line up
+        with torch.no_grad():
+            ref = model(ids).logits
+        out = eng.logits(ids)[..., :300]
+        assert (out - ref).abs().max().item() < 1e-5, cfg.arch
+    assert config_from_hf(lc).n_kv_head == 2 and config_from_hf(hc).tie_embeddings
+    with pytest.raises(ValueError):
+        config_from_hf({"model_type": "bert"})
