@@ -107,3 +107,28 @@ def config_from_hf(hf_config) -> "GPTConfig":
 
 
 __all__ += ["convert_hf_gpt2", "convert_hf_llama", "config_from_hf"]
+
+
+def main(argv=None) -> int:
+    """python -m rustral_b200.utils.hf convert --arch {gpt2,llama} IN.safetensors OUT.safetensors
+    Rewrites a Hugging Face checkpoint file under this framework's parameter names (fp32), ready for
+    `LMTrainer.load_state_dict` or `python -m rustral_b200.serve.http_server --weights`."""
+    import argparse
+    ap = argparse.ArgumentParser(prog="rustral_b200.utils.hf", description=main.__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    c = sub.add_parser("convert")
+    c.add_argument("--arch", choices=["gpt2", "llama"], required=True)
+    c.add_argument("--tie-embeddings", action="store_true", help="(llama) the model shares its embedding with the LM head")
+    c.add_argument("src")
+    c.add_argument("dst")
+    a = ap.parse_args(argv)
+    tensors, _ = st.load_file(a.src)
+    out = convert_hf_gpt2(tensors) if a.arch == "gpt2" else convert_hf_llama(tensors, tie_embeddings=a.tie_embeddings)
+    save_state_dict_to_file(out, a.dst)
+    print(f"wrote {a.dst}: {len(out)} tensors, {sum(v.numel() for v in out.values())} parameters")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
