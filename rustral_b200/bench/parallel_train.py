@@ -63,6 +63,8 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--capacity-factor", type=float, default=1.5, help="expert-parallel receive capacity (x balanced share)")
+    ap.add_argument("--init-from", help="safetensors checkpoint (unsharded, this framework's names; see utils.hf for "
+                    "Hugging Face conversion): every rank loads its shard instead of the random initialisation")
     ap.add_argument("--unfused", action="store_true")
     ap.add_argument("--same-batch", action="store_true", help="train on one fixed batch (tests: the loss must fall)")
     a = ap.parse_args(argv)
@@ -121,6 +123,9 @@ def main(argv=None):
                               first_layer=pp_idx * per_stage, last_layer=(pp_idx + 1) * per_stage if pp_idx < a.pp - 1 else cfg.n_layer,
                               has_embed=pp_idx == 0, has_head=pp_idx == a.pp - 1, seed=1, fsdp=fsdp_ctx,
                               cp=cp_ctx, cp_striped=not a.cp_contiguous, dp_group=dist.group.WORLD if cp_ctx is not None else None)
+    if a.init_from:
+        from ..io import safetensors_io as st
+        model.load_state_dict(st.load_file(a.init_from)[0])
     # expert parallel: ZeRO-1 over the data-parallel ranks for the dense (replicated) parameters
     opt = MixedPrecisionAdamW(model, lr=a.lr, use_zero1=a.ep > 1)
     dp = a.ep * a.fsdp                                         # data-parallel replicas (these ranks see different data)

@@ -198,6 +198,76 @@ class ParallelDecoderLM:
     def parameters(self):
         return list(self.params.values())
 
+    # ------------------------------------------------------------------------------------------------ checkpoints
+    def _shard_plan(self) -> dict:
+        """local parameter name -> function(full state dict) giving this rank's tensor, for dense (non-MoE) models.
+        The full state uses the checkpoint names of the single-GPU engine (tok_embed.embed, layers.N.attn.wq.weight,
+        ..., ffn.gate_up.weight, head.weight), which is also what utils.hf.convert_hf_llama produces."""
+        c, tp, r = self.cfg, self.tp, self.tp_rank
+        hd = c.head_dim
+        hq, hk, f, v = c.n_head // tp, c.n_kv_head // tp, c.ffn_hidden // tp, c.vocab_size // tp
+        rows = lambda t, n: t[r * n:(r + 1) * n]
+        plan = {}
+        if self.has_embed:
+            plan["wte"] = lambda s: s["tok_embed.embed"]
+        if self.has_head:
+            plan["final_norm"] = lambda s: s["final_norm.weight"]
+            plan["head"] = lambda s: rows(s["head.weight"], v)
+        for l in range(self.first_layer, self.last_layer):
+            p, q = f"l{l}.", f"layers.{l}."
+            plan[p + "attn_norm"] = lambda s, q=q: s[q + "ln1.weight"]
+            plan[p + "mlp_norm"] = lambda s, q=q: s[q + "ln2.weight"]
+            plan[p + "wqkv"] = lambda s, q=q: torch.cat([rows(s[q + "attn.wq.weight"], hq * hd), rows(s[q + "attn.wk.weight"], hk * hd),
+                                                         rows(s[q + "attn.wv.weight"], hk * hd)], 0)
+            plan[p + "wo"] = lambda s, q=q: s[q + "attn.wo.weight"][:, r * hq * hd:(r + 1) * hq * hd]
+            plan[p + "wgu"] = lambda s, q=q: torch.cat([rows(s[q + "ffn.gate_up.weight"][:c.ffn_hidden], f),
+                                                        rows(s[q + "ffn.gate_up.weight"][c.ffn_hidden:], f)], 0)
+            plan[p + "wdown"] = lambda s, q=q: s[q + "ffn.down.weight"][:, r * f:(r + 1) * f]
+        return plan
+
+    def load_state_dict(self, state: dict) -> None:
+        """Loads an UNSHARDED dense checkpoint: every rank reads the full state and keeps its tensor-parallel /
+        pipeline (/ FSDP row) shard.  Strict for the parameters this rank owns: a missing tensor or a shape mismatch
+        raises before anything is written."""
+        if self.cfg.num_experts:
+            raise ValueError("load_state_dict covers dense models; expert weights have no single-GPU checkpoint format")
+        staged = {}
+        for name, pick in self._shard_plan().items():
+            try:
+                t = pick(state)
+            except KeyError as e:
+                raise KeyError(f"checkpoint is missing {e.args[0]!r} (needed for {name})") from None
+            if name in self.fsdp_shards:
+                W, rr = self.fsdp.world, self.fsdp.rank
+                n = t.shape[0] // W
+                t = t[rr * n:(rr + 1) * n]
+            if tuple(t.shape) != tuple(self.params[name].shape):
+                raise ValueError(f"{name}: checkpoint gives {tuple(t.shape)}, the model holds {tuple(self.params[name].shape)}")
+            staged[name] = t
+        with torch.no_grad():
+            for name, t in staged.items():
+                self.params[name].copy_(t.to(self.params[name].device, self.params[name].dtype))
+
+    def state_dict(self) -> dict:
+        """The unsharded checkpoint of a model held by ONE rank (no tensor / pipeline / FSDP sharding): fp32 tensors
+        under the single-GPU engine's names."""
+        if self.tp != 1 or self.fsdp is not None or self.cfg.num_experts or not (self.has_embed and self.has_head) or \
+                self.first_layer != 0 or self.last_layer != self.cfg.n_layer:
+            raise ValueError("state_dict exports unsharded dense models only")
+        c, P = self.cfg, self.params
+        hd = c.head_dim
+        qe, ke = c.n_head * hd, (c.n_head + c.n_kv_head) * hd
+        f32 = lambda t: t.detach().float().cpu().clone()
+        out = {"tok_embed.embed": f32(P["wte"]), "final_norm.weight": f32(P["final_norm"]), "head.weight": f32(P["head"])}
+        for l in range(c.n_layer):
+            p, q = f"l{l}.", f"layers.{l}."
+            w = f32(P[p + "wqkv"])
+            out[q + "attn.wq.weight"], out[q + "attn.wk.weight"], out[q + "attn.wv.weight"] = w[:qe].clone(), w[qe:ke].clone(), w[ke:].clone()
+            out[q + "attn.wo.weight"] = f32(P[p + "wo"])
+            out[q + "ffn.gate_up.weight"], out[q + "ffn.down.weight"] = f32(P[p + "wgu"]), f32(P[p + "wdown"])
+            out[q + "ln1.weight"], out[q + "ln2.weight"] = f32(P[p + "attn_norm"]), f32(P[p + "mlp_norm"])
+        return out
+
     def local_param_count(self) -> int:
         return sum(p.numel() for p in self.params.values())
 

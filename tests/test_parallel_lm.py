@@ -47,3 +47,52 @@ def test_parallel_lm_gpu_matches_cpu(moe):
     for n in ("l0.wqkv", "l1.wo", "wte", "head"):
         a, b = gpu.params[n].grad.float().cpu(), cpu.params[n].grad.float()
         assert (a - b).norm() / (b.norm() + 1e-9) < 8e-2, n
+
+
+def test_parallel_lm_loads_hugging_face_llama_and_shards_it_for_tensor_parallelism():
+    """A Llama built by `transformers` -> utils.hf -> ParallelDecoderLM: the training loss equals Hugging Face's (bf16
+    parameters, so to about 1e-2); the tensor-parallel shards of a two-rank layout tile the full tensors exactly; a
+    state_dict round trip is lossless."""
+    transformers = pytest.importorskip("transformers")
+    from rustral_b200.parallel.process_group import ProcessGroup
+    from rustral_b200.utils.hf import convert_hf_llama
+    torch.manual_seed(0)
+    lc = transformers.LlamaConfig(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                  num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=32, rope_theta=10000.0,
+                                  rms_norm_eps=1e-5, tie_word_embeddings=False, attention_dropout=0.0)
+    hf = transformers.LlamaForCausalLM(lc).eval()
+    state = convert_hf_llama(hf.state_dict())
+    cfg = ParallelLMConfig(vocab_size=256, d_model=64, n_layer=2, n_head=4, n_kv_head=2, ffn_hidden=128, seq_len=32,
+                           rope_theta=10000.0, eps=1e-5)
+    model = ParallelDecoderLM(cfg, "cpu", seed=9)
+    model.load_state_dict(state)
+    tokens = torch.randint(0, 256, (3, 33), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf(tokens[:, :-1], labels=None).logits.float()
+        ref_loss = torch.nn.functional.cross_entropy(ref.reshape(-1, 256), tokens[:, 1:].reshape(-1))
+        loss = model.forward_loss(tokens)
+    assert abs(float(loss) - float(ref_loss)) < 2e-2, (float(loss), float(ref_loss))
+    back = model.state_dict()
+    assert set(back) == set(state)
+    for k in state:
+        assert torch.equal(back[k], state[k].bfloat16().float()), k
+    with pytest.raises(KeyError):
+        model.load_state_dict({k: v for k, v in state.items() if k != "layers.1.ffn.down.weight"})
+    with pytest.raises(ValueError):
+        model.load_state_dict(dict(state, **{"final_norm.weight": torch.ones(3)}))
+    # two tensor-parallel ranks: the shards tile the full tensors
+    groups = ProcessGroup.new_threaded(2)
+    shards = []
+    for pg in groups:
+        m = ParallelDecoderLM(cfg, "cpu", tp_pg=pg, seed=9)
+        m.load_state_dict(state)
+        shards.append(m.params)
+    hd, full = 16, model.params
+    q0, q1 = shards[0]["l0.wqkv"], shards[1]["l0.wqkv"]
+    assert torch.equal(torch.cat([q0[:2 * hd], q1[:2 * hd]]), full["l0.wqkv"][:4 * hd])                 # query heads
+    assert torch.equal(torch.cat([q0[2 * hd:3 * hd], q1[2 * hd:3 * hd]]), full["l0.wqkv"][4 * hd:6 * hd])  # key heads
+    assert torch.equal(torch.cat([shards[0]["l1.wo"], shards[1]["l1.wo"]], 1), full["l1.wo"])
+    assert torch.equal(torch.cat([shards[0]["l1.wdown"], shards[1]["l1.wdown"]], 1), full["l1.wdown"])
+    assert torch.equal(torch.cat([shards[0]["l0.wgu"][:64], shards[1]["l0.wgu"][:64]]), full["l0.wgu"][:128])
+    assert torch.equal(torch.cat([shards[0]["head"], shards[1]["head"]]), full["head"])
+    assert torch.equal(shards[1]["wte"], full["wte"])
