@@ -474,3 +474,28 @@ def test_gemm_tuning_table_feeds_cached_plans_back_into_gemm(tmp_path):
     assert k.config_space().size() == 2 and k.default_config() == {"impl": 0}
     assert k.input_signature() == "bmedium_smedium_h12_kv12_d64_11".replace("bmedium", "btiny")
     assert k.flops() == 4.0 * 4 * 1024 * 1024 * 12 * 64 * 3.5 * 0.5
+
+
+def test_safetensors_files_interoperate_with_the_reference_implementation(tmp_path):
+    """Files written here are read by the `safetensors` package and the other way round: dtypes, shapes, metadata."""
+    sft = pytest.importorskip("safetensors.torch")
+    from rustral_b200.io import safetensors_io as st
+    g = torch.Generator().manual_seed(0)
+    tensors = {"w.f32": torch.randn(3, 5, generator=g), "w.bf16": torch.randn(4, 2, generator=g).bfloat16(),
+               "w.f16": torch.randn(7, generator=g).half(), "ids": torch.arange(6, dtype=torch.int64).view(2, 3),
+               "scalar": torch.tensor(2.5), "empty": torch.zeros(0, 4)}
+    ours = str(tmp_path / "ours.safetensors")
+    st.save_file(tensors, ours, {"format": "pt", "note": "written by rustral_b200"})
+    theirs = sft.load_file(ours)
+    assert set(theirs) == set(tensors)
+    for k, v in tensors.items():
+        assert theirs[k].dtype == v.dtype and theirs[k].shape == v.shape and torch.equal(theirs[k], v), k
+    from safetensors import safe_open
+    with safe_open(ours, framework="pt") as f:
+        assert f.metadata()["note"] == "written by rustral_b200"
+    other = str(tmp_path / "theirs.safetensors")
+    sft.save_file({k: v.contiguous() for k, v in tensors.items()}, other, metadata={"origin": "safetensors"})
+    back, meta = st.load_file(other)
+    assert meta.get("origin") == "safetensors" and set(back) == set(tensors)
+    for k, v in tensors.items():
+        assert back[k].dtype == v.dtype and torch.equal(back[k], v), k
