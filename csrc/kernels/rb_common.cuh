@@ -21,7 +21,8 @@ enum StatusBits : unsigned int {
   kStatusMbarTimeout = 1u << 0,   // an mbarrier wait inside a kernel ran out
   kStatusFlagTimeout = 1u << 1,   // a global-memory flag wait (peer / other CTA) ran out
   kStatusBadArg      = 1u << 2,   // a kernel saw an argument it cannot handle
-  kStatusBounds      = 1u << 3,   // a bounds check (RB_BOUNDS builds) caught an index
+  kStatusBounds      = 1u << 3,   // reserved for index checks (today the kernels that read indices from memory clamp
+                                  // or skip out-of-range entries, and the host validates them before the launch)
 };
 
 // The status buffer is four words in global memory, one buffer per device, owned by the host
