@@ -1,5 +1,5 @@
 // C interface of the host runtime library (librb200_runtime.so): paged-KV block allocator, continuous-batching
-// scheduler core, tile-configuration search, a memory-mapped token loader and an asynchronous checkpoint file writer.  No GPU code; bound with ctypes.
+// scheduler core, tile-configuration search, a memory-mapped token loader with a background batch prefetcher, and an asynchronous checkpoint file writer.  No GPU code; bound with ctypes.
 #pragma once
 #include <stdint.h>
 #ifdef __cplusplus
@@ -47,6 +47,19 @@ int rb_tokens_gather(const RbTokenFile* f, const int64_t* offsets, int batch, in
 // Deterministic window offsets for (seed, step): uniform over valid starts.
 void rb_tokens_sample_offsets(const RbTokenFile* f, uint64_t seed, uint64_t step, int batch, int seq_len_plus1,
                               int64_t* offsets_out);
+
+// ---- background batch prefetcher over a token file -------------------------------------------------------------------
+// A worker thread fills `depth` caller-provided buffers (each batch * seq_len_plus1 int64, typically pinned host
+// memory) with the batches of steps first_step, first_step + 1, ... exactly as rb_tokens_sample_offsets +
+// rb_tokens_gather produce them for (seed, step).  next: blocks until the batch of the next step in order is ready and
+// returns its buffer index (step_out receives the step), -2 on timeout (timeout_ms < 0 waits for ever), -3 when the
+// worker failed.  release: hands the buffer back once the caller has consumed it.  The file must outlive the prefetcher.
+typedef struct RbPrefetcher RbPrefetcher;
+RbPrefetcher* rb_prefetch_create(const RbTokenFile* f, uint64_t seed, uint64_t first_step, int batch, int seq_len_plus1,
+                                 int depth, int64_t* const* buffers);
+int rb_prefetch_next(RbPrefetcher* p, int timeout_ms, uint64_t* step_out);
+int rb_prefetch_release(RbPrefetcher* p, int index);
+void rb_prefetch_destroy(RbPrefetcher* p);
 
 // ---- continuous-batching scheduler core -----------------------------------------------------------------------------
 // Decisions of one serving iteration over the block allocator `alloc` (not owned): retire finished requests, resume

@@ -50,6 +50,10 @@ def declare_runtime(lib) -> None:
     _sig(lib, "rb_tokens_len", [P], LL)
     _sig(lib, "rb_tokens_gather", [P, P, I, I, P], I)
     _sig(lib, "rb_tokens_sample_offsets", [P, C.c_uint64, C.c_uint64, I, I, P])
+    _sig(lib, "rb_prefetch_create", [P, C.c_uint64, C.c_uint64, I, I, I, P], P)
+    _sig(lib, "rb_prefetch_next", [P, I, P], I)
+    _sig(lib, "rb_prefetch_release", [P, I], I)
+    _sig(lib, "rb_prefetch_destroy", [P])
     _sig(lib, "rb_sched_create", [P, I, I, D, I], P)
     _sig(lib, "rb_sched_destroy", [P])
     _sig(lib, "rb_sched_add", [P, I, I, I, I, LL], LL)

@@ -111,6 +111,11 @@ class TokenFileDataset:
             raise IndexError("token window out of range")
         return out
 
+    def prefetcher(self, batch_size: int, depth: int = 3, first_step: int = 0, pin: bool | None = None) -> "TokenBatchPrefetcher":
+        """Batches of consecutive steps gathered by a native worker thread into `depth` (pinned) buffers, ahead of the
+        consumer; the data of step s equals `batch(s, batch_size)`."""
+        return TokenBatchPrefetcher(self, batch_size, depth, first_step, pin)
+
     def close(self):
         if self._h:
             self._lib.rb_tokens_close(self._h)
@@ -179,6 +184,57 @@ def simple_loader(items, batch_size: int) -> DataLoader:
 
 def shuffled_loader(items, batch_size: int, seed: int = 0) -> DataLoader:
     return DataLoader(InMemoryDataset(items), DataLoaderConfig(batch_size, True, seed))
+
+
+class TokenBatchPrefetcher:
+    """Handle on the native prefetcher (csrc/runtime/prefetch.cpp).  `next()` returns (tokens, step): a view of one of
+    the ring's buffers, valid until `release(tokens)` (or the next `next()`, which releases the previous batch unless
+    `hold=True` was passed).  Typical loop: `t, _ = pf.next(); dev = t.to("cuda", non_blocking=True); ...` and release
+    after the copy has been ordered before the next use of the stream."""
+
+    def __init__(self, dataset: "TokenFileDataset", batch_size: int, depth: int = 3, first_step: int = 0, pin: bool | None = None):
+        self._ds, self._lib = dataset, dataset._lib
+        n = dataset.seq_len + 1
+        pin = torch.cuda.is_available() if pin is None else (pin and torch.cuda.is_available())
+        self._bufs = [torch.empty((batch_size, n), dtype=torch.int64, pin_memory=pin) for _ in range(depth)]
+        ptrs = (C.c_void_p * depth)(*[b.data_ptr() for b in self._bufs])
+        self._h = self._lib.rb_prefetch_create(dataset._h, dataset.seed, first_step, batch_size, n, depth, ptrs)
+        if not self._h:
+            raise ValueError("TokenBatchPrefetcher: bad sizes (file shorter than one window, depth outside 1..64, ...)")
+        self._held: list = []
+        self._auto = None
+
+    def next(self, timeout_s: float | None = None, hold: bool = False):
+        if self._auto is not None:
+            self.release(self._auto)
+            self._auto = None
+        step = C.c_uint64()
+        idx = self._lib.rb_prefetch_next(self._h, -1 if timeout_s is None else int(timeout_s * 1000), C.byref(step))
+        if idx == -2:
+            raise TimeoutError("no batch became ready in time (are all buffers held?)")
+        if idx < 0:
+            raise IndexError("token window out of range")
+        self._held.append(idx)
+        if not hold:
+            self._auto = idx
+        return self._bufs[idx], int(step.value)
+
+    def release(self, batch) -> None:
+        idx = batch if isinstance(batch, int) else next(i for i, b in enumerate(self._bufs) if b.data_ptr() == batch.data_ptr())
+        if idx in self._held:
+            self._held.remove(idx)
+            self._lib.rb_prefetch_release(self._h, idx)
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.rb_prefetch_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:   # noqa: BLE001
+            pass
 
 
 class PinnedBatchPrefetcher:

@@ -499,3 +499,34 @@ def test_safetensors_files_interoperate_with_the_reference_implementation(tmp_pa
     assert meta.get("origin") == "safetensors" and set(back) == set(tensors)
     for k, v in tensors.items():
         assert back[k].dtype == v.dtype and torch.equal(back[k], v), k
+
+
+def test_native_token_prefetcher_serves_the_same_batches_in_order(tmp_path):
+    """The C++ worker fills a ring of buffers ahead of the consumer; step for step the data equals the synchronous
+    `batch(step)`, buffers are recycled only after release, and a held ring times out instead of overwriting."""
+    import numpy as np
+    from rustral_b200.data.datasets import TokenFileDataset
+    path = tmp_path / "tokens.bin"
+    np.arange(5000, dtype=np.uint16).tofile(path)
+    ds = TokenFileDataset(str(path), seq_len=16, bytes_per_token=2, seed=7)
+    pf = ds.prefetcher(batch_size=4, depth=3, first_step=10, pin=False)
+    try:
+        for s in range(10, 30):
+            t, step = pf.next(timeout_s=10)
+            assert step == s and torch.equal(t, ds.batch(s, 4)) and t.shape == (4, 17)
+            assert bool((t[:, 1:] - t[:, :-1] == 1).all())                      # windows are contiguous runs of the file
+        held = [pf.next(timeout_s=10, hold=True) for _ in range(3)]              # the whole ring in the consumer's hands
+        assert [h[1] for h in held] == [30, 31, 32]
+        with pytest.raises(TimeoutError):
+            pf.next(timeout_s=0.2, hold=True)
+        snapshot = held[0][0].clone()
+        pf.release(held[1][0])
+        t, step = pf.next(timeout_s=10, hold=True)
+        assert step == 33 and torch.equal(held[0][0], snapshot)                  # a held buffer is never overwritten
+        assert torch.equal(t, ds.batch(33, 4))
+    finally:
+        pf.close()
+        pf.close()
+    with pytest.raises(ValueError):
+        TokenFileDataset(str(path), seq_len=6000, bytes_per_token=2).prefetcher(2)
+    ds.close()
