@@ -98,6 +98,26 @@ class LMTrainer:
             return float(self._loss_host)
         return float(self.step_device(tokens_host, lr))
 
+    def fit_token_file(self, dataset, steps: int, first_step: int = 0, lr_schedule=None, on_step=None, depth: int = 3) -> list:
+        """Trains `steps` optimizer steps on a `data.TokenFileDataset`: a native worker thread gathers the windows of
+        the coming steps into pinned buffers while the GPU works on the current one.  With several ranks every rank
+        passes a dataset with its own seed, so that the ranks draw different windows.  `lr_schedule(step) -> lr`,
+        `on_step(step, loss)`.  Returns the losses.  Resuming at `first_step` reproduces the data of an uninterrupted run."""
+        if dataset.seq_len != self.model_cfg.seq_len:
+            raise ValueError(f"the dataset serves windows of {dataset.seq_len} tokens, the model takes {self.model_cfg.seq_len}")
+        pf = dataset.prefetcher(self.local_batch, depth, first_step)
+        losses = []
+        try:
+            for _ in range(steps):
+                tokens, s = pf.next()
+                loss = self.step(tokens, lr_schedule(s) if lr_schedule is not None else None)
+                losses.append(loss)
+                if on_step is not None:
+                    on_step(s, loss)
+        finally:
+            pf.close()
+        return losses
+
     # -------------------------------------------------------------------------------------------------
     def state_dict(self) -> dict:
         if self.comm is not None:
