@@ -106,6 +106,14 @@ class FusedZeroComm:
         P = self.t.engine.params
         torch.distributed.all_gather_into_tensor(P.master, self.master, group=self.t.pg)
 
+    def reload_master(self) -> None:
+        """After a checkpoint has been loaded into the full-size master buffer: refresh this rank's shard copy."""
+        self.master.copy_(self.t.engine.params.master[self.t.shard])
+
+    def optimizer_shard(self) -> tuple:
+        """(m, v): Adam moments of this rank's flat shard."""
+        return self.m, self.v
+
     def close(self):
         for b in (self.grad_buf, self.lowp_buf, self.norm_buf, self.pad):
             b.close()

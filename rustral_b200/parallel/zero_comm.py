@@ -64,6 +64,14 @@ class NcclZeroComm:
         dist.all_gather(parts, P.master[t.shard].clone(), group=t.pg)
         P.master.copy_(torch.cat(parts))
 
+    def reload_master(self) -> None:
+        """Nothing to refresh: this path updates the shard of the full-size master buffer in place."""
+
+    def optimizer_shard(self) -> tuple:
+        """(m, v): Adam moments of this rank's flat shard (views of the full-size buffers)."""
+        P = self.t.engine.params
+        return P.m[self.t.shard], P.v[self.t.shard]
+
     def close(self) -> None:
         pass
 

@@ -132,3 +132,37 @@ class LMTrainer:
 
     def load_state_dict(self, state: dict) -> None:
         self.engine.params.load_state_dict(state)
+        if self.comm is not None:
+            self.comm.reload_master()
+
+    def optimizer_state(self) -> tuple:
+        """(tensors, meta) of THIS rank's optimizer state: the Adam moments of its shard of the flat parameter space
+        and the step count.  Together with `state_dict()` it makes a resumed run continue bit for bit; every rank
+        saves its own (the layout of `DistributedCheckpointManager`: one file per rank)."""
+        if self.comm is not None:
+            m, v = self.comm.optimizer_shard()
+        else:
+            P = self.engine.params
+            m, v = P.m, P.v
+        tensors = {"adam.m": m.detach().float().cpu().clone(), "adam.v": v.detach().float().cpu().clone()}
+        meta = {"step": int(self.engine.step_count), "world": self.world, "rank": self.rank,
+                "shard_off": int(self.shard.start), "shard_len": int(self.shard_len)}
+        return tensors, meta
+
+    def load_optimizer_state(self, tensors: dict, meta: dict) -> None:
+        """Strict: the state must come from the same rank of a run with the same number of ranks and the same shard."""
+        from ..core.errors import SerializationError
+        want = {"world": self.world, "rank": self.rank, "shard_off": int(self.shard.start), "shard_len": int(self.shard_len)}
+        got = {k: int(meta.get(k, -1)) for k in want}
+        if got != want:
+            raise SerializationError(f"optimizer state was saved for {got}, this rank is {want}")
+        if self.comm is not None:
+            m, v = self.comm.optimizer_shard()
+        else:
+            m, v = self.engine.params.m, self.engine.params.v
+        for name, dst in (("adam.m", m), ("adam.v", v)):
+            if name not in tensors or tuple(tensors[name].shape) != tuple(dst.shape):
+                raise SerializationError(f"optimizer state: {name} missing or of the wrong size")
+        m.copy_(tensors["adam.m"].to(m.device))
+        v.copy_(tensors["adam.v"].to(v.device))
+        self.engine.step_count = int(meta["step"])

@@ -163,3 +163,32 @@ def test_trainer_fits_a_token_file_through_the_native_prefetcher(tmp_path):
     assert la == lb                                                         # same data, bit-identical trajectory
     with pytest.raises(ValueError):
         tr.fit_token_file(TokenFileDataset(str(path), seq_len=8), 1)
+
+
+def test_resume_with_optimizer_state_continues_bit_for_bit():
+    """Weights + Adam moments + step count: a run stopped after 3 steps and resumed in a fresh trainer reproduces the
+    uninterrupted 6-step run exactly; without the optimizer state it does not."""
+    from rustral_b200.core.errors import SerializationError
+    from rustral_b200.runtime.lm_trainer import LMTrainer, TrainConfig
+    cfg = preset("llama-test", seq_len=16, d_model=32, ffn_dim=64, n_layer=1, n_head=2, n_kv_head=1, vocab_size=64)
+    tc = lambda: TrainConfig(global_batch=4, micro_batch=4, lr=1e-2, seed=0)
+    g = torch.Generator().manual_seed(0)
+    batches = [torch.randint(0, 64, (4, 17), generator=g) for _ in range(6)]
+    full = LMTrainer(cfg, tc(), "cpu")
+    want = [full.step(b) for b in batches]
+    first = LMTrainer(cfg, tc(), "cpu")
+    got = [first.step(b) for b in batches[:3]]
+    weights, (opt_tensors, opt_meta) = first.state_dict(), first.optimizer_state()
+    assert opt_meta["step"] == 3 and opt_tensors["adam.m"].abs().sum() > 0
+    resumed = LMTrainer(cfg, tc(), "cpu")
+    resumed.load_state_dict(weights)
+    resumed.load_optimizer_state(opt_tensors, opt_meta)
+    got += [resumed.step(b) for b in batches[3:]]
+    assert got == want
+    cold = LMTrainer(cfg, tc(), "cpu")
+    cold.load_state_dict(weights)
+    assert [cold.step(b) for b in batches[3:]] != want[3:]                  # fresh moments: a different trajectory
+    with pytest.raises(SerializationError):
+        resumed.load_optimizer_state(opt_tensors, dict(opt_meta, world=2))
+    with pytest.raises(SerializationError):
+        resumed.load_optimizer_state({"adam.m": opt_tensors["adam.m"]}, opt_meta)
