@@ -20,6 +20,8 @@ def main():
     ap.add_argument("--device", default="cuda")
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--model", default="gpt2-test")
+    ap.add_argument("--resume-check", action="store_true",
+                    help="snapshot weights + per-rank optimizer state, resume in a second trainer, compare the next steps")
     a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     if a.device == "cuda":
@@ -47,8 +49,19 @@ def main():
     if a.device == "cuda":
         torch.cuda.synchronize()
         status = _native.read_status()[0]
+    resume = None
+    if a.resume_check:
+        opt_tensors, opt_meta = tr.optimizer_state()
+        tr2 = LMTrainer(cfg, TrainConfig(global_batch=8, micro_batch=2, lr=1e-3, comm=a.comm), dev)
+        tr2.load_state_dict(sd)
+        tr2.load_optimizer_state(opt_tensors, opt_meta)
+        cont = [tr.step(local) for _ in range(2)]
+        again = [tr2.step(local) for _ in range(2)]
+        resume = {"continued": cont, "resumed": again, "shard_len": opt_meta["shard_len"], "world": opt_meta["world"],
+                  "moments_numel": int(opt_tensors["adam.m"].numel())}
+        tr2.close()
     if rank == 0:
-        print(json.dumps({"losses": losses, "checksum": checksum, "probe": probe, "status": status,
+        print(json.dumps({"losses": losses, "checksum": checksum, "probe": probe, "status": status, "resume": resume,
                           "comm": type(tr.comm).__name__ if tr.comm is not None else "none"}))
     tr.close()
     dist.destroy_process_group()

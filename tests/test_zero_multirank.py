@@ -11,11 +11,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "mp_zero_worker.py")
 
 
-def _run(nproc, comm, device, port, extra_env=None):
+def _run(nproc, comm, device, port, extra_env=None, extra_args=()):
     env = dict(os.environ)
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
-           "127.0.0.1", "--master-port", str(port), WORKER, "--comm", comm, "--device", device]
+           "127.0.0.1", "--master-port", str(port), WORKER, "--comm", comm, "--device", device, *extra_args]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
@@ -29,6 +29,15 @@ def test_zero_two_cpu_ranks_match_one_rank():
         assert abs(a - b) < 1e-4, (one["losses"], two["losses"])
     assert abs(one["checksum"] - two["checksum"]) < 1e-3 * abs(one["checksum"])
     assert two["losses"][-1] < two["losses"][0]
+
+
+def test_zero_two_cpu_ranks_resume_from_per_rank_optimizer_state():
+    """Each rank saves the Adam moments of ITS shard; a second trainer that loads weights + that state continues
+    exactly like the first."""
+    out = _run(2, "nccl", "cpu", 29613, extra_args=["--resume-check"])
+    r = out["resume"]
+    assert r["world"] == 2 and r["moments_numel"] == r["shard_len"]
+    assert r["continued"] == r["resumed"]
 
 
 @pytest.mark.gpu
