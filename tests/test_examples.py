@@ -187,3 +187,21 @@ def test_bench_reference_arm_prints_one_json_line():
     doc = json.loads(lines[0])
     assert doc["impl"] == "reference" and (("unavailable" in doc and isinstance(doc["unavailable"], str) and "\n" not in doc["unavailable"])
                                            or "value" in doc)
+
+
+def test_pretraining_example_checkpoints_asynchronously_and_resumes_exactly(tmp_path):
+    """Token file -> prefetcher -> trainer -> asynchronous checkpoints; a run stopped at step 8 and resumed to 12
+    reproduces the losses of the uninterrupted 12-step run."""
+    mod = _load_example("pretrain_lm")
+    common = ["--model", "gpt2-test", "--layers", "1", "--seq-len", "16", "--d-model", "32", "--global-batch", "4",
+              "--micro-batch", "4", "--warmup", "2", "--checkpoint-every", "4", "--device", "cpu", "--lr", "3e-3"]
+    full = mod.main([*common, "--steps", "12", "--out", str(tmp_path / "full")])
+    assert full["loss_last"] < full["loss_first"] and full["last_checkpoint"] == 12
+    for s in (4, 8, 12):
+        d = tmp_path / "full" / f"step_{s}"
+        assert (d / "model.safetensors").exists() and (d / "optimizer_rank_0.safetensors").exists() and (d / "complete.json").exists()
+    part = mod.main([*common, "--steps", "12", "--stop-after", "8", "--out", str(tmp_path / "part")])
+    assert part["losses"] == full["losses"][:8] and part["last_checkpoint"] == 8
+    rest = mod.main([*common, "--steps", "12", "--out", str(tmp_path / "part"), "--resume"])
+    assert rest["first_step"] == 8 and rest["losses"] == full["losses"][8:]
+    assert json.load(open(tmp_path / "part" / "summary.json"))["last_checkpoint"] == 12
