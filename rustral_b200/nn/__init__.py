@@ -20,4 +20,5 @@ from .lstm import LstmConfig, LstmCell, GruCell, RnnCell, StackedLstm, Bidirecti
 from .sequential import Sequential2, Sequential, chain
 from .readout import Readout, MultiReadout, BinaryReadout
 
+from ..serve.kv_cache import CacheQuantization, CacheConfig, KVCache, SlidingWindowCache, PagedCache, BatchedCache  # noqa: E402,F401  (the reference keeps these in its nn crate)
 __all__ = [n for n in dir() if not n.startswith("_")]
