@@ -43,7 +43,7 @@ def test_parallel_lm_gpu_matches_cpu(moe):
     lc.backward()
     lg = gpu.forward_loss(tokens.cuda())
     lg.backward()
-    assert abs(float(lc) - float(lg)) < 3e-2, (float(lc), float(lg))
+    assert abs(float(lc.detach()) - float(lg.detach())) < 3e-2, (float(lc.detach()), float(lg.detach()))
     for n in ("l0.wqkv", "l1.wo", "wte", "head"):
         a, b = gpu.params[n].grad.float().cpu(), cpu.params[n].grad.float()
         assert (a - b).norm() / (b.norm() + 1e-9) < 8e-2, n
