@@ -248,6 +248,41 @@ class ParallelDecoderLM:
             for name, t in staged.items():
                 self.params[name].copy_(t.to(self.params[name].device, self.params[name].dtype))
 
+    def gather_state_dict(self) -> dict:
+        """Collective over the tensor-parallel group: the unsharded checkpoint (fp32, single-GPU engine names) of a
+        dense model that is sharded over tensor-parallel ranks, assembled on every rank.  The inverse of
+        `load_state_dict`; pipeline stages return the layers (and embedding / head) they own."""
+        if self.cfg.num_experts or self.fsdp is not None:
+            raise ValueError("gather_state_dict covers dense tensor- / pipeline-parallel models")
+        c, P, tp = self.cfg, self.params, self.tp
+        hd = c.head_dim
+        hq, hk, f = c.n_head // tp, c.n_kv_head // tp, c.ffn_hidden // tp
+        f32 = lambda t: t.detach().float().cpu().clone()
+
+        def gather(t):
+            """Every rank's copy of a sharded tensor, in rank order."""
+            if tp == 1:
+                return [f32(t)]
+            return [f32(x) for x in self.tp_pg.all_gather(t.detach().contiguous())]
+        out = {}
+        if self.has_embed:
+            out["tok_embed.embed"] = f32(P["wte"])
+        if self.has_head:
+            out["final_norm.weight"] = f32(P["final_norm"])
+            out["head.weight"] = torch.cat(gather(P["head"]), 0)
+        for l in range(self.first_layer, self.last_layer):
+            p, q = f"l{l}.", f"layers.{l}."
+            parts = gather(P[p + "wqkv"])
+            out[q + "attn.wq.weight"] = torch.cat([x[:hq * hd] for x in parts], 0)
+            out[q + "attn.wk.weight"] = torch.cat([x[hq * hd:(hq + hk) * hd] for x in parts], 0)
+            out[q + "attn.wv.weight"] = torch.cat([x[(hq + hk) * hd:] for x in parts], 0)
+            out[q + "attn.wo.weight"] = torch.cat(gather(P[p + "wo"]), 1)
+            parts = gather(P[p + "wgu"])
+            out[q + "ffn.gate_up.weight"] = torch.cat([x[:f] for x in parts] + [x[f:] for x in parts], 0)
+            out[q + "ffn.down.weight"] = torch.cat(gather(P[p + "wdown"]), 1)
+            out[q + "ln1.weight"], out[q + "ln2.weight"] = f32(P[p + "attn_norm"]), f32(P[p + "mlp_norm"])
+        return out
+
     def state_dict(self) -> dict:
         """The unsharded checkpoint of a model held by ONE rank (no tensor / pipeline / FSDP sharding): fp32 tensors
         under the single-GPU engine's names."""

@@ -89,6 +89,26 @@ def convert_hf_llama(state: dict, n_layer: int | None = None, tie_embeddings: bo
     return out
 
 
+def export_hf_llama(state: dict, ffn_dim: int | None = None, tie_embeddings: bool = False) -> dict:
+    """The inverse of `convert_hf_llama`: this framework's names -> Hugging Face Llama names, so that a model trained
+    here loads into `transformers.LlamaForCausalLM.load_state_dict`."""
+    out = {"model.embed_tokens.weight": state["tok_embed.embed"], "model.norm.weight": state["final_norm.weight"]}
+    if not tie_embeddings:
+        out["lm_head.weight"] = state["head.weight"]
+    layers = 1 + max(int(k.split(".")[1]) for k in state if k.startswith("layers."))
+    for l in range(layers):
+        p, h = f"layers.{l}.", f"model.layers.{l}."
+        for src, dst in (("wq", "q_proj"), ("wk", "k_proj"), ("wv", "v_proj"), ("wo", "o_proj")):
+            out[h + f"self_attn.{dst}.weight"] = state[p + f"attn.{src}.weight"]
+        gu = state[p + "ffn.gate_up.weight"]
+        f = ffn_dim or gu.shape[0] // 2
+        out[h + "mlp.gate_proj.weight"], out[h + "mlp.up_proj.weight"] = gu[:f].clone(), gu[f:].clone()
+        out[h + "mlp.down_proj.weight"] = state[p + "ffn.down.weight"]
+        out[h + "input_layernorm.weight"] = state[p + "ln1.weight"]
+        out[h + "post_attention_layernorm.weight"] = state[p + "ln2.weight"]
+    return out
+
+
 def config_from_hf(hf_config) -> "GPTConfig":
     """GPTConfig for a Hugging Face GPT-2 or Llama configuration object (or dict)."""
     from ..models.config import GPTConfig
@@ -106,7 +126,7 @@ def config_from_hf(hf_config) -> "GPTConfig":
     raise ValueError(f"unsupported Hugging Face model type {c.get('model_type')!r}")
 
 
-__all__ += ["convert_hf_gpt2", "convert_hf_llama", "config_from_hf"]
+__all__ += ["convert_hf_gpt2", "convert_hf_llama", "export_hf_llama", "config_from_hf"]
 
 
 def main(argv=None) -> int:

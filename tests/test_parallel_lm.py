@@ -24,7 +24,7 @@ def test_parallel_lm_trains_on_cpu(moe):
         loss.backward()
         opt.accumulate()
         opt.step()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
     assert losses[-1] < losses[0] - 0.2, losses
     assert cfg.num_params() > 0 and cfg.flops_per_token() > 0
 
@@ -72,6 +72,11 @@ def test_parallel_lm_loads_hugging_face_llama_and_shards_it_for_tensor_paralleli
         ref_loss = torch.nn.functional.cross_entropy(ref.reshape(-1, 256), tokens[:, 1:].reshape(-1))
         loss = model.forward_loss(tokens)
     assert abs(float(loss) - float(ref_loss)) < 2e-2, (float(loss), float(ref_loss))
+    from rustral_b200.utils.hf import export_hf_llama
+    exported = export_hf_llama(state)                       # and back into transformers: names and values round-trip
+    ref_sd = {k: v for k, v in hf.state_dict().items() if "rotary_emb" not in k}
+    assert set(exported) == set(ref_sd) and all(torch.equal(exported[k], ref_sd[k].float()) for k in ref_sd)
+    hf.load_state_dict(exported, strict=False)
     back = model.state_dict()
     assert set(back) == set(state)
     for k in state:
@@ -96,3 +101,38 @@ def test_parallel_lm_loads_hugging_face_llama_and_shards_it_for_tensor_paralleli
     assert torch.equal(torch.cat([shards[0]["l0.wgu"][:64], shards[1]["l0.wgu"][:64]]), full["l0.wgu"][:128])
     assert torch.equal(torch.cat([shards[0]["head"], shards[1]["head"]]), full["head"])
     assert torch.equal(shards[1]["wte"], full["wte"])
+
+
+def test_tensor_parallel_shards_gather_back_into_the_full_checkpoint():
+    """load_state_dict (shard) and gather_state_dict (collective reassembly) are inverses on two tensor-parallel ranks,
+    and a tensor-parallel forward of the loaded model gives the single-rank loss."""
+    import threading
+    from rustral_b200.parallel.process_group import ProcessGroup
+    cfg = ParallelLMConfig(vocab_size=256, d_model=64, n_layer=2, n_head=4, n_kv_head=2, ffn_hidden=128, seq_len=32)
+    full = ParallelDecoderLM(cfg, "cpu", seed=4)
+    state = full.state_dict()
+    tokens = torch.randint(0, 256, (2, 33), generator=torch.Generator().manual_seed(2))
+    with torch.no_grad():
+        want = float(full.forward_loss(tokens))
+    groups = ProcessGroup.new_threaded(2)
+    results, errors = [None, None], []
+
+    def worker(i):
+        try:
+            m = ParallelDecoderLM(cfg, "cpu", tp_pg=groups[i], seed=77)
+            m.load_state_dict(state)
+            with torch.no_grad():
+                loss = float(m.forward_loss(tokens))
+            results[i] = (m.gather_state_dict(), loss)
+        except Exception as e:      # noqa: BLE001
+            errors.append(e)
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not errors, errors
+    for gathered, loss in results:
+        assert set(gathered) == set(state) and abs(loss - want) < 2e-2
+        for k in state:
+            assert torch.equal(gathered[k], state[k]), k
