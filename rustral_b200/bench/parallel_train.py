@@ -65,6 +65,8 @@ def main(argv=None):
     ap.add_argument("--capacity-factor", type=float, default=1.5, help="expert-parallel receive capacity (x balanced share)")
     ap.add_argument("--init-from", help="safetensors checkpoint (unsharded, this framework's names; see utils.hf for "
                     "Hugging Face conversion): every rank loads its shard instead of the random initialisation")
+    ap.add_argument("--save-dir", help="after training, write the unsharded checkpoint (dense models): one file per pipeline "
+                    "stage (stage<k>.safetensors, reassembled over the tensor-parallel ranks); their union is the model")
     ap.add_argument("--unfused", action="store_true")
     ap.add_argument("--same-batch", action="store_true", help="train on one fixed batch (tests: the loss must fall)")
     a = ap.parse_args(argv)
@@ -215,6 +217,14 @@ def main(argv=None):
             "model_tflops_per_s_per_gpu": round(cfg.flops_per_token() * tokens / (ms_step / 1e3) / 1e12 / world, 1),
             "losses": [round(v, 4) for v in lt.tolist()], "device_status": int(status),
             "data": "synthetic (uniform random token ids), random-init weights"}))
+    if a.save_dir and not cfg.num_experts and a.fsdp == 1:
+        from ..io import safetensors_io as st
+        state = model.gather_state_dict()                      # collective over the tensor-parallel group
+        writes = tp_idx == 0 and (a.pp > 1 or a.tp > 1 or rank == 0)
+        if writes:
+            os.makedirs(a.save_dir, exist_ok=True)
+            st.save_file(state, os.path.join(a.save_dir, f"stage{pp_idx}.safetensors"),
+                         {"layers": f"{model.first_layer}-{model.last_layer}", "config": a.config})
     if world > 1:
         dist.barrier()
     if fused_tp is not None:
