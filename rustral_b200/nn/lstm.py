@@ -127,6 +127,28 @@ class GruCell(RnnCell):
         x, h = x_state
         return self.step(x, h, ctx)
 
+    def forward_sequence(self, xs, ctx: ForwardCtx, state=None):
+        """Inference: the input projections of all steps are one GEMM, so a step is one GEMM plus the gate arithmetic.
+        With gradients: the generic loop."""
+        needs_grad = torch.is_grad_enabled() and (xs.requires_grad or (ctx is not None and ctx.is_training()))
+        if needs_grad:
+            return super().forward_sequence(xs, ctx, state)
+        T, B, I = xs.shape
+        H = self.hidden_size
+        with torch.no_grad():
+            h = state if state is not None else self.initial_state(B, ctx, xs)
+            wx, wh, b = self.wx.tensor.detach(), self.wh.tensor.detach(), self.b.tensor.detach()
+            gx_all = ops.linear(xs.reshape(T * B, I).contiguous(), wx, b).view(T, B, 3 * H).float()
+            outs = torch.empty((T, B, H), dtype=xs.dtype, device=xs.device)
+            for t in range(T):
+                gx, gh = gx_all[t], ops.linear(h, wh).float()
+                r = torch.sigmoid(gx[:, :H] + gh[:, :H])
+                z = torch.sigmoid(gx[:, H:2 * H] + gh[:, H:2 * H])
+                n = torch.tanh(gx[:, 2 * H:] + r * gh[:, 2 * H:])
+                h = ((1 - z) * n + z * h.float()).to(xs.dtype)
+                outs[t] = h
+        return outs, h
+
 
 class StackedLstm(Module, Trainable, Saveable):
     def __init__(self, cells: list):

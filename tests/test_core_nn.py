@@ -530,3 +530,21 @@ def test_native_token_prefetcher_serves_the_same_batches_in_order(tmp_path):
     with pytest.raises(ValueError):
         TokenFileDataset(str(path), seq_len=6000, bytes_per_token=2).prefetcher(2)
     ds.close()
+
+
+def test_recurrent_inference_sequences_match_the_generic_loop():
+    """GruCell's one-GEMM-per-step inference path equals the differentiable per-step loop; training mode keeps gradients."""
+    from rustral_b200.core import CpuBackend, ForwardCtx
+    from rustral_b200.nn import GruCell, LstmCell, RnnCell
+    be = CpuBackend()
+    xs = torch.randn(9, 4, 12, generator=torch.Generator().manual_seed(0))
+    for cls in (GruCell, LstmCell):
+        cell = cls.new(be, 12, 16, seed=3)
+        fast, state = cell.forward_sequence(xs, ForwardCtx.inference(be))
+        slow, _ = RnnCell.forward_sequence(cell, xs, ForwardCtx.inference(be))
+        assert torch.allclose(fast, slow, atol=1e-6) and not fast.requires_grad
+        assert torch.equal(cell.hidden_of(state), fast[-1])
+        train, _ = cell.forward_sequence(xs, ForwardCtx.train(be))
+        assert train.requires_grad
+        train.sum().backward()
+        assert all(p.tensor.grad is not None for p in cell.parameters())
