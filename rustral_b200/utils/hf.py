@@ -109,6 +109,25 @@ def export_hf_llama(state: dict, ffn_dim: int | None = None, tie_embeddings: boo
     return out
 
 
+def export_hf_gpt2(state: dict) -> dict:
+    """The inverse of `convert_hf_gpt2`: this framework's names -> Hugging Face GPT-2 names and Conv1D layouts
+    (`transformer.*`, projections as [in, out]; the tied `lm_head.weight` is included)."""
+    out = {"transformer.wte.weight": state["tok_embed.embed"], "transformer.wpe.weight": state["pos_embed.embed"],
+           "transformer.ln_f.weight": state["final_norm.weight"], "transformer.ln_f.bias": state["final_norm.bias"],
+           "lm_head.weight": state["tok_embed.embed"]}
+    layers = 1 + max(int(k.split(".")[1]) for k in state if k.startswith("layers."))
+    for l in range(layers):
+        p, h = f"layers.{l}.", f"transformer.h.{l}."
+        out[h + "attn.c_attn.weight"] = torch.cat([state[p + f"attn.{nm}.weight"].t() for nm in ("wq", "wk", "wv")], 1).contiguous()
+        out[h + "attn.c_attn.bias"] = torch.cat([state[p + f"attn.{nm}.bias"] for nm in ("wq", "wk", "wv")], 0)
+        out[h + "attn.c_proj.weight"], out[h + "attn.c_proj.bias"] = state[p + "attn.wo.weight"].t().contiguous(), state[p + "attn.wo.bias"]
+        out[h + "mlp.c_fc.weight"], out[h + "mlp.c_fc.bias"] = state[p + "ffn.fc1.weight"].t().contiguous(), state[p + "ffn.fc1.bias"]
+        out[h + "mlp.c_proj.weight"], out[h + "mlp.c_proj.bias"] = state[p + "ffn.fc2.weight"].t().contiguous(), state[p + "ffn.fc2.bias"]
+        for src, dst in (("ln1", "ln_1"), ("ln2", "ln_2")):
+            out[h + dst + ".weight"], out[h + dst + ".bias"] = state[p + src + ".weight"], state[p + src + ".bias"]
+    return out
+
+
 def config_from_hf(hf_config) -> "GPTConfig":
     """GPTConfig for a Hugging Face GPT-2 or Llama configuration object (or dict)."""
     from ..models.config import GPTConfig
@@ -126,7 +145,7 @@ def config_from_hf(hf_config) -> "GPTConfig":
     raise ValueError(f"unsupported Hugging Face model type {c.get('model_type')!r}")
 
 
-__all__ += ["convert_hf_gpt2", "convert_hf_llama", "export_hf_llama", "config_from_hf"]
+__all__ += ["convert_hf_gpt2", "convert_hf_llama", "export_hf_llama", "export_hf_gpt2", "config_from_hf"]
 
 
 def main(argv=None) -> int:

@@ -271,3 +271,33 @@ def test_engine_loop_batches_concurrent_http_style_requests():
         assert loop.generate(prompts[0], 10, timeout=60) == want[0]     # and the loop is still alive
     finally:
         loop.shutdown()
+
+
+def test_paged_serving_engine_generates_the_tokens_hugging_face_generates():
+    """Independent oracle for the whole serving path (paged KV cache, prefill + decode, continuous batching): greedy
+    tokens equal `transformers` greedy generation for a GPT-2 and a Llama model; a model trained here exports back."""
+    transformers = pytest.importorskip("transformers")
+    from rustral_b200.utils.hf import config_from_hf, convert_hf_gpt2, convert_hf_llama, export_hf_gpt2
+    torch.manual_seed(0)
+    hc = transformers.GPT2Config(vocab_size=200, n_positions=48, n_embd=64, n_layer=2, n_head=4, resid_pdrop=0.0,
+                                 embd_pdrop=0.0, attn_pdrop=0.0)
+    lc = transformers.LlamaConfig(vocab_size=200, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                  num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=48, rope_theta=10000.0,
+                                  rms_norm_eps=1e-5, tie_word_embeddings=False, attention_dropout=0.0)
+    prompts = [[5, 17, 3, 99, 42], [7, 7, 8], [150, 2, 31, 64, 11, 9, 120]]
+    for hf_cfg, cls, conv in ((hc, transformers.GPT2LMHeadModel, convert_hf_gpt2), (lc, transformers.LlamaForCausalLM, convert_hf_llama)):
+        model = cls(hf_cfg).eval()
+        cfg = config_from_hf(hf_cfg)
+        runner = ModelRunner(cfg, device="cpu", num_blocks=32)
+        runner.params.load_state_dict(conv(model.state_dict()))
+        eng = ServingEngine(runner, max_batch_size=4)
+        ids = [eng.submit(p, 10) for p in prompts]                  # all three in one continuous batch
+        eng.run_to_completion()
+        for p, rid in zip(prompts, ids):
+            with torch.no_grad():
+                ref = model.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, pad_token_id=0)[0, len(p):].tolist()
+            assert eng.scheduler.get(rid).generated == ref, (cfg.arch, p)
+        if cfg.arch == "gpt2":
+            back = export_hf_gpt2(runner.params.state_dict())
+            ref_sd = {k: v for k, v in model.state_dict().items() if not k.endswith((".attn.bias", ".attn.masked_bias"))}
+            assert set(back) == set(ref_sd) and all(torch.allclose(back[k], ref_sd[k].float(), atol=1e-7) for k in ref_sd)
