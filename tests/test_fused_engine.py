@@ -137,6 +137,32 @@ def test_hugging_face_checkpoints_convert_and_reproduce_hf_logits():
             ref = model(ids).logits
         out = eng.logits(ids)[..., :300]
         assert (out - ref).abs().max().item() < 1e-5, cfg.arch
+        # the hand-scheduled backward pass against Hugging Face's autograd: loss and a gradient of every kind
+        tgt = torch.randint(0, 300, (2, 32), generator=torch.Generator().manual_seed(3))
+        eng2 = FusedGPTEngine(cfg, "cpu", micro_batch=2)
+        eng2.params.load_state_dict(conv(model.state_dict()))
+        loss = eng2.train_step(ids, tgt, do_step=False)
+        model.zero_grad()
+        hf_loss = torch.nn.functional.cross_entropy(model(ids).logits.reshape(-1, 300), tgt.reshape(-1))
+        hf_loss.backward()
+        assert abs(float(loss) - float(hf_loss.detach())) < 1e-5
+        hf_grads = {k: v.grad for k, v in model.named_parameters()}
+        if cfg.arch == "gpt2":
+            pairs = [("layers.1.ffn.fc1.weight", hf_grads["transformer.h.1.mlp.c_fc.weight"].t()),
+                     ("layers.0.attn.wo.weight", hf_grads["transformer.h.0.attn.c_proj.weight"].t()),
+                     ("layers.0.ln1.bias", hf_grads["transformer.h.0.ln_1.bias"]),
+                     ("pos_embed.embed", hf_grads["transformer.wpe.weight"]),
+                     ("tok_embed.embed", hf_grads["transformer.wte.weight"])]          # tied: embedding + LM head
+        else:
+            pairs = [("layers.1.ffn.down.weight", hf_grads["model.layers.1.mlp.down_proj.weight"]),
+                     ("layers.0.attn.wo.weight", hf_grads["model.layers.0.self_attn.o_proj.weight"]),
+                     ("layers.0.ln1.weight", hf_grads["model.layers.0.input_layernorm.weight"]),
+                     ("head.weight", hf_grads["lm_head.weight"]),
+                     ("tok_embed.embed", hf_grads["model.embed_tokens.weight"])]
+        for name, want in pairs:
+            got = eng2.params.g(name)[:want.shape[0]]
+            err = (got - want).abs().max().item()
+            assert err <= 1e-4 * (want.abs().max().item() + 1e-3) + 1e-6, f"{cfg.arch} {name}: {err}"
     assert config_from_hf(lc).n_kv_head == 2 and config_from_hf(hc).tie_embeddings
     with pytest.raises(ValueError):
         config_from_hf({"model_type": "bert"})
