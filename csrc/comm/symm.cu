@@ -68,10 +68,30 @@ struct ZeroDev {
   float* norms[kMaxWorld];
 };
 
+// The [world] pointer tables are device arrays owned by the caller's communicator; every CTA copies them into
+// shared memory.  Nothing about them is cached on the host, so a communicator that is closed and another one that
+// is created later in the same process never see each other's (unmapped) peer addresses.
+__device__ __forceinline__ void load_tables(ZeroDev& d, const RbZeroArgs& a) {
+  const int r = threadIdx.x;
+  if (r < a.world) {
+    d.grads[r] = reinterpret_cast<const float*>(a.grad_ptrs_dev[r]);
+    d.lowp[r] = reinterpret_cast<__nv_bfloat16*>(a.lowp_ptrs_dev[r]);
+    d.pads[r] = reinterpret_cast<unsigned int*>(a.pad_ptrs_dev[r]);
+    d.norms[r] = reinterpret_cast<float*>(a.norm_ptrs_dev[r]);
+  }
+}
+
+// Two u32 counters ("last CTA" election of the two kernels) live behind the per-CTA partial sums in the caller's
+// scratch: partials[kZeroCounterSlot], partials[kZeroCounterSlot + 1].  They start at zero and are reset by the last CTA.
+constexpr int kZeroCounterSlot = 1536;
+constexpr int kZeroMaxGrid = 1024;
+
 __global__ void __launch_bounds__(kZeroThreads)
-zero_reduce_kernel(ZeroDev d, RbZeroArgs a, unsigned int* status, unsigned int* block_counter) {
+zero_reduce_kernel(RbZeroArgs a, unsigned int* status) {
+  __shared__ ZeroDev d;
   __shared__ int ok_sh;
   __shared__ float red[kZeroThreads / 32];
+  load_tables(d, a);
   if (threadIdx.x == 0)
     ok_sh = wait_flags(reinterpret_cast<const unsigned int*>(a.local_pad), a.world, 0, a.epoch,
                        static_cast<unsigned long long>(a.limit_ms) * 1000000ull, status, 10) ? 1 : 0;
@@ -82,11 +102,19 @@ zero_reduce_kernel(ZeroDev d, RbZeroArgs a, unsigned int* status, unsigned int* 
     const long long n4 = a.shard_len / 4;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+      // All peer loads of an element are issued back to back (up to eight requests in flight per thread, spread over
+      // all the peers at once, so no GPU is everybody's first target), then summed in rank order: the value does not
+      // depend on timing.
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-      for (int r = 0; r < a.world; ++r) {   // fixed order: the reduced value does not depend on timing
-        const float4 g = *(reinterpret_cast<const float4*>(d.grads[r] + a.shard_off) + i);   // peer load over NVLink
-        acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+      for (int r0 = 0; r0 < a.world; r0 += 8) {
+        float4 g[8];
+        const int nr = min(8, a.world - r0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j < nr) g[j] = *(reinterpret_cast<const float4*>(d.grads[r0 + j] + a.shard_off) + i);   // peer load over NVLink
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j < nr) { acc.x += g[j].x; acc.y += g[j].y; acc.z += g[j].z; acc.w += g[j].w; }
       }
       reinterpret_cast<float4*>(a.grad_shard)[i] = acc;
       sq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
@@ -100,6 +128,7 @@ zero_reduce_kernel(ZeroDev d, RbZeroArgs a, unsigned int* status, unsigned int* 
     for (int w = 0; w < kZeroThreads / 32; ++w) t += red[w];
     a.partials[blockIdx.x] = t;
     __threadfence();
+    unsigned int* block_counter = reinterpret_cast<unsigned int*>(a.partials + kZeroCounterSlot);
     const unsigned int done = atomicAdd(block_counter, 1u);
     if (done == gridDim.x - 1) {
       // last CTA: fold the per-CTA partials in index order and publish to every rank
@@ -118,9 +147,11 @@ zero_reduce_kernel(ZeroDev d, RbZeroArgs a, unsigned int* status, unsigned int* 
 // Phase 2: AdamW on the shard, push bf16 parameters to every rank.
 // ------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kZeroThreads)
-zero_adam_push_kernel(ZeroDev d, RbZeroArgs a, unsigned int* status, unsigned int* block_counter) {
+zero_adam_push_kernel(RbZeroArgs a, unsigned int* status) {
+  __shared__ ZeroDev d;
   __shared__ int ok_sh;
   __shared__ float coef_sh;
+  load_tables(d, a);
   if (threadIdx.x == 0) {
     const bool ok = wait_flags(reinterpret_cast<const unsigned int*>(a.local_pad), a.world, 1, a.epoch,
                                static_cast<unsigned long long>(a.limit_ms) * 1000000ull, status, 11);
@@ -163,13 +194,16 @@ zero_adam_push_kernel(ZeroDev d, RbZeroArgs a, unsigned int* status, unsigned in
       o.x = pack_bf16x2(p[0], p[1]);
       o.y = pack_bf16x2(p[2], p[3]);
 #pragma unroll 1
-      for (int r = 0; r < a.world; ++r)   // the all-gather: a direct store into every rank's working copy
+      for (int j = 0; j < a.world; ++j) {   // the all-gather: a direct store into every rank's working copy
+        const int r = (a.rank + 1 + j) % a.world;
         *reinterpret_cast<uint2*>(d.lowp[r] + a.shard_off + i * 4) = o;
+      }
     }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
+    unsigned int* block_counter = reinterpret_cast<unsigned int*>(a.partials + kZeroCounterSlot) + 1;
     const unsigned int done = atomicAdd(block_counter, 1u);
     if (done == gridDim.x - 1) {
       __threadfence_system();
@@ -259,38 +293,6 @@ tp_allreduce_kernel(void* const* __restrict__ stage_ptrs, void* const* __restric
 
 }  // namespace rb
 
-namespace {
-unsigned int* block_counter() {
-  static unsigned int* ptrs[64] = {nullptr};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return nullptr;
-  if (!ptrs[dev]) {
-    unsigned int* p = nullptr;
-    if (cudaMalloc(&p, 2 * sizeof(unsigned int)) != cudaSuccess) return nullptr;
-    cudaMemset(p, 0, 2 * sizeof(unsigned int));
-    ptrs[dev] = p;
-  }
-  return ptrs[dev];
-}
-
-// Copies the [world] pointer arrays (device memory) into the by-value kernel argument.
-int load_dev(const RbZeroArgs& a, rb::ZeroDev& d) {
-  if (a.world < 1 || a.world > rb::kMaxWorld) return -1;
-  void* tmp[4][rb::kMaxWorld];
-  const void* src[4] = {a.grad_ptrs_dev, a.lowp_ptrs_dev, a.pad_ptrs_dev, a.norm_ptrs_dev};
-  for (int k = 0; k < 4; ++k)
-    if (cudaMemcpy(tmp[k], src[k], sizeof(void*) * a.world, cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
-  for (int r = 0; r < a.world; ++r) {
-    d.grads[r] = reinterpret_cast<const float*>(tmp[0][r]);
-    d.lowp[r] = reinterpret_cast<__nv_bfloat16*>(tmp[1][r]);
-    d.pads[r] = reinterpret_cast<unsigned int*>(tmp[2][r]);
-    d.norms[r] = reinterpret_cast<float*>(tmp[3][r]);
-  }
-  return 0;
-}
-}  // namespace
-
 RB_API void* rb_symm_alloc(long long bytes) {
   void* p = nullptr;
   if (bytes <= 0 || cudaMalloc(&p, static_cast<size_t>(bytes)) != cudaSuccess) return nullptr;
@@ -332,39 +334,28 @@ RB_API int rb_wait_all(const void* local_pad, int world, int channel, unsigned i
   return static_cast<int>(cudaGetLastError());
 }
 
-static rb::ZeroDev g_zero_dev;
-static const void* g_zero_dev_key = nullptr;
-
-static int zero_prepare(const RbZeroArgs* a) {
+static int zero_check(const RbZeroArgs* a) {
   if (!a || a->shard_len <= 0 || (a->shard_len % 4) || (a->shard_off % 4)) return -1;
-  if (g_zero_dev_key != a->grad_ptrs_dev) {   // pointer tables are fixed for the life of a trainer: read them once
-    const int rc = load_dev(*a, g_zero_dev);
-    if (rc != 0) return rc;
-    g_zero_dev_key = a->grad_ptrs_dev;
-  }
+  if (a->world < 1 || a->world > rb::kMaxWorld || a->rank < 0 || a->rank >= a->world) return -1;
+  if (!a->grad_ptrs_dev || !a->lowp_ptrs_dev || !a->pad_ptrs_dev || !a->norm_ptrs_dev || !a->partials) return -1;
   return 0;
 }
 
 RB_API int rb_zero_reduce(const RbZeroArgs* a, void* stream_v) {
-  const int rc = zero_prepare(a);
+  const int rc = zero_check(a);
   if (rc != 0) return rc;
-  unsigned int* ctr = block_counter();
-  if (!ctr) return -3;
   int grid = rbhost::device_sm_count() * 2;
-  if (grid > 1024) grid = 1024;
-  rb::zero_reduce_kernel<<<grid, rb::kZeroThreads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
-      g_zero_dev, *a, rbhost::status_ptr(), ctr);
+  if (grid > rb::kZeroMaxGrid) grid = rb::kZeroMaxGrid;
+  rb::zero_reduce_kernel<<<grid, rb::kZeroThreads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(*a, rbhost::status_ptr());
   return static_cast<int>(cudaGetLastError());
 }
 
 RB_API int rb_zero_adam_push(const RbZeroArgs* a, void* stream_v) {
-  const int rc = zero_prepare(a);
+  const int rc = zero_check(a);
   if (rc != 0) return rc;
-  unsigned int* ctr = block_counter();
-  if (!ctr) return -3;
-  const int grid = rbhost::device_sm_count() * 2;
-  rb::zero_adam_push_kernel<<<grid, rb::kZeroThreads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
-      g_zero_dev, *a, rbhost::status_ptr(), ctr + 1);
+  int grid = rbhost::device_sm_count() * 2;
+  if (grid > rb::kZeroMaxGrid) grid = rb::kZeroMaxGrid;
+  rb::zero_adam_push_kernel<<<grid, rb::kZeroThreads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(*a, rbhost::status_ptr());
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -33,7 +33,8 @@ typedef struct RbZeroArgs {
   float* master;                // local fp32 [shard_len]
   float* m;                     // local fp32 [shard_len]
   float* v;                     // local fp32 [shard_len]
-  float* partials;              // local fp32 scratch [>= 1024]
+  float* partials;              // local fp32 scratch [2048], zero-filled once by the caller: per-CTA partial sums in
+                                // [0, 1024), two u32 "last CTA" counters at [1536] and [1537] (the kernels reset them)
   long long shard_off;          // first flat index this rank owns
   long long shard_len;
   long long decay_end;          // flat indices below this get weight decay

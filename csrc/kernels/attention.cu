@@ -565,7 +565,8 @@ RB_API int rb_attention_fwd(const RbAttnArgs* a, void* stream_v) {
   if (a->head_dim == 64) {
     rb::attn_fwd_kernel<64><<<grid, rb::kAttnThreads, smem, stream>>>(p);
   } else {
-    static bool cfg = false;
+    static bool cfg_dev[64] = {false};
+    bool& cfg = cfg_dev[rbhost::device_slot()];
     if (!cfg) { cudaFuncSetAttribute(rb::attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); cfg = true; }
     rb::attn_fwd_kernel<128><<<grid, rb::kAttnThreads, smem, stream>>>(p);
   }
@@ -589,7 +590,8 @@ RB_API int rb_attention_bwd(const RbAttnArgs* a, void* stream_v) {
   const int smem_kv = 6 * rb::kTile * a->head_dim * 2 + 4 * rb::kTile * static_cast<int>(sizeof(float));
   const int smem_q = 6 * rb::kTile * a->head_dim * 2;
   if (a->head_dim == 64) {
-    static bool cfg = false;
+    static bool cfg_dev[64] = {false};
+    bool& cfg = cfg_dev[rbhost::device_slot()];
     if (!cfg) {
       cudaFuncSetAttribute(rb::attn_bwd_dkv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_kv);
       cudaFuncSetAttribute(rb::attn_bwd_dq_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q);
@@ -599,7 +601,8 @@ RB_API int rb_attention_bwd(const RbAttnArgs* a, void* stream_v) {
     rb::attn_bwd_dkv_kernel<64><<<kvgrid, rb::kAttnThreads, smem_kv, stream>>>(p);
     rb::attn_bwd_dq_kernel<64><<<qgrid, rb::kAttnThreads, smem_q, stream>>>(p);
   } else {
-    static bool cfg = false;
+    static bool cfg_dev[64] = {false};
+    bool& cfg = cfg_dev[rbhost::device_slot()];
     if (!cfg) {
       cudaFuncSetAttribute(rb::attn_bwd_dkv_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_kv);
       cudaFuncSetAttribute(rb::attn_bwd_dq_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q);

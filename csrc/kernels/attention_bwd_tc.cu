@@ -511,7 +511,8 @@ int bt_launch(const CUtensorMap* tq, const CUtensorMap* tk, const CUtensorMap* t
               const rb::BtParams& p, dim3 grid, cudaStream_t stream) {
   auto kern = rb::attn_bwd_tc_kernel<D, MODE>;
   const int smem = rb::BtSmem<D, MODE>::kTotal + 1024;
-  static bool cfg = false;
+  static bool cfg_dev[64] = {false};
+    bool& cfg = cfg_dev[rbhost::device_slot()];
   if (!cfg) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);

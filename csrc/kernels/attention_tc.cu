@@ -369,12 +369,14 @@ RB_API int rb_attention_fwd_tc(const RbAttnArgs* a, void* stream_v) {
   dim3 grid((a->seq_q + rb::kTcTile - 1) / rb::kTcTile, a->heads, a->batch);
   if (a->head_dim == 64) {
     const int smem = rb::TcSmem<64>::kTotal;
-    static bool cfg = false;
+    static bool cfg_dev[64] = {false};
+    bool& cfg = cfg_dev[rbhost::device_slot()];
     if (!cfg) { cudaFuncSetAttribute(rb::attn_fwd_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); cfg = true; }
     rb::attn_fwd_tc_kernel<64><<<grid, rb::kTcThreads, smem, stream>>>(*tq, *tk, *tv, p, rbhost::status_ptr());
   } else {
     const int smem = rb::TcSmem<128>::kTotal;
-    static bool cfg = false;
+    static bool cfg_dev[64] = {false};
+    bool& cfg = cfg_dev[rbhost::device_slot()];
     if (!cfg) { cudaFuncSetAttribute(rb::attn_fwd_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); cfg = true; }
     rb::attn_fwd_tc_kernel<128><<<grid, rb::kTcThreads, smem, stream>>>(*tq, *tk, *tv, p, rbhost::status_ptr());
   }

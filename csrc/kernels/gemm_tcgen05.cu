@@ -970,7 +970,8 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
   const bool staged = can_stage && (g.peer_mode == 2 || staged_store_default());
   if (g.peer_mode == 2 && !staged) return -11;
   const int smem = (staged ? L::kTotalStaged : L::kTotal) + 1024;
-  static int configured = 0;   // per instantiation: largest size set so far
+  static int configured_dev[64] = {0};   // per instantiation and device: largest size set so far
+  int& configured = configured_dev[rbhost::device_slot()];
   if (configured < smem) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -1052,7 +1053,8 @@ int launch_pair(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* t
   const bool staged = !g.out_f32 && !g.accumulate && splits <= 1 && (g.N % 8 == 0) && staged_store_default() &&
                       L::kTotalStaged + 1024 <= 232448;
   const int smem = (staged ? L::kTotalStaged : L::kTotal) + 1024;
-  static int configured = 0;
+  static int configured_dev[64] = {0};
+  int& configured = configured_dev[rbhost::device_slot()];
   if (configured < smem) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);

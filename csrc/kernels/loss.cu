@@ -51,18 +51,24 @@ __device__ __forceinline__ void block_online_reduce(float& m, float& s, float* s
 }
 
 __global__ void __launch_bounds__(kCeThreads)
-cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
+cross_entropy_kernel(const __nv_bfloat16* logits, long long ld, const long long* __restrict__ targets,
                      float* __restrict__ loss, float* __restrict__ lse_out, __nv_bfloat16* dlogits, long long ldd,
                      int n_valid, int n_pad, float grad_scale, long long ignore_index) {
   __shared__ float sh_m[32], sh_s[32];
   const long long row = blockIdx.x;
   const __nv_bfloat16* x = logits + row * ld;
   const long long tgt = targets[row];
+  const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= n_valid;
+  // `dlogits` may be the same memory as `logits` (the gradient overwrites the logits): the target logit is read
+  // here, before the reduction's barriers, because other warps start storing gradients right after them; and the
+  // row is read with plain loads, not through the read-only path.
+  float x_tgt = 0.f;
+  if (threadIdx.x == 0 && !ignored) x_tgt = __bfloat162float(x[tgt]);
   const bool vec_ok = ((ld & 7) == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
   float m = -INFINITY, s = 0.f;
   const int n8 = vec_ok ? (n_valid / 8) : 0;
   for (int i = threadIdx.x; i < n8; i += blockDim.x) {
-    uint4 u = __ldg(reinterpret_cast<const uint4*>(x) + i);
+    uint4 u = reinterpret_cast<const uint4*>(x)[i];
     float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
     const float lm = fmaxf(fmaxf(fmaxf(f0.x, f0.y), fmaxf(f1.x, f1.y)), fmaxf(fmaxf(f2.x, f2.y), fmaxf(f3.x, f3.y)));
     const float mm = fmaxf(m, lm);
@@ -78,10 +84,9 @@ cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, con
   }
   block_online_reduce(m, s, sh_m, sh_s);
   const float lse = m + logf(s);
-  const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= n_valid;
   if (threadIdx.x == 0) {
     if (lse_out) lse_out[row] = lse;
-    loss[row] = ignored ? 0.f : lse - __bfloat162float(x[tgt]);
+    loss[row] = ignored ? 0.f : lse - x_tgt;
   }
   if (dlogits == nullptr) return;
   __nv_bfloat16* dx = dlogits + row * ldd;
@@ -94,7 +99,7 @@ cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, con
     if (c0 < n_valid) {
       float f[8];
       if (c0 + 8 <= n_valid) {
-        uint4 u = __ldg(reinterpret_cast<const uint4*>(x) + i);
+        uint4 u = reinterpret_cast<const uint4*>(x)[i];
         float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
         f[0] = f0.x; f[1] = f0.y; f[2] = f1.x; f[3] = f1.y; f[4] = f2.x; f[5] = f2.y; f[6] = f3.x; f[7] = f3.y;
       } else {

@@ -411,6 +411,14 @@ const CUtensorMap* get_tmap_4d(const void* base, int elem_bytes, const uint64_t 
 
 int device_sm_count();
 
+// Index of the current device, clamped to [0, 64): kernel attributes such as the dynamic shared-memory opt-in are
+// per device, so the "already configured" guards of the launchers are arrays indexed by this.
+inline int device_slot() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return dev < 0 ? 0 : (dev > 63 ? 63 : dev);
+}
+
 // Per-device status buffer (4 x u32, zero-initialised on first use; nullptr if allocation failed).
 unsigned int* status_ptr();
 

@@ -84,6 +84,9 @@ int rb_sched_state(const RbScheduler* s, int64_t id);                       // -
 void rb_sched_stats(const RbScheduler* s, int64_t* out4);                   // completed, preempted, admitted, generated tokens
 int rb_sched_list(const RbScheduler* s, int which, int64_t* ids, int cap);  // which: 0 pending, 1 running, 2 paused; returns count
 void rb_sched_forget(RbScheduler* s, int64_t id);                           // drops the record of a completed request
+// Removes an unfinished request from whichever queue holds it, frees its blocks and drops its record.  Returns 1 when
+// a request was removed, 0 when it had already completed, -1 when the id is unknown.
+int rb_sched_abort(RbScheduler* s, int64_t id);
 
 // ---- asynchronous checkpoint file writer ----------------------------------------------------------------------------
 // Worker threads write each job to "<path>.partial", fsync and rename it into place.  submit_* return a ticket (> 0)

@@ -242,6 +242,25 @@ int rb_sched_list(const RbScheduler* s, int which, int64_t* ids, int cap) {
   return n;
 }
 
+int rb_sched_abort(RbScheduler* s, int64_t id) {
+  if (!s) return -1;
+  auto it = s->reqs.find(id);
+  if (it == s->reqs.end()) return -1;
+  Req& r = it->second;
+  if (r.state == kCompleted) return 0;
+  auto drop = [&](std::deque<int64_t>& q) {
+    auto p = std::find(q.begin(), q.end(), id);
+    if (p != q.end()) q.erase(p);
+  };
+  drop(s->pending);
+  drop(s->paused);
+  auto p = std::find(s->running.begin(), s->running.end(), id);
+  if (p != s->running.end()) s->running.erase(p);
+  rb_ba_free(s->alloc, id);                     // no-op when the request holds no blocks
+  s->reqs.erase(it);
+  return 1;
+}
+
 void rb_sched_forget(RbScheduler* s, int64_t id) {
   if (!s) return;
   auto it = s->reqs.find(id);

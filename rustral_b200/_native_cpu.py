@@ -66,6 +66,7 @@ def declare_runtime(lib) -> None:
     _sig(lib, "rb_sched_stats", [P, P])
     _sig(lib, "rb_sched_list", [P, I, P, I], I)
     _sig(lib, "rb_sched_forget", [P, LL])
+    _sig(lib, "rb_sched_abort", [P, LL], C.c_int)
     _sig(lib, "rb_aw_create", [I], P)
     _sig(lib, "rb_aw_destroy", [P])
     _sig(lib, "rb_aw_submit_copy", [P, C.c_char_p, P, LL], LL)

@@ -122,6 +122,7 @@ class Adam(Optimizer):
         self.weight_decay, self.decoupled, self.max_grad_norm = weight_decay, decoupled, max_grad_norm
         self.state: dict = {}       # ParameterId -> AdamState
         self._master: dict = {}     # fp32 master copies of low-precision parameters
+        self._master_seen: dict = {}  # ParameterId -> (data_ptr, tensor version) of the parameter after our last write
         self._names: dict = {}
 
     def with_betas(self, b1: float, b2: float):
@@ -170,15 +171,34 @@ class Adam(Optimizer):
                 if p.tensor.dtype == torch.float32:
                     master, lowp = p.tensor.view(-1), None
                 else:
-                    master = self._master.get(p.id)
-                    if master is None:
-                        master = self._master[p.id] = p.tensor.detach().float().view(-1).clone()
+                    master = self._fresh_master(p)
                     lowp = p.tensor.view(-1) if p.tensor.dtype == torch.bfloat16 else None
                 ops.adam_step(master, st.m, st.v, g, lr=self.lr, beta1=self.beta1, beta2=self.beta2, eps=self.eps,
                               weight_decay=self.weight_decay, step=st.t, decoupled=self.decoupled, p_lowp=lowp,
                               max_grad_norm=self.max_grad_norm, grad_norm=grad_norm)
                 if p.tensor.dtype not in (torch.float32, torch.bfloat16):
                     p.tensor.copy_(master.view(p.shape).to(p.tensor.dtype))
+                if p.tensor.dtype != torch.float32:
+                    self._master_seen[p.id] = (p.tensor.data_ptr(), p.tensor._version)
+
+    def _fresh_master(self, p: Parameter) -> torch.Tensor:
+        """The fp32 master copy of a low-precision parameter.  The copy is re-derived from the parameter whenever
+        somebody else wrote the parameter since this optimizer's last step (a state-dict load, a re-initialisation, a
+        tied-weight copy): such writes bump the tensor's version counter or replace its storage, the optimizer's own
+        kernel write does neither."""
+        master = self._master.get(p.id)
+        seen = self._master_seen.get(p.id)
+        now = (p.tensor.data_ptr(), p.tensor._version)
+        if master is None or master.numel() != p.numel() or master.device != p.tensor.device or (seen is not None and seen != now):
+            master = self._master[p.id] = p.tensor.detach().float().reshape(-1).clone()
+        return master
+
+    def reset_master(self, params=None) -> None:
+        """Forgets the fp32 master copies (of `params`, or all): the next step re-derives them from the parameters."""
+        ids = list(self._master) if params is None else [p.id for p in params]
+        for pid in ids:
+            self._master.pop(pid, None)
+            self._master_seen.pop(pid, None)
 
     # ---- checkpoints ---------------------------------------------------------------------------------------------
     def save_checkpoint(self, params=None) -> AdamCheckpoint:
@@ -188,8 +208,11 @@ class Adam(Optimizer):
                           ((getattr(x, "name", None), x) if isinstance(x, Parameter) else x for x in params)})
         state = {}
         for pid, st in self.state.items():
-            state[names.get(pid, str(int(pid)))] = {"m": st.m.detach().cpu().tolist(), "v": st.v.detach().cpu().tolist(),
-                                                    "t": st.t, "shape": [st.m.numel()]}
+            entry = {"m": st.m.detach().cpu().tolist(), "v": st.v.detach().cpu().tolist(), "t": st.t,
+                     "shape": [st.m.numel()]}
+            if pid in self._master:      # low-precision parameter: the fp32 master copy is part of the state
+                entry["master"] = self._master[pid].detach().cpu().tolist()
+            state[names.get(pid, str(int(pid)))] = entry
         return AdamCheckpoint(self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, self.decoupled, state)
 
     def load_checkpoint(self, ckpt: AdamCheckpoint, named_params) -> None:
@@ -204,11 +227,24 @@ class Adam(Optimizer):
             if len(s["m"]) != p.numel():
                 raise ShapeMismatch((p.numel(),), (len(s["m"]),), f"optimizer state of {name}")
             dev = p.tensor.device
+            master = None
+            if "master" in s and p.tensor.dtype != torch.float32:
+                if len(s["master"]) != p.numel():
+                    raise ShapeMismatch((p.numel(),), (len(s["master"]),), f"master copy of {name}")
+                master = torch.tensor(s["master"], dtype=torch.float32, device=dev)
             staged[p.id] = (name, AdamState(torch.tensor(s["m"], dtype=torch.float32, device=dev),
-                                            torch.tensor(s["v"], dtype=torch.float32, device=dev), int(s["t"])))
-        for pid, (name, st) in staged.items():
+                                            torch.tensor(s["v"], dtype=torch.float32, device=dev), int(s["t"])), master, p)
+        for pid, (name, st, master, p) in staged.items():
             self.state[pid] = st
             self._names[pid] = name
+            self._master.pop(pid, None)
+            self._master_seen.pop(pid, None)
+            if master is not None:
+                # the saved master copy continues the run exactly; the working copy is rounded from it
+                self._master[pid] = master
+                with torch.no_grad():
+                    p.tensor.copy_(master.view(p.shape).to(p.tensor.dtype))
+                self._master_seen[pid] = (p.tensor.data_ptr(), p.tensor._version)
 
 
 def AdamW(lr: float = 1e-3, weight_decay: float = 0.01, **kw) -> Adam:

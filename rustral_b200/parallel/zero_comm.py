@@ -77,11 +77,12 @@ class NcclZeroComm:
 
 
 def make_zero_comm(trainer, kind: str = "auto"):
+    """"fused" / "auto" on a CUDA device: the peer-memory kernels, and an error if they cannot be set up (there is no
+    quiet switch to the library path: a run that asked for the fused kernels either uses them or stops).  "nccl", or
+    CPU ranks: library collectives."""
     if kind in ("auto", "fused") and trainer.device.type == "cuda":
-        try:
-            from .fused_zero import FusedZeroComm
-            return FusedZeroComm(trainer)
-        except Exception:
-            if kind == "fused":
-                raise
+        from .fused_zero import FusedZeroComm
+        return FusedZeroComm(trainer)
+    if kind == "fused":
+        raise ValueError("the fused ZeRO kernels need CUDA devices")
     return NcclZeroComm(trainer)

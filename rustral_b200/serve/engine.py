@@ -49,8 +49,16 @@ class ServingEngine:
                arrival_time: float | None = None) -> int:
         if len(prompt) == 0:
             raise ValueError("empty prompt")
+        if max_tokens < 1:
+            raise ValueError("max_tokens must be at least 1")
         if len(prompt) + max_tokens > self.runner.cfg.seq_len:
             raise ValueError(f"prompt + max_tokens exceeds the model's context of {self.runner.cfg.seq_len}")
+        # A request that could never hold its whole sequence in the KV cache would sit at the head of the queue for
+        # ever (admission keeps the order when memory is short) and stall everything behind it: refuse it here.
+        cache = self.runner.cache
+        need = cache.blocks_needed(len(prompt) + max_tokens + 1)
+        if need > cache.num_blocks:
+            raise ValueError(f"request needs {need} KV blocks of {cache.block_size} tokens, the cache has {cache.num_blocks}")
         rid = self.scheduler.add_request(prompt, max_tokens, priority, self.eos_id, arrival_time)
         if callback is not None:
             self.callbacks[rid] = callback
@@ -106,6 +114,16 @@ class ServingEngine:
         if not keep_record:
             self.release(rid)
         return tokens
+
+    def abort_all(self) -> list:
+        """Removes every unfinished request (after a failed model step: retrying it would fail the same way), frees
+        their KV blocks and returns their ids."""
+        sch = self.scheduler
+        ids = [r.id for r in list(sch.pending)] + list(sch.running.keys()) + [r.id for r in list(sch.paused)]
+        for rid in ids:
+            sch.abort(rid)
+            self.callbacks.pop(rid, None)
+        return ids
 
     def release(self, rid: int) -> None:
         """Forgets a COMPLETED request: its entry in the scheduler (and the native core) and in `scheduler.completed`."""

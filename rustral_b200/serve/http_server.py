@@ -150,6 +150,8 @@ class EngineLoop:
         self._inbox: "queue.Queue" = queue.Queue(maxsize=max_pending)
         self._waiting: dict = {}                     # request id -> (result box, event) of the handler waiting for it
         self.steps = 0
+        self.failed_steps = 0
+        self.last_error = None
         self._stop = False
         self._thread = threading.Thread(target=self._run, daemon=True, name="rustral-engine-loop")
         self._thread.start()
@@ -190,6 +192,10 @@ class EngineLoop:
                     eng.step()
                     self.steps += 1
                 except Exception as e:   # noqa: BLE001 - a failed step must not strand the waiting handlers
+                    # the requests of the failed step leave the scheduler too: stepping them again would fail again
+                    eng.abort_all()
+                    self.failed_steps += 1
+                    self.last_error = e
                     for box, ev in self._waiting.values():
                         box.append((False, e))
                         ev.set()

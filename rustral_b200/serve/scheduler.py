@@ -231,6 +231,19 @@ class PyScheduler:
                 self.paused.append(r)
                 self.stats.preempted += 1
 
+    def abort(self, rid: int) -> bool:
+        """Removes an unfinished request from whichever queue holds it and frees its blocks."""
+        r = self.get(rid)
+        if r is None or r.state is RequestState.COMPLETED:
+            return False
+        self.running.pop(rid, None)
+        for q in (self.pending, self.paused):
+            for x in list(q):
+                if x.id == rid:
+                    q.remove(x)
+        self.cache.free(rid)
+        return True
+
     def get(self, rid: int):
         if rid in self.running:
             return self.running[rid]
@@ -344,6 +357,13 @@ class Scheduler:
     # ---- inspection ---------------------------------------------------------------------------------------------
     def get(self, rid: int):
         return self.requests.get(rid)
+
+    def abort(self, rid: int) -> bool:
+        """Removes an unfinished request from whichever queue holds it, frees its blocks and drops its record."""
+        if self._lib.rb_sched_abort(self._h, int(rid)) == 1:
+            self.requests.pop(rid, None)
+            return True
+        return False
 
     def forget(self, rid: int) -> None:
         """Drops a completed request's record (long-running servers call this after delivering the result)."""

@@ -69,9 +69,10 @@ def _run_noalloc(fn, x, dy, dres, gamma, mean, rstd, rms):
     return dx, dg, db
 
 
-def _close(a, b, tol=2e-2):
-    a, b = a.float(), b.float()
-    assert (a - b).abs().max().item() <= tol * (b.abs().max().item() + 1e-6)
+def _close(a, b):
+    # both entry points run the same deterministic kernels (ordered partial sums, no atomics): the results are equal
+    # bit for bit, not merely close
+    assert torch.equal(a, b)
 
 
 @pytest.mark.parametrize("rms", [False, True])
