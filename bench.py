@@ -10,7 +10,10 @@ Two timed regions of `steps` optimizer steps each, both after `warmup` untimed s
   * device-timed: token ids already on the device, CUDA events around the steps (max over ranks) -> "value";
   * end to end through the public API (LMTrainer.step): every step copies that step's token ids from pinned host
     memory and reads the loss back to the host -> "e2e".
-Rank 0 prints one JSON line.  `--impl reference` reports that the reference cannot be run here.
+Rank 0 prints one JSON line.  `--impl reference` reports that the reference cannot be run here.  `--impl torch` runs
+the same model, batch and optimizer in plain PyTorch (baseline/torch_gpt2.py: cuBLAS, SDPA, fused AdamW, FSDP) and
+prints the same line for it; the framework's own run ends with a short run of that arm on the same GPUs and reports
+`vs_baseline` = own tokens/s / its tokens/s (`--no-baseline` skips it).
 """
 from __future__ import annotations
 
@@ -28,7 +31,10 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
+    ap.add_argument("--zero-stage", type=int, default=3, choices=[2, 3])
+    ap.add_argument("--no-baseline", action="store_true", help="skip the plain-PyTorch run behind vs_baseline")
+    ap.add_argument("--baseline-steps", type=int, default=0, help="timed steps of the plain-PyTorch run (default: min(steps, 5))")
     ap.add_argument("--model", default="gpt2-small")
     ap.add_argument("--global-batch", type=int, default=256)
     ap.add_argument("--micro-batch", type=int, default=32)
@@ -93,6 +99,15 @@ def reference_arm(args):
     return 0
 
 
+def run_torch_arm(args, model, device, rank, world, steps, warmup):
+    """The plain-PyTorch arm (no code of this framework on its step)."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+    import torch_gpt2
+    return torch_gpt2.run(vocab=model.vocab_padded, seq_len=model.seq_len, n_layer=model.n_layer, heads=model.n_head,
+                          d_model=model.d_model, ffn=model.ffn_dim, global_batch=args.global_batch,
+                          micro_batch=args.micro_batch, steps=steps, warmup=warmup, device=device, rank=rank, world=world)
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -130,7 +145,36 @@ def main():
     if args.layers:
         overrides["n_layer"] = args.layers
     model = preset(args.model, **overrides)
-    tcfg = TrainConfig(global_batch=args.global_batch, micro_batch=args.micro_batch, comm=args.comm)
+    if model.arch != "gpt2" and (args.impl == "torch" or not args.no_baseline):
+        raise SystemExit("the plain-PyTorch arm covers the GPT-2 family only: pass --no-baseline")
+    data_note = "synthetic (uniform random token ids, fresh batch per step; random-init N(0,0.02) weights)"
+    l2_note = "no explicit flush: each step streams >10 GB of activations and a fresh batch, far beyond the 126 MB L2"
+    if args.impl == "torch":
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        r = run_torch_arm(args, model, device, rank, world, args.steps, args.warmup)
+        clocks = sampler.stop() if rank == 0 else None
+        if rank == 0:
+            tokens = r["tokens_per_step"]
+            print(json.dumps({
+                "impl": "torch", "metric": "train_tokens_per_s", "value": round(tokens / (r["ms_per_step"] / 1e3), 1),
+                "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": round(r["ms_per_step"], 3), "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "bf16", "data": data_note,
+                "config": {"model": args.model, "global_batch": args.global_batch, "seq_len": model.seq_len,
+                           "parallelism": f"dp{world}-fsdp-full-shard" if world > 1 else "single",
+                           "micro_batch": r["micro_batch"], "optimizer": "torch.optim.AdamW(fused), fp32 parameters, bf16 autocast, grad clip 1.0",
+                           "stack": "nn.Linear (cuBLAS), F.scaled_dot_product_attention, F.cross_entropy, torch FSDP", "l2": l2_note},
+                "clocks": clocks,
+                "e2e": {"value": round(tokens / (r["e2e_ms_per_step"] / 1e3), 1), "unit": "tokens/s",
+                        "ms_per_step": round(r["e2e_ms_per_step"], 3), "h2d_bytes_per_step": r["h2d_bytes_per_step"],
+                        "d2h_bytes_per_step": r["d2h_bytes_per_step"]},
+                "gpu_launches": 0, "peak_mem_bytes": r["peak_mem_bytes"], "final_loss": round(r["final_loss"], 4)}))
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+    tcfg = TrainConfig(global_batch=args.global_batch, micro_batch=args.micro_batch, comm=args.comm, zero_stage=args.zero_stage)
     trainer = LMTrainer(model, tcfg, device)
     _native.kernels().rb_init()
 
@@ -188,27 +232,48 @@ def main():
     e2e_ms_per_step = float(e2e_s) * 1e3 / args.steps
 
     bits, where = _native.read_status()
+    symm_bytes = trainer.symmetric_bytes()
+    peak_mem = torch.cuda.max_memory_allocated(device) + symm_bytes     # peer-mapped buffers bypass torch's allocator
+    state_bytes = trainer.state_bytes()
+    label = trainer.parallelism
+    comm_name = type(trainer.comm).__name__ if trainer.comm is not None else "none"
+    # ---------------------------------------------------------------- plain-PyTorch arm on the same GPUs
+    baseline = None
+    if not args.no_baseline:
+        trainer.close()
+        del trainer
+        torch.cuda.empty_cache()
+        try:
+            bsteps = args.baseline_steps or min(args.steps, 5)
+            r = run_torch_arm(args, model, device, rank, world, bsteps, min(args.warmup, 3))
+            baseline = {"impl": "torch", "value": round(args.global_batch * S / (r["ms_per_step"] / 1e3), 1),
+                        "ms_per_step": round(r["ms_per_step"], 3), "steps": bsteps,
+                        "e2e_value": round(args.global_batch * S / (r["e2e_ms_per_step"] / 1e3), 1),
+                        "peak_mem_bytes": r["peak_mem_bytes"]}
+        except Exception as e:      # noqa: BLE001 - the framework's own number must still be printed
+            baseline = {"impl": "torch", "failed": f"{type(e).__name__}: {e}"[:300]}
     tokens = args.global_batch * S
     value = tokens / (dev_ms_per_step / 1e3)
     e2e_value = tokens / (e2e_ms_per_step / 1e3)
     if rank == 0:
         flops = model.flops_per_token() * tokens
-        comm_name = type(trainer.comm).__name__ if trainer.comm is not None else "none"
+        ratio = round(value / baseline["value"], 4) if baseline and "value" in baseline else None
         out = {
             "metric": "train_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms_per_step, 3),
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic (uniform random token ids, fresh batch per step; random-init N(0,0.02) weights)",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": ratio, "baseline": baseline, "dtype": "bf16",
+            "data": data_note,
             "config": {"model": args.model, "global_batch": args.global_batch, "seq_len": S,
-                       "parallelism": f"dp{world}-zero{tcfg.zero_stage}" if world > 1 else "single",
-                       "micro_batch": trainer.micro_batch, "optimizer": "AdamW, fp32 master weights, grad clip 1.0",
+                       "parallelism": label, "zero_stage": tcfg.zero_stage if world > 1 else None,
+                       "micro_batch": min(args.micro_batch, local_b), "optimizer": "AdamW, fp32 master weights, grad clip 1.0",
                        "comm": comm_name, "layers": model.n_layer, "d_model": model.d_model,
                        "vocab": model.vocab_size, "vocab_padded": model.vocab_padded,
-                       "l2": "no explicit flush: each step streams >10 GB of activations and a fresh batch, far beyond the 126 MB L2"},
+                       "l2": l2_note},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms_per_step, 3),
                     "h2d_bytes_per_step": local_b * (S + 1) * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
+            "peak_mem_bytes": peak_mem, "symmetric_bytes": symm_bytes, "state_bytes": state_bytes,
             "model_tflops_per_s": round(flops / (dev_ms_per_step / 1e3) / 1e12, 1),
             "final_loss": round(final_loss, 4), "final_loss_e2e": round(final_loss_e2e, 4),
             "device_status": bits,

@@ -9,38 +9,11 @@
 #include <string.h>
 
 #include "rb_common.cuh"
+#include "flags.cuh"
 
 namespace rb {
 
 constexpr int kSignalSlots = 64;   // channels per pad = kSignalSlots / world is never needed: pad is [channel][world]
-
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// Bounded wait on `world` flags of one channel of the local pad.  One thread polls; returns false on expiry.
-__device__ __forceinline__ bool wait_flags(const unsigned int* pad, int world, int channel, unsigned int value,
-                                           unsigned long long limit_ns, unsigned int* status, unsigned int where) {
-  const unsigned int* f = pad + channel * world;
-  const unsigned long long t0 = globaltimer_ns();
-  for (int r = 0; r < world; ++r) {
-    while (true) {
-      const unsigned int v = ld_acquire_sys(f + r);
-      if (static_cast<int>(v - value) >= 0) break;     // wrap-safe "v >= value"
-      if (globaltimer_ns() - t0 > limit_ns) {
-        status_set(status, kStatusFlagTimeout, where);
-        return false;
-      }
-      __nanosleep(200);
-    }
-  }
-  return true;
-}
 
 __global__ void signal_all_kernel(void* const* pad_ptrs, int world, int my_rank, int channel, unsigned int value) {
   const int r = threadIdx.x;

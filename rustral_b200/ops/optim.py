@@ -87,7 +87,10 @@ def sumsq(x, out=None, found_inf=None, accumulate=False):
 
 def sqrt_scalar(x, out=None):
     if not x.is_cuda:
-        return x.sqrt()
+        if out is None:
+            return x.sqrt()
+        out.copy_(x.sqrt())
+        return out
     out = out if out is not None else torch.empty_like(x)
     N.check(N.kernels().rb_sqrt_scalar(x.data_ptr(), out.data_ptr(), N.stream_ptr()), "rb_sqrt_scalar")
     return out

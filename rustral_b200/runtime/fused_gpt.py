@@ -113,20 +113,7 @@ class FlatParams:
         self._init(seed)
 
     def _init(self, seed: int) -> None:
-        cfg = self.cfg
-        gen = torch.Generator().manual_seed(seed)
-        host = torch.zeros(self.total, dtype=torch.float32)
-        for s in self.specs:
-            v = host[s.offset:s.offset + s.numel].view(s.shape)
-            if s.init == "ones":
-                v.fill_(1.0)
-            elif s.init == "normal":
-                v.normal_(0.0, cfg.init_std, generator=gen)
-            elif s.init == "normal_scaled":
-                v.normal_(0.0, cfg.init_std / math.sqrt(2 * cfg.n_layer), generator=gen)
-            if s.name in ("tok_embed.embed", "head.weight") and cfg.vocab_padded > cfg.vocab_size:
-                v[cfg.vocab_size:].zero_()     # padded vocabulary rows stay inert
-        self.master.copy_(host)
+        self.master.copy_(init_flat_host(self.cfg, self.specs, self.total, seed))
         self.sync_lowp()
 
     def sync_lowp(self) -> None:
@@ -145,51 +132,106 @@ class FlatParams:
     def g(self, name):
         return self.view(self.grad, name)
 
+    # ---- hooks of the sharded store (parallel/zero3.py): nothing to do when every rank holds everything ---------
+    per_micro_reduce = False
+
+    def begin_micro(self, first_micro: bool) -> None:
+        pass
+
+    def acquire(self, bucket: int, prefetch=None) -> None:
+        pass
+
+    def begin_grads(self, bucket: int) -> None:
+        pass
+
+    def grads_done(self, bucket: int) -> None:
+        pass
+
+    def end_micro(self) -> None:
+        pass
+
+    def state_key(self):
+        return ()
+
+    def get_state(self):
+        return None
+
+    def set_state(self, st) -> None:
+        pass
+
     # ---- checkpoint views ---------------------------------------------------------------------------------
     def state_dict(self) -> dict:
         """fp32 tensors keyed by parameter name, vocabulary padding removed; fused projections are split into the
         per-matrix names of the reference (attn.wq / wk / wv)."""
-        cfg = self.cfg
-        out = {}
-        hd = cfg.head_dim
-        for s in self.specs:
-            t = self.view(self.master, s.name).detach().float().cpu().clone()
-            if s.name in ("tok_embed.embed", "head.weight"):
-                t = t[:cfg.vocab_size].clone()
-            if ".attn.wqkv." in s.name:
-                q_end, k_end = cfg.n_head * hd, (cfg.n_head + cfg.n_kv_head) * hd
-                for nm, sl in (("wq", slice(0, q_end)), ("wk", slice(q_end, k_end)), ("wv", slice(k_end, None))):
-                    out[s.name.replace("wqkv", nm)] = t[sl].clone()
-            else:
-                out[s.name] = t
-        return out
+        return flat_to_state(self.cfg, self.specs, self.master.detach().float().cpu())
 
     def load_state_dict(self, state: dict) -> None:
         """Strict: every expected key present, no extra keys, shapes equal; nothing is written before all checks pass."""
-        from ..core.errors import SerializationError, ShapeMismatch
-        expected = self.state_dict()
-        missing = [k for k in expected if k not in state]
-        extra = [k for k in state if k not in expected]
-        if missing:
-            raise SerializationError(f"missing keys: {missing}")
-        if extra:
-            raise SerializationError(f"unexpected keys: {extra}")
-        for k, t in expected.items():
-            if tuple(state[k].shape) != tuple(t.shape):
-                raise ShapeMismatch(t.shape, state[k].shape, k)
-        cfg = self.cfg
         host = self.master.detach().cpu().clone()
-        for s in self.specs:
-            v = host[s.offset:s.offset + s.numel].view(s.shape)
-            if ".attn.wqkv." in s.name:
-                parts = [state[s.name.replace("wqkv", nm)].float() for nm in ("wq", "wk", "wv")]
-                v.copy_(torch.cat(parts, 0))
-            elif s.name in ("tok_embed.embed", "head.weight"):
-                v[:cfg.vocab_size].copy_(state[s.name].float())
-            else:
-                v.copy_(state[s.name].float())
+        state_to_flat(self.cfg, self.specs, state, host)
         self.master.copy_(host)
         self.sync_lowp()
+
+
+def init_flat_host(cfg: GPTConfig, specs: list, total: int, seed: int) -> torch.Tensor:
+    """Host fp32 image of freshly initialised parameters in the flat layout of `specs` (same values for every way of
+    distributing them afterwards: one generator, parameters drawn in `specs` order)."""
+    gen = torch.Generator().manual_seed(seed)
+    host = torch.zeros(total, dtype=torch.float32)
+    for s in specs:
+        v = host[s.offset:s.offset + s.numel].view(s.shape)
+        if s.init == "ones":
+            v.fill_(1.0)
+        elif s.init == "normal":
+            v.normal_(0.0, cfg.init_std, generator=gen)
+        elif s.init == "normal_scaled":
+            v.normal_(0.0, cfg.init_std / math.sqrt(2 * cfg.n_layer), generator=gen)
+        if s.name in ("tok_embed.embed", "head.weight") and cfg.vocab_padded > cfg.vocab_size:
+            v[cfg.vocab_size:].zero_()     # padded vocabulary rows stay inert
+    return host
+
+
+def flat_to_state(cfg: GPTConfig, specs: list, host: torch.Tensor) -> dict:
+    """Named fp32 tensors from a host image in the flat layout: vocabulary padding removed, the fused QKV projection
+    split into the per-matrix names of the reference (attn.wq / wk / wv)."""
+    out = {}
+    hd = cfg.head_dim
+    for s in specs:
+        t = host[s.offset:s.offset + s.numel].view(s.shape).clone()
+        if s.name in ("tok_embed.embed", "head.weight"):
+            t = t[:cfg.vocab_size].clone()
+        if ".attn.wqkv." in s.name:
+            q_end, k_end = cfg.n_head * hd, (cfg.n_head + cfg.n_kv_head) * hd
+            for nm, sl in (("wq", slice(0, q_end)), ("wk", slice(q_end, k_end)), ("wv", slice(k_end, None))):
+                out[s.name.replace("wqkv", nm)] = t[sl].clone()
+        else:
+            out[s.name] = t
+    return out
+
+
+def state_to_flat(cfg: GPTConfig, specs: list, state: dict, host: torch.Tensor) -> None:
+    """Writes named tensors into a host image in the flat layout.  Strict: every expected key present, no extra keys,
+    shapes equal; `host` is only written after all checks have passed."""
+    from ..core.errors import SerializationError, ShapeMismatch
+    expected = flat_to_state(cfg, specs, host)
+    missing = [k for k in expected if k not in state]
+    extra = [k for k in state if k not in expected]
+    if missing:
+        raise SerializationError(f"missing keys: {missing}")
+    if extra:
+        raise SerializationError(f"unexpected keys: {extra}")
+    for k, t in expected.items():
+        if tuple(state[k].shape) != tuple(t.shape):
+            raise ShapeMismatch(t.shape, state[k].shape, k)
+    for s in specs:
+        v = host[s.offset:s.offset + s.numel].view(s.shape)
+        if ".attn.wqkv." in s.name:
+            parts = [state[s.name.replace("wqkv", nm)].float() for nm in ("wq", "wk", "wv")]
+            v.copy_(torch.cat(parts, 0))
+        elif s.name in ("tok_embed.embed", "head.weight"):
+            v[:cfg.vocab_size].copy_(state[s.name].float())
+        else:
+            v.copy_(state[s.name].float())
 
 
 class FusedGPTEngine:
@@ -197,16 +239,18 @@ class FusedGPTEngine:
 
     def __init__(self, cfg: GPTConfig, device=None, micro_batch: int = 8, seed: int = 0, lr: float = 3e-4,
                  betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1, max_grad_norm: float = 1.0,
-                 flat_pad_to: int = ALIGN):
+                 flat_pad_to: int = ALIGN, params=None):
+        """`params`: a parameter store to use instead of a `FlatParams` built here (the sharded store of ZeRO-3,
+        `parallel.zero3.ShardedParams`)."""
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.cfg = cfg
         self.device = torch.device(device)
         self.micro_batch = micro_batch
-        self.params = FlatParams(cfg, self.device, seed, pad_to=flat_pad_to)
+        self.params = params if params is not None else FlatParams(cfg, self.device, seed, pad_to=flat_pad_to)
         self.lr, self.betas, self.eps, self.weight_decay, self.max_grad_norm = lr, betas, eps, weight_decay, max_grad_norm
         self.step_count = 0
-        self.act_dtype = self.params.lowp.dtype
+        self.act_dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         self._acts = None
         self._acts_tokens = 0
         self.loss_acc = torch.zeros((), dtype=torch.float32, device=self.device)
@@ -251,11 +295,15 @@ class FusedGPTEngine:
         H, Hk, D = cfg.n_head, cfg.n_kv_head, cfg.head_dim
         scale = 1.0 / math.sqrt(D)
         x = A["layers"][0]["x"]
+        # bucket 0 (embeddings, final norm, head) stays usable for the whole pass; block l is bucket 1 + l, gathered
+        # one block ahead when the parameters are sharded (no-ops otherwise)
+        P.acquire(0, prefetch=1)
         ops.embedding_forward(ids.reshape(-1), P.w("tok_embed.embed"),
                               P.w("pos_embed.embed") if cfg.arch == "gpt2" else None, S, out=x)
         for l, L in enumerate(A["layers"]):
             p = f"layers.{l}."
             x = L["x"]
+            P.acquire(1 + l, prefetch=(2 + l) if l + 1 < cfg.n_layer else None)
             _, m1, r1 = norm_ops.norm_forward(x, P.w(p + "ln1.weight"), None if rms else P.w(p + "ln1.bias"),
                                               cfg.norm_eps, rms, out=L["ln1"])
             L["rstd1"] = r1
@@ -306,7 +354,10 @@ class FusedGPTEngine:
         rms = cfg.arch == "llama"
         H, Hk, D = cfg.n_head, cfg.n_kv_head, cfg.head_dim
         scale = 1.0 / math.sqrt(D)
-        acc = not first_micro
+        P.begin_micro(first_micro)
+        # a sharded store reduces every micro-batch's gradients into its shard: the local buffers are written afresh
+        fresh = first_micro or P.per_micro_reduce
+        acc = not fresh
         logits = self.forward(ids)
         A = self._acts
         loss_rows, _, dlogits = ops.cross_entropy_fwd_bwd(logits, targets.reshape(-1), cfg.vocab_size, grad_scale,
@@ -314,6 +365,7 @@ class FusedGPTEngine:
         ops.binary("add", self.loss_acc.view(1), ops.sum_all(loss_rows).view(1), out=self.loss_acc.view(1))
 
         head_name = "tok_embed.embed" if cfg.tie_embeddings else "head.weight"
+        P.begin_grads(0)
         gemm(dlogits, A["xf"], a_mn=True, b_mn=True, out=P.g(head_name), accumulate=acc)
         dxf = gemm(dlogits, P.w(head_name), b_mn=True, out_dtype=self.act_dtype)
         dx, _, _ = norm_ops.norm_backward(dxf, A["xf_in"], P.w("final_norm.weight"), A["meanf"], A["rstdf"], rms,
@@ -322,6 +374,8 @@ class FusedGPTEngine:
         for l in range(cfg.n_layer - 1, -1, -1):
             L = A["layers"][l]
             p = f"layers.{l}."
+            P.acquire(1 + l, prefetch=l if l > 0 else None)
+            P.begin_grads(1 + l)
             if rms:
                 gemm(dx, L["h"], a_mn=True, b_mn=True, out=P.g(p + "ffn.down.weight"), accumulate=acc)
                 dh = gemm(dx, P.w(p + "ffn.down.weight"), b_mn=True, out_dtype=self.act_dtype)
@@ -365,20 +419,23 @@ class FusedGPTEngine:
             dx, _, _ = norm_ops.norm_backward(dln1, L["x"], P.w(p + "ln1.weight"), None if rms else L["mean1"],
                                               L["rstd1"], rms, dres=dx1, dgamma=P.g(p + "ln1.weight"),
                                               dbeta=None if rms else P.g(p + "ln1.bias"), accumulate=acc)
+            P.grads_done(1 + l)
         # embeddings
-        if first_micro:
+        if fresh:
             if cfg.arch == "gpt2":
                 ops.scalar_op("fill", P.g("pos_embed.embed").view(-1), 0.0, out=P.g("pos_embed.embed").view(-1))
             if not cfg.tie_embeddings:
                 ops.scalar_op("fill", P.g("tok_embed.embed").view(-1), 0.0, out=P.g("tok_embed.embed").view(-1))
         ops.embedding_backward(ids.reshape(-1), dx, P.g("tok_embed.embed"),
                                P.g("pos_embed.embed") if cfg.arch == "gpt2" else None, S)
+        P.grads_done(0)
+        P.end_micro()
 
     def _forward_backward_graphed(self, ids, targets, grad_scale: float, first_micro: bool) -> None:
         """`forward_backward` replayed from a CUDA graph.  One graph per (shape, first_micro, grad_scale); the first
         two calls of a key run eagerly (lazy kernel configuration, scratch allocation, tensor-map cache), the third
         is captured and every later one is a copy of the token ids into static buffers plus one graph launch."""
-        key = (tuple(ids.shape), bool(first_micro), float(grad_scale))
+        key = (tuple(ids.shape), bool(first_micro), float(grad_scale), self.params.state_key())
         g = self._fb_graphs.get(key)
         if g is None:
             g = {"calls": 0, "graph": None, "ids": torch.empty_like(ids, memory_format=torch.contiguous_format),
@@ -400,7 +457,9 @@ class FusedGPTEngine:
             g["launches"] = _native.launch_count - before      # kernels recorded in the graph
             _native.launch_count = before                      # nothing ran during capture
             g["graph"] = graph
+            g["store_state"] = self.params.get_state()         # host-side bookkeeping of the store after this pass
         g["graph"].replay()
+        self.params.set_state(g["store_state"])
         _native.launch_count += g["launches"]                  # a replay launches every recorded kernel
 
     @staticmethod

@@ -30,8 +30,15 @@ class TrainConfig:
     weight_decay: float = 0.1
     max_grad_norm: float = 1.0
     seed: int = 0
-    zero_stage: int = 3              # 0: plain DP all-reduce; 1/2/3: sharded optimizer (+ gradients, + parameters)
-    comm: str = "auto"               # "nccl": library collectives; "fused": peer-memory kernels; "auto": fused if available
+    # How the data-parallel ranks share the training state (one rank: everything is local, the stage is moot):
+    #   3: parameters, gradients and optimizer state sharded; each block's parameters are gathered just before it runs
+    #      (forward and backward) and its gradients reduce-scattered right after its backward, overlapped with compute
+    #      (parallel/zero3.py);
+    #   2: optimizer state and the gradient reduction sharded, every rank keeps a full bf16 working copy and a full
+    #      fp32 gradient buffer; the owner pushes updated parameters into every rank's copy after the step
+    #      (parallel/fused_zero.py, or library collectives in parallel/zero_comm.py).
+    zero_stage: int = 3
+    comm: str = "auto"               # "nccl": library collectives; "fused": peer-memory kernels; "auto": fused on CUDA devices
 
 
 class LMTrainer:
@@ -58,20 +65,70 @@ class LMTrainer:
         self.micro_batch = min(c.micro_batch, self.local_batch)
         if self.local_batch % self.micro_batch:
             raise ValueError("the per-rank batch must be a multiple of the micro-batch")
+        if c.zero_stage not in (2, 3):
+            raise ValueError("zero_stage must be 2 or 3")
+        self.zero_stage = c.zero_stage if self.world > 1 else 0
+        store = None
+        if self.zero_stage == 3:
+            from ..parallel.zero3 import ShardedParams
+            peer = self.device.type == "cuda" and c.comm in ("auto", "fused")
+            if c.comm == "fused" and not peer:
+                raise ValueError("the fused ZeRO kernels need CUDA devices")
+            store = ShardedParams(model, self.device, c.seed, group=process_group, transport="peer" if peer else "collective")
         self.engine = FusedGPTEngine(model, self.device, self.micro_batch, c.seed, c.lr, c.betas, c.eps, c.weight_decay,
-                                     c.max_grad_norm, flat_pad_to=ALIGN * self.world)
+                                     c.max_grad_norm, flat_pad_to=ALIGN * self.world, params=store)
+        if store is not None and not store.transport.overlapped:
+            self.engine.use_graphs = False           # library collectives are issued eagerly
         self.tokens_per_step = c.global_batch * model.seq_len
         P = self.engine.params
-        self.shard_len = P.total // self.world
-        self.shard = slice(self.rank * self.shard_len, (self.rank + 1) * self.shard_len)
+        if store is not None:
+            self.shard_len = P.shard_len
+            self.shard = slice(self.rank * P.shard_len, (self.rank + 1) * P.shard_len)   # position in rank-major order
+        else:
+            self.shard_len = P.total // self.world
+            self.shard = slice(self.rank * self.shard_len, (self.rank + 1) * self.shard_len)
         self._dev_tokens = None
         self._loss_host = torch.zeros((), dtype=torch.float32).pin_memory() if self.device.type == "cuda" else None
         self._norm_buf = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._grad_lowp = None
         self.comm = None
-        if self.world > 1:
+        if self.zero_stage == 3:
+            from ..parallel.zero3 import Zero3Comm
+            self.comm = Zero3Comm(self)
+        elif self.world > 1:
             from ..parallel.zero_comm import make_zero_comm
             self.comm = make_zero_comm(self, c.comm)
+
+    @property
+    def parallelism(self) -> str:
+        """Truthful label of how the ranks share the state, e.g. "dp8-zero3-peer", "dp8-zero2-push", "single"."""
+        if self.world == 1:
+            return "single"
+        kind = type(self.comm).__name__
+        tr = getattr(self.engine.params, "transport", None)
+        how = {"Zero3Comm": "peer" if getattr(tr, "overlapped", False) else "collective",
+               "FusedZeroComm": "push", "NcclZeroComm": "nccl"}.get(kind, kind)
+        return f"dp{self.world}-zero{self.zero_stage}-{how}"
+
+    def symmetric_bytes(self) -> int:
+        """Bytes this rank holds in peer-mapped buffers; they come from the driver directly, not from torch's
+        allocator, so torch's memory statistics do not count them."""
+        owner = getattr(self.engine.params, "transport", None) if self.zero_stage == 3 else self.comm
+        bufs = getattr(owner, "_symm", None)
+        if bufs is None and owner is not None:
+            bufs = [getattr(owner, n) for n in ("grad_buf", "lowp_buf", "norm_buf", "pad") if hasattr(owner, n)]
+        return int(sum(getattr(b, "nbytes", 0) for b in (bufs or [])))
+
+    def state_bytes(self) -> dict:
+        """Bytes of parameters, gradients and optimizer state held by THIS rank (activations excluded)."""
+        P = self.engine.params
+        if self.zero_stage == 3:
+            return P.state_bytes()
+        lp = P.lowp.element_size()
+        if self.comm is not None and hasattr(self.comm, "master"):      # stage 2 over peer memory
+            return {"param_full": P.total * lp, "grad_full": P.total * 4, "optimizer_shard": 3 * self.shard_len * 4,
+                    "grad_shard": self.shard_len * 4, "unsharded_leftover": 3 * P.total * 4}
+        return {"param_full": P.total * lp, "grad_full": P.total * 4, "optimizer_full": 3 * P.total * 4}
 
     # -------------------------------------------------------------------------------------------------
     def step_device(self, tokens_dev: torch.Tensor, lr: float | None = None) -> torch.Tensor:
@@ -82,7 +139,9 @@ class LMTrainer:
         if not ids.is_contiguous():
             ids, tgt = ids.contiguous(), tgt.contiguous()
         loss = eng.train_step(ids, tgt, total_tokens=self.tokens_per_step, lr=lr, do_step=(self.world == 1))
-        if self.world > 1:
+        if self.zero_stage == 3:
+            loss = self.comm.reduce_and_step(eng.loss_acc, lr)       # the summed token loss; the exchange scales it
+        elif self.world > 1:
             loss = self.comm.reduce_and_step(loss, lr)
         return loss
 
@@ -146,14 +205,15 @@ class LMTrainer:
             m, v = P.m, P.v
         tensors = {"adam.m": m.detach().float().cpu().clone(), "adam.v": v.detach().float().cpu().clone()}
         meta = {"step": int(self.engine.step_count), "world": self.world, "rank": self.rank,
-                "shard_off": int(self.shard.start), "shard_len": int(self.shard_len)}
+                "shard_off": int(self.shard.start), "shard_len": int(self.shard_len), "zero_stage": int(self.zero_stage)}
         return tensors, meta
 
     def load_optimizer_state(self, tensors: dict, meta: dict) -> None:
         """Strict: the state must come from the same rank of a run with the same number of ranks and the same shard."""
         from ..core.errors import SerializationError
-        want = {"world": self.world, "rank": self.rank, "shard_off": int(self.shard.start), "shard_len": int(self.shard_len)}
-        got = {k: int(meta.get(k, -1)) for k in want}
+        want = {"world": self.world, "rank": self.rank, "shard_off": int(self.shard.start), "shard_len": int(self.shard_len),
+                "zero_stage": int(self.zero_stage)}
+        got = {k: int(meta.get(k, want[k] if k == "zero_stage" else -1)) for k in want}
         if got != want:
             raise SerializationError(f"optimizer state was saved for {got}, this rank is {want}")
         if self.comm is not None:

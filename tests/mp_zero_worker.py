@@ -20,6 +20,10 @@ def main():
     ap.add_argument("--device", default="cuda")
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--model", default="gpt2-test")
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--zero-stage", type=int, default=3)
+    ap.add_argument("--reopen", action="store_true",
+                    help="close the trainer, build a second one in the same process and step it (peer tables must not be reused)")
     ap.add_argument("--resume-check", action="store_true",
                     help="snapshot weights + per-rank optimizer state, resume in a second trainer, compare the next steps")
     a = ap.parse_args()
@@ -34,8 +38,9 @@ def main():
     from rustral_b200 import _native
     from rustral_b200.models.config import preset
     from rustral_b200.runtime.lm_trainer import LMTrainer, TrainConfig
-    cfg = preset(a.model)
-    tr = LMTrainer(cfg, TrainConfig(global_batch=8, micro_batch=2, lr=1e-3, comm=a.comm), dev)
+    cfg = preset(a.model, **({"n_layer": a.layers} if a.layers else {}))
+    tcfg = lambda: TrainConfig(global_batch=8, micro_batch=2, lr=1e-3, comm=a.comm, zero_stage=a.zero_stage)
+    tr = LMTrainer(cfg, tcfg(), dev)
     g = torch.Generator().manual_seed(7)
     data = torch.randint(0, cfg.vocab_size, (8, cfg.seq_len + 1), generator=g, dtype=torch.int64)
     local = data[rank * tr.local_batch:(rank + 1) * tr.local_batch].contiguous()
@@ -52,7 +57,7 @@ def main():
     resume = None
     if a.resume_check:
         opt_tensors, opt_meta = tr.optimizer_state()
-        tr2 = LMTrainer(cfg, TrainConfig(global_batch=8, micro_batch=2, lr=1e-3, comm=a.comm), dev)
+        tr2 = LMTrainer(cfg, tcfg(), dev)
         tr2.load_state_dict(sd)
         tr2.load_optimizer_state(opt_tensors, opt_meta)
         cont = [tr.step(local) for _ in range(2)]
@@ -60,9 +65,19 @@ def main():
         resume = {"continued": cont, "resumed": again, "shard_len": opt_meta["shard_len"], "world": opt_meta["world"],
                   "moments_numel": int(opt_tensors["adam.m"].numel())}
         tr2.close()
+    comm_name = type(tr.comm).__name__ if tr.comm is not None else "none"
+    label, state_bytes = tr.parallelism, tr.state_bytes()
+    reopened = None
+    if a.reopen:
+        tr.close()
+        tr = LMTrainer(cfg, tcfg(), dev)              # same process, new symmetric buffers and peer tables
+        reopened = [tr.step(local) for _ in range(a.steps)]
+        if a.device == "cuda":
+            torch.cuda.synchronize()
+            status |= _native.read_status()[0]
     if rank == 0:
         print(json.dumps({"losses": losses, "checksum": checksum, "probe": probe, "status": status, "resume": resume,
-                          "comm": type(tr.comm).__name__ if tr.comm is not None else "none"}))
+                          "comm": comm_name, "parallelism": label, "state_bytes": state_bytes, "reopened": reopened}))
     tr.close()
     dist.destroy_process_group()
 

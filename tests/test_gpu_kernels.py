@@ -56,8 +56,25 @@ def test_cross_entropy(rows, n_valid, n_pad, cuda_status):
     assert gg[:, n_valid:].abs().sum().item() == 0
     # in-place variant
     l2 = logits.cuda().clone()
-    ops.cross_entropy_fwd_bwd(l2, t.cuda(), n_valid, 0.25, dlogits=l2)
+    loss_inplace, lse_inplace, _ = ops.cross_entropy_fwd_bwd(l2, t.cuda(), n_valid, 0.25, dlogits=l2)
     assert torch.equal(l2, gg)
+    # the loss of the in-place call is the out-of-place loss bit for bit: the target logit is read before any
+    # thread of the row's block overwrites it with a gradient
+    assert torch.equal(loss_inplace, lg) and torch.equal(lse_inplace, lseg)
+
+
+def test_cross_entropy_in_place_loss_is_exact_on_many_wide_rows(cuda_status):
+    """Wide rows (several chunks per thread) and targets near the start of the row, where the first gradient stores
+    land: the per-row loss of the in-place form equals the out-of-place form exactly, on every repetition."""
+    rows, n = 512, 50304
+    g = torch.Generator().manual_seed(11)
+    logits = (torch.randn(rows, n, generator=g) * 3).to(torch.bfloat16).cuda()
+    t = torch.randint(0, 64, (rows,), generator=g).cuda()
+    want, _, _ = ops.cross_entropy_fwd_bwd(logits, t, 50257, 1.0)
+    for _ in range(3):
+        l2 = logits.clone()
+        got, _, _ = ops.cross_entropy_fwd_bwd(l2, t, 50257, 1.0, dlogits=l2)
+        assert torch.equal(got, want)
 
 
 def test_softmax_rows(cuda_status):

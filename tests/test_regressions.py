@@ -1,0 +1,130 @@
+"""Regression cases for faults found by review: each test fails on the code before its fix."""
+import threading
+
+import pytest
+import torch
+
+from rustral_b200.core.parameter import Parameter
+from rustral_b200.models.config import preset
+from rustral_b200.optim import Adam, AdamCheckpoint
+from rustral_b200.serve.engine import ServingEngine
+from rustral_b200.serve.model_runner import ModelRunner
+from rustral_b200.serve.scheduler import PyScheduler, Scheduler
+
+
+# ---------------------------------------------------------------------------------------------- optimizer master copies
+def _lowp_param(seed=0, n=64):
+    g = torch.Generator().manual_seed(seed)
+    return Parameter("w", torch.randn(n, generator=g).to(torch.bfloat16))
+
+
+def test_adam_uses_weights_loaded_after_its_first_step():
+    """A state-dict load (an in-place write by somebody else) after the first step must not be reverted by the
+    optimizer's fp32 master copy at the next step."""
+    p = _lowp_param()
+    opt = Adam(lr=1e-2)
+    g = torch.ones(64)
+    opt.step([p], {p.id: g})
+    loaded = torch.full((64,), 3.0, dtype=torch.bfloat16)
+    with torch.no_grad():
+        p.tensor.copy_(loaded)                               # e.g. load_state_dict
+    opt.step([p], {p.id: g})
+    # the step moved the LOADED weights by about lr, it did not jump back to the pre-load trajectory
+    assert (p.tensor.float() - 3.0).abs().max() < 0.05
+    # and an explicit reset does the same for writes the version counter cannot see
+    p.tensor.data = torch.full((64,), -2.0, dtype=torch.bfloat16)
+    opt.reset_master([p])
+    opt.step([p], {p.id: g})
+    assert (p.tensor.float() + 2.0).abs().max() < 0.05
+
+
+def test_adam_master_is_not_rederived_without_external_writes():
+    """Without outside writes the fp32 master keeps the bits bf16 cannot hold: many tiny steps accumulate."""
+    p = Parameter("w", torch.ones(8, dtype=torch.bfloat16))
+    opt = Adam(lr=1e-4)                                       # 1e-4 is below bf16 resolution at 1.0 (2^-8)
+    for _ in range(60):
+        opt.step([p], {p.id: torch.ones(8)})
+    master = opt._master[p.id]
+    assert float(master[0]) < 1.0 - 50e-4                     # the fp32 copy moved ...
+    assert float(p.tensor[0]) < 1.0                           # ... and eventually so did the rounded copy
+
+
+def test_adam_checkpoint_carries_the_master_copy():
+    """A resumed run continues the uninterrupted run bit for bit: the fp32 master copy is part of the checkpoint."""
+    g = torch.Generator().manual_seed(3)
+    grads = [torch.randn(64, generator=g) for _ in range(6)]
+    a = _lowp_param(1)
+    opt_a = Adam.adamw(lr=3e-3, weight_decay=0.1)
+    for gr in grads[:3]:
+        opt_a.step([a], {a.id: gr})
+    ck = AdamCheckpoint.from_json(opt_a.save_checkpoint([("w", a)]).to_json())
+    assert "master" in ck.state["w"]
+    b = Parameter("w", a.tensor.clone())
+    opt_b = Adam.adamw(lr=1.0)
+    opt_b.load_checkpoint(ck, [("w", b)])
+    for gr in grads[3:]:
+        opt_a.step([a], {a.id: gr})
+        opt_b.step([b], {b.id: gr})
+    assert torch.equal(a.tensor, b.tensor)
+    assert torch.equal(opt_a._master[a.id], opt_b._master[b.id])
+
+
+# ---------------------------------------------------------------------------------------------- serving admission
+def _engine(num_blocks=4, seq_len=256):
+    cfg = preset("gpt2-test", seq_len=seq_len, d_model=64, ffn_dim=128)
+    return ServingEngine(ModelRunner(cfg, device="cpu", num_blocks=num_blocks), max_batch_size=4)
+
+
+def test_submit_refuses_requests_that_can_never_fit_the_cache():
+    eng = _engine(num_blocks=4)                               # 4 blocks of 16 tokens
+    with pytest.raises(ValueError, match="KV blocks"):
+        eng.submit(list(range(1, 60)), 20)                    # 59 + 20 + 1 tokens = 5 blocks
+    with pytest.raises(ValueError, match="max_tokens"):
+        eng.submit([1, 2, 3], 0)
+    assert not eng.scheduler.has_work()
+    # a request that does fit still runs, and nothing is left behind
+    assert len(eng.generate([1, 2, 3], 4)) == 4
+    assert eng.runner.cache.free_blocks == 4
+
+
+@pytest.mark.parametrize("cls", [PyScheduler, Scheduler])
+def test_scheduler_abort_frees_blocks_in_every_queue(cls):
+    from rustral_b200.serve.kv_cache import PagedCache
+    cache = PagedCache(8, 16)
+    s = cls(cache, max_batch_size=2)
+    ids = [s.add_request(list(range(20)), 4) for _ in range(4)]
+    batch = s.schedule()                                      # two admitted (2 blocks each), two pending
+    assert len(batch) == 2 and cache.free_blocks == 4
+    assert s.abort(ids[0]) and s.abort(ids[3])
+    assert cache.free_blocks == 6
+    assert not s.abort(12345)
+    s.abort(ids[1]); s.abort(ids[2])
+    assert not s.has_work() and cache.free_blocks == 8
+
+
+def test_engine_loop_drops_the_requests_of_a_failed_step():
+    """When the model step raises, the waiting handlers get the error, the requests leave the scheduler (the loop does
+    not retry the failing step for ever) and the loop keeps serving."""
+    from rustral_b200.serve.http_server import EngineLoop
+    eng = _engine(num_blocks=32, seq_len=64)
+    real_prefill = eng.runner.prefill
+    calls = {"n": 0}
+
+    def flaky(rid, ids):
+        calls["n"] += 1
+        if calls["n"] == 1:
+            raise RuntimeError("injected model failure")
+        return real_prefill(rid, ids)
+    eng.runner.prefill = flaky
+    loop = EngineLoop(eng)
+    try:
+        with pytest.raises(RuntimeError, match="injected"):
+            loop.generate([1, 2, 3], 4, timeout=60)
+        assert loop.failed_steps == 1
+        deadline = threading.Event()
+        deadline.wait(0.2)
+        assert not eng.scheduler.has_work() and eng.runner.cache.free_blocks == 32
+        assert len(loop.generate([1, 2, 3], 4, timeout=60)) == 4       # still alive, step no longer failing
+        assert calls["n"] == 2
+    finally:
+        loop.shutdown()
