@@ -24,11 +24,9 @@ __global__ void epoch_advance_kernel(unsigned int* p) {
 // all-gather of one bucket's parameters (pull)
 // ---------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kZ3Threads) zero3_gather_kernel(RbZero3Gather a, unsigned int* status) {
-  __shared__ const uint4* src[kZ3MaxWorld];
+  // Shared memory is kept to one word: this kernel is meant to run beside GEMM CTAs that take almost all of an SM's
+  // shared memory, and fits in what they leave.
   __shared__ int ok_sh;
-  if (threadIdx.x < a.world)
-    src[threadIdx.x] = reinterpret_cast<const uint4*>(
-        reinterpret_cast<const __nv_bfloat16*>(a.lowp_ptrs_dev[threadIdx.x]) + a.shard_off);
   if (threadIdx.x == 0)
     ok_sh = wait_flags_from(reinterpret_cast<const unsigned int*>(a.local_pad), a.world, a.channel,
                             static_cast<long long>(*a.epoch_dev), static_cast<unsigned long long>(a.limit_ms) * 1000000ull,
@@ -41,7 +39,7 @@ __global__ void __launch_bounds__(kZ3Threads) zero3_gather_kernel(RbZero3Gather 
   // Peers are visited starting with the next rank, so that at any moment the ranks pull from different GPUs.
   for (int j = 0; j < a.world; ++j) {
     const int r = (a.rank + 1 + j) % a.world;
-    const uint4* s = src[r];
+    const uint4* s = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.lowp_ptrs_dev[r]) + a.shard_off);
     uint4* d = dst + r * n8;
     long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     for (; i + 3 * stride < n8; i += 4 * stride) {          // four independent 16-byte requests in flight per thread
@@ -56,20 +54,12 @@ __global__ void __launch_bounds__(kZ3Threads) zero3_gather_kernel(RbZero3Gather 
 // reduce-scatter of one bucket's gradients (pull), accumulated into the gradient shard
 // ---------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kZ3Threads) zero3_reduce_kernel(RbZero3Reduce a, unsigned int* status) {
-  __shared__ const float4* src[kZ3MaxWorld];
-  __shared__ unsigned int* pads[kZ3MaxWorld];
-  __shared__ int ok_sh;
+  __shared__ int ok_sh;                    // one word of shared memory only (see the gather kernel)
   const unsigned int epoch = *a.epoch_dev;
-  if (threadIdx.x < a.world) {
-    src[threadIdx.x] = reinterpret_cast<const float4*>(
-        reinterpret_cast<const float*>(a.grad_ptrs_dev[threadIdx.x]) + static_cast<long long>(a.rank) * a.n_per_rank);
-    pads[threadIdx.x] = reinterpret_cast<unsigned int*>(a.pad_ptrs_dev[threadIdx.x]);
-  }
-  __syncthreads();
   // This kernel is stream-ordered after the kernels that wrote this rank's gradients of the bucket: tell every peer.
   if (blockIdx.x == 0 && threadIdx.x < a.world) {
     __threadfence_system();
-    st_release_sys(pads[threadIdx.x] + a.ready_channel * a.world + a.rank, epoch);
+    st_release_sys(reinterpret_cast<unsigned int*>(a.pad_ptrs_dev[threadIdx.x]) + a.ready_channel * a.world + a.rank, epoch);
   }
   if (threadIdx.x == 0)
     ok_sh = wait_flags(reinterpret_cast<const unsigned int*>(a.local_pad), a.world, a.ready_channel, epoch,
@@ -79,6 +69,11 @@ __global__ void __launch_bounds__(kZ3Threads) zero3_reduce_kernel(RbZero3Reduce 
     const long long n4 = a.n_per_rank / 4;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     float4* dst = reinterpret_cast<float4*>(a.shard_dst);
+    const long long my_off = static_cast<long long>(a.rank) * a.n_per_rank;
+    const float4* src[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      src[j] = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.grad_ptrs_dev[j < a.world ? j : 0]) + my_off);
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
       // all peers' values are requested back to back, then added in rank order: independent of timing
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -87,7 +82,9 @@ __global__ void __launch_bounds__(kZ3Threads) zero3_reduce_kernel(RbZero3Reduce 
         const int nr = min(8, a.world - r0);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          if (j < nr) g[j] = src[r0 + j][i];
+          if (j < nr)
+            g[j] = r0 == 0 ? src[j][i]
+                           : (reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.grad_ptrs_dev[r0 + j]) + my_off))[i];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           if (j < nr) { acc.x += g[j].x; acc.y += g[j].y; acc.z += g[j].z; acc.w += g[j].w; }
@@ -106,9 +103,42 @@ __global__ void __launch_bounds__(kZ3Threads) zero3_reduce_kernel(RbZero3Reduce 
     if (done == gridDim.x - 1) {
       // every CTA of this rank has finished reading the peers' buffers: they may overwrite them
       __threadfence_system();
-      for (int r = 0; r < a.world; ++r) st_release_sys(pads[r] + a.consumed_channel * a.world + a.rank, epoch);
+      for (int r = 0; r < a.world; ++r)
+        st_release_sys(reinterpret_cast<unsigned int*>(a.pad_ptrs_dev[r]) + a.consumed_channel * a.world + a.rank, epoch);
       *a.counter = 0;
     }
+  }
+}
+
+__global__ void zero3_signal_kernel(void* const* pad_ptrs, int world, int rank, int channel, const unsigned int* epoch_dev) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<unsigned int*>(pad_ptrs[r]) + channel * world + rank, *epoch_dev);
+  }
+}
+
+__global__ void __launch_bounds__(kZ3Threads) zero3_sum_kernel(RbZero3Sum a) {
+  const long long n4 = a.n / 4;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  float4* dst = reinterpret_cast<float4*>(a.dst);
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r0 = 0; r0 < a.num_src; r0 += 8) {
+      float4 g[8];
+      const int nr = min(8, a.num_src - r0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < nr) g[j] = reinterpret_cast<const float4*>(a.src[r0 + j])[i];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < nr) { acc.x += g[j].x; acc.y += g[j].y; acc.z += g[j].z; acc.w += g[j].w; }
+    }
+    if (a.accumulate) {
+      const float4 o = dst[i];
+      acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+    }
+    dst[i] = acc;
   }
 }
 
@@ -217,6 +247,8 @@ __global__ void __launch_bounds__(kZ3Threads) zero3_adam_kernel(RbZero3Step a, u
 }  // namespace rb
 
 namespace {
+int block_threads(int threads) { return (threads == 64 || threads == 128) ? threads : rb::kZ3Threads; }
+
 int clamp_grid(long long work_items, int max_ctas) {
   long long blocks = (work_items + rb::kZ3Threads - 1) / rb::kZ3Threads;
   const int cap = max_ctas > 0 ? max_ctas : 64;
@@ -238,7 +270,7 @@ RB_API int rb_zero3_gather(const RbZero3Gather* a, void* stream_v) {
   if (a->n_per_rank <= 0 || (a->n_per_rank % 8) || (a->shard_off % 8) || a->channel < 0 || a->limit_ms <= 0) return -1;
   if (reinterpret_cast<uintptr_t>(a->dst) & 15) return -2;
   const int grid = clamp_grid(a->n_per_rank / 8, a->max_ctas);
-  rb::zero3_gather_kernel<<<grid, rb::kZ3Threads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(*a, rbhost::status_ptr());
+  rb::zero3_gather_kernel<<<grid, block_threads(a->threads), 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(*a, rbhost::status_ptr());
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -248,7 +280,26 @@ RB_API int rb_zero3_reduce(const RbZero3Reduce* a, void* stream_v) {
   if (a->n_per_rank <= 0 || (a->n_per_rank % 4) || a->ready_channel < 0 || a->consumed_channel < 0 || a->limit_ms <= 0) return -1;
   if (reinterpret_cast<uintptr_t>(a->shard_dst) & 15) return -2;
   const int grid = clamp_grid(a->n_per_rank / 4, a->max_ctas);
-  rb::zero3_reduce_kernel<<<grid, rb::kZ3Threads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(*a, rbhost::status_ptr());
+  rb::zero3_reduce_kernel<<<grid, block_threads(a->threads), 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(*a, rbhost::status_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
+RB_API int rb_zero3_signal(void* const* pad_ptrs_dev, int world, int rank, int channel, const unsigned int* epoch_dev,
+                           void* stream_v) {
+  if (!pad_ptrs_dev || !epoch_dev || world < 1 || world > rb::kZ3MaxWorld || rank < 0 || rank >= world || channel < 0) return -1;
+  rb::zero3_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(pad_ptrs_dev, world, rank, channel, epoch_dev);
+  return static_cast<int>(cudaGetLastError());
+}
+
+RB_API int rb_zero3_sum(const RbZero3Sum* a, void* stream_v) {
+  if (!a || !a->dst || a->n <= 0 || (a->n % 4) || a->num_src < 1 || a->num_src > 16) return -1;
+  for (int i = 0; i < a->num_src; ++i)
+    if (!a->src[i] || (reinterpret_cast<uintptr_t>(a->src[i]) & 15)) return -2;
+  if (reinterpret_cast<uintptr_t>(a->dst) & 15) return -2;
+  long long blocks = (a->n / 4 + rb::kZ3Threads - 1) / rb::kZ3Threads;
+  const long long cap = 4LL * rbhost::device_sm_count();
+  if (blocks > cap) blocks = cap;
+  rb::zero3_sum_kernel<<<static_cast<int>(blocks), rb::kZ3Threads, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(*a);
   return static_cast<int>(cudaGetLastError());
 }
 

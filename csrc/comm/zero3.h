@@ -33,6 +33,7 @@ typedef struct RbZero3Gather {
   long long n_per_rank;            // elements per rank in this bucket (multiple of 8)
   void* dst;                       // local bf16 landing buffer [world * n_per_rank]
   int world, rank, limit_ms, max_ctas;
+  int threads;                     // threads per CTA: 64, 128 or 256 (anything else: 256)
 } RbZero3Gather;
 int rb_zero3_gather(const RbZero3Gather* a, void* stream);
 
@@ -47,8 +48,24 @@ typedef struct RbZero3Reduce {
   int accumulate;                  // 0: shard_dst = sum; 1: shard_dst += sum
   unsigned int* counter;           // one u32, zero before the first call; the kernel resets it
   int world, rank, limit_ms, max_ctas;
+  int threads;                     // threads per CTA: 64, 128 or 256 (anything else: 256)
 } RbZero3Reduce;
 int rb_zero3_reduce(const RbZero3Reduce* a, void* stream);
+
+// Writes *epoch_dev into slot (channel, rank) of every rank's pad (release order after a system-scope fence): everything
+// this stream wrote before is visible to a peer that sees the flag.  One tiny CTA.
+int rb_zero3_signal(void* const* pad_ptrs_dev, int world, int rank, int channel, const unsigned int* epoch_dev, void* stream);
+
+// dst[i] (+)= src[0][i] + src[1][i] + ... (fixed order, fp32), n a multiple of 4: the local half of a reduce-scatter
+// whose remote slices were brought in by the copy engines.
+typedef struct RbZero3Sum {
+  const float* src[16];
+  float* dst;
+  long long n;
+  int num_src;
+  int accumulate;
+} RbZero3Sum;
+int rb_zero3_sum(const RbZero3Sum* a, void* stream);
 
 // Waits until all `world` flags of `channel` in the local pad are >= *epoch_dev + delta (delta <= 0).
 int rb_zero3_wait(const void* local_pad, int world, int channel, const unsigned int* epoch_dev, int delta, int limit_ms,

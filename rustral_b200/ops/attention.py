@@ -44,10 +44,14 @@ def _fill(args, q, k, v, o, causal, scale):
 
 N.optional_sig("rb_attention_fwd_tc", [N.C.POINTER(N.RbAttnArgs), N.c_void_p])
 N.optional_sig("rb_attention_bwd_tc", [N.C.POINTER(N.RbAttnArgs), N.c_void_p])
+N.optional_sig("rb_attention_fwd_tc2", [N.C.POINTER(N.RbAttnArgs), N.c_int, N.c_void_p])
 N._LAUNCHES["rb_attention_bwd_tc"] = 3
 
-# "tc": tcgen05 / TMEM kernel (falls back to "mma" for shapes it does not take); "mma": the mma.sync kernel.
+# "tc2": tcgen05 kernel with two query tiles per CTA in ping-pong (falls back to "tc" for shapes it does not take);
+# "tc": one query tile per CTA; "mma": the mma.sync kernel.
 FORWARD_IMPL = __import__("os").environ.get("RUSTRAL_ATTN_IMPL", "tc")
+# share of the exponentials computed by a polynomial on the FMA pipe in the "tc2" kernel: every k-th pair (0 = none)
+FORWARD_POLY_EVERY = int(__import__("os").environ.get("RUSTRAL_ATTN_POLY", "0"))
 BACKWARD_IMPL = __import__("os").environ.get("RUSTRAL_ATTN_BWD_IMPL", FORWARD_IMPL)
 
 
@@ -63,7 +67,19 @@ def attention_forward(q, k, v, causal: bool, scale: float, out=None, want_lse: b
     _fill(a, q, k, v, o, causal, scale)
     a.lse = N.ptr(lse)
     lib = N.kernels()
-    if (impl or FORWARD_IMPL) == "tc" and hasattr(lib, "rb_attention_fwd_tc"):
+    which = impl or FORWARD_IMPL
+    if which.startswith("tc2") and hasattr(lib, "rb_attention_fwd_tc2"):
+        # "tc2:4" selects the polynomial share explicitly; adding 16 ("tc2:16", "tc2:20") selects the variant that
+        # reads the scores from TMEM twice and keeps fewer registers live
+        poly = int(which[4:]) if len(which) > 4 else FORWARD_POLY_EVERY
+        if D == 128 and (poly & 15) not in (0, 4):
+            poly = (poly & 16) | 4
+        rc = lib.rb_attention_fwd_tc2(a, poly, N.stream_ptr())
+        if rc != -9:
+            N.check(rc, "rb_attention_fwd_tc2")
+            return o, lse
+        which = "tc"
+    if which == "tc" and hasattr(lib, "rb_attention_fwd_tc"):
         rc = lib.rb_attention_fwd_tc(a, N.stream_ptr())
         if rc != -9:
             N.check(rc, "rb_attention_fwd_tc")

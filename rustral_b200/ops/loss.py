@@ -7,11 +7,13 @@ from .. import _native as N
 
 
 def cross_entropy_fwd_bwd(logits2: torch.Tensor, targets: torch.Tensor, n_valid: int | None = None,
-                          grad_scale: float = 1.0, ignore_index: int = -100, dlogits=None, want_grad: bool = True):
+                          grad_scale: float = 1.0, ignore_index: int = -100, dlogits=None, want_grad: bool = True,
+                          loss_out=None):
     """Per-row loss (fp32 [rows]) and, when `want_grad`, ``(softmax - onehot) * grad_scale``.
 
     ``logits2`` is [rows, n_pad]; only the first ``n_valid`` columns take part (a padded vocabulary).
-    ``dlogits`` may alias ``logits2`` to overwrite the logits in place.
+    ``dlogits`` may alias ``logits2`` to overwrite the logits in place.  ``loss_out`` (fp32 [rows], optional)
+    receives the per-row loss instead of a new tensor.
     """
     rows, n_pad = logits2.shape
     n_valid = n_pad if n_valid is None else n_valid
@@ -30,13 +32,16 @@ def cross_entropy_fwd_bwd(logits2: torch.Tensor, targets: torch.Tensor, n_valid:
             full = torch.zeros(rows, n_pad)
             full[:, :n_valid] = p
             grad.copy_(full.to(grad.dtype))
+        if loss_out is not None:
+            loss_out.copy_(loss)
+            loss = loss_out
         return loss, lse, grad
     if logits2.dtype != torch.bfloat16:
         raise TypeError("cross_entropy: CUDA logits must be bf16")
     if logits2.stride(1) != 1:
         raise ValueError("cross_entropy: logits need a contiguous last dimension")
     targets = targets.to(torch.int64)
-    loss = torch.empty(rows, dtype=torch.float32, device=logits2.device)
+    loss = loss_out if loss_out is not None else torch.empty(rows, dtype=torch.float32, device=logits2.device)
     lse = torch.empty(rows, dtype=torch.float32, device=logits2.device)
     grad = None
     if want_grad:

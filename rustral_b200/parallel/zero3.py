@@ -46,14 +46,18 @@ CH_PARAMS, CH_NORM, CH_BASE = 4, 5, 8
 class RbZero3Gather(C.Structure):
     _fields_ = [("lowp_ptrs_dev", N.c_void_p), ("local_pad", N.c_void_p), ("epoch_dev", N.c_void_p), ("channel", N.c_int),
                 ("shard_off", N.c_ll), ("n_per_rank", N.c_ll), ("dst", N.c_void_p),
-                ("world", N.c_int), ("rank", N.c_int), ("limit_ms", N.c_int), ("max_ctas", N.c_int)]
+                ("world", N.c_int), ("rank", N.c_int), ("limit_ms", N.c_int), ("max_ctas", N.c_int), ("threads", N.c_int)]
 
 
 class RbZero3Reduce(C.Structure):
     _fields_ = [("grad_ptrs_dev", N.c_void_p), ("pad_ptrs_dev", N.c_void_p), ("local_pad", N.c_void_p),
                 ("epoch_dev", N.c_void_p), ("ready_channel", N.c_int), ("consumed_channel", N.c_int),
                 ("n_per_rank", N.c_ll), ("shard_dst", N.c_void_p), ("accumulate", N.c_int), ("counter", N.c_void_p),
-                ("world", N.c_int), ("rank", N.c_int), ("limit_ms", N.c_int), ("max_ctas", N.c_int)]
+                ("world", N.c_int), ("rank", N.c_int), ("limit_ms", N.c_int), ("max_ctas", N.c_int), ("threads", N.c_int)]
+
+
+class RbZero3Sum(C.Structure):
+    _fields_ = [("src", N.c_void_p * 16), ("dst", N.c_void_p), ("n", N.c_ll), ("num_src", N.c_int), ("accumulate", N.c_int)]
 
 
 class RbZero3Step(C.Structure):
@@ -73,6 +77,8 @@ N.optional_sig("rb_epoch_advance", [N.c_void_p, N.c_void_p])
 N.optional_sig("rb_zero3_gather", [C.POINTER(RbZero3Gather), N.c_void_p])
 N.optional_sig("rb_zero3_reduce", [C.POINTER(RbZero3Reduce), N.c_void_p])
 N.optional_sig("rb_zero3_wait", [N.c_void_p, N.c_int, N.c_int, N.c_void_p, N.c_int, N.c_int, N.c_void_p])
+N.optional_sig("rb_zero3_signal", [N.c_void_p, N.c_int, N.c_int, N.c_int, N.c_void_p, N.c_void_p])
+N.optional_sig("rb_zero3_sum", [C.POINTER(RbZero3Sum), N.c_void_p])
 N.optional_sig("rb_zero3_publish", [C.POINTER(RbZero3Step), N.c_void_p])
 N.optional_sig("rb_zero3_adam", [C.POINTER(RbZero3Step), N.c_void_p])
 
@@ -198,19 +204,43 @@ class _CollectiveTransport:
 
 
 class _PeerTransport:
-    """The kernels of csrc/comm/zero3.cu on two side streams."""
+    """Peer memory over NVLink on two side streams.  Two data planes:
+
+    "dma" (default): the bulk bytes are moved by the copy engines (stream-ordered device-to-device copies from the
+    peers' mapped buffers), so no SM is taken from the GEMMs, whose persistent CTAs fill every SM's shared memory and
+    leave no room for a second kernel to run beside them.  Kernels only carry the flags (one tiny CTA each: "my
+    gradients of bucket b are written", bounded waits, "I am done reading your buffer") and the local part of the
+    reduce-scatter (`rb_zero3_sum` on the main stream: own slice + the pulled slices, rank order, into the shard).
+    "kernel": `rb_zero3_gather` / `rb_zero3_reduce` pull with peer loads from inside the kernels.
+    """
     overlapped = True
 
     def __init__(self, sp: "ShardedParams", limit_ms: int = 5000, gather_ctas: int = 48, reduce_ctas: int = 64):
-        from .symm import SignalPad, SymmetricBuffer
+        import os
+        from .symm import SignalPad, SymmetricBuffer, tensor_from_ptr
         self.sp = sp
-        self._SymmetricBuffer = SymmetricBuffer
-        self.limit_ms, self.gather_ctas, self.reduce_ctas = limit_ms, gather_ctas, reduce_ctas
+        self._SymmetricBuffer, self._tensor_from_ptr = SymmetricBuffer, tensor_from_ptr
+        # Tuning knobs (environment): CTAs and threads per CTA of the gather / reduce kernels, "dma" to move the
+        # parameter slices with the copy engines instead of a kernel, "serial" to issue everything on the main stream.
+        self.gather_ctas = int(os.environ.get("RUSTRAL_Z3_GATHER_CTAS", gather_ctas))
+        self.reduce_ctas = int(os.environ.get("RUSTRAL_Z3_REDUCE_CTAS", reduce_ctas))
+        self.threads = int(os.environ.get("RUSTRAL_Z3_THREADS", 256))
+        self.gather_mode = os.environ.get("RUSTRAL_Z3_GATHER", "dma")
+        self.reduce_mode = os.environ.get("RUSTRAL_Z3_REDUCE", "dma")
+        self.serial = os.environ.get("RUSTRAL_Z3_SERIAL", "0") == "1"
+        if self.serial:
+            self.reduce_mode = "kernel"
+        self._stage, self._peer_grad, self._pending_sums = {}, {}, []
+        self.limit_ms = limit_ms
         dev = sp.device
         self.pad = SignalPad(sp.group, dev)
         self.slots = SymmetricBuffer(max(256, 8 * sp.world), sp.group, dev)
         self._symm = [self.pad, self.slots]
-        self.gs, self.rs = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        if self.serial:
+            self.gs = self.rs = None
+        else:
+            self.gs, self.rs = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        self._params_waited = False
         self.micro_epoch = torch.zeros(1, dtype=torch.int32, device=dev)      # advanced once per micro-batch
         self.step_epoch = torch.zeros(1, dtype=torch.int32, device=dev)       # optimizer steps completed by this rank
         self.counters = torch.zeros(8, dtype=torch.int32, device=dev)
@@ -218,6 +248,7 @@ class _PeerTransport:
         self.loss_out = torch.zeros((), dtype=torch.float32, device=dev)
         self._gather_ev, self._grad_bufs = {}, {}
         self._pending_reduce = False
+        self._pending_gather = False
         nb = len(sp.buckets)
         if (CH_BASE + 2 * nb) * sp.world > 16384:
             raise ValueError("too many buckets for the signal pad")
@@ -228,6 +259,7 @@ class _PeerTransport:
         buf = self._SymmetricBuffer(n * 2, self.sp.group, self.sp.device)
         self._symm.append(buf)
         self.lowp_buf = buf
+        self._peer_lowp = [self._tensor_from_ptr(p, n * 2, self.sp.device).view(torch.bfloat16) for p in buf.peer_ptrs]
         return buf.view(torch.bfloat16, n)
 
     def alloc_grad_buffer(self, n):
@@ -235,26 +267,52 @@ class _PeerTransport:
         self._symm.append(buf)
         t = buf.view(torch.float32, n)
         self._grad_bufs[t.data_ptr()] = buf
+        sp = self.sp
+        self._peer_grad[t.data_ptr()] = [self._tensor_from_ptr(p, n * 4, sp.device).view(torch.float32) for p in buf.peer_ptrs]
+        if self.reduce_mode == "dma":
+            # landing area for the peers' copies of this rank's slice: (world - 1) slices of the largest bucket it serves
+            self._stage[t.data_ptr()] = torch.empty((sp.world - 1) * (n // sp.world), dtype=torch.float32, device=sp.device)
         return t
 
     # -- one micro-batch -------------------------------------------------------------------------------------
     def begin_micro(self):
         N.check(N.kernels().rb_epoch_advance(self.micro_epoch.data_ptr(), N.stream_ptr()), "rb_epoch_advance")
+        self._params_waited = False
 
-    def gather(self, b: Bucket, dst: torch.Tensor):
+    def _gather_on(self, b: Bucket, dst: torch.Tensor):
         sp = self.sp
-        main = torch.cuda.current_stream(sp.device)
-        self.gs.wait_stream(main)          # the landing buffer's previous occupant has been consumed by kernels issued so far
+        if self.gather_mode == "dma":
+            # copy engines move the slices; one bounded wait per micro-batch makes sure every peer has published the
+            # parameters of the last step (the flag is per step, not per bucket)
+            if not self._params_waited:
+                N.check(N.kernels().rb_zero3_wait(self.pad.local_ptr, sp.world, CH_PARAMS, self.step_epoch.data_ptr(), 0,
+                                                  self.limit_ms, N.stream_ptr()), "rb_zero3_wait")
+                self._params_waited = True
+            n, off = b.n_per_rank, b.shard_start
+            for j in range(sp.world):
+                r = (sp.rank + 1 + j) % sp.world
+                dst[r * n:(r + 1) * n].copy_(self._peer_lowp[r][off:off + n], non_blocking=True)
+            return
         a = RbZero3Gather()
         a.lowp_ptrs_dev, a.local_pad = self.lowp_buf.ptrs_dev.data_ptr(), self.pad.local_ptr
         a.epoch_dev, a.channel = self.step_epoch.data_ptr(), CH_PARAMS
         a.shard_off, a.n_per_rank, a.dst = b.shard_start, b.n_per_rank, dst.data_ptr()
         a.world, a.rank, a.limit_ms, a.max_ctas = sp.world, sp.rank, self.limit_ms, self.gather_ctas
+        a.threads = self.threads
+        N.check(N.kernels().rb_zero3_gather(a, N.stream_ptr()), "rb_zero3_gather")
+
+    def gather(self, b: Bucket, dst: torch.Tensor):
+        if self.serial:
+            self._gather_on(b, dst)
+            return
+        main = torch.cuda.current_stream(self.sp.device)
+        self.gs.wait_stream(main)          # the landing buffer's previous occupant has been consumed by kernels issued so far
         with torch.cuda.stream(self.gs):
-            N.check(N.kernels().rb_zero3_gather(a, N.stream_ptr()), "rb_zero3_gather")
+            self._gather_on(b, dst)
             ev = torch.cuda.Event()
             ev.record(self.gs)
         self._gather_ev[b.index] = ev
+        self._pending_gather = True
 
     def wait_gather(self, b: Bucket):
         ev = self._gather_ev.pop(b.index, None)
@@ -269,10 +327,56 @@ class _PeerTransport:
         N.check(N.kernels().rb_zero3_wait(self.pad.local_ptr, self.sp.world, CH_BASE + len(self.sp.buckets) + prev[0],
                                           self.micro_epoch.data_ptr(), prev[1], self.limit_ms, N.stream_ptr()), "rb_zero3_wait")
 
-    def reduce(self, b: Bucket, buf: torch.Tensor, slot, accumulate: bool):
+    def _reduce_dma(self, b: Bucket, buf: torch.Tensor, accumulate: bool):
+        sp, lib = self.sp, N.kernels()
+        W, rank, npr = sp.world, sp.rank, b.n_per_rank
+        main = torch.cuda.current_stream(sp.device)
+        ready, consumed = CH_BASE + b.index, CH_BASE + len(sp.buckets) + b.index
+        N.check(lib.rb_zero3_signal(self.pad.ptrs_dev.data_ptr(), W, rank, ready, self.micro_epoch.data_ptr(), N.stream_ptr()),
+                "rb_zero3_signal")
+        # the fork also orders these copies behind the sum that last read this staging area (issued on the main stream)
+        self.rs.wait_stream(main)
+        stage, peers = self._stage[buf.data_ptr()], self._peer_grad[buf.data_ptr()]
+        src = [None] * W
+        with torch.cuda.stream(self.rs):
+            N.check(lib.rb_zero3_wait(self.pad.local_ptr, W, ready, self.micro_epoch.data_ptr(), 0, self.limit_ms,
+                                      N.stream_ptr()), "rb_zero3_wait")
+            for k in range(W - 1):
+                r = (rank + 1 + k) % W
+                dst = stage[k * npr:(k + 1) * npr]
+                dst.copy_(peers[r][rank * npr:(rank + 1) * npr], non_blocking=True)
+                src[r] = dst
+            N.check(lib.rb_zero3_signal(self.pad.ptrs_dev.data_ptr(), W, rank, consumed, self.micro_epoch.data_ptr(),
+                                        N.stream_ptr()), "rb_zero3_signal")
+            ev = torch.cuda.Event()
+            ev.record(self.rs)
+        src[rank] = buf[rank * npr:(rank + 1) * npr]
+        self._pending_sums.append((b, src, accumulate, ev))
+        self._pending_reduce = True
+        self._flush_sums(keep=1)
+
+    def _flush_sums(self, keep: int):
+        """Adds the pulled slices of all but the `keep` most recent buckets into the gradient shard (main stream)."""
         sp = self.sp
         main = torch.cuda.current_stream(sp.device)
-        self.rs.wait_stream(main)
+        while len(self._pending_sums) > keep:
+            b, src, accumulate, ev = self._pending_sums.pop(0)
+            main.wait_event(ev)
+            a = RbZero3Sum()
+            for i, t in enumerate(src):                                  # rank order: the sum does not depend on timing
+                a.src[i] = t.data_ptr()
+            a.dst = sp.gshard[b.shard_start:b.shard_start + b.n_per_rank].data_ptr()
+            a.n, a.num_src, a.accumulate = b.n_per_rank, sp.world, int(accumulate)
+            N.check(N.kernels().rb_zero3_sum(a, N.stream_ptr()), "rb_zero3_sum")
+
+    def reduce(self, b: Bucket, buf: torch.Tensor, slot, accumulate: bool):
+        sp = self.sp
+        if self.reduce_mode == "dma":
+            self._reduce_dma(b, buf, accumulate)
+            return
+        main = torch.cuda.current_stream(sp.device)
+        if not self.serial:
+            self.rs.wait_stream(main)
         symm = self._grad_bufs[buf.data_ptr()]
         a = RbZero3Reduce()
         a.grad_ptrs_dev, a.pad_ptrs_dev, a.local_pad = symm.ptrs_dev.data_ptr(), self.pad.ptrs_dev.data_ptr(), self.pad.local_ptr
@@ -282,13 +386,24 @@ class _PeerTransport:
         a.shard_dst = sp.gshard[b.shard_start:b.shard_start + b.n_per_rank].data_ptr()
         a.accumulate, a.counter = int(accumulate), self.counters[0:1].data_ptr()
         a.world, a.rank, a.limit_ms, a.max_ctas = sp.world, sp.rank, self.limit_ms, self.reduce_ctas
+        a.threads = self.threads
+        if self.serial:
+            N.check(N.kernels().rb_zero3_reduce(a, N.stream_ptr()), "rb_zero3_reduce")
+            return
         with torch.cuda.stream(self.rs):
             N.check(N.kernels().rb_zero3_reduce(a, N.stream_ptr()), "rb_zero3_reduce")
         self._pending_reduce = True
 
     def end_micro(self):
+        if self.serial:
+            return
         main = torch.cuda.current_stream(self.sp.device)
-        main.wait_stream(self.gs)
+        self._flush_sums(keep=0)
+        # only streams that took work in this micro-batch are joined: inside a graph capture, waiting for a stream
+        # that was never forked from the capturing stream would make the capture depend on work outside it
+        if self._pending_gather:
+            main.wait_stream(self.gs)
+            self._pending_gather = False
         if self._pending_reduce:
             main.wait_stream(self.rs)
             self._pending_reduce = False
@@ -319,6 +434,7 @@ class _PeerTransport:
         a.world, a.rank, a.limit_ms = sp.world, sp.rank, self.limit_ms
         N.check(lib.rb_zero3_publish(a, N.stream_ptr()), "rb_zero3_publish")
         N.check(lib.rb_zero3_adam(a, N.stream_ptr()), "rb_zero3_adam")
+        self._params_waited = False
         return self.loss_out
 
     def close(self):
@@ -478,7 +594,8 @@ class ShardedParams:
         lp = self.lowp_shard.element_size()
         return {"param_shard": self.shard_len * lp, "optimizer_shard": 3 * self.shard_len * 4, "grad_shard": self.shard_len * 4,
                 "param_landing": sum(t.numel() for t in self.pbuf + [self.pbuf0]) * lp,
-                "grad_landing": sum(t.numel() for t in self.gbuf + [self.gbuf0]) * 4}
+                "grad_landing": sum(t.numel() for t in self.gbuf + [self.gbuf0]) * 4,
+                "grad_staging": sum(t.numel() for t in getattr(self.transport, "_stage", {}).values()) * 4}
 
     def close(self) -> None:
         self.transport.close()

@@ -69,7 +69,7 @@ def test_zero3_trainer_can_be_closed_and_rebuilt_in_one_process():
 @pytest.mark.parametrize("comm,stage", [("nccl", 2), ("fused", 2), ("nccl", 3), ("fused", 3)])
 def test_zero_two_gpus_match_one_gpu(comm, stage):
     env = {"NCCL_NVLS_ENABLE": "0"}
-    one = _run(1, "nccl", "cuda", 29621, env)
+    one = _run(1, "nccl", "cuda", 29621, env, extra_args=["--steps", "6"])
     two = _run(2, comm, "cuda", 29622 + 2 * stage + (comm == "fused"), env, extra_args=["--zero-stage", str(stage), "--steps", "6"])
     assert two["status"] == 0
     want = {("nccl", 2): "dp2-zero2-nccl", ("fused", 2): "dp2-zero2-push", ("nccl", 3): "dp2-zero3-collective",
