@@ -170,6 +170,54 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+class WeightGradStore:
+    """Deferred weight-gradient work of `linear` layers.
+
+    Inside ``with WeightGradStore.defer() as queue:`` the backward pass of every `linear` computes only the gradient
+    of its input (the part the previous pipeline stage is waiting for); the weight and bias gradient GEMMs are pushed
+    onto `queue` and run later with ``WeightGradStore.run(queue)``, which accumulates them into ``.grad`` of the leaf
+    tensors exactly as autograd would have.  This is what the zero-bubble pipeline schedule is built from (the
+    reference only names that schedule: crates/distributed/src/pipeline_parallel.rs:55-62)."""
+    # The queue is looked up per thread first (CPU tensors: autograd runs the backward pass on the calling thread, and
+    # ranks may be threads of one process), then process-wide (CUDA tensors: autograd runs their backward functions on
+    # a worker thread of the device; one rank per process).
+    _tls = __import__("threading").local()
+    _process_queue = None
+
+    class _Defer:
+        def __enter__(self):
+            self.q = []
+            WeightGradStore._tls.queue = self.q
+            WeightGradStore._process_queue = self.q
+            return self.q
+
+        def __exit__(self, *exc):
+            WeightGradStore._tls.queue = None
+            if WeightGradStore._process_queue is self.q:       # another thread's deferral may have replaced it
+                WeightGradStore._process_queue = None
+            return False
+
+    @classmethod
+    def current(cls):
+        q = getattr(cls._tls, "queue", None)
+        return q if q is not None else cls._process_queue
+
+    @classmethod
+    def defer(cls):
+        return cls._Defer()
+
+    @staticmethod
+    def run(queue) -> None:
+        with torch.no_grad():
+            for fn in queue:
+                fn()
+        queue.clear()
+
+    @staticmethod
+    def _accumulate(leaf: torch.Tensor, g: torch.Tensor) -> None:
+        leaf.grad = g if leaf.grad is None else leaf.grad.add_(g)
+
+
 class _LinearFn(torch.autograd.Function):
     """y = act(x W^T + b) (+ residual); W is [out, in] as in the reference's Linear (crates/nn/src/linear.rs:21)."""
 
@@ -181,6 +229,8 @@ class _LinearFn(torch.autograd.Function):
         res2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
         y = gemm(x2, w, bias=bias, act=act, residual=res2, aux_out=pre, out_dtype=x.dtype)
         ctx.save_for_backward(x2, w, pre)
+        ctx.w_leaf = w if w.is_leaf else None                      # where a deferred weight gradient is accumulated
+        ctx.b_leaf = bias if (bias is not None and bias.is_leaf) else None
         ctx.act = act
         ctx.has_bias = bias is not None
         ctx.has_res = residual is not None
@@ -202,9 +252,22 @@ class _LinearFn(torch.autograd.Function):
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             dx = gemm(dz, w, b_mn=True, out_dtype=x2.dtype).reshape(ctx.x_shape)
+        queue = WeightGradStore.current()
+        want_b = ctx.has_bias and ctx.needs_input_grad[2]
+        if queue is not None and ctx.w_leaf is not None and (not want_b or ctx.b_leaf is not None):
+            w_leaf, b_leaf, want_w = ctx.w_leaf, ctx.b_leaf, ctx.needs_input_grad[1]
+
+            def later():
+                if want_w:
+                    WeightGradStore._accumulate(w_leaf, gemm(dz, x2, a_mn=True, b_mn=True, out_dtype=w_leaf.dtype))
+                if want_b:
+                    from .elementwise import sum_dim0
+                    WeightGradStore._accumulate(b_leaf, sum_dim0(dz).to(b_leaf.dtype))
+            queue.append(later)
+            return dx, None, None, None, dres
         if ctx.needs_input_grad[1]:
             dw = gemm(dz, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
-        if ctx.has_bias and ctx.needs_input_grad[2]:
+        if want_b:
             from .elementwise import sum_dim0
             db = sum_dim0(dz).to(w.dtype)
         return dx, dw, db, None, dres

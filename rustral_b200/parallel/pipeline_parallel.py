@@ -61,8 +61,12 @@ class StageSplitter:
 
 
 def pipeline_bubble_fraction(schedule: PipelineSchedule, num_stages: int, num_micro: int) -> float:
+    """Idle share of a stage's time, with forward, input-gradient and weight-gradient passes of equal length t (so one
+    micro-batch costs 3t).  GPipe and 1F1B idle for (S - 1) whole micro-batches: (S - 1) / (M + S - 1).  The zero-bubble
+    schedule sends the input gradient on before it does the weight-gradient work, which shortens the wait of each
+    earlier stage from t_F + t_B + t_W to t_F + t_B - t_W per hop: (S - 1) / (3 M + S - 1)."""
     if schedule is PipelineSchedule.ZERO_BUBBLE:
-        return 0.0
+        return (num_stages - 1) / (3 * num_micro + num_stages - 1)
     return (num_stages - 1) / (num_micro + num_stages - 1)
 
 
@@ -99,6 +103,7 @@ class PipelineParallel:
         self.act_shape, self.act_dtype, self.device = tuple(act_shape), act_dtype, torch.device(device)
         self._comm_stream = torch.cuda.Stream(self.device) if (self.device.type == "cuda" and config.async_comm) else None
         self.after_backward = None      # optional callable run after every micro-batch backward (e.g. fp32 accumulation)
+        self.deferred_weight_grads = 0  # weight-gradient jobs that ran after their input gradient had been sent on
 
     # ---- p2p ------------------------------------------------------------------------------------------------------------
     def _recv(self, src: int, tag: int) -> torch.Tensor:
@@ -139,13 +144,21 @@ class PipelineParallel:
     def _backward(self, i: int, saved: dict) -> None:
         st = self.stage
         x, out = saved.pop(i)
-        if st.is_last:
-            out.backward()
+        g = None if st.is_last else self._recv(st.stage_id + 1, 2 * i + 1)
+        if self.cfg.schedule is PipelineSchedule.ZERO_BUBBLE:
+            # input gradients first; the previous stage gets its gradient before this stage starts on the weight
+            # gradients of its linear layers, which then run while that stage already works on its own backward pass
+            from ..ops.matmul import WeightGradStore
+            with WeightGradStore.defer() as deferred:
+                out.backward(g)
+            if not st.is_first:
+                self._send(x.grad, st.stage_id - 1, 2 * i + 1)
+            self.deferred_weight_grads += len(deferred)
+            WeightGradStore.run(deferred)
         else:
-            g = self._recv(st.stage_id + 1, 2 * i + 1)
             out.backward(g)
-        if not st.is_first:
-            self._send(x.grad, st.stage_id - 1, 2 * i + 1)
+            if not st.is_first:
+                self._send(x.grad, st.stage_id - 1, 2 * i + 1)
         if self.after_backward is not None:
             self.after_backward()
 

@@ -143,11 +143,12 @@ def test_tensor_parallel_pair_matches_dense():
     assert torch.allclose(torch.cat([o[1] for o in out], 1), p, atol=1e-5)
 
 
-@pytest.mark.parametrize("schedule", ["gpipe", "1f1b"])
+@pytest.mark.parametrize("schedule", ["gpipe", "1f1b", "zero_bubble"])
 def test_pipeline_schedules_match_sequential(schedule):
     from rustral_b200.parallel.pipeline_parallel import (PipelineConfig, PipelineParallel, PipelineSchedule, PipelineStage,
                                                          StageSplitter, pipeline_bubble_fraction)
-    sched = PipelineSchedule.SIMPLE if schedule == "gpipe" else PipelineSchedule.INTERLEAVED
+    sched = {"gpipe": PipelineSchedule.SIMPLE, "1f1b": PipelineSchedule.INTERLEAVED,
+             "zero_bubble": PipelineSchedule.ZERO_BUBBLE}[schedule]
     mk = lambda: [LinearBuilder(16, 16).with_bias().seed(10 + i).build(B) for i in range(6)]
     torch.manual_seed(1)
     X, Y = [torch.randn(4, 16) for _ in range(5)], [torch.randn(4, 16) for _ in range(5)]
@@ -171,13 +172,16 @@ def test_pipeline_schedules_match_sequential(schedule):
         st = PipelineStage(r, 3, fwd, [p for l in mine for p in l.parameters()])
         pp = PipelineParallel(st, pg, PipelineConfig(5, sched), (4, 16))
         loss = pp.train_step(X if r == 0 else None, Y if r == 2 else None, (lambda o, t: ((o - t) ** 2).mean()) if r == 2 else None)
-        return loss, [p.tensor.grad.clone() for p in st.parameters]
+        return loss, [p.tensor.grad.clone() for p in st.parameters], pp.deferred_weight_grads
     out = run_ranks(3, fn)
+    # zero bubble: every linear's weight gradient (2 layers x 5 micro-batches per stage) ran after the send upstream
+    assert all(o[2] == (10 if schedule == "zero_bubble" else 0) for o in out)
     assert abs(float(out[2][0]) - tot) < 1e-6
     for r in range(3):
         want = [p.tensor.grad for l in ref[2 * r:2 * r + 2] for p in l.parameters()]
         assert all(torch.allclose(a, b, atol=1e-6) for a, b in zip(out[r][1], want))
     assert pipeline_bubble_fraction(PipelineSchedule.INTERLEAVED, 4, 8) == pytest.approx(3 / 11)
+    assert pipeline_bubble_fraction(PipelineSchedule.ZERO_BUBBLE, 4, 8) == pytest.approx(3 / 27)
     assert StageSplitter.balance_by_params([10, 10, 10, 10, 40, 40], 3) == [[0, 1, 2, 3], [4], [5]]
 
 
