@@ -7,12 +7,11 @@
 //     QK(j+1, A) S_A  = Q_A K_j+1^T
 //     PV(j, B), QK(j+1, B)
 // so while softmax warp group A turns S_A into P_A the tensor cores work for tile B and the other way round.
-// Softmax (warps 0-3 for A, 4-7 for B, one query row per thread): S is read from TMEM ONCE into registers, the
-// probabilities are written back as packed bf16 over the first 64 columns of the same S buffer, O stays in TMEM and
+// Softmax (warps 0-3 for A, 4-7 for B, one query row per thread): S is read from TMEM once into registers (the
+// producer warp group hands most of its registers to the softmax groups with setmaxnreg), the probabilities are written back as packed bf16 over the first 64 columns of the same S buffer, O stays in TMEM and
 // is only rescaled when the running row maximum moved by more than 2^8 (the stale maximum keeps the exponentials
-// bounded by 256, exact after the final division by the row sum).  A share of the exponentials is computed with a
-// polynomial on the FMA pipe, since at head dim 64 the 16 ex2 / clock / SM of the special-function unit, not the
-// tensor pipe, bound a block.  Warp 8 is the TMA producer (Q once, K / V through a ring of stages), warp 9 issues MMAs.
+// bounded by 256, exact after the final division by the row sum).  A share of the exponentials can be computed with a
+// polynomial on the FMA pipe (template parameter; off by default, see rb_attention_fwd_tc2).  Warp 8 is the TMA producer (Q once, K / V through a ring of stages), warp 9 issues MMAs.
 //
 // Same semantics as the other forward kernels (causal alignment to the end of the keys, GQA, log-sum-exp output).
 // Replaces the reference's materialised-score attention (crates/nn/src/attention.rs:640-836).
@@ -22,7 +21,7 @@
 
 namespace rb {
 
-constexpr int kF2Threads = 320;
+constexpr int kF2Threads = 384;          // warps 0-7 softmax, 8 TMA, 9 MMA, 10-11 only give their registers away
 constexpr int kF2Tile = 128;
 constexpr float kF2Log2e = 1.4426950408889634f;
 constexpr float kF2RescaleThreshold = 8.f;   // log2 units
@@ -54,6 +53,14 @@ __device__ __forceinline__ float f2_ex2_poly(float x) {
   p = fmaf(p, f, 1.0f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
+
+// Register reallocation between warp groups (four consecutive warps, all of which must execute the instruction): the
+// producer group shrinks to a few registers per thread and the softmax groups grow, so that a whole row of 128 scores
+// fits in registers.
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t* r) {
   asm volatile(
@@ -92,7 +99,7 @@ struct F2Smem {
   static constexpr int kTotal = kBar + kNumBars * 8 + 16;
 };
 
-template <int D, int kPolyEvery, bool kTwoPass>
+template <int D, int kPolyEvery>
 __global__ void __launch_bounds__(kF2Threads, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, F2Params p, unsigned int* status) {
@@ -162,6 +169,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
+  if (warp >= 8) {
+  setmaxnreg_dec<56>();
   if (warp == 8) {
     if (lane == 0) {
       // ---------------------------------------------------------------- TMA producer
@@ -233,7 +242,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (ok) umma_commit(bar_kvempty + 8 * s);               // every MMA that read stage s has been issued
       }
     }
+  }
   } else {
+    setmaxnreg_inc<224>();
     // ------------------------------------------------------------------ softmax + epilogue, one query row per thread
     const int t = warp >> 2;                                   // query tile of this warp group
     const int wq = warp & 3;                                   // TMEM lane quarter of this warp
@@ -253,42 +264,29 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int key_lim = p.causal ? min(p.seq_k - 1, q_idx + shift) : p.seq_k - 1;     // last visible key
       const bool need_mask = (k0 + kF2Tile - 1 > key_lim);
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-      // maximum over 32 scores starting at key kb (masked keys count as -inf)
-      auto chunk_max = [&](const uint32_t* v, int kb) {
-        if (need_mask) {
+      // maximum over 32 scores (masked keys have been set to -inf)
+      auto chunk_max = [&](const uint32_t* v) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, kb + i <= key_lim ? __uint_as_float(v[i]) : -INFINITY);
-            mx1 = fmaxf(mx1, kb + i + 1 <= key_lim ? __uint_as_float(v[i + 1]) : -INFINITY);
-            mx2 = fmaxf(mx2, kb + i + 2 <= key_lim ? __uint_as_float(v[i + 2]) : -INFINITY);
-            mx3 = fmaxf(mx3, kb + i + 3 <= key_lim ? __uint_as_float(v[i + 3]) : -INFINITY);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, __uint_as_float(v[i]));
-            mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
-            mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
-          }
+        for (int i = 0; i < 32; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(v[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
         }
       };
-      uint32_t r[kTwoPass ? 64 : 128];               // two passes: a double buffer of 32-column chunks
-      if constexpr (kTwoPass) {
-        tmem_ld_32x32_ptr(tmem_s, r);
+      // the whole row of 128 scores is read from TMEM once and stays in registers (224 per thread after the
+      // reallocation above)
+      uint32_t r[128];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld_wait();
-          if (c < 3) tmem_ld_32x32_ptr(tmem_s + (c + 1) * 32, r + ((c + 1) & 1) * 32);   // next chunk in flight
-          chunk_max(r + (c & 1) * 32, k0 + c * 32);
-        }
-      } else {
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32_ptr(tmem_s + c * 32, r + c * 32);
+      tmem_ld_wait();
+      if (need_mask) {                               // only blocks that cross the causal diagonal or the end of the keys
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld_32x32_ptr(tmem_s + c * 32, r + c * 32);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 4; ++c) chunk_max(r + c * 32, k0 + c * 32);
+        for (int i = 0; i < 128; ++i)
+          if (k0 + i > key_lim) r[i] = 0xff800000u;   // -inf: ignored by the maximum, exp2 gives exactly 0
       }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) chunk_max(r + c * 32);
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       // Keep the old maximum unless the new one is more than 2^threshold larger: exponentials stay <= 2^threshold.
       const bool grow = (mx > m_run) && ((mx - m_run) * sl2 > kF2RescaleThreshold || m_run == -INFINITY);
@@ -331,7 +329,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             p0 = f2_ex2(x0);
             p1 = f2_ex2(x1);
           }
-          if (need_mask) {
+          if (kPolyEvery > 0 && need_mask) {           // the polynomial clamps its argument: zero masked keys explicitly
             if (kb + 2 * ii > key_lim) p0 = 0.f;
             if (kb + 2 * ii + 1 > key_lim) p1 = 0.f;
           }
@@ -340,24 +338,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           packed[ii] = pack_bf16x2(p0, p1);
         }
       };
-      if constexpr (kTwoPass) {
-        tmem_ld_32x32_ptr(tmem_s, r);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld_wait();
-          if (c < 3) tmem_ld_32x32_ptr(tmem_s + (c + 1) * 32, r + ((c + 1) & 1) * 32);
-          uint32_t packed[16];
-          chunk_exp(r + (c & 1) * 32, k0 + c * 32, c, packed);
-          // columns [16c, 16c + 16) lie inside score chunks that are already in registers
-          tmem_st_32x16(tmem_s + c * 16, packed);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t packed[16];
-          chunk_exp(r + c * 32, k0 + c * 32, c, packed);
-          tmem_st_32x16(tmem_s + c * 16, packed);
-        }
+      for (int c = 0; c < 4; ++c) {
+        uint32_t packed[16];
+        chunk_exp(r + c * 32, k0 + c * 32, c, packed);
+        // columns [16c, 16c + 16) of the score buffer: every score is already in registers
+        tmem_st_32x16(tmem_s + c * 16, packed);
       }
       l_run += rs0 + rs1;
       tmem_st_wait();
@@ -417,10 +403,10 @@ const CUtensorMap* f2_make_map(const void* base, const long long* strides, int s
   return rbhost::get_tmap_4d(base, 2, dims, str, box, 1, err);
 }
 
-template <int D, int P, bool TWO>
+template <int D, int P>
 int f2_launch(const CUtensorMap* tq, const CUtensorMap* tk, const CUtensorMap* tv, const rb::F2Params& p, dim3 grid,
               cudaStream_t stream) {
-  auto kern = rb::attn_fwd2_kernel<D, P, TWO>;
+  auto kern = rb::attn_fwd2_kernel<D, P>;
   const int smem = rb::F2Smem<D>::kTotal + 1024;
   static bool cfg_dev[64] = {false};
   bool& cfg = cfg_dev[rbhost::device_slot()];
@@ -435,7 +421,8 @@ int f2_launch(const CUtensorMap* tq, const CUtensorMap* tk, const CUtensorMap* t
 }  // namespace
 
 // Forward pass with two query tiles per CTA.  `poly_every`: 0 = every exponential on the special-function unit,
-// k = 2, 3, 4 = every k-th pair of keys on the FMA-pipe polynomial.  Returns -9 for problems this kernel does not
+// 4 = every fourth pair of keys on the FMA-pipe polynomial (measured slower on B200 at both head dims: 218 us against
+// 191 us for batch 32 x 12 heads x 1024 x 64; kept for parts whose special-function unit is the limit).  Returns -9 for problems this kernel does not
 // take (the caller then uses another forward kernel).
 RB_API int rb_attention_fwd_tc2(const RbAttnArgs* a, int poly_every, void* stream_v) {
   if (a->batch <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->heads % a->kv_heads) return -1;
@@ -466,22 +453,16 @@ RB_API int rb_attention_fwd_tc2(const RbAttnArgs* a, int poly_every, void* strea
   p.scale = a->scale;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   dim3 grid((a->seq_q + 2 * rb::kF2Tile - 1) / (2 * rb::kF2Tile), a->heads, a->batch);
-  const bool two = (poly_every & 16) != 0;      // bit 4: read the scores from TMEM twice (fewer registers)
-  const int pe = poly_every & 15;
-#define RB_F2(DD, PP) (two ? f2_launch<DD, PP, true>(tq, tk, tv, p, grid, stream) : f2_launch<DD, PP, false>(tq, tk, tv, p, grid, stream))
   if (a->head_dim == 64) {
-    switch (pe) {
-      case 0: return RB_F2(64, 0);
-      case 2: return RB_F2(64, 2);
-      case 3: return RB_F2(64, 3);
-      case 4: return RB_F2(64, 4);
+    switch (poly_every) {
+      case 0: return f2_launch<64, 0>(tq, tk, tv, p, grid, stream);
+      case 4: return f2_launch<64, 4>(tq, tk, tv, p, grid, stream);
       default: return -1;
     }
   }
-  switch (pe) {
-    case 0: return RB_F2(128, 0);
-    case 4: return RB_F2(128, 4);
+  switch (poly_every) {
+    case 0: return f2_launch<128, 0>(tq, tk, tv, p, grid, stream);
+    case 4: return f2_launch<128, 4>(tq, tk, tv, p, grid, stream);
     default: return -1;
   }
-#undef RB_F2
 }

@@ -1,7 +1,7 @@
 """Micro-benchmarks of single kernels with roofline fractions.
 
     python -m rustral_b200.bench.kernels gemm --m 32768 --n 2304 --k 768 [--act gelu] [--iters 10]
-    python -m rustral_b200.bench.kernels attention --batch 32 --seq 1024 --heads 12 --head-dim 64 [--impl tc|mma] [--backward]
+    python -m rustral_b200.bench.kernels attention --batch 32 --seq 1024 --heads 12 --head-dim 64 [--impl tc2|tc|mma] [--backward]
     python -m rustral_b200.bench.kernels norm --rows 32768 --n 768
     python -m rustral_b200.bench.kernels adam --numel 124000000
 
@@ -160,7 +160,7 @@ def main(argv=None):
     t.add_argument("--heads", type=int, default=12)
     t.add_argument("--kv-heads", type=int, default=0)
     t.add_argument("--head-dim", type=int, default=64)
-    t.add_argument("--impl", default="tc", choices=["tc", "mma"])
+    t.add_argument("--impl", default="tc2", help="tc2 (two query tiles per CTA; tc2:<n> picks a variant), tc (one tile per CTA) or mma")
     t.add_argument("--no-causal", dest="causal", action="store_false")
     t.add_argument("--backward", action="store_true")
     n = sub.add_parser("norm")

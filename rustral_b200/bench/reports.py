@@ -1,0 +1,353 @@
+"""Benchmark orchestration and reporting around the schema-v2 harness documents of `rustral_b200.bench`.
+
+    python -m rustral_b200.bench.reports run-all --suite cpu --suite torch-cpu --repeats 5 --out results/
+    python -m rustral_b200.bench.reports compare --harness results/<stamp>.json --runs runs/v0.1.0 --out report.md
+    python -m rustral_b200.bench.reports index --runs-dir runs [--check]
+    python -m rustral_b200.bench.reports bmf combined.json bmf.json
+    python -m rustral_b200.bench.reports emnlp --harness combined.json --runs runs/v0.1.0 --out emnlp_report.md
+
+What each sub-command does, and the script of the reference whose job it takes over:
+
+* run-all   runs one or more suites (this framework on CPU / on the B200, plain PyTorch on CPU / CUDA as the
+            comparison arm) over the shared workload list, merges the per-suite documents into one combined document
+            and writes it with a Markdown summary (scripts/bench/run_all.py:1-314; the JAX / TensorFlow /
+            ONNX-Runtime suites of the reference are not offered: those packages are not part of this installation);
+* compare   a comparative Markdown report: per-workload table across suites with the speed-up against a chosen
+            baseline suite, and the NLP task aggregates (mean +- std over seeds) of this framework next to the PyTorch
+            twins (scripts/bench/comparative_report.py);
+* index     regenerates `INDEX.md` from every `<runs-dir>/<version>/manifest.json`, or with --check fails when the
+            file on disk is stale (scripts/bench/regen_index.py);
+* bmf       converts a combined document into Bencher Metric Format: `<suite>/<backend>/<device>/<name>` ->
+            latency in ns with lower / upper values (scripts/bench/to_bencher_bmf.py);
+* emnlp     the paper-style experiment report: environment, micro-benchmark tables per suite, NLP tables
+            (scripts/bench/build_emnlp_report.py).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+import time
+from pathlib import Path
+
+from . import SCHEMA_VERSION, Sample, ci95_mean_ms, machine_info, samples_to_json, time_runs, validate_schema
+
+SUITES = ("cpu", "b200", "torch-cpu", "torch-cuda")
+
+
+# ------------------------------------------------------------------------------------------------- plain-PyTorch suite
+def _torch_workloads(device: str, heavy: bool) -> list:
+    """The comparison arm: the workloads of `workloads.build_workloads` (same names and shapes) written with stock
+    torch modules only."""
+    import torch
+    import torch.nn.functional as F
+    dev = torch.device(device)
+    g = torch.Generator().manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, generator=g).to(dev)
+    out = []
+    for n in (128, 256, 512):
+        a, b = rnd(n, n), rnd(n, n)
+        out.append((f"matmul.{n}x{n}x{n}", {"m": n, "k": n, "n": n}, lambda a=a, b=b: a @ b, 0))
+    for r, c in ((32, 64), (32, 256), (64, 1024)):
+        x = rnd(r, c)
+        out.append((f"softmax_dim.{r}x{c}", {"rows": r, "cols": c}, lambda x=x: torch.softmax(x, -1), 0))
+    for b_, i, o in ((32, 256, 1024), (32, 1024, 256)):
+        lin = torch.nn.Linear(i, o).to(dev)
+        x = rnd(b_, i)
+        out.append((f"fused_linear_bias_gelu.{b_}x{i}->{o}", {"batch": b_, "in": i, "out": o},
+                    lambda lin=lin, x=x: F.gelu(lin(x), approximate="tanh"), sum(p.numel() for p in lin.parameters())))
+    for name, d, h, s_ in (("attention.small", 64, 4, 32), ("attention.medium", 256, 8, 128)):
+        q, k, v = (rnd(1, h, s_, d // h) for _ in range(3))
+        out.append((name, {"d_model": d, "heads": h, "seq": s_, "head_dim": d // h},
+                    lambda q=q, k=k, v=v: F.scaled_dot_product_attention(q, k, v), 0))
+    for name, c, hw, o in (("conv2d.small", 1, 28, 8), ("conv2d.medium", 3, 64, 16), ("conv2d.large", 3, 224, 32)):
+        conv = torch.nn.Conv2d(c, o, 3).to(dev)
+        x = rnd(4, c, hw, hw)
+        out.append((name, {"channels": c, "hw": hw, "out": o}, lambda conv=conv, x=x: conv(x), sum(p.numel() for p in conv.parameters())))
+    for name, hsz, steps in (("lstm_forward.small", 128, 10), ("lstm_forward.medium", 256, 50), ("lstm_forward.large", 512, 100)):
+        lstm = torch.nn.LSTM(hsz, hsz).to(dev)
+        xs = rnd(steps, 1, hsz)
+        out.append((name, {"hidden": hsz, "steps": steps}, lambda lstm=lstm, xs=xs: lstm(xs), sum(p.numel() for p in lstm.parameters())))
+    mlp = torch.nn.Sequential(torch.nn.Linear(128, 256), torch.nn.ReLU(), torch.nn.Linear(256, 64)).to(dev)
+    opt = torch.optim.Adam(mlp.parameters(), lr=1e-3)
+    xb, yb = rnd(32, 128), rnd(32, 64)
+
+    def mlp_step():
+        opt.zero_grad(set_to_none=True)
+        loss = ((mlp(xb) - yb) ** 2).mean()
+        loss.backward()
+        opt.step()
+    out.append(("mlp_train_step", {"batch": 32, "dims": [128, 256, 64]}, mlp_step, sum(p.numel() for p in mlp.parameters())))
+    n_opt = 100_000_000 if heavy else 10_000_000
+    slabs = [torch.nn.Parameter(torch.zeros(n_opt // 8, device=dev)) for _ in range(8)]
+    for p_ in slabs:
+        p_.grad = torch.ones_like(p_)
+    sgd, adam = torch.optim.SGD(slabs, lr=0.01), torch.optim.Adam(slabs, lr=1e-3)
+    out.append(("optimizer_step.sgd", {"params": n_opt}, lambda: sgd.step(), n_opt))
+    out.append(("optimizer_step.adam", {"params": n_opt}, lambda: adam.step(), n_opt))
+    layer = torch.nn.TransformerEncoderLayer(128, 4, 512, dropout=0.0, activation="gelu", batch_first=True, norm_first=True)
+    enc = torch.nn.TransformerEncoder(layer, 2, enable_nested_tensor=False).to(dev)
+    emb = torch.nn.Embedding(1024, 128).to(dev)
+    ids = torch.randint(0, 1024, (1, 128), generator=g).to(dev)
+    out.append(("transformer_encoder.forward", {"layers": 2, "d_model": 128, "heads": 4, "ffn": 512, "seq": 128, "vocab": 1024},
+                lambda: enc(emb(ids)), sum(p.numel() for p in enc.parameters()) + emb.weight.numel()))
+    return out
+
+
+def run_torch_suite(device: str, repeats: int, warmup: int, heavy: bool = False) -> dict:
+    import torch
+    samples = []
+    for name, params, fn, nparams in _torch_workloads(device, heavy):
+        if name == "mlp_train_step" or name.startswith("optimizer_step"):
+            runs = time_runs(fn, warmup, repeats, cuda=(device != "cpu"))
+        else:
+            with torch.no_grad():
+                runs = time_runs(fn, warmup, repeats, cuda=(device != "cpu"))
+        samples.append(Sample(name, "pytorch", device if device == "cpu" else "cuda", "f32", nparams, params, runs))
+    return json.loads(samples_to_json(samples, suite="torch-" + ("cpu" if device == "cpu" else "cuda")))
+
+
+def run_suite(suite: str, repeats: int, warmup: int, heavy: bool = False) -> dict | None:
+    """One suite's schema-v2 document, or None when the suite cannot run here (no GPU for the CUDA suites)."""
+    import torch
+    if suite in ("b200", "torch-cuda") and not torch.cuda.is_available():
+        return None
+    if suite in ("cpu", "b200"):
+        from . import workloads
+        doc = json.loads(workloads.run("cpu" if suite == "cpu" else "cuda", repeats, warmup, heavy))
+        doc["suite"] = "rustral-b200-" + ("cpu" if suite == "cpu" else "b200")
+        return doc
+    if suite in ("torch-cpu", "torch-cuda"):
+        return run_torch_suite("cpu" if suite == "torch-cpu" else "cuda", repeats, warmup, heavy)
+    raise ValueError(f"unknown suite {suite!r}; choose from {SUITES}")
+
+
+def combine(docs: list) -> dict:
+    """Merges suite documents into one combined document: the samples carry their suite name."""
+    samples = []
+    for d in docs:
+        for s in d["samples"]:
+            samples.append(dict(s, suite=d["suite"]))
+    return {"schema_version": SCHEMA_VERSION, "suite": "combined", "suites": [d["suite"] for d in docs],
+            "machine": docs[0]["machine"] if docs else machine_info(), "samples": samples}
+
+
+def _key(s: dict) -> str:
+    return s["name"]
+
+
+def summary_markdown(doc: dict, baseline_suite: str | None = None) -> str:
+    """Per-workload table: one column per suite (mean ms +- 95 % CI), optional speed-up against `baseline_suite`."""
+    suites = list(dict.fromkeys(s.get("suite", doc.get("suite", "?")) for s in doc["samples"]))
+    rows: dict = {}
+    for s in doc["samples"]:
+        rows.setdefault(_key(s), {})[s.get("suite", doc.get("suite", "?"))] = s
+    head = ["workload"] + suites + ([f"speed-up vs {baseline_suite}"] if baseline_suite else [])
+    lines = ["| " + " | ".join(head) + " |", "|" + "---|" * len(head)]
+    for k, by in rows.items():
+        cells = [k]
+        for su in suites:
+            s = by.get(su)
+            if s is None:
+                cells.append("-")
+                continue
+            ci = s.get("ci95_ms")
+            cells.append(f"{s['mean_ms']:.4f}" + (f" +- {ci:.4f}" if ci else ""))
+        if baseline_suite:
+            base = by.get(baseline_suite)
+            best = [by[su]["mean_ms"] for su in suites if su != baseline_suite and su in by]
+            cells.append(f"{base['mean_ms'] / min(best):.2f}x" if base and best and min(best) > 0 else "-")
+        lines.append("| " + " | ".join(cells) + " |")
+    return "\n".join(lines) + "\n"
+
+
+def cmd_run_all(a) -> int:
+    docs = []
+    for su in a.suite or ["cpu", "torch-cpu"]:
+        d = run_suite(su, a.repeats, a.warmup, a.heavy)
+        if d is None:
+            print(f"suite {su}: skipped (needs a CUDA device)", file=sys.stderr)
+            continue
+        errs = validate_schema(d)
+        if errs:
+            raise SystemExit(f"suite {su} produced an invalid document: {errs}")
+        docs.append(d)
+    if not docs:
+        raise SystemExit("no suite could run")
+    doc = combine(docs)
+    out = Path(a.out)
+    out.mkdir(parents=True, exist_ok=True)
+    stamp = time.strftime("%Y%m%d_%H%M%S")
+    (out / f"{stamp}.json").write_text(json.dumps(doc, indent=1))
+    (out / "summary.md").write_text(f"# Benchmark summary ({stamp})\n\n" + summary_markdown(doc, a.baseline))
+    print(out / f"{stamp}.json")
+    return 0
+
+
+# ------------------------------------------------------------------------------------------------- comparative report
+def _mean_std(xs: list) -> tuple:
+    if not xs:
+        return float("nan"), float("nan")
+    return (float(xs[0]), 0.0) if len(xs) == 1 else (statistics.mean(xs), statistics.stdev(xs))
+
+
+def _pm(m: float, s: float, nd: int = 4) -> str:
+    if m != m:
+        return "n/a"
+    return f"{m:.{nd}f}" if not s or s != s else f"{m:.{nd}f} +- {s:.{nd}f}"
+
+
+def nlp_section(title: str, ours: Path, twin: Path, metric: str) -> str:
+    """Mean +- std over seeds of `metric` and of the training throughput for this framework and its PyTorch twin
+    (curated documents written by `bench.manifest.curate`)."""
+    lines = [f"## {title}", ""]
+    for label, path in (("this framework", ours), ("PyTorch twin", twin)):
+        if path is None or not path.exists():
+            lines.append(f"*{label}: no curated file at `{path}`*")
+            continue
+        doc = json.loads(path.read_text())
+        runs = doc.get("runs", [])
+        vals = [r[metric] for r in runs if isinstance(r.get(metric), (int, float))]
+        thr = [r["throughput"] for r in runs if isinstance(r.get("throughput"), (int, float))]
+        lines.append(f"* {label}: {metric} {_pm(*_mean_std(vals))} over {len(vals)} seed(s); "
+                     f"throughput {_pm(*_mean_std(thr), nd=1)} per second")
+    return "\n".join(lines) + "\n"
+
+
+def cmd_compare(a) -> int:
+    parts = [f"# Comparative report ({time.strftime('%Y-%m-%d')})", ""]
+    if a.harness:
+        docs = [json.loads(Path(p).read_text()) for p in a.harness]
+        merged = docs[0] if len(docs) == 1 and docs[0].get("suite") == "combined" else combine(
+            [d for d in docs if d.get("suite") != "combined"] or docs)
+        m = merged.get("machine", {})
+        parts += ["## Micro-benchmarks", "", f"Machine: {m.get('os', '?')} / {m.get('cpu', '?')} / {m.get('gpu', 'no GPU')}", "",
+                  summary_markdown(merged, a.baseline)]
+    if a.runs:
+        base = Path(a.runs)
+        parts.append(nlp_section("SST-2 classifier (dev accuracy)", base / "nlp" / "sst2.json", base / "nlp" / "sst2_pytorch.json", "accuracy"))
+        parts.append(nlp_section("WikiText-2 word LM (dev perplexity)", base / "nlp" / "wikitext2.json",
+                                 base / "nlp" / "wikitext2_pytorch.json", "perplexity"))
+    text = "\n".join(parts)
+    if a.out:
+        Path(a.out).parent.mkdir(parents=True, exist_ok=True)
+        Path(a.out).write_text(text)
+    else:
+        print(text)
+    return 0
+
+
+def cmd_emnlp(a) -> int:
+    """The experiment report: environment block, one micro-benchmark table per suite, the NLP aggregates."""
+    parts = ["# Experiments report", "", "## Environment", ""]
+    docs = [json.loads(Path(p).read_text()) for p in (a.harness or [])]
+    m = (docs[0].get("machine") if docs else None) or machine_info()
+    parts += [f"* {k}: {v}" for k, v in m.items()] + [""]
+    for d in docs:
+        for su in (d.get("suites") or [d.get("suite")]):
+            rows = [s for s in d["samples"] if s.get("suite", d.get("suite")) == su]
+            if not rows:
+                continue
+            parts += [f"## Micro-benchmarks: {su}", "", "| workload | mean ms | 95 % CI | min ms | runs |", "|---|---|---|---|---|"]
+            for s in rows:
+                ci = s.get("ci95_ms")
+                parts.append(f"| {_key(s)} | {s['mean_ms']:.4f} | {ci:.4f} | {s.get('min_ms', float('nan')):.4f} | {len(s['runs_ms'])} |"
+                             if ci else f"| {_key(s)} | {s['mean_ms']:.4f} | - | {s.get('min_ms', float('nan')):.4f} | {len(s['runs_ms'])} |")
+            parts.append("")
+    if a.runs:
+        base = Path(a.runs)
+        parts.append(nlp_section("SST-2", base / "nlp" / "sst2.json", base / "nlp" / "sst2_pytorch.json", "accuracy"))
+        parts.append(nlp_section("WikiText-2", base / "nlp" / "wikitext2.json", base / "nlp" / "wikitext2_pytorch.json", "perplexity"))
+    Path(a.out).parent.mkdir(parents=True, exist_ok=True)
+    Path(a.out).write_text("\n".join(parts))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------------- release index
+INDEX_BOUNDARY = "## Index"
+_REQUIRED = ("version", "git_sha", "date")
+
+
+def index_table(runs_dir: Path) -> str:
+    rows = []
+    for mf in sorted(runs_dir.glob("*/manifest.json")):
+        doc = json.loads(mf.read_text())
+        missing = [k for k in _REQUIRED if k not in doc]
+        if missing:
+            raise ValueError(f"{mf}: missing keys {missing}")
+        suites = sorted(p.stem for p in mf.parent.glob("*.json") if p.name != "manifest.json")
+        rows.append((doc["version"], doc["date"], doc["git_sha"][:12], doc.get("machine", "?"), ", ".join(suites) or "-"))
+    lines = ["| version | date | git sha | machine | suites |", "|---|---|---|---|---|"]
+    lines += ["| " + " | ".join(r) + " |" for r in rows]
+    return "\n".join(lines) + "\n"
+
+
+def cmd_index(a) -> int:
+    runs = Path(a.runs_dir)
+    index = runs / "INDEX.md"
+    head = index.read_text().split(INDEX_BOUNDARY)[0] if index.exists() else "# Benchmark snapshots\n\n"
+    want = head + INDEX_BOUNDARY + "\n\n" + index_table(runs)
+    if a.check:
+        if not index.exists() or index.read_text() != want:
+            print(f"{index} is stale: run `python -m rustral_b200.bench.reports index --runs-dir {runs}`", file=sys.stderr)
+            return 1
+        return 0
+    index.write_text(want)
+    return 0
+
+
+# ------------------------------------------------------------------------------------------------- Bencher Metric Format
+def to_bmf(doc: dict) -> dict:
+    out = {}
+    for s in doc["samples"]:
+        name = "/".join([s.get("suite", doc.get("suite", "?")), s["backend"], s["device"], _key(s)])
+        runs = s["runs_ms"]
+        out[name] = {"latency": {"value": statistics.mean(runs) * 1e6, "lower_value": min(runs) * 1e6, "upper_value": max(runs) * 1e6}}
+    return out
+
+
+def cmd_bmf(a) -> int:
+    src = sys.stdin.read() if a.input == "-" else Path(a.input).read_text()
+    Path(a.output).write_text(json.dumps(to_bmf(json.loads(src)), indent=1))
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="rustral_b200.bench.reports")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("run-all")
+    p.add_argument("--suite", action="append", choices=SUITES)
+    p.add_argument("--repeats", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--heavy", action="store_true")
+    p.add_argument("--baseline", default=None, help="suite the speed-up column is computed against")
+    p.add_argument("--out", default="benchmarks/results")
+    p.set_defaults(fn=cmd_run_all)
+    p = sub.add_parser("compare")
+    p.add_argument("--harness", action="append")
+    p.add_argument("--runs", default=None, help="a snapshot directory with nlp/<task>.json and nlp/<task>_pytorch.json")
+    p.add_argument("--baseline", default=None)
+    p.add_argument("--out", default=None)
+    p.set_defaults(fn=cmd_compare)
+    p = sub.add_parser("emnlp")
+    p.add_argument("--harness", action="append")
+    p.add_argument("--runs", default=None)
+    p.add_argument("--out", required=True)
+    p.set_defaults(fn=cmd_emnlp)
+    p = sub.add_parser("index")
+    p.add_argument("--runs-dir", required=True)
+    p.add_argument("--check", action="store_true")
+    p.set_defaults(fn=cmd_index)
+    p = sub.add_parser("bmf")
+    p.add_argument("input")
+    p.add_argument("output")
+    p.set_defaults(fn=cmd_bmf)
+    a = ap.parse_args(argv)
+    return a.fn(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -257,8 +257,6 @@ class FusedGPTEngine:
         # CUDA-graph replay of the micro-batch forward + backward (about 380 launches): RUSTRAL_TRAIN_GRAPHS=0 disables it
         self.use_graphs = self.device.type == "cuda" and os.environ.get("RUSTRAL_TRAIN_GRAPHS", "1") != "0"
         self._fb_graphs: dict = {}
-        # rows per chunk of the head / loss / head-input-gradient sequence (0: whole micro-batch at once)
-        self.head_chunk_rows = int(os.environ.get("RUSTRAL_HEAD_CHUNK", "0"))
         self.grad_norm_sq = torch.zeros((), dtype=torch.float32, device=self.device)
         self.grad_norm = torch.zeros((), dtype=torch.float32, device=self.device)
         self.kernel_launches = 0
@@ -282,7 +280,7 @@ class FusedGPTEngine:
             layers.append(L)
         acts = dict(layers=layers, xf_in=e(T, d), xf=e(T, d), rstdf=e(T, dtype=torch.float32),
                     meanf=e(T, dtype=torch.float32), logits=e(T, cfg.vocab_padded),
-                    row_loss=e(T, dtype=torch.float32), dxf=e(T, d))
+                    row_loss=e(T, dtype=torch.float32))
         self._acts, self._acts_tokens = acts, T
         return acts
 
@@ -361,37 +359,15 @@ class FusedGPTEngine:
         fresh = first_micro or P.per_micro_reduce
         acc = not fresh
         head_name = "tok_embed.embed" if cfg.tie_embeddings else "head.weight"
-        R = self.head_chunk_rows
-        if R and 0 < R < T and T % R == 0 and self.device.type == "cuda":
-            # Head, loss and the input gradient of the head in row chunks small enough for a chunk of logits to stay
-            # in the L2 cache from the GEMM that writes it, through the loss kernel that turns it into its gradient,
-            # to the GEMM that reads the gradient: the logits cross HBM once (written back as gradients for the
-            # weight-gradient GEMM below) instead of five times.
-            self.forward(ids, want_logits=False)
-            A = self._acts
-            logits = A["logits"]
-            loss_rows = A["row_loss"]
-            dxf = A["dxf"]
-            tflat = targets.reshape(-1)
-            for r0 in range(0, T, R):
-                lg = logits[r0:r0 + R]
-                gemm(A["xf"][r0:r0 + R], P.w(head_name), out=lg)
-                ops.cross_entropy_fwd_bwd(lg, tflat[r0:r0 + R], cfg.vocab_size, grad_scale, dlogits=lg,
-                                          loss_out=loss_rows[r0:r0 + R])
-                gemm(lg, P.w(head_name), b_mn=True, out=dxf[r0:r0 + R])
-            dlogits = logits
-        else:
-            logits = self.forward(ids)
-            A = self._acts
-            loss_rows, _, dlogits = ops.cross_entropy_fwd_bwd(logits, targets.reshape(-1), cfg.vocab_size, grad_scale,
-                                                              dlogits=logits)
-            dxf = None
+        logits = self.forward(ids)
+        A = self._acts
+        loss_rows, _, dlogits = ops.cross_entropy_fwd_bwd(logits, targets.reshape(-1), cfg.vocab_size, grad_scale,
+                                                          dlogits=logits)
         ops.binary("add", self.loss_acc.view(1), ops.sum_all(loss_rows).view(1), out=self.loss_acc.view(1))
 
         P.begin_grads(0)
         gemm(dlogits, A["xf"], a_mn=True, b_mn=True, out=P.g(head_name), accumulate=acc)
-        if dxf is None:
-            dxf = gemm(dlogits, P.w(head_name), b_mn=True, out_dtype=self.act_dtype)
+        dxf = gemm(dlogits, P.w(head_name), b_mn=True, out_dtype=self.act_dtype)
         dx, _, _ = norm_ops.norm_backward(dxf, A["xf_in"], P.w("final_norm.weight"), A["meanf"], A["rstdf"], rms,
                                           dgamma=P.g("final_norm.weight"),
                                           dbeta=None if rms else P.g("final_norm.bias"), accumulate=acc)

@@ -1,0 +1,79 @@
+"""Report tooling around the benchmark harness documents (rustral_b200/bench/reports.py)."""
+import json
+
+import pytest
+
+from rustral_b200.bench import Sample, samples_to_json, validate_schema
+from rustral_b200.bench import reports as R
+
+
+def _doc(suite, scale):
+    samples = [Sample("matmul.128x128x128", "b", "cpu", "f32", None, {"m": 128}, [1.0 * scale, 1.2 * scale, 1.1 * scale]),
+               Sample("softmax_dim.32x64", "b", "cpu", "f32", None, {"rows": 32}, [0.5 * scale, 0.5 * scale])]
+    d = json.loads(samples_to_json(samples, suite=suite))
+    assert validate_schema(d) == []
+    return d
+
+
+def test_combine_and_summary_speedup_column():
+    ours, base = _doc("rustral-b200-cpu", 1.0), _doc("torch-cpu", 2.0)
+    doc = R.combine([ours, base])
+    assert doc["suites"] == ["rustral-b200-cpu", "torch-cpu"] and len(doc["samples"]) == 4
+    md = R.summary_markdown(doc, "torch-cpu")
+    row = [l for l in md.splitlines() if l.startswith("| matmul")][0]
+    assert "2.00x" in row and "1.1000" in row and "2.2000" in row      # baseline mean / our mean
+    assert "speed-up vs torch-cpu" in md.splitlines()[0]
+
+
+def test_bmf_export_names_and_units():
+    bmf = R.to_bmf(R.combine([_doc("suiteA", 1.0)]))
+    k = "suiteA/b/cpu/matmul.128x128x128"
+    assert k in bmf
+    lat = bmf[k]["latency"]
+    assert lat["lower_value"] == pytest.approx(1.0e6) and lat["upper_value"] == pytest.approx(1.2e6)
+    assert lat["value"] == pytest.approx(1.1e6)
+
+
+def test_index_regeneration_and_stale_check(tmp_path):
+    for v, sha in (("v0.1.0", "a" * 40), ("v0.2.0", "b" * 40)):
+        d = tmp_path / v
+        d.mkdir()
+        (d / "manifest.json").write_text(json.dumps({"version": v, "git_sha": sha, "date": "2026-01-01", "machine": "b200"}))
+        (d / "cpu.json").write_text("{}")
+    (tmp_path / "INDEX.md").write_text("# Snapshots\n\nhand-written introduction\n\n## Index\n\nold table\n")
+    assert R.main(["index", "--runs-dir", str(tmp_path), "--check"]) == 1          # stale
+    assert R.main(["index", "--runs-dir", str(tmp_path)]) == 0
+    text = (tmp_path / "INDEX.md").read_text()
+    assert "hand-written introduction" in text and "| v0.2.0 | 2026-01-01 | bbbbbbbbbbbb | b200 | cpu |" in text
+    assert R.main(["index", "--runs-dir", str(tmp_path), "--check"]) == 0
+    (tmp_path / "v0.2.0" / "manifest.json").write_text(json.dumps({"version": "v0.2.0"}))
+    with pytest.raises(ValueError, match="missing keys"):
+        R.index_table(tmp_path)
+
+
+def test_compare_and_emnlp_reports(tmp_path):
+    h = tmp_path / "h.json"
+    h.write_text(json.dumps(R.combine([_doc("rustral-b200-cpu", 1.0), _doc("torch-cpu", 3.0)])))
+    nlp = tmp_path / "runs" / "nlp"
+    nlp.mkdir(parents=True)
+    (nlp / "sst2.json").write_text(json.dumps({"runs": [{"accuracy": 0.5, "throughput": 100.0}, {"accuracy": 0.7, "throughput": 120.0}]}))
+    (nlp / "sst2_pytorch.json").write_text(json.dumps({"runs": [{"accuracy": 0.6, "throughput": 80.0}]}))
+    out = tmp_path / "cmp.md"
+    assert R.main(["compare", "--harness", str(h), "--runs", str(tmp_path / "runs"), "--baseline", "torch-cpu", "--out", str(out)]) == 0
+    text = out.read_text()
+    assert "3.00x" in text and "accuracy 0.6000 +- 0.1414 over 2 seed(s)" in text and "PyTorch twin: accuracy 0.6000 over 1" in text
+    assert "no curated file" in text                                    # the WikiText-2 files are absent
+    out2 = tmp_path / "emnlp.md"
+    assert R.main(["emnlp", "--harness", str(h), "--runs", str(tmp_path / "runs"), "--out", str(out2)]) == 0
+    t2 = out2.read_text()
+    assert "## Micro-benchmarks: torch-cpu" in t2 and "## Environment" in t2
+
+
+def test_torch_suite_mirrors_the_framework_workload_names():
+    import torch
+    from rustral_b200.bench import workloads
+    from rustral_b200.core import CpuBackend
+    ours = {n for n, _, _ in workloads.build_workloads(CpuBackend())}
+    twin = {n for n, _, _, _ in R._torch_workloads("cpu", heavy=False)}
+    assert twin <= ours and len(twin) >= 17
+    assert R.run_suite("torch-cuda", 1, 0) is None or torch.cuda.is_available()

@@ -322,6 +322,41 @@ def test_flash_attention_forward_tcgen05(B, Sq, Sk, H, Hk, D, causal, cuda_statu
         assert torch.equal(o2, o_tc)
 
 
+@pytest.mark.parametrize("B,Sq,Sk,H,Hk,D,causal", [(1, 128, 128, 1, 1, 64, True), (2, 128, 128, 4, 4, 64, True), (1, 200, 200, 3, 3, 64, True),
+                                                  (2, 96, 96, 4, 2, 64, False), (1, 256, 256, 4, 1, 128, True),
+                                                  (1, 77, 77, 2, 2, 128, False), (2, 1024, 1024, 2, 2, 64, True),
+                                                  (1, 64, 320, 2, 2, 64, True), (1, 384, 384, 2, 2, 128, True),
+                                                  (1, 640, 640, 2, 2, 64, True), (1, 512, 512, 2, 1, 128, False)])
+@pytest.mark.parametrize("poly", [0, 4])
+def test_flash_attention_forward_two_tile_kernel(B, Sq, Sk, H, Hk, D, causal, poly, cuda_status):
+    """The ping-pong kernel (P in TMEM, output accumulated in TMEM with lazy rescaling) against the fp32 reference and
+    the log-sum-exp of the mma.sync kernel; odd sizes exercise a missing second query tile and partial tiles."""
+    q, k, v = _bf((B, Sq, H, D), 1), _bf((B, Sk, Hk, D), 2), _bf((B, Sk, Hk, D), 3)
+    ref = attn_ops.attention_reference(q, k, v, causal)
+    scale = 1 / math.sqrt(D)
+    o2, lse2 = attn_ops.attention_forward(q.cuda(), k.cuda(), v.cuda(), causal, scale, impl=f"tc2:{poly}")
+    _, lse_mma = attn_ops.attention_forward(q.cuda(), k.cuda(), v.cuda(), causal, scale, impl="mma")
+    _close(o2, ref, what="tc2 o")
+    _close(lse2, lse_mma, tol=1e-3, what="tc2 lse")
+    o3, lse3 = attn_ops.attention_forward(q.cuda(), k.cuda(), v.cuda(), causal, scale, impl=f"tc2:{poly}")
+    assert torch.equal(o2, o3) and torch.equal(lse2, lse3)          # run-twice determinism
+    if Sq == Sk and H == Hk:                                        # packed QKV views through the 4-D tensor maps
+        qkv = torch.cat([q.reshape(B, Sq, -1), k.reshape(B, Sq, -1), v.reshape(B, Sq, -1)], -1).cuda()
+        qs, ks, vs = (qkv[:, :, i * H * D:(i + 1) * H * D].view(B, Sq, H, D) for i in range(3))
+        o4, _ = attn_ops.attention_forward(qs, ks, vs, causal, scale, impl=f"tc2:{poly}")
+        assert torch.equal(o4, o2)
+
+
+def test_flash_attention_two_tile_kernel_rescales_sharp_rows(cuda_status):
+    """Scores with a large spread move the running maximum by more than the lazy-rescale threshold again and again:
+    the accumulator in TMEM is rescaled in place and the result still matches the reference."""
+    B, S, H, D = 1, 1024, 2, 64
+    q, k, v = _bf((B, S, H, D), 1, 4.0), _bf((B, S, H, D), 2, 4.0), _bf((B, S, H, D), 3)
+    ref = attn_ops.attention_reference(q, k, v, True)
+    o, _ = attn_ops.attention_forward(q.cuda(), k.cuda(), v.cuda(), True, 1 / math.sqrt(D), impl="tc2:0")
+    _close(o, ref, tol=2e-2, what="sharp rows")
+
+
 @pytest.mark.parametrize("B,Sq,Sk,H,Hk,D,causal", [
     (2, 256, 256, 4, 4, 64, True), (1, 384, 384, 2, 2, 128, True), (2, 200, 200, 4, 2, 64, True),
     (1, 128, 320, 4, 1, 64, True), (2, 160, 288, 2, 2, 128, False), (1, 512, 512, 3, 3, 64, False),
