@@ -155,22 +155,56 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy, const __nv
     for (int j = 0; j < 8; ++j) { ag[c][j] = 0.f; ab[c][j] = 0.f; }
   }
 
-  for (long long base = static_cast<long long>(blockIdx.x) * RPB; base < rows;
-       base += static_cast<long long>(gridDim.x) * RPB) {
+  // gamma is the same for every row: kept packed in registers
+  uint4 gpk[CHUNKS];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = col_of<CHUNKS, WPR>(wr, c, lane);
+    gpk[c] = col < n ? *reinterpret_cast<const uint4*>(gamma + col) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  // The three input rows (x, dy, residual-branch gradient) of the NEXT row this warp will process are requested
+  // before the current row's reductions, packed as loaded: the kernel is bound by memory latency otherwise.
+  uint4 nx[CHUNKS], ny[CHUNKS], nr[CHUNKS];
+  float nmean = 0.f, nrstd = 0.f;
+  auto fetch = [&](long long row) {
+    const bool valid = row < rows;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = col_of<CHUNKS, WPR>(wr, c, lane);
+      const bool in = valid && col < n;
+      nx[c] = in ? *reinterpret_cast<const uint4*>(x + row * ldx + col) : make_uint4(0u, 0u, 0u, 0u);
+      ny[c] = in ? *reinterpret_cast<const uint4*>(dy + row * lddy + col) : make_uint4(0u, 0u, 0u, 0u);
+      nr[c] = (in && dres) ? *reinterpret_cast<const uint4*>(dres + row * lddres + col) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    nmean = (RMS || !valid) ? 0.f : mean_in[row];
+    nrstd = valid ? rstd_in[row] : 0.f;
+  };
+  auto unpack8 = [](const uint4& u, float (&v)[8]) {
+    const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+    v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y; v[4] = f2.x; v[5] = f2.y; v[6] = f3.x; v[7] = f3.y;
+  };
+  const long long step = static_cast<long long>(gridDim.x) * RPB;
+  fetch(static_cast<long long>(blockIdx.x) * RPB + slot);
+  for (long long base = static_cast<long long>(blockIdx.x) * RPB; base < rows; base += step) {
     const long long row = base + slot;
     const bool valid = row < rows;
     float xv[CHUNKS][8], gy[CHUNKS][8];
-    load_row<CHUNKS, WPR>(x + row * ldx, n, wr, lane, valid, xv);
-    load_row<CHUNKS, WPR>(dy + row * lddy, n, wr, lane, valid, gy);
-    const float mean = (RMS || !valid) ? 0.f : mean_in[row];
-    const float rstd = valid ? rstd_in[row] : 0.f;
+    uint4 rpk[CHUNKS];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      unpack8(nx[c], xv[c]);
+      unpack8(ny[c], gy[c]);
+      rpk[c] = nr[c];
+    }
+    const float mean = nmean, rstd = nrstd;
+    if (base + step < rows) fetch(row + step);          // every warp of the CTA takes this branch together
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
       const int col = col_of<CHUNKS, WPR>(wr, c, lane);
       if (valid && col < n) {
         float g[8];
-        load8(gamma + col, g);
+        unpack8(gpk[c], g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float xhat = (xv[c][j] - mean) * rstd;
@@ -197,7 +231,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy, const __nv
         for (int j = 0; j < 8; ++j) o[j] = rstd * (gy[c][j] - s1 - xv[c][j] * s2);
         if (dres) {
           float r[8];
-          load8(dres + row * lddres + col, r);
+          unpack8(rpk[c], r);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += r[j];
         }
@@ -235,7 +269,20 @@ norm_bwd_reduce_kernel(const float* __restrict__ partial, int num_partials, int 
   const int col = blockIdx.x * 32 + tx;
   float a = 0.f, b = 0.f;
   if (col < n) {
-    for (int p = ty; p < num_partials; p += 8) {
+    // eight independent loads per array are requested before they are added (in the same order as a plain loop):
+    // the fold is a chain of dependent additions, but its loads need not wait for one another
+    int p = ty;
+    for (; p + 56 < num_partials; p += 64) {
+      float va[8], vb[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        va[u] = partial[static_cast<long long>(p + 8 * u) * n + col];
+        vb[u] = dbeta ? partial[static_cast<long long>(num_partials + p + 8 * u) * n + col] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { a += va[u]; b += vb[u]; }
+    }
+    for (; p < num_partials; p += 8) {
       a += partial[static_cast<long long>(p) * n + col];
       if (dbeta) b += partial[static_cast<long long>(num_partials + p) * n + col];
     }

@@ -102,6 +102,16 @@ def bench_norm(a):
     x = torch.randn(a.rows, a.n, device="cuda").bfloat16()
     g = torch.ones(a.n, device="cuda").bfloat16()
     b = torch.zeros(a.n, device="cuda").bfloat16()
+    if a.backward:
+        # backward with the residual-branch gradient folded in: reads x, dy, dres and writes dx (2 bytes each)
+        y, mean, rstd = Nn.norm_forward(x, g, b, 1e-5, False)
+        dy, dres = torch.randn_like(x), torch.randn_like(x)
+        dg = torch.empty(a.n, dtype=torch.float32, device="cuda")
+        db = torch.empty(a.n, dtype=torch.float32, device="cuda")
+        dx = torch.empty_like(x)
+        fn = lambda: Nn.norm_backward(dy, x, g, mean, rstd, False, dres=dres, dgamma=dg, dbeta=db, dx_out=dx)
+        ms = timed(fn, a.warmup, a.iters)
+        return report("layer_norm_bwd", ms, 0, 8.0 * a.rows * a.n, {"rows": a.rows, "n": a.n})
     fn = lambda: Nn.layer_norm(x, g, b, 1e-5)
     ms = timed(fn, a.warmup, a.iters)
     return report("layer_norm_fwd", ms, 0, 4.0 * a.rows * a.n, {"rows": a.rows, "n": a.n})
@@ -166,6 +176,7 @@ def main(argv=None):
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=32768)
     n.add_argument("--n", type=int, default=768)
+    n.add_argument("--backward", action="store_true")
     d = sub.add_parser("adam")
     d.add_argument("--numel", type=int, default=124_000_000)
     pg = sub.add_parser("paged")
