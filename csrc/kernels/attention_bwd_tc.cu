@@ -27,8 +27,7 @@ namespace rb {
 constexpr int kBtTile = 128;
 constexpr int kBtColGroups = 2;                    // compute warps = 4 lane quarters x this many column groups
 constexpr int kBtComputeWarps = 4 * kBtColGroups;
-constexpr int kBtThreads = 32 * (kBtComputeWarps + 4);   // + TMA warp, MMA warp and two warps that only complete the
-                                                            // producer warp group for the register reallocation
+constexpr int kBtThreads = 32 * (kBtComputeWarps + 2);
 constexpr int kBtColsPerGroup = kBtTile / kBtColGroups;   // keys per compute thread and step
 constexpr float kBtLog2e = 1.4426950408889634f;
 constexpr int MODE_DKV = 0;
@@ -43,13 +42,6 @@ struct BtParams {
   int seq_q, seq_k, heads, kv_heads, causal, batch;
   float scale;
 };
-
-// Register reallocation between warp groups: the producer group keeps a few registers per thread, the compute groups
-// grow so that a thread's 64 scores and 64 dP values of a step fit in registers at once.
-template <int N>
-__device__ __forceinline__ void bt_setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N>
-__device__ __forceinline__ void bt_setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 __device__ __forceinline__ float bt_ex2(float x) {
   float y;
@@ -218,8 +210,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   // Running counters: `wi` counts this CTA's work items, `git` its steps over all items, `ai` its items that have at
   // least one step; the barrier phases follow them, so every role derives the same parities independently.
-  if (warp >= kBtComputeWarps) {
-  bt_setmaxnreg_dec<64>();
   if (warp == kBtComputeWarps) {
     if (lane == 0) {
       // ---------------------------------------------------------------- TMA producer
@@ -348,9 +338,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         umma_commit(bar_res_empty + 8 * rsl);     // every product that reads this resident pair has completed by then
       }
     }
-  }
   } else {
-    bt_setmaxnreg_inc<216>();
     // ------------------------------------------------------------------ P / dS and the read-out of every item
     const int qtr = warp & 3, cg = warp >> 2;              // TMEM lane quarter, column group
     constexpr int GC = kBtColsPerGroup;                    // columns (keys) per thread and step: 64 or 32
@@ -392,33 +380,37 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!mbar_wait(bar_sdp_full, git & 1, abort_flag, status, 46)) { ok = false; break; }
         tc_fence_after();
         uint32_t pp[GC / 2], ds[GC / 2];                     // GC columns each, packed bf16 pairs
-        // all GC columns of S and of dP are requested at once and waited for once
+        // 16 columns of S and of dP per step; the loads of step c + 1 are in flight while step c is computed
         const uint32_t ts = tmem_s + lane_off + cg * GC, td = tmem_dp + lane_off + cg * GC;
-        uint32_t rs[GC], rd[GC];
+        uint32_t rs[2][16], rd[2][16];
+        tmem_ld_32x16(ts, rs[0]);
+        tmem_ld_32x16(td, rd[0]);
 #pragma unroll
         for (int c = 0; c < GC / 16; ++c) {
-          tmem_ld_32x16(ts + c * 16, *reinterpret_cast<uint32_t(*)[16]>(rs + c * 16));
-          tmem_ld_32x16(td + c * 16, *reinterpret_cast<uint32_t(*)[16]>(rd + c * 16));
+          tmem_ld_wait();
+          if (c + 1 < GC / 16) {
+            tmem_ld_32x16(ts + (c + 1) * 16, rs[(c + 1) & 1]);
+            tmem_ld_32x16(td + (c + 1) * 16, rd[(c + 1) & 1]);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float p0 = bt_ex2(fmaf(__uint_as_float(rs[c & 1][2 * i]), sl2, -lse2));
+            float p1 = bt_ex2(fmaf(__uint_as_float(rs[c & 1][2 * i + 1]), sl2, -lse2));
+            if (need_mask) {
+              const int key = kbase + c * 16 + 2 * i;
+              if (key > key_lim) p0 = 0.f;
+              if (key + 1 > key_lim) p1 = 0.f;
+            }
+            const float d0 = p0 * (__uint_as_float(rd[c & 1][2 * i]) - dlt);
+            const float d1 = p1 * (__uint_as_float(rd[c & 1][2 * i + 1]) - dlt);
+            pp[c * 8 + i] = pack_bf16x2(p0, p1);
+            ds[c * 8 + i] = pack_bf16x2(d0, d1);
+          }
         }
-        tmem_ld_wait();
         // S and dP are in registers: the next pair of products may overwrite them
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_sdp_empty);
-#pragma unroll
-        for (int i = 0; i < GC / 2; ++i) {
-          float p0 = bt_ex2(fmaf(__uint_as_float(rs[2 * i]), sl2, -lse2));
-          float p1 = bt_ex2(fmaf(__uint_as_float(rs[2 * i + 1]), sl2, -lse2));
-          if (need_mask) {
-            const int key = kbase + 2 * i;
-            if (key > key_lim) p0 = 0.f;
-            if (key + 1 > key_lim) p1 = 0.f;
-          }
-          const float d0 = p0 * (__uint_as_float(rd[2 * i]) - dlt);
-          const float d1 = p1 * (__uint_as_float(rd[2 * i + 1]) - dlt);
-          pp[i] = pack_bf16x2(p0, p1);
-          ds[i] = pack_bf16x2(d0, d1);
-        }
         // the previous step's dV / dK / dQ products have finished reading P and dS
         if (!mbar_wait(bar_p_empty, (git & 1) ^ 1, abort_flag, status, 47)) { ok = false; break; }
         // 64 keys are one 128-byte-swizzled atom (row `row`, eight 16-byte chunks); this thread owns GC / 8 of the chunks

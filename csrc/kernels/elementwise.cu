@@ -178,12 +178,12 @@ sum_dim0_stage1_vec(const __nv_bfloat16* __restrict__ a, long long lda, float* _
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (col < cols) {
     long long r = lo + ry;
-    for (; r + 24 < hi; r += 32) {                       // four independent 16-byte loads in flight
-      uint4 v[4];
+    for (; r + 56 < hi; r += 64) {                       // eight independent 16-byte loads in flight
+      uint4 v[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) v[u] = __ldg(reinterpret_cast<const uint4*>(a + (r + 8 * u) * lda + col));
+      for (int u = 0; u < 8; ++u) v[u] = __ldg(reinterpret_cast<const uint4*>(a + (r + 8 * u) * lda + col));
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         const uint32_t* w = reinterpret_cast<const uint32_t*>(&v[u]);
 #pragma unroll
         for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(w[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
@@ -214,7 +214,15 @@ sum_dim0_stage2(const float* __restrict__ partial, int slabs, float* __restrict_
   const int col = blockIdx.x * blockDim.x + threadIdx.x;
   if (col >= cols) return;
   float acc = 0.f;
-  for (int s = 0; s < slabs; ++s) acc += partial[static_cast<long long>(s) * cols + col];
+  int s = 0;
+  for (; s + 7 < slabs; s += 8) {          // the loads of eight slabs are requested together, then added in slab order
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = partial[static_cast<long long>(s + u) * cols + col];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc += v[u];
+  }
+  for (; s < slabs; ++s) acc += partial[static_cast<long long>(s) * cols + col];
   out[col] = accumulate ? out[col] + acc : acc;
 }
 // Single-kernel variant for when no scratch is available: one thread per column walks all rows.
