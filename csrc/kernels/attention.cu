@@ -555,6 +555,7 @@ bool ptr_ok(const void* p) { return p != nullptr && (reinterpret_cast<uintptr_t>
 }  // namespace
 
 RB_API int rb_attention_fwd(const RbAttnArgs* a, void* stream_v) {
+  if (a->kv_lens) return -9;                 // key-padding lengths are not implemented by the mma.sync kernels
   rb::AttnParams p;
   if (!fill_params(a, p)) return -1;
   if (!ptr_ok(a->q) || !ptr_ok(a->k) || !ptr_ok(a->v) || !ptr_ok(a->o)) return -2;
@@ -574,6 +575,7 @@ RB_API int rb_attention_fwd(const RbAttnArgs* a, void* stream_v) {
 }
 
 RB_API int rb_attention_bwd(const RbAttnArgs* a, void* stream_v) {
+  if (a->kv_lens) return -9;                 // key-padding lengths are not implemented by the mma.sync kernels
   rb::AttnParams p;
   if (!fill_params(a, p)) return -1;
   if (!ptr_ok(a->q) || !ptr_ok(a->k) || !ptr_ok(a->v) || !ptr_ok(a->o) || !ptr_ok(a->d_o) || !ptr_ok(a->dq) ||

@@ -16,9 +16,17 @@ typedef struct RbAttnArgs {
   int batch, heads, kv_heads, seq_q, seq_k, head_dim;
   int causal;              // with seq_q < seq_k the queries are aligned to the end of the keys
   float scale;             // softmax scale, usually 1/sqrt(head_dim)
+  const int* kv_lens;      // optional [batch]: keys at positions >= kv_lens[b] are padding and invisible (NULL: all seq_k
+                           // keys are real).  Taken by the "tc2" kernels; the others return -9 when it is set.
 } RbAttnArgs;
 int rb_attention_fwd(const RbAttnArgs* args, void* stream);
 int rb_attention_bwd(const RbAttnArgs* args, void* stream);
+// tcgen05 paths (attention_tc.cu, attention_fwd2.cu, attention_bwd_tc.cu, attention_bwd2.cu); -9: shape not taken
+int rb_attention_fwd_tc(const RbAttnArgs* args, void* stream);
+int rb_attention_fwd_tc2(const RbAttnArgs* args, int poly_every, void* stream);
+int rb_attention_bwd_tc(const RbAttnArgs* args, void* stream);
+int rb_attention_delta_tc(const RbAttnArgs* args, void* stream);
+int rb_attention_bwd_tc2(const RbAttnArgs* args, void* stream);
 #ifdef __cplusplus
 }
 #endif

@@ -523,9 +523,29 @@ int bt_launch(const CUtensorMap* tq, const CUtensorMap* tk, const CUtensorMap* t
 }
 }  // namespace
 
+// delta[b, h, r] = sum_d dO * O (fp32), the row term of the softmax gradient; shared by both tcgen05 backward paths.
+RB_API int rb_attention_delta_tc(const RbAttnArgs* a, void* stream_v) {
+  const int D = a->head_dim;
+  if (D != 64 && D != 128) return -9;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  const long long rows = static_cast<long long>(a->heads) * a->seq_q;
+  const int rows_per_block = 256 / (D / 8);
+  dim3 dgrid(static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block), a->batch);
+  const __nv_bfloat16* o = reinterpret_cast<const __nv_bfloat16*>(a->o);
+  const __nv_bfloat16* d_o = reinterpret_cast<const __nv_bfloat16*>(a->d_o);
+  if (D == 64)
+    rb::attn_delta_tc_kernel<64><<<dgrid, 256, 0, stream>>>(o, d_o, a->delta, a->o_strides[0], a->o_strides[1],
+                                                             a->o_strides[2], a->heads, a->seq_q);
+  else
+    rb::attn_delta_tc_kernel<128><<<dgrid, 256, 0, stream>>>(o, d_o, a->delta, a->o_strides[0], a->o_strides[1],
+                                                              a->o_strides[2], a->heads, a->seq_q);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // Backward pass on the tcgen05 path (three launches: delta, dK/dV, dQ).  Returns -9 when the problem is outside what
 // these kernels take (the caller then uses rb_attention_bwd).
 RB_API int rb_attention_bwd_tc(const RbAttnArgs* a, void* stream_v) {
+  if (a->kv_lens) return -9;                 // key-padding lengths: only the second-generation kernels take them
   if (a->batch <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->heads % a->kv_heads) return -1;
   if (a->head_dim != 64 && a->head_dim != 128) return -9;
   if (a->seq_q <= 0 || a->seq_k <= 0 || (a->causal && a->seq_q > a->seq_k)) return -1;
@@ -546,17 +566,7 @@ RB_API int rb_attention_bwd_tc(const RbAttnArgs* a, void* stream_v) {
   if (!tq || !tk || !tv || !tdo) return err ? err : -5;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
 
-  const long long rows = static_cast<long long>(a->heads) * a->seq_q;
-  const int rows_per_block = 256 / (D / 8);
-  dim3 dgrid(static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block), a->batch);
-  const __nv_bfloat16* o = reinterpret_cast<const __nv_bfloat16*>(a->o);
-  const __nv_bfloat16* d_o = reinterpret_cast<const __nv_bfloat16*>(a->d_o);
-  if (D == 64)
-    rb::attn_delta_tc_kernel<64><<<dgrid, 256, 0, stream>>>(o, d_o, a->delta, a->o_strides[0], a->o_strides[1],
-                                                             a->o_strides[2], a->heads, a->seq_q);
-  else
-    rb::attn_delta_tc_kernel<128><<<dgrid, 256, 0, stream>>>(o, d_o, a->delta, a->o_strides[0], a->o_strides[1],
-                                                              a->o_strides[2], a->heads, a->seq_q);
+  rb_attention_delta_tc(a, stream_v);
 
   rb::BtParams p;
   p.lse = a->lse; p.delta = a->delta;

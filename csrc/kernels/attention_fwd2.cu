@@ -32,6 +32,7 @@ struct F2Params {
   long long o_bs, o_rs, o_hs;
   int seq_q, seq_k, heads, kv_heads, causal;
   float scale;
+  const int* kv_lens;       // optional [batch]: number of real keys
 };
 
 __device__ __forceinline__ float f2_ex2(float x) {
@@ -127,7 +128,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int hk = h / (p.heads / p.kv_heads);
   const int q0 = m_blk * 2 * kF2Tile;
   const int shift = p.seq_k - p.seq_q;
-  const int n_all = (p.seq_k + kF2Tile - 1) / kF2Tile;
+  // keys at positions >= kv_len are padding: never visible, and key blocks that hold only padding are skipped
+  const int kv_len = p.kv_lens ? max(0, min(p.seq_k, p.kv_lens[b])) : p.seq_k;
+  const int n_all = (kv_len + kF2Tile - 1) / kF2Tile;
   // key blocks seen by tile A and by tile B (0: the tile starts beyond the last query)
   auto blocks_of = [&](int qt) {
     int n = qt < p.seq_q ? n_all : 0;
@@ -261,7 +264,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!mbar_wait(bar_sfull + 8 * t, j & 1, abort_flag, status, 46)) { ok = false; break; }
       tc_fence_after();
       const int k0 = j * kF2Tile;
-      const int key_lim = p.causal ? min(p.seq_k - 1, q_idx + shift) : p.seq_k - 1;     // last visible key
+      const int key_lim = p.causal ? min(kv_len - 1, q_idx + shift) : kv_len - 1;     // last visible key
       const bool need_mask = (k0 + kF2Tile - 1 > key_lim);
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
       // maximum over 32 scores (masked keys have been set to -inf)
@@ -352,6 +355,13 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lane == 0) mbar_arrive(bar_pfull + 8 * t);
     }
     if (ok && nt > 0) ok = mbar_wait(bar_oready + 8 * t, (nt - 1) & 1, abort_flag, status, 48);
+    if (nt == 0 && q_idx < p.seq_q && q0 + t * kF2Tile < p.seq_q) {
+      // no visible key at all (every key of this batch entry is padding): the output row is zero
+      __nv_bfloat16* op = p.out + b * p.o_bs + h * p.o_hs + static_cast<long long>(q_idx) * p.o_rs;
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(op)[c] = make_uint4(0u, 0u, 0u, 0u);
+      if (p.lse != nullptr) p.lse[(static_cast<long long>(b) * p.heads + h) * p.seq_q + q_idx] = 0.f;
+    }
     if (ok && nt > 0) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -451,6 +461,7 @@ RB_API int rb_attention_fwd_tc2(const RbAttnArgs* a, int poly_every, void* strea
   p.o_bs = a->o_strides[0]; p.o_rs = a->o_strides[1]; p.o_hs = a->o_strides[2];
   p.seq_q = a->seq_q; p.seq_k = a->seq_k; p.heads = a->heads; p.kv_heads = a->kv_heads; p.causal = a->causal;
   p.scale = a->scale;
+  p.kv_lens = a->kv_lens;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   dim3 grid((a->seq_q + 2 * rb::kF2Tile - 1) / (2 * rb::kF2Tile), a->heads, a->batch);
   if (a->head_dim == 64) {

@@ -338,6 +338,7 @@ const CUtensorMap* make_map(const void* base, const long long* strides, int seq,
 // Forward pass on the tcgen05 path.  Returns -9 when the problem is outside what this kernel takes (the caller then
 // uses rb_attention_fwd).
 RB_API int rb_attention_fwd_tc(const RbAttnArgs* a, void* stream_v) {
+  if (a->kv_lens) return -9;                 // key-padding lengths: only the second-generation kernels take them
   if (a->batch <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->heads % a->kv_heads) return -1;
   if (a->head_dim != 64 && a->head_dim != 128) return -9;
   if (a->seq_q <= 0 || a->seq_k <= 0 || (a->causal && a->seq_q > a->seq_k)) return -1;

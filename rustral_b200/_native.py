@@ -46,7 +46,7 @@ class RbAttnArgs(C.Structure):
         ("q_strides", c_ll * 3), ("k_strides", c_ll * 3), ("v_strides", c_ll * 3), ("o_strides", c_ll * 3),
         ("dq_strides", c_ll * 3), ("dk_strides", c_ll * 3), ("dv_strides", c_ll * 3),
         ("batch", c_int), ("heads", c_int), ("kv_heads", c_int), ("seq_q", c_int), ("seq_k", c_int),
-        ("head_dim", c_int), ("causal", c_int), ("scale", c_float),
+        ("head_dim", c_int), ("causal", c_int), ("scale", c_float), ("kv_lens", c_void_p),
     ]
 
 

@@ -93,7 +93,8 @@ def bench_attention(a):
     o, lse = A.attention_forward(q, k, v, a.causal, sc, impl=a.impl)
     do = torch.randn_like(o)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    ms = timed(lambda: A.attention_backward(do, q, k, v, o, lse, a.causal, sc, dq, dk, dv), a.warmup, a.iters)
+    bwd_impl = a.bwd_impl or None
+    ms = timed(lambda: A.attention_backward(do, q, k, v, o, lse, a.causal, sc, dq, dk, dv, impl=bwd_impl), a.warmup, a.iters)
     return report("attention_bwd", ms, 2.5 * flops_fwd, 0, {"batch": B, "seq": S, "heads": H, "head_dim": D})
 
 
@@ -173,6 +174,7 @@ def main(argv=None):
     t.add_argument("--impl", default="tc2", help="tc2 (two query tiles per CTA; tc2:<n> picks a variant), tc (one tile per CTA) or mma")
     t.add_argument("--no-causal", dest="causal", action="store_false")
     t.add_argument("--backward", action="store_true")
+    t.add_argument("--bwd-impl", default="", help="backward implementation: tc2, tc or mma (default: the library default)")
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=32768)
     n.add_argument("--n", type=int, default=768)

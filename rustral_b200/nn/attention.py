@@ -52,11 +52,29 @@ def causal_mask_tape(backend, seq_len: int) -> torch.Tensor:
     return causal_mask(backend, seq_len, -1e9)
 
 
+class KeyPaddingMask:
+    """A key-padding mask given as the number of real keys per batch entry (the keys behind them are padding).  The
+    flash kernels take it directly: padded key blocks are skipped, no [S, S] mask tensor exists."""
+
+    def __init__(self, lengths):
+        self.lengths = lengths if torch.is_tensor(lengths) else torch.tensor(list(lengths), dtype=torch.int32)
+
+    @classmethod
+    def from_token_ids(cls, ids: torch.Tensor, pad_id: int = 0):
+        """Lengths of right-padded id rows [B, S]: position of the last non-pad token + 1."""
+        keep = ids != pad_id
+        pos = torch.arange(1, ids.shape[1] + 1, device=ids.device)
+        return cls((keep * pos).amax(-1).to(torch.int32))
+
+
 def scaled_dot_product_attention(q, k, v, mask=None, causal: bool = False, scale: float | None = None):
-    """q [B,S,H,D], k/v [B,Sk,Hkv,D].  With an explicit additive mask the reference math runs (fp32, O(S^2));
-    otherwise the flash kernels."""
+    """q [B,S,H,D], k/v [B,Sk,Hkv,D].  `mask`: None, a `KeyPaddingMask` (flash kernels, padded keys skipped) or an
+    additive tensor broadcastable to [B,H,S,Sk] (reference math in fp32, O(S^2) memory: arbitrary masks are rare and
+    are not what the kernels are built for)."""
     if mask is None:
         return ops.flash_attention(q, k, v, causal, scale)
+    if isinstance(mask, KeyPaddingMask):
+        return ops.flash_attention(q, k, v, causal, scale, kv_lens=mask.lengths)
     B, Sq, H, D = q.shape
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))

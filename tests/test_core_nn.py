@@ -549,3 +549,29 @@ def test_recurrent_inference_sequences_match_the_generic_loop():
         assert train.requires_grad
         train.sum().backward()
         assert all(p.tensor.grad is not None for p in cell.parameters())
+
+
+def test_key_padding_mask_matches_truncated_keys_and_ignores_padding_values():
+    """A `KeyPaddingMask` gives every batch entry the attention over its real keys only: same result as cutting the
+    padding off, whatever the padded positions hold; an entry without real keys gives zero rows."""
+    from rustral_b200.nn.attention import KeyPaddingMask, scaled_dot_product_attention
+    from rustral_b200.ops import attention as A
+    g = torch.Generator().manual_seed(3)
+    q, k, v = torch.randn(3, 6, 4, 8, generator=g), torch.randn(3, 9, 2, 8, generator=g), torch.randn(3, 9, 2, 8, generator=g)
+    lens = [9, 4, 0]
+    out = scaled_dot_product_attention(q, k, v, KeyPaddingMask(lens))
+    for b, n in enumerate(lens):
+        if n == 0:
+            assert out[b].abs().max() == 0
+            continue
+        want = A.attention_reference(q[b:b + 1], k[b:b + 1, :n], v[b:b + 1, :n], False)
+        assert torch.allclose(out[b:b + 1], want, atol=1e-6)
+    k2, v2 = k.clone(), v.clone()
+    k2[1, 4:], v2[1, 4:] = 1e4, -1e4                       # garbage in the padding must not leak
+    assert torch.allclose(scaled_dot_product_attention(q, k2, v2, KeyPaddingMask(lens))[1], out[1], atol=1e-6)
+    ids = torch.tensor([[5, 6, 7, 0, 0], [1, 0, 0, 0, 0], [1, 2, 3, 4, 5]])
+    assert KeyPaddingMask.from_token_ids(ids).lengths.tolist() == [3, 1, 5]
+    # gradients flow through the masked form and vanish on padded keys
+    kk = k.clone().requires_grad_()
+    scaled_dot_product_attention(q, kk, v, KeyPaddingMask(lens)).sum().backward()
+    assert kk.grad[1, 4:].abs().max() == 0 and kk.grad[1, :4].abs().max() > 0
