@@ -163,9 +163,9 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& ep, uint32_t (&r)
         for (int j = 0; j < 32; ++j)
           if (col0 + j < N) ap[j] = __float2bfloat16(v[j]);
       }
-      // the backward pass sees the bf16-rounded pre-activation; use the same value here
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __bfloat162float(__float2bfloat16(v[j]));
+      // The activation is applied to the unrounded fp32 value; the backward pass differentiates at the bf16-rounded
+      // one it reads back (a relative difference of 2^-9 in the argument).  Rounding here as well costs two conversions
+      // per element in an epilogue whose conversion and special-function work already exceeds the main loop at K = 768.
     }
     if (ep.act == RB_ACT_GELU) {
 #pragma unroll

@@ -20,10 +20,6 @@ def rel_err(a, b):
 
 
 def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="check")
-    ap.add_argument("--iters", type=int, default=10)
-    a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     torch.cuda.set_device(dev)
@@ -32,7 +28,7 @@ def main():
     from rustral_b200.ops import moe as M
     from rustral_b200.parallel.expert_parallel import FusedEP, ep_moe_mlp
     out = {"world": world}
-    if a.mode == "check":
+    if True:
         E, d, F, T, k = 2 * world, 128, 256, 200 + 8 * rank, 2
         g = torch.Generator().manual_seed(11)
         router_w = (torch.randn(E, d, generator=g) * 0.5).bfloat16().to(dev)
@@ -71,34 +67,6 @@ def main():
                           "dw2": rel_err(res[0][3], dw2[rank * El:(rank + 1) * El]),
                           "drouter": rel_err(res[0][4], rwr.grad)}
         out["err"] = errs
-        ep.close()
-    else:
-        # config-4-like layer: d 2048, FFN 8192 SwiGLU, 8 experts, top-2, 8192 local tokens
-        E, d, F, T, k = 8, 2048, 8192, 8192, 2
-        El = E // world
-        ep = FusedEP(None, dev, E, d, max_tokens=T, k=k)
-        x = torch.randn(T, d, device=dev).bfloat16()
-        router_w = (torch.randn(E, d, device=dev) * 0.02).bfloat16()
-        w1 = (torch.randn(El, 2 * F, d, device=dev) * 0.02).bfloat16()
-        w2 = (torch.randn(El, d, F, device=dev) * 0.02).bfloat16()
-
-        def fwd():
-            with torch.no_grad():
-                ep_moe_mlp(x, router_w, w1, w2, ep, k=k)
-
-        for _ in range(3):
-            fwd()
-        dist.barrier(); torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(a.iters):
-            fwd()
-        e1.record(); torch.cuda.synchronize()
-        ms = torch.tensor([e0.elapsed_time(e1) / a.iters], device=dev, dtype=torch.float64)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        flops = 2.0 * T * k * d * (3 * F)          # per rank on average (uniform routing)
-        out["ep_layer_fwd_ms"] = round(float(ms), 3)
-        out["expert_tflops_per_gpu"] = round(flops / (float(ms) * 1e-3) / 1e12, 1)
         ep.close()
     torch.cuda.synchronize()
     st = torch.tensor([_native.read_status()[0]], device=dev)

@@ -1,10 +1,9 @@
-"""Worker for the peer-memory ring attention test and micro-benchmark: one rank per GPU under torch.distributed.run.
+"""Worker for the peer-memory ring attention test: one rank per GPU under torch.distributed.run.
 
---mode check : forward and backward of contiguous and striped, causal and full attention over a sequence sharded
-               across the ranks, against an fp32 PyTorch attention of the whole sequence and against the send / recv
-               ring; run twice for bit-reproducibility; copy-kernel and copy-engine pulls.
---mode bench : device time (max over ranks) of forward + backward, peer-memory ring against the send / recv ring.
-Rank 0 prints one JSON line.
+Forward and backward of contiguous and striped, causal and full attention over a sequence sharded across the ranks,
+against an fp32 PyTorch attention of the whole sequence and against the send / recv ring; run twice for
+bit-reproducibility; copy-kernel and copy-engine pulls.  Rank 0 prints one JSON line.  (Timings: the `ring` mode of
+`rustral_b200.bench.comm_kernels`.)
 """
 import argparse
 import json
@@ -84,72 +83,21 @@ def check(rank, world, dev, group):
     return out
 
 
-def bench(rank, world, dev, group, a):
-    from rustral_b200.parallel.peer_ring import PeerRing
-    from rustral_b200.parallel.process_group import ProcessGroup
-    from rustral_b200.parallel.sequence_parallel import RingAttention, SequenceParallelConfig
-    B, Sl, H, Hkv, D = a.batch, a.seq_local, a.heads, a.kv_heads, a.head_dim
-    gen = torch.Generator().manual_seed(rank)
-    mk = lambda h: torch.randn(B, Sl, h, D, generator=gen).bfloat16().to(dev).requires_grad_()
-    q, k, v = mk(H), mk(Hkv), mk(Hkv)
-    do = torch.randn(B, Sl, H, D, generator=gen).bfloat16().to(dev)
-    pg = ProcessGroup.from_torch(group)
-    out = {"shape": [B, Sl, H, Hkv, D], "world": world}
-    for striped in (False, True):
-        variants = {"relay": None, "peer_kernel": PeerRing(group, dev, k.numel(), 64), "peer_engine": PeerRing(group, dev, k.numel(), -1)}
-        for name, ring in variants.items():
-            ra = RingAttention(pg, SequenceParallelConfig(world, striped=striped, causal=True)).use_peer_memory(ring)
-
-            def step():
-                for t in (q, k, v):
-                    t.grad = None
-                ra(q, k, v).backward(do)
-            for _ in range(3):
-                step()
-            torch.cuda.synchronize()
-            dist.barrier(group)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(a.iters):
-                step()
-            e1.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) / a.iters], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
-            out[f"{'striped' if striped else 'contig'}_{name}_ms"] = float(t)
-        for ring in variants.values():
-            if ring is not None:
-                ring.close()
-    return out
-
-
 def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="check")
-    ap.add_argument("--iters", type=int, default=5)
-    ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--seq-local", type=int, default=8192)
-    ap.add_argument("--heads", type=int, default=16)
-    ap.add_argument("--kv-heads", type=int, default=4)
-    ap.add_argument("--head-dim", type=int, default=128)
-    a = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     group = dist.group.WORLD
-    res = check(rank, world, dev, group) if a.mode == "check" else bench(rank, world, dev, group, a)
+    res = check(rank, world, dev, group)
     gathered = [None] * world
     dist.all_gather_object(gathered, res)
     if rank == 0:
-        if a.mode == "check":
-            merged = {"status_max": max(g["status"] for g in gathered), "canaries_ok": all(g["canaries_ok"] for g in gathered),
-                      "repeatable": all(g["repeatable"] for g in gathered),
-                      "errs": {key: max(max(g["errs"][key]) for g in gathered) for key in res["errs"]},
-                      "relay_match": {key: max(g["relay_match"][key] for g in gathered) for key in res["relay_match"]}}
-            print(json.dumps(merged))
-        else:
-            print(json.dumps(res))
+        merged = {"status_max": max(g["status"] for g in gathered), "canaries_ok": all(g["canaries_ok"] for g in gathered),
+                  "repeatable": all(g["repeatable"] for g in gathered),
+                  "errs": {key: max(max(g["errs"][key]) for g in gathered) for key in res["errs"]},
+                  "relay_match": {key: max(g["relay_match"][key] for g in gathered) for key in res["relay_match"]}}
+        print(json.dumps(merged))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -1,9 +1,8 @@
 """Worker for the fused tensor-parallel GEMM tests and micro-benchmark: one rank per GPU under torch.distributed.run.
 
---mode check : ag_gemm and gemm_rs against all_gather / reduce_scatter + fp32 matmul, twice (bit-reproducibility and
+ag_gemm and gemm_rs against all_gather / reduce_scatter + fp32 matmul, twice (bit-reproducibility and
                workspace parity), then a sequence-parallel column->row MLP, fused against the collective path,
                forward and backward.
---mode bench : device time of the fused primitives against NCCL collective + the same GEMM kernel, max over ranks.
 Rank 0 prints one JSON line.
 """
 import argparse
@@ -114,89 +113,7 @@ def check(tp, rank, world, dev):
     return out
 
 
-def bench(tp, rank, world, dev, iters):
-    from rustral_b200.ops.matmul import gemm
-    res = []
-    # (rows per rank, K, N of the all-gather GEMM) and the mirrored reduce-scatter GEMM, Llama-8B-like TP shapes
-    shapes = [(8192 // world, 4096, 3 * 4096 // world), (8192 // world, 4096, 2 * 14336 // world)]
-    for rows, K, Nn in shapes:
-        M = rows * world
-        x_local = torch.randn(rows, K, device=dev).bfloat16()
-        w = torch.randn(Nn, K, device=dev).bfloat16() * 0.02
-        gathered = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
-
-        def fused_ag():
-            tp.ag_gemm(x_local, w)
-
-        def nccl_ag():
-            dist.all_gather_into_tensor(gathered, x_local)
-            gemm(gathered, w)
-
-        def gemm_only():
-            gemm(gathered, w)
-
-        x2 = torch.randn(M, Nn, device=dev).bfloat16()        # row layer: [M, k_local = Nn] x [K, Nn]^T
-        w2 = torch.randn(K, Nn, device=dev).bfloat16() * 0.02
-        part = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
-        red = torch.empty(rows, K, dtype=torch.bfloat16, device=dev)
-
-        def fused_rs():
-            tp.gemm_rs(x2, w2)
-
-        def nccl_rs():
-            gemm(x2, w2, out=part)
-            dist.reduce_scatter_tensor(red, part)
-
-        def gemm_only2():
-            gemm(x2, w2, out=part)
-
-        # FSDP: weight [Nn * world, K] row-sharded, tokens local
-        wsh = tp.shard_weight(w)
-        w_gathered = torch.empty(Nn * world, K, dtype=torch.bfloat16, device=dev)
-        xt = torch.randn(M, K, device=dev).bfloat16()
-
-        def fused_fsdp():
-            tp.fsdp_gemm(xt, wsh)
-
-        def nccl_fsdp():
-            dist.all_gather_into_tensor(w_gathered, w)
-            gemm(xt, w_gathered)
-
-        def gemm_only3():
-            gemm(xt, w_gathered)
-
-        row = {"rows_per_rank": rows, "K": K, "N": Nn}
-        for name, fn in (("fused_fsdp_gemm", fused_fsdp), ("nccl_allgather_w_then_gemm", nccl_fsdp), ("gemm_alone_fsdp_shape", gemm_only3),
-                         ("fused_ag_gemm", fused_ag), ("nccl_ag_then_gemm", nccl_ag), ("gemm_alone", gemm_only),
-                         ("fused_gemm_rs", fused_rs), ("gemm_then_nccl_rs", nccl_rs), ("gemm_alone_rs_shape", gemm_only2)):
-            for _ in range(3):
-                fn()
-            dist.barrier()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(iters):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
-            ms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev, dtype=torch.float64)
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-            row[name + "_us"] = round(float(ms) * 1e3, 1)
-        flops = 2.0 * M * K * Nn
-        row["fused_ag_tflops"] = round(flops / (row["fused_ag_gemm_us"] * 1e-6) / 1e12, 1)
-        row["fused_rs_tflops"] = round(flops / (row["fused_gemm_rs_us"] * 1e-6) / 1e12, 1)
-        # bytes each GPU must pull (ag) or push (rs) over NVLink
-        row["nvlink_bytes_ag"] = (world - 1) * rows * K * 2
-        row["nvlink_bytes_rs"] = (world - 1) * rows * K * 2
-        res.append(row)
-    return res
-
-
 def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="check")
-    ap.add_argument("--iters", type=int, default=20)
-    a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     torch.cuda.set_device(dev)
@@ -205,10 +122,7 @@ def main():
     from rustral_b200.parallel.fused_tp import FusedTP
     tp = FusedTP(None, dev)
     out = {"world": world}
-    if a.mode == "check":
-        out.update(check(tp, rank, world, dev))
-    else:
-        out["bench"] = bench(tp, rank, world, dev, a.iters)
+    out.update(check(tp, rank, world, dev))
     torch.cuda.synchronize()
     bufs = [tp.pad] + [b for ws in tp._ws.values() for b in (getattr(ws, "shard", None) or getattr(ws, "slots", None) or [ws.buf])]
     out["canaries_ok"] = all(b.check_canaries() for b in bufs)

@@ -11,11 +11,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "mp_tp_worker.py")
 
 
-def _run(nproc, mode, port):
+def _run(nproc, port):
     env = dict(os.environ)
     env["NCCL_NVLS_ENABLE"] = "0"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
-           "127.0.0.1", "--master-port", str(port), WORKER, "--mode", mode, "--iters", "5"]
+           "127.0.0.1", "--master-port", str(port), WORKER]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     return json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
@@ -24,7 +24,7 @@ def _run(nproc, mode, port):
 @pytest.mark.gpu
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_fused_tp_two_gpus():
-    out = _run(2, "check", 29641)
+    out = _run(2, 29641)
     assert out["status_max"] == 0 and out["canaries_ok"]
     assert out["ag_gemm_err"] < 1e-2 and out["ag_gemm_repeatable"]
     assert out["gemm_rs_err"] < 1e-2 and out["gemm_rs_repeatable"]
