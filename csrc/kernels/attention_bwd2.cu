@@ -67,7 +67,8 @@ struct B2Smem {
   static constexpr int kStream = kResStages * 2 * kTileBytes;
   static constexpr int kStats = kStream + kStages * 2 * kTileBytes;     // [2 steps][lse2 | delta][128] fp32
   static constexpr int kBar = kStats + 2 * 2 * 128 * 4;
-  static constexpr int kNumBars = 2 * kResStages + 2 * kStages + 8;
+  // + s_full[2], s_empty, dp_full[2], p_full[2], ds_full[2], acc_full, acc_empty
+  static constexpr int kNumBars = 2 * kResStages + 2 * kStages + 11;
   static constexpr int kTotal = kBar + kNumBars * 8 + 16;
   // TMEM columns
   static constexpr int kSBufs = (MODE == B2_DKV && D == 64) ? 2 : 1;    // S (S^T) buffers
@@ -93,8 +94,9 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t b0 = smem_u32(bars);
   const uint32_t bar_res = b0, bar_res_empty = bar_res + 8 * RS, bar_tfull = bar_res_empty + 8 * RS,
                  bar_tempty = bar_tfull + 8 * ST, bar_sfull = bar_tempty + 8 * ST /* [2] */, bar_sempty = bar_sfull + 16,
-                 bar_dpfull = bar_sempty + 8 /* [2] */, bar_pfull = bar_dpfull + 16, bar_dsfull = bar_pfull + 8,
-                 bar_accfull = bar_dsfull + 8, bar_accempty = bar_accfull + 8;
+                 bar_dpfull = bar_sempty + 8 /* [2] */, bar_pfull = bar_dpfull + 16 /* [2] */, bar_dsfull = bar_pfull + 16 /* [2] */,
+                 bar_accfull = bar_dsfull + 16, bar_accempty = bar_accfull + 8;
+  static_assert(2 * RS + 2 * ST + 11 == L::kNumBars, "barrier count");
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
   float* stats = reinterpret_cast<float*>(smem + L::kStats);
@@ -157,8 +159,13 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int s = 0; s < ST; ++s) { mbar_init(bar_tfull + 8 * s, 1); mbar_init(bar_tempty + 8 * s, 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(bar_sfull + 8 * s, 1); mbar_init(bar_dpfull + 8 * s, 1); }
     mbar_init(bar_sempty, kB2ComputeWarps);
-    mbar_init(bar_pfull, kB2ComputeWarps);
-    mbar_init(bar_dsfull, kB2ComputeWarps);
+    // P-ready and dS-ready barriers alternate between two by step: the compute warps can finish step g + 1 (whose
+    // scores were issued ahead) before the issuer has looked at step g, and a single barrier would then be two phases
+    // ahead of the parity the issuer waits for.  Step g + 2 cannot complete before the issuer has passed step g.
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(bar_pfull + 8 * h, kB2ComputeWarps);
+      mbar_init(bar_dsfull + 8 * h, kB2ComputeWarps);
+    }
     mbar_init(bar_accfull, 1);
     mbar_init(bar_accempty, kB2ComputeWarps);
     *abort_flag = 0;
@@ -293,17 +300,17 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               issue_s(g + 1);
               issue_dp(g + 1);                                   // the other dP buffer: read last by dQ(g - 1), issued
             }
-            if (!mbar_wait(bar_dsfull, g & 1, abort_flag, status, 68)) { ok = false; break; }
+            if (!mbar_wait(bar_dsfull + 8 * (g & 1), (g >> 1) & 1, abort_flag, status, 68)) { ok = false; break; }
             tc_fence_after();
             issue_acc(L::kColAcc0, L::kColDp + (g & 1) * 128, t0, it == 0);          // dQ += dS K
           } else {
             if (more && !mbar_wait(bar_tfull + 8 * ((g + 1) % ST), ((g + 1) / ST) & 1, abort_flag, status, 66)) { ok = false; break; }
             if (more && SB == 2) { tc_fence_after(); issue_s(g + 1); }                // other S^T buffer: free since dV(g - 1)
-            if (!mbar_wait(bar_pfull, g & 1, abort_flag, status, 69)) { ok = false; break; }
+            if (!mbar_wait(bar_pfull + 8 * (g & 1), (g >> 1) & 1, abort_flag, status, 69)) { ok = false; break; }
             tc_fence_after();
             issue_acc(L::kColAcc1, L::kColS + (SB == 2 ? (g & 1) * 128 : 0), t1, it == 0);   // dV += P^T dO
             if (more && SB == 1) issue_s(g + 1);                                      // reuses the buffer dV(g) just read
-            if (!mbar_wait(bar_dsfull, g & 1, abort_flag, status, 68)) { ok = false; break; }
+            if (!mbar_wait(bar_dsfull + 8 * (g & 1), (g >> 1) & 1, abort_flag, status, 68)) { ok = false; break; }
             tc_fence_after();
             issue_acc(L::kColAcc0, L::kColDp, t0, it == 0);                           // dK += dS^T Q
             if (more) issue_dp(g + 1);                                                // reuses the buffer dK(g) just read
@@ -419,7 +426,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_pfull);
+          if (lane == 0) mbar_arrive(bar_pfull + 8 * (g & 1));
         }
         // ---- dS = P * (dP - delta) -> packed bf16 over this thread's part of the dP buffer
         if (!mbar_wait(bar_dpfull + 8 * db, (DB == 2 ? (g >> 1) : g) & 1, abort_flag, status, 71)) { ok = false; break; }
@@ -450,7 +457,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_dsfull);
+        if (lane == 0) mbar_arrive(bar_dsfull + 8 * (g & 1));
         if (MODE == B2_DKV && it + 1 < w.n_it) stats[((g + 1) & 1) * 256 + ct] = stat_next;
       }
       if (!ok) break;

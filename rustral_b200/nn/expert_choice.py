@@ -66,8 +66,11 @@ class ExpertChoiceRouter(Module, Trainable, Saveable):
         for e in range(c.num_experts):
             rows = ops.gather_rows(x2.contiguous(), idx[e]) if not x2.requires_grad else x2[idx[e]]
             y = expert_fn(e, rows)
-            out.index_add_(0, idx[e], y.float() * gate[e][:, None])
-            served.index_add_(0, idx[e], torch.ones_like(idx[e], dtype=torch.int32))
+            # An expert's chosen tokens are distinct (top-c of one row of the affinity matrix), so its contribution is
+            # added with a gather, an addition and a plain scatter: no floating-point atomics, and the experts are
+            # folded in index order, so the result is the same on every run.
+            out.index_put_((idx[e],), out[idx[e]] + y.float() * gate[e][:, None])
+            served.index_put_((idx[e],), served[idx[e]] + 1)
         per = [int(idx.shape[1])] * c.num_experts
         self.last_stats = ExpertChoiceStats(min(per), max(per), sum(per) / len(per), 1.0, int((served == 0).sum()))
         return out.to(x.dtype).reshape(x.shape)

@@ -10,14 +10,19 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200 with `-m gpu`)")
     config.addinivalue_line("markers", "multigpu: needs two or more CUDA devices")
+    config.addinivalue_line("markers", "perf: performance floors on a B200; selected only with `-m perf`")
 
 
 def pytest_collection_modifyitems(config, items):
-    if torch.cuda.is_available():
-        return
+    # the performance tier only runs when it is asked for by name (timing tests do not belong in a correctness run)
+    perf_selected = "perf" in (config.getoption("-m") or "")
+    skip_perf = pytest.mark.skip(reason="performance tier: select it with `-m perf` on a B200")
     skip = pytest.mark.skip(reason="no CUDA device")
+    have_gpu = torch.cuda.is_available()
     for item in items:
-        if "gpu" in item.keywords or "multigpu" in item.keywords:
+        if "perf" in item.keywords and not (perf_selected and have_gpu):
+            item.add_marker(skip_perf)
+        elif not have_gpu and ("gpu" in item.keywords or "multigpu" in item.keywords):
             item.add_marker(skip)
 
 

@@ -360,8 +360,10 @@ def test_flash_attention_two_tile_kernel_rescales_sharp_rows(cuda_status):
 @pytest.mark.parametrize("B,Sq,Sk,H,Hk,D,causal", [
     (2, 256, 256, 4, 4, 64, True), (1, 384, 384, 2, 2, 128, True), (2, 200, 200, 4, 2, 64, True),
     (1, 128, 320, 4, 1, 64, True), (2, 160, 288, 2, 2, 128, False), (1, 512, 512, 3, 3, 64, False),
+    (1, 1024, 1024, 2, 2, 64, True), (1, 640, 640, 4, 2, 128, True),
 ])
-def test_flash_attention_backward_tcgen05(B, Sq, Sk, H, Hk, D, causal, cuda_status):
+@pytest.mark.parametrize("impl", ["tc", "tc2"])
+def test_flash_attention_backward_tcgen05(B, Sq, Sk, H, Hk, D, causal, impl, cuda_status):
     q, k, v = _bf((B, Sq, H, D), 1), _bf((B, Sk, Hk, D), 2), _bf((B, Sk, Hk, D), 3)
     do = _bf((B, Sq, H, D), 4)
     qc, kc, vc = (t.float().requires_grad_() for t in (q, k, v))
@@ -369,18 +371,41 @@ def test_flash_attention_backward_tcgen05(B, Sq, Sk, H, Hk, D, causal, cuda_stat
     scale = 1 / math.sqrt(D)
     qg, kg, vg, dog = q.cuda(), k.cuda(), v.cuda(), do.cuda()
     o, lse = attn_ops.attention_forward(qg, kg, vg, causal, scale, impl="tc")
-    dq, dk, dv = attn_ops.attention_backward(dog, qg, kg, vg, o, lse, causal, scale, impl="tc")
+    dq, dk, dv = attn_ops.attention_backward(dog, qg, kg, vg, o, lse, causal, scale, impl=impl)
     _close(dq, qc.grad, tol=3e-2, what="tc dq")
     _close(dk, kc.grad, tol=3e-2, what="tc dk")
     _close(dv, vc.grad, tol=3e-2, what="tc dv")
     # bit-reproducible: no atomics anywhere in the backward pass
-    dq2, dk2, dv2 = attn_ops.attention_backward(dog, qg, kg, vg, o, lse, causal, scale, impl="tc")
+    dq2, dk2, dv2 = attn_ops.attention_backward(dog, qg, kg, vg, o, lse, causal, scale, impl=impl)
     assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
     # the mma.sync path gives the same gradients within rounding
     dq3, dk3, dv3 = attn_ops.attention_backward(dog, qg, kg, vg, o, lse, causal, scale, impl="mma")
     _close(dq, dq3, tol=3e-2, what="tc vs mma dq")
     _close(dk, dk3, tol=3e-2, what="tc vs mma dk")
     _close(dv, dv3, tol=3e-2, what="tc vs mma dv")
+
+
+@pytest.mark.parametrize("B,S,H,Hk,D,causal,lens", [
+    (3, 256, 2, 2, 64, False, [256, 100, 1]), (2, 384, 4, 2, 128, True, [384, 130]), (2, 200, 2, 2, 64, False, [200, 0]),
+])
+def test_flash_attention_key_padding_lengths(B, S, H, Hk, D, causal, lens, cuda_status):
+    """Per-sequence key counts (a key-padding mask): keys at or past a sequence's length get no weight and no gradient;
+    a sequence of length 0 yields zero output and zero gradients."""
+    q, k, v, do = _bf((B, S, H, D), 1), _bf((B, S, Hk, D), 2), _bf((B, S, Hk, D), 3), _bf((B, S, H, D), 4)
+    L = torch.tensor(lens, dtype=torch.int32)
+    qc, kc, vc = (t.float().requires_grad_() for t in (q, k, v))
+    ref = attn_ops.attention_reference(qc, kc, vc, causal, None, L)
+    (ref * do.float()).sum().backward()
+    scale = 1 / math.sqrt(D)
+    qg, kg, vg, dog, Lg = q.cuda(), k.cuda(), v.cuda(), do.cuda(), L.cuda()
+    o, lse = attn_ops.attention_forward(qg, kg, vg, causal, scale, kv_lens=Lg)
+    _close(o, ref, tol=2e-2, what="kv_lens o")
+    dq, dk, dv = attn_ops.attention_backward(dog, qg, kg, vg, o, lse, causal, scale, kv_lens=Lg)
+    _close(dq, qc.grad, tol=3e-2, what="kv_lens dq")
+    _close(dk, kc.grad, tol=3e-2, what="kv_lens dk")
+    _close(dv, vc.grad, tol=3e-2, what="kv_lens dv")
+    for b, n in enumerate(lens):
+        assert not dk[b, n:].any() and not dv[b, n:].any(), "padded keys received a gradient"
 
 
 def test_bounded_wait_expires_and_reports_without_losing_the_context():
