@@ -47,6 +47,9 @@ struct EpiParams {
   int accumulate;
   float alpha;
   int staged;   // bf16 output goes through a per-warp shared-memory tile and leaves as whole 128/256-byte row segments
+  const float* row_scale;   // fp32 [M] or nullptr: multiplies row i of the accumulator (8-bit operands: per-token scale)
+  const float* col_scale;   // fp32 [N] or nullptr: multiplies column j (per-output-channel weight scale)
+  int fp8_b_format;         // 8-bit operands: format of B in the instruction descriptor (0 = e4m3, 1 = e5m2); A is e4m3
 };
 
 // Grouped (mixture-of-experts) execution over a permuted token buffer whose expert segments are whole tiles.
@@ -126,6 +129,26 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& ep, uint32_t (&r)
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
   const bool full = (col0 + 32 <= N);
+
+  if (ep.row_scale != nullptr) {
+    const float rs = __ldg(ep.row_scale + row);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= rs;
+  }
+  if (ep.col_scale != nullptr) {
+    if (full) {
+      const float4* cp = reinterpret_cast<const float4*>(ep.col_scale + col0);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float4 c = __ldg(cp + q);
+        v[q * 4 + 0] *= c.x; v[q * 4 + 1] *= c.y; v[q * 4 + 2] *= c.z; v[q * 4 + 3] *= c.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < N) v[j] *= __ldg(ep.col_scale + col0 + j);
+    }
+  }
 
   if (ep.bias != nullptr) {
     if (full) {
@@ -281,7 +304,9 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& ep, uint32_t (&r
   epilogue_store(ep, v, row, col0, N);
 }
 
-template <int A_MN, int B_MN, int BLOCK_N, int STAGES>
+// FP8 = 1: both operands hold e4m3 bytes (K-major only).  A 128-byte swizzle row then carries 128 elements, so K, lda
+// and ldb arrive halved (in units of two bytes) and only the TMA coordinates, which count elements, are doubled back.
+template <int A_MN, int B_MN, int BLOCK_N, int STAGES, int FP8 = 0>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
                  int K, int group_m, int num_splits, int kb_per_split, long long d_split_stride, EpiParams ep,
@@ -413,14 +438,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t sa = smem_base + s * L::kStageBytes;
           const uint32_t sb = sa + L::kABytes;
           if (A_MN == 0) {
-            tma_load_2d(sa, &tmA, kb * kBlockK, m_blk * kBlockM, full);
+            tma_load_2d(sa, &tmA, kb * kBlockK * (FP8 ? 2 : 1), m_blk * kBlockM, full);
           } else {
 #pragma unroll
             for (int j = 0; j < kBlockM / 64; ++j)
               tma_load_2d(sa + j * (kBlockK * 128), &tmA, m_blk * kBlockM + j * 64, kb * kBlockK, full);
           }
           if (B_MN == 0) {
-            tma_load_2d(sb, &tmB, kb * kBlockK, b_row_off + n_blk * BLOCK_N, full);
+            tma_load_2d(sb, &tmB, kb * kBlockK * (FP8 ? 2 : 1), b_row_off + n_blk * BLOCK_N, full);
           } else {
 #pragma unroll
             for (int j = 0; j < BLOCK_N / 64; ++j)
@@ -432,7 +457,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     if (lane == 0) {
       // ------------------------------------------------------------------ MMA issuer
-      constexpr uint32_t idesc = umma_idesc_bf16(kBlockM, BLOCK_N, A_MN, B_MN);
+      const uint32_t idesc = FP8 ? (umma_idesc_e4m3(kBlockM, BLOCK_N) | (static_cast<uint32_t>(ep.fp8_b_format) << 10))
+                                 : umma_idesc_bf16(kBlockM, BLOCK_N, A_MN, B_MN);
       uint32_t it = 0, t = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_units && ok; tile += gridDim.x, ++t) {
@@ -456,7 +482,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                      : umma_smem_desc_sw128(sa + k * (kUmmaK * 2), 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc_sw128(sb + k * (kUmmaK * 128), kBlockK * 128, 1024)
                                      : umma_smem_desc_sw128(sb + k * (kUmmaK * 2), 16, 1024);
-            umma_bf16_ss(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+            if (FP8) umma_f8_ss(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+            else umma_bf16_ss(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(bar_empty + 8 * s);   // frees the smem stage once these MMAs have read it
         }
@@ -652,7 +679,7 @@ struct SmemLayoutPair {
   static constexpr int kTotalStaged = kStagingOffset + kNumEpilogueWarps * kStagingBytesPerWarp;
 };
 
-template <int A_MN, int B_MN, int BLOCK_N, int STAGES>
+template <int A_MN, int B_MN, int BLOCK_N, int STAGES, int FP8 = 0>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
                       int K, int group_m, int num_splits, int kb_per_split, long long d_split_stride, EpiParams ep,
@@ -740,14 +767,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           const uint32_t sa = smem_base + s * L::kStageBytes;
           const uint32_t sb = sa + L::kABytes;
           if (A_MN == 0) {
-            tma_load_2d_pair(sa, &tmA, kb * kBlockK, a_row, full);
+            tma_load_2d_pair(sa, &tmA, kb * kBlockK * (FP8 ? 2 : 1), a_row, full);
           } else {
 #pragma unroll
             for (int j = 0; j < kBlockM / 64; ++j)
               tma_load_2d_pair(sa + j * (kBlockK * 128), &tmA, a_row + j * 64, kb * kBlockK, full);
           }
           if (B_MN == 0) {
-            tma_load_2d_pair(sb, &tmB, kb * kBlockK, b_row, full);
+            tma_load_2d_pair(sb, &tmB, kb * kBlockK * (FP8 ? 2 : 1), b_row, full);
           } else {
 #pragma unroll
             for (int j = 0; j < BLOCK_N / 2 / 64; ++j)
@@ -759,7 +786,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   } else if (warp == 1) {
     if (lane == 0 && cta_rank == 0) {
       // ------------------------------------------------------------------ MMA issuer (leader CTA only)
-      constexpr uint32_t idesc = umma_idesc_bf16(kPairM, BLOCK_N, A_MN, B_MN);
+      const uint32_t idesc = FP8 ? (umma_idesc_e4m3(kPairM, BLOCK_N) | (static_cast<uint32_t>(ep.fp8_b_format) << 10))
+                                 : umma_idesc_bf16(kPairM, BLOCK_N, A_MN, B_MN);
       uint32_t it = 0, t = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_units && ok; tile += num_clusters, ++t) {
@@ -781,7 +809,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                                      : umma_smem_desc_sw128(sa + k * (kUmmaK * 2), 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc_sw128(sb + k * (kUmmaK * 128), kBlockK * 128, 1024)
                                      : umma_smem_desc_sw128(sb + k * (kUmmaK * 2), 16, 1024);
-            umma_bf16_ss_pair(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+            if (FP8) umma_f8_ss_pair(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+            else umma_bf16_ss_pair(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit_pair(bar_empty + 8 * s, 3);     // both CTAs may refill this stage
         }
@@ -960,10 +989,10 @@ bool staged_store_default() {
   return v == 1;
 }
 
-template <int A_MN, int B_MN, int BLOCK_N, int STAGES>
+template <int A_MN, int B_MN, int BLOCK_N, int STAGES, int FP8 = 0>
 int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, int grid, int splits, cudaStream_t stream) {
   using L = rb::SmemLayout<BLOCK_N, STAGES>;
-  auto kern = rb::gemm_bf16_kernel<A_MN, B_MN, BLOCK_N, STAGES>;
+  auto kern = rb::gemm_bf16_kernel<A_MN, B_MN, BLOCK_N, STAGES, FP8>;
   // Staged (coalesced) stores: plain bf16 outputs whose rows are whole 16-byte chunks.  Always on for peer stores.
   const bool can_stage = !g.out_f32 && !g.accumulate && splits <= 1 && (g.N % 8 == 0) && g.group_mode != 2 &&
                          L::kTotalStaged + 1024 <= 232448;
@@ -985,8 +1014,12 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
   ep.aux_out = reinterpret_cast<__nv_bfloat16*>(g.aux_out); ep.ld_aux_out = g.ld_aux_out;
   ep.act = g.act; ep.out_f32 = g.out_f32; ep.accumulate = g.accumulate; ep.alpha = g.alpha;
   ep.staged = staged ? 1 : 0;
+  ep.row_scale = reinterpret_cast<const float*>(g.a_scale);
+  ep.col_scale = reinterpret_cast<const float*>(g.b_scale);
+  ep.fp8_b_format = g.ab_fp8 == 2 ? 1 : 0;
   const int group_m = g.group_m > 0 ? g.group_m : 8;
-  const int num_kb = (g.K + rb::kBlockK - 1) / rb::kBlockK;
+  const int k_units = FP8 ? (g.K + 1) / 2 : g.K;          // the kernel counts K in two-byte units
+  const int num_kb = (k_units + rb::kBlockK - 1) / rb::kBlockK;
   int kb_per = num_kb;
   long long slab = 0;
   if (splits > 1) {
@@ -1012,7 +1045,7 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
     peer.a_peer[r] = reinterpret_cast<const __nv_bfloat16*>(g.peer_ptrs[r]);
     peer.d_peer[r] = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(g.peer_ptrs[r]));
   }
-  kern<<<grid, rb::kNumThreads, smem, stream>>>(*ta, *tb, g.M, g.N, g.K, group_m, splits, kb_per, slab, ep, grp, peer,
+  kern<<<grid, rb::kNumThreads, smem, stream>>>(*ta, *tb, g.M, g.N, k_units, group_m, splits, kb_per, slab, ep, grp, peer,
                                                 rbhost::status_ptr());
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || splits <= 1) return static_cast<int>(e);
@@ -1044,12 +1077,12 @@ bool pair_kernel_enabled() {
   return v == 1;
 }
 
-template <int A_MN, int B_MN>
+template <int A_MN, int B_MN, int FP8 = 0>
 int launch_pair(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb_half, int clusters, int splits,
                 cudaStream_t stream) {
   constexpr int BLOCK_N = 256, STAGES = 6;
   using L = rb::SmemLayoutPair<BLOCK_N, STAGES>;
-  auto kern = rb::gemm_bf16_pair_kernel<A_MN, B_MN, BLOCK_N, STAGES>;
+  auto kern = rb::gemm_bf16_pair_kernel<A_MN, B_MN, BLOCK_N, STAGES, FP8>;
   const bool staged = !g.out_f32 && !g.accumulate && splits <= 1 && (g.N % 8 == 0) && staged_store_default() &&
                       L::kTotalStaged + 1024 <= 232448;
   const int smem = (staged ? L::kTotalStaged : L::kTotal) + 1024;
@@ -1068,8 +1101,12 @@ int launch_pair(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* t
   ep.aux_out = reinterpret_cast<__nv_bfloat16*>(g.aux_out); ep.ld_aux_out = g.ld_aux_out;
   ep.act = g.act; ep.out_f32 = g.out_f32; ep.accumulate = g.accumulate; ep.alpha = g.alpha;
   ep.staged = staged ? 1 : 0;
+  ep.row_scale = reinterpret_cast<const float*>(g.a_scale);
+  ep.col_scale = reinterpret_cast<const float*>(g.b_scale);
+  ep.fp8_b_format = g.ab_fp8 == 2 ? 1 : 0;
   const int group_m = g.group_m > 0 ? g.group_m : 4;      // in 256-row units
-  const int num_kb = (g.K + rb::kBlockK - 1) / rb::kBlockK;
+  const int k_units = FP8 ? (g.K + 1) / 2 : g.K;
+  const int num_kb = (k_units + rb::kBlockK - 1) / rb::kBlockK;
   int kb_per = num_kb;
   long long slab = 0;
   if (splits > 1) {
@@ -1090,7 +1127,7 @@ int launch_pair(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* t
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *ta, *tb_half, g.M, g.N, g.K, group_m, splits, kb_per, slab, ep,
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *ta, *tb_half, g.M, g.N, k_units, group_m, splits, kb_per, slab, ep,
                                      rbhost::status_ptr());
   if (e != cudaSuccess || splits <= 1) return static_cast<int>(e);
   const long long n4 = slab / 4;
@@ -1119,6 +1156,7 @@ void pick_plan(const RbGemmArgs& g, int sms, int& bn_out, int& splits_out) {
   const int cands[4] = {256, 192, 128, 64};
   const int split_cands[7] = {1, 2, 3, 4, 6, 8, 12};
   const bool can_split = g.group_mode == 0 && g.peer_mode == 0 && g.workspace != nullptr && g.act == RB_ACT_NONE && !g.aux_out &&
+                         !g.a_scale && !g.b_scale && !g.ab_fp8 &&
                          (g.N % 4 == 0) && (static_cast<long long>(g.M) * g.N % 4 == 0) && (!g.residual || (g.ldr % 4 == 0));
   const bool pair_ok = g.peer_mode == 0 && g.group_mode == 0 && g.M > 128 && g.max_ctas == 0 && pair_kernel_enabled();
   long long best = -1;
@@ -1141,6 +1179,35 @@ void pick_plan(const RbGemmArgs& g, int sms, int& bn_out, int& splits_out) {
   }
 }
 
+// 8-bit floating-point operands: byte tensor maps with 128-element boxes, K-major only.
+int gemm_fp8(const RbGemmArgs& g, int sms, int bn, int splits, cudaStream_t stream) {
+  if (g.a_mn_major || g.b_mn_major || g.peer_mode != 0 || g.group_mode == 2) return -12;
+  if ((g.lda & 15) || (g.ldb & 15) || (g.K & 15)) return -2;
+  int err = 0;
+  const CUtensorMap* ta = rbhost::get_tmap_2d(g.a, 1, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, 128, 128, 1, &err);
+  if (!ta) return err ? err : -5;
+  const uint64_t b_experts = g.group_mode == 1 ? (uint64_t)g.num_experts : 1;
+  if (bn == 256 && g.group_mode == 0 && g.M > 128 && g.max_ctas == 0 && pair_kernel_enabled()) {
+    const CUtensorMap* tb_half = rbhost::get_tmap_2d(g.b, 1, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, 128, 128, 1, &err);
+    if (!tb_half) return err ? err : -5;
+    const long long tiles2 = (long long)((g.M + 255) / 256) * ((g.N + 255) / 256) * splits;
+    const int max_clusters = sms / 2;
+    const int clusters = static_cast<int>(tiles2 < max_clusters ? tiles2 : max_clusters);
+    return launch_pair<0, 0, 1>(g, ta, tb_half, clusters, splits, stream);
+  }
+  const CUtensorMap* tb = rbhost::get_tmap_2d(g.b, 1, (uint64_t)g.K, (uint64_t)g.N * b_experts, (uint64_t)g.ldb, 128, (uint32_t)bn, 1, &err);
+  if (!tb) return err ? err : -5;
+  const long long tiles = (long long)((g.M + 127) / 128) * ((g.N + bn - 1) / bn) * splits;
+  int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;
+  switch (bn) {
+    case 256: return launch<0, 0, 256, 4, 1>(g, ta, tb, grid, splits, stream);
+    case 192: return launch<0, 0, 192, 5, 1>(g, ta, tb, grid, splits, stream);
+    case 128: return launch<0, 0, 128, 6, 1>(g, ta, tb, grid, splits, stream);
+    default: return launch<0, 0, 64, 8, 1>(g, ta, tb, grid, splits, stream);
+  }
+}
+
 }  // namespace
 
 RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
@@ -1148,9 +1215,8 @@ RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return -1;
   // TMA needs 16-byte aligned bases and pitches
-  if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15) || (g.lda & 7) ||
-      (g.ldb & 7))
-    return -2;
+  if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15)) return -2;
+  if (!g.ab_fp8 && ((g.lda & 7) || (g.ldb & 7))) return -2;
   // vector epilogue accesses need 16-byte aligned rows
   const int dalign = g.out_f32 ? 4 : 8;
   if ((g.ldd % dalign) || (reinterpret_cast<uintptr_t>(g.d) & 15)) return -3;
@@ -1158,6 +1224,8 @@ RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
   if (g.aux_in && ((g.ld_aux_in & 7) || (reinterpret_cast<uintptr_t>(g.aux_in) & 15))) return -3;
   if (g.aux_out && ((g.ld_aux_out & 7) || (reinterpret_cast<uintptr_t>(g.aux_out) & 15))) return -3;
   if (g.bias && (reinterpret_cast<uintptr_t>(g.bias) & 15)) return -3;
+  if (g.a_scale && (reinterpret_cast<uintptr_t>(g.a_scale) & 3)) return -3;
+  if (g.b_scale && (reinterpret_cast<uintptr_t>(g.b_scale) & 15)) return -3;
   if ((g.act >= RB_ACT_DGELU && g.act <= RB_ACT_MUL) && !g.aux_in) return -4;
 
   if (g.group_mode < 0 || g.group_mode > 2) return -8;
@@ -1193,6 +1261,8 @@ RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
   int bn = 128, splits = 1;
   pick_plan(g, sms, bn, splits);
   if (g.splits > 1 && splits != g.splits) return -7;   // a forced split count that cannot be honoured
+
+  if (g.ab_fp8) return gemm_fp8(g, sms, bn, splits, stream);
 
   int err = 0;
   const CUtensorMap* ta = g.a_mn_major

@@ -54,6 +54,12 @@ typedef struct RbGemmArgs {
   void* ready_flags;           // mode 1 / 3: local u32 counters, one per 128-row block of the gathered operand
   const void* peer_ptrs[8];    // mode 1 / 3: every rank's shard [rows_per_rank, K] of A / B; mode 2: every rank's receive buffer
                                //         [peer_world][rows_per_rank, ldd] (this rank writes slot peer_rank)
+  // 8-bit floating-point operands (tcgen05 kind::f8f6f4, fp32 accumulation): a and b hold e4m3 bytes, both K-major,
+  // lda / ldb / K count bytes (multiples of 16).  Plain and grouped mode 1 problems only.  For every operand type the
+  // accumulator of row i, column j is multiplied by a_scale[i] * b_scale[j] (each may be NULL) before the bias.
+  int ab_fp8;                  // 0: bf16 operands; 1: a and b e4m3; 2: a e4m3, b e5m2
+  const void* a_scale;         // fp32 [M] or NULL: one scale per row of A (per token)
+  const void* b_scale;         // fp32 [N] or NULL: one scale per row of B (per output channel)
 } RbGemmArgs;
 
 // Returns 0 on success, a negative code for rejected arguments, a positive cudaError otherwise.

@@ -1,6 +1,7 @@
 """Micro-benchmarks of single kernels with roofline fractions.
 
     python -m rustral_b200.bench.kernels gemm --m 32768 --n 2304 --k 768 [--act gelu] [--iters 10]
+    python -m rustral_b200.bench.kernels gemm-fp8 --m 8192 --n 8192 --k 8192
     python -m rustral_b200.bench.kernels attention --batch 32 --seq 1024 --heads 12 --head-dim 64 [--impl tc2|tc|mma] [--backward]
     python -m rustral_b200.bench.kernels norm --rows 32768 --n 768
     python -m rustral_b200.bench.kernels adam --numel 124000000
@@ -76,6 +77,26 @@ def bench_gemm(a):
     nbytes = 2.0 * (a.m * a.k + a.n * a.k + a.m * a.n * (2 if pre is not None else 1))
     return report("gemm_bf16_tcgen05", ms, 2.0 * a.m * a.n * a.k, nbytes,
                   {"m": a.m, "n": a.n, "k": a.k, "act": a.act})
+
+
+def bench_gemm_fp8(a):
+    """e4m3 x e4m3 product with per-row and per-column scales and a bf16 output, against the bf16 kernel on the same shape."""
+    from ..ops import quant as Q
+    from ..ops.matmul import gemm
+    dev = "cuda"
+    x = torch.randn(a.m, a.k, device=dev).bfloat16()
+    w = (torch.randn(a.n, a.k, device=dev) * 0.02).bfloat16()
+    a8, sa = Q.quantize_fp8_rows(x)
+    b8, sb = Q.quantize_fp8_rows(w)
+    out = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=dev)
+    ms = timed(lambda: Q.gemm_fp8(a8, sa, b8, sb, out=out, block_n=a.block_n), a.warmup, a.iters)
+    ms16 = timed(lambda: gemm(x, w, out=out), a.warmup, a.iters)
+    msq = timed(lambda: Q.quantize_fp8_rows(x, out=a8, scales=sa), a.warmup, a.iters)
+    flops = 2.0 * a.m * a.n * a.k
+    return report("gemm_e4m3_tcgen05", ms, flops, 0,
+                  {"m": a.m, "n": a.n, "k": a.k, "bf16_us": round(ms16 * 1e3, 2), "bf16_tflops": round(flops / ms16 / 1e9, 1),
+                   "speedup_over_bf16": round(ms16 / ms, 3), "quantize_rows_us": round(msq * 1e3, 2),
+                   "quantize_gbs": round(3.0 * a.m * a.k / msq / 1e6, 1)})
 
 
 def bench_attention(a):
@@ -165,6 +186,11 @@ def main(argv=None):
     g.add_argument("--act", default="none")
     g.add_argument("--bias", action="store_true")
     g.add_argument("--block-n", type=int, default=0)
+    g8 = sub.add_parser("gemm-fp8")
+    g8.add_argument("--m", type=int, default=8192)
+    g8.add_argument("--n", type=int, default=8192)
+    g8.add_argument("--k", type=int, default=8192)
+    g8.add_argument("--block-n", type=int, default=0)
     t = sub.add_parser("attention")
     t.add_argument("--batch", type=int, default=32)
     t.add_argument("--seq", type=int, default=1024)
@@ -189,7 +215,7 @@ def main(argv=None):
     pg.add_argument("--head-dim", type=int, default=128)
     pg.add_argument("--block-size", type=int, default=16)
     a = ap.parse_args(argv)
-    return {"paged": bench_paged, "gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam}[a.op](a)
+    return {"paged": bench_paged, "gemm": bench_gemm, "gemm-fp8": bench_gemm_fp8, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam}[a.op](a)
 
 
 if __name__ == "__main__":

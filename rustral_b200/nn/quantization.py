@@ -1,6 +1,15 @@
 """Weight quantization: INT8 (per-tensor / per-channel / asymmetric), INT4 group-wise, FP8 formats, fake-quant for QAT
-(crates/nn/src/quantization.rs:27-560).  Weights are stored quantized; the forward pass dequantizes into the compute
-dtype and runs the tensor-core GEMM (the reference dequantizes to f32 and calls a plain matmul)."""
+(crates/nn/src/quantization.rs:27-560).  Weights are stored quantized (the reference dequantizes to f32 and calls a
+plain matmul).  Forward pass on CUDA tensors:
+
+* FP8 (e4m3 / e5m2 weights, one scale per output channel): the tokens are quantised to e4m3 with one scale per row by
+  `rb_quantize_fp8_rows`, the product runs on `tcgen05.mma kind::f8f6f4` and the scales and the bias are applied in the
+  GEMM epilogue (`ops.quant.gemm_fp8`).
+* INT8: `rb_dequant_int8_bf16` expands `q - zero_point` to bf16 (exact), the bf16 tensor-core GEMM multiplies the scale
+  back in its epilogue (per tensor: alpha; per channel: column scales).
+* INT4 groups: `rb_dequant_int4_bf16` expands to bf16, then the bf16 GEMM.
+
+CPU tensors compute the same quantities in fp32."""
 from __future__ import annotations
 
 import enum
@@ -65,22 +74,60 @@ class QuantParams:
 
 
 class QuantizedLinear(Module):
-    """int8 weights [out, in] with per-tensor or per-output-channel scales."""
+    """8-bit weights [out, in]: int8 with a per-tensor or per-output-channel scale (and zero point), or e4m3 / e5m2 bytes
+    with one scale per output channel."""
 
-    def __init__(self, qweight, params: QuantParams, bias=None, compute_dtype=torch.float32):
-        self.qweight, self.params, self.bias, self.compute_dtype = qweight, params, bias, compute_dtype
+    def __init__(self, qweight, params: QuantParams, bias=None, compute_dtype=torch.float32,
+                 scheme: QuantizationScheme = QuantizationScheme.INT8):
+        self.qweight, self.params, self.bias, self.compute_dtype, self.scheme = qweight, params, bias, compute_dtype, scheme
 
     @classmethod
     def from_linear(cls, linear, scheme: QuantizationScheme = QuantizationScheme.INT8):
         w = linear.weight.tensor.detach()
+        bias = None if linear.bias is None else linear.bias.tensor.detach()
+        if scheme in (QuantizationScheme.FP8_E4M3, QuantizationScheme.FP8_E5M2):
+            f = w.float()
+            fmax, fdt = (448.0, torch.float8_e4m3fn) if scheme is QuantizationScheme.FP8_E4M3 else (57344.0, torch.float8_e5m2)
+            amax = f.abs().amax(1)
+            scale = torch.where(amax > 0, amax / fmax, torch.ones_like(amax))
+            q = (f / scale[:, None]).clamp(-fmax, fmax).to(fdt).view(torch.uint8)
+            return cls(q, QuantParams(scale.contiguous(), torch.zeros_like(scale)), bias, w.dtype, scheme)
         per_ch = scheme is QuantizationScheme.INT8_PER_CHANNEL
         p = QuantParams.from_tensor(w, symmetric=scheme is not QuantizationScheme.INT8_ASYMMETRIC, dim=1 if per_ch else None)
-        return cls(p.quantize(w), p, None if linear.bias is None else linear.bias.tensor.detach(), w.dtype)
+        return cls(p.quantize(w), p, bias, w.dtype, scheme)
+
+    @property
+    def is_fp8(self) -> bool:
+        return self.scheme in (QuantizationScheme.FP8_E4M3, QuantizationScheme.FP8_E5M2)
 
     def dequantized_weight(self):
+        if self.is_fp8:
+            fdt = torch.float8_e4m3fn if self.scheme is QuantizationScheme.FP8_E4M3 else torch.float8_e5m2
+            return (self.qweight.view(fdt).float() * self.params.scale[:, None]).to(self.compute_dtype)
         return self.params.dequantize(self.qweight, self.compute_dtype)
 
     def forward(self, x, ctx: ForwardCtx | None = None):
+        from ..ops import quant as Q
+        x2 = x.reshape(-1, x.shape[-1])
+        out_f = self.qweight.shape[0]
+        if self.is_fp8:
+            # tokens -> e4m3 with one scale per row; product on the 8-bit tensor-core path
+            a8, a_scale = Q.quantize_fp8_rows(x2)
+            bias = None if self.bias is None else (self.bias.to(torch.bfloat16) if x.is_cuda else self.bias)
+            y = Q.gemm_fp8(a8, a_scale, self.qweight, self.params.scale, bias=bias,
+                           out_dtype=torch.bfloat16 if x.is_cuda else x.dtype, b_e5m2=self.scheme is QuantizationScheme.FP8_E5M2)
+            return y.to(x.dtype).reshape(*x.shape[:-1], out_f)
+        if x.is_cuda and not self.is_fp8 and self.qweight.shape[1] % 16 == 0:
+            zp = self.params.zero_point
+            wq = Q.dequant_int8(self.qweight, None if not bool((zp != 0).any()) else zp)       # q - z in bf16, exact
+            scale = self.params.scale.reshape(-1).float()
+            xb = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
+            bias = None if self.bias is None else self.bias.to(torch.bfloat16)
+            if scale.numel() == 1:
+                y = ops.gemm(xb.contiguous(), wq, bias=bias, alpha=float(scale))
+            else:
+                y = ops.gemm(xb.contiguous(), wq, bias=bias, col_scale=scale.contiguous())
+            return y.to(x.dtype).reshape(*x.shape[:-1], out_f)
         return ops.linear(x, self.dequantized_weight().contiguous(), self.bias)
 
     def memory_bytes(self) -> int:
@@ -117,6 +164,14 @@ class GPTQLinear(Module):
         return g.view(out, inn).to(self.compute_dtype)
 
     def forward(self, x, ctx: ForwardCtx | None = None):
+        if x.is_cuda and self.shape[1] % 32 == 0 and self.group_size % 32 == 0:
+            from ..ops import quant as Q
+            w = Q.dequant_int4(self.packed, self.scales, self.group_size)                        # bf16, one kernel
+            x2 = x.reshape(-1, x.shape[-1])
+            xb = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
+            bias = None if self.bias is None else self.bias.to(torch.bfloat16)
+            y = ops.gemm(xb.contiguous(), w, bias=bias)
+            return y.to(x.dtype).reshape(*x.shape[:-1], self.shape[0])
         return ops.linear(x, self.dequantized_weight().contiguous(), self.bias)
 
     def memory_bytes(self) -> int:

@@ -104,8 +104,9 @@ def set_plan_hook(fn) -> None:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, act: str = "none",
          residual=None, aux_in=None, aux_out=None, out=None, out_dtype=None, accumulate: bool = False,
          alpha: float = 1.0, block_n: int = 0, group_m: int = 0, max_ctas: int = 0, splits: int = 0,
-         peer: dict | None = None) -> torch.Tensor:
-    """`peer` selects the tensor-parallel modes of the kernel (see parallel/fused_tp.py): a dict with `mode`
+         peer: dict | None = None, row_scale=None, col_scale=None) -> torch.Tensor:
+    """`row_scale` (fp32 [M]) / `col_scale` (fp32 [N]) multiply the accumulator's rows / columns before the bias (weight
+    scales of quantised layers).  `peer` selects the tensor-parallel modes of the kernel (see parallel/fused_tp.py): a dict with `mode`
     (1: remote row blocks of A are pulled from the peers' shards inside the kernel; 2: output row blocks are
     stored into their owner's receive slot), `world`, `rank`, `rows_per_rank`, `epoch`, `ready_flags` (pointer,
     mode 1) and `peer_ptrs` (one device address per rank)."""
@@ -121,6 +122,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if act not in N.ACT:
         raise ValueError(f"gemm: unknown epilogue activation {act!r}")
     if not a.is_cuda:
+        if row_scale is not None or col_scale is not None:
+            a = a.float().t() if a_mn else a.float()
+            a_mn = False
+            if row_scale is not None:
+                a = a * row_scale.float()[:, None]
+            if col_scale is not None:
+                b = (b.float().t() if b_mn else b.float()) * col_scale.float()[:, None]
+                b_mn = False
         return _gemm_cpu(a, b, a_mn, b_mn, bias, act, residual, aux_in, aux_out, out, out_dtype, accumulate, alpha)
 
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
@@ -156,6 +165,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     g.accumulate = int(accumulate)
     g.alpha = alpha
     g.block_n, g.group_m, g.max_ctas, g.splits = block_n, group_m, max_ctas, splits
+    for t, n_, nm in ((row_scale, M, "row_scale"), (col_scale, Nn, "col_scale")):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != n_ or not t.is_contiguous() or t.device != a.device):
+            raise TypeError(f"gemm: {nm} must be a contiguous fp32 vector of {n_} elements on the operands' device")
+    g.a_scale, g.b_scale = N.ptr(row_scale), N.ptr(col_scale)
+    if row_scale is not None or col_scale is not None:
+        splits = g.splits = 1                    # the scales are applied by the GEMM's own epilogue
     if peer is not None:
         g.peer_mode, g.peer_world, g.peer_rank = peer["mode"], peer["world"], peer["rank"]
         g.rows_per_rank, g.peer_epoch = peer["rows_per_rank"], peer["epoch"] & 0xFFFFFFFF

@@ -4,6 +4,11 @@ inter-token latency and output tokens/s.
     python -m rustral_b200.serve.bench_serving --model llama-8b --layers 4 --requests 64 --rate 8
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29720 \
         -m rustral_b200.serve.bench_serving --model llama-8b --tp 8 --requests 2000 --rate 8
+    python -m rustral_b200.serve.bench_serving --model llama-8b --layers 8 --requests 300 --rates 8 16 32 64
+
+`--rates` runs the workload once per arrival rate (ascending) and stops after the first rate whose p99 time to first
+token exceeds `--ttft-limit-ms`: below that point tokens/s follows the offered load, at it the engine is saturated and
+tokens/s is its capacity.  `--prefill-chunk` is the number of prompt tokens a step processes besides its decode batch.
 
 With `--tp N` every rank runs the same engine on its shard of the model (one-shot peer-memory all-reduce after the
 attention-output and down projections, all-gather of the vocabulary-sharded logits); rank 0's clock decides when a
@@ -37,6 +42,9 @@ def main(argv=None):
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--time-limit", type=float, default=3600.0)
+    ap.add_argument("--rates", type=float, nargs="+", default=None, help="arrival-rate sweep (requests/s), ascending")
+    ap.add_argument("--ttft-limit-ms", type=float, default=1000.0, help="the sweep stops once p99 TTFT exceeds this")
+    ap.add_argument("--prefill-chunk", type=int, default=2048, help="prompt tokens per step (0: whole prompts, one pass each)")
     a = ap.parse_args(argv)
     over = {"n_layer": a.layers} if a.layers else {}
     cfg = preset(a.model, **over)
@@ -50,7 +58,7 @@ def main(argv=None):
         if dist.get_world_size() != a.tp:
             raise SystemExit(f"--tp {a.tp} but WORLD_SIZE={dist.get_world_size()}")
         from ..parallel.tp_inference import TPInferenceComm
-        rows = max(a.prompt[1], a.max_batch)
+        rows = max(a.prompt[1], a.max_batch, a.prefill_chunk + a.max_batch)
         tp = TPInferenceComm(None, dev, max_elems=rows * max(cfg.d_model, cfg.vocab_padded // a.tp))
         clock = tp.broadcast_scalar
     else:
@@ -61,15 +69,28 @@ def main(argv=None):
     else:
         params = None
     runner = ModelRunner(cfg, params=params, device=dev, num_blocks=a.blocks, block_size=a.page, seed=a.seed, tp=tp)
-    eng = ServingEngine(runner, max_batch_size=a.max_batch)
+    eng = ServingEngine(runner, max_batch_size=a.max_batch, prefill_chunk=a.prefill_chunk)
     # warm-up: one short request end to end
     eng.generate(list(range(1, 33)), 4)
     eng.scheduler.completed.clear()
-    m = run_poisson_workload(eng, a.requests, a.rate, tuple(a.prompt), tuple(a.output), a.seed, a.time_limit, clock)
     out = {"metric": "serving", "model": a.model, "layers": cfg.n_layer, "requests": a.requests, "rate_per_s": a.rate,
-           "page_size": a.page, "decoding": "greedy", "tp": a.tp,
+           "page_size": a.page, "decoding": "greedy", "tp": a.tp, "prefill_chunk": a.prefill_chunk, "max_batch": a.max_batch,
            "data": "synthetic uniform random prompt tokens; random-init weights"}
-    out.update(m.to_dict())
+    if a.rates:
+        sweep, saturated = [], None
+        for rate in sorted(a.rates):
+            eng.scheduler.completed.clear()
+            m = run_poisson_workload(eng, a.requests, rate, tuple(a.prompt), tuple(a.output), a.seed, a.time_limit, clock)
+            row = {"rate_per_s": rate, **m.to_dict()}
+            sweep.append(row)
+            if m.ttft_p99_ms > a.ttft_limit_ms:
+                saturated = rate
+                break
+        out.update({"sweep": sweep, "saturated_at_rate": saturated,
+                    "capacity_tokens_per_s": max(r["output_tokens_per_s"] for r in sweep)})
+    else:
+        m = run_poisson_workload(eng, a.requests, a.rate, tuple(a.prompt), tuple(a.output), a.seed, a.time_limit, clock)
+        out.update(m.to_dict())
     if a.tp > 1:
         from .. import _native
         st = torch.tensor([_native.read_status()[0]], device=dev)

@@ -37,9 +37,15 @@ def _pct(xs, q):
 
 class ServingEngine:
     def __init__(self, runner: ModelRunner, max_batch_size: int = 64, policy: SchedulingPolicy = SchedulingPolicy.FCFS,
-                 sampler: Sampler | None = None, eos_id: int | None = None):
+                 sampler: Sampler | None = None, eos_id: int | None = None, prefill_chunk: int = 2048,
+                 max_prefill_tokens: int = 8192):
+        """`prefill_chunk`: prompt tokens processed per step, summed over all requests in prefill (0: whole prompts, one
+        model pass per prompt).  A longer prompt is spread over several steps, each of which also serves the decode
+        batch, so that a long prompt delays the running requests by one chunk's time, not by the whole prompt's."""
         self.runner = runner
-        self.scheduler = Scheduler(runner.cache, max_batch_size, policy)
+        self.prefill_chunk = int(prefill_chunk)
+        self._prefill_pos: dict = {}          # request id -> prompt tokens already in the cache
+        self.scheduler = Scheduler(runner.cache, max_batch_size, policy, max_prefill_tokens=max_prefill_tokens)
         self.sampler = sampler or Sampler.greedy()
         self.eos_id = eos_id
         self.callbacks: dict = {}
@@ -65,8 +71,11 @@ class ServingEngine:
         return rid
 
     def step(self) -> dict:
-        """One iteration: schedule, run the model (prefills one by one, decodes as one batch), sample, update.
-        Returns request id -> new token."""
+        """One iteration: schedule, run the model, sample, update.  Returns request id -> new token.
+
+        With `prefill_chunk` > 0 the step is ONE model pass over up to `prefill_chunk` prompt tokens (several short
+        prompts, or the next piece of a long one) plus the decode batch; a request whose prompt is not finished yet
+        yields no token in this step.  A step without prompt work replays the decode graph."""
         sch = self.scheduler
         done_before = len(sch.completed)
         batch = sch.schedule()
@@ -74,20 +83,39 @@ class ServingEngine:
             cb = self.callbacks.pop(r.id, None)
             if cb is not None:
                 cb(r)
+        scheduled = set(batch.request_ids)
+        for rid in [rid for rid in self._prefill_pos if rid not in scheduled]:
+            del self._prefill_pos[rid]             # paused, aborted or finished: a resumed request starts over
         if len(batch) == 0:
             return {}
         outputs = {}
         vocab = self.runner.cfg.vocab_size
-        dec_ids, dec_tok, dec_len = [], [], []
+        dec_ids, dec_tok, dec_len, chunks = [], [], [], []
+        budget = self.prefill_chunk
         for rid, inp, n, pre in zip(batch.request_ids, batch.input_ids, batch.seq_lens, batch.is_prefill):
-            if pre:
-                logits = self.runner.prefill(rid, inp)
-                outputs[rid] = int(self.sampler.sample(logits[:vocab].unsqueeze(0))[0])
-            else:
+            if not pre:
                 dec_ids.append(rid)
                 dec_tok.append(inp[0])
                 dec_len.append(n)
-        if dec_ids:
+            elif self.prefill_chunk <= 0:
+                logits = self.runner.prefill(rid, inp)
+                outputs[rid] = int(self.sampler.sample(logits[:vocab].unsqueeze(0))[0])
+            elif budget > 0:
+                pos = self._prefill_pos.get(rid, 0)
+                take = min(len(inp) - pos, budget)
+                budget -= take
+                chunks.append((rid, inp[pos:pos + take], pos, pos + take == len(inp)))
+        if chunks:
+            chunk_logits, dec_logits = self.runner.step_mixed(chunks, dec_ids, dec_tok, dec_len)
+            for (rid, toks, pos, last), lg in zip(chunks, chunk_logits):
+                if last:
+                    self._prefill_pos.pop(rid, None)
+                    outputs[rid] = int(self.sampler.sample(lg[:vocab].unsqueeze(0))[0])
+                else:
+                    self._prefill_pos[rid] = pos + len(toks)
+            if dec_ids:
+                outputs.update(dict(zip(dec_ids, self.sampler.sample(dec_logits[:, :vocab]).tolist())))
+        elif dec_ids:
             logits = self.runner.decode(dec_ids, dec_tok, dec_len)
             toks = self.sampler.sample(logits[:, :vocab]).tolist()
             outputs.update(dict(zip(dec_ids, toks)))

@@ -126,6 +126,93 @@ class ModelRunner:
             self.tp.end_step()
         return logits
 
+    # ---- mixed step: prompt chunks and decode tokens through the same GEMMs ---------------------------------------------
+    @torch.no_grad()
+    def step_mixed(self, chunks: list, dec_ids: list, dec_tok: list, dec_len: list):
+        """One model pass over several prompt chunks and the decode batch.
+
+        `chunks`: list of (seq_id, tokens, start, want_logits): `tokens` are positions [start, start + len) of the
+        sequence's prefix; everything before `start` is already in the cache.  `dec_*`: as for `decode`.  All rows go
+        through the projections, the MLP and the collectives together (the weights are read once per step); attention
+        runs per part: the flash kernel for a chunk (its keys are the sequence's cached prefix, gathered from the pages,
+        plus the chunk itself; causal mask aligned to the end), the paged kernel for the decode rows.
+        Returns (list of logits [vocab_padded] or None per chunk, decode logits [len(dec_ids), vocab_padded] or None).
+        (Batched and chunked prefill of the reference's scheduler: crates/nn/src/continuous_batching.rs:248-295.)"""
+        cfg, P, dev, bs = self.cfg, self.params, self.device, self.block_size
+        H, Hk, D = self.n_head, self.n_kv_head, cfg.head_dim
+        rms = cfg.arch == "llama"
+        nd = len(dec_ids)
+        ids_h, pos_h, slot_h, spans, ctx_slots = [], [], [], [], []
+        for seq_id, tokens, start, _ in chunks:
+            table = self.cache.block_table(seq_id)
+            L = len(tokens)
+            r0 = len(ids_h)
+            ids_h += list(tokens)
+            pos_h += list(range(start, start + L))
+            slot_h += [table[p_ // bs] * bs + p_ % bs for p_ in range(start, start + L)]
+            spans.append((r0, r0 + L))
+            # cache slots of the whole visible prefix (earlier chunks and this one)
+            ctx_slots.append(None if start == 0 else
+                             torch.tensor([table[p_ // bs] * bs + p_ % bs for p_ in range(start + L)], dtype=torch.int64, device=dev))
+        rd = len(ids_h)
+        for seq_id, tok, n in zip(dec_ids, dec_tok, dec_len):
+            table = self.cache.block_table(seq_id)
+            ids_h.append(tok)
+            pos_h.append(n - 1)
+            slot_h.append(table[(n - 1) // bs] * bs + (n - 1) % bs)
+        T = len(ids_h)
+        ids = torch.tensor(ids_h, dtype=torch.int64, device=dev)
+        pos = torch.tensor(pos_h, dtype=torch.int64, device=dev)
+        slots = torch.tensor(slot_h, dtype=torch.int64, device=dev)
+        if nd:
+            width = max(len(self.cache.block_table(s_)) for s_ in dec_ids)
+            bt = self._fill_tables(dec_ids, width).to(dev)
+            ctx = torch.tensor(dec_len, dtype=torch.int32, device=dev)
+        x = self._embed(ids, pos)
+        scale = 1.0 / math.sqrt(D)
+        nb = self.cache.k[0].shape[0]
+        for l in range(cfg.n_layer):
+            p = f"layers.{l}."
+            h = self._norm(x, p + "ln1")
+            qkv = gemm(h, P.w(p + "attn.wqkv.weight"), bias=None if rms else P.w(p + "attn.wqkv.bias"))
+            if rms:
+                rope_ops.rope_(qkv, H + Hk, D, positions=pos, theta=cfg.rope_theta)
+            k2, v2 = qkv[:, H * D:(H + Hk) * D], qkv[:, (H + Hk) * D:]
+            paged_ops.kv_append(k2, v2, self.cache.k[l], self.cache.v[l], slots)
+            a = torch.empty((T, H * D), dtype=qkv.dtype, device=dev)
+            for (r0, r1), cs in zip(spans, ctx_slots):
+                L = r1 - r0
+                q = qkv[r0:r1, :H * D].view(1, L, H, D)
+                if cs is None:
+                    kk, vv = k2[r0:r1].view(1, L, Hk, D), v2[r0:r1].view(1, L, Hk, D)
+                else:
+                    kk = ops.gather_rows(self.cache.k[l].view(nb * bs, Hk * D), cs).view(1, -1, Hk, D)
+                    vv = ops.gather_rows(self.cache.v[l].view(nb * bs, Hk * D), cs).view(1, -1, Hk, D)
+                if dev.type == "cuda":
+                    attn_ops.attention_forward(q, kk, vv, True, scale, out=a[r0:r1].view(1, L, H, D), want_lse=False)
+                else:
+                    a[r0:r1] = attn_ops.attention_reference(q, kk, vv, True, scale).reshape(L, H * D)
+            if nd:
+                paged_ops.paged_attention_decode(qkv[rd:, :H * D], self.cache.k[l], self.cache.v[l], bt, ctx, scale, out=a[rd:])
+            x = self._row_parallel(a, P.w(p + "attn.wo.weight"), None if rms else P.w(p + "attn.wo.bias"), x)
+            x = self._mlp(x, p)
+        # logits only where a token is sampled: the last row of every chunk that completes its prompt, and the decode rows
+        want = [r1 - 1 for (r0, r1), c in zip(spans, chunks) if c[3]]
+        rows = want + list(range(rd, T))
+        chunk_logits, dec_logits = [None] * len(chunks), None
+        if rows:
+            sel = x if rows == list(range(T)) else x.index_select(0, torch.tensor(rows, dtype=torch.int64, device=dev))
+            logits = self._head(sel.contiguous())
+            it = iter(range(len(want)))
+            for i, c in enumerate(chunks):
+                if c[3]:
+                    chunk_logits[i] = logits[next(it)]
+            if nd:
+                dec_logits = logits[len(want):]
+        if self.tp is not None:
+            self.tp.end_step()
+        return chunk_logits, dec_logits
+
     # ---- decode ------------------------------------------------------------------------------------------------------
     def _decode_body(self, ids, ctx, bt):
         """The device-side part of a decode step on static tensors (captured into a CUDA graph per batch size)."""

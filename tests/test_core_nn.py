@@ -221,31 +221,6 @@ def test_profilers_pool_numerics_and_fusion():
     assert r.passed and r.max_abs_err < 1e-5
 
 
-def test_moe_quantization_conv_lstm_readouts():
-    ctx = ForwardCtx.train(B)
-    layer = ExpertLayer.new(B, MoEConfig(32, 4, 64, 2))
-    x = torch.randn(3, 10, 32, requires_grad=True)
-    out = layer(x, ctx)
-    (out.output.sum() + out.aux_loss).backward()
-    assert all(p.grad is not None for p in layer.parameters()) and 0 < float(out.aux_loss.detach()) < 0.1
-    assert ExpertParallel(8, 4, 1).local_experts() == [1, 5]
-    lin = LinearBuilder(128, 16).with_bias().build(B)
-    xi = torch.randn(4, 128)
-    assert (QuantizedLinear.from_linear(lin)(xi) - lin(xi)).abs().max() < 0.1
-    assert GPTQLinear.from_linear(lin, 64).memory_bytes() < lin.weight.tensor.numel() * 4 / 6
-    fq = QATTrainer.fake_quantize(xi.clone().requires_grad_(), 8)
-    fq.sum().backward()
-    conv = Conv2d.new(B, Conv2dConfig(5, 3, 3, in_channels=2))
-    img = torch.randn(2, 2, 8, 8)
-    assert torch.allclose(conv(img), torch.nn.functional.conv2d(img, conv.weight.tensor, conv.bias.tensor, padding=1), atol=1e-5)
-    from rustral_b200.symbolic import Vocabulary
-    labels = Vocabulary.with_specials("<unk>", ["pos", "neg"])
-    ro = Readout.new(B, labels, 8)
-    pred = ro.predict(torch.randn(3, 8), ctx)
-    assert len(pred) == 3 and pred[0].label in labels.tokens() and 0 <= pred[0].score <= 1
-    assert len(MultiReadout.new(B, ["a", "b", "c"], 8).top_k(torch.randn(2, 8), ctx, 2)[0]) == 2
-
-
 def test_onnx_export_structure_and_dashboard():
     from rustral_b200.utils import onnx_export, tui
     w, b = torch.randn(3, 4), torch.randn(3)

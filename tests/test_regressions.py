@@ -107,15 +107,15 @@ def test_engine_loop_drops_the_requests_of_a_failed_step():
     not retry the failing step for ever) and the loop keeps serving."""
     from rustral_b200.serve.http_server import EngineLoop
     eng = _engine(num_blocks=32, seq_len=64)
-    real_prefill = eng.runner.prefill
+    real_pass = eng.runner.step_mixed
     calls = {"n": 0}
 
-    def flaky(rid, ids):
+    def flaky(*args):
         calls["n"] += 1
         if calls["n"] == 1:
             raise RuntimeError("injected model failure")
-        return real_prefill(rid, ids)
-    eng.runner.prefill = flaky
+        return real_pass(*args)
+    eng.runner.step_mixed = flaky
     loop = EngineLoop(eng)
     try:
         with pytest.raises(RuntimeError, match="injected"):

@@ -301,3 +301,38 @@ def test_paged_serving_engine_generates_the_tokens_hugging_face_generates():
             back = export_hf_gpt2(runner.params.state_dict())
             ref_sd = {k: v for k, v in model.state_dict().items() if not k.endswith((".attn.bias", ".attn.masked_bias"))}
             assert set(back) == set(ref_sd) and all(torch.allclose(back[k], ref_sd[k].float(), atol=1e-7) for k in ref_sd)
+
+
+@pytest.mark.parametrize("name", ["gpt2-test", "llama-test"])
+def test_chunked_and_batched_prefill_generate_the_same_tokens_as_whole_prompt_prefill(name):
+    """Prompts cut into chunks of 4 or 7 tokens that share their model pass with other prompts' chunks and with the decode
+    batch (the later chunks attend to keys gathered from the pages) give the tokens of one-prompt-at-a-time prefill."""
+    cfg = preset(name, seq_len=64, d_model=64, ffn_dim=128)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 23, 9, 1, 16)]
+    results, steps = {}, {}
+    for chunk in (0, 4, 7, 2048):
+        runner = ModelRunner(cfg, device="cpu", num_blocks=32, block_size=4)
+        eng = ServingEngine(runner, max_batch_size=4, prefill_chunk=chunk)
+        ids = [eng.submit(p, 6) for p in prompts[:3]]
+        eng.step()                                     # the remaining requests arrive while the first are being served
+        ids += [eng.submit(p, 6) for p in prompts[3:]]
+        eng.run_to_completion()
+        results[chunk] = [eng.scheduler.get(r).generated for r in ids]
+        steps[chunk] = eng.steps
+        assert runner.cache.free_blocks == 32 and not eng._prefill_pos
+    assert results[4] == results[0] and results[7] == results[0] and results[2048] == results[0]
+    assert steps[4] > steps[2048]                      # small chunks spread the 23-token prompt over several steps
+
+
+def test_a_long_prompt_does_not_stall_running_requests_for_more_than_a_chunk():
+    cfg = preset("gpt2-test", seq_len=64, d_model=64, ffn_dim=128)
+    eng = ServingEngine(ModelRunner(cfg, device="cpu", num_blocks=32, block_size=4), max_batch_size=4, prefill_chunk=8)
+    a = eng.submit([1, 2, 3], 12)
+    eng.step()                                         # request a is decoding now
+    b = eng.submit(list(range(1, 41)), 2)              # 40-token prompt: five chunks
+    produced = []
+    for _ in range(5):
+        out = eng.step()
+        produced.append((a in out, b in out))
+    assert produced == [(True, False)] * 4 + [(True, True)]
