@@ -58,10 +58,7 @@ __device__ __forceinline__ float f2_ex2_poly(float x) {
 // Register reallocation between warp groups (four consecutive warps, all of which must execute the instruction): the
 // producer group shrinks to a few registers per thread and the softmax groups grow, so that a whole row of 128 scores
 // fits in registers.
-template <int N>
-__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N>
-__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+// (setmaxnreg_inc / setmaxnreg_dec: rb_common.cuh)
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t* r) {
   asm volatile(

@@ -283,14 +283,18 @@ __global__ void transpose_kernel(const T* __restrict__ a, T* __restrict__ out, i
 
 template <typename T, bool SCATTER>
 __global__ void __launch_bounds__(256)
-rows_kernel(const T* __restrict__ a, const long long* __restrict__ idx, T* __restrict__ out, long long n_idx, int cols, long long limit) {
+rows_kernel(const T* __restrict__ a, const long long* __restrict__ idx, T* __restrict__ out, long long n_idx, int cols,
+            long long limit RB_BOUNDS_PARAM) {
   const long long n = n_idx * cols;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
     const long long r = i / cols;
     const int c = static_cast<int>(i - r * cols);
     const long long j = idx[r];
-    if (j < 0 || j >= limit) continue;   // out-of-range indices are skipped, never dereferenced
+    if (j < 0 || j >= limit) {           // out-of-range indices are skipped, never dereferenced
+      if (c == 0) RB_BOUNDS_HIT(102);
+      continue;
+    }
     if (SCATTER) out[j * cols + c] = a[i];
     else out[i] = a[j * cols + c];
   }
@@ -470,14 +474,14 @@ RB_API int rb_transpose(const void* a, void* out, int rows, int cols, int dtype,
 RB_API int rb_gather_rows(const void* a, const long long* idx, void* out, long long n_idx, int cols, long long src_rows, int dtype, void* stream_v) {
   if (n_idx <= 0 || cols <= 0) return 0;
   const int grid = rb::ew_grid(n_idx * cols);
-  RB_BY_DTYPE((rb::rows_kernel<float, false><<<grid, 256, 0, RB_STREAM>>>((const float*)a, idx, (float*)out, n_idx, cols, src_rows)),
-              (rb::rows_kernel<__nv_bfloat16, false><<<grid, 256, 0, RB_STREAM>>>((const __nv_bfloat16*)a, idx, (__nv_bfloat16*)out, n_idx, cols, src_rows)))
+  RB_BY_DTYPE((rb::rows_kernel<float, false><<<grid, 256, 0, RB_STREAM>>>((const float*)a, idx, (float*)out, n_idx, cols, src_rows RB_BOUNDS_ARG)),
+              (rb::rows_kernel<__nv_bfloat16, false><<<grid, 256, 0, RB_STREAM>>>((const __nv_bfloat16*)a, idx, (__nv_bfloat16*)out, n_idx, cols, src_rows RB_BOUNDS_ARG)))
 }
 RB_API int rb_scatter_rows(const void* a, const long long* idx, void* out, long long n_idx, int cols, long long dst_rows, int dtype, void* stream_v) {
   if (n_idx <= 0 || cols <= 0) return 0;
   const int grid = rb::ew_grid(n_idx * cols);
-  RB_BY_DTYPE((rb::rows_kernel<float, true><<<grid, 256, 0, RB_STREAM>>>((const float*)a, idx, (float*)out, n_idx, cols, dst_rows)),
-              (rb::rows_kernel<__nv_bfloat16, true><<<grid, 256, 0, RB_STREAM>>>((const __nv_bfloat16*)a, idx, (__nv_bfloat16*)out, n_idx, cols, dst_rows)))
+  RB_BY_DTYPE((rb::rows_kernel<float, true><<<grid, 256, 0, RB_STREAM>>>((const float*)a, idx, (float*)out, n_idx, cols, dst_rows RB_BOUNDS_ARG)),
+              (rb::rows_kernel<__nv_bfloat16, true><<<grid, 256, 0, RB_STREAM>>>((const __nv_bfloat16*)a, idx, (__nv_bfloat16*)out, n_idx, cols, dst_rows RB_BOUNDS_ARG)))
 }
 RB_API int rb_broadcast_to(const void* a, void* out, long long arows, long long acols, long long rows, long long cols, int dtype, void* stream_v) {
   if (rows <= 0 || cols <= 0 || arows <= 0 || acols <= 0) return -1;

@@ -15,7 +15,7 @@ namespace rb {
 __global__ void __launch_bounds__(128)
 embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ wte,
                      const __nv_bfloat16* __restrict__ wpe, __nv_bfloat16* __restrict__ out, long long tokens, int dim,
-                     int seq_len, long long vocab) {
+                     int seq_len, long long vocab RB_BOUNDS_PARAM) {
   const int chunks = dim / 8;
   const long long total = tokens * chunks;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -23,7 +23,10 @@ embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __r
     const long long t = i / chunks;
     const int c = static_cast<int>(i - t * chunks) * 8;
     long long id = ids[t];
-    if (id < 0 || id >= vocab) id = 0;   // out-of-range ids read row 0 instead of faulting
+    if (id < 0 || id >= vocab) {         // out-of-range ids read row 0 instead of faulting
+      if (c == 0) RB_BOUNDS_HIT(101);
+      id = 0;
+    }
     uint4 a = __ldg(reinterpret_cast<const uint4*>(wte + id * dim + c));
     if (wpe) {
       const uint4 b = __ldg(reinterpret_cast<const uint4*>(wpe + (t % seq_len) * dim + c));
@@ -156,7 +159,7 @@ RB_API int rb_embedding_fwd(const long long* ids, const void* wte, const void* w
   if (blocks > 148LL * 32) blocks = 148LL * 32;
   rb::embedding_fwd_kernel<<<static_cast<int>(blocks), 128, 0, stream>>>(
       ids, reinterpret_cast<const __nv_bfloat16*>(wte), reinterpret_cast<const __nv_bfloat16*>(wpe),
-      reinterpret_cast<__nv_bfloat16*>(out), tokens, dim, seq_len < 1 ? 1 : seq_len, vocab);
+      reinterpret_cast<__nv_bfloat16*>(out), tokens, dim, seq_len < 1 ? 1 : seq_len, vocab RB_BOUNDS_ARG);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -53,12 +53,13 @@ __device__ __forceinline__ void block_online_reduce(float& m, float& s, float* s
 __global__ void __launch_bounds__(kCeThreads)
 cross_entropy_kernel(const __nv_bfloat16* logits, long long ld, const long long* __restrict__ targets,
                      float* __restrict__ loss, float* __restrict__ lse_out, __nv_bfloat16* dlogits, long long ldd,
-                     int n_valid, int n_pad, float grad_scale, long long ignore_index) {
+                     int n_valid, int n_pad, float grad_scale, long long ignore_index RB_BOUNDS_PARAM) {
   __shared__ float sh_m[32], sh_s[32];
   const long long row = blockIdx.x;
   const __nv_bfloat16* x = logits + row * ld;
   const long long tgt = targets[row];
   const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= n_valid;
+  if (ignored && tgt != ignore_index && threadIdx.x == 0) RB_BOUNDS_HIT(105);     // not a class and not the ignore marker
   // `dlogits` may be the same memory as `logits` (the gradient overwrites the logits): the target logit is read
   // here, before the reduction's barriers, because other warps start storing gradients right after them; and the
   // row is read with plain loads, not through the read-only path.
@@ -233,7 +234,7 @@ RB_API int rb_cross_entropy(const void* logits, long long ld, const long long* t
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   rb::cross_entropy_kernel<<<rows, rb::kCeThreads, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(logits), ld, targets, loss, lse, reinterpret_cast<__nv_bfloat16*>(dlogits),
-      ldd, n_valid, n_pad, grad_scale, ignore_index);
+      ldd, n_valid, n_pad, grad_scale, ignore_index RB_BOUNDS_ARG);
   return static_cast<int>(cudaGetLastError());
 }
 

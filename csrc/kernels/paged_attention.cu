@@ -19,7 +19,7 @@ namespace rb {
 __global__ void __launch_bounds__(128)
 kv_append_kernel(const __nv_bfloat16* __restrict__ k_new, long long ld_k, const __nv_bfloat16* __restrict__ v_new,
                  long long ld_v, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
-                 const long long* __restrict__ slots, long long tokens, int row_elems, long long num_slots) {
+                 const long long* __restrict__ slots, long long tokens, int row_elems, long long num_slots RB_BOUNDS_PARAM) {
   const int chunks = row_elems / 8;
   const long long total = tokens * chunks;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -27,6 +27,7 @@ kv_append_kernel(const __nv_bfloat16* __restrict__ k_new, long long ld_k, const 
     const long long t = i / chunks;
     const int c = static_cast<int>(i - t * chunks) * 8;
     const long long slot = slots[t];
+    if (slot >= num_slots && c == 0) RB_BOUNDS_HIT(103);           // a negative slot means "skip this token"
     if (slot < 0 || slot >= num_slots) continue;
     *reinterpret_cast<uint4*>(k_cache + slot * row_elems + c) = *reinterpret_cast<const uint4*>(k_new + t * ld_k + c);
     *reinterpret_cast<uint4*>(v_cache + slot * row_elems + c) = *reinterpret_cast<const uint4*>(v_new + t * ld_v + c);
@@ -77,7 +78,8 @@ __global__ void __launch_bounds__(kPaWarps * 32, 3)
 paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, const __nv_bfloat16* __restrict__ k_cache,
                           const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables, int max_blocks,
                           const int* __restrict__ context_lens, int heads, int kv_heads, int block_size,
-                          long long num_blocks, float scale, int g0, int gcount, float* __restrict__ partial, int nsplit) {
+                          long long num_blocks, float scale, int g0, int gcount, float* __restrict__ partial, int nsplit
+                          RB_BOUNDS_PARAM) {
   constexpr int LPR = D / 8;                 // lanes per K / V row (16-byte pieces)
   constexpr int RPI = 32 / LPR;              // rows fetched per warp instruction
   constexpr int NLD = 32 / RPI;              // load instructions per 32-row tile
@@ -133,7 +135,10 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, long long ld_q, c
     if (tok < t_end) {
       const int blk_idx = tok / block_size;
       int blk = blk_idx < max_blocks ? block_tables[static_cast<long long>(b) * max_blocks + blk_idx] : -1;
-      if (blk < 0 || blk >= num_blocks) blk = 0;                     // corrupt tables read block 0 instead of faulting
+      if (blk < 0 || blk >= num_blocks) {                            // corrupt tables read block 0 instead of faulting
+        RB_BOUNDS_HIT(104);
+        blk = 0;
+      }
       slot = blk * block_size + (tok - blk_idx * block_size);
     }
     n_next = min(32, t_end - first);
@@ -317,7 +322,7 @@ RB_API int rb_kv_append(const void* k_new, long long ld_k, const void* v_new, lo
   rb::kv_append_kernel<<<static_cast<int>(blocks), 128, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
       reinterpret_cast<const __nv_bfloat16*>(k_new), ld_k, reinterpret_cast<const __nv_bfloat16*>(v_new), ld_v,
       reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache), slot_mapping, tokens, row,
-      num_slots);
+      num_slots RB_BOUNDS_ARG);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -361,11 +366,11 @@ RB_API int rb_paged_attention_decode(const void* q, long long ld_q, void* out, l
     if (head_dim == 128)
       rb::paged_decode_split_kernel<128><<<grid, rb::kPaWarps * 32, smem, stream>>>(Q, ld_q, K, V, block_tables, max_blocks,
                                                                                 context_lens, heads, kv_heads, block_size,
-                                                                                num_blocks, scale, g0, gc, scratch, nsplit);
+                                                                                num_blocks, scale, g0, gc, scratch, nsplit RB_BOUNDS_ARG);
     else
       rb::paged_decode_split_kernel<64><<<grid, rb::kPaWarps * 32, smem, stream>>>(Q, ld_q, K, V, block_tables, max_blocks,
                                                                                context_lens, heads, kv_heads, block_size,
-                                                                               num_blocks, scale, g0, gc, scratch, nsplit);
+                                                                               num_blocks, scale, g0, gc, scratch, nsplit RB_BOUNDS_ARG);
   }
   dim3 mgrid(batch, heads);
   if (head_dim == 128)

@@ -60,8 +60,8 @@ quantize_fp8_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uin
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    const float scale = amax > 0.f ? amax * (1.f / 448.f) : 1.f;
-    const float inv = 1.f / scale;
+    const float scale = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
+    const float inv = __fdiv_rn(1.f, scale);      // elements are multiplied by the rounded reciprocal (the CPU path does the same)
     if (lane == 0) scales[row] = scale;
     uint2* op = reinterpret_cast<uint2*>(out + row * ldo);
     auto emit = [&](int v, const uint4& q) {

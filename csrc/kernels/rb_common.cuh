@@ -21,8 +21,7 @@ enum StatusBits : unsigned int {
   kStatusMbarTimeout = 1u << 0,   // an mbarrier wait inside a kernel ran out
   kStatusFlagTimeout = 1u << 1,   // a global-memory flag wait (peer / other CTA) ran out
   kStatusBadArg      = 1u << 2,   // a kernel saw an argument it cannot handle
-  kStatusBounds      = 1u << 3,   // reserved for index checks (today the kernels that read indices from memory clamp
-                                  // or skip out-of-range entries, and the host validates them before the launch)
+  kStatusBounds      = 1u << 3,   // an out-of-range index was met (reported only by a -DRB_BOUNDS build; see below)
 };
 
 // The status buffer is four words in global memory, one buffer per device, owned by the host
@@ -33,6 +32,20 @@ __device__ __forceinline__ void status_set(unsigned int* status, unsigned int bi
   atomicOr(&status[0], bits);
   if (where) atomicMax(&status[1], where);
 }
+
+// Index checks.  Kernels that read indices from memory (token ids, row indices, cache slots, block tables, class targets)
+// never dereference an out-of-range one: they clamp or skip it.  A library built with -DRB_BOUNDS additionally reports
+// every such index: bit kStatusBounds of the status word and a "where" code (101 embedding id, 102 gather / scatter row,
+// 103 cache slot, 104 block-table entry, 105 cross-entropy target).  Nothing traps; the kernel carries on as before.
+#ifdef RB_BOUNDS
+#define RB_BOUNDS_PARAM , unsigned int* rb_bounds_status
+#define RB_BOUNDS_ARG , rbhost::status_ptr()
+#define RB_BOUNDS_HIT(where) rb::status_set(rb_bounds_status, rb::kStatusBounds, (where))
+#else
+#define RB_BOUNDS_PARAM
+#define RB_BOUNDS_ARG
+#define RB_BOUNDS_HIT(where) ((void)0)
+#endif
 
 // Wait limits (nanoseconds of %globaltimer).
 constexpr unsigned long long kMbarWaitLimitNs = 1000ull * 1000ull * 1000ull;   // 1 s
@@ -247,6 +260,14 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
                ::"r"(bar), "h"(cta_mask)
                : "memory");
 }
+
+// Register reallocation between the warp groups (4 aligned warps each) of a CTA.  Every warp of a group executes the
+// instruction; the compiler honours the new limit for the code that follows only when the instruction opens a branch
+// taken by whole warp groups.
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }

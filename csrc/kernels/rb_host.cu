@@ -183,4 +183,13 @@ RB_API int rb_status_read(unsigned int* out, int clear) {
 // Allocates the status buffer (first call on a device allocates; do it before any stream capture).
 RB_API int rb_init() { return rbhost::status_ptr() ? 0 : -1; }
 
+// Bit 0: the library was compiled with -DRB_BOUNDS (index checks report through the status word).
+RB_API int rb_build_flags() {
+#ifdef RB_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 RB_API int rb_sm_count() { return rbhost::device_sm_count(); }

@@ -75,15 +75,19 @@ def _compile_group(sources, headers, out_lib: Path, compiler_cmd, link_cmd, verb
     return out_lib
 
 
-def build_kernels(force: bool = False, verbose: bool = False) -> Path:
+def build_kernels(force: bool = False, verbose: bool = False, bounds: bool = False) -> Path:
+    """`bounds`: the checking variant ``librb200_kernels_bounds.so`` (-DRB_BOUNDS: every kernel that reads indices from
+    memory reports an out-of-range one through the status word; it never traps).  `RUSTRAL_BOUNDS=1` makes the package
+    load that variant."""
     srcs = sorted((CSRC / "kernels").glob("*.cu")) + sorted((CSRC / "comm").glob("*.cu"))
     hdrs = sorted((CSRC / "kernels").glob("*.h")) + sorted((CSRC / "kernels").glob("*.cuh")) + \
         sorted((CSRC / "comm").glob("*.h")) + sorted((CSRC / "comm").glob("*.cuh"))
     nvcc = _nvcc()
     inc = ["-I", str(CSRC / "kernels"), "-I", str(CSRC / "comm")]
+    extra = ["-DRB_BOUNDS"] if bounds else []
     return _compile_group(
-        srcs, hdrs, LIB_DIR / "librb200_kernels.so",
-        lambda s, o: [nvcc, *NVCC_FLAGS, *inc, "-c", s, "-o", o],
+        srcs, hdrs, LIB_DIR / ("librb200_kernels_bounds.so" if bounds else "librb200_kernels.so"),
+        lambda s, o: [nvcc, *NVCC_FLAGS, *extra, *inc, "-c", s, "-o", o],
         lambda objs, out: [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", *objs, "-o", out],
         verbose, force)
 
@@ -112,6 +116,7 @@ def build_all(force: bool = False, verbose: bool = False) -> dict:
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     out = {}
     out["kernels"] = build_kernels(force, verbose)
+    out["kernels_bounds"] = build_kernels(force, verbose, bounds=True)
     if any((CSRC / "cpu").glob("*.cpp")):
         out["cpu"] = build_cpu(force, verbose)
     if any((CSRC / "runtime").glob("*.cpp")):

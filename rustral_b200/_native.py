@@ -8,6 +8,7 @@ the host runtime library (built on demand with g++ when absent, since they need 
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 from pathlib import Path
 
@@ -66,8 +67,14 @@ class NativeError(RuntimeError):
     """A native entry point rejected its arguments or CUDA reported an error."""
 
 
+# RUSTRAL_BOUNDS=1 selects the index-checking build of the kernel library (see _build.build_kernels).
+# RUSTRAL_KERNEL_LIB names another build of the library (a file name inside the package's _lib folder or a path).
+KERNEL_LIB = os.environ.get("RUSTRAL_KERNEL_LIB") or (
+    "librb200_kernels_bounds.so" if os.environ.get("RUSTRAL_BOUNDS", "0") not in ("", "0") else "librb200_kernels.so")
+
+
 def _load(name: str) -> C.CDLL:
-    path = LIB_DIR / name
+    path = Path(name) if os.path.isabs(name) else LIB_DIR / name
     if not path.exists():
         raise FileNotFoundError(str(path))
     return C.CDLL(str(path))
@@ -82,7 +89,7 @@ def kernels() -> C.CDLL:
         lib = _libs.get("kernels")
         if lib is None:
             try:
-                lib = _load("librb200_kernels.so")
+                lib = _load(KERNEL_LIB)
             except (OSError, FileNotFoundError) as e:
                 raise NativeError(
                     "librb200_kernels.so is not built or cannot be loaded; run "
@@ -139,6 +146,7 @@ def _declare_kernels(lib: C.CDLL) -> None:
 
     sig("rb_init", [])
     sig("rb_sm_count", [])
+    sig("rb_build_flags", [])
     sig("rb_status_read", [C.POINTER(C.c_uint), c_int])
     sig("rb_gemm_bf16", [C.POINTER(RbGemmArgs), P])
     sig("rb_norm_bwd_num_partials", [c_int, c_int])

@@ -33,7 +33,7 @@ def quantize_fp8_rows(x: torch.Tensor, out: torch.Tensor | None = None, scales: 
         f = x.float()
         amax = f.abs().amax(1)
         sc = torch.where(amax > 0, amax / E4M3_MAX, torch.ones_like(amax))
-        q = (f / sc[:, None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(torch.uint8)
+        q = (f * (1.0 / sc)[:, None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(torch.uint8)
         if out is not None:
             out.copy_(q)
             q = out
