@@ -249,3 +249,49 @@ def test_readouts_return_labels_with_probabilities():
     assert len(pred) == 3 and all(p.label in labels.tokens() and 0 <= p.score <= 1 for p in pred)
     top = MultiReadout.new(B, ["a", "b", "c"], 8).top_k(h[:2], ctx, 2)
     assert len(top) == 2 and len(top[0]) == 2 and top[0][0].score >= top[0][1].score
+
+
+# ---------------------------------------------------------------------------------------------- dashboard
+def test_dashboard_panes_keys_leak_warnings_and_json_dump(tmp_path):
+    import io
+    import json
+    import time
+    from rustral_b200.core import MemoryProfiler
+    from rustral_b200.utils import tui
+    cfg = tui.DashboardConfig(title="run-7", history_len=16, dump_path=str(tmp_path / "state.json"), alt_screen=False)
+    d = tui.TrainingDashboard(config=cfg)
+    d.set_total_epochs(4); d.set_total_batches(10); d.set_epoch(1); d.set_batch(5); d.set_step(15)
+    for i in range(40):
+        d.record_loss(2.0 / (i + 1)); d.record_lr(1e-3 * 0.9 ** i)
+    d.record_accuracy(0.75)
+    assert len(d.losses) == 16 and d.current_loss() == 2.0 / 40          # rolling window
+    d.record_loss(float("nan"))
+    assert any("non-finite loss" in w for w in d.warnings)
+    prof = MemoryProfiler(capacity_bytes=1000)
+    prof.alloc("weights", 600); h = prof.alloc("activations", 320); prof.free(h); prof.alloc("scratch", 330)
+    d.attach_memory_profiler(prof, leak_age_s=0.0)
+    keys = iter(["", "p", "p", "c", "zq"])
+    r = tui.DashboardRenderer(d, io.StringIO(), ansi=False, width=90, keys=lambda: next(keys))
+    assert r.render_frame() is False
+    assert d.oom_risk_level() is tui.OomRiskLevel.CRITICAL and d.memory_used == 930 and d.memory_peak == 930
+    assert sorted(l.tag for l in d.leaks) == ["scratch", "weights"] and (d.allocs, d.deallocs) == (3, 1)
+    panes = r.render_panes(90)
+    for needle in ("┌─ progress", "┌─ metrics", "┌─ memory", "┌─ warnings and events", "epoch     1/4", "batch     5/10",
+                   "OOM risk: CRITICAL", "LEAK weights: 600 B", "weights", "q quit"):
+        assert needle in panes, needle
+    assert all(len(line) == 90 for line in panes.splitlines()[1:])            # every box line fills the width
+    state = json.loads((tmp_path / "state.json").read_text())
+    assert state["memory"]["oom_risk"] == "critical" and len(state["leaks"]) == 2 and state["step"] == 15
+    assert r.render_frame() is False and r.paused                           # "p"
+    assert r.render_frame() is False and not r.paused                       # "p" again
+    assert r.render_frame() is False and d.has_leaks()                      # "c" clears; the same frame's poll finds them again
+    assert r.handle_key("c") is False and not d.has_leaks()
+    assert r.render_frame() is True and not r.is_running()                  # unknown key ignored, then "q"
+    # a config handed to run_dashboard yields a dashboard with a render thread that stops on request
+    d2 = tui.run_dashboard(tui.DashboardConfig(refresh_ms=10, alt_screen=False), file=io.StringIO())
+    d2.record_loss(1.0)
+    time.sleep(0.05)
+    d2.render_thread.stop_event.set()
+    d2.render_thread.join(timeout=2)
+    assert not d2.render_thread.is_alive()
+    assert tui.format_bytes(1536) == "1.50 KiB" and tui.format_duration(3725) == "1:02:05" and tui.format_duration(None) == "--:--"
