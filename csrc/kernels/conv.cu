@@ -78,3 +78,141 @@ RB_API int rb_conv2d_fwd(const void* x, const void* w, const void* bias, void* y
       pad_w, Ho, Wo);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Training path (and large filter banks): convolution as one GEMM over unfolded patches.
+//   rb_im2col        x [N, C, H, W] -> cols [N * Ho * Wo, Kp]: row (n, ho, wo), column (c, i, j) = the tap's pixel or zero;
+//                    columns [C * kh * kw, Kp) are zero padding so that rows have a 16-byte pitch for TMA
+//   rb_col2im        the adjoint: dx[n, c, h, w] = sum of dcols over the (row, column) pairs that read that pixel, as a
+//                    gather per pixel in a fixed order (no atomics)
+//   rb_nhwc_to_nchw  y2 [N * L, ld] (first O columns) -> y [N, O, L]         (the GEMM's output into the layer's layout)
+//   rb_nchw_to_nhwc  dy [N, O, L] -> dy2 [N * L, Op] with zero columns [O, Op) (the layer's gradient into the GEMM's layout)
+// ------------------------------------------------------------------------------------------------------------------
+namespace rb {
+
+__global__ void __launch_bounds__(256)
+im2col_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ cols, int N, int C, int H, int W, int kh, int kw,
+              int stride, int pad_h, int pad_w, int Ho, int Wo, int Kp) {
+  const long long total = static_cast<long long>(N) * Ho * Wo * Kp;
+  const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+  const int K = C * kh * kw;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int k = static_cast<int>(i % Kp);
+    const long long row = i / Kp;
+    __nv_bfloat16 v = __float2bfloat16(0.f);
+    if (k < K) {
+      const int wo = static_cast<int>(row % Wo), ho = static_cast<int>((row / Wo) % Ho), n = static_cast<int>(row / (static_cast<long long>(Wo) * Ho));
+      const int j = k % kw, ii = (k / kw) % kh, c = k / (kw * kh);
+      const int h = ho * stride - pad_h + ii, w = wo * stride - pad_w + j;
+      if (h >= 0 && h < H && w >= 0 && w < W) v = x[((static_cast<long long>(n) * C + c) * H + h) * W + w];
+    }
+    cols[i] = v;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+col2im_kernel(const __nv_bfloat16* __restrict__ dcols, __nv_bfloat16* __restrict__ dx, int N, int C, int H, int W, int kh, int kw,
+              int stride, int pad_h, int pad_w, int Ho, int Wo, int Kp) {
+  const long long total = static_cast<long long>(N) * C * H * W;
+  const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int w = static_cast<int>(i % W), h = static_cast<int>((i / W) % H), c = static_cast<int>((i / (static_cast<long long>(W) * H)) % C);
+    const int n = static_cast<int>(i / (static_cast<long long>(W) * H * C));
+    float acc = 0.f;
+    for (int ii = 0; ii < kh; ++ii) {
+      const int hn = h + pad_h - ii;
+      if (hn < 0 || hn % stride) continue;
+      const int ho = hn / stride;
+      if (ho >= Ho) continue;
+      for (int j = 0; j < kw; ++j) {
+        const int wn = w + pad_w - j;
+        if (wn < 0 || wn % stride) continue;
+        const int wo = wn / stride;
+        if (wo >= Wo) continue;
+        const long long row = (static_cast<long long>(n) * Ho + ho) * Wo + wo;
+        acc += __bfloat162float(dcols[row * Kp + (c * kh + ii) * kw + j]);
+      }
+    }
+    dx[i] = __float2bfloat16(acc);
+  }
+}
+
+// 32 x 32 tiles through shared memory: both sides are read and written along their contiguous dimension
+__global__ void __launch_bounds__(256)
+nhwc_nchw_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int L, int O, long long ld_src,
+                 long long ld_dst_rows, int to_nchw) {
+  // to_nchw: src [n][l][o] (pitch ld_src) -> dst [n][o][l];   else: src [n][o][l] -> dst [n][l][o] (pitch ld_dst_rows, zero fill)
+  __shared__ __nv_bfloat16 tile[32][33];
+  const int n = blockIdx.z;
+  const int l0 = blockIdx.x * 32, o0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;          // 32 x 8
+  if (to_nchw) {
+    for (int r = ty; r < 32; r += 8) {
+      const int l = l0 + r, o = o0 + tx;
+      tile[r][tx] = (l < L && o < O) ? src[(static_cast<long long>(n) * L + l) * ld_src + o] : __float2bfloat16(0.f);
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+      const int o = o0 + r, l = l0 + tx;
+      if (o < O && l < L) dst[(static_cast<long long>(n) * O + o) * L + l] = tile[tx][r];
+    }
+  } else {
+    const int Op = static_cast<int>(ld_dst_rows);
+    for (int r = ty; r < 32; r += 8) {
+      const int o = o0 + r, l = l0 + tx;
+      tile[r][tx] = (o < O && l < L) ? src[(static_cast<long long>(n) * O + o) * L + l] : __float2bfloat16(0.f);
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+      const int l = l0 + r, o = o0 + tx;
+      if (l < L && o < Op) dst[(static_cast<long long>(n) * L + l) * Op + o] = tile[tx][r];
+    }
+  }
+}
+
+}  // namespace rb
+
+namespace {
+inline int conv_out(int size, int pad, int k, int stride) { return (size + 2 * pad - k) / stride + 1; }
+inline int conv_grid(long long total) { long long b = (total + 255) / 256; return static_cast<int>(b < 148 * 16 ? (b > 0 ? b : 1) : 148 * 16); }
+}  // namespace
+
+RB_API int rb_im2col(const void* x, void* cols, int N, int C, int H, int W, int kh, int kw, int stride, int pad_h, int pad_w, int Kp,
+                     void* stream) {
+  if (!x || !cols || N <= 0 || C <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad_h < 0 || pad_w < 0 || Kp < C * kh * kw) return -1;
+  const int Ho = conv_out(H, pad_h, kh, stride), Wo = conv_out(W, pad_w, kw, stride);
+  if (Ho <= 0 || Wo <= 0) return -1;
+  const long long total = static_cast<long long>(N) * Ho * Wo * Kp;
+  rb::im2col_kernel<<<conv_grid(total), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(cols), N, C, H, W, kh, kw, stride, pad_h, pad_w, Ho, Wo, Kp);
+  return static_cast<int>(cudaGetLastError());
+}
+
+RB_API int rb_col2im(const void* dcols, void* dx, int N, int C, int H, int W, int kh, int kw, int stride, int pad_h, int pad_w, int Kp,
+                     void* stream) {
+  if (!dcols || !dx || N <= 0 || C <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad_h < 0 || pad_w < 0 || Kp < C * kh * kw) return -1;
+  const int Ho = conv_out(H, pad_h, kh, stride), Wo = conv_out(W, pad_w, kw, stride);
+  if (Ho <= 0 || Wo <= 0) return -1;
+  const long long total = static_cast<long long>(N) * C * H * W;
+  rb::col2im_kernel<<<conv_grid(total), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dcols), reinterpret_cast<__nv_bfloat16*>(dx), N, C, H, W, kh, kw, stride, pad_h, pad_w, Ho, Wo, Kp);
+  return static_cast<int>(cudaGetLastError());
+}
+
+RB_API int rb_nhwc_to_nchw(const void* src, long long ld_src, void* dst, int N, int L, int O, void* stream) {
+  if (!src || !dst || N <= 0 || L <= 0 || O <= 0 || ld_src < O || N > 65535) return -1;
+  dim3 grid((L + 31) / 32, (O + 31) / 32, N);
+  if (grid.y > 65535) return -1;
+  rb::nhwc_nchw_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(src), reinterpret_cast<__nv_bfloat16*>(dst), L, O, ld_src, 0, 1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+RB_API int rb_nchw_to_nhwc(const void* src, void* dst, int N, int L, int O, int Op, void* stream) {
+  if (!src || !dst || N <= 0 || L <= 0 || O <= 0 || Op < O || N > 65535) return -1;
+  dim3 grid((L + 31) / 32, (Op + 31) / 32, N);
+  if (grid.y > 65535) return -1;
+  rb::nhwc_nchw_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(src), reinterpret_cast<__nv_bfloat16*>(dst), L, O, 0, Op, 0);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -10,6 +10,15 @@ extern "C" {
 // on the im2col + GEMM path.
 int rb_conv2d_fwd(const void* x, const void* w, const void* bias, void* y, int N, int C, int H, int W, int O, int kh, int kw,
                   int stride, int pad_h, int pad_w, void* stream);
+// Convolution as a GEMM over unfolded patches (training, large filter banks); all tensors bf16 and dense.
+//   rb_im2col: x [N, C, H, W] -> cols [N * Ho * Wo, Kp], column (c, i, j) of row (n, ho, wo) holds the tap's pixel (zero
+//   outside the image); columns from C * kh * kw up to Kp are zero.   rb_col2im: its adjoint, dcols -> dx, no atomics.
+int rb_im2col(const void* x, void* cols, int N, int C, int H, int W, int kh, int kw, int stride, int pad_h, int pad_w, int Kp, void* stream);
+int rb_col2im(const void* dcols, void* dx, int N, int C, int H, int W, int kh, int kw, int stride, int pad_h, int pad_w, int Kp, void* stream);
+//   rb_nhwc_to_nchw: src [N * L, ld_src] (first O columns) -> dst [N, O, L];  rb_nchw_to_nhwc: src [N, O, L] -> dst [N * L, Op]
+//   with zeros in columns [O, Op).
+int rb_nhwc_to_nchw(const void* src, long long ld_src, void* dst, int N, int L, int O, void* stream);
+int rb_nchw_to_nhwc(const void* src, void* dst, int N, int L, int O, int Op, void* stream);
 #ifdef __cplusplus
 }
 #endif

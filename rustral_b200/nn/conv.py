@@ -1,7 +1,8 @@
 """Conv2d and pooling (crates/nn/src/conv.rs:7-340).  NCHW input, any number of input channels (the reference assumes
 one, conv.rs:47-57).  Two paths: small filter banks in inference run the direct kernel of csrc/kernels/conv.cu (one
 launch: taps, bias and the NCHW store); everything else, and every call that needs gradients, is lowered to one GEMM
-on the unfolded patches (im2col), which on the B200 backend is the tcgen05 kernel."""
+on the unfolded patches (im2col), which on the B200 backend is the tcgen05 kernel with native unfolding, folding and
+layout kernels around it, forward and backward (`_Conv2dGemmFn`); CPU tensors use `F.unfold` and the reference GEMM."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -15,7 +16,66 @@ from ..core import ForwardCtx, Module, Parameter, Saveable, Trainable, ShapeMism
 
 
 N_.optional_sig("rb_conv2d_fwd", [N_.c_void_p, N_.c_void_p, N_.c_void_p, N_.c_void_p] + [N_.c_int] * 10 + [N_.c_void_p])
+_P, _I = N_.c_void_p, N_.c_int
+N_.optional_sig("rb_im2col", [_P, _P] + [_I] * 10 + [_P])
+N_.optional_sig("rb_col2im", [_P, _P] + [_I] * 10 + [_P])
+N_.optional_sig("rb_nhwc_to_nchw", [_P, N_.c_ll, _P, _I, _I, _I, _P])
+N_.optional_sig("rb_nchw_to_nhwc", [_P, _P, _I, _I, _I, _I, _P])
 DIRECT_MAX_FILTER_ELEMS = 12288          # the direct kernel keeps the filter bank in 48 KB of shared memory as fp32
+
+
+class _Conv2dGemmFn(torch.autograd.Function):
+    """Convolution of bf16 CUDA tensors as one tcgen05 GEMM over unfolded patches, forward and backward, with native
+    kernels for the unfolding (`rb_im2col`), its adjoint (`rb_col2im`) and the NHWC <-> NCHW copies around the GEMMs
+    (csrc/kernels/conv.cu).  Backward: dW = dY^T cols, db = column sums of dY, dcols = dY W, dx = col2im(dcols)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, stride, pad):
+        N, C, H, W = x.shape
+        O, _, kh, kw = weight.shape
+        ho, wo = (H + 2 * pad[0] - kh) // stride + 1, (W + 2 * pad[1] - kw) // stride + 1
+        L, K = ho * wo, C * kh * kw
+        Kp, Op = (K + 7) // 8 * 8, (O + 7) // 8 * 8            # 16-byte row pitches for the GEMM's operands and output
+        lib = N_.kernels()
+        x = x.contiguous()
+        cols = torch.empty((N * L, Kp), dtype=torch.bfloat16, device=x.device)
+        N_.check(lib.rb_im2col(x.data_ptr(), cols.data_ptr(), N, C, H, W, kh, kw, stride, pad[0], pad[1], Kp, N_.stream_ptr()), "rb_im2col")
+        wmat = torch.zeros((Op, Kp), dtype=torch.bfloat16, device=x.device)
+        wmat[:O, :K] = weight.detach().reshape(O, K)
+        bvec = None
+        if bias is not None:
+            bvec = torch.zeros(Op, dtype=torch.bfloat16, device=x.device)
+            bvec[:O] = bias.detach()
+        y2 = ops.gemm(cols, wmat, bias=bvec)                   # [N * L, Op]
+        y = torch.empty((N, O, ho, wo), dtype=torch.bfloat16, device=x.device)
+        N_.check(lib.rb_nhwc_to_nchw(y2.data_ptr(), y2.stride(0), y.data_ptr(), N, L, O, N_.stream_ptr()), "rb_nhwc_to_nchw")
+        ctx.save_for_backward(cols, wmat)
+        ctx.geom = (N, C, H, W, O, kh, kw, stride, pad, L, K, Kp, Op)
+        ctx.has_bias = bias is not None
+        ctx.w_dtype = weight.dtype
+        ctx.b_dtype = None if bias is None else bias.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        cols, wmat = ctx.saved_tensors
+        N, C, H, W, O, kh, kw, stride, pad, L, K, Kp, Op = ctx.geom
+        lib = N_.kernels()
+        dy = dy.contiguous().to(torch.bfloat16)
+        dy2 = torch.empty((N * L, Op), dtype=torch.bfloat16, device=dy.device)
+        N_.check(lib.rb_nchw_to_nhwc(dy.data_ptr(), dy2.data_ptr(), N, L, O, Op, N_.stream_ptr()), "rb_nchw_to_nhwc")
+        dx = dw = db = None
+        if ctx.needs_input_grad[1]:
+            dwm = ops.gemm(dy2, cols, a_mn=True, b_mn=True, out_dtype=torch.float32)      # [Op, Kp] = dY^T cols
+            dw = dwm[:O, :K].reshape(O, C, kh, kw).to(ctx.w_dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = ops.sum_dim0(dy2)[:O].to(ctx.b_dtype)
+        if ctx.needs_input_grad[0]:
+            dcols = ops.gemm(dy2, wmat, b_mn=True)                                        # [N * L, Kp] = dY W
+            dx = torch.empty((N, C, H, W), dtype=torch.bfloat16, device=dy.device)
+            N_.check(lib.rb_col2im(dcols.data_ptr(), dx.data_ptr(), N, C, H, W, kh, kw, stride, pad[0], pad[1], Kp, N_.stream_ptr()),
+                     "rb_col2im")
+        return dx, dw, db, None, None
 
 
 def _conv2d_direct(x, weight, bias, stride: int, pad) -> torch.Tensor:
@@ -67,6 +127,8 @@ class Conv2d(Module, Trainable, Saveable):
         if (x.is_cuda and x.dtype == torch.bfloat16 and not needs_grad
                 and c.out_channels * C * c.kernel_h * c.kernel_w <= DIRECT_MAX_FILTER_ELEMS):
             return _conv2d_direct(x, self.weight.tensor, None if self.bias is None else self.bias.tensor, c.stride, pad)
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            return _Conv2dGemmFn.apply(x, self.weight.tensor, None if self.bias is None else self.bias.tensor, c.stride, pad)
         cols = F.unfold(x.float(), (c.kernel_h, c.kernel_w), padding=pad, stride=c.stride)       # [N, C*kh*kw, L]
         L = cols.shape[-1]
         a = cols.transpose(1, 2).reshape(N * L, -1).to(x.dtype).contiguous()

@@ -6,8 +6,105 @@ from dataclasses import dataclass
 
 import torch
 
+from .. import _native as N_
 from .. import ops
 from ..core import ForwardCtx, Module, Parameter, Saveable, Trainable, InvalidArgument
+
+_P, _I = N_.c_void_p, N_.c_int
+N_.optional_sig("rb_ec_select", [_P, _I, _I, _I, _P, _P, _P])
+N_.optional_sig("rb_ec_table", [_P, _I, _I, _I, _P, _P])
+N_.optional_sig("rb_ec_combine", [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P])
+N_.optional_sig("rb_ec_combine_bwd", [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P])
+
+
+def ec_select(probs: torch.Tensor, cap: int):
+    """Per expert (column of `probs` [T, E], fp32) the `cap` tokens with the largest probability, in ascending token
+    order; ties at the threshold go to the lower token index.  Returns (idx int64 [E, cap], gate fp32 [E, cap])."""
+    T, E = probs.shape
+    if probs.is_cuda:
+        p = probs.detach().float().contiguous()
+        idx = torch.empty((E, cap), dtype=torch.int64, device=probs.device)
+        gate = torch.empty((E, cap), dtype=torch.float32, device=probs.device)
+        N_.check(N_.kernels().rb_ec_select(p.data_ptr(), T, E, cap, idx.data_ptr(), gate.data_ptr(), N_.stream_ptr()), "rb_ec_select")
+        return idx, gate
+    pt = probs.detach().float().t()                                         # [E, T]
+    order = torch.argsort(pt, dim=1, descending=True, stable=True)[:, :cap]  # stable: ties keep the lower index first
+    idx = torch.sort(order, dim=1).values
+    return idx, pt.gather(1, idx)
+
+
+def ec_table(idx: torch.Tensor, T: int) -> torch.Tensor:
+    """table[t, e] = position of token t in expert e's list (int32), -1 when expert e did not choose it."""
+    E, cap = idx.shape
+    if idx.is_cuda:
+        table = torch.empty((T, E), dtype=torch.int32, device=idx.device)
+        N_.check(N_.kernels().rb_ec_table(idx.data_ptr(), T, E, cap, table.data_ptr(), N_.stream_ptr()), "rb_ec_table")
+        return table
+    table = torch.full((T, E), -1, dtype=torch.int32)
+    table[idx.reshape(-1), torch.arange(E).repeat_interleave(cap)] = torch.arange(cap, dtype=torch.int32).repeat(E)
+    return table
+
+
+def _combine(y, gate, table, T, out_f32=False):
+    E = table.shape[1]
+    cap = y.shape[0] // E
+    out = torch.empty((T, y.shape[1]), dtype=torch.float32 if out_f32 else torch.bfloat16, device=y.device)
+    N_.check(N_.kernels().rb_ec_combine(y.data_ptr(), N_.ptr(gate), table.data_ptr(), out.data_ptr(), T, E, cap, y.shape[1], int(out_f32),
+                                        N_.stream_ptr()), "rb_ec_combine")
+    return out
+
+
+class _EcGatherFn(torch.autograd.Function):
+    """rows[e * cap + s] = x[idx[e, s]]; backward: every token sums the gradients of the rows it was copied to, in expert
+    order (the combine kernel with unit weights)."""
+
+    @staticmethod
+    def forward(ctx, x2, idx_flat, table):
+        ctx.save_for_backward(table)
+        ctx.T = x2.shape[0]
+        return ops.gather_rows(x2.contiguous(), idx_flat)
+
+    @staticmethod
+    def backward(ctx, drows):
+        (table,) = ctx.saved_tensors
+        return _combine(drows.contiguous(), None, table, ctx.T), None, None
+
+
+class _EcCombineFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y_all, gate_flat, idx_flat, table, T):
+        y_all, gate_flat = y_all.contiguous(), gate_flat.contiguous()
+        ctx.save_for_backward(y_all, gate_flat, idx_flat)
+        ctx.T = T
+        return _combine(y_all, gate_flat, table, T)
+
+    @staticmethod
+    def backward(ctx, dout):
+        y_all, gate_flat, idx_flat = ctx.saved_tensors
+        n, d = y_all.shape
+        dy = torch.empty_like(y_all)
+        dgate = torch.empty(n, dtype=torch.float32, device=y_all.device)
+        N_.check(N_.kernels().rb_ec_combine_bwd(dout.contiguous().data_ptr(), idx_flat.data_ptr(), gate_flat.data_ptr(), y_all.data_ptr(),
+                                                dy.data_ptr(), dgate.data_ptr(), n, ctx.T, d, N_.stream_ptr()), "rb_ec_combine_bwd")
+        return dy, dgate, None, None, None
+
+
+class _EcGateFn(torch.autograd.Function):
+    """The chosen probabilities as a differentiable function of `probs`: the gradient of probs[t, e] is the gradient of
+    the gate at table[t, e] (or zero), a gather, so no scattered accumulation is needed."""
+
+    @staticmethod
+    def forward(ctx, probs, gate_sel, table):
+        ctx.save_for_backward(table)
+        return gate_sel.reshape(-1).clone()
+
+    @staticmethod
+    def backward(ctx, dgate):
+        (table,) = ctx.saved_tensors
+        T, E = table.shape
+        cap = dgate.numel() // E
+        pos = torch.arange(E, device=table.device)[None, :] * cap + table.clamp_min(0).long()
+        return torch.where(table >= 0, dgate[pos], torch.zeros((), dtype=dgate.dtype, device=dgate.device)), None, None
 
 
 @dataclass
@@ -55,11 +152,34 @@ class ExpertChoiceRouter(Module, Trainable, Saveable):
         vals, idx = torch.topk(probs.t(), cap, dim=-1)          # per expert: its highest-affinity tokens
         return idx, vals, probs
 
+    def _forward_native(self, x, x2, expert_fn):
+        """bf16 CUDA tensors: selection, row gather, combine and their backward passes are the kernels of
+        csrc/kernels/expert_choice.cu; the experts see one contiguous [capacity, d] block each."""
+        c = self.config
+        T, E = x2.shape[0], c.num_experts
+        cap = min(c.capacity(), T)
+        w = self.router.tensor.to(x2.dtype)
+        if E % 8:                                   # the GEMM's output rows need a 16-byte pitch: zero rows up to a multiple of 8
+            w = torch.nn.functional.pad(w, (0, 0, 0, (-E) % 8))
+        logits = ops.linear(x2, w)[:, :E].float()
+        probs = ops.softmax(logits)
+        idx, gate_sel = ec_select(probs, cap)
+        table = ec_table(idx, T)
+        idx_flat = idx.reshape(-1)
+        gate = _EcGateFn.apply(probs, gate_sel, table)
+        rows = _EcGatherFn.apply(x2, idx_flat, table)
+        y_all = torch.cat([expert_fn(e, rows[e * cap:(e + 1) * cap]).to(x2.dtype) for e in range(E)], 0)
+        out = _EcCombineFn.apply(y_all, gate, idx_flat, table, T)
+        self.last_stats = ExpertChoiceStats(cap, cap, float(cap), 1.0, int((table.max(1).values < 0).sum()))
+        return out.to(x.dtype).reshape(x.shape)
+
     def forward(self, x, expert_fn, ctx: ForwardCtx):
         """expert_fn(e, tokens [n, d]) -> [n, d].  Output: sum over choosing experts of gate * expert output."""
         c = self.config
         x2 = x.reshape(-1, c.d_model)
         c.validate_for_batch(x2.shape[0])
+        if x2.is_cuda and x2.dtype == torch.bfloat16 and c.d_model % 8 == 0:
+            return self._forward_native(x, x2, expert_fn)
         idx, gate, probs = self.select(x2)
         out = torch.zeros(x2.shape, dtype=torch.float32, device=x2.device)
         served = torch.zeros(x2.shape[0], dtype=torch.int32, device=x2.device)

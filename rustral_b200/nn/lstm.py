@@ -1,5 +1,9 @@
 """Recurrent cells (crates/nn/src/lstm.rs:10-470): LSTM (gate order i, f, o, g), GRU (standard equations: the reset gate
-is used, which the reference computes and ignores, lstm.rs:203-300), stacked and bidirectional wrappers."""
+is used, which the reference computes and ignores, lstm.rs:203-300), stacked and bidirectional wrappers.
+
+On the GPU (bf16) a step is the two projection GEMMs plus one fused gate kernel, in training as in inference: the gate
+kernels of csrc/kernels/rnn.cu have backward counterparts, wrapped as autograd functions here, so the backward pass of
+a step is one gate kernel plus the GEMMs' own dgrad / wgrad kernels.  CPU tensors use the tensor-op form."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -11,7 +15,67 @@ from .. import ops
 from ..core import ForwardCtx, Module, Parameter, Saveable, StatefulModule, Trainable
 
 
-N_.optional_sig("rb_lstm_gates_fwd", [N_.c_void_p, N_.c_ll, N_.c_void_p, N_.c_void_p, N_.c_void_p, N_.c_int, N_.c_int, N_.c_void_p])
+_P, _LL, _I = N_.c_void_p, N_.c_ll, N_.c_int
+N_.optional_sig("rb_lstm_gates_fwd", [_P, _LL, _P, _P, _P, _I, _I, _P])
+N_.optional_sig("rb_lstm_gates_bwd", [_P, _LL, _P, _P, _P, _P, _P, _LL, _P, _I, _I, _P])
+N_.optional_sig("rb_gru_gates_fwd", [_P, _LL, _P, _LL, _P, _P, _I, _I, _P])
+N_.optional_sig("rb_gru_gates_bwd", [_P, _LL, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _P])
+
+
+def _native_cell_ok(t: torch.Tensor, hidden: int) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and hidden % 2 == 0
+
+
+class _LstmGatesFn(torch.autograd.Function):
+    """(h, c) = cell update from the pre-activations [B, 4H] (order i | f | o | g) and c_prev, one kernel each way
+    (`rb_lstm_gates_fwd` / `rb_lstm_gates_bwd`; the backward recomputes the activations from the saved pre-activations)."""
+
+    @staticmethod
+    def forward(ctx, gates, c_prev):
+        gates, c_prev = gates.contiguous(), c_prev.contiguous()
+        B, H = c_prev.shape
+        h, c = torch.empty_like(c_prev), torch.empty_like(c_prev)
+        N_.check(N_.kernels().rb_lstm_gates_fwd(gates.data_ptr(), gates.stride(0), c_prev.data_ptr(), h.data_ptr(), c.data_ptr(),
+                                                B, H, N_.stream_ptr()), "rb_lstm_gates_fwd")
+        ctx.save_for_backward(gates, c_prev, c)
+        return h, c
+
+    @staticmethod
+    def backward(ctx, dh, dc):
+        gates, c_prev, c = ctx.saved_tensors
+        B, H = c_prev.shape
+        dh = torch.zeros_like(c) if dh is None else dh.contiguous()
+        dc = None if dc is None else dc.contiguous()
+        dgates, dc_prev = torch.empty_like(gates), torch.empty_like(c_prev)
+        N_.check(N_.kernels().rb_lstm_gates_bwd(gates.data_ptr(), gates.stride(0), c_prev.data_ptr(), c.data_ptr(), dh.data_ptr(),
+                                                N_.ptr(dc), dgates.data_ptr(), dgates.stride(0), dc_prev.data_ptr(), B, H,
+                                                N_.stream_ptr()), "rb_lstm_gates_bwd")
+        return dgates, dc_prev
+
+
+class _GruGatesFn(torch.autograd.Function):
+    """h = GRU cell update from gx = x W_x^T + b, gh = h_prev W_h^T ([B, 3H], order r | z | n) and h_prev."""
+
+    @staticmethod
+    def forward(ctx, gx, gh, h_prev):
+        gx, gh, h_prev = gx.contiguous(), gh.contiguous(), h_prev.contiguous()
+        B, H = h_prev.shape
+        h = torch.empty_like(h_prev)
+        N_.check(N_.kernels().rb_gru_gates_fwd(gx.data_ptr(), gx.stride(0), gh.data_ptr(), gh.stride(0), h_prev.data_ptr(),
+                                               h.data_ptr(), B, H, N_.stream_ptr()), "rb_gru_gates_fwd")
+        ctx.save_for_backward(gx, gh, h_prev)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        gx, gh, h_prev = ctx.saved_tensors
+        B, H = h_prev.shape
+        dgx, dgh, dhp = torch.empty((B, 3 * H), dtype=gx.dtype, device=gx.device), torch.empty((B, 3 * H), dtype=gx.dtype, device=gx.device), \
+            torch.empty_like(h_prev)
+        N_.check(N_.kernels().rb_gru_gates_bwd(gx.data_ptr(), gx.stride(0), gh.data_ptr(), gh.stride(0), h_prev.data_ptr(),
+                                               dh.contiguous().data_ptr(), dgx.data_ptr(), dgh.data_ptr(), dhp.data_ptr(), B, H,
+                                               N_.stream_ptr()), "rb_gru_gates_bwd")
+        return dgx, dgh, dhp
 
 
 @dataclass
@@ -65,6 +129,10 @@ class LstmCell(RnnCell):
     def step(self, x, state, ctx=None):
         h, c = state
         H = self.hidden_size
+        if _native_cell_ok(x, H):
+            # training and inference on the GPU: two GEMMs (the second adds the first as its residual) and the gate kernel
+            gates = ops.linear(h, self.wh.tensor, None, "none", ops.linear(x, self.wx.tensor, self.b.tensor))
+            return _LstmGatesFn.apply(gates, c)
         gates = ops.linear(x, self.wx.tensor, self.b.tensor) + ops.linear(h, self.wh.tensor)
         gf = gates.float()
         i, f, o, g = torch.sigmoid(gf[:, :H]), torch.sigmoid(gf[:, H:2 * H]), torch.sigmoid(gf[:, 2 * H:3 * H]), torch.tanh(gf[:, 3 * H:])
@@ -116,6 +184,8 @@ class GruCell(RnnCell):
 
     def step(self, x, h, ctx=None):
         H = self.hidden_size
+        if _native_cell_ok(x, H):
+            return _GruGatesFn.apply(ops.linear(x, self.wx.tensor, self.b.tensor), ops.linear(h, self.wh.tensor), h)
         gx = ops.linear(x, self.wx.tensor, self.b.tensor).float()
         gh = ops.linear(h, self.wh.tensor).float()
         r = torch.sigmoid(gx[:, :H] + gh[:, :H])
@@ -140,7 +210,14 @@ class GruCell(RnnCell):
             wx, wh, b = self.wx.tensor.detach(), self.wh.tensor.detach(), self.b.tensor.detach()
             gx_all = ops.linear(xs.reshape(T * B, I).contiguous(), wx, b).view(T, B, 3 * H).float()
             outs = torch.empty((T, B, H), dtype=xs.dtype, device=xs.device)
+            native = _native_cell_ok(xs, H)
+            if native:
+                gx_all = gx_all.to(xs.dtype)
             for t in range(T):
+                if native:
+                    h = _GruGatesFn.apply(gx_all[t], ops.linear(h, wh), h)
+                    outs[t] = h
+                    continue
                 gx, gh = gx_all[t], ops.linear(h, wh).float()
                 r = torch.sigmoid(gx[:, :H] + gh[:, :H])
                 z = torch.sigmoid(gx[:, H:2 * H] + gh[:, H:2 * H])
