@@ -46,7 +46,8 @@ struct EpiParams {
   int out_f32;
   int accumulate;
   float alpha;
-  int staged;   // bf16 output goes through a per-warp shared-memory tile and leaves as whole 128/256-byte row segments
+  int staged;   // 1: bf16 output goes through a per-warp shared-memory tile and leaves as whole 128/256-byte row segments;
+                // 2: the same tile leaves through a TMA store (tensor maps tmD / tmAux; 64-column tiles only)
   const float* row_scale;   // fp32 [M] or nullptr: multiplies row i of the accumulator (8-bit operands: per-token scale)
   const float* col_scale;   // fp32 [N] or nullptr: multiplies column j (per-output-channel weight scale)
   int fp8_b_format;         // 8-bit operands: format of B in the instruction descriptor (0 = e4m3, 1 = e5m2); A is e4m3
@@ -115,7 +116,7 @@ struct SmemLayout {
   static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16;
   // optional output staging (EpiParams::staged): per epilogue warp 32 rows x kStageCols bf16
   static constexpr int kStageCols = (BLOCK_N % 128 == 0) ? 64 : 32;
-  static constexpr int kStagingOffset = (kTotal + 15) & ~15;
+  static constexpr int kStagingOffset = (kTotal + 1023) & ~1023;   // 1024-byte aligned: the tiles are also TMA-store sources (128B swizzle)
   static constexpr int kStagingBytesPerWarp = 32 * kStageCols * 2;
   static constexpr int kTotalStaged = kStagingOffset + kNumEpilogueWarps * kStagingBytesPerWarp;
 };
@@ -308,7 +309,8 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams& ep, uint32_t (&r
 // and ldb arrive halved (in units of two bytes) and only the TMA coordinates, which count elements, are doubled back.
 template <int A_MN, int B_MN, int BLOCK_N, int STAGES, int FP8 = 0>
 __global__ void __launch_bounds__(kNumThreads, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux, int M, int N,
                  int K, int group_m, int num_splits, int kb_per_split, long long d_split_stride, EpiParams ep,
                  GroupInfo grp, PeerInfo peer, unsigned int* status) {
   using L = SmemLayout<BLOCK_N, STAGES>;
@@ -495,6 +497,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;   // TMEM lane quarter this warp may read
     const int ew = warp - 2;  // 0..7
     const int cgrp = ew >> 2; // which half of the tile's columns this warp handles
+    bool store_pending = false;   // a bulk tensor store of this warp's staging tile may still be reading it
     // ---- all-gather duty (peer modes 1 and 3): every epilogue warp of every CTA owns a strided share of the 16-row
     // pieces of the remote rows, in the order the tiles consume them.  A warp pulls pieces whenever its next
     // accumulator is not ready yet, and finishes its share after its last tile; nothing a piece needs ever waits.
@@ -577,6 +580,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int c = cgrp * (BLOCK_N / 64) + h * (SC / 32) + cc;
             uint32_t r[32];
             tmem_ld_32x32(taddr + c * 32, r);
+            if (cc == 0 && store_pending) {
+              // the bulk store issued for the previous block has to be done reading the tile before it is overwritten
+              if (lane == 0) tma_store_wait_read<0>();
+              __syncwarp();
+              store_pending = false;
+            }
             tmem_ld_wait();
             if (last_pass && cc == SC / 32 - 1) {
               tc_fence_before();
@@ -605,6 +614,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                            "r"(pack_bf16x2(v[qq * 8 + 4], v[qq * 8 + 5])), "r"(pack_bf16x2(v[qq * 8 + 6], v[qq * 8 + 7]))
                            : "memory");
             }
+          }
+          if (SC == 64 && epu.staged == 2) {
+            // the tile leaves through a bulk tensor store; rows and columns past the matrix are clipped by the copy
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(pre_pass ? &tmAux : &tmD, stg, n_blk * BLOCK_N + cgrp * (BLOCK_N / 2) + h * SC,
+                           static_cast<int>(static_cast<long long>(m_blk) * kBlockM + q * 32));
+              tma_store_commit();
+            }
+            store_pending = true;
+            continue;
           }
           __syncwarp();
           constexpr int RPI = 32 / CPR;                            // rows written per warp instruction
@@ -643,6 +664,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     while (next_item < remote_items && !*abort_flag) copy_one();
+    if (lane == 0) tma_store_wait<0>();      // bulk stores of the last tiles have left shared memory and landed
   }
 
   __syncthreads();
@@ -674,14 +696,15 @@ struct SmemLayoutPair {
   static constexpr int kBarOffset = STAGES * kStageBytes;
   static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16;
   static constexpr int kStageCols = (BLOCK_N % 128 == 0) ? 64 : 32;
-  static constexpr int kStagingOffset = (kTotal + 15) & ~15;
+  static constexpr int kStagingOffset = (kTotal + 1023) & ~1023;   // 1024-byte aligned: the tiles are also TMA-store sources (128B swizzle)
   static constexpr int kStagingBytesPerWarp = 32 * kStageCols * 2;
   static constexpr int kTotalStaged = kStagingOffset + kNumEpilogueWarps * kStagingBytesPerWarp;
 };
 
 template <int A_MN, int B_MN, int BLOCK_N, int STAGES, int FP8 = 0>
 __global__ void __launch_bounds__(kNumThreads, 1)
-gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux, int M, int N,
                       int K, int group_m, int num_splits, int kb_per_split, long long d_split_stride, EpiParams ep,
                       unsigned int* status) {
   using L = SmemLayoutPair<BLOCK_N, STAGES>;
@@ -822,6 +845,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int q = warp & 3;
     const int ew = warp - 2;
     const int cgrp = ew >> 2;
+    bool store_pending = false;
     uint32_t t = 0;
     for (int tile = cluster_id; tile < num_units; tile += num_clusters, ++t) {
       int m_blk, n_blk, kb0, kb1, split;
@@ -855,6 +879,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const int c = cgrp * (BLOCK_N / 64) + h * (SC / 32) + cc;
             uint32_t r[32];
             tmem_ld_32x32(taddr + c * 32, r);
+            if (cc == 0 && store_pending) {
+              // the bulk store issued for the previous block has to be done reading the tile before it is overwritten
+              if (lane == 0) tma_store_wait_read<0>();
+              __syncwarp();
+              store_pending = false;
+            }
             tmem_ld_wait();
             if (last_pass && cc == SC / 32 - 1) {
               tc_fence_before();
@@ -879,6 +909,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                            "r"(pack_bf16x2(v[qq * 8 + 4], v[qq * 8 + 5])), "r"(pack_bf16x2(v[qq * 8 + 6], v[qq * 8 + 7]))
                            : "memory");
             }
+          }
+          if (SC == 64 && epu.staged == 2) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(pre_pass ? &tmAux : &tmD, stg, n_blk * BLOCK_N + cgrp * (BLOCK_N / 2) + h * SC, static_cast<int>(row0));
+              tma_store_commit();
+            }
+            store_pending = true;
+            continue;
           }
           __syncwarp();
           constexpr int RPI = 32 / CPR;
@@ -911,6 +951,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (row < M && col0 < N) epilogue_chunk(epu, r, row, col0, N);
       }
     }
+    if (lane == 0) tma_store_wait<0>();
   }
 
   tc_fence_before();
@@ -989,9 +1030,21 @@ bool staged_store_default() {
   return v == 1;
 }
 
+// RUSTRAL_GEMM_TMA_STORE=1 sends staged 64-column tiles out through bulk tensor stores instead of ld.shared / st.global.
+bool tma_store_default() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("RUSTRAL_GEMM_TMA_STORE");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+
 template <int A_MN, int B_MN, int BLOCK_N, int STAGES, int FP8 = 0>
 int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, int grid, int splits, cudaStream_t stream) {
   using L = rb::SmemLayout<BLOCK_N, STAGES>;
+  const CUtensorMap* td = ta;        // placeholders unless the bulk-store epilogue is chosen below
+  const CUtensorMap* tx = ta;
   auto kern = rb::gemm_bf16_kernel<A_MN, B_MN, BLOCK_N, STAGES, FP8>;
   // Staged (coalesced) stores: plain bf16 outputs whose rows are whole 16-byte chunks.  Always on for peer stores.
   const bool can_stage = !g.out_f32 && !g.accumulate && splits <= 1 && (g.N % 8 == 0) && g.group_mode != 2 &&
@@ -1014,6 +1067,13 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
   ep.aux_out = reinterpret_cast<__nv_bfloat16*>(g.aux_out); ep.ld_aux_out = g.ld_aux_out;
   ep.act = g.act; ep.out_f32 = g.out_f32; ep.accumulate = g.accumulate; ep.alpha = g.alpha;
   ep.staged = staged ? 1 : 0;
+  if (staged && g.peer_mode == 0 && L::kStageCols == 64 && tma_store_default()) {
+    int err = 0;
+    td = rbhost::get_tmap_2d(g.d, 2, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ldd, 64, 32, 1, &err);
+    tx = g.aux_out ? rbhost::get_tmap_2d(g.aux_out, 2, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ld_aux_out, 64, 32, 1, &err) : td;
+    if (td && tx) ep.staged = 2;
+    else { td = ta; tx = ta; }
+  }
   ep.row_scale = reinterpret_cast<const float*>(g.a_scale);
   ep.col_scale = reinterpret_cast<const float*>(g.b_scale);
   ep.fp8_b_format = g.ab_fp8 == 2 ? 1 : 0;
@@ -1045,7 +1105,7 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
     peer.a_peer[r] = reinterpret_cast<const __nv_bfloat16*>(g.peer_ptrs[r]);
     peer.d_peer[r] = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(g.peer_ptrs[r]));
   }
-  kern<<<grid, rb::kNumThreads, smem, stream>>>(*ta, *tb, g.M, g.N, k_units, group_m, splits, kb_per, slab, ep, grp, peer,
+  kern<<<grid, rb::kNumThreads, smem, stream>>>(*ta, *tb, *td, *tx, g.M, g.N, k_units, group_m, splits, kb_per, slab, ep, grp, peer,
                                                 rbhost::status_ptr());
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || splits <= 1) return static_cast<int>(e);
@@ -1101,6 +1161,15 @@ int launch_pair(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* t
   ep.aux_out = reinterpret_cast<__nv_bfloat16*>(g.aux_out); ep.ld_aux_out = g.ld_aux_out;
   ep.act = g.act; ep.out_f32 = g.out_f32; ep.accumulate = g.accumulate; ep.alpha = g.alpha;
   ep.staged = staged ? 1 : 0;
+  const CUtensorMap* td = ta;
+  const CUtensorMap* tx = ta;
+  if (staged && tma_store_default()) {
+    int err = 0;
+    td = rbhost::get_tmap_2d(g.d, 2, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ldd, 64, 32, 1, &err);
+    tx = g.aux_out ? rbhost::get_tmap_2d(g.aux_out, 2, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ld_aux_out, 64, 32, 1, &err) : td;
+    if (td && tx) ep.staged = 2;
+    else { td = ta; tx = ta; }
+  }
   ep.row_scale = reinterpret_cast<const float*>(g.a_scale);
   ep.col_scale = reinterpret_cast<const float*>(g.b_scale);
   ep.fp8_b_format = g.ab_fp8 == 2 ? 1 : 0;
@@ -1127,7 +1196,7 @@ int launch_pair(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* t
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *ta, *tb_half, g.M, g.N, k_units, group_m, splits, kb_per, slab, ep,
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *ta, *tb_half, *td, *tx, g.M, g.N, k_units, group_m, splits, kb_per, slab, ep,
                                      rbhost::status_ptr());
   if (e != cudaSuccess || splits <= 1) return static_cast<int>(e);
   const long long n4 = slab / 4;
