@@ -1030,12 +1030,14 @@ bool staged_store_default() {
   return v == 1;
 }
 
-// RUSTRAL_GEMM_TMA_STORE=1 sends staged 64-column tiles out through bulk tensor stores instead of ld.shared / st.global.
+// Staged 64-column tiles leave through bulk tensor stores (one instruction per tile instead of eight ld.shared /
+// st.global pairs per thread); RUSTRAL_GEMM_TMA_STORE=0 keeps the load / store loop.  Measured on one B200, same process:
+// bias + GELU + saved pre-activation 32768 x 3072 x 768 224 -> 194 us, QKV shape 99.3 -> 95.3 us, 8192^3 unchanged.
 bool tma_store_default() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("RUSTRAL_GEMM_TMA_STORE");
-    v = (e && e[0] == '1') ? 1 : 0;
+    v = (e && e[0] == '0') ? 0 : 1;
   }
   return v == 1;
 }

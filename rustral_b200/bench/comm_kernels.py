@@ -11,6 +11,8 @@ line.
 * tp    all-gather -> GEMM, GEMM -> reduce-scatter and the sharded-weight gather -> GEMM fused over peer memory
         (`parallel.fused_tp.FusedTP`) against NCCL collective + the same GEMM kernel, and the GEMM alone;
 * ep    one expert-parallel MoE layer forward (peer-memory dispatch / combine + grouped GEMM);
+* nvls  in-switch reduce-scatter and all-reduce (`parallel.nvls.MulticastBuffer`: multimem.ld_reduce / multimem.st) against
+        NCCL's reduce_scatter_tensor / all_reduce on the same sizes;
 * ring  ring / striped context-parallel attention forward + backward: send / recv relay against K / V pulled from peer
         memory by a kernel or by the copy engines.
 """
@@ -176,9 +178,60 @@ def bench_ring(rank, world, dev, group, a):
 
 
 
+def bench_nvls(rank, world, dev, iters):
+    """In-switch collectives (multimem.ld_reduce / multimem.st over an NVLink multicast buffer) against NCCL on the same
+    sizes.  The kernels alone, back to back; ranks are aligned by a barrier before each timed loop."""
+    from rustral_b200.parallel.nvls import MulticastBuffer
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t) * 1e3                                    # microseconds, slowest rank
+
+    rows = []
+    for mb in (28, 256):                                         # one GPT-2-small layer's fp32 gradients; a large bucket
+        n = mb * (1 << 20) // 4 // (world * 128) * (world * 128)
+        buf = MulticastBuffer(n * 4, None, dev)
+        buf.view(torch.float32, n).normal_()
+        per = n // world
+        shard = torch.empty(per, device=dev)
+        src = torch.randn(n, device=dev)
+        t_mc = timed(lambda: buf.reduce_into(shard, rank * per))
+        t_nccl = timed(lambda: dist.reduce_scatter_tensor(shard, src))
+        # bytes that reach this rank: its slice once through the switch; over peer loads it would be (world - 1) slices
+        rows.append({"op": "reduce_scatter_f32", "mbytes": mb, "multimem_us": round(t_mc, 1), "nccl_us": round(t_nccl, 1),
+                     "multimem_gbs_in": round(per * 4 / t_mc / 1e3, 1), "nccl_over_multimem": round(t_nccl / t_mc, 2)})
+        torch.cuda.synchronize()
+        dist.barrier()
+        buf.close()
+    for rows_, cols in ((64, 4096), (2048, 4096)):               # decode batch / prefill chunk activations, bf16
+        n = rows_ * cols
+        buf = MulticastBuffer(n * 2, None, dev)
+        buf.view(torch.bfloat16, n).normal_()
+        x = torch.randn(n, device=dev).bfloat16()
+        t_mc = timed(lambda: buf.all_reduce_slice_(torch.bfloat16))
+        t_nccl = timed(lambda: dist.all_reduce(x))
+        rows.append({"op": "all_reduce_bf16", "shape": [rows_, cols], "multimem_us": round(t_mc, 1), "nccl_us": round(t_nccl, 1),
+                     "nccl_over_multimem": round(t_nccl / t_mc, 2)})
+        torch.cuda.synchronize()
+        dist.barrier()
+        buf.close()
+    return {"bench": rows}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["tp", "ep", "ring"])
+    ap.add_argument("what", choices=["tp", "ep", "ring", "nvls"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--seq-local", type=int, default=8192)
@@ -201,6 +254,8 @@ def main(argv=None):
         tp.close()
     elif a.what == "ep":
         out.update(bench_ep(rank, world, dev, a.iters))
+    elif a.what == "nvls":
+        out.update(bench_nvls(rank, world, dev, a.iters))
     else:
         out.update(bench_ring(rank, world, dev, dist.group.WORLD, a))
     torch.cuda.synchronize()

@@ -212,6 +212,8 @@ class _PeerTransport:
     gradients of bucket b are written", bounded waits, "I am done reading your buffer") and the local part of the
     reduce-scatter (`rb_zero3_sum` on the main stream: own slice + the pulled slices, rank order, into the shard).
     "kernel": `rb_zero3_gather` / `rb_zero3_reduce` pull with peer loads from inside the kernels.
+    "nvls" (reduce only, `RUSTRAL_Z3_REDUCE=nvls`): the gradient staging buffers are bound to an NVLink multicast object
+    and a rank's slice is reduced inside the switch by one `multimem.ld_reduce` pass (`parallel/nvls.py`).
     """
     overlapped = True
 
@@ -263,6 +265,14 @@ class _PeerTransport:
         return buf.view(torch.bfloat16, n)
 
     def alloc_grad_buffer(self, n):
+        if self.reduce_mode == "nvls":
+            # bound to an NVLink multicast object: the reduce-scatter is one multimem.ld_reduce pass over the own slice
+            from .nvls import MulticastBuffer
+            buf = MulticastBuffer(n * 4, self.sp.group, self.sp.device)
+            self._symm.append(buf)
+            t = buf.view(torch.float32, n)
+            self._grad_bufs[t.data_ptr()] = buf
+            return t
         buf = self._SymmetricBuffer(n * 4, self.sp.group, self.sp.device)
         self._symm.append(buf)
         t = buf.view(torch.float32, n)
@@ -369,10 +379,32 @@ class _PeerTransport:
             a.n, a.num_src, a.accumulate = b.n_per_rank, sp.world, int(accumulate)
             N.check(N.kernels().rb_zero3_sum(a, N.stream_ptr()), "rb_zero3_sum")
 
+    def _reduce_nvls(self, b: Bucket, buf: torch.Tensor, accumulate: bool):
+        """Reduce-scatter through the switch: flag "my gradients are written", (side stream) wait for everybody's flag,
+        one `multimem.ld_reduce` pass over this rank's slice straight into the gradient shard, flag "done reading"."""
+        sp, lib = self.sp, N.kernels()
+        W, rank, npr = sp.world, sp.rank, b.n_per_rank
+        ready, consumed = CH_BASE + b.index, CH_BASE + len(sp.buckets) + b.index
+        N.check(lib.rb_zero3_signal(self.pad.ptrs_dev.data_ptr(), W, rank, ready, self.micro_epoch.data_ptr(), N.stream_ptr()),
+                "rb_zero3_signal")
+        main = torch.cuda.current_stream(sp.device)
+        self.rs.wait_stream(main)
+        mc = self._grad_bufs[buf.data_ptr()]
+        with torch.cuda.stream(self.rs):
+            N.check(lib.rb_zero3_wait(self.pad.local_ptr, W, ready, self.micro_epoch.data_ptr(), 0, self.limit_ms, N.stream_ptr()),
+                    "rb_zero3_wait")
+            mc.reduce_into(sp.gshard[b.shard_start:b.shard_start + npr], rank * npr, accumulate, self.reduce_ctas)
+            N.check(lib.rb_zero3_signal(self.pad.ptrs_dev.data_ptr(), W, rank, consumed, self.micro_epoch.data_ptr(), N.stream_ptr()),
+                    "rb_zero3_signal")
+        self._pending_reduce = True
+
     def reduce(self, b: Bucket, buf: torch.Tensor, slot, accumulate: bool):
         sp = self.sp
         if self.reduce_mode == "dma":
             self._reduce_dma(b, buf, accumulate)
+            return
+        if self.reduce_mode == "nvls":
+            self._reduce_nvls(b, buf, accumulate)
             return
         main = torch.cuda.current_stream(sp.device)
         if not self.serial:

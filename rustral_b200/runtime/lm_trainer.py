@@ -106,7 +106,8 @@ class LMTrainer:
             return "single"
         kind = type(self.comm).__name__
         tr = getattr(self.engine.params, "transport", None)
-        how = {"Zero3Comm": "peer" if getattr(tr, "overlapped", False) else "collective",
+        peer = "peer-nvls" if getattr(tr, "reduce_mode", "") == "nvls" else "peer"
+        how = {"Zero3Comm": peer if getattr(tr, "overlapped", False) else "collective",
                "FusedZeroComm": "push", "NcclZeroComm": "nccl"}.get(kind, kind)
         return f"dp{self.world}-zero{self.zero_stage}-{how}"
 

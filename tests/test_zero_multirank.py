@@ -90,3 +90,33 @@ def test_fused_zero_trainer_can_be_closed_and_rebuilt_in_one_process(stage):
                extra_args=["--reopen", "--zero-stage", str(stage), "--steps", "6"])
     assert out["status"] == 0
     assert out["reopened"] == out["losses"]
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_nvlink_multicast_collectives_match_peer_loads():
+    """multimem.ld_reduce / multimem.st kernels (in-switch reduce-scatter, all-reduce, broadcast) against sums formed from
+    the peers' buffers with plain loads."""
+    env = dict(os.environ)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29661", os.path.join(ROOT, "tests", "mp_nvls_worker.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    if "no NVLink multicast address" in res.stdout + res.stderr:
+        pytest.skip("this machine has no NVLink multicast")
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["status_max"] == 0 and out["reduce_repeatable"] and out["broadcast_ok"]
+    assert out["reduce_max_err"] < 1e-5 and out["accumulate_max_err"] < 1e-5 and out["allreduce_max_err"] < 1e-5
+    assert out["allreduce_bf16_rel_err"] < 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_zero3_with_in_switch_reduce_scatter_matches_one_gpu():
+    """ZeRO-3 with the gradient reduce-scatter done by multimem.ld_reduce through the NVSwitch."""
+    one = _run(1, "nccl", "cuda", 29671, extra_args=["--steps", "6"])
+    two = _run(2, "fused", "cuda", 29672, {"RUSTRAL_Z3_REDUCE": "nvls"}, extra_args=["--zero-stage", "3", "--steps", "6"])
+    assert two["status"] == 0 and two["parallelism"] == "dp2-zero3-peer-nvls"
+    for a, b in zip(one["losses"], two["losses"]):
+        assert abs(a - b) < 3e-2, (one["losses"], two["losses"])
+    assert abs(one["checksum"] - two["checksum"]) < 2e-3 * abs(one["checksum"])
