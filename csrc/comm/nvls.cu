@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "flags.cuh"
 #include "nvls.h"
 #include "rb_common.cuh"
 
@@ -92,6 +93,43 @@ mc_broadcast_kernel(const uint4* __restrict__ src, void* mc, long long count) {
     mc_st_b32x4(base + i, __ldg(src + i));
 }
 
+// One-shot all-reduce of a small activation for tensor-parallel inference: raise this rank's flag on every peer, wait
+// (bounded) for all flags, then every rank reads the whole tensor through the multicast address, i.e. summed inside the
+// switch (bf16 pairs, fp32 accumulation), adds the residual and writes its own output.  One load per 16 bytes instead of
+// one per rank, and `world` times fewer bytes into each GPU than the peer-load kernel (`rb_tp_allreduce`).
+__global__ void __launch_bounds__(256)
+tp_allreduce_mc_kernel(const void* __restrict__ mc_stage, void* const* __restrict__ pad_ptrs, const unsigned int* __restrict__ local_pad,
+                       int world, int rank, int channel, const unsigned int* __restrict__ epoch_dev, unsigned long long limit_ns,
+                       const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out, long long n8,
+                       unsigned int* status) {
+  __shared__ int ok_s;
+  const unsigned int epoch = *epoch_dev;
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<unsigned int*>(pad_ptrs[threadIdx.x]) + channel * world + rank, epoch);
+  }
+  if (threadIdx.x == 0) ok_s = wait_flags(local_pad, world, channel, epoch, limit_ns, status, 130 + channel) ? 1 : 0;
+  __syncthreads();
+  if (!ok_s) return;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    uint4 u = mc_ld_reduce_bf16x8(reinterpret_cast<const uint4*>(mc_stage) + i);
+    if (residual) {
+      const uint4 r = __ldg(reinterpret_cast<const uint4*>(residual) + i);
+      const uint32_t* pu = reinterpret_cast<const uint32_t*>(&u);
+      const uint32_t* pr = reinterpret_cast<const uint32_t*>(&r);
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = unpack_bf16x2(pu[j]), b = unpack_bf16x2(pr[j]);
+        o[j] = pack_bf16x2(a.x + b.x, a.y + b.y);
+      }
+      u = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    reinterpret_cast<uint4*>(out)[i] = u;
+  }
+}
+
 }  // namespace rb
 
 namespace {
@@ -127,5 +165,19 @@ RB_API int rb_mc_broadcast(const void* src, void* mc, long long byte_offset, lon
   if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(mc)) & 15) return -2;
   rb::mc_broadcast_kernel<<<mc_grid(nbytes / 16, max_ctas), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint4*>(src), reinterpret_cast<uint8_t*>(mc) + byte_offset, nbytes / 16);
+  return static_cast<int>(cudaGetLastError());
+}
+
+RB_API int rb_tp_allreduce_mc(const void* mc_stage, void* const* pad_ptrs_dev, const void* local_pad, int world, int rank, int channel,
+                              const unsigned int* epoch_dev, int limit_ms, const void* residual, void* out, int rows, int cols,
+                              void* stream) {
+  if (!mc_stage || !pad_ptrs_dev || !local_pad || !epoch_dev || !out || world < 1 || world > 8 || rank < 0 || rank >= world) return -1;
+  if (rows <= 0 || cols <= 0 || (cols % 8) || channel < 0 || limit_ms <= 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(mc_stage) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residual)) & 15) return -2;
+  const long long n8 = static_cast<long long>(rows) * (cols / 8);
+  rb::tp_allreduce_mc_kernel<<<mc_grid(n8, 148 * 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      mc_stage, pad_ptrs_dev, reinterpret_cast<const unsigned int*>(local_pad), world, rank, channel, epoch_dev,
+      static_cast<unsigned long long>(limit_ms) * 1000000ull, reinterpret_cast<const __nv_bfloat16*>(residual),
+      reinterpret_cast<__nv_bfloat16*>(out), n8, rbhost::status_ptr());
   return static_cast<int>(cudaGetLastError());
 }

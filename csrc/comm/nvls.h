@@ -11,6 +11,10 @@ int rb_mc_reduce_f32(const void* mc, long long elem_offset, void* dst, long long
 int rb_mc_allreduce(void* mc, long long byte_offset, long long nbytes, int bf16, int max_ctas, void* stream);
 // Copies nbytes from local memory `src` to offset byte_offset of every rank's buffer.
 int rb_mc_broadcast(const void* src, void* mc, long long byte_offset, long long nbytes, int max_ctas, void* stream);
+// One-shot all-reduce for tensor-parallel inference: out = sum over ranks of the staged [rows, cols] bf16 tensor at the
+// multicast address `mc_stage` (+ residual).  Flags as in rb_tp_allreduce (signal pad, device-resident epoch, bounded wait).
+int rb_tp_allreduce_mc(const void* mc_stage, void* const* pad_ptrs_dev, const void* local_pad, int world, int rank, int channel,
+                       const unsigned int* epoch_dev, int limit_ms, const void* residual, void* out, int rows, int cols, void* stream);
 #ifdef __cplusplus
 }
 #endif

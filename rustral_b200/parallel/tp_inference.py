@@ -16,18 +16,32 @@ from .symm import SignalPad, SymmetricBuffer
 
 P, I = N.c_void_p, N.c_int
 N.optional_sig("rb_tp_allreduce", [P, P, P, I, I, I, N.C.c_uint, P, I, P, P, I, I, I, P])
+N.optional_sig("rb_tp_allreduce_mc", [P, P, P, I, I, I, P, I, P, P, I, I, P])
 
 
 class TPInferenceComm:
-    def __init__(self, group, device, max_elems: int, limit_ms: int = 5000):
+    """`transport`: "peer" (default; `RUSTRAL_TP_ALLREDUCE` overrides): every rank sums the peers' staged tensors with
+    plain peer loads in rank order.  "nvls": the staging buffers are bound to an NVLink multicast object and the sum is
+    formed inside the NVSwitch (`multimem.ld_reduce`, `csrc/comm/nvls.cu`): one load per 16 bytes instead of one per rank;
+    the all-gather keeps the peer loads."""
+
+    def __init__(self, group, device, max_elems: int, limit_ms: int = 5000, transport: str | None = None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.device = torch.device(device)
         self.max_elems = max_elems
         self.limit_ms = limit_ms
+        import os
+        self.transport = transport or os.environ.get("RUSTRAL_TP_ALLREDUCE", "peer")
+        if self.transport not in ("peer", "nvls"):
+            raise ValueError(f"TPInferenceComm: unknown transport {self.transport!r}")
         self.pad = SignalPad(group, self.device)
-        self.stage = [SymmetricBuffer(max_elems * 2, group, self.device) for _ in range(2)]
+        if self.transport == "nvls":
+            from .nvls import MulticastBuffer
+            self.stage = [MulticastBuffer(max_elems * 2, group, self.device) for _ in range(2)]
+        else:
+            self.stage = [SymmetricBuffer(max_elems * 2, group, self.device) for _ in range(2)]
         self.calls = 0                   # host count of collective calls: selects the staging buffer
         # The epoch the flags carry lives on the device and is advanced by a kernel before every collective, so a
         # decode step captured in a CUDA graph uses fresh epochs at every replay.
@@ -44,6 +58,11 @@ class TPInferenceComm:
         self.calls += 1
         st = self.stage[self.calls & 1]
         self.epoch_dev.add_(1)
+        if self.transport == "nvls" and not gather:
+            N.check(N.kernels().rb_tp_allreduce_mc(st.mc_ptr, self.pad.ptrs_dev.data_ptr(), self.pad.local_ptr, self.world, self.rank,
+                                                   0, self.epoch_dev.data_ptr(), self.limit_ms, N.ptr(residual), out.data_ptr(),
+                                                   rows, cols, N.stream_ptr()), "rb_tp_allreduce_mc")
+            return out
         N.check(N.kernels().rb_tp_allreduce(st.ptrs_dev.data_ptr(), self.pad.ptrs_dev.data_ptr(), self.pad.local_ptr,
                                             self.world, self.rank, 0, 0, self.epoch_dev.data_ptr(), self.limit_ms,
                                             N.ptr(residual), out.data_ptr(), rows, cols, gather, N.stream_ptr()),

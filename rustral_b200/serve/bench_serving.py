@@ -44,6 +44,8 @@ def main(argv=None):
     ap.add_argument("--time-limit", type=float, default=3600.0)
     ap.add_argument("--rates", type=float, nargs="+", default=None, help="arrival-rate sweep (requests/s), ascending")
     ap.add_argument("--ttft-limit-ms", type=float, default=1000.0, help="the sweep stops once p99 TTFT exceeds this")
+    ap.add_argument("--tp-allreduce", default=None, choices=["peer", "nvls"],
+                    help="per-layer all-reduce of the tensor-parallel ranks: peer loads (default) or in-switch multimem reduction")
     ap.add_argument("--prefill-chunk", type=int, default=2048, help="prompt tokens per step (0: whole prompts, one pass each)")
     a = ap.parse_args(argv)
     over = {"n_layer": a.layers} if a.layers else {}
@@ -59,7 +61,7 @@ def main(argv=None):
             raise SystemExit(f"--tp {a.tp} but WORLD_SIZE={dist.get_world_size()}")
         from ..parallel.tp_inference import TPInferenceComm
         rows = max(a.prompt[1], a.max_batch, a.prefill_chunk + a.max_batch)
-        tp = TPInferenceComm(None, dev, max_elems=rows * max(cfg.d_model, cfg.vocab_padded // a.tp))
+        tp = TPInferenceComm(None, dev, max_elems=rows * max(cfg.d_model, cfg.vocab_padded // a.tp), transport=a.tp_allreduce)
         clock = tp.broadcast_scalar
     else:
         dev = "cuda" if torch.cuda.is_available() else "cpu"
@@ -74,7 +76,7 @@ def main(argv=None):
     eng.generate(list(range(1, 33)), 4)
     eng.scheduler.completed.clear()
     out = {"metric": "serving", "model": a.model, "layers": cfg.n_layer, "requests": a.requests, "rate_per_s": a.rate,
-           "page_size": a.page, "decoding": "greedy", "tp": a.tp, "prefill_chunk": a.prefill_chunk, "max_batch": a.max_batch,
+           "page_size": a.page, "decoding": "greedy", "tp": a.tp, "tp_allreduce": (tp.transport if tp is not None else None), "prefill_chunk": a.prefill_chunk, "max_batch": a.max_batch,
            "data": "synthetic uniform random prompt tokens; random-init weights"}
     if a.rates:
         sweep, saturated = [], None

@@ -25,11 +25,12 @@ def main():
     cfg = GPTConfig(vocab_size=1000, seq_len=512, n_layer=2, n_head=4, n_kv_head=2, d_model=256, ffn_dim=512, arch="llama",
                     vocab_multiple=128)
     full = FlatParams(cfg, dev, seed=3)                       # the same on every rank
-    tp = TPInferenceComm(None, dev, max_elems=512 * 1024)
+    tp = TPInferenceComm(None, dev, max_elems=512 * 1024, transport=os.environ.get("TP_TRANSPORT", "peer"))
+    out_transport = tp.transport
     ref = ModelRunner(cfg, params=full, device=dev, num_blocks=64)
     shard = ModelRunner(cfg, params=InferenceWeights.shard_of(full, cfg, rank, world), device=dev, num_blocks=64, tp=tp)
     prompt = torch.randint(0, cfg.vocab_size, (77,), generator=torch.Generator().manual_seed(1)).tolist()
-    out = {"world": world}
+    out = {"world": world, "transport": out_transport}
     # go through the engines: same greedy tokens from both
     e_ref, e_tp = ServingEngine(ref), ServingEngine(shard)
     t_ref = e_ref.generate(prompt, 12)

@@ -42,20 +42,25 @@ def test_gpu_engine_continuous_batching_completes(cuda_status):
 
 @pytest.mark.gpu
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_tensor_parallel_serving_matches_single_gpu():
+@pytest.mark.parametrize("transport", ["peer", "nvls"])
+def test_tensor_parallel_serving_matches_single_gpu(transport):
+    """`nvls`: the per-layer all-reduces are summed inside the NVSwitch (multimem.ld_reduce); all ranks must still hold
+    bit-identical logits, or their samplers would part ways."""
     import json
     import os
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ)
-    env["NCCL_NVLS_ENABLE"] = "0"
+    env["TP_TRANSPORT"] = transport
+    if transport == "peer":
+        env["NCCL_NVLS_ENABLE"] = "0"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29681", os.path.join(root, "tests", "mp_serve_worker.py")]
+           "--master-port", "29681" if transport == "peer" else "29683", os.path.join(root, "tests", "mp_serve_worker.py")]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=root)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
-    assert out["status_max"] == 0 and out["ranks_identical"]
+    assert out["status_max"] == 0 and out["ranks_identical"] and out["transport"] == transport
     assert out["prefill_rel_err"] < 3e-2, out
     # greedy decoding of random-init logits can flip on near ties; the first tokens must agree
     assert out["tokens_ref"][:4] == out["tokens_tp"][:4], out
