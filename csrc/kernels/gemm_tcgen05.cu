@@ -124,12 +124,14 @@ struct SmemLayout {
 // Epilogue arithmetic on 32 consecutive accumulator columns of one output row (everything but the final store).
 // STORE_AUX: write the pre-activation to aux_out from here (one 64-byte piece per thread).  PRE_ONLY: stop after
 // the bias, leaving the pre-activation in v (the staged path writes it out itself, coalesced).
-template <bool STORE_AUX = true, bool PRE_ONLY = false>
+// POST_ONLY: v already holds the pre-activation; only the activation and the residual are applied.
+template <bool STORE_AUX = true, bool PRE_ONLY = false, bool POST_ONLY = false>
 __device__ __forceinline__ void epilogue_math(const EpiParams& ep, uint32_t (&r)[32], long long row, int col0, int N,
                                               float (&v)[32]) {
+  const bool full = (col0 + 32 <= N);
+  if (!POST_ONLY) {
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
-  const bool full = (col0 + 32 <= N);
 
   if (ep.row_scale != nullptr) {
     const float rs = __ldg(ep.row_scale + row);
@@ -167,6 +169,8 @@ __device__ __forceinline__ void epilogue_math(const EpiParams& ep, uint32_t (&r)
         if (col0 + j < N) v[j] += __bfloat162float(ep.bias[col0 + j]);
     }
   }
+
+  }   // !POST_ONLY
 
   if (PRE_ONLY) return;
 
@@ -565,6 +569,92 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         constexpr int NB = (BLOCK_N / 2) / SC;                    // column blocks per warp group
         const bool two_pass = epu.aux_out != nullptr &&
                               (epu.act == RB_ACT_GELU || epu.act == RB_ACT_RELU || epu.act == RB_ACT_SILU);
+        if (SC == 64 && epu.staged == 2 && two_pass) {
+          // One pass over the accumulator: the pre-activation is rounded to bf16, kept packed in registers for the 64
+          // columns of a block and sent to aux_out by a bulk store; the activation is computed from the rounded values
+          // while that store reads the tile, and follows through the same tile to d.
+#pragma unroll 1
+          for (int h = 0; h < NB; ++h) {
+            uint32_t keep[2][16];
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+              const int c = cgrp * (BLOCK_N / 64) + h * 2 + cc;
+              uint32_t r[32];
+              tmem_ld_32x32(taddr + c * 32, r);
+              if (cc == 0 && store_pending) {
+                if (lane == 0) tma_store_wait_read<0>();
+                __syncwarp();
+                store_pending = false;
+              }
+              tmem_ld_wait();
+              if (h == NB - 1 && cc == 1) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+              }
+              const int col0 = n_blk * BLOCK_N + c * 32;
+              float v[32];
+              if (empty_k) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0u;
+              }
+              if (row < M && col0 < N) {
+                epilogue_math<false, true>(epu, r, row, col0, N, v);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = 0.f;
+              }
+#pragma unroll
+              for (int i = 0; i < 16; ++i) keep[cc][i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+#pragma unroll
+              for (int qq = 0; qq < 4; ++qq) {
+                const uint32_t addr = stg + lane * (SC * 2) + (((cc * 4 + qq) ^ (lane & (CPR - 1))) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(keep[cc][qq * 4 + 0]), "r"(keep[cc][qq * 4 + 1]),
+                             "r"(keep[cc][qq * 4 + 2]), "r"(keep[cc][qq * 4 + 3]) : "memory");
+              }
+            }
+            const int colb = n_blk * BLOCK_N + cgrp * (BLOCK_N / 2) + h * SC;
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmAux, stg, colb, static_cast<int>((static_cast<long long>(m_blk) * kBlockM + q * 32)));
+              tma_store_commit();
+            }
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+              const int col0 = colb + cc * 32;
+              float v[32];
+              uint32_t dummy[32];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float2 f = unpack_bf16x2(keep[cc][i]);
+                v[2 * i] = f.x; v[2 * i + 1] = f.y;
+              }
+              if (row < M && col0 < N) epilogue_math<false, false, true>(epu, dummy, row, col0, N, v);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) keep[cc][i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+            }
+            if (lane == 0) tma_store_wait_read<0>();       // the pre-activation tile has been read out
+            __syncwarp();
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+              for (int qq = 0; qq < 4; ++qq) {
+                const uint32_t addr = stg + lane * (SC * 2) + (((cc * 4 + qq) ^ (lane & (CPR - 1))) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(keep[cc][qq * 4 + 0]), "r"(keep[cc][qq * 4 + 1]),
+                             "r"(keep[cc][qq * 4 + 2]), "r"(keep[cc][qq * 4 + 3]) : "memory");
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmD, stg, colb, static_cast<int>((static_cast<long long>(m_blk) * kBlockM + q * 32)));
+              tma_store_commit();
+            }
+            store_pending = true;
+          }
+          continue;
+        }
         const int num_pass = two_pass ? 2 : 1;
 #pragma unroll 1
         for (int hp = 0; hp < NB * num_pass; ++hp) {
@@ -866,6 +956,92 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         constexpr int NB = (BLOCK_N / 2) / SC;
         const bool two_pass = epu.aux_out != nullptr &&
                               (epu.act == RB_ACT_GELU || epu.act == RB_ACT_RELU || epu.act == RB_ACT_SILU);
+        if (SC == 64 && epu.staged == 2 && two_pass) {
+          // One pass over the accumulator: the pre-activation is rounded to bf16, kept packed in registers for the 64
+          // columns of a block and sent to aux_out by a bulk store; the activation is computed from the rounded values
+          // while that store reads the tile, and follows through the same tile to d.
+#pragma unroll 1
+          for (int h = 0; h < NB; ++h) {
+            uint32_t keep[2][16];
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+              const int c = cgrp * (BLOCK_N / 64) + h * 2 + cc;
+              uint32_t r[32];
+              tmem_ld_32x32(taddr + c * 32, r);
+              if (cc == 0 && store_pending) {
+                if (lane == 0) tma_store_wait_read<0>();
+                __syncwarp();
+                store_pending = false;
+              }
+              tmem_ld_wait();
+              if (h == NB - 1 && cc == 1) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(tempty_leader);
+              }
+              const int col0 = n_blk * BLOCK_N + c * 32;
+              float v[32];
+              if (false) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0u;
+              }
+              if (row < M && col0 < N) {
+                epilogue_math<false, true>(epu, r, row, col0, N, v);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = 0.f;
+              }
+#pragma unroll
+              for (int i = 0; i < 16; ++i) keep[cc][i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+#pragma unroll
+              for (int qq = 0; qq < 4; ++qq) {
+                const uint32_t addr = stg + lane * (SC * 2) + (((cc * 4 + qq) ^ (lane & (CPR - 1))) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(keep[cc][qq * 4 + 0]), "r"(keep[cc][qq * 4 + 1]),
+                             "r"(keep[cc][qq * 4 + 2]), "r"(keep[cc][qq * 4 + 3]) : "memory");
+              }
+            }
+            const int colb = n_blk * BLOCK_N + cgrp * (BLOCK_N / 2) + h * SC;
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmAux, stg, colb, static_cast<int>(row0));
+              tma_store_commit();
+            }
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+              const int col0 = colb + cc * 32;
+              float v[32];
+              uint32_t dummy[32];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float2 f = unpack_bf16x2(keep[cc][i]);
+                v[2 * i] = f.x; v[2 * i + 1] = f.y;
+              }
+              if (row < M && col0 < N) epilogue_math<false, false, true>(epu, dummy, row, col0, N, v);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) keep[cc][i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+            }
+            if (lane == 0) tma_store_wait_read<0>();       // the pre-activation tile has been read out
+            __syncwarp();
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+              for (int qq = 0; qq < 4; ++qq) {
+                const uint32_t addr = stg + lane * (SC * 2) + (((cc * 4 + qq) ^ (lane & (CPR - 1))) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(keep[cc][qq * 4 + 0]), "r"(keep[cc][qq * 4 + 1]),
+                             "r"(keep[cc][qq * 4 + 2]), "r"(keep[cc][qq * 4 + 3]) : "memory");
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmD, stg, colb, static_cast<int>(row0));
+              tma_store_commit();
+            }
+            store_pending = true;
+          }
+          continue;
+        }
         const int num_pass = two_pass ? 2 : 1;
 #pragma unroll 1
         for (int hp = 0; hp < NB * num_pass; ++hp) {
