@@ -13,7 +13,8 @@ namespace rb {
 // one warp per (token, choice) pair; lanes cover the row with 16-byte vectors
 __global__ void __launch_bounds__(256)
 ep_push_rows_kernel(const __nv_bfloat16* __restrict__ src, int pairs, int k, int d, const int* __restrict__ dest_rank,
-                    const int* __restrict__ dest_row, const float* __restrict__ scale, void* const* __restrict__ peer_bufs) {
+                    const int* __restrict__ dest_row, const float* __restrict__ scale, void* const* __restrict__ peer_bufs,
+                    void* const* __restrict__ peer_counts) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n8 = d / 8;
@@ -34,6 +35,15 @@ ep_push_rows_kernel(const __nv_bfloat16* __restrict__ src, int pairs, int k, int
         }
       }
       dst[i] = v;
+    }
+    if (peer_counts != nullptr) {
+      // the row is complete: count it for the 128-row tile it belongs to, so that the owner's grouped GEMM can start on
+      // that tile as soon as all of its rows have arrived
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_system();
+        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(reinterpret_cast<unsigned int*>(peer_counts[r]) + (row >> 7)), "r"(1u) : "memory");
+      }
     }
   }
 }
@@ -134,12 +144,12 @@ bool bad_row(const void* p, int d) { return !p || (reinterpret_cast<uintptr_t>(p
 }  // namespace
 
 RB_API int rb_ep_push_rows(const void* src, int tokens, int k, int d, const int* dest_rank, const int* dest_row,
-                           const float* scale, void* const* peer_bufs_dev, void* stream_v) {
+                           const float* scale, void* const* peer_bufs_dev, void* const* peer_counts_dev, void* stream_v) {
   if (bad_row(src, d) || tokens < 0 || k <= 0 || !dest_rank || !dest_row || !peer_bufs_dev) return -1;
   if (tokens == 0) return 0;
   const int pairs = tokens * k;
   rb::ep_push_rows_kernel<<<grid_for(pairs), 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
-      reinterpret_cast<const __nv_bfloat16*>(src), pairs, k, d, dest_rank, dest_row, scale, peer_bufs_dev);
+      reinterpret_cast<const __nv_bfloat16*>(src), pairs, k, d, dest_rank, dest_row, scale, peer_bufs_dev, peer_counts_dev);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -67,6 +67,8 @@ struct GroupInfo {
   const int* offsets;
   int b_expert_rows;
   long long d_expert_stride;
+  const unsigned int* tile_arrived;   // mode 1, optional: rows of A's 128-row tiles stored so far by the dispatching ranks
+  const int* tile_expected;           //                    rows each tile has to receive before it may be read
 };
 
 // Fusion with tensor-parallel collectives over peer memory (NVLink loads / stores issued by this kernel).
@@ -102,6 +104,11 @@ __device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) 
 }
 __device__ __forceinline__ void red_release_gpu_add(unsigned int* p, unsigned int v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
 constexpr int kCopyParts = 32;    // a remote 128-row block is pulled as 32 pieces of 4 rows, by different warps of different CTAs
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
@@ -414,6 +421,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (grp.mode == 1) {
           const int e = __ldg(grp.tile_expert + m_blk);
           b_row_off = (e < 0 ? 0 : e) * grp.b_expert_rows;
+        }
+        if (grp.mode == 1 && grp.tile_arrived != nullptr) {
+          // expert-parallel dispatch still in flight: this 128-row tile of A is complete once every rank has stored the
+          // rows it routes here (counted with system-scope release adds by the dispatch kernels)
+          const unsigned int want = static_cast<unsigned int>(__ldg(grp.tile_expected + m_blk));
+          const unsigned long long t0 = globaltimer_ns();
+          while (ld_acquire_sys_u32(grp.tile_arrived + m_blk) < want) {
+            if (*abort_flag || globaltimer_ns() - t0 > kFlagWaitLimitNs) {
+              *abort_flag = 1;
+              status_set(status, kStatusFlagTimeout, 6);
+              ok = false;
+              break;
+            }
+            __nanosleep(100);
+          }
+          if (!ok) break;
+          fence_proxy_async_all();
         }
         if (peer.mode == 1 || peer.mode == 3) {
           // remote 128-row blocks this tile reads: wait until the copy warps have landed all their pieces
@@ -1273,6 +1297,8 @@ int launch(const RbGemmArgs& g, const CUtensorMap* ta, const CUtensorMap* tb, in
   grp.num_m_tiles = reinterpret_cast<const int*>(g.num_m_tiles);
   grp.offsets = reinterpret_cast<const int*>(g.expert_offsets);
   grp.b_expert_rows = g.b_expert_rows; grp.d_expert_stride = g.d_expert_stride;
+  grp.tile_arrived = reinterpret_cast<const unsigned int*>(g.tile_arrived);
+  grp.tile_expected = reinterpret_cast<const int*>(g.tile_expected);
   rb::PeerInfo peer;
   memset(&peer, 0, sizeof(peer));
   peer.mode = g.peer_mode; peer.world = g.peer_world; peer.rank = g.peer_rank; peer.rows_per_rank = g.rows_per_rank;
@@ -1477,6 +1503,7 @@ RB_API int rb_gemm_bf16(const RbGemmArgs* args, void* stream_v) {
 
   if (g.group_mode < 0 || g.group_mode > 2) return -8;
   if (g.group_mode == 1 && (!g.tile_expert || !g.num_m_tiles || g.b_expert_rows <= 0)) return -8;
+  if ((g.tile_arrived == nullptr) != (g.tile_expected == nullptr) || (g.tile_arrived && g.group_mode != 1)) return -8;
   if (g.group_mode == 1 && g.b_mn_major && (g.K % 64)) return -8;     // expert K ranges must be whole k-blocks
   if (g.group_mode == 2 && (!g.expert_offsets || g.num_experts <= 0 || !g.a_mn_major || !g.b_mn_major)) return -8;
   if (g.peer_mode < 0 || g.peer_mode > 3) return -11;

@@ -57,6 +57,11 @@ typedef struct RbGemmArgs {
   // 8-bit floating-point operands (tcgen05 kind::f8f6f4, fp32 accumulation): a and b hold e4m3 bytes, both K-major,
   // lda / ldb / K count bytes (multiples of 16).  Plain and grouped mode 1 problems only.  For every operand type the
   // accumulator of row i, column j is multiplied by a_scale[i] * b_scale[j] (each may be NULL) before the bias.
+  // grouped mode 1 fed by an expert-parallel dispatch that is still in flight: tile_arrived[i] (device u32, written by
+  // the ranks that store rows of 128-row tile i of A) is waited for (bounded) to reach tile_expected[i] before tile i
+  // of A is loaded.  Both NULL: A is complete when the kernel starts.
+  const void* tile_arrived;
+  const void* tile_expected;
   int ab_fp8;                  // 0: bf16 operands; 1: a and b e4m3; 2: a e4m3, b e5m2
   const void* a_scale;         // fp32 [M] or NULL: one scale per row of A (per token)
   const void* b_scale;         // fp32 [N] or NULL: one scale per row of B (per output channel)

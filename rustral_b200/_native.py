@@ -36,6 +36,7 @@ class RbGemmArgs(C.Structure):
         ("expert_offsets", c_void_p), ("b_expert_rows", c_int), ("d_expert_stride", c_ll),
         ("peer_mode", c_int), ("peer_world", c_int), ("peer_rank", c_int), ("rows_per_rank", c_int),
         ("peer_epoch", C.c_uint), ("ready_flags", c_void_p), ("peer_ptrs", c_void_p * 8),
+        ("tile_arrived", c_void_p), ("tile_expected", c_void_p),
         ("ab_fp8", c_int), ("a_scale", c_void_p), ("b_scale", c_void_p),
     ]
 

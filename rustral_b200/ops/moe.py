@@ -163,9 +163,11 @@ def _segments(pl: MoEPlan):
 
 
 def grouped_gemm(xp: torch.Tensor, W: torch.Tensor, pl: MoEPlan, *, b_mn: bool = False, act: str = "none", aux_out=None,
-                 aux_in=None, out: torch.Tensor | None = None) -> torch.Tensor:
+                 aux_in=None, out: torch.Tensor | None = None, arrived=None) -> torch.Tensor:
     """Per-expert matmul over the permuted buffer.  b_mn False: W [E, N, K], y = xp @ W[e]^T.  b_mn True: W [E, K, N]
-    (the dgrad form: y = xp @ W[e])."""
+    (the dgrad form: y = xp @ W[e]).  `arrived` = (counters, expected): int32 device tensors with one entry per
+    128-row tile of `xp`; the kernel starts on a tile once its counter has reached the expected number of rows (rows
+    that other ranks are still storing into `xp`; see parallel/expert_parallel.py)."""
     E = pl.num_experts
     rows = xp.shape[0]
     Nn = W.shape[2] if b_mn else W.shape[1]
@@ -193,6 +195,8 @@ def grouped_gemm(xp: torch.Tensor, W: torch.Tensor, pl: MoEPlan, *, b_mn: bool =
     g.group_mode, g.num_experts = 1, E
     g.tile_expert, g.num_m_tiles = pl.tile_expert.data_ptr(), pl.num_tiles.data_ptr()
     g.b_expert_rows = W.shape[1]
+    if arrived is not None:
+        g.tile_arrived, g.tile_expected = arrived[0].data_ptr(), arrived[1].data_ptr()
     N.check(N.kernels().rb_gemm_bf16(g, N.stream_ptr()), "rb_gemm_bf16[grouped]")
     return y
 

@@ -9,7 +9,11 @@ Experts are split over the ranks of a group (`E / W` consecutive experts per ran
                    receive buffer (expert segments padded to 128 rows, sources in rank order inside a segment) and the
                    tile -> expert table of its own grouped GEMM
   dispatch         `rb_ep_push_rows`: token rows are stored straight into the owner's receive buffer (peer stores);
-                   that buffer IS the A operand of the grouped tcgen05 GEMM, there is no intermediate permuted copy
+                   that buffer IS the A operand of the grouped tcgen05 GEMM, there is no intermediate permuted copy.
+                   Every stored row adds one to the counter of its 128-row tile on the owner, and the owner's GEMM waits
+                   (bounded) per tile until the tile's counter reaches the number of rows the plan expects there, so
+                   it works on the tiles that are complete while other ranks are still storing the rest: there is no
+                   barrier between dispatch and the first expert GEMM (`RUSTRAL_EP_GRANULAR=0` restores it)
   experts          grouped GEMM -> SwiGLU / GELU -> grouped GEMM on the local experts
   combine          `rb_ep_pull_combine`: every rank pulls its tokens' expert outputs from the owners' output buffers
                    (peer loads) and applies the routing weights in choice order (deterministic)
@@ -32,7 +36,7 @@ from ..ops.matmul import gemm
 from .symm import SignalPad, SymmetricBuffer
 
 P, I = N.c_void_p, N.c_int
-N.optional_sig("rb_ep_push_rows", [P, I, I, I, P, P, P, P, P])
+N.optional_sig("rb_ep_push_rows", [P, I, I, I, P, P, P, P, P, P])
 N.optional_sig("rb_ep_pull_combine", [P, I, I, I, P, P, P, P, P, P])
 N.optional_sig("rb_ep_pull_dot", [P, P, I, I, I, P, P, P, P])
 N.optional_sig("rb_ep_zero_padding", [P, P, P, I, I, P])
@@ -44,6 +48,7 @@ class EPPlan:
     dest_row: torch.Tensor        # int32 [T * k]
     counts_global: torch.Tensor   # int32 [E]: tokens per expert over all ranks (for the load-balancing loss)
     recv: M.MoEPlan               # grouped-GEMM plan of this rank's receive buffer (local experts)
+    tile_rows: torch.Tensor | None = None  # int32 [cap / 128]: rows every 128-row tile of the receive buffer is going to get
     tokens: int
     k: int
     dropped: torch.Tensor | None = None   # number of this rank's (token, choice) pairs beyond the capacity (device scalar)
@@ -72,6 +77,9 @@ class FusedEP:
         self.pad = SignalPad(group, self.device)
         # x in / y out (forward), dy in / dx out (backward); all peer-visible
         self.bufs = {name: SymmetricBuffer(nbytes, group, self.device) for name in ("x", "y", "dy", "dx")}
+        # rows arrived per 128-row tile of the two buffers that peers push into
+        self.granular = __import__("os").environ.get("RUSTRAL_EP_GRANULAR", "1") != "0"
+        self.counts = {name: SymmetricBuffer(4 * (self.cap // 128), group, self.device) for name in ("x", "dy")}
         self.epoch = 0
 
     def view(self, name: str) -> torch.Tensor:
@@ -113,21 +121,35 @@ class FusedEP:
         tile_expert = torch.where(tiles < recv_off[-1], te, torch.full_like(te, -1)).to(torch.int32)
         num_tiles = (recv_off[-1:] // 128).to(torch.int32)
         recv = M.MoEPlan(my_counts, recv_off.to(torch.int32), None, None, tile_expert, num_tiles, self.cap, El, k)
-        return EPPlan(dest_rank, dest_row, seg.to(torch.int32), recv, T, k, dropped)
+        # rows each tile receives: the part of its expert's segment [start, start + count) that falls into the tile
+        seg_end = recv_off[:-1] + my_counts.long()
+        tile_rows = (seg_end[te.clamp(max=El - 1)] - tiles).clamp(min=0, max=128)
+        tile_rows = torch.where(tiles < recv_off[-1], tile_rows, torch.zeros_like(tile_rows)).to(torch.int32)
+        return EPPlan(dest_rank, dest_row, seg.to(torch.int32), recv, T, k, dropped, tile_rows)
 
     # ---------------------------------------------------------------------------------------------- transport
-    def push(self, src: torch.Tensor, pl: EPPlan, to: str, scale=None) -> torch.Tensor:
-        """Rows of `src` [T, d] into the owners' buffer `to`; returns this rank's (now filled) buffer."""
+    def push(self, src: torch.Tensor, pl: EPPlan, to: str, scale=None):
+        """Rows of `src` [T, d] into the owners' buffer `to`.  Returns (this rank's buffer, arrived): with tile-granular
+        dispatch `arrived` = (counters, expected rows) for the first grouped GEMM that reads the buffer, which waits per
+        tile, and the buffer is complete only once that GEMM has run; otherwise `arrived` is None and the buffer is
+        complete on return."""
+        cnt = self.counts[to]
+        counters = cnt.view(torch.int32, self.cap // 128)
+        if self.granular:
+            counters.zero_()                          # before the barrier: nobody adds to them until it has passed
         self.sync()                                   # the owners are done with the previous contents
         buf = self.bufs[to]
         N.check(N.kernels().rb_ep_push_rows(src.contiguous().data_ptr(), pl.tokens, pl.k, self.d, pl.dest_rank.data_ptr(),
-                                            pl.dest_row.data_ptr(), N.ptr(scale), buf.ptrs_dev.data_ptr(), N.stream_ptr()),
+                                            pl.dest_row.data_ptr(), N.ptr(scale), buf.ptrs_dev.data_ptr(),
+                                            cnt.ptrs_dev.data_ptr() if self.granular else None, N.stream_ptr()),
                 "rb_ep_push_rows")
-        self.sync()                                   # every rank's rows have landed
+        if not self.granular:
+            self.sync()                               # every rank's rows have landed
         mine = self.view(to)
+        # the padding rows of every expert segment are this rank's to clear (no peer writes them)
         N.check(N.kernels().rb_ep_zero_padding(mine.data_ptr(), pl.recv.offsets.data_ptr(), pl.recv.counts.data_ptr(),
                                                self.El, self.d, N.stream_ptr()), "rb_ep_zero_padding")
-        return mine
+        return mine, ((counters, pl.tile_rows) if self.granular else None)
 
     def pull(self, pl: EPPlan, frm: str, w=None, residual=None, synced: bool = False) -> torch.Tensor:
         if not synced:
@@ -146,7 +168,7 @@ class FusedEP:
         return dw
 
     def close(self) -> None:
-        for b in self.bufs.values():
+        for b in list(self.bufs.values()) + list(self.counts.values()):
             b.close()
         self.pad.close()
 
@@ -161,13 +183,13 @@ class _EPMoEMlpFn(torch.autograd.Function):
         logits = gemm(x, router_w, out_dtype=torch.float32)
         idx, w, probs = M.route(logits, k, renorm)
         pl = ep.plan(idx)
-        xp = ep.push(x, pl, "x")
+        xp, arrived = ep.push(x, pl, "x")
         if kind == "swiglu":
-            pre = M.grouped_gemm(xp, w1, pl.recv)
+            pre = M.grouped_gemm(xp, w1, pl.recv, arrived=arrived)
             h = rotary.swiglu_forward(pre)
         else:
             pre = torch.empty((ep.cap, w1.shape[1]), dtype=x.dtype, device=x.device)
-            h = M.grouped_gemm(xp, w1, pl.recv, act="gelu", aux_out=pre)
+            h = M.grouped_gemm(xp, w1, pl.recv, act="gelu", aux_out=pre, arrived=arrived)
         M.grouped_gemm(h, w2, pl.recv, out=ep.view("y"))
         y = ep.pull(pl, "y", w=w)
         f = pl.counts_global.float() / float(max(1, T * k * ep.world))
@@ -185,14 +207,14 @@ class _EPMoEMlpFn(torch.autograd.Function):
         # the owners recompute their expert outputs for the routing-weight gradient
         ep.sync()
         M.grouped_gemm(h, w2, pl.recv, out=ep.view("y"))
-        dyp = ep.push(dy, pl, "dy", scale=w.reshape(-1).contiguous())          # w_j * dy at every slot (syncs inside)
-        dw = ep.pull_dot(dy, pl, "y")                                            # [T, k]
+        dyp, arrived = ep.push(dy, pl, "dy", scale=w.reshape(-1).contiguous())  # w_j * dy at every slot
+        dh = M.grouped_gemm(dyp, w2, pl.recv, b_mn=True, arrived=arrived)        # waits per tile; dyp is complete after it
         dw2 = M.grouped_wgrad(dyp, h, pl.recv)
-        dh = M.grouped_gemm(dyp, w2, pl.recv, b_mn=True)
         dpre = rotary.swiglu_backward(dh, pre) if kind == "swiglu" else unary_bwd("gelu", pre, dh)
         dw1 = M.grouped_wgrad(dpre, xp, pl.recv)
         M.grouped_gemm(dpre, w1, pl.recv, b_mn=True, out=ep.view("dx"))
-        dx_experts = ep.pull(pl, "dx")
+        dx_experts = ep.pull(pl, "dx")                                           # barrier inside: the owners' y and dx are complete
+        dw = ep.pull_dot(dy, pl, "y")                                            # [T, k]
         aux_scale = float(daux) if daux is not None else 0.0
         T = x.shape[0]
         # load-balancing term: f uses the global counts, scaled to the local token count convention of route_backward
