@@ -48,10 +48,10 @@ class EPPlan:
     dest_row: torch.Tensor        # int32 [T * k]
     counts_global: torch.Tensor   # int32 [E]: tokens per expert over all ranks (for the load-balancing loss)
     recv: M.MoEPlan               # grouped-GEMM plan of this rank's receive buffer (local experts)
-    tile_rows: torch.Tensor | None = None  # int32 [cap / 128]: rows every 128-row tile of the receive buffer is going to get
     tokens: int
     k: int
     dropped: torch.Tensor | None = None   # number of this rank's (token, choice) pairs beyond the capacity (device scalar)
+    tile_rows: torch.Tensor | None = None  # int32 [cap / 128]: rows every 128-row tile of the receive buffer is going to get
 
 
 class FusedEP:
