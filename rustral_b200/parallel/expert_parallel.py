@@ -107,7 +107,7 @@ class FusedEP:
         e = idx.reshape(-1).long()
         pos = local.slot_pos.long() - local.offsets.long()[e]          # position inside this rank's group for expert e
         row = base[e] + pos
-        fits = row < self.cap                                         # the same verdict on every rank
+        fits = row < self.cap                                         # the same answer on every rank
         dest_row = torch.where(fits, row, torch.full_like(row, -1)).to(torch.int32)
         dest_rank = (e // El).to(torch.int32)
         dropped = (~fits).sum()

@@ -114,6 +114,22 @@ class ProcessGroup:
             raise CommunicationError(str(e)) from e
         return t
 
+    def all_reduce_sum_async(self, t: torch.Tensor, name: str = ""):
+        """Starts an in-place sum; returns a handle with `wait()`.  Over torch.distributed the collective runs on the
+        backend's own stream / thread while the caller goes on (the handle's `wait` orders the current stream behind it);
+        the threaded and single-process groups complete at once."""
+        if self.backend in ("single", "threaded"):
+            self.all_reduce_sum(t, name)
+
+            class _Done:
+                def wait(self_inner):
+                    return True
+            return _Done()
+        try:
+            return dist.all_reduce(t, group=self.group, async_op=True)
+        except RuntimeError as e:
+            raise CommunicationError(str(e)) from e
+
     def all_reduce_mean(self, t: torch.Tensor, name: str = "") -> torch.Tensor:
         self.all_reduce_sum(t, name)
         t.div_(self.world_size)

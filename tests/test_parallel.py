@@ -498,3 +498,33 @@ def test_asynchronous_distributed_checkpoint_is_published_only_when_finished(tmp
     for r, (before, after, step, flat, opt) in enumerate(out):
         assert before == [] and after == [5] and step == 500 and opt == {"t": 5}
         assert flat == [100.0 * r + i for i in range(6)]
+
+
+@pytest.mark.parametrize("wire", [torch.float32, torch.bfloat16])
+def test_overlapped_gradient_reducer_launches_buckets_during_backward(wire):
+    """Buckets are reduced as soon as the backward pass has produced their gradients, last layer first; the result is the
+    synchronous bucketed all-reduce's (exactly with fp32 on the wire, within bf16 rounding with bf16)."""
+    from rustral_b200.parallel.data_parallel import DataParallelTrainer, OverlappedGradientReducer
+    torch.manual_seed(0)
+    X, Y = torch.randn(8, 6), torch.randn(8, 3)
+
+    def fn(pg):
+        out = {}
+        for overlap in (False, True):
+            m = _model()
+            tr = DataParallelTrainer(pg, Adam.adamw(1e-2, 0.0), bucket_bytes=64, overlap=overlap, wire_dtype=wire)
+            for _ in range(3):
+                tr.step(m.parameters(), list(range(8)), lambda idx, ctx: ((m(X[idx]) - Y[idx]) ** 2).mean())
+            out[overlap] = _flat(m)
+            if overlap:
+                red = tr._reducer
+                out["order"] = list(red.launch_order)
+                out["nbuckets"] = len(red.buckets)
+        return out
+    res = run_ranks(2, fn)
+    for r in res:
+        tol = 0 if wire is torch.float32 else 2e-3
+        assert (r[True] - r[False]).abs().max() <= tol
+        # one bucket per parameter here: both buckets of the last layer start before either bucket of the first layer
+        assert r["nbuckets"] == 4 and sorted(r["order"][:2]) == [0, 1] and sorted(r["order"][2:]) == [2, 3]
+    assert torch.equal(res[0][True], res[1][True])
