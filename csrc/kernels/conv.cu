@@ -216,3 +216,99 @@ RB_API int rb_nchw_to_nhwc(const void* src, void* dst, int N, int L, int O, int 
       reinterpret_cast<const __nv_bfloat16*>(src), reinterpret_cast<__nv_bfloat16*>(dst), L, O, 0, Op, 0);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Max pooling (crates/nn/src/conv.rs:228-340 pools on the host).  Forward writes the window maximum and the flat index
+// (h * W + w) of the element that produced it (first maximum in row-major window order); backward is a gather per input
+// element over the windows that contain it, so overlapping windows (stride < kernel) need no atomics.
+// ------------------------------------------------------------------------------------------------------------------
+namespace rb {
+
+template <typename T> __device__ __forceinline__ float pool_ld(const T* p);
+template <> __device__ __forceinline__ float pool_ld<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float pool_ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void pool_st(T* p, float v);
+template <> __device__ __forceinline__ void pool_st<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void pool_st<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+max_pool2d_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int* __restrict__ idx, long long planes, int H, int W, int k,
+                      int stride, int Ho, int Wo) {
+  const long long total = planes * Ho * Wo;
+  const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int wo = static_cast<int>(i % Wo), ho = static_cast<int>((i / Wo) % Ho);
+    const long long pl = i / (static_cast<long long>(Wo) * Ho);
+    const T* xp = x + pl * H * W;
+    float best = -INFINITY;
+    int arg = (ho * stride) * W + wo * stride;
+    for (int a = 0; a < k; ++a) {
+      const int h = ho * stride + a;
+      if (h >= H) break;
+      for (int b = 0; b < k; ++b) {
+        const int w = wo * stride + b;
+        if (w >= W) break;
+        const float v = pool_ld(xp + h * W + w);
+        if (v > best || (v != v && best == best)) { best = v; arg = h * W + w; }      // NaN wins, like the reference math
+      }
+    }
+    pool_st(y + i, best);
+    idx[i] = arg;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+max_pool2d_bwd_kernel(const T* __restrict__ dy, const int* __restrict__ idx, T* __restrict__ dx, long long planes, int H, int W,
+                      int k, int stride, int Ho, int Wo) {
+  const long long total = planes * H * W;
+  const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int w = static_cast<int>(i % W), h = static_cast<int>((i / W) % H);
+    const long long pl = i / (static_cast<long long>(W) * H);
+    const int me = h * W + w;
+    // windows (ho, wo) with ho * stride <= h < ho * stride + k
+    const int ho_hi = min(Ho - 1, h / stride), wo_hi = min(Wo - 1, w / stride);
+    const int ho_lo = max(0, (h - k + stride) / stride), wo_lo = max(0, (w - k + stride) / stride);
+    float acc = 0.f;
+    for (int ho = ho_lo; ho <= ho_hi; ++ho)
+      for (int wo = wo_lo; wo <= wo_hi; ++wo) {
+        const long long o = (pl * Ho + ho) * Wo + wo;
+        if (idx[o] == me) acc += pool_ld(dy + o);
+      }
+    pool_st(dx + i, acc);
+  }
+}
+
+}  // namespace rb
+
+RB_API int rb_max_pool2d_fwd(const void* x, void* y, int* idx, long long planes, int H, int W, int k, int stride, int is_bf16,
+                             void* stream) {
+  if (!x || !y || !idx || planes <= 0 || H <= 0 || W <= 0 || k <= 0 || stride <= 0 || k > H || k > W) return -1;
+  const int Ho = (H - k) / stride + 1, Wo = (W - k) / stride + 1;
+  const long long total = planes * Ho * Wo;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (is_bf16)
+    rb::max_pool2d_fwd_kernel<__nv_bfloat16><<<conv_grid(total), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x),
+                                                                              reinterpret_cast<__nv_bfloat16*>(y), idx, planes, H, W, k, stride, Ho, Wo);
+  else
+    rb::max_pool2d_fwd_kernel<float><<<conv_grid(total), 256, 0, s>>>(reinterpret_cast<const float*>(x), reinterpret_cast<float*>(y), idx,
+                                                                      planes, H, W, k, stride, Ho, Wo);
+  return static_cast<int>(cudaGetLastError());
+}
+
+RB_API int rb_max_pool2d_bwd(const void* dy, const int* idx, void* dx, long long planes, int H, int W, int k, int stride, int is_bf16,
+                             void* stream) {
+  if (!dy || !dx || !idx || planes <= 0 || H <= 0 || W <= 0 || k <= 0 || stride <= 0 || k > H || k > W) return -1;
+  const int Ho = (H - k) / stride + 1, Wo = (W - k) / stride + 1;
+  const long long total = planes * H * W;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (is_bf16)
+    rb::max_pool2d_bwd_kernel<__nv_bfloat16><<<conv_grid(total), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(dy), idx,
+                                                                              reinterpret_cast<__nv_bfloat16*>(dx), planes, H, W, k, stride, Ho, Wo);
+  else
+    rb::max_pool2d_bwd_kernel<float><<<conv_grid(total), 256, 0, s>>>(reinterpret_cast<const float*>(dy), idx, reinterpret_cast<float*>(dx),
+                                                                      planes, H, W, k, stride, Ho, Wo);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -19,6 +19,11 @@ int rb_col2im(const void* dcols, void* dx, int N, int C, int H, int W, int kh, i
 //   with zeros in columns [O, Op).
 int rb_nhwc_to_nchw(const void* src, long long ld_src, void* dst, int N, int L, int O, void* stream);
 int rb_nchw_to_nhwc(const void* src, void* dst, int N, int L, int O, int Op, void* stream);
+// Max pooling without padding over `planes` = N * C images of H x W (dense): y [planes, Ho, Wo], idx (int32) the flat
+// position h * W + w of each window's maximum; Ho = (H - k) / stride + 1.  Backward: dx[p] = sum of dy over the windows
+// whose maximum is p (a gather, no atomics).  bf16 or fp32 elements.
+int rb_max_pool2d_fwd(const void* x, void* y, int* idx, long long planes, int H, int W, int k, int stride, int is_bf16, void* stream);
+int rb_max_pool2d_bwd(const void* dy, const int* idx, void* dx, long long planes, int H, int W, int k, int stride, int is_bf16, void* stream);
 #ifdef __cplusplus
 }
 #endif

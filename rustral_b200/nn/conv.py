@@ -156,9 +156,47 @@ class Conv2d(Module, Trainable, Saveable):
             yield "bias", self.bias
 
 
+N_.optional_sig("rb_max_pool2d_fwd", [_P, _P, _P, N_.c_ll, _I, _I, _I, _I, _I, _P])
+N_.optional_sig("rb_max_pool2d_bwd", [_P, _P, _P, N_.c_ll, _I, _I, _I, _I, _I, _P])
+
+
+class _MaxPool2dFn(torch.autograd.Function):
+    """Max pooling of CUDA tensors (bf16 or fp32, NCHW) on the kernels of csrc/kernels/conv.cu: the forward keeps the
+    position of every window's maximum, the backward gathers per input element (overlapping windows need no atomics)."""
+
+    @staticmethod
+    def forward(ctx, x, kernel, stride):
+        x = x.contiguous()
+        N, C, H, W = x.shape
+        ho, wo = (H - kernel) // stride + 1, (W - kernel) // stride + 1
+        y = torch.empty((N, C, ho, wo), dtype=x.dtype, device=x.device)
+        idx = torch.empty((N, C, ho, wo), dtype=torch.int32, device=x.device)
+        N_.check(N_.kernels().rb_max_pool2d_fwd(x.data_ptr(), y.data_ptr(), idx.data_ptr(), N * C, H, W, kernel, stride,
+                                                int(x.dtype == torch.bfloat16), N_.stream_ptr()), "rb_max_pool2d_fwd")
+        ctx.save_for_backward(idx)
+        ctx.geom = (N, C, H, W, kernel, stride)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (idx,) = ctx.saved_tensors
+        N, C, H, W, kernel, stride = ctx.geom
+        dy = dy.contiguous()
+        dx = torch.empty((N, C, H, W), dtype=dy.dtype, device=dy.device)
+        N_.check(N_.kernels().rb_max_pool2d_bwd(dy.data_ptr(), idx.data_ptr(), dx.data_ptr(), N * C, H, W, kernel, stride,
+                                                int(dy.dtype == torch.bfloat16), N_.stream_ptr()), "rb_max_pool2d_bwd")
+        return dx, None, None
+
+
 def max_pool2d(x: torch.Tensor, kernel: int = 2, stride: int | None = None) -> torch.Tensor:
-    return F.max_pool2d(x, kernel, stride or kernel)
+    stride = stride or kernel
+    if x.is_cuda and x.dim() == 4 and x.dtype in (torch.bfloat16, torch.float32) and kernel <= min(x.shape[2], x.shape[3]):
+        return _MaxPool2dFn.apply(x, kernel, stride)
+    return F.max_pool2d(x, kernel, stride)
 
 
 def global_max_pool2d(x: torch.Tensor) -> torch.Tensor:
+    """[N, C, H, W] -> [N, C]: one window covering the whole image."""
+    if x.is_cuda and x.dim() == 4 and x.shape[2] == x.shape[3] and x.dtype in (torch.bfloat16, torch.float32):
+        return max_pool2d(x, x.shape[2]).reshape(x.shape[0], x.shape[1])
     return x.amax((2, 3))

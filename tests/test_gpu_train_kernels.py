@@ -116,3 +116,22 @@ def test_expert_choice_router_trains_on_native_kernels(cuda_status):
     assert_close(dev.router.tensor.grad, ref.router.tensor.grad, "attention_grad", "drouter")
     for e in range(E):
         assert_close(wd[e].grad, wr[e].grad, "attention_grad", f"dW{e}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,W,k,stride", [(8, 8, 2, 2), (9, 11, 3, 2), (7, 7, 3, 1), (6, 6, 6, 6)])
+def test_max_pool2d_forward_and_backward(H, W, k, stride, dtype, cuda_status):
+    from rustral_b200.nn.conv import global_max_pool2d, max_pool2d
+    g = torch.Generator().manual_seed(H * 10 + k)
+    x = torch.randn(3, 4, H, W, generator=g).to(dtype)
+    xr = x.float().clone().requires_grad_()            # a copy: for fp32 `x.float()` is x itself
+    yr = torch.nn.functional.max_pool2d(xr, k, stride)
+    dy = torch.randn(yr.shape, generator=g).to(dtype)
+    yr.backward(dy.float())
+    xd = x.detach().cuda().requires_grad_()
+    yd = max_pool2d(xd, k, stride)
+    yd.backward(dy.cuda())
+    assert torch.equal(yd.float().cpu(), yr.detach().to(dtype).float())
+    assert torch.allclose(xd.grad.float().cpu(), xr.grad, atol=2e-2 if dtype is torch.bfloat16 else 1e-6)
+    if H == W:
+        assert torch.equal(global_max_pool2d(x.cuda()).float().cpu(), x.float().amax((2, 3)))
