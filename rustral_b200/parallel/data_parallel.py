@@ -83,8 +83,9 @@ class OverlappedGradientReducer:
     def finish(self) -> None:
         """Call after backward(): launches what is still pending (parameters that got no gradient leave their bucket
         incomplete), waits for every bucket, writes the averaged gradients back and re-arms the hooks' counters."""
-        for bi, left in enumerate(self._left):
-            if left > 0 and left < len(self.buckets[bi]) or (left > 0 and any(t.grad is not None for t in self.buckets[bi])):
+        launched = {bi for bi, *_ in self._inflight}
+        for bi in range(len(self.buckets)):
+            if bi not in launched and any(t.grad is not None for t in self.buckets[bi]):
                 self._launch(bi)
         for bi, bucket, flat, work in self._inflight:
             work.wait()
