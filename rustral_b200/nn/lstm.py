@@ -22,6 +22,9 @@ N_.optional_sig("rb_gru_gates_fwd", [_P, _LL, _P, _LL, _P, _P, _I, _I, _P])
 N_.optional_sig("rb_gru_gates_bwd", [_P, _LL, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _P])
 
 
+_SEQ_GRAPHS = __import__("os").environ.get("RUSTRAL_RNN_GRAPHS", "1") != "0"
+
+
 def _native_cell_ok(t: torch.Tensor, hidden: int) -> bool:
     return t.is_cuda and t.dtype == torch.bfloat16 and hidden % 2 == 0
 
@@ -152,19 +155,50 @@ class LstmCell(RnnCell):
         if not xs.is_cuda or xs.dtype != torch.bfloat16 or needs_grad or H % 8:
             return super().forward_sequence(xs, ctx, state)
         T, B, I = xs.shape
-        lib = N_.kernels()
         with torch.no_grad():
             h, c = state if state is not None else self.initial_state(B, ctx, xs)
-            h, c = h.contiguous(), c.contiguous().clone()
-            wx, wh, bias = self.wx.tensor.detach(), self.wh.tensor.detach(), self.b.tensor.detach()
-            xproj = ops.linear(xs.reshape(T * B, I).contiguous(), wx, bias).view(T, B, 4 * H)
-            outs = torch.empty((T, B, H), dtype=xs.dtype, device=xs.device)
-            for t in range(T):
-                gates = ops.linear(h, wh, None, "none", xproj[t])
-                N_.check(lib.rb_lstm_gates_fwd(gates.data_ptr(), gates.stride(0), c.data_ptr(), outs[t].data_ptr(), c.data_ptr(),
-                                               B, H, N_.stream_ptr()), "rb_lstm_gates_fwd")
-                h = outs[t]
+            if T >= 4 and _SEQ_GRAPHS and not torch.cuda.is_current_stream_capturing():
+                return self._graphed_sequence(xs, h, c)
+            return self._sequence_body(xs, h.contiguous(), c.contiguous().clone())
+
+    def _sequence_body(self, xs, h, c):
+        """One input-projection GEMM for all steps, then per step one GEMM (with that projection as its residual) and the
+        fused gate kernel; `c` is updated in place."""
+        T, B, I = xs.shape
+        H = self.hidden_size
+        lib = N_.kernels()
+        wx, wh, bias = self.wx.tensor.detach(), self.wh.tensor.detach(), self.b.tensor.detach()
+        xproj = ops.linear(xs.reshape(T * B, I).contiguous(), wx, bias).view(T, B, 4 * H)
+        outs = torch.empty((T, B, H), dtype=xs.dtype, device=xs.device)
+        for t in range(T):
+            gates = ops.linear(h, wh, None, "none", xproj[t])
+            N_.check(lib.rb_lstm_gates_fwd(gates.data_ptr(), gates.stride(0), c.data_ptr(), outs[t].data_ptr(), c.data_ptr(),
+                                           B, H, N_.stream_ptr()), "rb_lstm_gates_fwd")
+            h = outs[t]
         return outs, (h, c)
+
+    def _graphed_sequence(self, xs, h0, c0):
+        """A sequence is 2 T + 1 small launches, each of which costs more on the host than on the device: the second call
+        with the same shapes and weights captures them into a CUDA graph, later calls copy the inputs into the graph's
+        static tensors and replay it (`RUSTRAL_RNN_GRAPHS=0` turns this off)."""
+        key = (tuple(xs.shape), xs.device.index, self.wx.tensor.data_ptr(), self.wh.tensor.data_ptr(), self.b.tensor.data_ptr())
+        graphs = self.__dict__.setdefault("_seq_graphs", {})
+        g = graphs.get(key)
+        if g is None:
+            graphs[key] = {"graph": None}                     # first use: run eagerly (kernels configure themselves lazily)
+            return self._sequence_body(xs, h0.contiguous(), c0.contiguous().clone())
+        if g["graph"] is None:
+            g["xs"], g["h0"], g["c0"] = torch.empty_like(xs), torch.empty_like(h0), torch.empty_like(c0)
+            g["xs"].copy_(xs); g["h0"].copy_(h0); g["c0"].copy_(c0)
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                c_work = g["c0"].clone()
+                g["outs"], (g["h"], g["c"]) = self._sequence_body(g["xs"], g["h0"], c_work)
+            g["graph"] = graph
+        g["xs"].copy_(xs); g["h0"].copy_(h0); g["c0"].copy_(c0)
+        g["graph"].replay()
+        return g["outs"].clone(), (g["h"].clone(), g["c"].clone())
 
 
 class GruCell(RnnCell):

@@ -515,3 +515,12 @@ def test_lstm_inference_sequence_matches_fp32_recurrence(T, B, I, H, cuda_status
     assert torch.equal(h, outs[-1])
     slow, _ = super(LstmCell, cell).forward_sequence(xs, ForwardCtx.inference(be))
     _close(outs, slow, tol=3e-2, what="fast vs generic lstm path")
+    # second call captures the sequence into a CUDA graph, the third and fourth replay it (new inputs, new initial state)
+    outs2, (h2, c2) = cell.forward_sequence(xs, ForwardCtx.inference(be))
+    outs3, (h3, c3) = cell.forward_sequence(xs, ForwardCtx.inference(be))
+    assert torch.equal(outs2, outs) and torch.equal(outs3, outs) and torch.equal(c3, c) and torch.equal(h3, h)
+    xs_b = _bf((T, B, I), 16).cuda()
+    st = (_bf((B, H), 17, 0.3).cuda(), _bf((B, H), 18, 0.3).cuda())
+    got, (hg, cg) = cell.forward_sequence(xs_b, ForwardCtx.inference(be), st)
+    want, (hw, cw) = cell._sequence_body(xs_b, st[0].contiguous(), st[1].contiguous().clone())
+    assert torch.equal(got, want) and torch.equal(cg, cw) and torch.equal(st[1], _bf((B, H), 18, 0.3).cuda())
