@@ -336,3 +336,19 @@ def test_a_long_prompt_does_not_stall_running_requests_for_more_than_a_chunk():
         out = eng.step()
         produced.append((a in out, b in out))
     assert produced == [(True, False)] * 4 + [(True, True)]
+
+
+def test_serving_benchmark_rate_sweep_stops_at_saturation(capsys):
+    """The sweep reports one row per rate, the capacity, and stops after the first rate whose p99 TTFT exceeds the limit."""
+    import json
+    from rustral_b200.serve import bench_serving
+    bench_serving.main(["--model", "gpt2-test", "--requests", "5", "--rates", "400", "100", "200", "--prompt", "4", "10",
+                        "--output", "2", "3", "--blocks", "64", "--ttft-limit-ms", "1e9", "--prefill-chunk", "6"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert [r["rate_per_s"] for r in out["sweep"]] == [100.0, 200.0, 400.0] and out["saturated_at_rate"] is None
+    assert all(r["completed"] == 5 for r in out["sweep"]) and out["prefill_chunk"] == 6
+    assert out["capacity_tokens_per_s"] == max(r["output_tokens_per_s"] for r in out["sweep"])
+    bench_serving.main(["--model", "gpt2-test", "--requests", "4", "--rates", "50", "100", "--prompt", "4", "10", "--output", "2", "3",
+                        "--blocks", "64", "--ttft-limit-ms", "0"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert len(out["sweep"]) == 1 and out["saturated_at_rate"] == 50.0
