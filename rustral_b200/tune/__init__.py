@@ -484,6 +484,9 @@ class _StrategySearch:
     def best(self):
         return self.handle.best()
 
+    def num_evals(self) -> int:
+        return self.handle.num_evals()
+
 
 class GridSearch(_StrategySearch):
     strategy = Strategy.GRID
