@@ -5,6 +5,8 @@
     python -m rustral_b200.bench.reports index --runs-dir runs [--check]
     python -m rustral_b200.bench.reports bmf combined.json bmf.json
     python -m rustral_b200.bench.reports emnlp --harness combined.json --runs runs/v0.1.0 --out emnlp_report.md
+    python -m rustral_b200.bench.reports regress --baseline old.json --current new.json --fail-on-regression
+    python -m rustral_b200.bench.reports site --runs-dir runs --out site/
 
 What each sub-command does, and the script of the reference whose job it takes over:
 
@@ -20,7 +22,15 @@ What each sub-command does, and the script of the reference whose job it takes o
 * bmf       converts a combined document into Bencher Metric Format: `<suite>/<backend>/<device>/<name>` ->
             latency in ns with lower / upper values (scripts/bench/to_bencher_bmf.py);
 * emnlp     the paper-style experiment report: environment, micro-benchmark tables per suite, NLP tables
-            (scripts/bench/build_emnlp_report.py).
+            (scripts/bench/build_emnlp_report.py);
+* regress   a regression gate between two harness documents: workloads are matched by (suite, name, params), the ratio
+            of means is reported, and with --fail-on-regression the exit status is 1 when a workload is slower than
+            --max-slowdown times the baseline AND the two 95 % confidence intervals do not overlap (so noise alone does
+            not fail a build); --require-matching fails on workloads that disappeared
+            (scripts/bench/compare_harness.py);
+* site      a static HTML dashboard: `index.html` listing every snapshot under --runs-dir with its manifest, and one
+            page per snapshot with a sortable table per suite; no scripts are fetched and nothing is loaded at view
+            time (scripts/bench/render_site.py).
 """
 from __future__ import annotations
 
@@ -315,6 +325,139 @@ def cmd_bmf(a) -> int:
     return 0
 
 
+# ------------------------------------------------------------------------------------------------- regression gate
+def _sample_index(doc: dict) -> dict:
+    """(suite, name, sorted params) -> sample, for per-suite and combined documents alike."""
+    out = {}
+    for s in doc.get("samples") or []:
+        params = s.get("params") if isinstance(s.get("params"), dict) else {}
+        out[(str(s.get("suite", doc.get("suite", "?"))), str(s.get("name", "")), tuple(sorted((str(k), str(v)) for k, v in params.items())))] = s
+    return out
+
+
+def _interval(s: dict) -> tuple:
+    ci = s.get("ci95_ms")
+    if ci is None and len(s.get("runs_ms") or []) >= 2:
+        ci = ci95_mean_ms(s["runs_ms"])
+    m = float(s["mean_ms"])
+    return (m - ci, m + ci) if ci else (m, m)
+
+
+def regress(base: dict, cur: dict, max_slowdown: float = 1.15) -> dict:
+    """Rows of matched workloads with their ratio; a row is a regression when it is slower than `max_slowdown` times the
+    baseline and the confidence intervals of the two means are disjoint."""
+    bi, ci = _sample_index(base), _sample_index(cur)
+    rows, skipped = [], []
+    for k in sorted(bi):
+        if k not in ci:
+            continue
+        bm, cm = bi[k].get("mean_ms"), ci[k].get("mean_ms")
+        if not isinstance(bm, (int, float)) or not isinstance(cm, (int, float)) or bm <= 0 or not math.isfinite(cm):
+            skipped.append(k)
+            continue
+        ratio = cm / bm
+        (_, b_hi), (c_lo, _) = _interval(bi[k]), _interval(ci[k])
+        rows.append({"suite": k[0], "name": k[1], "params": dict(k[2]), "baseline_ms": bm, "current_ms": cm, "ratio": ratio,
+                     "regression": ratio > max_slowdown and c_lo > b_hi})
+    return {"rows": rows, "skipped": skipped, "missing": [k for k in sorted(bi) if k not in ci],
+            "extra": [k for k in sorted(ci) if k not in bi]}
+
+
+def cmd_regress(a) -> int:
+    res = regress(json.loads(Path(a.baseline).read_text()), json.loads(Path(a.current).read_text()), a.max_slowdown)
+    bad = [r for r in res["rows"] if r["regression"]]
+    print(f"compared {len(res['rows'])} workloads ({len(res['skipped'])} without a usable mean); {len(bad)} regression(s) "
+          f"beyond {a.max_slowdown:.2f}x")
+    for r in res["rows"]:
+        label = r["name"] + ("." + ".".join(f"{k}={v}" for k, v in r["params"].items()) if r["params"] else "")
+        print(f"  {r['suite']:<12} {label:<48} {r['baseline_ms']:>10.4f} -> {r['current_ms']:>10.4f} ms   x{r['ratio']:.3f}"
+              + ("   REGRESSION" if r["regression"] else ""))
+    for title, keys in (("missing in current", res["missing"]), ("new in current", res["extra"])):
+        if keys:
+            print(f"{title}: " + ", ".join(f"{k[0]}/{k[1]}" for k in keys[:40]) + (" ..." if len(keys) > 40 else ""))
+    if a.require_matching and res["missing"]:
+        print("FAIL: workloads of the baseline are missing in the current document", file=sys.stderr)
+        return 1
+    if a.fail_on_regression and bad:
+        print(f"FAIL: {len(bad)} workload(s) regressed", file=sys.stderr)
+        return 1
+    return 0
+
+
+# ------------------------------------------------------------------------------------------------- static dashboard
+_PAGE = """<!doctype html><html><head><meta charset="utf-8"><title>{title}</title><style>
+body{{font:14px/1.45 system-ui,sans-serif;margin:2rem auto;max-width:72rem;padding:0 1rem;color:#1b1f24}}
+table{{border-collapse:collapse;margin:.5rem 0 1.5rem}}th,td{{border:1px solid #d0d7de;padding:.25rem .6rem;text-align:right}}
+th{{background:#f6f8fa;cursor:pointer}}td:first-child,th:first-child{{text-align:left}}code{{background:#f6f8fa;padding:0 .25rem}}
+</style></head><body><h1>{title}</h1>{body}<script>
+document.querySelectorAll("th").forEach(function(th){{th.onclick=function(){{var t=th.closest("table"),i=th.cellIndex,
+r=[].slice.call(t.tBodies[0].rows),d=th.dataset.d=th.dataset.d=="1"?"-1":"1";r.sort(function(a,b){{var x=a.cells[i].textContent,
+y=b.cells[i].textContent,n=parseFloat(x)-parseFloat(y);return d*(isNaN(n)?x.localeCompare(y):n)}});r.forEach(function(e){{t.tBodies[0].appendChild(e)}})}}}});
+</script></body></html>"""
+
+
+def _suite_tables(docs: list) -> str:
+    import html
+    parts = []
+    for d in docs:
+        for su in (d.get("suites") or [d.get("suite", "?")]):
+            rows = [s for s in d.get("samples") or [] if s.get("suite", d.get("suite")) == su]
+            if not rows:
+                continue
+            parts.append(f"<h2>{html.escape(str(su))}</h2><table><thead><tr><th>workload</th><th>backend</th><th>device</th>"
+                         "<th>mean ms</th><th>95 % CI</th><th>min ms</th><th>runs</th></tr></thead><tbody>")
+            for s in rows:
+                ci = s.get("ci95_ms")
+                parts.append("<tr><td>{}</td><td>{}</td><td>{}</td><td>{:.4f}</td><td>{}</td><td>{:.4f}</td><td>{}</td></tr>".format(
+                    html.escape(_key(s)), html.escape(str(s.get("backend", "?"))), html.escape(str(s.get("device", "?"))),
+                    float(s["mean_ms"]), f"{ci:.4f}" if ci else "-", float(s.get("min_ms", min(s.get("runs_ms") or [float("nan")]))),
+                    len(s.get("runs_ms") or [])))
+            parts.append("</tbody></table>")
+    return "".join(parts)
+
+
+def render_site(runs_dir: Path, out: Path) -> list:
+    """Writes index.html plus one page per `<runs-dir>/<version>/` holding harness documents; returns the written paths.
+    An empty or absent runs directory still yields a valid landing page."""
+    import html
+    out.mkdir(parents=True, exist_ok=True)
+    written, items = [], []
+    versions = sorted(p for p in runs_dir.iterdir() if p.is_dir()) if runs_dir.is_dir() else []
+    for vdir in versions:
+        docs, manifest = [], {}
+        for f in sorted(vdir.glob("*.json")):
+            try:
+                doc = json.loads(f.read_text())
+            except json.JSONDecodeError:
+                continue
+            if f.name == "manifest.json":
+                manifest = doc
+            elif isinstance(doc, dict) and isinstance(doc.get("samples"), list):
+                docs.append(doc)
+        if not docs and not manifest:
+            continue
+        meta = "".join(f"<li>{html.escape(str(k))}: <code>{html.escape(str(v))}</code></li>" for k, v in manifest.items()
+                       if not isinstance(v, (dict, list)))
+        body = (f"<p><a href='index.html'>all snapshots</a></p><ul>{meta}</ul>" + (_suite_tables(docs) or "<p>no harness documents</p>"))
+        page = out / f"{vdir.name}.html"
+        page.write_text(_PAGE.format(title=html.escape(f"Benchmarks {vdir.name}"), body=body))
+        written.append(page)
+        n = sum(len(d["samples"]) for d in docs)
+        items.append(f"<tr><td><a href='{html.escape(vdir.name)}.html'>{html.escape(vdir.name)}</a></td><td>{html.escape(str(manifest.get('date', '-')))}</td>"
+                     f"<td>{html.escape(str(manifest.get('git_sha', '-'))[:12])}</td><td>{len(docs)}</td><td>{n}</td></tr>")
+    body = ("<table><thead><tr><th>snapshot</th><th>date</th><th>git sha</th><th>suites</th><th>workloads</th></tr></thead><tbody>"
+            + "".join(items) + "</tbody></table>") if items else "<p>no snapshots yet</p>"
+    index = out / "index.html"
+    index.write_text(_PAGE.format(title="Benchmark snapshots", body=body))
+    return [index] + written
+
+
+def cmd_site(a) -> int:
+    for p in render_site(Path(a.runs_dir), Path(a.out)):
+        print(p)
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="rustral_b200.bench.reports")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -345,6 +488,17 @@ def main(argv=None) -> int:
     p.add_argument("input")
     p.add_argument("output")
     p.set_defaults(fn=cmd_bmf)
+    p = sub.add_parser("regress")
+    p.add_argument("--baseline", required=True)
+    p.add_argument("--current", required=True)
+    p.add_argument("--max-slowdown", type=float, default=1.15, help="allowed current mean / baseline mean")
+    p.add_argument("--fail-on-regression", action="store_true")
+    p.add_argument("--require-matching", action="store_true", help="fail when a baseline workload is absent from the current document")
+    p.set_defaults(fn=cmd_regress)
+    p = sub.add_parser("site")
+    p.add_argument("--runs-dir", required=True)
+    p.add_argument("--out", required=True)
+    p.set_defaults(fn=cmd_site)
     a = ap.parse_args(argv)
     return a.fn(a)
 

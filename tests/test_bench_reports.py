@@ -77,3 +77,43 @@ def test_torch_suite_mirrors_the_framework_workload_names():
     twin = {n for n, _, _, _ in R._torch_workloads("cpu", heavy=False)}
     assert twin <= ours and len(twin) >= 17
     assert R.run_suite("torch-cuda", 1, 0) is None or torch.cuda.is_available()
+
+
+def test_regression_gate_needs_both_a_slowdown_and_disjoint_intervals(tmp_path):
+    base = _doc("s", 1.0)
+    slow = _doc("s", 2.5)                                   # 2.5x slower, intervals far apart
+    res = R.regress(base, slow, 1.15)
+    assert [r["regression"] for r in res["rows"]] == [True, True] and res["rows"][0]["ratio"] == pytest.approx(2.5)
+    noisy = json.loads(samples_to_json([Sample("matmul.128x128x128", "b", "cpu", "f32", None, {"m": 128}, [0.5, 2.5, 0.9]),
+                                        Sample("other", "b", "cpu", "f32", None, {}, [1.0, 1.0])], suite="s"))
+    res = R.regress(base, noisy, 1.15)                     # mean 1.3 vs 1.1 (x1.18) but the interval is wide: not a failure
+    assert len(res["rows"]) == 1 and res["rows"][0]["ratio"] > 1.15 and not res["rows"][0]["regression"]
+    assert [k[1] for k in res["missing"]] == ["softmax_dim.32x64"] and [k[1] for k in res["extra"]] == ["other"]
+    b, c, n = tmp_path / "b.json", tmp_path / "c.json", tmp_path / "n.json"
+    b.write_text(json.dumps(base)); c.write_text(json.dumps(slow)); n.write_text(json.dumps(noisy))
+    assert R.main(["regress", "--baseline", str(b), "--current", str(c)]) == 0                     # report only
+    assert R.main(["regress", "--baseline", str(b), "--current", str(c), "--fail-on-regression"]) == 1
+    assert R.main(["regress", "--baseline", str(b), "--current", str(c), "--fail-on-regression", "--max-slowdown", "3.0"]) == 0
+    assert R.main(["regress", "--baseline", str(b), "--current", str(n), "--fail-on-regression"]) == 0
+    assert R.main(["regress", "--baseline", str(b), "--current", str(n), "--require-matching"]) == 1
+    assert R.main(["regress", "--baseline", str(b), "--current", str(b), "--fail-on-regression", "--require-matching"]) == 0
+
+
+def test_static_site_lists_snapshots_and_escapes_names(tmp_path):
+    out = tmp_path / "site"
+    assert [p.name for p in R.render_site(tmp_path / "absent", out)] == ["index.html"]
+    assert "no snapshots yet" in (out / "index.html").read_text()
+    runs = tmp_path / "runs"
+    for v, scale in (("v0.1.0", 1.0), ("v0.2.0", 0.5)):
+        (runs / v).mkdir(parents=True)
+        (runs / v / "cpu.json").write_text(json.dumps(_doc("cpu<suite>", scale)))
+        (runs / v / "manifest.json").write_text(json.dumps({"version": v, "git_sha": "a" * 40, "date": "2026-01-01"}))
+    (runs / "v0.2.0" / "broken.json").write_text("{not json")
+    (runs / "empty").mkdir()
+    pages = R.render_site(runs, out)
+    assert [p.name for p in pages] == ["index.html", "v0.1.0.html", "v0.2.0.html"]
+    idx = (out / "index.html").read_text()
+    assert "v0.1.0.html" in idx and "aaaaaaaaaaaa" in idx and "empty" not in idx
+    page = (out / "v0.2.0.html").read_text()
+    assert "cpu&lt;suite&gt;" in page and "<suite>" not in page and "matmul.128x128x128" in page and "0.5500" in page
+    assert R.main(["site", "--runs-dir", str(runs), "--out", str(out)]) == 0
