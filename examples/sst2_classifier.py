@@ -85,6 +85,38 @@ def evaluate(model, data, batch):
     return {"loss": loss_sum / n, "accuracy": (conf[0][0] + conf[1][1]) / n, "confusion": conf, "hist": hist}
 
 
+def parity_one_step(model, rows, lr, a, seq_len, d_model, ffn_dim):
+    """Runs one training step on `rows` and writes everything an outside implementation needs to repeat it: the batch,
+    the hyper-parameters, every parameter before the step, the logits, the loss, every gradient and every parameter
+    after one Adam step (`python -m rustral_b200.bench.sst2_parity <dump>` repeats it in plain PyTorch and compares;
+    the reference's counterpart is scripts/eval/sst2_parity_one_step.py)."""
+    from rustral_b200.nn.loss import CrossEntropyLoss
+    ctx = ForwardCtx.train()
+    ids = model.collate([x for x, _ in rows])
+    labels = model.collate_targets([y for _, y in rows])
+    named = list(model.named_parameters())
+    before = {n: p.tensor.detach().float().cpu().reshape(-1).tolist() for n, p in named}
+    shapes = {n: list(p.tensor.shape) for n, p in named}
+    model.zero_grad()
+    logits = model.forward(ids, ctx)
+    loss = CrossEntropyLoss()(logits.float(), labels)
+    loss.backward()
+    grads = {n: (p.tensor.grad.detach().float().cpu().reshape(-1).tolist() if p.tensor.grad is not None else None) for n, p in named}
+    Adam(lr=lr).step([p for _, p in named])
+    after = {n: p.tensor.detach().float().cpu().reshape(-1).tolist() for n, p in named}
+    path = a.parity_dump or os.path.join(a.out_dir, "parity.json")
+    os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+    with open(path, "w") as f:
+        json.dump({"task": "sst2_parity_one_step", "ids": ids.cpu().tolist(), "labels": labels.cpu().tolist(),
+                   "config": {"seq_len": seq_len, "d_model": d_model, "num_heads": a.num_heads, "ffn_dim": ffn_dim,
+                              "num_layers": a.num_layers, "pad_id": model._pad_id, "lr": lr, "layer_norm_eps": 1e-5,
+                              "adam": {"beta1": 0.9, "beta2": 0.999, "eps": 1e-8}, "gelu": "tanh"},
+                   "shapes": shapes, "params_before": before, "logits": logits.detach().float().cpu().reshape(-1).tolist(),
+                   "loss": float(loss), "grads": grads, "params_after": after}, f)
+    print(f"parity: batch={len(rows)} loss={float(loss):.6f}; wrote {path}")
+    return path
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--quick", action="store_true")
@@ -103,6 +135,10 @@ def main(argv=None):
     ap.add_argument("--vocab", help="reuse a vocab.txt instead of fitting one")
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--out-dir", default="out/sst2")
+    ap.add_argument("--parity-one-step", action="store_true",
+                    help="one forward / backward / Adam step on the first --parity-batch examples, dumped for an independent check")
+    ap.add_argument("--parity-batch", type=int, default=8)
+    ap.add_argument("--parity-dump", default=None, help="where the one-step record goes (default <out-dir>/parity.json)")
     a = ap.parse_args(argv)
     quick = a.quick and not a.paper
     epochs = a.epochs or (1 if quick else 10 if a.paper else 40 if a.overfit_32 else 3)
@@ -136,6 +172,8 @@ def main(argv=None):
     total_params = model.num_parameters()
     print(f"sst2: train={len(tr)} dev={len(dv)} vocab={len(tok.vocab)} params={total_params} epochs={epochs} lr={lr} "
           f"offline={os.environ.get('RUSTRAL_DATASET_OFFLINE') == '1'}")
+    if a.parity_one_step:
+        return parity_one_step(model, tr[:a.parity_batch], lr, a, seq_len, d_model, ffn_dim)
     opt = Sgd(lr=lr) if a.sgd else Adam(lr=lr)
     t0 = time.perf_counter()
     report = Trainer.classification(opt).epochs(epochs).batch_size(a.batch).shuffle(True).seed(a.seed % (1 << 31)) \

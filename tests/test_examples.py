@@ -3,6 +3,8 @@ import importlib.util
 import json
 import os
 
+import pytest
+
 
 def test_tiny_lm_cpu_trains_and_roundtrips(tmp_path):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -205,3 +207,26 @@ def test_pretraining_example_checkpoints_asynchronously_and_resumes_exactly(tmp_
     rest = mod.main([*common, "--steps", "12", "--out", str(tmp_path / "part"), "--resume"])
     assert rest["first_step"] == 8 and rest["losses"] == full["losses"][8:]
     assert json.load(open(tmp_path / "part" / "summary.json"))["last_checkpoint"] == 12
+
+
+@pytest.mark.parametrize("layers", [0, 2])
+def test_sst2_one_step_parity_against_plain_pytorch(tmp_path, monkeypatch, layers):
+    """The example's one-step dump is reproduced by an independent torch.nn.functional model + torch.optim.Adam, and a
+    tampered dump is caught (scripts/eval/sst2_parity_one_step.py)."""
+    from rustral_b200.bench import sst2_parity
+    _stage_sst2(tmp_path, monkeypatch, reps=2)
+    dump = tmp_path / "parity.json"
+    _load_example("sst2_classifier").main(["--overfit-32", "--num-layers", str(layers), "--parity-one-step", "--parity-batch", "8",
+                                           "--parity-dump", str(dump), "--out-dir", str(tmp_path / "o")])
+    doc = json.load(open(dump))
+    assert len(doc["ids"]) == 8 and doc["config"]["num_layers"] == layers and set(doc["grads"]) == set(doc["params_before"])
+    res = sst2_parity.check(doc)
+    assert res["ok"], res
+    assert res["logits"]["max_abs"] < 1e-5 and abs(res["loss"][0] - res["loss"][1]) < 1e-5
+    head = [r for r in res["grads"] if r["name"] == "head.weight"][0]
+    assert head["sign_agree"] == 1.0 and head["rel_l2"] < 1e-4 and head["norm_torch"] > 0
+    assert sst2_parity.main([str(dump)]) == 0
+    doc["grads"]["head.weight"] = [-g for g in doc["grads"]["head.weight"]]        # a sign error must be reported
+    bad = tmp_path / "bad.json"
+    bad.write_text(json.dumps(doc))
+    assert sst2_parity.main([str(bad)]) == 1
