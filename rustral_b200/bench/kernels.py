@@ -5,11 +5,18 @@
     python -m rustral_b200.bench.kernels attention --batch 32 --seq 1024 --heads 12 --head-dim 64 [--impl tc2|tc|mma] [--backward]
     python -m rustral_b200.bench.kernels norm --rows 32768 --n 768
     python -m rustral_b200.bench.kernels adam --numel 124000000
+    python -m rustral_b200.bench.kernels launch-overhead [--calls 5000]
 
 Timing: CUDA events around each call on the current stream, `--warmup` untimed calls first, a 256 MiB buffer is
 overwritten between timed calls so every call starts with a cold L2; the median is reported.  Fractions are
 against the copy bandwidth and cuBLAS bf16 throughput measured on the same GPU type (`MEASURED_PEAKS.json` at the
 repository root when present, else 6650 GB/s and 1590 TFLOP/s).  One JSON line per run.
+
+`launch-overhead` measures the host side instead: small operations (a 128^3 product, softmax and LayerNorm of 32 x 256,
+an elementwise add) are issued `--calls` times back to back and the wall time per call is reported (the GPU work is a few
+microseconds, so the issue rate is the host's), next to the same call bracketed by two CUDA events, which is how the
+workload table times one call, and next to `torch.add` / `torch.mm` on the same tensors as the yardstick of what a
+native-extension launch costs on this machine.
 """
 from __future__ import annotations
 
@@ -174,6 +181,46 @@ def bench_paged(a):
                    "kv_cache_bytes": int(kv_bytes)})
 
 
+def bench_launch_overhead(a):
+    import time
+
+    from .. import ops
+    from ..core import B200Backend
+    table = B200Backend("cuda:0").ops()
+    x = torch.randn(128, 128, device="cuda").bfloat16()
+    y = torch.randn(128, 128, device="cuda").bfloat16()
+    r = torch.randn(32, 256, device="cuda").bfloat16()
+    w, b = torch.ones(256, device="cuda").bfloat16(), torch.zeros(256, device="cuda").bfloat16()
+    cases = [("op_table.matmul 128^3", lambda: table.matmul(x, y)), ("ops.gemm 128^3", lambda: ops.gemm(x, y, b_mn=True)),
+             ("ops.linear 128^3", lambda: ops.linear(x, y)), ("ops.softmax 32x256", lambda: ops.softmax(r)),
+             ("ops.layer_norm 32x256", lambda: ops.layer_norm(r, w, b, 1e-5)), ("ops.gelu 32x256", lambda: ops.gelu(r)),
+             ("ops.binary add 32x256", lambda: ops.binary("add", r, r)),
+             ("torch.add 32x256", lambda: torch.add(r, r)), ("torch.mm 128^3", lambda: torch.mm(x, y))]
+    rows = []
+    for name, fn in cases:
+        for _ in range(50):
+            fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(a.calls):
+            fn()
+        host_us = (time.perf_counter() - t0) / a.calls * 1e6
+        torch.cuda.synchronize()
+        ev = []
+        for _ in range(50):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ev.append(e0.elapsed_time(e1) * 1e3)
+        ev.sort()
+        rows.append({"call": name, "host_us_per_call": round(host_us, 2), "event_bracketed_us": round(ev[len(ev) // 2], 2)})
+    out = {"kernel": "launch-overhead", "calls": a.calls, "rows": rows}
+    print(json.dumps(out))
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="rustral_b200.bench.kernels")
     ap.add_argument("--warmup", type=int, default=3)
@@ -214,8 +261,10 @@ def main(argv=None):
     pg.add_argument("--kv-heads", type=int, default=8)
     pg.add_argument("--head-dim", type=int, default=128)
     pg.add_argument("--block-size", type=int, default=16)
+    lo = sub.add_parser("launch-overhead")
+    lo.add_argument("--calls", type=int, default=5000)
     a = ap.parse_args(argv)
-    return {"paged": bench_paged, "gemm": bench_gemm, "gemm-fp8": bench_gemm_fp8, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam}[a.op](a)
+    return {"launch-overhead": bench_launch_overhead, "paged": bench_paged, "gemm": bench_gemm, "gemm-fp8": bench_gemm_fp8, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam}[a.op](a)
 
 
 if __name__ == "__main__":

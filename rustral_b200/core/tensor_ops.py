@@ -12,6 +12,19 @@ import torch
 from .errors import InvalidArgument, ShapeMismatch
 
 
+_OPS = None
+
+
+def _ops_mod():
+    """The kernel-wrapper package, imported on first use (it imports this package) and then kept: the op table is on the
+    path of every small launch, where a `from .. import` statement per call is measurable."""
+    global _OPS
+    if _OPS is None:
+        from .. import ops
+        _OPS = ops
+    return _OPS
+
+
 class TensorOps:
     def __init__(self, backend):
         self.backend = backend
@@ -40,7 +53,7 @@ class TensorOps:
 
     # ---- GEMM family ----------------------------------------------------------------------------------
     def _gemm(self, a, b_nk, bias=None, act="none"):
-        from .. import ops
+        ops = _ops_mod()
         if a.is_cuda and a.dtype == torch.float32:
             out = ops.gemm(ops.cast_f32_to_bf16(a.contiguous()), ops.cast_f32_to_bf16(b_nk.contiguous()),
                            bias=None if bias is None else ops.cast_f32_to_bf16(bias.contiguous()), act=act,
@@ -50,7 +63,7 @@ class TensorOps:
 
     def matmul(self, a, b):
         """[m,k] x [k,n]."""
-        from .. import ops
+        ops = _ops_mod()
         if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
             raise ShapeMismatch((a.shape[0], "k"), b.shape, "matmul")
         if a.is_cuda and a.dtype == torch.float32:
@@ -63,12 +76,12 @@ class TensorOps:
         return self._gemm(x, weight, bias)
 
     def transpose(self, a):
-        from .. import ops
+        ops = _ops_mod()
         return ops.transpose2d(a)
 
     # ---- elementwise ------------------------------------------------------------------------------------
     def _bin(self, op, a, b):
-        from .. import ops
+        ops = _ops_mod()
         return ops.binary(op, a, b)
 
     def add(self, a, b): return self._bin("add", a, b)
@@ -82,7 +95,7 @@ class TensorOps:
         return self._bin("div", a, b)
 
     def _un(self, op, a):
-        from .. import ops
+        ops = _ops_mod()
         return ops.unary(op, a)
 
     def relu(self, a): return self._un("relu", a)
@@ -104,40 +117,40 @@ class TensorOps:
         return self._un("sqrt", a)
 
     def add_scalar(self, a, s):
-        from .. import ops
+        ops = _ops_mod()
         return ops.scalar_op("add_scalar", a, s)
 
     def mul_scalar(self, a, s):
-        from .. import ops
+        ops = _ops_mod()
         return ops.scalar_op("mul_scalar", a, s)
 
     def gt_scalar(self, a, s):
-        from .. import ops
+        ops = _ops_mod()
         return ops.scalar_op("gt_scalar", a, s)
 
     def add_row_vector(self, a, v):
-        from .. import ops
+        ops = _ops_mod()
         if a.shape[-1] != v.shape[-1]:
             raise ShapeMismatch((a.shape[-1],), v.shape, "add_row_vector")
         return ops.add_row_vector(a, v)
 
     def dropout(self, x, p: float, training: bool):
-        from .. import ops
+        ops = _ops_mod()
         import random
         return ops.dropout(x, p, training, seed=random.getrandbits(48))
 
     def dropout_with_seed(self, x, p: float, seed: int, training: bool = True):
-        from .. import ops
+        ops = _ops_mod()
         return ops.dropout(x, p, training, seed=seed)
 
     # ---- softmax / reductions ------------------------------------------------------------------------------
     def softmax(self, a):
         """Softmax over ALL elements (the reference's `softmax`); use softmax_dim for rows."""
-        from .. import ops
+        ops = _ops_mod()
         return ops.softmax(a.reshape(1, -1)).reshape(a.shape)
 
     def log_softmax(self, a):
-        from .. import ops
+        ops = _ops_mod()
         return ops.log_softmax(a.reshape(1, -1)).reshape(a.shape)
 
     def _dim_last(self, a, dim, fn):
@@ -147,23 +160,23 @@ class TensorOps:
         return fn(a.transpose(dim, -1).contiguous()).transpose(dim, -1).contiguous()
 
     def softmax_dim(self, a, dim: int):
-        from .. import ops
+        ops = _ops_mod()
         return self._dim_last(a, dim, ops.softmax)
 
     def log_softmax_dim(self, a, dim: int):
-        from .. import ops
+        ops = _ops_mod()
         return self._dim_last(a, dim, ops.log_softmax)
 
     def sum_all(self, a):
-        from .. import ops
+        ops = _ops_mod()
         return ops.sum_all(a)
 
     def sum_dim0(self, a):
-        from .. import ops
+        ops = _ops_mod()
         return ops.sum_dim0(a.reshape(a.shape[0], -1)).to(a.dtype).reshape(a.shape[1:])
 
     def sum_dim(self, a, dim: int, keepdim: bool = False):
-        from .. import ops
+        ops = _ops_mod()
         dim = dim % a.dim()
         moved = a.movedim(dim, 0).contiguous()
         r = ops.sum_dim0(moved.reshape(moved.shape[0], -1)).to(a.dtype).reshape(moved.shape[1:])
@@ -180,23 +193,23 @@ class TensorOps:
         return self.mul_scalar(self.sum_dim(self.mul(d, d), dim, keepdim), 1.0 / max(n, 1))
 
     def argmax(self, a):
-        from .. import ops
+        ops = _ops_mod()
         return int(ops.argmax_rows(a.reshape(1, -1))[0])
 
     def argmax_rows(self, a):
-        from .. import ops
+        ops = _ops_mod()
         return ops.argmax_rows(a)
 
     # ---- data movement -----------------------------------------------------------------------------------------
     def gather_rows(self, table, ids):
-        from .. import ops
+        ops = _ops_mod()
         ids = torch.as_tensor(ids, dtype=torch.int64, device=table.device)
         if ids.numel() and (int(ids.min()) < 0 or int(ids.max()) >= table.shape[0]):
             raise InvalidArgument("gather_rows: index out of range")
         return ops.gather_rows(table, ids)
 
     def broadcast_to(self, a, shape):
-        from .. import ops
+        ops = _ops_mod()
         if len(shape) == 2:
             return ops.broadcast_to(a, shape[0], shape[1])
         return a.expand(tuple(shape)).contiguous()
@@ -205,7 +218,7 @@ class TensorOps:
         return self.broadcast_to(a, shape)
 
     def concat(self, tensors, dim: int = 0):
-        from .. import ops
+        ops = _ops_mod()
         ts = list(tensors)
         if ts[0].is_cuda and ts[0].dim() == 2 and dim in (1, -1):
             rows = ts[0].shape[0]
@@ -236,18 +249,18 @@ class TensorInPlaceOps:
 
     @staticmethod
     def add_assign(a, b):
-        from .. import ops
+        ops = _ops_mod()
         return ops.binary("add", a, b, out=a)
 
     @staticmethod
     def mul_assign(a, b):
-        from .. import ops
+        ops = _ops_mod()
         return ops.binary("mul", a, b, out=a)
 
     @staticmethod
     def axpy(alpha: float, x, y):
         """y += alpha * x"""
-        from .. import ops
+        ops = _ops_mod()
         return ops.binary("add", y, ops.scalar_op("mul_scalar", x, alpha), out=y)
 
 
@@ -292,7 +305,7 @@ class AttentionOps:
         self.backend = backend
 
     def flash_attention_2(self, q, k, v, causal: bool = False, scale=None):
-        from .. import ops
+        ops = _ops_mod()
         return ops.flash_attention(q, k, v, causal, scale)
 
     def flash_attention_2_with_mask(self, q, k, v, mask, scale=None):

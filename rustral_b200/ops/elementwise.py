@@ -20,7 +20,7 @@ _scratch: dict = {}
 
 
 def _f32_scratch(device, n: int) -> torch.Tensor:
-    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    key = N.stream_key(device)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < n:
         buf = torch.empty(max(n, 4096), dtype=torch.float32, device=device)
@@ -137,15 +137,15 @@ class _UnaryFn(torch.autograd.Function):
 
 def gelu(x):
     """tanh-approximated GELU (crates/ndarray-backend/src/lib.rs:565), differentiable."""
-    return _UnaryFn.apply(x, "gelu")
+    return _UnaryFn.apply(x, "gelu") if N.wants_grad(x) else unary("gelu", x)
 
 
 def relu(x):
-    return _UnaryFn.apply(x, "relu")
+    return _UnaryFn.apply(x, "relu") if N.wants_grad(x) else unary("relu", x)
 
 
 def silu(x):
-    return _UnaryFn.apply(x, "silu")
+    return _UnaryFn.apply(x, "silu") if N.wants_grad(x) else unary("silu", x)
 
 
 def add_row_vector(a, v):

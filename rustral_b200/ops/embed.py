@@ -9,7 +9,7 @@ _scratch: dict = {}
 
 
 def _int_scratch(device, n: int) -> torch.Tensor:
-    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    key = N.stream_key(device)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < n:
         buf = torch.empty(n, dtype=torch.int32, device=device)
@@ -80,4 +80,6 @@ class _EmbeddingFn(torch.autograd.Function):
 
 def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     """Row gather ``table[ids]`` with a deterministic gradient (crates/nn/src/embedding.rs:71-79)."""
+    if not N.wants_grad(table):
+        return embedding_forward(ids, table).reshape(*ids.shape, table.shape[1])
     return _EmbeddingFn.apply(ids, table)

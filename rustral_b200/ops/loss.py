@@ -79,7 +79,7 @@ def cross_entropy(logits, targets, n_valid: int | None = None, ignore_index: int
 
 
 def _softmax_impl(x, log_mode: bool):
-    x2 = x.reshape(-1, x.shape[-1])
+    x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])      # a reshape, even as a no-op view, costs about 2 us
     if not x.is_cuda:
         f = torch.log_softmax if log_mode else torch.softmax
         return f(x2.float(), -1).to(x.dtype).reshape(x.shape)
@@ -91,7 +91,7 @@ def _softmax_impl(x, log_mode: bool):
     N.check(N.kernels().rb_softmax_rows(x2.data_ptr(), y.data_ptr(), x2.shape[0], x2.shape[1], x2.stride(0),
                                         y.stride(0), int(log_mode), int(x2.dtype == torch.bfloat16), N.stream_ptr()),
             "rb_softmax_rows")
-    return y.reshape(x.shape)
+    return y if x.dim() == 2 else y.reshape(x.shape)
 
 
 class _SoftmaxFn(torch.autograd.Function):
@@ -122,10 +122,14 @@ class _SoftmaxFn(torch.autograd.Function):
 
 def softmax(x):
     """Softmax over the last dimension."""
+    if not N.wants_grad(x):
+        return _softmax_impl(x, False)
     return _SoftmaxFn.apply(x, False)
 
 
 def log_softmax(x):
     """Log-softmax over the last dimension with the exact gradient (the reference's tape op uses a
     placeholder backward, crates/autodiff/src/lib.rs:611-626)."""
+    if not N.wants_grad(x):
+        return _softmax_impl(x, True)
     return _SoftmaxFn.apply(x, True)

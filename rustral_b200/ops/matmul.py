@@ -10,6 +10,7 @@ Epilogue order: ``+ bias`` -> activation (or multiply by ``act'(aux_in)``) -> ``
 from __future__ import annotations
 
 import math
+import threading
 
 import torch
 
@@ -83,12 +84,23 @@ WORKSPACE_BYTES = 128 << 20
 
 def _workspace(device) -> torch.Tensor:
     """Split-K scratch, one per device and stream, allocated on first use."""
-    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    key = N.stream_key(device)
     ws = _workspaces.get(key)
     if ws is None:
         ws = torch.empty(WORKSPACE_BYTES, dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+_plain_tls = threading.local()
+
+
+def _plain_args() -> dict:
+    """Per-thread cache of filled argument blocks (autograd runs backward GEMMs on its own thread)."""
+    d = getattr(_plain_tls, "args", None)
+    if d is None:
+        d = _plain_tls.args = {}
+    return d
 
 
 # Optional tile-plan table: fn(M, N, K, a_mn, b_mn, out_is_f32) -> {"block_n", "splits", "group_m"} or None.  Installed by
@@ -145,6 +157,33 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         plan = _PLAN_HOOK(M, Nn, K, a_mn, b_mn, out.dtype == torch.float32)
         if plan:
             block_n, splits, group_m = int(plan.get("block_n", 0)), int(plan.get("splits", 0)), int(plan.get("group_m", 0))
+    if (bias is None and residual is None and aux_in is None and aux_out is None and row_scale is None
+            and col_scale is None and peer is None):
+        # Plain product: the argument block of a (shape, strides, plan) is filled once and kept; a call only writes the
+        # three addresses (and the split-K workspace), which halves the Python time of a small launch.
+        cache = _plain_args()
+        key = (M, Nn, K, a_mn, b_mn, act, out.dtype, accumulate, alpha, block_n, group_m, max_ctas, splits,
+               a.stride(0), b.stride(0), out.stride(0))
+        g = cache.get(key)
+        if g is None:
+            if len(cache) > 4096:
+                cache.clear()
+            g = N.RbGemmArgs()
+            g.lda, g.ldb, g.ldd = a.stride(0), b.stride(0), out.stride(0)
+            g.M, g.N, g.K = M, Nn, K
+            g.a_mn_major, g.b_mn_major = int(a_mn), int(b_mn)
+            g.act = N.ACT[act]
+            g.out_f32 = int(out.dtype == torch.float32)
+            g.accumulate = int(accumulate)
+            g.alpha = alpha
+            g.block_n, g.group_m, g.max_ctas, g.splits = block_n, group_m, max_ctas, splits
+            cache[key] = g
+        g.a, g.b, g.d = a.data_ptr(), b.data_ptr(), out.data_ptr()
+        if splits != 1 and K >= 2048 and act == "none":
+            ws = _workspace(a.device)
+            g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel()
+        N.check(N.kernels().rb_gemm_bf16(g, N.stream_ptr()), "rb_gemm_bf16")
+        return out
     for t, nm in ((bias, "bias"), (residual, "residual"), (aux_in, "aux_in"), (aux_out, "aux_out")):
         if t is not None and t.dtype != torch.bfloat16:
             raise TypeError(f"gemm: {nm} must be bf16")
@@ -290,4 +329,10 @@ class _LinearFn(torch.autograd.Function):
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias=None, act: str = "none", residual=None) -> torch.Tensor:
     """Differentiable fused linear: ``act(x @ w.T + bias) + residual``."""
+    if not N.wants_grad(x, w, bias, residual):
+        if x.dim() == 2:
+            return gemm(x, w, bias=bias, act=act, residual=residual, out_dtype=x.dtype)
+        res2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
+        y = gemm(x.reshape(-1, x.shape[-1]), w, bias=bias, act=act, residual=res2, out_dtype=x.dtype)
+        return y.reshape(*x.shape[:-1], w.shape[0])
     return _LinearFn.apply(x, w, bias, act, residual)

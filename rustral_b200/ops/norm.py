@@ -10,7 +10,7 @@ _scratch: dict = {}
 
 def _partial_scratch(device, numel: int) -> torch.Tensor:
     """Grow-only fp32 scratch for the parameter-gradient partials, one per device and stream."""
-    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    key = N.stream_key(device)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < numel:
         buf = torch.empty(max(numel, 1 << 16), dtype=torch.float32, device=device)
@@ -18,8 +18,9 @@ def _partial_scratch(device, numel: int) -> torch.Tensor:
     return buf
 
 
-def norm_forward(x2: torch.Tensor, gamma: torch.Tensor, beta, eps: float, rms: bool, out=None):
-    """x2: [rows, n].  Returns (y, mean, rstd); mean is None for RMSNorm."""
+def norm_forward(x2: torch.Tensor, gamma: torch.Tensor, beta, eps: float, rms: bool, out=None, want_stats: bool = True):
+    """x2: [rows, n].  Returns (y, mean, rstd); mean is None for RMSNorm, and both are None on a CUDA tensor when
+    `want_stats` is False (inference: nothing will run backward)."""
     rows, n = x2.shape
     if not x2.is_cuda:
         xf = x2.float()
@@ -42,10 +43,14 @@ def norm_forward(x2: torch.Tensor, gamma: torch.Tensor, beta, eps: float, rms: b
     if x2.dtype != torch.bfloat16 or gamma.dtype != torch.bfloat16:
         raise TypeError("norm: CUDA tensors must be bf16")
     y = out if out is not None else torch.empty((rows, n), dtype=x2.dtype, device=x2.device)
-    mean = None if rms else torch.empty(rows, dtype=torch.float32, device=x2.device)
-    rstd = torch.empty(rows, dtype=torch.float32, device=x2.device)
+    mean = rstd = None
+    if want_stats:
+        if rms:
+            rstd = torch.empty(rows, dtype=torch.float32, device=x2.device)
+        else:
+            mean, rstd = torch.empty((2, rows), dtype=torch.float32, device=x2.device).unbind(0)
     N.check(N.kernels().rb_norm_fwd(x2.data_ptr(), x2.stride(0), gamma.data_ptr(), N.ptr(beta), y.data_ptr(),
-                                    y.stride(0), N.ptr(mean), rstd.data_ptr(), rows, n, eps, int(rms),
+                                    y.stride(0), N.ptr(mean), N.ptr(rstd), rows, n, eps, int(rms),
                                     N.stream_ptr()), "rb_norm_fwd")
     return y, mean, rstd
 
@@ -117,10 +122,22 @@ class _NormFn(torch.autograd.Function):
                 None, None)
 
 
+def _norm_inference(x, gamma, beta, eps, rms):
+    x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = norm_forward(x2, gamma, beta, eps, rms, want_stats=False)[0]
+    return y if x.dim() == 2 else y.reshape(x.shape)
+
+
 def layer_norm(x, gamma, beta, eps: float = 1e-5):
     """Population variance, eps inside the square root (crates/nn/src/normalization.rs:87-158)."""
+    if not N.wants_grad(x, gamma, beta):
+        return _norm_inference(x, gamma, beta, eps, False)
     return _NormFn.apply(x, gamma, beta, eps, False)
 
 
 def rms_norm(x, gamma, eps: float = 1e-5):
+    if not N.wants_grad(x, gamma):
+        return _norm_inference(x, gamma, None, eps, True)
     return _NormFn.apply(x, gamma, None, eps, True)

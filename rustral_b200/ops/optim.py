@@ -9,7 +9,7 @@ _scratch: dict = {}
 
 
 def _f32_scratch(device, n: int) -> torch.Tensor:
-    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    key = N.stream_key(device)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < n:
         buf = torch.empty(n, dtype=torch.float32, device=device)
