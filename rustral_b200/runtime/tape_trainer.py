@@ -106,6 +106,13 @@ class TapeTrainer:
                 for p in params:
                     p.zero_grad()
                 tape.values[loss].backward()
+                # a parameter brought onto the tape with watch_parameter() is a separate leaf that shares the
+                # parameter's storage: its gradient lands on that leaf and is handed to the parameter here
+                for p in params:
+                    tid = tape.param_map.get(p.id)
+                    g = tape.values[tid].grad if tid is not None else None
+                    if g is not None:
+                        p.tensor.grad = g if p.tensor.grad is None else p.tensor.grad + g
                 self.optimizer.step(params)
                 if self.tensor_pool is not None:
                     self.tensor_pool.begin_step()

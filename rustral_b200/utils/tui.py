@@ -167,6 +167,9 @@ class TrainingDashboard:
             if now - self._rate_t >= 1.0:
                 self.throughput = self._rate_n / (now - self._rate_t)
                 self._rate_t, self._rate_n = now, 0
+                self._rate_settled = True
+            elif not getattr(self, "_rate_settled", False) and now > self._rate_t:
+                self.throughput = self._rate_n / (now - self._rate_t)     # provisional until the first full second
 
     def _push(self, hist: list, v: float) -> None:
         hist.append(float(v))

@@ -128,3 +128,29 @@ def test_engine_loop_drops_the_requests_of_a_failed_step():
         assert calls["n"] == 2
     finally:
         loop.shutdown()
+
+
+def test_trainer_updates_parameters_that_the_model_put_on_the_tape_itself():
+    """A model whose forward_tape brings its parameters onto the tape with watch_parameter() trains through the Trainer
+    builder: the gradients land on the tape's leaves, not on `parameter.tensor.grad`, and the trainer must collect them
+    from there (it used to step with no gradients at all, leaving such a model at its initial loss)."""
+    import torch
+    from rustral_b200.core import CpuBackend
+    from rustral_b200.core.module import Module, Trainable
+    from rustral_b200.nn import LinearBuilder
+    from rustral_b200.optim import Sgd
+    from rustral_b200.runtime.tape_trainer import SupervisedTapeModel, Trainer
+    be = CpuBackend()
+
+    class M(Module, Trainable, SupervisedTapeModel):
+        def __init__(self):
+            self.lin = LinearBuilder(2, 2).with_bias().seed(1).build(be)
+
+        def forward_tape(self, x, tape, ctx):
+            return tape.linear_tape(tape.constant(x), tape.watch_parameter(self.lin.weight), tape.watch_parameter(self.lin.bias))
+    m = M()
+    before = m.lin.weight.tensor.detach().clone()
+    data = [([1.0, 0.0], 0), ([0.0, 1.0], 1)] * 4
+    rep = Trainer.classification(Sgd(0.5)).epochs(20).batch_size(4).fit(be, m, data)
+    assert not torch.equal(before, m.lin.weight.tensor.detach())
+    assert rep.epochs[-1].mean_loss < 0.5 * rep.epochs[0].mean_loss and rep.accuracy == 1.0
