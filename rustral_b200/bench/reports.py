@@ -7,6 +7,7 @@
     python -m rustral_b200.bench.reports emnlp --harness combined.json --runs runs/v0.1.0 --out emnlp_report.md
     python -m rustral_b200.bench.reports regress --baseline old.json --current new.json --fail-on-regression
     python -m rustral_b200.bench.reports site --runs-dir runs --out site/
+    python -m rustral_b200.bench.reports queue --out benchmarks [--nlp benchmark|paper|off] [--strict]
 
 What each sub-command does, and the script of the reference whose job it takes over:
 
@@ -28,6 +29,11 @@ What each sub-command does, and the script of the reference whose job it takes o
             --max-slowdown times the baseline AND the two 95 % confidence intervals do not overlap (so noise alone does
             not fail a build); --require-matching fails on workloads that disappeared
             (scripts/bench/compare_harness.py);
+* queue     the whole measurement campaign as one sequential job list with a log: micro-benchmark suites of this
+            framework, the plain-PyTorch suites, the multi-seed NLP evaluation, its PyTorch twins, and the comparative
+            report at the end.  Every step is time-stamped in `<out>/queue_logs/<stamp>/run.log` (`latest` points at the
+            newest), a failing optional step is recorded and skipped over (with --strict it fails the run), and a
+            `done` file marks completion (scripts/bench/queue_all_benchmarks.sh, scripts/run_paper_experiments.sh);
 * site      a static HTML dashboard: `index.html` listing every snapshot under --runs-dir with its manifest, and one
             page per snapshot with a sortable table per suite; no scripts are fetched and nothing is loaded at view
             time (scripts/bench/render_site.py).
@@ -458,6 +464,110 @@ def cmd_site(a) -> int:
     return 0
 
 
+# ------------------------------------------------------------------------------------------------- campaign queue
+def run_queue(out: Path, suites: list, repeats: int, warmup: int, nlp: str, seeds: str, device: str, strict: bool,
+              torch_twins: bool = True, steps_override: list | None = None) -> dict:
+    """Runs the job list in order; returns {"failures": n, "steps": [(name, "ok" | "failed: ..." | "skipped")], "report": path}.
+    `steps_override` replaces the job list with [(name, optional, callable)] (used by tests)."""
+    stamp = time.strftime("%Y%m%d_%H%M%S")
+    logdir = out / "queue_logs" / stamp
+    logdir.mkdir(parents=True, exist_ok=True)
+    latest = out / "queue_logs" / "latest"
+    try:
+        if latest.is_symlink() or latest.exists():
+            latest.unlink()
+        latest.symlink_to(stamp)
+    except OSError:
+        pass
+    log_path = logdir / "run.log"
+    results, harness_docs, runs_dir = [], [], out / "runs" / stamp
+    report = out / "reports" / f"comparative_queue_{stamp}.md"
+
+    def log(msg: str) -> None:
+        with open(log_path, "a") as f:
+            f.write(f"[{time.strftime('%Y-%m-%dT%H:%M:%S')}] {msg}\n")
+
+    def suites_step(names):
+        def go():
+            docs = [d for d in (run_suite(su, repeats, warmup) for su in names) if d is not None]
+            if not docs:
+                raise RuntimeError("no suite of this step can run on this machine")
+            doc = combine(docs)
+            path = out / "results" / f"{stamp}_{'_'.join(names)}.json"
+            path.parent.mkdir(parents=True, exist_ok=True)
+            path.write_text(json.dumps(doc, indent=1))
+            harness_docs.append(str(path))
+        return go
+
+    def nlp_step():
+        from . import nlp_eval
+        rc = nlp_eval.main([f"--{nlp}", "--seeds", seeds, "--device", device, "--out", str(runs_dir / "nlp"), "--clean"])
+        if rc:
+            raise RuntimeError(f"nlp_eval exit status {rc}")
+
+    def twin_step(task):
+        def go():
+            from . import torch_baselines
+            argv = ["--task", task, "--seeds", seeds, "--device", device, "--out", str(runs_dir / "nlp")]
+            vocabs = sorted((runs_dir / "nlp" / "raw" / "sst2").glob("seed*/vocab.txt"))     # written by the first seed's run
+            if task == "sst2" and vocabs:
+                argv += ["--vocab", str(vocabs[0])]
+            if nlp == "benchmark":
+                argv.append("--quick")
+            rc = torch_baselines.main(argv)
+            if rc:
+                raise RuntimeError(f"torch_baselines exit status {rc}")
+        return go
+
+    def report_step():
+        ns = argparse.Namespace(harness=harness_docs or None, runs=str(runs_dir) if (runs_dir / "nlp").is_dir() else None,
+                                baseline=None, out=str(report))
+        cmd_compare(ns)
+
+    ours = [su for su in suites if not su.startswith("torch")]
+    theirs = [su for su in suites if su.startswith("torch")]
+    steps = steps_override
+    if steps is None:
+        steps = []
+        if ours:
+            steps.append((f"micro-benchmarks: {', '.join(ours)}", False, suites_step(ours)))
+        if theirs:
+            steps.append((f"micro-benchmarks: {', '.join(theirs)}", True, suites_step(theirs)))
+        if nlp != "off":
+            steps.append((f"NLP evaluation ({nlp}, seeds {seeds})", False, nlp_step))
+            if torch_twins:
+                steps += [("PyTorch twin: sst2", True, twin_step("sst2")), ("PyTorch twin: wikitext2", True, twin_step("wikitext2"))]
+        steps.append(("comparative report", False, report_step))
+    failures = 0
+    log(f"queue start: {len(steps)} step(s), out={out}")
+    for i, (name, optional, fn) in enumerate(steps, 1):
+        log(f"=== [{i}/{len(steps)}] {name} ===")
+        t0 = time.perf_counter()
+        try:
+            fn()
+            results.append((name, "ok"))
+            log(f"[{i}] ok in {time.perf_counter() - t0:.1f} s")
+        except (Exception, SystemExit) as e:      # noqa: BLE001 - a failed step must not stop the queue
+            results.append((name, f"failed: {type(e).__name__}: {e}"))
+            if optional and not strict:
+                log(f"[{i}] FAILED (optional, continuing): {type(e).__name__}: {e}")
+            else:
+                failures += 1
+                log(f"[{i}] FAILED: {type(e).__name__}: {e}")
+    log(f"queue done: {failures} failure(s)")
+    (logdir / "done").write_text(f"{failures}\n")
+    return {"failures": failures, "steps": results, "report": str(report), "log": str(log_path)}
+
+
+def cmd_queue(a) -> int:
+    res = run_queue(Path(a.out), a.suite or ["cpu", "b200", "torch-cpu", "torch-cuda"], a.repeats, a.warmup, a.nlp, a.seeds, a.device,
+                    a.strict, not a.no_torch_twins)
+    for name, status in res["steps"]:
+        print(f"{status.split(':')[0]:<7} {name}")
+    print(f"log: {res['log']}\nreport: {res['report']}")
+    return 1 if res["failures"] else 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="rustral_b200.bench.reports")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -495,6 +605,17 @@ def main(argv=None) -> int:
     p.add_argument("--fail-on-regression", action="store_true")
     p.add_argument("--require-matching", action="store_true", help="fail when a baseline workload is absent from the current document")
     p.set_defaults(fn=cmd_regress)
+    p = sub.add_parser("queue")
+    p.add_argument("--out", default="benchmarks")
+    p.add_argument("--suite", action="append", choices=SUITES, help="default: every suite (those that need a GPU are skipped without one)")
+    p.add_argument("--repeats", type=int, default=5)
+    p.add_argument("--warmup", type=int, default=1)
+    p.add_argument("--nlp", choices=["benchmark", "paper", "off"], default="benchmark")
+    p.add_argument("--seeds", default="0,1,2")
+    p.add_argument("--device", default="cpu")
+    p.add_argument("--no-torch-twins", action="store_true")
+    p.add_argument("--strict", action="store_true", help="optional steps that fail count as failures")
+    p.set_defaults(fn=cmd_queue)
     p = sub.add_parser("site")
     p.add_argument("--runs-dir", required=True)
     p.add_argument("--out", required=True)

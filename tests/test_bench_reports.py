@@ -117,3 +117,31 @@ def test_static_site_lists_snapshots_and_escapes_names(tmp_path):
     page = (out / "v0.2.0.html").read_text()
     assert "cpu&lt;suite&gt;" in page and "<suite>" not in page and "matmul.128x128x128" in page and "0.5500" in page
     assert R.main(["site", "--runs-dir", str(runs), "--out", str(out)]) == 0
+
+
+def test_queue_logs_every_step_survives_optional_failures_and_marks_completion(tmp_path):
+    ran = []
+
+    def ok(name):
+        return lambda: ran.append(name)
+
+    def boom():
+        raise RuntimeError("no torch here")
+    steps = [("first", False, ok("first")), ("optional twin", True, boom), ("last", False, ok("last"))]
+    res = R.run_queue(tmp_path, [], 1, 0, "off", "0", "cpu", strict=False, steps_override=steps)
+    assert ran == ["first", "last"] and res["failures"] == 0
+    assert [s for _, s in res["steps"]] == ["ok", "failed: RuntimeError: no torch here", "ok"]
+    log = open(res["log"]).read()
+    assert "[1/3] first" in log and "FAILED (optional, continuing)" in log and "queue done: 0 failure(s)" in log
+    latest = tmp_path / "queue_logs" / "latest"
+    assert (latest / "done").read_text().strip() == "0" and (latest / "run.log").exists()
+    res = R.run_queue(tmp_path, [], 1, 0, "off", "0", "cpu", strict=True, steps_override=steps)
+    assert res["failures"] == 1
+
+
+def test_queue_runs_the_cpu_suite_and_writes_the_comparative_report(tmp_path):
+    res = R.run_queue(tmp_path, ["cpu"], repeats=1, warmup=0, nlp="off", seeds="0", device="cpu", strict=False)
+    assert res["failures"] == 0 and [s for _, s in res["steps"]] == ["ok", "ok"]
+    text = open(res["report"]).read()
+    assert "Micro-benchmarks" in text and "matmul.128x128x128" in text
+    assert len(list((tmp_path / "results").glob("*_cpu.json"))) == 1
