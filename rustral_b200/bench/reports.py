@@ -225,9 +225,15 @@ def nlp_section(title: str, ours: Path, twin: Path, metric: str) -> str:
             lines.append(f"*{label}: no curated file at `{path}`*")
             continue
         doc = json.loads(path.read_text())
-        runs = doc.get("runs", [])
-        vals = [r[metric] for r in runs if isinstance(r.get(metric), (int, float))]
-        thr = [r["throughput"] for r in runs if isinstance(r.get("throughput"), (int, float))]
+        # a curated run is {"seed", "manifest": {...}}: the metric is the document's own `metric` key (dev_accuracy,
+        # dev_perplexity) inside the manifest, the rate is samples or tokens per second; flat runs are accepted as well
+        runs = [r.get("manifest", r) if isinstance(r, dict) else {} for r in doc.get("runs", [])]
+        keys = [k for k in (doc.get("metric"), metric, "dev_" + metric) if k]
+        vals = [next(float(r[k]) for k in keys if isinstance(r.get(k), (int, float))) for r in runs
+                if any(isinstance(r.get(k), (int, float)) for k in keys)]
+        rate_keys = ("throughput", "tokens_per_sec", "samples_per_sec")
+        thr = [next(float(r[k]) for k in rate_keys if isinstance(r.get(k), (int, float))) for r in runs
+               if any(isinstance(r.get(k), (int, float)) for k in rate_keys)]
         lines.append(f"* {label}: {metric} {_pm(*_mean_std(vals))} over {len(vals)} seed(s); "
                      f"throughput {_pm(*_mean_std(thr), nd=1)} per second")
     return "\n".join(lines) + "\n"

@@ -230,3 +230,16 @@ def test_sst2_one_step_parity_against_plain_pytorch(tmp_path, monkeypatch, layer
     bad = tmp_path / "bad.json"
     bad.write_text(json.dumps(doc))
     assert sst2_parity.main([str(bad)]) == 1
+
+
+def test_campaign_queue_runs_the_nlp_evaluation_its_twins_and_the_report(tmp_path, monkeypatch):
+    """The one-shot job list: NLP evaluation of this framework, the plain-PyTorch twins on the same vocabulary, and the
+    comparative report with both (scripts/bench/queue_all_benchmarks.sh with RUN_NLP_PAPER / RUN_NLP_PYTORCH)."""
+    from rustral_b200.bench import reports
+    _stage_sst2(tmp_path, monkeypatch, reps=3)
+    _stage_wikitext_into(tmp_path / "cache")
+    res = reports.run_queue(tmp_path / "bench", [], repeats=1, warmup=0, nlp="benchmark", seeds="0", device="cpu", strict=True)
+    assert res["failures"] == 0, res["steps"]
+    assert [n for n, _ in res["steps"]] == ["NLP evaluation (benchmark, seeds 0)", "PyTorch twin: sst2", "PyTorch twin: wikitext2", "comparative report"]
+    text = open(res["report"]).read()
+    assert "SST-2 classifier" in text and "WikiText-2" in text and "PyTorch" in text and "over 1 seed" in text
