@@ -145,6 +145,8 @@ class Trainer:
     def __init__(self, optimizer, classification: bool):
         self._opt, self._cls = optimizer, classification
         self._cfg = TapeTrainerConfig()
+        self._metrics = None
+        self.on_epoch = None           # callback(EpochStats); `attach_dashboard(builder)` sets it
 
     @classmethod
     def classification(cls, optimizer):
@@ -170,6 +172,16 @@ class Trainer:
         self._cfg.seed = s
         return self
 
+    def metrics(self, logger):
+        """A `MetricsLogger` that receives the per-epoch training summary."""
+        self._metrics = logger
+        return self
+
+    def epoch_callback(self, fn):
+        self.on_epoch = fn
+        return self
+
     def fit(self, backend, model, data) -> TrainingReport:
-        tr = TapeTrainer(self._cfg, self._opt, backend)
+        tr = TapeTrainer(self._cfg, self._opt, backend, self._metrics)
+        tr.on_epoch = self.on_epoch
         return tr.fit_classification(model, data) if self._cls else tr.fit(model, data)

@@ -23,11 +23,15 @@ class TuiHook:
             self.thread = run_dashboard(self.dashboard, refresh_s, file, self.stop_event) if start_thread else None
 
     def on_epoch(self, stats) -> None:
-        """`stats` has epoch / train_loss (and optionally val_loss, samples_per_s): what TapeTrainer reports."""
-        loss = getattr(stats, "train_loss", getattr(stats, "loss", 0.0))
+        """`stats` is what a trainer reports per epoch: the tape trainers' `EpochStats` (epoch, examples, mean_loss,
+        elapsed, accuracy) or any object with `train_loss` / `loss` and `samples_per_s` / `examples_per_sec`."""
+        loss = next((getattr(stats, k) for k in ("mean_loss", "train_loss", "loss") if getattr(stats, k, None) is not None), 0.0)
+        rate = next((getattr(stats, k) for k in ("samples_per_s", "examples_per_sec") if getattr(stats, k, None)), None)
+        if rate is None:
+            n, dt = getattr(stats, "examples", None), getattr(stats, "elapsed", None)
+            rate = n / dt if n and dt else 0.0
         snap = EpochSnapshot(epoch=int(getattr(stats, "epoch", 0)), loss=float(loss),
-                             accuracy=getattr(stats, "accuracy", None),
-                             examples_per_sec=float(getattr(stats, "samples_per_s", getattr(stats, "examples_per_sec", 0.0)) or 0.0))
+                             accuracy=getattr(stats, "accuracy", None), examples_per_sec=float(rate))
         snap.push_to_dashboard(self.dashboard)
         if torch.cuda.is_available():
             free, total = torch.cuda.mem_get_info()
