@@ -28,8 +28,13 @@ class CacheQuantization(enum.Enum):
         return {"fp32": 4, "fp16": 2, "bf16": 2, "fp8": 1, "int8": 1}[self.value]
 
     def torch_dtype(self):
-        return {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16, "fp8": torch.int8,
+        return {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn,
                 "int8": torch.int8}[self.value]
+
+    @property
+    def scaled(self) -> bool:
+        """8-bit formats are stored with one scale per tensor (absmax / 127 for int8, absmax / 448 for e4m3)."""
+        return self in (CacheQuantization.FP8, CacheQuantization.INT8)
 
 
 @dataclass
@@ -86,31 +91,37 @@ class KVCache:
         n = k_new.shape[2]
         if self.len + n > self.config.max_seq_len:
             raise InvalidArgument(f"KV cache overflow: {self.len} + {n} > {self.config.max_seq_len}")
-        if self.k.dtype == torch.int8:
-            kq, self.k_scale = self._quant(k_new, self.k_scale)
-            vq, self.v_scale = self._quant(v_new, self.v_scale)
-            self.k[:, :, self.len:self.len + n] = kq
-            self.v[:, :, self.len:self.len + n] = vq
-        else:
-            self.k[:, :, self.len:self.len + n] = k_new.to(self.k.dtype)
-            self.v[:, :, self.len:self.len + n] = v_new.to(self.v.dtype)
+        self.k[:, :, self.len:self.len + n] = self._encode(k_new, "k")
+        self.v[:, :, self.len:self.len + n] = self._encode(v_new, "v")
         self.len += n
 
-    def _quant(self, t, scale):
-        """Per-tensor absmax / 127; the scale is fixed by the first append (later values saturate)."""
-        if self.len == 0:
+    def _encode(self, t: torch.Tensor, which: str) -> torch.Tensor:
+        """Values in the storage format.  8-bit formats use one scale per tensor, fixed by the first append after a
+        reset (absmax over that append; later values beyond it saturate)."""
+        q = self.config.quantization
+        if not q.scaled:
+            return t.to(self.k.dtype)
+        top = 127.0 if q is CacheQuantization.INT8 else 448.0
+        name = which + "_scale"
+        if self._empty():
             amax = float(t.abs().max())
-            scale = amax / 127.0 if amax > 0 else 1.0
-        return torch.clamp(torch.round(t.float() / scale), -127, 127).to(torch.int8), scale
+            setattr(self, name, amax / top if amax > 0 else 1.0)
+        x = (t.float() / getattr(self, name)).clamp(-top, top)
+        return torch.round(x).to(torch.int8) if q is CacheQuantization.INT8 else x.to(torch.float8_e4m3fn)
+
+    def _decode(self, t: torch.Tensor, which: str) -> torch.Tensor:
+        if not self.config.quantization.scaled:
+            return t
+        return t.float() * getattr(self, which + "_scale")
+
+    def _empty(self) -> bool:
+        return self.len == 0
 
     def get(self):
         return self.get_range(0, self.len)
 
     def get_range(self, start: int, end: int):
-        k, v = self.k[:, :, start:end], self.v[:, :, start:end]
-        if self.k.dtype == torch.int8:
-            return k.float() * self.k_scale, v.float() * self.v_scale
-        return k, v
+        return self._decode(self.k[:, :, start:end], "k"), self._decode(self.v[:, :, start:end], "v")
 
     def reset(self) -> None:
         self.len = 0
@@ -132,20 +143,27 @@ class SlidingWindowCache(KVCache):
 
     def append(self, k_new, v_new) -> None:
         n = k_new.shape[2]
+        kq, vq = self._encode(k_new, "k"), self._encode(v_new, "v")
         for i in range(n):
             pos = self.total % self.window
-            self.k[:, :, pos] = k_new[:, :, i].to(self.k.dtype)
-            self.v[:, :, pos] = v_new[:, :, i].to(self.v.dtype)
+            self.k[:, :, pos] = kq[:, :, i]
+            self.v[:, :, pos] = vq[:, :, i]
             self.total += 1
         self.len = min(self.total, self.window)
+
+    def _empty(self) -> bool:
+        return self.total == 0
+
+    def reset(self) -> None:
+        self.len = self.total = 0
 
     def get(self):
         """Entries in chronological order."""
         if self.total <= self.window:
-            return self.k[:, :, :self.len], self.v[:, :, :self.len]
+            return self._decode(self.k[:, :, :self.len], "k"), self._decode(self.v[:, :, :self.len], "v")
         start = self.total % self.window
         idx = (torch.arange(self.window, device=self.k.device) + start) % self.window
-        return self.k[:, :, idx], self.v[:, :, idx]
+        return self._decode(self.k[:, :, idx], "k"), self._decode(self.v[:, :, idx], "v")
 
 
 class PagedCache:
