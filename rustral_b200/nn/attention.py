@@ -126,7 +126,8 @@ class SelfAttention(Module, Trainable, Saveable):
             q = ops.rope(q, S, pos_offset=pos_offset, theta=c.rope_theta)
             k = ops.rope(k, S, pos_offset=pos_offset, theta=c.rope_theta)
         with ctx.profile("attention", q.shape):
-            a = scaled_dot_product_attention(q, k, v, mask, c.causal and mask is None)
+            # an additive mask tensor is taken to hold the causal part itself; key-padding lengths only hide keys
+            a = scaled_dot_product_attention(q, k, v, mask, c.causal and (mask is None or isinstance(mask, KeyPaddingMask)))
         a = self._dropout(a.reshape(B, S, c.num_heads * c.head_dim), ctx)
         y = self._proj[3](a, ctx, residual)
         return y.squeeze(0) if squeeze else y
