@@ -232,7 +232,8 @@ class GruCell(RnnCell):
         return self.step(x, h, ctx)
 
     def forward_sequence(self, xs, ctx: ForwardCtx, state=None):
-        """Inference: the input projections of all steps are one GEMM, so a step is one GEMM plus the gate arithmetic.
+        """Inference: the input projections of all steps are one GEMM, so a step is one GEMM plus the gate arithmetic
+        (on the GPU: the fused gate kernel, and from the second call on a CUDA-graph replay of the whole sequence).
         With gradients: the generic loop."""
         needs_grad = torch.is_grad_enabled() and (xs.requires_grad or (ctx is not None and ctx.is_training()))
         if needs_grad:
@@ -241,17 +242,14 @@ class GruCell(RnnCell):
         H = self.hidden_size
         with torch.no_grad():
             h = state if state is not None else self.initial_state(B, ctx, xs)
+            if _native_cell_ok(xs, H) and H % 8 == 0:
+                if T >= 4 and _SEQ_GRAPHS and not torch.cuda.is_current_stream_capturing():
+                    return self._graphed_sequence(xs, h)
+                return self._sequence_body(xs, h.contiguous())
             wx, wh, b = self.wx.tensor.detach(), self.wh.tensor.detach(), self.b.tensor.detach()
             gx_all = ops.linear(xs.reshape(T * B, I).contiguous(), wx, b).view(T, B, 3 * H).float()
             outs = torch.empty((T, B, H), dtype=xs.dtype, device=xs.device)
-            native = _native_cell_ok(xs, H)
-            if native:
-                gx_all = gx_all.to(xs.dtype)
             for t in range(T):
-                if native:
-                    h = _GruGatesFn.apply(gx_all[t], ops.linear(h, wh), h)
-                    outs[t] = h
-                    continue
                 gx, gh = gx_all[t], ops.linear(h, wh).float()
                 r = torch.sigmoid(gx[:, :H] + gh[:, :H])
                 z = torch.sigmoid(gx[:, H:2 * H] + gh[:, H:2 * H])
@@ -259,6 +257,44 @@ class GruCell(RnnCell):
                 h = ((1 - z) * n + z * h.float()).to(xs.dtype)
                 outs[t] = h
         return outs, h
+
+    def _sequence_body(self, xs, h):
+        """GPU inference: one input-projection GEMM for all steps, then per step the hidden projection GEMM and the fused
+        gate kernel, which writes the new hidden state straight into the output sequence."""
+        T, B, I = xs.shape
+        H = self.hidden_size
+        lib = N_.kernels()
+        wx, wh, bias = self.wx.tensor.detach(), self.wh.tensor.detach(), self.b.tensor.detach()
+        gx_all = ops.linear(xs.reshape(T * B, I).contiguous(), wx, bias).view(T, B, 3 * H)
+        outs = torch.empty((T, B, H), dtype=xs.dtype, device=xs.device)
+        for t in range(T):
+            gh = ops.linear(h, wh)
+            N_.check(lib.rb_gru_gates_fwd(gx_all[t].data_ptr(), gx_all[t].stride(0), gh.data_ptr(), gh.stride(0), h.data_ptr(),
+                                          outs[t].data_ptr(), B, H, N_.stream_ptr()), "rb_gru_gates_fwd")
+            h = outs[t]
+        return outs, h
+
+    def _graphed_sequence(self, xs, h0):
+        """Same scheme as the LSTM's: eager on first use, captured on the second call with the same shapes and weights,
+        replayed afterwards (`RUSTRAL_RNN_GRAPHS=0` turns it off)."""
+        key = (tuple(xs.shape), xs.device.index, self.wx.tensor.data_ptr(), self.wh.tensor.data_ptr(), self.b.tensor.data_ptr())
+        graphs = self.__dict__.setdefault("_seq_graphs", {})
+        g = graphs.get(key)
+        if g is None:
+            graphs[key] = {"graph": None}
+            return self._sequence_body(xs, h0.contiguous())
+        if g["graph"] is None:
+            g["xs"], g["h0"] = torch.empty_like(xs), torch.empty_like(h0.contiguous())
+            g["xs"].copy_(xs); g["h0"].copy_(h0)
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                g["outs"], g["h"] = self._sequence_body(g["xs"], g["h0"])
+            g["graph"] = graph
+        g["xs"].copy_(xs); g["h0"].copy_(h0)
+        g["graph"].replay()
+        outs = g["outs"].clone()
+        return outs, outs[-1]
 
 
 class StackedLstm(Module, Trainable, Saveable):

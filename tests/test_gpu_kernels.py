@@ -524,3 +524,36 @@ def test_lstm_inference_sequence_matches_fp32_recurrence(T, B, I, H, cuda_status
     got, (hg, cg) = cell.forward_sequence(xs_b, ForwardCtx.inference(be), st)
     want, (hw, cw) = cell._sequence_body(xs_b, st[0].contiguous(), st[1].contiguous().clone())
     assert torch.equal(got, want) and torch.equal(cg, cw) and torch.equal(st[1], _bf((B, H), 18, 0.3).cuda())
+
+
+@pytest.mark.parametrize("T,B,I,H", [(12, 1, 128, 128), (7, 5, 40, 64)])
+def test_gru_inference_sequence_matches_fp32_recurrence_and_replays_from_a_graph(T, B, I, H, cuda_status):
+    """GruCell's GPU inference path (one input-projection GEMM, then per step the hidden projection and the fused gate
+    kernel writing into the output sequence) against the recurrence in fp32 PyTorch; the second call captures a CUDA graph,
+    later calls replay it with new inputs and a new initial state."""
+    from rustral_b200.core import B200Backend, ForwardCtx
+    from rustral_b200.nn import GruCell
+    be = B200Backend()
+    cell = GruCell.new(be, I, H, seed=5)
+    cell.b.tensor.data.copy_(_bf((3 * H,), 8, 0.1).cuda())
+    xs = _bf((T, B, I), 6).cuda()
+    ctx = ForwardCtx.inference(be)
+    outs, h = cell.forward_sequence(xs, ctx)
+    wx, wh, b = cell.wx.tensor.float().cpu(), cell.wh.tensor.float().cpu(), cell.b.tensor.float().cpu()
+    hr, ref = torch.zeros(B, H), []
+    for t in range(T):
+        gx, gh = xs[t].float().cpu() @ wx.t() + b, hr @ wh.t()
+        r, z = torch.sigmoid(gx[:, :H] + gh[:, :H]), torch.sigmoid(gx[:, H:2 * H] + gh[:, H:2 * H])
+        n = torch.tanh(gx[:, 2 * H:] + r * gh[:, 2 * H:])
+        hr = (1 - z) * n + z * hr
+        ref.append(hr)
+    ref = torch.stack(ref)
+    assert outs.shape == (T, B, H) and not outs.requires_grad and torch.equal(h, outs[-1])
+    _close(outs, ref, tol=3e-2, what="gru outputs")
+    outs2, _ = cell.forward_sequence(xs, ctx)                 # captures
+    outs3, h3 = cell.forward_sequence(xs, ctx)                # replays
+    assert torch.equal(outs2, outs) and torch.equal(outs3, outs) and torch.equal(h3, h)
+    xs_b, h0 = _bf((T, B, I), 16).cuda(), _bf((B, H), 17, 0.3).cuda()
+    got, hg = cell.forward_sequence(xs_b, ctx, h0)
+    want, hw = cell._sequence_body(xs_b, h0.contiguous())
+    assert torch.equal(got, want) and torch.equal(hg, hw) and torch.equal(h0, _bf((B, H), 17, 0.3).cuda())
