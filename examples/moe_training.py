@@ -43,7 +43,7 @@ def main(argv=None):
     dev, dt = backend.device(), backend.dtype
     x, y = clusters(2048, a.seed)
     x, y = x.to(dev, dt), y.to(dev)
-    net, opt, ce = MoEClassifier(backend, 32, a.experts, 4, a.seed), Adam(lr=3e-3), CrossEntropyLoss()
+    net, opt, ce = MoEClassifier(backend, 64, a.experts, 4, a.seed), Adam(lr=3e-3), CrossEntropyLoss()
 
     def routing():
         with torch.no_grad():

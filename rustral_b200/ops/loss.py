@@ -75,6 +75,17 @@ class _CrossEntropyFn(torch.autograd.Function):
 def cross_entropy(logits, targets, n_valid: int | None = None, ignore_index: int = -100):
     """Mean cross-entropy over rows whose target is not `ignore_index`; per-row softmax (the eager loss of the
     reference soft-maxes over the whole tensor, crates/nn/src/loss.rs:95, which is only right for one row)."""
+    if logits.is_cuda and logits.dtype == torch.float32:
+        # fp32 logits on the GPU (a head evaluated in full precision): the row log-softmax kernel with its exact
+        # gradient, then the target column of every row; the fused kernel below is the bf16 path
+        l2 = logits.reshape(-1, logits.shape[-1])
+        if n_valid is not None and n_valid < l2.shape[1]:
+            l2 = l2[:, :n_valid]
+        lp = log_softmax(l2.contiguous())
+        t = targets.reshape(-1).to(torch.int64)
+        valid = (t != ignore_index) & (t >= 0) & (t < l2.shape[1])
+        picked = lp.gather(1, torch.where(valid, t, torch.zeros_like(t))[:, None])[:, 0]
+        return -(picked * valid).sum() / valid.sum().clamp_min(1)
     return _CrossEntropyFn.apply(logits, targets, n_valid, ignore_index)
 
 

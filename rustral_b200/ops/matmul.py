@@ -78,6 +78,74 @@ def _gemm_cpu(a, b, a_mn, b_mn, bias, act, residual, aux_in, aux_out, out, out_d
     return out
 
 
+def _round8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+def _row_aligned(t, mult: int = 8) -> bool:
+    """A 2-D operand the kernel can address: 16-byte aligned base, row pitch a multiple of `mult` elements."""
+    return t is None or (t.data_ptr() % 16 == 0 and (t.shape[0] == 1 or t.stride(0) % mult == 0) and t.stride(-1) == 1)
+
+
+def _needs_padding(a, b, bias, residual, aux_in, aux_out, out, out_dtype, n: int) -> bool:
+    """True when a tensor of the call does not meet the kernel's addressing rules (TMA operands and vector stores want
+    16-byte aligned bases and row pitches): layer sizes such as 2 -> 8 or 10 classes."""
+    out_mult = 4 if out_dtype == torch.float32 else 8
+    if out is None:
+        if n % out_mult:
+            return True
+    elif not _row_aligned(out, out_mult):
+        return True
+    if not (_row_aligned(a) and _row_aligned(b) and _row_aligned(residual) and _row_aligned(aux_in) and _row_aligned(aux_out)):
+        return True
+    if (a.shape[0] == 1 and a.shape[1] % 8) or (b.shape[0] == 1 and b.shape[1] % 8):
+        return True
+    return bias is not None and bias.data_ptr() % 16 != 0
+
+
+def _gemm_padded(a, b, *, a_mn, b_mn, bias, act, residual, aux_in, aux_out, out, out_dtype, accumulate, alpha, row_scale,
+                 col_scale, call=None):
+    """The same product with every dimension the kernel addresses by rows rounded up to a multiple of 8: operands are
+    copied into zero-filled buffers, the kernel runs on those, and the live corner of the result is copied back.  Zeros
+    in the contraction add nothing; padded rows and columns of the output are discarded.  This is the path of small or
+    odd layer sizes, where two extra copies do not matter; aligned shapes never come here."""
+    call = call or gemm
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    Nn = b.shape[1] if b_mn else b.shape[0]
+    M8 = _round8(M) if a_mn else M
+    N8 = _round8(Nn)
+    K8 = _round8(K)
+
+    def pad(t, rows, cols):
+        if t is None:
+            return None
+        z = torch.zeros((rows, cols), dtype=t.dtype, device=t.device)
+        z[:t.shape[0], :t.shape[1]] = t
+        return z
+
+    def padv(v, n):
+        if v is None:
+            return None
+        z = torch.zeros(n, dtype=v.dtype, device=v.device)
+        z[:v.numel()] = v.reshape(-1)
+        return z
+    ap = pad(a, K8, M8) if a_mn else pad(a, M8, K8)
+    bp = pad(b, K8, N8) if b_mn else pad(b, N8, K8)
+    outp = torch.zeros((M8, N8), dtype=out_dtype, device=a.device)
+    acc = bool(accumulate and out is not None)
+    if acc:
+        outp[:M, :Nn] = out
+    auxp = torch.zeros((M8, N8), dtype=aux_out.dtype, device=a.device) if aux_out is not None else None
+    call(ap, bp, a_mn=a_mn, b_mn=b_mn, bias=padv(bias, N8), act=act, residual=pad(residual, M8, N8), aux_in=pad(aux_in, M8, N8),
+         aux_out=auxp, out=outp, accumulate=acc, alpha=alpha, row_scale=padv(row_scale, M8), col_scale=padv(col_scale, N8))
+    if aux_out is not None:
+        aux_out.copy_(auxp[:M, :Nn])
+    if out is not None:
+        out.copy_(outp[:M, :Nn])
+        return out
+    return outp[:M, :Nn].contiguous() if (M8 != M or N8 != Nn) else outp
+
+
 _workspaces: dict = {}
 WORKSPACE_BYTES = 128 << 20
 
@@ -148,6 +216,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         raise TypeError("gemm: CUDA operands must be bf16 (accumulation is fp32)")
     if a.stride(1) != 1 or b.stride(1) != 1:
         raise ValueError("gemm: operands must have a contiguous last dimension")
+    # the cheap integer test settles the common aligned call; the full check runs only when it fails or optional tensors exist
+    suspect = (((a.stride(0) | b.stride(0)) & 7) or (Nn & (3 if out_dtype == torch.float32 else 7))
+               or ((a.data_ptr() | b.data_ptr()) & 15) or out is not None or bias is not None or residual is not None
+               or aux_in is not None or aux_out is not None)
+    if suspect and peer is None and _needs_padding(a, b, bias, residual, aux_in, aux_out, out, out_dtype, Nn):
+        return _gemm_padded(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act=act, residual=residual, aux_in=aux_in, aux_out=aux_out,
+                            out=out, out_dtype=out_dtype, accumulate=accumulate, alpha=alpha, row_scale=row_scale,
+                            col_scale=col_scale)
     if out is None:
         out = torch.empty((M, Nn), dtype=out_dtype, device=a.device)
         accumulate = False

@@ -135,3 +135,24 @@ def test_max_pool2d_forward_and_backward(H, W, k, stride, dtype, cuda_status):
     assert torch.allclose(xd.grad.float().cpu(), xr.grad, atol=2e-2 if dtype is torch.bfloat16 else 1e-6)
     if H == W:
         assert torch.equal(global_max_pool2d(x.cuda()).float().cpu(), x.float().amax((2, 3)))
+
+
+@pytest.mark.parametrize("rows,fin,fout", [(4, 2, 8), (33, 18, 96), (33, 96, 2), (64, 256, 10), (5, 12, 1)])
+def test_linear_layers_of_sizes_the_kernel_cannot_address_run_on_padded_copies(rows, fin, fout, cuda_status):
+    """2 -> 8, 18 -> 96, 96 -> 2, 10 classes, a single output: row pitches that are not multiples of 16 bytes.  Forward
+    and all three gradients through `ops.linear` equal the CPU reference on the same bf16-rounded values."""
+    from rustral_b200 import ops
+    g = torch.Generator().manual_seed(rows * 1000 + fin)
+    x = (torch.randn(rows, fin, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(fout, fin, generator=g) * 0.2).to(torch.bfloat16)
+    b = (torch.randn(fout, generator=g) * 0.1).to(torch.bfloat16)
+    res = (torch.randn(rows, fout, generator=g) * 0.1).to(torch.bfloat16)
+    outs = []
+    for dev in ("cpu", "cuda"):
+        xd, wd, bd = (t.detach().clone().to(dev).requires_grad_() for t in (x, w, b))
+        y = ops.linear(xd, wd, bd, "gelu", res.to(dev))
+        assert y.shape == (rows, fout) and y.is_contiguous()
+        y.float().square().sum().backward()
+        outs.append((y.detach().float().cpu(), xd.grad.float().cpu(), wd.grad.float().cpu(), bd.grad.float().cpu()))
+    for name, c, got in zip(("y", "dx", "dw", "db"), *outs):
+        assert_close(got, c, "gemm_act", what=f"{name} of linear {fin}->{fout}")

@@ -154,3 +154,56 @@ def test_trainer_updates_parameters_that_the_model_put_on_the_tape_itself():
     rep = Trainer.classification(Sgd(0.5)).epochs(20).batch_size(4).fit(be, m, data)
     assert not torch.equal(before, m.lin.weight.tensor.detach())
     assert rep.epochs[-1].mean_loss < 0.5 * rep.epochs[0].mean_loss and rep.accuracy == 1.0
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("act", ["none", "gelu", "dgelu"])
+def test_padded_gemm_path_gives_the_same_result_as_the_direct_one(a_mn, b_mn, act):
+    """Layer sizes the kernel cannot address (2 -> 8, 10 classes, 3x3 filters over one channel) run on zero-padded copies;
+    the padding and the copy back are checked here against the direct product, for every operand layout, with bias,
+    residual, saved pre-activation, activation-gradient input, scales and accumulation."""
+    import torch
+    from rustral_b200.ops import matmul as mm
+    g = torch.Generator().manual_seed(3)
+    M, N, K = 5, 10, 3
+    a = torch.randn((K, M) if a_mn else (M, K), generator=g)
+    b = torch.randn((K, N) if b_mn else (N, K), generator=g)
+    bias, res, aux = torch.randn(N, generator=g), torch.randn(M, N, generator=g), torch.randn(M, N, generator=g)
+    rs, cs = torch.rand(M, generator=g) + 0.5, torch.rand(N, generator=g) + 0.5
+    kw = dict(a_mn=a_mn, b_mn=b_mn, bias=bias, act=act, residual=res, aux_in=aux if act == "dgelu" else None, alpha=0.7)
+    seen = {}
+
+    def spy(ap, bp, **k):
+        seen["shapes"] = (tuple(ap.shape), tuple(bp.shape), tuple(k["out"].shape), k["bias"].shape[0])
+        return mm.gemm(ap, bp, **k)
+    for accumulate in (False, True):
+        want_aux = torch.zeros(M, N) if act == "gelu" else None
+        got_aux = torch.zeros(M, N) if act == "gelu" else None
+        out0 = torch.randn(M, N, generator=torch.Generator().manual_seed(9))
+        want = mm.gemm(a, b, **kw, aux_out=want_aux, out=out0.clone(), accumulate=accumulate, row_scale=rs, col_scale=cs)
+        got = mm._gemm_padded(a, b, **kw, aux_out=got_aux, out=out0.clone(), out_dtype=torch.float32, accumulate=accumulate,
+                              row_scale=rs, col_scale=cs, call=spy)
+        assert torch.allclose(got, want, atol=1e-5)
+        if act == "gelu":
+            assert torch.allclose(got_aux, want_aux, atol=1e-5)
+    M8 = 8 if a_mn else 5
+    assert seen["shapes"] == ((8, M8) if a_mn else (5, 8), (8, 16) if b_mn else (16, 8), (M8, 16), 16)
+    fresh = mm._gemm_padded(a, b, **kw, aux_out=None, out=None, out_dtype=torch.float32, accumulate=False, row_scale=None,
+                            col_scale=None)
+    assert fresh.shape == (M, N) and fresh.is_contiguous()
+    assert torch.allclose(fresh, mm.gemm(a, b, **kw), atol=1e-5)
+
+
+def test_alignment_check_flags_exactly_the_shapes_the_kernel_cannot_address():
+    import torch
+    from rustral_b200.ops.matmul import _needs_padding
+    bf = torch.bfloat16
+    ok_a, ok_b = torch.zeros(32, 64, dtype=bf), torch.zeros(48, 64, dtype=bf)
+    assert not _needs_padding(ok_a, ok_b, None, None, None, None, None, bf, 48)
+    assert _needs_padding(torch.zeros(4, 2, dtype=bf), torch.zeros(8, 2, dtype=bf), None, None, None, None, None, bf, 8)     # K = 2
+    assert _needs_padding(ok_a, torch.zeros(10, 64, dtype=bf), None, None, None, None, None, bf, 10)                        # N = 10
+    assert not _needs_padding(ok_a, torch.zeros(12, 64, dtype=bf), None, None, None, None, None, torch.float32, 12)          # fp32 rows of 12 are fine
+    assert _needs_padding(ok_a, ok_b, None, torch.zeros(32, 50, dtype=bf)[:, :48], None, None, None, bf, 48)                # residual pitch 50
+    assert _needs_padding(ok_a[:, 1:], ok_b[:, 1:], None, None, None, None, None, bf, 48)                                   # bases off by 2 bytes
+    assert _needs_padding(ok_a, ok_b, torch.zeros(49, dtype=bf)[1:], None, None, None, None, bf, 48)                        # bias base
+    assert _needs_padding(ok_a, ok_b, None, None, None, None, torch.zeros(32, 52, dtype=bf)[:, :48], bf, 48)               # given output
