@@ -87,18 +87,29 @@ def deserialize(blob: bytes) -> tuple:
         header = json.loads(blob[8:8 + hlen].decode())
     except (UnicodeDecodeError, json.JSONDecodeError) as e:
         raise SafeTensorError(f"corrupt header: {e}") from e
+    if not isinstance(header, dict):
+        raise SafeTensorError("corrupt header: the top level must be an object")
     meta = header.pop("__metadata__", {}) or {}
+    if not isinstance(meta, dict):
+        raise SafeTensorError("corrupt header: __metadata__ must be an object")
     base = 8 + hlen
     out = {}
     for name, info in header.items():
-        dt, shape = info["dtype"], tuple(info["shape"])
-        lo, hi = info["data_offsets"]
+        try:
+            dt, shape = info["dtype"], tuple(info["shape"])
+            lo, hi = info["data_offsets"]
+            ok = isinstance(dt, str) and all(isinstance(d, int) and not isinstance(d, bool) and d >= 0 for d in shape) \
+                and isinstance(lo, int) and isinstance(hi, int)
+        except (KeyError, TypeError, ValueError):
+            ok = False
+        if not ok:
+            raise SafeTensorError(f"{name}: malformed entry (needs dtype, shape, data_offsets)")
         if dt not in _RDT:
             raise DTypeMismatch(f"{name}: unknown dtype {dt}")
         n = 1
         for d in shape:
             n *= d
-        if hi - lo != n * _SIZE[dt] or base + hi > len(blob) or lo < 0:
+        if lo < 0 or hi < lo or hi - lo != n * _SIZE[dt] or base + hi > len(blob):
             raise SafeTensorError(f"{name}: data range does not match shape {shape} of dtype {dt}")
         raw = blob[base + lo:base + hi]
         if dt == "BF16":
