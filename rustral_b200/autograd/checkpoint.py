@@ -54,6 +54,24 @@ class _CheckpointFn(torch.autograd.Function):
         return (None, None, *res)
 
 
+class CheckpointedSegment:
+    """A segment of the forward pass kept as (input, function) instead of its activations
+    (crates/autodiff/src/checkpoint.rs:64-93): `recompute(ctx)` runs the function on the saved input again, which is what
+    the backward pass of `checkpoint_segment` does internally.  `input_id` / `output_id` are the tape ids when the
+    segment was recorded on a tape, else None."""
+
+    def __init__(self, input_value: torch.Tensor, forward_fn, input_id=None, output_id=None):
+        self.input_value = input_value.detach()
+        self.forward_fn = forward_fn
+        self.input_id, self.output_id = input_id, output_id
+
+    def recompute(self, ctx=None) -> torch.Tensor:
+        return self.forward_fn(self.input_value, ctx) if ctx is not None else self.forward_fn(self.input_value)
+
+    def saved_bytes(self) -> int:
+        return self.input_value.numel() * self.input_value.element_size()
+
+
 def checkpoint_segment(fn, *inputs, parameters=()):
     """Runs `fn(*inputs)` keeping only `inputs`; activations inside are recomputed in the backward pass.  Parameters used
     inside `fn` must be listed in `parameters` (their tensors) so that they receive gradients."""

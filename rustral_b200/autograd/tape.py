@@ -201,6 +201,13 @@ class GradExt:
         return None if tid is None else grads.get(tid)
 
 
+class GradExtFromStore:
+    """The store-based half of `GradExt` under its own name (crates/autodiff/src/lib.rs:1293-1310): look a parameter's
+    gradient up in a `GradientStore` through a parameter map, without the tape at hand."""
+
+    gradient_from_store = staticmethod(GradExt.gradient_from_store)
+
+
 class TapeModule:
     """Mixin: `forward_tape(input_id, tape, ctx) -> TensorId` in terms of a module's ordinary differentiable forward."""
 

@@ -98,6 +98,17 @@ class GpuProfiler:
             s["mean_us"] = s["total_us"] / s["count"]
         return out
 
+    def profile_summary(self) -> "ProfileSummary":
+        """Totals per category (crates/wgpu-backend/src/profiler.rs:196-216); `summary()` above is per event name."""
+        self.resolve()
+        cats: dict = {}
+        for e in self.events:
+            t, n = cats.get(e.category, (0.0, 0))
+            cats[e.category] = (t + e.duration_us, n + 1)
+        peak = max((m.allocated_bytes for m in self.memory_events), default=0)
+        cur = self.memory_events[-1].allocated_bytes if self.memory_events else 0
+        return ProfileSummary(len(self.events) + len(self._pending), len(self.events), peak, cur, cats)
+
     def export_chrome_trace(self, path: str | None = None) -> str:
         self.resolve()
         trace = [{"name": e.name, "cat": e.category, "ph": "X", "ts": e.start_us, "dur": e.duration_us, "pid": 0,
@@ -113,6 +124,15 @@ class GpuProfiler:
 
     def clear(self) -> None:
         self.events, self.memory_events, self._pending = [], [], []
+
+
+@dataclass
+class ProfileSummary:
+    total_events: int
+    completed_events: int
+    total_memory_allocated: int          # peak of the recorded memory samples
+    current_memory: int
+    category_times: dict                 # category -> (total microseconds, count)
 
 
 def export_chrome_trace(profiler: GpuProfiler, path: str | None = None) -> str:

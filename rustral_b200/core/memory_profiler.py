@@ -2,6 +2,7 @@
 (crates/core/src/memory_profiler.rs:52-393).  On CUDA, `sample_device()` also records the allocator's counters."""
 from __future__ import annotations
 
+import enum
 import json
 import time
 from dataclasses import dataclass, field
@@ -22,6 +23,45 @@ class OOMRisk:
     LOW, MEDIUM, HIGH, CRITICAL = "low", "medium", "high", "critical"
 
 
+class OomRisk(enum.Enum):
+    """The four risk levels as an enumeration (crates/core/src/memory_profiler.rs:345-362); `predict_oom_risk` returns the
+    plain strings, `OomRisk(value)` turns one into a member."""
+    LOW = "low"
+    MEDIUM = "medium"
+    HIGH = "high"
+    CRITICAL = "critical"
+
+    def as_str(self) -> str:
+        return self.value
+
+
+@dataclass
+class MemorySnapshot:
+    """State of the profiler at one moment (crates/core/src/memory_profiler.rs:43-50).  Also answers the dictionary keys
+    `label`, `t`, `current`, `peak`, `by_tag`."""
+    timestamp: float
+    total_allocated: int
+    peak_allocated: int
+    num_allocations: int
+    by_tag: dict
+    label: str = ""
+
+    def __getitem__(self, key):
+        return {"label": self.label, "t": self.timestamp, "current": self.total_allocated, "peak": self.peak_allocated,
+                "by_tag": self.by_tag, "num_allocations": self.num_allocations}[key]
+
+
+@dataclass
+class MemorySummary:
+    """Totals since the profiler was created (crates/core/src/memory_profiler.rs:325-336, 365-372)."""
+    current_bytes: int
+    peak_bytes: int
+    total_allocations: int
+    total_deallocations: int
+    active_count: int
+    duration: float
+
+
 class MemoryProfiler:
     def __init__(self, capacity_bytes: int | None = None):
         self.events: list = []
@@ -34,6 +74,7 @@ class MemoryProfiler:
             capacity_bytes = torch.cuda.get_device_properties(0).total_memory
         self.capacity_bytes = capacity_bytes or (1 << 62)
         self.snapshots: list = []
+        self._t0 = time.time()
 
     def alloc(self, tag: str, nbytes: int) -> int:
         h = self._next
@@ -66,9 +107,20 @@ class MemoryProfiler:
         return n
 
     def snapshot(self, label: str = "") -> dict:
-        s = {"label": label, "t": time.time(), "current": self.current, "peak": self.peak, "by_tag": dict(self.by_tag)}
+        s = MemorySnapshot(time.time(), self.current, self.peak, len(self.active), dict(self.by_tag), label)
         self.snapshots.append(s)
         return s
+
+    def summary(self) -> MemorySummary:
+        allocs = sum(1 for e in self.events if e.kind == "alloc")
+        frees = sum(1 for e in self.events if e.kind == "free")
+        return MemorySummary(self.current, self.peak, allocs, frees, allocs - frees, time.time() - self._t0)
+
+    def reset(self) -> None:
+        """Forgets events, live allocations and peaks; the clock of `summary().duration` restarts."""
+        self.events.clear(); self.active.clear(); self.by_tag.clear(); self.snapshots.clear()
+        self.current = self.peak = 0
+        self._t0 = time.time()
 
     def predict_oom_risk(self, planned_bytes: int = 0) -> str:
         """< 0.5 low, < 0.75 medium, < 0.9 high, else critical (fraction of capacity after the planned allocation)."""

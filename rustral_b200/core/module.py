@@ -66,7 +66,14 @@ class NamedParameters:
 
 class Trainable(NamedParameters):
     def parameters(self) -> list:
-        return [p for _, p in self.named_parameters()]
+        """Every parameter once, in first-appearance order.  A parameter shared by two sub-modules (tied embeddings, one
+        layer used twice) has two names in `named_parameters()` but is one entry here, so that an optimizer steps it once."""
+        seen, out = set(), []
+        for _, p in self.named_parameters():
+            if id(p) not in seen:
+                seen.add(id(p))
+                out.append(p)
+        return out
 
     def num_parameters(self) -> int:
         return sum(p.numel() for p in self.parameters())

@@ -49,9 +49,51 @@ class ValidationReport:
     has_nan: bool
 
 
+@dataclass
+class ValidationResult:
+    """The comparison outcome under the reference's field names (crates/core/src/numerics.rs:228-275)."""
+    passed: bool
+    max_abs_diff: float
+    max_rel_diff: float
+    num_violations: int
+    total_elements: int
+
+    def violation_rate(self) -> float:
+        """Share of elements outside the tolerance, in per cent."""
+        return 100.0 * self.num_violations / self.total_elements if self.total_elements else 0.0
+
+
+class NumericsError(AssertionError):
+    """Raised by `NumericsValidator.check`: a tolerance was exceeded, a length differed or a NaN appeared
+    (crates/core/src/numerics.rs:181-212).  `kind` is "tolerance_exceeded", "length_mismatch" or "nan"."""
+
+    def __init__(self, kind: str, message: str, result: "ValidationResult | None" = None):
+        super().__init__(message)
+        self.kind, self.result = kind, result
+
+
 class NumericsValidator:
     def __init__(self, config: NumericsConfig | None = None):
         self.config = config or NumericsConfig()
+
+    def validate(self, actual, expected, dtype: DType = DType.F32) -> ValidationResult:
+        r = self.validate_arrays(actual, expected, dtype)
+        return ValidationResult(r.ok, r.max_abs_err, r.max_rel_err, r.violations, r.total)
+
+    def check(self, actual, expected, dtype: DType = DType.F32, what: str = "") -> ValidationResult:
+        """`validate`, raising `NumericsError` instead of returning a failed result."""
+        a, e = torch.as_tensor(actual), torch.as_tensor(expected)
+        if a.numel() != e.numel():
+            raise NumericsError("length_mismatch", f"{what}: {a.numel()} elements against {e.numel()}")
+        rep = self.validate_arrays(a, e, dtype)
+        res = ValidationResult(rep.ok, rep.max_abs_err, rep.max_rel_err, rep.violations, rep.total)
+        if rep.has_nan:
+            raise NumericsError("nan", f"{what}: NaN in the values under test", res)
+        if not rep.ok:
+            tol = self.config.for_dtype(dtype)
+            raise NumericsError("tolerance_exceeded", f"{what}: {rep.violations} of {rep.total} elements beyond rtol {tol.rtol:g} / atol "
+                                f"{tol.atol:g} for {dtype.value} (max |diff| {rep.max_abs_err:.3g})", res)
+        return res
 
     def validate_arrays(self, actual, expected, dtype: DType = DType.F32) -> ValidationReport:
         a = torch.as_tensor(actual).double().flatten()

@@ -70,10 +70,83 @@ class OperationStats:
                 "shape_buckets": dict(self.shape_buckets)}
 
 
+class MatmulDim(enum.Enum):
+    """Size class of one GEMM dimension: Tiny < 256, Small <= 512, Medium < 2048, Large < 8192, XLarge
+    (crates/core/src/operation_profiler.rs:123-146)."""
+    TINY = "tiny"
+    SMALL = "small"
+    MEDIUM = "medium"
+    LARGE = "large"
+    XLARGE = "xlarge"
+
+    @classmethod
+    def from_size(cls, size: int) -> "MatmulDim":
+        return cls.TINY if size < 256 else cls.SMALL if size <= 512 else cls.MEDIUM if size < 2048 else \
+            cls.LARGE if size < 8192 else cls.XLARGE
+
+
+@dataclass(frozen=True)
+class ShapeBucket:
+    """Coarse class of a tensor shape for aggregating timings (crates/core/src/operation_profiler.rs:108-184): Small / Medium
+    / Large / XLarge by the largest dimension (< 512, < 2048, < 8192), or a matmul bucket of three `MatmulDim`s.
+    `shape_bucket()` above is the finer power-of-two key the profiler records by default."""
+    kind: str                       # "small" | "medium" | "large" | "xlarge" | "matmul"
+    m: MatmulDim | None = None
+    n: MatmulDim | None = None
+    k: MatmulDim | None = None
+
+    @classmethod
+    def from_dims(cls, dims) -> "ShapeBucket":
+        mx = max((int(d) for d in dims), default=0)
+        return cls("small" if mx < 512 else "medium" if mx < 2048 else "large" if mx < 8192 else "xlarge")
+
+    @classmethod
+    def from_matmul_dims(cls, m: int, n: int, k: int) -> "ShapeBucket":
+        return cls("matmul", MatmulDim.from_size(m), MatmulDim.from_size(n), MatmulDim.from_size(k))
+
+    def __str__(self) -> str:
+        return self.kind if self.kind != "matmul" else f"matmul[{self.m.value},{self.n.value},{self.k.value}]"
+
+
+@dataclass
+class ProfilingHooks:
+    """Which measurements a profiler takes (crates/core/src/operation_profiler.rs:45-75).  `OperationProfiler.with_hooks`
+    applies them: without `per_op_timing` guards record nothing, without `cpu_gpu_breakdown` everything is timed on the
+    host clock, without `shape_bucket_recording` all calls of an operation share one bucket."""
+    cpu_gpu_breakdown: bool = True
+    per_op_timing: bool = True
+    memory_tracking: bool = False
+    shape_bucket_recording: bool = True
+
+    @classmethod
+    def all(cls) -> "ProfilingHooks":
+        return cls(True, True, True, True)
+
+    @classmethod
+    def none(cls) -> "ProfilingHooks":
+        return cls(False, False, False, False)
+
+
+@dataclass
+class SnapshotOp:
+    """One row of a profiler snapshot (crates/core/src/operation_profiler.rs:341-347)."""
+    name: str
+    count: int
+    avg_ms: float
+    max_ms: float
+    device_type: str
+
+
 @dataclass
 class ProfilerSnapshot:
     ops: dict
     total_ms: float
+
+    def rows(self) -> list:
+        """The operations as `SnapshotOp` rows, most expensive first."""
+        out = [SnapshotOp(n, int(d.get("count", 0)), float(d.get("mean_ms", d.get("total_ms", 0.0) / max(1, d.get("count", 1)))),
+                          float(d.get("max_ms", 0.0)), str(d.get("device_type", "cpu"))) for n, d in self.ops.items()]
+        return sorted(out, key=lambda r: -r.avg_ms * r.count)
 
     def to_json(self) -> str:
         return json.dumps({"total_ms": self.total_ms, "ops": self.ops}, indent=2, sort_keys=True)
@@ -125,6 +198,13 @@ class OperationProfiler:
         self.max_pending = max_pending
         self.stats: dict = {}
         self._pending: list = []
+        self.hooks = ProfilingHooks()
+
+    def with_hooks(self, hooks: ProfilingHooks) -> "OperationProfiler":
+        self.hooks = hooks
+        self.enabled = self.enabled and hooks.per_op_timing
+        self.use_cuda_events = self.use_cuda_events and hooks.cpu_gpu_breakdown
+        return self
 
     @classmethod
     def ci_safe(cls) -> "OperationProfiler":
@@ -137,6 +217,8 @@ class OperationProfiler:
         return OperationGuard(self, name, shape, device)
 
     def record(self, name: str, ms: float, device: DeviceType = DeviceType.CPU, bucket: str = "-") -> None:
+        if not self.hooks.shape_bucket_recording:
+            bucket = "-"
         self.stats.setdefault(name, OperationStats()).record(ms, device, bucket)
 
     def resolve(self) -> None:

@@ -51,3 +51,30 @@ class ShapePolicy(enum.Enum):
 
     def prefers_arena_pool(self) -> bool:
         return self in (ShapePolicy.STATIC, ShapePolicy.DYNAMIC_BOUNDED)
+
+
+class ShapeExt:
+    """Element count of a plain shape sequence (crates/core/src/shape.rs:41-50): `ShapeExt.elem_count((2, 3, 4)) == 24`;
+    the empty shape is a scalar and counts one element."""
+
+    @staticmethod
+    def elem_count(shape) -> int:
+        n = 1
+        for d in shape:
+            n *= int(d)
+        return n
+
+
+class TensorShape:
+    """Anything that can report its shape (crates/core/src/shape.rs:57-60).  `TensorShape.shape_of(x)` reads it from
+    tensors, parameters, arrays and `Shape` objects alike."""
+
+    @staticmethod
+    def shape_of(x) -> tuple:
+        if isinstance(x, Shape):
+            return x.dims
+        t = getattr(x, "tensor", x)
+        shp = getattr(t, "shape", None)
+        if shp is None:
+            raise TypeError(f"{type(x).__name__} has no shape")
+        return tuple(int(d) for d in shp)

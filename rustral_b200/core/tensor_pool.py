@@ -6,6 +6,7 @@ captured into CUDA graphs, where buffers must keep their addresses, and (b) the 
 from __future__ import annotations
 
 import enum
+from dataclasses import dataclass
 
 import torch
 
@@ -66,10 +67,32 @@ class TensorPool:
         self._free.clear()
         self._lent.clear()
 
+    def pool_stats(self) -> "PoolStats":
+        """Contents of the free lists (crates/core/src/tensor_pool.rs:193-236); `stats()` has the hit counters."""
+        n = sum(len(v) for v in self._free.values())
+        nbytes = sum(t.numel() * t.element_size() for v in self._free.values() for t in v)
+        return PoolStats(n, nbytes, sum(1 for v in self._free.values() if v), self.max_per_shape, self.max_total)
+
+    def print_stats(self, file=None) -> None:
+        import sys
+        st, out = self.pool_stats(), file or sys.stdout
+        print("Tensor pool statistics:", file=out)
+        print(f"  total tensors: {st.total_tensors}\n  total memory: {st.total_memory_bytes / 1e6:.2f} MB\n"
+              f"  unique shapes: {st.unique_shapes}\n  max per shape: {st.max_size_per_shape}\n  max total: {st.max_total_tensors}", file=out)
+
     def stats(self) -> dict:
         tot = self.hits + self.misses
         return {"hits": self.hits, "misses": self.misses, "hit_rate": self.hits / tot if tot else 0.0,
                 "free": self.total_free(), "strategy": self.strategy.value}
+
+
+@dataclass
+class PoolStats:
+    total_tensors: int
+    total_memory_bytes: int
+    unique_shapes: int
+    max_size_per_shape: int
+    max_total_tensors: int
 
 
 class PooledTensor:

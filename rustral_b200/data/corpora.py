@@ -55,6 +55,22 @@ def load_sst2(split: str = "train") -> list:
     return out
 
 
+@dataclass
+class WikiText2Splits:
+    """The three splits as text (crates/data/src/datasets/wikitext2.rs:31-35)."""
+    train: str
+    valid: str
+    test: str
+
+    def __iter__(self):
+        return iter((self.train, self.valid, self.test))
+
+
+def load_wikitext2_splits() -> WikiText2Splits:
+    """All three splits at once, each from the cache or fetched like `load_wikitext2(split)`."""
+    return WikiText2Splits(load_wikitext2("train"), load_wikitext2("valid"), load_wikitext2("test"))
+
+
 def load_wikitext2(split: str = "train") -> str:
     name = f"wiki.{split}.tokens"
     path = os.path.join(cache_root(), "datasets", "wikitext-2", name)

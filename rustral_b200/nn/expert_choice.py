@@ -152,6 +152,12 @@ class ExpertChoiceRouter(Module, Trainable, Saveable):
         vals, idx = torch.topk(probs.t(), cap, dim=-1)          # per expert: its highest-affinity tokens
         return idx, vals, probs
 
+    def assignments(self, x) -> "ExpertAssignments":
+        """The routing decision for `x` as explicit (token, expert, weight) records."""
+        x2 = x.reshape(-1, self.config.d_model)
+        idx, gate, _ = self.select(x2)
+        return ExpertAssignments.from_selection(idx, gate, x2.shape[0])
+
     def _forward_native(self, x, x2, expert_fn):
         """bf16 CUDA tensors: selection, row gather, combine and their backward passes are the kernels of
         csrc/kernels/expert_choice.cu; the experts see one contiguous [capacity, d] block each."""
@@ -194,6 +200,37 @@ class ExpertChoiceRouter(Module, Trainable, Saveable):
         per = [int(idx.shape[1])] * c.num_experts
         self.last_stats = ExpertChoiceStats(min(per), max(per), sum(per) / len(per), 1.0, int((served == 0).sum()))
         return out.to(x.dtype).reshape(x.shape)
+
+
+@dataclass
+class TokenAssignment:
+    token_idx: int
+    expert_idx: int
+    weight: float
+
+
+@dataclass
+class ExpertAssignments:
+    """Who serves whom after expert-choice routing (crates/nn/src/expert_choice.rs:359-372): `assignments[e]` lists the
+    tokens expert `e` took with their gate weights."""
+    assignments: list
+    num_tokens: int
+
+    @classmethod
+    def from_selection(cls, idx: torch.Tensor, gate: torch.Tensor, num_tokens: int) -> "ExpertAssignments":
+        """`idx` / `gate`: [experts, capacity] as returned by `ExpertChoiceRouter.select`."""
+        rows = [[TokenAssignment(int(t), e, float(w)) for t, w in zip(idx[e].tolist(), gate[e].tolist())] for e in range(idx.shape[0])]
+        return cls(rows, num_tokens)
+
+    def tokens_of(self, expert: int) -> list:
+        return [a.token_idx for a in self.assignments[expert]]
+
+    def experts_of(self, token: int) -> list:
+        return [a.expert_idx for row in self.assignments for a in row if a.token_idx == token]
+
+    def unrouted_tokens(self) -> list:
+        seen = {a.token_idx for row in self.assignments for a in row}
+        return [t for t in range(self.num_tokens) if t not in seen]
 
 
 @dataclass

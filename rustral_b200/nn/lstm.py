@@ -87,6 +87,40 @@ class LstmConfig:
     hidden_size: int
 
 
+GruConfig = LstmConfig          # a GRU cell is configured by the same two sizes (crates/nn/src/lstm.rs:218-223)
+
+
+class LstmState(tuple):
+    """(hidden, cell) of an LSTM: what `LstmCell.step` returns and takes, with the reference's field names
+    (crates/nn/src/lstm.rs:33-38).  It is a plain 2-tuple, so `h, c = state` keeps working."""
+
+    def __new__(cls, hidden, cell):
+        return super().__new__(cls, (hidden, cell))
+
+    @property
+    def hidden(self):
+        return self[0]
+
+    @property
+    def cell(self):
+        return self[1]
+
+
+@dataclass
+class GruState:
+    """The hidden state of a GRU under the reference's name (crates/nn/src/lstm.rs:227-230); `GruCell` itself passes the
+    bare tensor, `GruState(h).hidden` wraps and unwraps it."""
+    hidden: torch.Tensor
+
+
+@dataclass
+class BidirectionalOutput:
+    """Both directions of a bidirectional pass, time-aligned, and their concatenation (crates/nn/src/lstm.rs:417-424)."""
+    forward: torch.Tensor
+    backward: torch.Tensor
+    concatenated: torch.Tensor
+
+
 class RnnCell(Module, Trainable, Saveable, StatefulModule):
     hidden_size: int
 
@@ -328,6 +362,13 @@ class BidirectionalRnn(Module, Trainable, Saveable):
         return torch.cat([of, torch.flip(ob, (0,))], -1), (sf, sb)
 
     forward = forward_sequence
+
+    def forward_directions(self, xs, ctx: ForwardCtx) -> BidirectionalOutput:
+        """The same pass with the two directions kept apart (the backward one re-aligned to the input's time order)."""
+        of, _ = self.fwd.forward_sequence(xs, ctx)
+        ob, _ = self.bwd.forward_sequence(torch.flip(xs, (0,)), ctx)
+        ob = torch.flip(ob, (0,))
+        return BidirectionalOutput(of, ob, torch.cat([of, ob], -1))
 
     def final_hidden(self, xs, ctx: ForwardCtx):
         _, (sf, sb) = self.forward_sequence(xs, ctx)

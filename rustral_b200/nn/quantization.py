@@ -100,6 +100,10 @@ class QuantizedLinear(Module):
     def is_fp8(self) -> bool:
         return self.scheme in (QuantizationScheme.FP8_E4M3, QuantizationScheme.FP8_E5M2)
 
+    def stored_bytes(self) -> int:
+        """Bytes of the quantised weight as stored: payload, scales, zero points (the bias is not part of it)."""
+        return sum(t.numel() * t.element_size() for t in (self.qweight, self.params.scale, self.params.zero_point))
+
     def dequantized_weight(self):
         if self.is_fp8:
             fdt = torch.float8_e4m3fn if self.scheme is QuantizationScheme.FP8_E4M3 else torch.float8_e5m2
@@ -155,6 +159,9 @@ class GPTQLinear(Module):
         return cls(packed, scales.squeeze(-1), (out, inn), group_size,
                    None if linear.bias is None else linear.bias.tensor.detach(), linear.weight.tensor.dtype)
 
+    def stored_bytes(self) -> int:
+        return self.packed.numel() * self.packed.element_size() + self.scales.numel() * self.scales.element_size()
+
     def dequantized_weight(self):
         out, inn = self.shape
         q = torch.empty((out, inn), dtype=torch.uint8, device=self.packed.device)
@@ -199,6 +206,46 @@ class QATTrainer:
         scale = (t.detach().abs().amax() / qmax).clamp_min(1e-12)
         q = torch.clamp(torch.round(t / scale), -qmax - 1, qmax) * scale
         return t + (q - t).detach()
+
+
+@dataclass
+class QuantizationStats:
+    """Size of a model's linear weights before and after quantisation (crates/nn/src/quantization.rs:499-506)."""
+    original_size_mb: float
+    quantized_size_mb: float
+    compression_ratio: float
+    layers_quantized: int
+    scheme: QuantizationScheme
+
+
+def quantize_model_with_stats(model, scheme: QuantizationScheme = QuantizationScheme.INT8, group_size: int = 128) -> QuantizationStats:
+    """`quantize_model` plus the accounting: fp32 bytes of every replaced weight against the stored bytes of its
+    quantised form (payload, scales and zero points)."""
+    from .linear import Linear
+    before = {}
+
+    def walk(m):
+        for v in vars(m).values():
+            for e in (v if isinstance(v, list) else [v]):
+                if isinstance(e, Linear):
+                    before[id(e)] = e.weight.tensor.numel() * 4
+                elif hasattr(e, "__dict__") and hasattr(e, "named_parameters"):
+                    walk(e)
+    walk(model)
+    n = quantize_model(model, scheme, group_size)
+    after = 0
+
+    def walk_q(m):
+        nonlocal after
+        for v in vars(m).values():
+            for e in (v if isinstance(v, list) else [v]):
+                if isinstance(e, (QuantizedLinear, GPTQLinear)):
+                    after += e.stored_bytes()
+                elif hasattr(e, "__dict__") and hasattr(e, "named_parameters"):
+                    walk_q(e)
+    walk_q(model)
+    orig = sum(before.values())
+    return QuantizationStats(orig / 2 ** 20, after / 2 ** 20, orig / after if after else 0.0, n, scheme)
 
 
 def quantize_model(model, scheme: QuantizationScheme = QuantizationScheme.INT8, group_size: int = 128):

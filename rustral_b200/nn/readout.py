@@ -1,12 +1,39 @@
 """Label heads (crates/nn/src/readout.rs:16-46, multi_readout.rs:11-131)."""
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import torch
 
 from .. import ops
 from ..core import ForwardCtx, Module, Saveable, Trainable
 from ..symbolic import LabelPrediction, Vocabulary
 from .linear import LinearBuilder
+
+
+@dataclass
+class ReadoutConfig:
+    """crates/nn/src/readout.rs:11-17."""
+    hidden_dim: int
+    labels: int
+
+
+@dataclass
+class BinaryPrediction:
+    """crates/nn/src/multi_readout.rs:115-122."""
+    logit: float
+    probability: float
+    predicted: bool
+
+
+@dataclass
+class LabelBinaryPrediction:
+    """One label's decision in a multi-label prediction (crates/nn/src/multi_readout.rs:23-34)."""
+    label: str
+    id: int
+    logit: float
+    probability: float
+    predicted: bool
 
 
 class Readout(Module, Trainable, Saveable):
@@ -56,6 +83,13 @@ class MultiReadout(Module, Trainable, Saveable):
         return [[LabelPrediction(self._labels[j], j, float(row[j])) for j in range(len(self._labels)) if row[j] >= self.threshold]
                 for row in s]
 
+    def predict_all(self, x, ctx: ForwardCtx) -> list:
+        """Every label's logit, probability and decision for every row (the reference's `predict_with_details`)."""
+        logits = torch.cat([h(x, ctx) for h in self.heads], -1).float().detach().cpu()
+        probs = torch.sigmoid(logits)
+        return [[LabelBinaryPrediction(self._labels[j], j, float(lr[j]), float(pr[j]), bool(pr[j] >= self.threshold))
+                 for j in range(len(self._labels))] for lr, pr in zip(logits, probs)]
+
     def top_k(self, x, ctx: ForwardCtx, k: int) -> list:
         s = self.forward(x, ctx).detach().cpu()
         out = []
@@ -79,3 +113,7 @@ class BinaryReadout(Module, Trainable, Saveable):
 
     def predict(self, x, ctx: ForwardCtx) -> list:
         return [bool(v >= self.threshold) for v in self.forward(x, ctx).detach().cpu().reshape(-1)]
+
+    def predict_detailed(self, x, ctx: ForwardCtx) -> list:
+        logits = self.projection(x, ctx).float().detach().cpu().reshape(-1)
+        return [BinaryPrediction(float(l), float(torch.sigmoid(l)), bool(torch.sigmoid(l) >= self.threshold)) for l in logits]

@@ -86,6 +86,17 @@ class SharedExpertLayer(Module, Trainable, Saveable):
             y = y + x2
         return self.output_proj(y, ctx).reshape(x.shape)
 
+    def routing(self, x) -> "HybridRouting":
+        """The gates of `x` spelled out (crates/nn/src/shared_expert.rs:122-127): every token passes through the shared
+        experts with weight `shared_weight`; `routed_gates` is the router's softmax over the routed experts and
+        `top_k_indices` / `top_k_weights` what was kept of it."""
+        c = self.config
+        x2 = x.reshape(-1, c.d_model).contiguous()
+        logits = ops.gemm(x2, self.router.tensor, out_dtype=torch.float32)
+        idx, w, probs = moe_ops.route(logits, c.top_k, c.renormalize)
+        return HybridRouting(torch.full((x2.shape[0],), float(c.shared_weight)), probs.detach().float().cpu(),
+                             idx.detach().long().cpu(), (w.detach().float() * c.routed_weight).cpu())
+
     def stats(self, x) -> SharedExpertStats:
         c = self.config
         logits = ops.gemm(x.reshape(-1, c.d_model).contiguous(), self.router.tensor, out_dtype=torch.float32)
@@ -93,6 +104,14 @@ class SharedExpertLayer(Module, Trainable, Saveable):
         counts = torch.bincount(idx.reshape(-1).long().cpu(), minlength=c.num_routed).tolist()
         mx = max(counts) or 1
         return SharedExpertStats(counts, (sum(counts) / len(counts)) / mx)
+
+
+@dataclass
+class HybridRouting:
+    shared_gate: torch.Tensor        # [tokens]
+    routed_gates: torch.Tensor       # [tokens, num_routed]
+    top_k_indices: torch.Tensor      # [tokens, top_k]
+    top_k_weights: torch.Tensor      # [tokens, top_k]
 
 
 @dataclass

@@ -195,9 +195,37 @@ class TransformerDecoder(Module, Trainable, Saveable):
         return int(ops.argmax_rows(logits[0, -1:].contiguous())[0])
 
 
+@dataclass
+class EncoderDecoderConfig:
+    """Configurations of both halves (crates/nn/src/transformer.rs:963-985).  With `shared_embeddings` and equal
+    vocabularies the decoder uses the encoder's token-embedding parameter (one tensor, listed once under the encoder)."""
+    encoder: TransformerEncoderConfig
+    decoder: "TransformerDecoderConfig"
+    shared_embeddings: bool = True
+
+    @classmethod
+    def symmetric(cls, d_model: int, num_heads: int, num_layers: int, ff_dim: int, **kw) -> "EncoderDecoderConfig":
+        return cls(TransformerEncoderConfig(d_model, num_heads, num_layers, ff_dim, **kw),
+                   TransformerDecoderConfig(d_model, num_heads, num_layers, ff_dim, **kw), True)
+
+    def with_shared_embeddings(self, shared: bool) -> "EncoderDecoderConfig":
+        self.shared_embeddings = shared
+        return self
+
+
 class TransformerEncoderDecoder(Module, Trainable, Saveable):
     def __init__(self, encoder: TransformerEncoder, decoder: TransformerDecoder):
         self.encoder, self.decoder = encoder, decoder
+
+    @classmethod
+    def from_config(cls, backend, config: EncoderDecoderConfig, src_vocab: int, tgt_vocab: int, seed: int = 42):
+        enc = TransformerEncoder.new(backend, config.encoder, src_vocab, seed)
+        dec = TransformerDecoder.new(backend, config.decoder, tgt_vocab, seed + 1000, cross_attention=True)
+        model = cls(enc, dec)
+        model.config = config
+        if config.shared_embeddings and src_vocab == tgt_vocab and config.encoder.d_model == config.decoder.d_model:
+            dec.token_embedding = enc.token_embedding          # one Parameter object: gradients of both uses accumulate
+        return model
 
     @classmethod
     def new(cls, backend, config: TransformerEncoderConfig, src_vocab: int, tgt_vocab: int, seed: int = 42):

@@ -89,6 +89,11 @@ class DistributedCheckpointManager:
         self.pg.barrier()
         return d
 
+    def load_shard(self, epoch: int) -> "ShardData":
+        """This rank's tensors and optimizer state of `epoch` as one record."""
+        _, tensors, opt = self.load(epoch)
+        return ShardData(tensors, opt)
+
     def _rotate(self) -> None:
         eps = self.list_checkpoints()
         for e in eps[:-self.keep_last_n] if self.keep_last_n > 0 else []:
@@ -229,6 +234,14 @@ class AsyncCheckpointWriter:
                 self._h = None
         except Exception:       # noqa: BLE001 - interpreter shutdown
             pass
+
+
+@dataclass
+class ShardData:
+    """One rank's part of a sharded checkpoint: its named parameter shards and, optionally, its optimizer state
+    (crates/distributed/src/checkpoint.rs:327-333).  `DistributedCheckpointManager.load_shard(epoch)` returns it."""
+    params: dict
+    optimizer: dict | None = None
 
 
 class ShardedCheckpoint:

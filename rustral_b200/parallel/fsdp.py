@@ -142,10 +142,12 @@ class FSDP:
         self.pg.all_reduce_mean(l, "fsdp_loss")
         return float(l)
 
-    def memory_stats(self) -> dict:
+    def memory_stats(self) -> "FSDPMemoryStats":
         shard_bytes = sum(sp.shard.numel() * 4 for sp in self.sharded)
         full_bytes = sum(sp.numel * 4 for sp in self.sharded)
-        return {"shard_bytes": shard_bytes, "full_bytes": full_bytes, "savings": 1.0 - shard_bytes / max(1, full_bytes)}
+        gathered = sum(1 for _, p in self.named if p.tensor.numel() > 0) if hasattr(self, "named") else 0
+        return FSDPMemoryStats(self.pg.world_size, sum(sp.numel for sp in self.sharded), sum(sp.shard.numel() for sp in self.sharded),
+                               (1.0 - shard_bytes / max(1, full_bytes)) * 100.0, gathered, shard_bytes, full_bytes)
 
     # ---- checkpoints -----------------------------------------------------------------------------------------------------
     def save_checkpoint(self) -> "FSDPCheckpoint":
@@ -157,6 +159,22 @@ class FSDP:
             raise RankMismatch("FSDP checkpoint belongs to another rank / world size")
         for sp in self.sharded:
             sp.shard.copy_(ck.shards[sp.name].to(sp.shard.device))
+
+
+@dataclass
+class FSDPMemoryStats:
+    """crates/distributed/src/fsdp.rs:389-425, plus the byte counts.  Also answers the dictionary keys `shard_bytes`,
+    `full_bytes` and `savings`."""
+    world_size: int
+    total_parameters: int
+    local_parameters: int
+    memory_reduction_percent: float
+    gathered_params: int
+    shard_bytes: int = 0
+    full_bytes: int = 0
+
+    def __getitem__(self, key):
+        return {"shard_bytes": self.shard_bytes, "full_bytes": self.full_bytes, "savings": self.memory_reduction_percent / 100.0}[key]
 
 
 @dataclass

@@ -190,9 +190,31 @@ class PipelineParallel:
             torch.cuda.current_stream().wait_stream(self._comm_stream)
         return torch.stack(losses).sum() if losses else None
 
-    def pipeline_stats(self) -> dict:
-        return {"bubble_fraction": pipeline_bubble_fraction(self.cfg.schedule, self.stage.num_stages, self.cfg.num_micro_batches),
-                "num_stages": self.stage.num_stages, "num_micro_batches": self.cfg.num_micro_batches}
+    def pipeline_stats(self) -> "PipelineStats":
+        bubble = pipeline_bubble_fraction(self.cfg.schedule, self.stage.num_stages, self.cfg.num_micro_batches)
+        return PipelineStats(self.stage.num_stages, self.cfg.num_micro_batches, self.cfg.schedule.name, bubble, 1.0 - bubble)
+
+
+@dataclass
+class PipelineStats:
+    """crates/distributed/src/pipeline_parallel.rs:339-375.  Also answers the dictionary keys of the same names."""
+    num_stages: int
+    num_micro_batches: int
+    schedule: str
+    bubble_fraction: float
+    efficiency: float
+
+    def __getitem__(self, key):
+        return getattr(self, key)
+
+
+class PipelineLayer:
+    """What a pipeline stage accepts as a layer: a module with `forward(x, ctx)` and `parameters()` (the reference's blanket
+    trait, pipeline_parallel.rs:109-111).  `PipelineLayer.check(obj)` says whether an object qualifies."""
+
+    @staticmethod
+    def check(obj) -> bool:
+        return callable(getattr(obj, "forward", None)) and callable(getattr(obj, "parameters", None))
 
 
 class PipelineComm:

@@ -8,6 +8,7 @@ all_gather, broadcast, barrier) this adds reduce_scatter, all_to_all, send and r
 """
 from __future__ import annotations
 
+import enum
 import threading
 
 import torch
@@ -53,6 +54,15 @@ class _ThreadedRendezvous:
         return vals
 
 
+class CommunicationBackend(enum.Enum):
+    """The transports a `ProcessGroup` can sit on (crates/distributed/src/lib.rs:107-125: SingleProcess, Threaded, Mpi;
+    here: one process, threads of one process sharing a rendezvous, or a torch.distributed group over gloo / NCCL).
+    `ProcessGroup.backend` holds the member's value; `ProcessGroup.communication_backend` the member itself."""
+    SINGLE_PROCESS = "single"
+    THREADED = "threaded"
+    TORCH = "torch"
+
+
 class ProcessGroup:
     def __init__(self, rank: int, world_size: int, backend: str, group=None, rendezvous=None, timeout_s: float = 60.0):
         if not (0 <= rank < world_size):
@@ -91,6 +101,10 @@ class ProcessGroup:
 
     def is_primary(self) -> bool:
         return self.rank == 0
+
+    @property
+    def communication_backend(self) -> "CommunicationBackend":
+        return CommunicationBackend(self.backend) if self.backend in ("single", "threaded", "torch") else CommunicationBackend.TORCH
 
     def _tag(self, name: str) -> str:
         self._seq += 1

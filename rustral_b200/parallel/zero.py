@@ -119,3 +119,48 @@ class ZeroMemoryStats:
     @classmethod
     def zero3(cls, P: int, W: int):
         return cls(2.0 * P / W, 4.0 * P / W, 12.0 * P / W)
+
+
+@dataclass
+class ZeRoMemoryStats:
+    """Per-rank megabytes under the reference's accounting (crates/distributed/src/zero.rs:286-345): parameters of
+    `param_size_bytes` each, Adam's two moments of the same size, gradients of the same size; `memory_saved_percent` is
+    against holding all of it on every rank.  `ZeroMemoryStats` above is this package's own bf16 + fp32-master model."""
+    local_params_mb: float
+    local_optimizer_states_mb: float
+    local_gradients_mb: float
+    total_params_mb: float
+    memory_saved_percent: float
+
+    @classmethod
+    def _make(cls, total_params: int, param_size_bytes: int, world_size: int, shard_grads: bool, shard_params: bool = True):
+        mb = total_params * param_size_bytes / (1024.0 * 1024.0)
+        lp = mb / world_size if shard_params else mb
+        lo = 2.0 * mb / world_size
+        lg = mb / world_size if shard_grads else mb
+        return cls(lp, lo, lg, mb, (1.0 - (lp + lo + lg) / (4.0 * mb)) * 100.0 if mb else 0.0)
+
+    @classmethod
+    def zero1(cls, total_params: int, param_size_bytes: int, world_size: int):
+        return cls._make(total_params, param_size_bytes, world_size, shard_grads=False)
+
+    @classmethod
+    def zero2(cls, total_params: int, param_size_bytes: int, world_size: int):
+        return cls._make(total_params, param_size_bytes, world_size, shard_grads=True)
+
+
+@dataclass
+class ZeroCheckpoint:
+    """A rank's optimizer shard as a typed record (crates/distributed/src/zero.rs:208-217): `ZeroCheckpoint.of(opt)` wraps
+    `opt.save_checkpoint()`, `restore(opt)` loads it back and refuses another rank or world size."""
+    rank: int
+    world_size: int
+    inner: dict
+
+    @classmethod
+    def of(cls, opt: ZeroOptimizer) -> "ZeroCheckpoint":
+        ck = opt.save_checkpoint()
+        return cls(ck["rank"], ck["world_size"], ck)
+
+    def restore(self, opt: ZeroOptimizer) -> None:
+        opt.load_checkpoint(self.inner)

@@ -133,12 +133,61 @@ class ZeroInfinity:
         if cuda:
             torch.cuda.current_stream().synchronize()
 
-    def memory_stats(self) -> dict:
+    def memory_stats(self) -> "ZeroInfinityStats":
         host = sum(3 * s.m.numel() * 4 for s in self.states.values() if s.location == StorageLocation.CPU)
-        return {"host_bytes": host, "nvme_bytes": self._nvme_used, "gpu_bytes": 0}
+        where = [s.location for s in self.states.values()]
+        total = sum((s.m.numel() if s.m is not None else getattr(s, "_n", 0)) for s in self.states.values())
+        return ZeroInfinityStats(total, where.count(StorageLocation.GPU), where.count(StorageLocation.CPU),
+                                 where.count(StorageLocation.NVME), self._nvme_used, host)
+
+
+@dataclass
+class ZeroInfinityStats:
+    """Where the optimizer states live (crates/distributed/src/zero_infinity.rs:504-527), plus the host bytes.  Compares
+    equal to, and indexes like, the dictionary {"host_bytes", "nvme_bytes", "gpu_bytes"}."""
+    total_params: int
+    gpu_states: int
+    cpu_states: int
+    nvme_states: int
+    nvme_bytes_used: int
+    host_bytes: int = 0
+
+    def as_dict(self) -> dict:
+        return {"host_bytes": self.host_bytes, "nvme_bytes": self.nvme_bytes_used, "gpu_bytes": 0}
+
+    def __getitem__(self, key):
+        return self.as_dict()[key]
+
+    def __eq__(self, other):
+        if isinstance(other, dict):
+            return self.as_dict() == other
+        return isinstance(other, ZeroInfinityStats) and vars(self) == vars(other)
+
+
+@dataclass
+class ZeROMemoryEstimate:
+    """crates/distributed/src/zero_infinity.rs:566-575 (bytes)."""
+    model_memory: int
+    optimizer_states: int
+    gradient_memory: int
+    gpu_memory: int
+    cpu_memory: int
+    nvme_memory: int
+    total_memory: int
 
 
 class ZeROInfinityEstimator:
     @staticmethod
     def estimate(num_params: int, world: int = 1) -> dict:
         return {"gpu_bytes": 2 * num_params + 4 * num_params, "host_bytes": 12 * num_params // world}
+
+    @staticmethod
+    def estimate_for(model_params: int, param_size_bytes: int, config: "ZeroInfinityConfig") -> ZeROMemoryEstimate:
+        """The reference's estimate: parameters and gradients on the GPU, Adam's two moments on the host and / or on
+        NVMe according to the configuration."""
+        model = model_params * param_size_bytes
+        opt = 2 * model
+        gpu = 2 * model
+        cpu = opt if config.cpu_offload else 0
+        nvme = opt if config.nvme_offload else 0
+        return ZeROMemoryEstimate(model, opt, model, gpu, cpu, nvme, gpu + cpu + nvme)

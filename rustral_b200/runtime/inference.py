@@ -10,6 +10,39 @@ class PoolClosed(RuntimeError):
     pass
 
 
+class InferenceResponse:
+    """What a worker hands back (crates/runtime/src/inference.rs:16-19): `output`, or `error` when the handler raised."""
+
+    __slots__ = ("output", "error")
+
+    def __init__(self, output=None, error: BaseException | None = None):
+        self.output, self.error = output, error
+
+    def unwrap(self):
+        if self.error is not None:
+            raise self.error
+        return self.output
+
+
+class InferenceRequest:
+    """One queued call (crates/runtime/src/inference.rs:7-13): the input and the reply slot the worker fills.
+    `InferencePool.submit` returns it; `wait()` blocks for the `InferenceResponse`."""
+
+    __slots__ = ("input", "_box", "_ev")
+
+    def __init__(self, inp):
+        self.input, self._box, self._ev = inp, [], threading.Event()
+
+    def wait(self, timeout: float | None = None) -> InferenceResponse:
+        if not self._ev.wait(timeout):
+            raise TimeoutError("inference timed out")
+        ok, val = self._box[0]
+        return InferenceResponse(val) if ok else InferenceResponse(error=val)
+
+    def done(self) -> bool:
+        return self._ev.is_set()
+
+
 class InferencePool:
     def __init__(self, workers: int, queue_bound: int, handler):
         self._q: queue.Queue = queue.Queue(maxsize=max(1, queue_bound))
@@ -31,17 +64,16 @@ class InferencePool:
                 box.append((False, e))
             ev.set()
 
-    def infer(self, inp, timeout: float | None = None):
+    def submit(self, inp, timeout: float | None = None) -> InferenceRequest:
+        """Queues `inp` and returns at once; several requests can be in flight from one caller."""
         if self._closed:
             raise PoolClosed("pool is shut down")
-        box, ev = [], threading.Event()
-        self._q.put((inp, box, ev), timeout=timeout)
-        if not ev.wait(timeout):
-            raise TimeoutError("inference timed out")
-        ok, val = box[0]
-        if not ok:
-            raise val
-        return val
+        req = InferenceRequest(inp)
+        self._q.put((inp, req._box, req._ev), timeout=timeout)
+        return req
+
+    def infer(self, inp, timeout: float | None = None):
+        return self.submit(inp, timeout).wait(timeout).unwrap()
 
     def shutdown(self):
         if self._closed:

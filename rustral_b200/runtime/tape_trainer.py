@@ -138,6 +138,15 @@ class TapeTrainer:
         return report
 
 
+class Classification:
+    """Task marker of the `Trainer` builder (crates/runtime/src/high_level_trainer.rs:22): accuracy is tracked and the
+    model's `loss_tape` defaults to cross-entropy.  `Trainer.for_task(Classification, opt)` is `Trainer.classification(opt)`."""
+
+
+class Regression:
+    """Task marker: no accuracy; the model supplies its own `loss_tape` (typically mean squared error)."""
+
+
 class Trainer:
     """Builder: Trainer.classification(opt).epochs(3).batch_size(32).shuffle(True).seed(0).fit(backend, model, data)
     (crates/runtime/src/high_level_trainer.rs:22-94)."""
@@ -155,6 +164,12 @@ class Trainer:
     @classmethod
     def regression(cls, optimizer):
         return cls(optimizer, False)
+
+    @classmethod
+    def for_task(cls, task, optimizer):
+        if task not in (Classification, Regression):
+            raise ValueError("task must be Classification or Regression")
+        return cls(optimizer, task is Classification)
 
     def epochs(self, n: int):
         self._cfg.epochs = n

@@ -11,6 +11,15 @@ class LabelPrediction:
     score: float
 
 
+class SymbolicError(ValueError):
+    """crates/symbolic/src/lib.rs:10-18: an insert into a frozen vocabulary (`kind` "frozen") or an id outside it
+    (`kind` "id_out_of_range"); raised by the strict accessors `try_insert` and `token_strict`."""
+
+    def __init__(self, kind: str, message: str):
+        super().__init__(message)
+        self.kind = kind
+
+
 class Vocabulary:
     """Insert-ordered symbol table with an unknown token at id 0; `freeze()` stops growth."""
 
@@ -38,6 +47,17 @@ class Vocabulary:
         self._tokens.append(token)
         self._ids[token] = i
         return i
+
+    def try_insert(self, token: str) -> int:
+        """`insert` that refuses a new token once the vocabulary is frozen instead of mapping it to the unknown id."""
+        if self._frozen and token not in self._ids:
+            raise SymbolicError("frozen", f"vocabulary is frozen; cannot insert token {token!r}")
+        return self.insert(token)
+
+    def token_strict(self, i: int) -> str:
+        if not (0 <= i < len(self._tokens)):
+            raise SymbolicError("id_out_of_range", f"id {i} is out of range")
+        return self._tokens[i]
 
     def freeze(self) -> None:
         self._frozen = True

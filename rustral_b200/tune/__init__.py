@@ -13,6 +13,7 @@ import ctypes as C
 import enum
 import json
 import os
+import sys
 import time
 from dataclasses import dataclass, field
 
@@ -215,8 +216,61 @@ class ConfigCache:
         tot = self.hits + self.misses
         return self.hits / tot if tot else 0.0
 
+    def stats(self) -> "CacheStats":
+        by_device: dict = {}
+        for e in self.entries.values():
+            by_device[e.device_id] = by_device.get(e.device_id, 0) + 1
+        return CacheStats(len(self.entries), by_device, self.path)
+
+
+@dataclass
+class CacheStats:
+    """What the configuration cache holds (crates/autotuner/src/cache.rs:208-272)."""
+    total_entries: int
+    by_device: dict
+    cache_path: str
+
+    def print(self, file=None) -> None:
+        out = file or sys.stdout
+        print("Config cache statistics:", file=out)
+        print(f"  total entries: {self.total_entries}", file=out)
+        print(f"  cache path: {self.cache_path}", file=out)
+        for dev, n in sorted(self.by_device.items()):
+            print(f"    {dev}: {n}", file=out)
+
+
+@dataclass
+class TunerStats:
+    """Running totals of an `AutoTuner` (crates/autotuner/src/tuner.rs:616-650).  Also answers the dictionary keys
+    `tuned` and `cache_hits`."""
+    total_tunings: int = 0
+    total_configs_tried: int = 0
+    total_tuning_time: float = 0.0
+    cache_hits: int = 0
+    cache_misses: int = 0
+
+    def hit_rate(self) -> float:
+        tot = self.cache_hits + self.cache_misses
+        return self.cache_hits / tot if tot else 0.0
+
+    def __getitem__(self, key):
+        return {"tuned": self.total_tunings, "cache_hits": self.cache_hits, "cache_misses": self.cache_misses,
+                "configs_tried": self.total_configs_tried}[key]
+
+    def print(self, file=None) -> None:
+        out = file or sys.stdout
+        print("AutoTuner statistics:", file=out)
+        print(f"  tuning sessions: {self.total_tunings}", file=out)
+        print(f"  configurations tried: {self.total_configs_tried}", file=out)
+        print(f"  tuning time: {self.total_tuning_time:.2f} s", file=out)
+        if self.total_tunings:
+            print(f"  average per session: {self.total_tuning_time / self.total_tunings:.2f} s", file=out)
+        if self.cache_hits + self.cache_misses:
+            print(f"  cache hit rate: {100.0 * self.hit_rate():.1f} %", file=out)
+
 
 TuningCache = ConfigCache
+TunerStrategy = Strategy          # the reference's name of the enumeration (crates/autotuner/src/tuner.rs:175)
 
 
 class TunableKernel:
@@ -284,7 +338,7 @@ class AutoTuner:
         if not self.config.device_id:
             self.config.device_id = torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu"
         self.cache = cache or ConfigCache(device_id=self.config.device_id)
-        self.stats = {"tuned": 0, "cache_hits": 0}
+        self.stats = TunerStats()
 
     def tune(self, kernel: TunableKernel) -> TuningResult:
         cfg = self.config
@@ -295,9 +349,10 @@ class AutoTuner:
         if cfg.use_cache:
             e = self.cache.get_config(kernel.kernel_id, cfg.device_id, cfg.dtype, bucket)
             if e is not None:
-                self.stats["cache_hits"] += 1
+                self.stats.cache_hits += 1
                 t = benchmark_kernel(kernel.with_config(e.config), cfg.warmup, cfg.timing, getattr(kernel, "host_timed", False))
                 return TuningResult(dict(e.config), t, t, 0, True)
+            self.stats.cache_misses += 1
         t_default = benchmark_kernel(kernel.with_config(default), cfg.warmup, cfg.timing, getattr(kernel, "host_timed", False))
         search = SearchHandle(kernel.config_space(), cfg.strategy, cfg.seed, min(cfg.max_evals, 5) if cfg.ci_mode else cfg.max_evals)
         search.report(default, t_default)
@@ -320,7 +375,9 @@ class AutoTuner:
         if cfg.cache_results:
             self.cache.store_config(kernel.kernel_id, cfg.device_id, cfg.dtype, bucket, best, t_best, search.num_evals())
             self.cache.save()
-        self.stats["tuned"] += 1
+        self.stats.total_tunings += 1
+        self.stats.total_configs_tried += search.num_evals()
+        self.stats.total_tuning_time += time.perf_counter() - t0
         return TuningResult(best, t_best, t_default, search.num_evals())
 
 
@@ -486,6 +543,9 @@ class _StrategySearch:
 
     def num_evals(self) -> int:
         return self.handle.num_evals()
+
+
+SearchStrategy = _StrategySearch     # the reference's trait name (crates/autotuner/src/search.rs:9)
 
 
 class GridSearch(_StrategySearch):
@@ -664,10 +724,14 @@ class KernelFactory:
         if cfg.enabled and cfg.use_cache:
             e = self.tuner.cache.get_config(kernel.kernel_id, cfg.device_id, cfg.dtype, kernel.input_signature())
             if e is not None:
-                self.tuner.stats["cache_hits"] += 1
+                self.tuner.stats.cache_hits += 1
                 config = dict(e.config)
         if config is None:
             config = self.tuner.tune(kernel).config
         if isinstance(kernel, ConfigurableKernel) and {"block_n", "splits"} <= set(config):
             kernel.apply_config(OpConfig.from_gemm_config(config, getattr(kernel, "M", 0)))
         return kernel, config
+
+
+from .kernel_config import (AlgorithmConfig, BlockSize, CacheConfig as KernelCacheConfig, KernelConfig, MatmulDimBucket,  # noqa: E402
+                            MemoryConfig, WorkgroupConfig)

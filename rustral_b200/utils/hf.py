@@ -15,11 +15,28 @@ def hub_url(model_id: str, revision: str = "main", filename: str = "model.safete
     return f"https://huggingface.co/{model_id}/resolve/{revision}/{filename}"
 
 
+class HfError(RuntimeError):
+    """crates/hf/src/lib.rs:53-75: `kind` is "hub" (the download failed or the file is not in the repository), "io" or
+    "tensor" (the file is not a readable safetensors file)."""
+
+    def __init__(self, kind: str, message: str):
+        super().__init__(message)
+        self.kind = kind
+
+
 def download_state_dict(model_id: str, revision: str = "main") -> dict:
     """name -> fp32 tensor (other dtypes are converted; the reference keeps only F32 entries)."""
-    path = fetch_url(hub_url(model_id, revision), None, os.path.join("hf", model_id.replace("/", "--"), revision),
-                     "model.safetensors")
-    tensors, _ = st.load_file(path)
+    try:
+        path = fetch_url(hub_url(model_id, revision), None, os.path.join("hf", model_id.replace("/", "--"), revision),
+                         "model.safetensors")
+    except FetchError as e:
+        raise HfError("hub", f"file 'model.safetensors' of repo '{model_id}' (revision {revision}) could not be fetched: {e}") from e
+    except OSError as e:
+        raise HfError("io", str(e)) from e
+    try:
+        tensors, _ = st.load_file(path)
+    except st.IoError as e:
+        raise HfError("tensor", f"{path}: {e}") from e
     return {k: v.float() for k, v in tensors.items() if v.is_floating_point()}
 
 
@@ -35,7 +52,7 @@ def load_from_hub(module, model_id: str, revision: str = "main", key_map=None, s
     module.load_state_dict(state, strict=strict)
 
 
-__all__ = ["hub_url", "download_state_dict", "save_state_dict_to_file", "load_from_hub", "FetchError"]
+__all__ = ["hub_url", "download_state_dict", "save_state_dict_to_file", "load_from_hub", "FetchError", "HfError"]
 
 
 # ---- checkpoint name conversion ---------------------------------------------------------------------------------

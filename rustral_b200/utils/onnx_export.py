@@ -57,10 +57,22 @@ def _node(op: str, inputs, outputs, name: str) -> bytes:
     return b"".join(_s(1, i) for i in inputs) + b"".join(_s(2, o) for o in outputs) + _s(3, name) + _s(4, op)
 
 
+class OnnxExportError(ValueError):
+    """A weight or bias whose size does not match the declared layer (crates/onnx-export/src/lib.rs:17-24); `kind` is
+    "weight_len" or "bias_len", `expected` / `got` are element counts."""
+
+    def __init__(self, kind: str, expected: int, got: int, message: str):
+        super().__init__(message)
+        self.kind, self.expected, self.got = kind, expected, got
+
+
 def export_linear_f32(in_features: int, out_features: int, weight: torch.Tensor, bias: torch.Tensor | None = None) -> bytes:
     """weight: [out, in] (this framework's layout) -> ONNX initializer W [in, out]; graph Y = X @ W (+ B)."""
     if tuple(weight.shape) != (out_features, in_features):
-        raise ValueError("weight must be [out_features, in_features]")
+        raise OnnxExportError("weight_len", in_features * out_features, weight.numel(),
+                              f"weight must be [out_features, in_features] = [{out_features}, {in_features}], got {tuple(weight.shape)}")
+    if bias is not None and bias.numel() != out_features:
+        raise OnnxExportError("bias_len", out_features, bias.numel(), f"bias must have {out_features} elements, got {bias.numel()}")
     W = weight.detach().float().t().contiguous()
     nodes = _ld(1, _node("MatMul", ["X", "W"], ["XW" if bias is not None else "Y"], "matmul"))
     inits = _ld(5, _tensor("W", W))
