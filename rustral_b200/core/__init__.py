@@ -19,4 +19,17 @@ from .numerics import (DType, Tolerance, NumericsConfig, NumericsValidator, OpFa
 from .fusion import (FusionPattern, PatternMatcher, FusionOptimizer, FusionTestHarness, FusionTestConfig,
                      FusionTestSuiteResult, OpType, Op, generate_random_data)
 
+PARALLEL_REDUCTIONS_ENV = "RUSTRAL_PARALLEL_REDUCTIONS"
+PAR_REDUCE_ENV = "RUSTRAL_PAR_REDUCE"
+
+
+def parallel_reductions_enabled() -> bool:
+    """True when RUSTRAL_PARALLEL_REDUCTIONS or its short form RUSTRAL_PAR_REDUCE is "1" (crates/core/src/lib.rs:8-23).
+    It concerns the CPU reference path only: by default its whole-tensor and column sums accumulate in float64, so the
+    fp32 result does not depend on how many threads split the work; with the switch on they are plain fp32 sums, faster
+    and subject to the association order of the thread count in use.  GPU reductions have a fixed order either way."""
+    import os
+    return os.environ.get(PARALLEL_REDUCTIONS_ENV) == "1" or os.environ.get(PAR_REDUCE_ENV) == "1"
+
+
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -162,7 +162,7 @@ def add_row_vector(a, v):
 def sum_dim0(a, out=None, accumulate: bool = False):
     """Column sums of a 2-D tensor, fp32 result, fixed summation order."""
     if not a.is_cuda:
-        r = a.float().sum(0)
+        r = a.float().sum(0) if (a.requires_grad or _par_reduce()) else a.double().sum(0).float()
         if out is not None:
             out.copy_(out + r if accumulate else r)
             return out
@@ -181,9 +181,16 @@ def sum_dim0(a, out=None, accumulate: bool = False):
     return out
 
 
+def _par_reduce() -> bool:
+    from ..core import parallel_reductions_enabled
+    return parallel_reductions_enabled()
+
+
 def sum_all(a):
     if not a.is_cuda:
-        return a.float().sum()
+        if a.requires_grad or _par_reduce():
+            return a.float().sum()
+        return a.double().sum().float()           # reproducible whatever the thread count (see core.parallel_reductions_enabled)
     a = _c(a)
     out = torch.empty((), dtype=torch.float32, device=a.device)
     scratch = _f32_scratch(a.device, 1024)

@@ -15,10 +15,14 @@ def pytest_configure(config):
 
 def pytest_collection_modifyitems(config, items):
     # the performance tier only runs when it is asked for by name (timing tests do not belong in a correctness run)
-    perf_selected = "perf" in (config.getoption("-m") or "")
-    skip_perf = pytest.mark.skip(reason="performance tier: select it with `-m perf` on a B200")
+    # RUSTRAL_RUN_GPU_PERF=1 selects the tier as well (the switch of the reference's tests/performance/gpu.rs)
+    perf_selected = "perf" in (config.getoption("-m") or "") or os.environ.get("RUSTRAL_RUN_GPU_PERF") == "1"
+    skip_perf = pytest.mark.skip(reason="performance tier: select it with `-m perf` or RUSTRAL_RUN_GPU_PERF=1 on a B200")
     skip = pytest.mark.skip(reason="no CUDA device")
     have_gpu = torch.cuda.is_available()
+    if not have_gpu and os.environ.get("RUSTRAL_REQUIRE_GPU") == "1":
+        # fail fast instead of skipping every GPU test (crates/wgpu-backend/tests/correctness.rs:8-22)
+        raise pytest.UsageError("RUSTRAL_REQUIRE_GPU=1 but no CUDA device is available")
     for item in items:
         if "perf" in item.keywords and not (perf_selected and have_gpu):
             item.add_marker(skip_perf)

@@ -177,3 +177,22 @@ def test_routing_comparison_is_the_load_formula():
     c = RoutingComparison.compare(num_tokens=1000, num_experts=8, top_k=2, observed_max_fraction=0.3)
     assert c.token_choice_max_load == pytest.approx(600.0) and c.expert_choice_max_load == pytest.approx(250.0)
     assert ExpertChoiceConfig(16, 4, 32, tokens_per_expert=8).tokens_per_expert == 8
+
+
+def test_parallel_reductions_switch(monkeypatch):
+    from rustral_b200 import ops
+    from rustral_b200.core import PAR_REDUCE_ENV, PARALLEL_REDUCTIONS_ENV, parallel_reductions_enabled
+    monkeypatch.delenv(PARALLEL_REDUCTIONS_ENV, raising=False)
+    monkeypatch.delenv(PAR_REDUCE_ENV, raising=False)
+    assert not parallel_reductions_enabled()
+    x = torch.full((1 << 20,), 0.1) * torch.arange(1, (1 << 20) + 1).float().reciprocal()
+    exact = float(x.double().sum())
+    serial = float(ops.sum_all(x))
+    assert serial == float(torch.tensor(exact, dtype=torch.float64).float())        # the float64 sum rounded once
+    assert float(ops.sum_dim0(x.view(1 << 10, 1 << 10)).sum()) == pytest.approx(exact, rel=1e-6)
+    monkeypatch.setenv(PAR_REDUCE_ENV, "1")
+    assert parallel_reductions_enabled()
+    assert float(ops.sum_all(x)) == pytest.approx(exact, rel=1e-5)                  # plain fp32 sum: close, not necessarily equal
+    monkeypatch.setenv(PAR_REDUCE_ENV, "0")
+    monkeypatch.setenv(PARALLEL_REDUCTIONS_ENV, "1")
+    assert parallel_reductions_enabled()

@@ -143,3 +143,11 @@ def test_memory_profiler_tracks_peaks_leaks_and_risk():
     assert mem.find_leaks() == [] and mem.snapshot()["current"] == 0
     events = json.loads(mem.export_timeline())
     assert [e["kind"] for e in events] == ["alloc", "alloc", "free", "free"]
+
+
+@pytest.mark.skipif(__import__("os").environ.get("RUSTRAL_TEST_HF_NETWORK") != "1",
+                    reason="network smoke test of the hub loader: set RUSTRAL_TEST_HF_NETWORK=1 (crates/hf/src/lib.rs:219)")
+def test_hub_download_smoke():
+    from rustral_b200.utils.hf import download_state_dict
+    state = download_state_dict("hf-internal-testing/tiny-random-gpt2")
+    assert state and all(v.dtype == torch.float32 for v in state.values())
