@@ -145,3 +145,32 @@ def test_queue_runs_the_cpu_suite_and_writes_the_comparative_report(tmp_path):
     text = open(res["report"]).read()
     assert "Micro-benchmarks" in text and "matmul.128x128x128" in text
     assert len(list((tmp_path / "results").glob("*_cpu.json"))) == 1
+
+
+def test_schema_files_accept_what_the_package_writes_and_name_what_is_wrong(tmp_path):
+    from rustral_b200.bench import manifest as M
+    from rustral_b200.bench import schemas
+    doc = _doc("s", 1.0)
+    assert schemas.check(doc, "schema_v2") == [] and schemas.check(R.combine([doc, _doc("t", 2.0)]), "schema_v2") == []
+    bad = json.loads(json.dumps(doc))
+    bad["schema_version"] = "1.0.0"
+    bad["samples"][0]["runs_ms"] = []
+    del bad["samples"][1]["dtype"]
+    bad["samples"][1]["outliers"] = [0.5]
+    errs = schemas.check(bad, "schema_v2")
+    assert any("$.schema_version" in e for e in errs) and any("$.samples[0].runs_ms: needs at least 1" in e for e in errs)
+    assert any("$.samples[1]: missing key 'dtype'" in e for e in errs) and any("$.samples[1].outliers[0]: expected integer" in e for e in errs)
+    man = M.write_manifest(str(tmp_path / "m.json"), "sst2_classifier", {
+        "model_type": "transformer_encoder", "seed": 1, "total_params": 10, "vocab_size": 5, "epochs": 1, "batch_size": 2,
+        "learning_rate": 1e-3, "dataset_hash_fnv1a": "0123456789abcdef", "train_elapsed_sec": 0.5, "dataset": "d", "tokenizer": "t",
+        "quick_mode": True, "dev_accuracy": 0.5, "dev_loss": 0.7, "samples_per_sec": 10.0},
+        {"train_label_counts": [1, 1], "dev_label_counts": [1, 1], "dev_confusion_matrix": [[1, 0], [0, 1]],
+         "dev_predicted_counts": [1, 1], "dev_positive_prob_hist": [0] * 10})
+    assert schemas.check(man, "manifest_schema") == []
+    assert any("dataset_hash_fnv1a" in e for e in schemas.check({**man, "dataset_hash_fnv1a": "xyz"}, "manifest_schema"))
+    assert any("is not one of" in e for e in schemas.check({**man, "task": "other"}, "manifest_schema"))
+    cur = M.curate("sst2_classifier", "dev_accuracy", "v0", [dict(man, seed=s) for s in (1, 2)])
+    assert schemas.check(cur, "curated_manifest_schema") == []
+    assert any("$.runs: needs at least 1" in e for e in schemas.check({**cur, "runs": []}, "curated_manifest_schema"))
+    with pytest.raises(KeyError):
+        schemas.load("nope")
