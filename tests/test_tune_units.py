@@ -140,3 +140,21 @@ def test_autotuner_keeps_the_default_when_the_gain_is_below_the_threshold_and_wh
     assert r.config == {"v": 0} and r.evaluated == 0 and k3.calls == []
     ci = TunerConfig.ci_safe()
     assert ci.ci_mode and ci.max_evals <= 5 and TunerConfig.fast().max_tuning_time_s <= TunerConfig().max_tuning_time_s
+
+
+def test_command_line_cache_and_shapes(tmp_path, monkeypatch, capsys):
+    from rustral_b200.tune import ConfigCache
+    from rustral_b200.tune.__main__ import main
+    monkeypatch.setenv("RUSTRAL_CACHE_DIR", str(tmp_path))
+    c = ConfigCache()
+    c.store_config("gemm_bf16_tcgen05", "B200", "bf16", "matmul_large_large_medium", {"block_n": 256}, 12.5, 8)
+    c.save()
+    assert main(["cache"]) == 0
+    out = capsys.readouterr().out
+    assert "total entries: 1" in out and "B200: 1" in out
+    assert main(["cache", "--json"]) == 0
+    assert '"block_n": 256' in capsys.readouterr().out
+    assert main(["shapes", "--model", "gpt2-small", "--tokens", "4096"]) == 0
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert len(lines) == 5 and lines[0].startswith("4096 x 2304 x 768") and "matmul_large_large_medium" in lines[0]
+    assert main(["cache", "--clear"]) == 0 and ConfigCache().entries == {}
