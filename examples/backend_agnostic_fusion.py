@@ -9,7 +9,7 @@ import torch
 
 from _common import backend_for, parser
 
-from rustral_b200.core import (FusionOptimizer, FusionPattern, FusionTestHarness, MemoryProfiler, OperationProfiler,
+from rustral_b200.core import (DType, FusionOptimizer, FusionPattern, FusionTestHarness, MemoryProfiler, OperationProfiler,
                                PatternMatcher, PoolStrategy, TensorPool, generate_random_data)
 from rustral_b200.nn import FusionHelper
 
@@ -33,7 +33,7 @@ def main(argv=None):
         def unfused():
             y = ops.add_row_vector(ops.matmul(x, ops.transpose(w)), b)
             return act(y) if act else y
-        r = harness.run_test(unfused, lambda: fuse.apply(pattern, x, w, b))
+        r = harness.run_test(unfused, lambda: fuse.apply(pattern, x, w, b), DType.BF16 if dt == torch.bfloat16 else DType.F32)
         results[pattern.value] = r
         print(f"{pattern.value:<18} max |fused - unfused| {r.max_abs_err:.2e}  unfused {r.unfused_ms:.3f} ms  fused {r.fused_ms:.3f} ms  x{r.speedup:.2f}")
     y = FusionHelper.try_linear_gelu(x, w, b)
