@@ -352,3 +352,49 @@ def test_serving_benchmark_rate_sweep_stops_at_saturation(capsys):
                         "--blocks", "64", "--ttft-limit-ms", "0"])
     out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert len(out["sweep"]) == 1 and out["saturated_at_rate"] == 50.0
+
+
+@pytest.mark.parametrize("chunk", [0, 5])
+def test_a_cache_too_small_for_all_requests_pauses_and_resumes_without_changing_any_output(chunk):
+    """Twelve requests through a cache that holds about four of them: requests are paused when a step cannot get a block,
+    their blocks are released, and they are recomputed from their tokens on resume.  With greedy sampling the generated
+    tokens must equal those of an engine with room for everything, whole-prompt or chunked prefill alike."""
+    cfg = preset("llama-test", seq_len=64, d_model=64, ffn_dim=128)
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist() for n in torch.randint(2, 14, (12,), generator=g)]
+    outs = {}
+    for blocks in (64, 20):
+        runner = ModelRunner(cfg, device="cpu", num_blocks=blocks, block_size=4, seed=1)
+        eng = ServingEngine(runner, max_batch_size=6, prefill_chunk=chunk)
+        ids = []
+        for i, p in enumerate(prompts):                # arrivals are spread over the first steps
+            ids.append(eng.submit(p, 10))
+            if i % 3 == 2:
+                eng.step()
+        eng.run_to_completion(max_steps=2000)
+        outs[blocks] = [eng.scheduler.get(r).generated for r in ids]
+        assert all(len(o) == 10 for o in outs[blocks]) and runner.cache.free_blocks == blocks and not eng._prefill_pos
+        if blocks == 20:
+            assert eng.scheduler.stats.preempted > 0    # the small cache really did run out
+    assert outs[20] == outs[64]
+
+
+def test_aborting_a_request_frees_its_blocks_and_leaves_the_others_untouched():
+    cfg = preset("gpt2-test", seq_len=64, d_model=64, ffn_dim=128)
+    prompts = [[5, 6, 7, 8, 9], [11, 12, 13], [21, 22, 23, 24, 25, 26, 27]]
+
+    def run(abort_second: bool):
+        runner = ModelRunner(cfg, device="cpu", num_blocks=32, block_size=4, seed=2)
+        eng = ServingEngine(runner, max_batch_size=4)
+        ids = [eng.submit(p, 8) for p in prompts]
+        eng.step(); eng.step()
+        if abort_second:
+            used = runner.cache.free_blocks
+            assert eng.scheduler.abort(ids[1]) and runner.cache.free_blocks > used
+            assert not eng.scheduler.abort(ids[1]) and not eng.scheduler.abort(999)
+        eng.run_to_completion()
+        assert runner.cache.free_blocks == 32
+        return [eng.scheduler.get(r).generated if eng.scheduler.get(r) is not None else None for r in ids]
+    full, cut = run(False), run(True)
+    assert cut[0] == full[0] and cut[2] == full[2] and len(full[1]) == 8
+    assert cut[1] is None or len(cut[1]) < 8
