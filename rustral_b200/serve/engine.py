@@ -143,6 +143,15 @@ class ServingEngine:
             self.release(rid)
         return tokens
 
+    def abort(self, rid: int) -> bool:
+        """Cancels one unfinished request: its KV blocks are freed and its prefill progress and callback are dropped.
+        False when the request is unknown or already finished."""
+        ok = self.scheduler.abort(rid)
+        if ok:
+            self.callbacks.pop(rid, None)
+            self._prefill_pos.pop(rid, None)
+        return ok
+
     def abort_all(self) -> list:
         """Removes every unfinished request (after a failed model step: retrying it would fail the same way), frees
         their KV blocks and returns their ids."""
@@ -151,6 +160,7 @@ class ServingEngine:
         for rid in ids:
             sch.abort(rid)
             self.callbacks.pop(rid, None)
+            self._prefill_pos.pop(rid, None)
         return ids
 
     def release(self, rid: int) -> None:

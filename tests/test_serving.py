@@ -390,11 +390,27 @@ def test_aborting_a_request_frees_its_blocks_and_leaves_the_others_untouched():
         eng.step(); eng.step()
         if abort_second:
             used = runner.cache.free_blocks
-            assert eng.scheduler.abort(ids[1]) and runner.cache.free_blocks > used
-            assert not eng.scheduler.abort(ids[1]) and not eng.scheduler.abort(999)
+            assert eng.abort(ids[1]) and runner.cache.free_blocks > used
+            assert not eng.abort(ids[1]) and not eng.abort(999)
         eng.run_to_completion()
         assert runner.cache.free_blocks == 32
         return [eng.scheduler.get(r).generated if eng.scheduler.get(r) is not None else None for r in ids]
     full, cut = run(False), run(True)
     assert cut[0] == full[0] and cut[2] == full[2] and len(full[1]) == 8
     assert cut[1] is None or len(cut[1]) < 8
+
+
+def test_aborting_during_chunked_prefill_drops_the_prefill_progress():
+    cfg = preset("gpt2-test", seq_len=64, d_model=64, ffn_dim=128)
+    eng = ServingEngine(ModelRunner(cfg, device="cpu", num_blocks=32, block_size=4), max_batch_size=4, prefill_chunk=4)
+    rid = eng.submit(list(range(1, 30)), 3)
+    eng.step()
+    assert eng._prefill_pos.get(rid) == 4                    # one chunk of the 29-token prompt is in the cache
+    assert eng.abort(rid) and rid not in eng._prefill_pos and eng.runner.cache.free_blocks == 32
+    other = eng.submit([3, 4, 5], 2)
+    eng.run_to_completion()
+    assert len(eng.scheduler.get(other).generated) == 2
+    eng2 = ServingEngine(ModelRunner(cfg, device="cpu", num_blocks=32, block_size=4), max_batch_size=4, prefill_chunk=4)
+    a = eng2.submit(list(range(1, 30)), 3)
+    eng2.step()
+    assert eng2.abort_all() == [a] and not eng2._prefill_pos and not eng2.scheduler.has_work()
