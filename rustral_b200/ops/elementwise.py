@@ -173,6 +173,8 @@ def sum_dim0(a, out=None, accumulate: bool = False):
     if out is None:
         out = torch.empty(cols, dtype=torch.float32, device=a.device)
         accumulate = False
+    if rows == 0:
+        return out if accumulate else out.zero_()
     lib = N.kernels()
     slabs = lib.rb_sum_dim0_slabs()
     partial = _f32_scratch(a.device, slabs * cols)

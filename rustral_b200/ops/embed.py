@@ -35,6 +35,8 @@ def embedding_forward(ids: torch.Tensor, wte: torch.Tensor, wpe=None, seq_len: i
         raise TypeError("embedding: CUDA tables must be bf16")
     flat = flat.to(torch.int64)
     y = out if out is not None else torch.empty((tokens, dim), dtype=wte.dtype, device=wte.device)
+    if tokens == 0:
+        return y
     N.check(N.kernels().rb_embedding_fwd(flat.data_ptr(), wte.data_ptr(), N.ptr(wpe), y.data_ptr(), tokens, dim,
                                          seq_len, wte.shape[0], N.stream_ptr()), "rb_embedding_fwd")
     return y

@@ -46,6 +46,8 @@ def cross_entropy_fwd_bwd(logits2: torch.Tensor, targets: torch.Tensor, n_valid:
     grad = None
     if want_grad:
         grad = dlogits if dlogits is not None else torch.empty_like(logits2)
+    if rows == 0:
+        return loss, lse, grad
     N.check(N.kernels().rb_cross_entropy(logits2.data_ptr(), logits2.stride(0), targets.data_ptr(), loss.data_ptr(),
                                          lse.data_ptr(), N.ptr(grad), grad.stride(0) if grad is not None else 0, rows,
                                          n_valid, n_pad, grad_scale, ignore_index, N.stream_ptr()),
@@ -99,6 +101,8 @@ def _softmax_impl(x, log_mode: bool):
     if x2.dtype not in (torch.float32, torch.bfloat16):
         raise TypeError("softmax: fp32 or bf16 only")
     y = torch.empty_like(x2)
+    if x2.numel() == 0:
+        return y if x.dim() == 2 else y.reshape(x.shape)
     N.check(N.kernels().rb_softmax_rows(x2.data_ptr(), y.data_ptr(), x2.shape[0], x2.shape[1], x2.stride(0),
                                         y.stride(0), int(log_mode), int(x2.dtype == torch.bfloat16), N.stream_ptr()),
             "rb_softmax_rows")

@@ -214,6 +214,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
         raise TypeError("gemm: CUDA operands must be bf16 (accumulation is fp32)")
+    if M == 0 or Nn == 0:
+        # an empty batch (or an empty layer): nothing to launch; a given output is left as it is
+        if aux_out is not None and aux_out.numel():
+            aux_out.zero_()
+        return out if out is not None else torch.empty((M, Nn), dtype=out_dtype, device=a.device)
+    if K == 0 and peer is None and row_scale is None and col_scale is None:
+        # an empty contraction (the weight gradient of an empty batch): the product is zero and only the epilogue is left;
+        # the reference formula does that with tensor ops on the operands' device
+        return _gemm_cpu(a, b, a_mn, b_mn, bias, act, residual, aux_in, aux_out, out, out_dtype, accumulate, alpha)
     if a.stride(1) != 1 or b.stride(1) != 1:
         raise ValueError("gemm: operands must have a contiguous last dimension")
     # the cheap integer test settles the common aligned call; the full check runs only when it fails or optional tensors exist

@@ -49,6 +49,8 @@ def norm_forward(x2: torch.Tensor, gamma: torch.Tensor, beta, eps: float, rms: b
             rstd = torch.empty(rows, dtype=torch.float32, device=x2.device)
         else:
             mean, rstd = torch.empty((2, rows), dtype=torch.float32, device=x2.device).unbind(0)
+    if rows == 0:
+        return y, mean, rstd
     N.check(N.kernels().rb_norm_fwd(x2.data_ptr(), x2.stride(0), gamma.data_ptr(), N.ptr(beta), y.data_ptr(),
                                     y.stride(0), N.ptr(mean), N.ptr(rstd), rows, n, eps, int(rms),
                                     N.stream_ptr()), "rb_norm_fwd")

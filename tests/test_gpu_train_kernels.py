@@ -156,3 +156,21 @@ def test_linear_layers_of_sizes_the_kernel_cannot_address_run_on_padded_copies(r
         outs.append((y.detach().float().cpu(), xd.grad.float().cpu(), wd.grad.float().cpu(), bd.grad.float().cpu()))
     for name, c, got in zip(("y", "dx", "dw", "db"), *outs):
         assert_close(got, c, "gemm_act", what=f"{name} of linear {fin}->{fout}")
+
+
+def test_empty_batches_run_through_the_gpu_wrappers_without_a_launch(cuda_status):
+    """A batch of zero rows is legal input: forward, loss and backward give empty or zero results as on the CPU."""
+    from rustral_b200 import ops
+    w = (torch.randn(16, 8) * 0.1).to(torch.bfloat16).cuda().requires_grad_()
+    b = torch.zeros(16, dtype=torch.bfloat16, device="cuda", requires_grad=True)
+    x = torch.zeros(0, 8, dtype=torch.bfloat16, device="cuda", requires_grad=True)
+    y = ops.linear(x, w, b, "gelu")
+    assert y.shape == (0, 16)
+    y.float().sum().backward()
+    assert x.grad.shape == (0, 8) and float(w.grad.float().abs().sum()) == 0.0 and float(b.grad.float().abs().sum()) == 0.0
+    assert ops.softmax(torch.zeros(0, 8, dtype=torch.bfloat16, device="cuda")).shape == (0, 8)
+    g, bt = torch.ones(8, dtype=torch.bfloat16, device="cuda"), torch.zeros(8, dtype=torch.bfloat16, device="cuda")
+    assert ops.layer_norm(torch.zeros(0, 8, dtype=torch.bfloat16, device="cuda"), g, bt).shape == (0, 8)
+    table = torch.zeros(10, 8, dtype=torch.bfloat16, device="cuda")
+    assert ops.embedding(torch.zeros(0, dtype=torch.int64, device="cuda"), table).shape == (0, 8)
+    assert ops.sum_dim0(torch.zeros(0, 8, dtype=torch.bfloat16, device="cuda")).tolist() == [0.0] * 8
