@@ -7,7 +7,7 @@ drives that entry point through its exported C symbol, exactly as such a caller 
 what the ordinary entry point (which takes caller-provided scratch) produces, on two calls in a row, because the
 built-in scratch is shared between calls and keeps the previous call's contents.
 
-The file name sorts last on purpose: a run that stops at the first failure has by then run every other test.
+The file name sorts behind the regular suites on purpose: a run that stops at the first failure has by then run them.
 """
 import ctypes as C
 
