@@ -28,9 +28,13 @@ class Embedding(Module, Trainable, Saveable):
         return cls(EmbeddingConfig(vocab_size, dim), backend.normal_parameter("embed", (vocab_size, dim), seed, scale), vocab)
 
     def forward(self, ids, ctx: ForwardCtx):
-        ids = torch.as_tensor(ids, dtype=torch.int64, device=self.embed.tensor.device)
-        if ids.numel() and (int(ids.max()) >= self.config.vocab_size or int(ids.min()) < 0):
-            raise InvalidArgument("Embedding: token id out of range")
+        ids = ids if torch.is_tensor(ids) else torch.as_tensor(ids, dtype=torch.int64)
+        if not ids.is_cuda:
+            # checked on the host while the ids are there; ids that already live on the GPU are not read back (that would
+            # stall the stream on every call): the kernel skips an out-of-range id and the index-checking build reports it
+            if ids.numel() and (int(ids.max()) >= self.config.vocab_size or int(ids.min()) < 0):
+                raise InvalidArgument("Embedding: token id out of range")
+        ids = ids.to(device=self.embed.tensor.device, dtype=torch.int64)
         with ctx.profile("embedding", ids.shape):
             return ops.embedding(ids, self.embed.tensor)
 
