@@ -15,8 +15,9 @@ def attention_reference(q, k, v, causal: bool, scale: float | None = None, kv_le
     Sk, Hk = k.shape[1], k.shape[2]
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     qf = q.float().permute(0, 2, 1, 3)
-    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(H // Hk, dim=1)
-    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(H // Hk, dim=1)
+    kf, vf = k.float().permute(0, 2, 1, 3), v.float().permute(0, 2, 1, 3)
+    if H != Hk:                                             # grouped-query attention: every K/V head serves H / Hk query heads
+        kf, vf = kf.repeat_interleave(H // Hk, dim=1), vf.repeat_interleave(H // Hk, dim=1)
     s = qf @ kf.transpose(-1, -2) * scale
     if causal:
         i = torch.arange(Sq, device=q.device)[:, None] + (Sk - Sq)

@@ -55,7 +55,9 @@ def act_grad_reference(name: str, x: torch.Tensor) -> torch.Tensor:
 def _gemm_cpu(a, b, a_mn, b_mn, bias, act, residual, aux_in, aux_out, out, out_dtype, accumulate, alpha):
     A = a.float().t() if a_mn else a.float()
     B = b.float().t() if b_mn else b.float()
-    v = alpha * (A @ B.t())
+    v = A @ B.t()
+    if alpha != 1.0:
+        v = v * alpha
     if bias is not None:
         v = v + bias.float()
     if act in _ACT_FWD:
@@ -69,8 +71,7 @@ def _gemm_cpu(a, b, a_mn, b_mn, bias, act, residual, aux_in, aux_out, out, out_d
     if residual is not None:
         v = v + residual.float()
     if out is None:
-        out = torch.empty(v.shape, dtype=out_dtype, device=a.device)
-        accumulate = False
+        return v if v.dtype == out_dtype else v.to(out_dtype)      # v is a fresh tensor: no second buffer, no copy
     if accumulate:
         out.copy_((out.float() + v).to(out.dtype))
     else:

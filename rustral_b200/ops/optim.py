@@ -1,6 +1,8 @@
 """Fused optimizer steps over flat fp32 state."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .. import _native as N
@@ -32,15 +34,18 @@ def adam_step(p, m, v, g, *, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=
             coef = max_grad_norm / (float(grad_norm) + 1e-6)
             if coef < 1.0:
                 gs *= coef
-        gf = g.float() * gs
-        if not decoupled:
+        gf = g.float()
+        if gs != 1.0:
+            gf = gf * gs
+        if not decoupled and weight_decay != 0.0:
             gf = gf + weight_decay * p
         m.mul_(beta1).add_(gf, alpha=1 - beta1)
         v.mul_(beta2).addcmul_(gf, gf, value=1 - beta2)
-        upd = (m / bc1) / ((v / bc2).sqrt() + eps)
-        if decoupled:
-            upd = upd + weight_decay * p
-        p.add_(upd, alpha=-lr)
+        # p -= lr * ((m / bc1) / (sqrt(v / bc2) + eps) + wd * p) with one temporary: sqrt(v / bc2) = sqrt(v) / sqrt(bc2)
+        denom = v.sqrt().div_(math.sqrt(bc2)).add_(eps)
+        if decoupled and weight_decay != 0.0:
+            p.mul_(1.0 - lr * weight_decay)
+        p.addcdiv_(m, denom, value=-lr / bc1)
         if p_lowp is not None:
             p_lowp.copy_(p.to(p_lowp.dtype))
         return
