@@ -67,6 +67,24 @@ class KeyPaddingMask:
         return cls((keep * pos).amax(-1).to(torch.int32))
 
 
+    @classmethod
+    def from_additive(cls, mask: torch.Tensor, check: bool = True):
+        """Lengths from an additive key mask of shape [B, Sk], [B, 1, Sk] or [B, 1, 1, Sk] (0 for real keys, -inf or a large
+        negative number for padding), so that code that builds such tensors can use the flash kernels.  The padding has
+        to be a suffix of every row; with `check` that is verified (one read-back of B x Sk booleans) and a mask of any
+        other form gives None, which the caller passes on as the tensor it has."""
+        m = mask.reshape(mask.shape[0], -1) if mask.dim() > 2 and mask.numel() == mask.shape[0] * mask.shape[-1] else mask
+        if m.dim() != 2:
+            return None
+        real = m > -1e4
+        lengths = real.sum(-1).to(torch.int32)
+        if check:
+            pos = torch.arange(m.shape[1], device=m.device)[None, :]
+            if not bool((real == (pos < lengths[:, None])).all()):
+                return None
+        return cls(lengths)
+
+
 def scaled_dot_product_attention(q, k, v, mask=None, causal: bool = False, scale: float | None = None):
     """q [B,S,H,D], k/v [B,Sk,Hkv,D].  `mask`: None, a `KeyPaddingMask` (flash kernels, padded keys skipped) or an
     additive tensor broadcastable to [B,H,S,Sk] (reference math in fp32, O(S^2) memory: arbitrary masks are rare and

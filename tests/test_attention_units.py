@@ -142,3 +142,16 @@ def test_feed_forward_blocks_match_their_formulas_with_and_without_bias():
     gu = x @ sw.gate_up.weight.tensor.t()
     want = (torch.nn.functional.silu(gu[..., :24]) * gu[..., 24:]) @ sw.down.weight.tensor.t()
     assert torch.allclose(sw(x, CTX), want, atol=1e-5)
+
+
+def test_key_padding_lengths_from_an_additive_mask_tensor():
+    q, k, v = _qkv(seed=21)
+    add = torch.zeros(2, 1, 1, 6)
+    add[1, :, :, 4:] = float("-inf")
+    kp = KeyPaddingMask.from_additive(add)
+    assert kp.lengths.tolist() == [6, 4]
+    assert torch.allclose(scaled_dot_product_attention(q, k, v, kp), scaled_dot_product_attention(q, k, v, add), atol=1e-5)
+    assert KeyPaddingMask.from_additive(torch.tensor([[0.0, -1e9, -1e9], [0.0, 0.0, 0.0]])).lengths.tolist() == [1, 3]
+    holes = torch.tensor([[0.0, float("-inf"), 0.0]])                      # padding in the middle is not a length
+    assert KeyPaddingMask.from_additive(holes) is None and KeyPaddingMask.from_additive(holes, check=False).lengths.tolist() == [2]
+    assert KeyPaddingMask.from_additive(torch.zeros(2, 4, 6, 6)) is None   # a full [B, H, S, S] mask is not a key mask
