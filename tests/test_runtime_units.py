@@ -162,3 +162,27 @@ def test_dashboard_hook_receives_the_trainers_loss_accuracy_and_rate():
     assert len(d.losses) == 5 and d.losses == pytest.approx([e.mean_loss for e in report.epochs])
     assert d.losses[-1] < d.losses[0] and d.losses[0] > 0.1            # real losses, not a default of zero
     assert d.accuracies[-1] == 1.0 and d.epoch == 4 and d.throughput > 0
+
+
+def test_trainer_builder_sends_epoch_summaries_to_a_metrics_logger(tmp_path):
+    import json
+    from rustral_b200.core.module import Module, Trainable
+    from rustral_b200.metrics import MetricsLogger, TensorBoardWriter
+    from rustral_b200.runtime.tape_trainer import SupervisedTapeModel, Trainer
+
+    class M(Module, Trainable, SupervisedTapeModel):
+        def __init__(self):
+            self.lin = LinearBuilder(2, 2).with_bias().seed(1).build(BE)
+
+        def forward_tape(self, x, tape, ctx):
+            return tape.apply("lin", lambda: self.lin(x, ctx))
+    seen = []
+    log = MetricsLogger([TensorBoardWriter(str(tmp_path), "fit")])
+    data = [([1.0, 0.0], 0), ([0.0, 1.0], 1)] * 8
+    report = Trainer.classification(Adam(0.1)).epochs(3).batch_size(4).metrics(log).epoch_callback(seen.append).fit(BE, M(), data)
+    rows = [json.loads(l) for l in open(tmp_path / "fit.jsonl")]
+    losses = [r["value"] for r in rows if r["name"] == "train/loss"]
+    assert losses == pytest.approx([e.mean_loss for e in report.epochs]) and [r["step"] for r in rows if r["name"] == "train/loss"] == [0, 1, 2]
+    assert [r["value"] for r in rows if r["name"] == "train/accuracy"][-1] == report.accuracy
+    assert [r["value"] for r in rows if r["name"] == "train/lr"] == [0.1, 0.1, 0.1]
+    assert [s.epoch for s in seen] == [0, 1, 2] and seen[-1].mean_loss == report.epochs[-1].mean_loss
