@@ -109,7 +109,7 @@ class NcclCommunicator:
     def version() -> str:
         try:
             return ".".join(str(v) for v in torch.cuda.nccl.version())
-        except Exception:
+        except (RuntimeError, AttributeError, AssertionError):     # a torch build without NCCL, or no CUDA runtime
             return "unavailable"
 
     def all_reduce(self, t: torch.Tensor, op: str = "sum") -> torch.Tensor:
