@@ -4,6 +4,7 @@ from __future__ import annotations
 import ctypes as C
 import mmap
 import os
+import queue
 import random
 import threading
 from dataclasses import dataclass
@@ -124,7 +125,7 @@ class TokenFileDataset:
     def __del__(self):
         try:
             self.close()
-        except Exception:   # noqa: BLE001
+        except Exception:   # noqa: BLE001 - interpreter shutdown: the library or its handle may already be gone
             pass
 
 
@@ -233,7 +234,7 @@ class TokenBatchPrefetcher:
     def __del__(self):
         try:
             self.close()
-        except Exception:   # noqa: BLE001
+        except Exception:   # noqa: BLE001 - interpreter shutdown: the library or its handle may already be gone
             pass
 
 
@@ -242,7 +243,6 @@ class PinnedBatchPrefetcher:
     of step i+1 overlaps the compute of step i."""
 
     def __init__(self, make_batch, depth: int = 2):
-        import queue
         self._make = make_batch
         self._q: "queue.Queue" = queue.Queue(maxsize=depth)
         self._stop = False
@@ -260,7 +260,7 @@ class PinnedBatchPrefetcher:
                 try:
                     self._q.put(b, timeout=0.1)
                     break
-                except Exception:   # noqa: BLE001 - queue.Full
+                except queue.Full:
                     continue
 
     def next(self) -> torch.Tensor:

@@ -145,3 +145,22 @@ def test_console_logger_and_progress_bar_write_text():
     bar.update(2)
     text = bar_out.getvalue()
     assert "[####....] 2/4" in text and "[########] 4/4" in text and "half" in text
+
+
+def test_pinned_batch_prefetcher_serves_batches_in_order_and_blocks_when_full():
+    import time
+
+    import torch
+    from rustral_b200.data.datasets import PinnedBatchPrefetcher
+    made = []
+
+    def make(step):
+        made.append(step)
+        return torch.full((4,), float(step))
+    pf = PinnedBatchPrefetcher(make, depth=2)
+    try:
+        time.sleep(0.35)                      # the producer fills the queue (2), holds one more batch and waits on the full queue
+        assert len(made) == 3
+        assert [float(pf.next()[0]) for _ in range(5)] == [0.0, 1.0, 2.0, 3.0, 4.0]
+    finally:
+        pf.close()
