@@ -1,0 +1,81 @@
+"""Property tests (hypothesis): invariants that must hold for any input, not just the hand-picked ones."""
+import torch
+from hypothesis import given, settings, strategies as st
+
+from rustral_b200.io import safetensors_io as sio
+from rustral_b200.nn import PagedCache
+from rustral_b200.parallel.checkpoint import reshard_flat
+from rustral_b200.parallel.compression import CompressionType, ErrorFeedbackCompression
+
+_DT = [torch.float32, torch.bfloat16, torch.float16, torch.int64, torch.int32, torch.uint8, torch.bool]
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.lists(st.tuples(st.text("abcxyz._0", min_size=1, max_size=8), st.sampled_from(range(len(_DT))),
+                          st.lists(st.integers(0, 5), min_size=0, max_size=3), st.integers(0, 1000)), min_size=0, max_size=6))
+def test_safetensors_round_trip_of_arbitrary_state(entries):
+    state = {}
+    for name, di, shape, seed in entries:
+        dt = _DT[di]
+        g = torch.Generator().manual_seed(seed)
+        t = torch.randint(0, 2, shape, generator=g).to(dt) if not dt.is_floating_point else (torch.randn(shape, generator=g) * 10).to(dt)
+        state[name] = t
+    back, meta = sio.deserialize(sio.serialize(state, {"n": len(state)}))
+    assert set(back) == set(state) and meta == {"n": str(len(state))}
+    for k, t in state.items():
+        assert back[k].dtype == t.dtype and back[k].shape == t.shape and torch.equal(back[k], t)
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(1, 200), st.integers(1, 8), st.integers(1, 8))
+def test_resharding_a_flat_buffer_keeps_every_element_in_order(n, old_world, new_world):
+    full = torch.arange(float(n))
+    per = (n + old_world - 1) // old_world
+    padded = torch.cat([full, torch.zeros(per * old_world - n)])
+    old = [padded[r * per:(r + 1) * per] for r in range(old_world)]
+    new = [reshard_flat(old, new_world, r) for r in range(new_world)]
+    assert len({s.numel() for s in new}) == 1                      # equal shards
+    joined = torch.cat(new)
+    assert torch.equal(joined[:n], full) and float(joined[n:].abs().sum()) == 0.0
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.lists(st.tuples(st.integers(0, 5), st.integers(1, 40), st.booleans()), min_size=1, max_size=40))
+def test_paged_cache_never_loses_or_shares_a_block(ops):
+    blocks, bs = 12, 4
+    c = PagedCache(blocks, bs, allocate_storage=False)
+    want = {}                                                       # sequence -> tokens it may hold
+    for seq, tokens, free in ops:
+        if free:
+            c.free(seq)
+            want.pop(seq, None)
+        else:
+            before = c.free_blocks
+            ok = c.allocate(seq, tokens)
+            if ok:
+                want[seq] = max(want.get(seq, 0), tokens)
+            else:
+                assert c.free_blocks == before                     # a refused request changes nothing
+        tables = {s: c.block_table(s) for s in want}
+        used = [b for t in tables.values() for b in t]
+        assert len(used) == len(set(used)) and all(0 <= b < blocks for b in used)            # no block is shared
+        assert c.free_blocks + len(used) == blocks                                            # none is lost
+        assert all(len(tables[s]) == (want[s] + bs - 1) // bs for s in want) and c.num_sequences() == len(want)
+    for s in list(want):
+        c.free(s)
+    assert c.free_blocks == blocks
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.sampled_from([CompressionType.ONE_BIT, CompressionType.FOUR_BIT, CompressionType.FP8, CompressionType.BF16]),
+       st.integers(1, 12), st.integers(0, 10_000))
+def test_error_feedback_conserves_the_sum_of_what_was_sent(kind, steps, seed):
+    g = torch.Generator().manual_seed(seed)
+    ef = ErrorFeedbackCompression(kind)
+    true = torch.zeros(64, dtype=torch.float64)
+    sent = torch.zeros(64, dtype=torch.float64)
+    for _ in range(steps):
+        x = torch.randn(64, generator=g)
+        true += x.double()
+        sent += ef.compress(x).double()
+    assert torch.allclose(true, sent + ef.residual.double(), atol=1e-4)      # nothing is dropped: it is sent or still owed
