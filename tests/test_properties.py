@@ -79,3 +79,73 @@ def test_error_feedback_conserves_the_sum_of_what_was_sent(kind, steps, seed):
         true += x.double()
         sent += ef.compress(x).double()
     assert torch.allclose(true, sent + ef.residual.double(), atol=1e-4)      # nothing is dropped: it is sent or still owed
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(0, 60), st.integers(1, 9), st.booleans(), st.booleans(), st.integers(0, 5))
+def test_a_loader_epoch_visits_every_item_once(n, batch, shuffle, drop_last, seed):
+    from rustral_b200.data.datasets import DataLoader, DataLoaderConfig, InMemoryDataset
+    items = list(range(n))
+    mk = lambda: DataLoader(InMemoryDataset(items), DataLoaderConfig(batch, shuffle, seed, 0, drop_last))
+    loader = mk()
+    epochs = [[b for b in loader] for _ in range(3)]
+    for batches in epochs:
+        flat = [x for b in batches for x in b]
+        kept = n - n % batch if drop_last else n
+        assert len(flat) == kept and len(set(flat)) == kept and set(flat) <= set(items)
+        assert all(len(b) == batch for b in batches[:-1]) and (not batches or 0 < len(batches[-1]) <= batch)
+        assert len(batches) == loader.num_batches()
+        if not shuffle:
+            assert flat == items[:kept]
+    assert [[b for b in mk()] for _ in range(1)][0] == epochs[0]                  # same seed, same first epoch
+    if shuffle and n >= 8 and not drop_last:
+        orders = [[x for b in e for x in b] for e in epochs]
+        assert orders[0] != orders[1] or orders[1] != orders[2]                  # reshuffled between epochs
+
+
+@settings(max_examples=50, deadline=None)
+@given(st.lists(st.lists(st.sampled_from(["alpha", "Beta", "gamma", "delta", "x", "y1", "Zed"]), min_size=0, max_size=8), min_size=1, max_size=8),
+       st.integers(0, 9))
+def test_word_tokenizer_round_trips_known_words_and_honours_the_vocabulary_cap(docs, cap):
+    import os
+    import tempfile
+    from rustral_b200.data.tokenizer import WordLevelConfig, WordLevelTokenizer
+    texts = [" ".join(d) for d in docs]
+    tok = WordLevelTokenizer.fit_from_iter(texts, WordLevelConfig(lowercase=True, max_vocab=cap))
+    v = tok.vocab
+    assert len(v.tokens) >= 4 and len(set(v.tokens[:4])) == 4 and [v.pad_id, v.unk_id, v.bos_id, v.eos_id] == [0, 1, 2, 3]
+    if cap:
+        assert len(v) <= max(cap, 4)
+    words = sorted({w.lower() for d in docs for w in d})
+    if cap == 0:
+        assert set(v.tokens[4:]) == set(words)
+        for t in texts:
+            assert tok.decode(tok.encode(t)) == " ".join(t.lower().split())
+    for t in texts:
+        ids = tok.encode_with_specials(t)
+        assert ids[0] == v.bos_id and ids[-1] == v.eos_id and all(0 <= i < len(v) for i in ids)
+        assert tok.decode(ids) == tok.decode(tok.encode(t))                        # specials are dropped by decode
+    assert tok.encode("neverseenword") == [v.unk_id]
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "vocab.txt")
+        tok.save_vocab(path)
+        again = WordLevelTokenizer.from_vocab_file(path)
+        assert again.vocab.tokens == v.tokens and all(again.encode(t) == tok.encode(t) for t in texts)
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 12), st.integers(2, 8), st.integers(0, 1000), st.booleans())
+def test_top_k_routing_invariants(tokens, experts, seed, renorm):
+    from rustral_b200.ops import moe
+    k = min(2, experts)
+    logits = torch.randn(tokens, experts, generator=torch.Generator().manual_seed(seed))
+    idx, w, probs = moe.route(logits, k, renorm)
+    assert idx.shape == (tokens, k) and torch.allclose(probs.sum(-1), torch.ones(tokens), atol=1e-6)
+    assert all(len(set(row)) == k for row in idx.tolist())                         # distinct experts per token
+    top = probs.topk(k, -1).values
+    picked = probs.gather(1, idx.long())
+    assert torch.allclose(picked, top, atol=1e-7)                                   # the k most probable ones, in order
+    if renorm:
+        assert torch.allclose(w.sum(-1), torch.ones(tokens), atol=1e-6)
+    else:
+        assert torch.allclose(w, picked, atol=1e-7)
