@@ -33,9 +33,18 @@ class PipelineConfig:
 class StageSplitter:
     @staticmethod
     def split_by_count(num_layers: int, num_stages: int) -> list:
-        """Contiguous ranges of ceil(L / S) layers per stage (pipeline_parallel.rs:163-179)."""
-        per = (num_layers + num_stages - 1) // num_stages
-        return [list(range(s * per, min(num_layers, (s + 1) * per))) for s in range(num_stages)]
+        """Contiguous ranges whose sizes differ by at most one, the larger ones first.  (The reference gives every stage
+        ceil(L / S) layers, pipeline_parallel.rs:163-179, which leaves the last stage empty for 5 layers on 4 stages; an
+        idle stage is an idle GPU.  The two rules agree whenever S divides L.)"""
+        if num_stages <= 0:
+            raise DistributedError("num_stages must be positive")
+        base, extra = divmod(num_layers, num_stages)
+        out, start = [], 0
+        for s in range(num_stages):
+            n = base + (1 if s < extra else 0)
+            out.append(list(range(start, start + n)))
+            start += n
+        return out
 
     @staticmethod
     def balance_by_params(param_counts: list, num_stages: int) -> list:
@@ -46,7 +55,9 @@ class StageSplitter:
         remaining_stages = num_stages
         for i, n in enumerate(param_counts):
             layers_left = len(param_counts) - i
-            if cur and acc + n / 2 > target and remaining_stages > 1 and layers_left >= remaining_stages - 1:
+            # cut when the stage is full, or when every layer that is left is needed to give the later stages one each
+            full = acc + n / 2 > target and layers_left >= remaining_stages - 1
+            if cur and remaining_stages > 1 and (full or layers_left == remaining_stages - 1):
                 stages.append(cur)
                 remaining_stages -= 1
                 cur, acc = [], 0.0

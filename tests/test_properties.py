@@ -149,3 +149,25 @@ def test_top_k_routing_invariants(tokens, experts, seed, renorm):
         assert torch.allclose(w.sum(-1), torch.ones(tokens), atol=1e-6)
     else:
         assert torch.allclose(w, picked, atol=1e-7)
+
+
+@settings(max_examples=80, deadline=None)
+@given(st.integers(0, 40), st.integers(1, 9))
+def test_stage_splitting_covers_every_layer_once_and_leaves_no_stage_idle_when_it_need_not(layers, stages):
+    from rustral_b200.parallel.pipeline_parallel import StageSplitter
+    parts = StageSplitter.split_by_count(layers, stages)
+    assert len(parts) == stages and [i for p in parts for i in p] == list(range(layers))         # contiguous cover
+    sizes = [len(p) for p in parts]
+    assert max(sizes) - min(sizes) <= 1 and sizes == sorted(sizes, reverse=True)
+    if layers >= stages:
+        assert min(sizes) >= 1
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.lists(st.integers(1, 1000), min_size=1, max_size=24), st.integers(1, 6))
+def test_parameter_balanced_splitting_is_a_contiguous_cover(counts, stages):
+    from rustral_b200.parallel.pipeline_parallel import StageSplitter
+    parts = StageSplitter.balance_by_params(counts, stages)
+    assert len(parts) == stages and [i for p in parts for i in p] == list(range(len(counts)))
+    if len(counts) >= stages:
+        assert all(parts[s] for s in range(stages))          # no empty stage when there are enough layers
