@@ -319,3 +319,195 @@ def test_checkpoint_manager_wraps_layers_and_memory_stats_show_the_saving():
     per_layer = 8 * 1024 * (8 * 768 + 2 * 3072) * 2
     assert m.without_bytes == 12 * per_layer and m.with_bytes < m.without_bytes and 0.3 < m.savings < 0.5
     assert MemoryStats.calculate(12, 8, 1024, 768, 3072, every_n=100).with_bytes > m.with_bytes   # fewer checkpoints keep more
+
+
+# ------------------------------------------------------------------------------------------------------ memory profiler
+def test_memory_profiler_tracks_allocations_by_tag_and_grades_the_oom_risk():
+    from rustral_b200.core.memory_profiler import AllocationEvent, AllocationTracker, MemoryProfiler, OOMRisk, OomRisk, global_profiler
+    p = MemoryProfiler(capacity_bytes=1000)
+    h1 = p.alloc("weights", 300)
+    h2 = p.alloc("activations", 300)
+    assert (p.current, p.peak, p.by_tag["weights"]) == (600, 600, 300)
+    assert p.predict_oom_risk() == OOMRisk.MEDIUM and p.predict_oom_risk(200) == OOMRisk.HIGH and p.predict_oom_risk(400) == OOMRisk.CRITICAL
+    assert OomRisk(p.predict_oom_risk()) is OomRisk.MEDIUM
+    p.free(h2)
+    p.free(h2)                                                            # a second free of the same handle changes nothing
+    assert (p.current, p.peak) == (300, 600) and p.predict_oom_risk() == OOMRisk.LOW
+    assert [(e.kind, e.tag, e.nbytes) for e in p.events] == [("alloc", "weights", 300), ("alloc", "activations", 300), ("free", "activations", 300)]
+    assert all(isinstance(e, AllocationEvent) for e in p.events)
+    assert [(h, tag, n) for h, tag, n in p.find_leaks()] == [(h1, "weights", 300)] and p.find_leaks(older_than_s=3600) == []
+    with AllocationTracker(p, "scratch", 50) as t:
+        assert p.current == 350 and t.h
+    assert p.current == 300 and t.h == 0
+    t.release()                                                           # idempotent
+    assert p.current == 300
+    tr = p.track_tensor("batch", torch.zeros(4, 4))
+    assert p.by_tag["batch"] == 64
+    tr.release()
+    assert p.by_tag["batch"] == 0
+    assert '"tag": "scratch"' in p.export_timeline()
+    assert global_profiler() is global_profiler()
+
+
+# ------------------------------------------------------------------------------------------------------------ dashboard
+def test_sparkline_and_progress_bar_render_fixed_width_text():
+    from rustral_b200.utils.tui import progress_bar, sparkline
+    assert sparkline([]) == "" and sparkline([float("nan"), None]) == ""
+    s = sparkline([0, 1, 2, 3], width=40)
+    assert len(s) == 4 and s[0] == "▁" and s[-1] == "█" and list(s) == sorted(s)
+    assert len(sparkline(range(100), width=10)) == 10 and set(sparkline([5, 5, 5])) == {"▁"}
+    assert progress_bar(0, 10, width=10) == "░" * 10 + "   0.0%"
+    assert progress_bar(5, 10, width=10) == "█" * 5 + "░" * 5 + "  50.0%"
+    assert progress_bar(20, 10, width=4) == "████ 100.0%" and progress_bar(1, 0, width=4).endswith("  0.0%")
+
+
+def test_tui_metrics_backend_routes_scalars_into_the_dashboard_by_name():
+    from rustral_b200.metrics import ScalarMetric
+    from rustral_b200.utils.tui import LeakWarning, TrainingDashboard, TuiMetricsBackend
+    be = TuiMetricsBackend()
+    dash = be.dashboard()
+    assert isinstance(dash, TrainingDashboard)
+    be.log_scalar(ScalarMetric("train/loss", 2.5, 7, 0.0))
+    be.log_scalar(ScalarMetric("val_accuracy", 0.75, 8, 0.0))
+    be.log_scalar(ScalarMetric("lr", 3e-4, 9, 0.0))
+    be.log_scalar(ScalarMetric("grad_norm", 1.0, 10, 0.0))               # not a dashboard series: only the step moves
+    assert dash.losses == [2.5] and dash.accuracies == [0.75] and dash.step == 10
+    be.log_scalar(ScalarMetric("loss", float("inf"), 11, 0.0))
+    assert len(dash.losses) == 2
+    shared = TrainingDashboard("shared")
+    assert TuiMetricsBackend(shared).dashboard() is shared
+    w = LeakWarning("kv", 1 << 20, 12.0)
+    assert (w.tag, w.nbytes, w.allocation_count) == ("kv", 1 << 20, 1)
+
+
+# ---------------------------------------------------------------------------------------------------- context parallel
+def test_sequence_sharding_and_context_parallel_bookkeeping():
+    from rustral_b200.parallel.process_group import DistributedError, ProcessGroup
+    from rustral_b200.parallel.sequence_parallel import (CommunicationStats, ContextParallel, ContextParallelConfig, DynamicLoadBalancer,
+                                                         compute_sequence_sharding)
+    assert compute_sequence_sharding(16, 4) == [(0, 4), (4, 8), (8, 12), (12, 16)]
+    cfg = ContextParallelConfig(num_devices=4, sequence_length=32768, block_size=4096)
+    cfg.validate()
+    assert cfg.tokens_per_device() == 8192 and cfg.striped and cfg.causal
+    with pytest.raises(DistributedError, match="divisible"):
+        ContextParallelConfig(num_devices=3, sequence_length=32768).validate()
+    with pytest.raises(DistributedError, match="block_size"):
+        ContextParallelConfig(num_devices=4, sequence_length=4 * 6000, block_size=4096).validate()
+    ContextParallelConfig(num_devices=4, sequence_length=4 * 1000, block_size=4096).validate()     # shorter than one block is fine
+    cp = ContextParallel(ProcessGroup.new_single_process(), ContextParallelConfig(num_devices=1, sequence_length=8, block_size=8))
+    x = torch.arange(16.0).view(1, 8, 2)
+    assert torch.equal(cp.shard_input(x), x)
+    st = cp.communication_stats(kv_heads=8, head_dim=128, batch=2)
+    assert isinstance(st, CommunicationStats) and st.steps == 0 and st.total_bytes == 0 and st.kv_bytes_per_step == 8 * 2 * 8 * 128 * 2 * 2
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(1, 8, 2, 4) for _ in range(3))
+    out = cp.forward(q, k, v)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True).transpose(1, 2)
+    assert torch.allclose(out.float(), ref, atol=1e-5)
+    lb = DynamicLoadBalancer(4, threshold=1.2)
+    assert lb.overloaded() == []
+    for r, t in enumerate((1.0, 1.0, 1.0, 2.0)):
+        lb.report(r, t)
+    assert lb.overloaded() == [3]
+    lb.report(3, 1.1)
+    assert lb.overloaded() == []
+
+
+# ------------------------------------------------------------------------------------------------------ fault tolerance
+def test_fault_records_and_the_in_memory_checkpoint_store():
+    from rustral_b200.parallel.fault_tolerance import (CheckpointStore, FaultStats, MembershipChange, MemoryCheckpointStore, NodeInfo,
+                                                       NodeState)
+    n = NodeInfo(3)
+    assert n.state is NodeState.HEALTHY and n.last_checkpoint == -1 and n.last_heartbeat == 0.0
+    ch = MembershipChange("shrink", [2], new_world_size=3, new_rank=2)
+    assert ch.kind == "shrink" and ch.ranks == [2] and MembershipChange("none").ranks == []
+    assert FaultStats() == FaultStats(0, 0, 0, 0)
+    for m in ("save", "load", "latest"):
+        with pytest.raises(NotImplementedError):
+            getattr(CheckpointStore(), m)(*([0, {}] if m == "save" else [0] if m == "load" else []))
+    store = MemoryCheckpointStore()
+    assert isinstance(store, CheckpointStore) and store.latest() is None
+    state = {"w": torch.ones(2)}
+    store.save(10, state)
+    state["w"].zero_()                                                    # the store keeps its own copy
+    store.save(20, state)
+    assert store.latest() == 20 and torch.equal(store.load(10)["w"], torch.ones(2)) and torch.equal(store.load(20)["w"], torch.zeros(2))
+
+
+# ------------------------------------------------------------------------------------------------------------------ MoE
+def test_top_k_gating_returns_normalised_weights_and_the_load_balance_loss():
+    from rustral_b200.core import CpuBackend, ForwardCtx
+    from rustral_b200.nn.moe import GatingOutput, MoEConfig, MoEOutput, MoEStats, TopKGating
+    cfg = MoEConfig(d_model=8, num_experts=4, expert_dim=16, top_k=2)
+    gate = TopKGating.new(CpuBackend(), cfg, seed=1)
+    torch.manual_seed(0)
+    x = torch.randn(32, 8)
+    g = gate.forward(x, ForwardCtx(CpuBackend()))
+    assert isinstance(g, GatingOutput) and g.indices.shape == (32, 2) and g.weights.shape == (32, 2) and g.probs.shape == (32, 4)
+    logits = x @ gate.gate_proj.tensor.detach().t()
+    probs = torch.softmax(logits, -1)
+    top_p, top_i = probs.topk(2, -1)
+    assert torch.equal(g.indices.long().sort(-1).values, top_i.sort(-1).values)
+    assert torch.allclose(g.probs, probs, atol=1e-6) and torch.allclose(g.weights.sum(-1), torch.ones(32), atol=1e-5)
+    f = torch.bincount(top_i.reshape(-1), minlength=4).float() / 64
+    assert abs(float(g.aux_loss) - float((f * probs.mean(0)).sum() * 4)) < 1e-6
+    assert [n for n, _ in gate.named_parameters()] == ["gate_proj"]
+    out = MoEOutput(torch.zeros(2, 8), torch.tensor(0.5))
+    stats = MoEStats([16, 16, 16, 16], 1.0, 0)
+    assert out.output.shape == (2, 8) and float(out.aux_loss) == 0.5 and sum(stats.tokens_per_expert) == 64 and stats.dropped_tokens == 0
+
+
+# ------------------------------------------------------------------------------------------------------ hub and layers
+def test_hub_url_and_loading_hub_weights_from_the_cache(tmp_path, monkeypatch):
+    from rustral_b200.core import CpuBackend
+    from rustral_b200.nn import Linear
+    from rustral_b200.utils.hf import HfError, download_state_dict, hub_url, load_from_hub, save_state_dict_to_file
+    assert hub_url("org/model") == "https://huggingface.co/org/model/resolve/main/model.safetensors"
+    assert hub_url("org/model", "v2", "config.json") == "https://huggingface.co/org/model/resolve/v2/config.json"
+    monkeypatch.setenv("RUSTRAL_CACHE_DIR", str(tmp_path))
+    monkeypatch.setenv("RUSTRAL_DATASET_OFFLINE", "1")
+    with pytest.raises(HfError) as e:
+        download_state_dict("org/absent")
+    assert e.value.kind == "hub"
+    d = tmp_path / "hf" / "org--model" / "main"
+    d.mkdir(parents=True)
+    lin = Linear.new(CpuBackend(), 4, 3, seed=5) if hasattr(Linear, "new") else Linear(CpuBackend(), 4, 3)
+    names = [n for n, _ in lin.named_parameters()]
+    want = {n: torch.full(tuple(p.tensor.shape), float(i + 1)) for i, (n, p) in enumerate(lin.named_parameters())}
+    save_state_dict_to_file({("model." + k): v for k, v in want.items()} | {"model.unused": torch.zeros(1)}, str(d / "model.safetensors"))
+    assert set(download_state_dict("org/model")) == {"model." + n for n in names} | {"model.unused"}
+    load_from_hub(lin, "org/model", key_map=lambda k: None if k.endswith("unused") else k[len("model."):])
+    for n, p in lin.named_parameters():
+        assert torch.equal(p.tensor.detach(), want[n]), n
+    (d / "model.safetensors").write_bytes(b"not a safetensors file")
+    with pytest.raises(HfError) as e:
+        download_state_dict("org/model")
+    assert e.value.kind == "tensor"
+
+
+def test_positional_encoding_adds_the_sinusoid_table_and_checks_the_length():
+    import math
+    from rustral_b200.core import CpuBackend, ForwardCtx, InvalidArgument
+    from rustral_b200.nn.transformer import PositionalEncoding
+    pe = PositionalEncoding(8, max_len=16)
+    ctx = ForwardCtx(CpuBackend())
+    y = pe.forward(torch.zeros(2, 5, 8), ctx)
+    assert y.shape == (2, 5, 8) and torch.equal(y[0], y[1])
+    for pos in (0, 3):
+        for i in (0, 2):
+            angle = pos / (10000.0 ** (2 * i / 8))
+            assert abs(float(y[0, pos, 2 * i]) - math.sin(angle)) < 1e-6 and abs(float(y[0, pos, 2 * i + 1]) - math.cos(angle)) < 1e-6
+    x = torch.randn(1, 4, 8, requires_grad=True)
+    pe.forward(x, ctx).sum().backward()
+    assert torch.equal(x.grad, torch.ones_like(x))                        # the table is a constant
+    with pytest.raises(InvalidArgument, match="max_len"):
+        pe.forward(torch.zeros(1, 17, 8), ctx)
+
+
+def test_scheduler_records_have_the_documented_fields():
+    from rustral_b200.serve.scheduler import Batch, RequestState, SchedulerStats
+    assert [s.name for s in RequestState] == ["WAITING", "PREFILL", "GENERATING", "PAUSED", "COMPLETED"]
+    b = Batch([1, 2], [[5, 6, 7], [9]], [3, 8], [[0], [1]], [True, False])
+    assert len(b.request_ids) == len(b.input_ids) == len(b.seq_lens) == len(b.block_tables) == len(b.is_prefill) == 2
+    s = SchedulerStats()
+    assert (s.completed, s.preempted, s.admitted, s.total_generated, s.total_latency) == (0, 0, 0, 0, 0.0)
