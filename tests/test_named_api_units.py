@@ -215,7 +215,7 @@ def test_default_backend_can_be_replaced_and_initialises_parameters_from_the_see
         a, b, c = (cpu.normal_parameter("w", (4, 5), s, 0.1) for s in (7, 7, 8))
         assert torch.equal(a.tensor, b.tensor) and not torch.equal(a.tensor, c.tensor) and a.name == "w"
         assert float(cpu.normal_parameter("z", (3,), 1, 0.0).tensor.detach().abs().sum()) == 0.0
-        u = cpu.uniform_parameter("u", (1000,), 2, 0.5).tensor
+        u = cpu.uniform_parameter("u", (1000,), 2, 0.5).tensor.detach()
         assert float(u.min()) >= -0.5 and float(u.max()) <= 0.5 and float(u.std()) > 0.2
         assert torch.equal(cpu.constant_parameter("c", (2, 2), 3.0).tensor, torch.full((2, 2), 3.0))
         assert cpu.parameter_from_vec("v", [1, 2, 3, 4, 5, 6], (2, 3)).tensor.tolist() == [[1, 2, 3], [4, 5, 6]]
@@ -511,3 +511,190 @@ def test_scheduler_records_have_the_documented_fields():
     assert len(b.request_ids) == len(b.input_ids) == len(b.seq_lens) == len(b.block_tables) == len(b.is_prefill) == 2
     s = SchedulerStats()
     assert (s.completed, s.preempted, s.admitted, s.total_generated, s.total_latency) == (0, 0, 0, 0, 0.0)
+
+
+# ------------------------------------------------------------------------------------------------------ MoE primitives
+def _routing_case(T=24, E=4, k=2, seed=0):
+    from rustral_b200.ops import moe as M
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(T, E, generator=g)
+    idx, w, probs = M.route(logits, k, True)
+    return M, logits, idx, w, probs
+
+
+def test_moe_plan_groups_slots_by_expert_on_128_row_segments():
+    M, _, idx, _, _ = _routing_case()
+    pl = M.plan(idx, 4)
+    assert isinstance(pl, M.MoEPlan) and pl.k == 2 and pl.num_experts == 4 and pl.max_rows % 128 == 0
+    assert pl.counts.tolist() == torch.bincount(idx.reshape(-1).long(), minlength=4).tolist() and int(pl.counts.sum()) == 48
+    assert all(int(o) % 128 == 0 for o in pl.offsets) and int(pl.offsets[0]) == 0
+    flat = idx.reshape(-1).long()
+    for s in range(48):                                                   # every slot lands inside its expert's segment
+        e, pos = int(flat[s]), int(pl.slot_pos[s])
+        assert int(pl.offsets[e]) <= pos < int(pl.offsets[e]) + int(pl.counts[e]) and int(pl.row_slot[pos]) == s
+    assert int((pl.row_slot >= 0).sum()) == 48 and len(set(pl.slot_pos.tolist())) == 48
+    ntiles = int(pl.num_tiles)
+    assert ntiles == int(pl.offsets[-1]) // 128 and pl.tile_expert[:ntiles].tolist() == sorted(pl.tile_expert[:ntiles].tolist())
+
+
+def test_grouped_gemm_and_its_gradients_follow_the_per_slot_definition():
+    M, _, idx, _, _ = _routing_case()
+    pl = M.plan(idx, 4)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(24, 8, generator=g)
+    W = torch.randn(4, 6, 8, generator=g)
+    xp = M.gather(x, pl)
+    y = M.grouped_gemm(xp, W, pl)
+    assert y.shape == (pl.max_rows, 6)
+    flat = idx.reshape(-1).long()
+    for s in (0, 7, 23, 47):
+        assert torch.allclose(y[int(pl.slot_pos[s])], x[s // 2] @ W[int(flat[s])].t(), atol=1e-5)
+    back = M.grouped_gemm(y, W, pl, b_mn=True)                           # dgrad form: rows times W[e] itself
+    s = 5
+    assert torch.allclose(back[int(pl.slot_pos[s])], (x[s // 2] @ W[int(flat[s])].t()) @ W[int(flat[s])], atol=1e-4)
+    dyp = torch.zeros(pl.max_rows, 6)
+    dyp[pl.slot_pos.long()] = torch.randn(48, 6, generator=g)
+    dW = M.grouped_wgrad(dyp, xp, pl)
+    ref = torch.zeros(4, 6, 8)
+    for s in range(48):
+        ref[int(flat[s])] += torch.outer(dyp[int(pl.slot_pos[s])], x[s // 2])
+    assert torch.allclose(dW, ref, atol=1e-4)
+    twice = M.grouped_wgrad(dyp, xp, pl, out=dW.clone(), accumulate=True)
+    assert torch.allclose(twice, 2 * ref, atol=1e-4)
+    dy = torch.randn(24, 6, generator=g)
+    dw = M.weight_grad(dy, y, pl)
+    assert dw.shape == (24, 2) and abs(float(dw[3, 1]) - float(dy[3] @ y[int(pl.slot_pos[7])])) < 1e-4
+
+
+@pytest.mark.parametrize("renorm", [True, False])
+def test_route_backward_equals_autograd_through_softmax_top_k_and_the_balance_loss(renorm):
+    from rustral_b200.ops import moe as M
+    T, E, k, scale = 16, 4, 2, 0.3
+    g = torch.Generator().manual_seed(2)
+    logits = torch.randn(T, E, generator=g, requires_grad=True)
+    idx, w, probs = M.route(logits.detach(), k, renorm)
+    dw = torch.randn(T, k, generator=g)
+    counts = torch.bincount(idx.reshape(-1).long(), minlength=E)
+    p = torch.softmax(logits, -1)
+    top = p.gather(1, idx.long())
+    wt = top / top.sum(-1, keepdim=True) if renorm else top
+    assert torch.allclose(wt.detach(), w, atol=1e-6)
+    loss = (wt * dw).sum() + scale * E * ((counts.float() / (T * k)) * p.mean(0)).sum()
+    ref, = torch.autograd.grad(loss, logits)
+    got = M.route_backward(probs, idx, w, dw, counts.to(torch.int32), renorm, scale)
+    assert torch.allclose(got, ref, atol=1e-5)
+
+
+# -------------------------------------------------------------------------------------------------------- data parallel
+def test_bucketize_keeps_order_and_never_splits_a_tensor():
+    from rustral_b200.parallel.data_parallel import bucketize
+    ts = [torch.zeros(n) for n in (10, 10, 30, 5, 100, 1)]
+    b = bucketize(ts, bucket_bytes=100)                                   # 25 floats per bucket
+    assert [[t.numel() for t in bk] for bk in b] == [[10, 10], [30], [5], [100], [1]]
+    assert [t for bk in b for t in bk] == ts or all(x is y for x, y in zip([t for bk in b for t in bk], ts))
+    assert bucketize([]) == [] and len(bucketize(ts)) == 1
+
+
+def test_gradient_accumulator_averages_over_micro_steps_and_ranks():
+    from rustral_b200.parallel.data_parallel import GradientAccumulator, all_reduce_gradients
+    from rustral_b200.parallel.process_group import ProcessGroup
+    acc = GradientAccumulator(ProcessGroup.new_single_process())
+    acc.accumulate({"w": torch.tensor([2.0, 4.0]), "b": torch.tensor([1.0])})
+    acc.accumulate({"w": torch.tensor([4.0, 0.0]), "b": torch.tensor([3.0])})
+    out = acc.all_reduce()
+    assert acc.steps == 2 and out["w"].tolist() == [3.0, 2.0] and out["b"].tolist() == [2.0]
+    acc.reset()
+    assert acc.steps == 0 and acc.acc == {}
+    g = [torch.tensor([1.0, 2.0])]
+    all_reduce_gradients(ProcessGroup.new_single_process(), g)
+    assert g[0].tolist() == [1.0, 2.0]                                    # one rank: the average is the value itself
+    import threading
+    res = [None, None]
+
+    def body(pg):
+        grads = [torch.full((3,), float(pg.rank + 1)), torch.full((2,), 10.0 * (pg.rank + 1))]
+        all_reduce_gradients(pg, grads, average=True, bucket_bytes=8)
+        res[pg.rank] = [t.tolist() for t in grads]
+
+    threads = [threading.Thread(target=body, args=(pg,)) for pg in ProcessGroup.new_threaded(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=30)
+    assert res[0] == res[1] == [[1.5] * 3, [15.0] * 2]
+
+
+# ------------------------------------------------------------------------------------------------------------ 3-D mesh
+def test_3d_config_validates_the_world_size_and_layers_follow_the_pipeline_coordinate():
+    from rustral_b200.parallel.parallelism_3d import Parallel3DConfig
+    from rustral_b200.parallel.process_group import DistributedError
+    c = Parallel3DConfig(dp=2, tp=2, pp=2)
+    assert c.total_gpus() == 8
+    c.validate(8)
+    with pytest.raises(DistributedError):
+        c.validate(4)
+    assert Parallel3DConfig().total_gpus() == 1
+
+
+# -------------------------------------------------------------------------------------------------------- small pieces
+def test_wants_grad_follows_autograd_state():
+    from rustral_b200 import _native as N
+    a, b = torch.zeros(2), torch.zeros(2, requires_grad=True)
+    assert not N.wants_grad(a, None) and N.wants_grad(a, b, None)
+    with torch.no_grad():
+        assert not N.wants_grad(a, b)
+    assert isinstance(N.have_kernels(), bool)
+
+
+def test_safetensors_error_types_and_state_tensor_record():
+    from rustral_b200.io import safetensors_io as st
+    for cls in (st.SafeTensorError, st.ShapeMismatchError, st.MissingTensor):
+        assert issubclass(cls, st.IoError)
+    t = st.StateTensor((2, 2), "F32", torch.zeros(2, 2))
+    assert t.shape == (2, 2) and t.dtype == "F32" and t.data.numel() == 4
+
+
+def test_registry_lookup_and_sst2_record():
+    from rustral_b200.data.corpora import Sst2Example
+    from rustral_b200.utils.model_zoo import Registry, RegistryEntry
+    e = RegistryEntry("gpt2-small", "openai-community/gpt2", "main", "supported", "", "examples/load_gpt2.py")
+    r = Registry("1", [e])
+    assert r.get("gpt2-small") is e and r.get("absent") is None
+    ex = Sst2Example("a fine film", 1)
+    assert (ex.text, ex.label) == ("a fine film", 1)
+
+
+def test_lr_scheduler_base_counts_steps_and_drives_an_attached_optimizer():
+    from rustral_b200.optim.lr_scheduler import LRScheduler
+
+    class Halving(LRScheduler):
+        def get_lr(self, step):
+            return 1.0 / (2 ** step)
+
+    class Opt:
+        lr = 0.0
+
+        def set_lr(self, v):
+            self.lr = v
+
+    s = Halving()
+    assert s.current_lr() == 1.0
+    assert s.step() == 0.5 and s.step() == 0.25 and s.current_lr() == 0.25
+    s.reset()
+    assert s.current_lr() == 1.0 and isinstance(s.name(), str)
+    with pytest.raises(NotImplementedError):
+        LRScheduler().get_lr(0)
+
+
+def test_cpu_forms_of_the_copy_and_cast_helpers():
+    from rustral_b200.ops.elementwise import strided_copy
+    from rustral_b200.ops.optim import cast_f32_to_bf16
+    src = torch.arange(24.0).view(4, 6)[:, 1:4]                           # row pitch 6, width 3
+    dst = torch.zeros(4, 8)[:, 2:5]
+    out = strided_copy(src, dst)
+    assert torch.equal(dst, src) and (out is dst or out is None or torch.equal(out, src))
+    x = torch.tensor([1.0, 1.0 + 2 ** -9, 3.14159, -2.5e-3])
+    y = cast_f32_to_bf16(x)
+    assert y.dtype == torch.bfloat16 and torch.equal(y, x.to(torch.bfloat16))
+    z = torch.empty(4, dtype=torch.bfloat16)
+    assert cast_f32_to_bf16(x, z) is z and torch.equal(z, y)
